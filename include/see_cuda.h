@@ -1,0 +1,113 @@
+/* see_cuda.h — the C ABI of the B200 executor backend (libsee_cuda.so).
+ *
+ * The reference has no C ABI: its executor backends are C++ classes behind
+ * `seeml::update_rt::ExecutorBackend` (reference: runtime/executor/backend.h:82-166),
+ * chosen by `CreateBackend` (reference: runtime/executor/backend.cc:26-60).
+ * Each entry point below is the C spelling of one member of that seam, so a
+ * maintainer's `CudaBackend : ExecutorBackend` adapter is one forwarding line
+ * per method; INTEGRATION.md shows it.  Plain pointers and sizes only.
+ *
+ * Every function returns 0 on success and a nonzero code on failure;
+ * see_cuda_last_error(h) then holds a one-line "<unit>: <message>" diagnostic.
+ * A handle is not thread-safe; use one handle per GPU.  There is no CPU
+ * fallback: with no sm_100 device see_cuda_create fails.
+ */
+#ifndef SEE_CUDA_H_
+#define SEE_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct see_cuda_backend see_cuda_backend;
+
+/* Per-range scalars (reference: runtime/executor/backend.h:56-63, StepParams). */
+typedef struct see_step_params {
+  float lr, beta1, beta2, eps, weight_decay;
+  uint32_t pad;
+  uint64_t step; /* 1-indexed AdamW timestep */
+} see_step_params;
+
+typedef struct see_cuda_counters {
+  uint64_t relaxed_executions; /* reference: backend.h:149-161 */
+  uint64_t fused_dispatches;   /* reference: backend.h:162-165 */
+  uint64_t kernel_launches;
+  uint64_t h2d_bytes, d2h_bytes;
+  uint64_t instructions;
+} see_cuda_counters;
+
+enum { SEE_OK = 0, SEE_ERROR = 1, SEE_REFUSED = 2 };
+enum { SEE_COHERENCE_STRICT = 0, SEE_COHERENCE_LAZY = 1 };
+
+/* CreateBackend(kCuda) — reference: runtime/executor/backend.cc:26-60.  On
+ * failure *out is NULL and see_cuda_create_error() names the reason. */
+int see_cuda_create(int device_ordinal, see_cuda_backend** out);
+const char* see_cuda_create_error(void);
+void see_cuda_destroy(see_cuda_backend* h);
+
+/* name() / device() — reference: backend.h:86-87. */
+const char* see_cuda_name(see_cuda_backend* h);
+const char* see_cuda_device(see_cuda_backend* h);
+const char* see_cuda_last_error(see_cuda_backend* h);
+
+/* Bind — reference: backend.h:89-101.  `arena` stays the caller's; the device
+ * slab is a mirror at the same offsets.  A refused bind keeps the previous one. */
+int see_cuda_bind(see_cuda_backend* h, uint8_t* arena, uint64_t arena_bytes,
+                  const uint8_t* rodata, uint64_t rodata_bytes);
+/* BindSource — reference: backend.h:103-109.  NULL unbinds. */
+int see_cuda_bind_source(see_cuda_backend* h, const uint8_t* data, uint64_t bytes);
+
+/* BeginRange / Execute / EndRange / Flush — reference: backend.h:119-147.
+ * `instructions` points at 64-byte instruction words (the plan's own bytes). */
+int see_cuda_begin_range(see_cuda_backend* h, const void* instructions, uint64_t count,
+                         uint64_t begin, uint64_t end);
+int see_cuda_execute(see_cuda_backend* h, const void* instruction, const see_step_params* params);
+int see_cuda_end_range(see_cuda_backend* h);
+int see_cuda_flush(see_cuda_backend* h);
+
+/* Convenience over the three calls above: BeginRange, Execute each of
+ * [begin, end), Flush, EndRange — the engine's ExecuteRange (reference:
+ * runtime/dispatcher/update_engine.cc:325-364).  On an Execute failure
+ * *failed_index (if not NULL) is the instruction's index. */
+int see_cuda_run_range(see_cuda_backend* h, const void* instructions, uint64_t count,
+                       uint64_t begin, uint64_t end, const see_step_params* params,
+                       uint64_t* failed_index);
+
+/* Coherence between the caller's host arena and the device slab (the seam's
+ * "after Flush the arena is readable by the CPU", backend.h:144-147, made
+ * explicit for discrete memory).  Strict (default): Flush downloads every
+ * range written since the previous Flush.  Lazy: only see_cuda_host_needs
+ * downloads.  The host announces its own writes in either mode. */
+int see_cuda_set_coherence(see_cuda_backend* h, int mode);
+int see_cuda_host_wrote(see_cuda_backend* h, uint64_t offset, uint64_t bytes);
+int see_cuda_host_needs(see_cuda_backend* h, uint64_t offset, uint64_t bytes);
+
+int see_cuda_counters_get(see_cuda_backend* h, see_cuda_counters* out);
+
+/* Knobs with no counterpart in the reference seam. */
+int see_cuda_set_stream(see_cuda_backend* h, void* cuda_stream);     /* run on the caller's stream */
+void* see_cuda_device_arena(see_cuda_backend* h);                      /* device address of offset 0 */
+int see_cuda_set_relaxed_allowed(see_cuda_backend* h, int allowed);  /* 0: always the exact kernels */
+/* Data parallelism: optimizer steps read gradients inside [block_offset,
+ * block_offset + block_bytes) as the rank-ordered sum of `ranks` gathered
+ * copies (device memory, copy r at gathered + r * block_bytes) times 1/ranks. */
+int see_cuda_set_gradient_gather(see_cuda_backend* h, int ranks, const void* gathered_device,
+                                 uint64_t block_offset, uint64_t block_bytes);
+/* Profile mode: CUDA-event pairs around every instruction (the profiler hook,
+ * reference: runtime/profiler/kernel_profile.h:25-72).  take_profile fills up
+ * to `capacity` records {opcode, index, ms, m, n, k} and returns the count. */
+typedef struct see_profile_record {
+  uint16_t opcode; uint16_t pad; uint32_t index; float ms; uint32_t pad2;
+  uint64_t m, n, k;
+} see_profile_record;
+int see_cuda_set_profiling(see_cuda_backend* h, int on);
+int64_t see_cuda_take_profile(see_cuda_backend* h, see_profile_record* out, uint64_t capacity);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SEE_CUDA_H_ */

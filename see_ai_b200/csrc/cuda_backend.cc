@@ -1,0 +1,671 @@
+#include "cuda_backend.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+#include "umma_gemm.h"
+
+namespace see {
+
+namespace {
+
+constexpr int kScalarSlots = 64;
+
+std::string CudaErr(cudaError_t e, const char* what) {
+  return std::string("cuda: ") + what + ": " + cudaGetErrorString(e);
+}
+
+void MergeExtent(std::vector<std::pair<uint64_t, uint64_t>>* list, uint64_t off, uint64_t bytes) {
+  if (bytes == 0) return;
+  for (auto& r : *list) {
+    if (off <= r.first + r.second && r.first <= off + bytes) {  // overlap or touch
+      const uint64_t b = std::min(off, r.first);
+      const uint64_t e = std::max(off + bytes, r.first + r.second);
+      r = {b, e - b};
+      return;
+    }
+  }
+  list->push_back({off, bytes});
+}
+
+}  // namespace
+
+struct CudaBackend::UmmaState {
+  umma::Context ctx;
+};
+
+CudaBackend::CudaBackend(int device) : device_(device) {}
+
+std::expected<std::unique_ptr<CudaBackend>, std::string> CudaBackend::Create(int device_ordinal) {
+  std::unique_ptr<CudaBackend> b(new CudaBackend(device_ordinal));
+  if (auto r = b->Init(); !r) return std::unexpected(r.error());
+  return b;
+}
+
+Status CudaBackend::Check(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return {};
+  return std::unexpected(CudaErr(e, what));
+}
+
+Status CudaBackend::Init() {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
+    return std::unexpected("cuda: no CUDA device is visible — this backend has no CPU fallback");
+  if (device_ < 0 || device_ >= count)
+    return std::unexpected("cuda: device ordinal " + std::to_string(device_) + " out of range");
+  if (auto r = Check(cudaSetDevice(device_), "cudaSetDevice"); !r) return r;
+  cudaDeviceProp prop{};
+  if (auto r = Check(cudaGetDeviceProperties(&prop, device_), "cudaGetDeviceProperties"); !r)
+    return r;
+  if (prop.major != 10)
+    return std::unexpected(std::string("cuda: device '") + prop.name +
+                           "' is not compute capability 10.x; the kernels are built for sm_100a only");
+  device_label_ = std::string(prop.name) + " (sm_" + std::to_string(prop.major) +
+                  std::to_string(prop.minor) + ", " + std::to_string(prop.multiProcessorCount) +
+                  " SMs), relaxed GEMMs on tcgen05 bf16 tensor cores";
+  if (auto r = Check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "stream"); !r)
+    return r;
+  own_stream_ = true;
+  void* p = nullptr;
+  const size_t scratch_bytes = 4096 + 256 * sizeof(double);
+  if (auto r = Check(cudaMalloc(&p, scratch_bytes), "scratch"); !r) return r;
+  if (auto r = Check(cudaMemset(p, 0, scratch_bytes), "scratch memset"); !r) return r;
+  uint8_t* base = static_cast<uint8_t*>(p);
+  d_status_ = reinterpret_cast<k::DeviceStatus*>(base);
+  d_sq_ = reinterpret_cast<double*>(base + 64);
+  d_clip_scale_ = reinterpret_cast<float*>(base + 128);
+  d_count_ = reinterpret_cast<unsigned long long*>(base + 192);
+  d_scalars_ = reinterpret_cast<k::AdamScalars*>(base + 256);
+  d_partials_ = reinterpret_cast<double*>(base + 4096);
+  if (auto r = Check(cudaMallocHost(reinterpret_cast<void**>(&h_scalars_),
+                                    kScalarSlots * sizeof(k::AdamScalars)), "pinned scalars"); !r)
+    return r;
+  if (auto r = Check(cudaMallocHost(reinterpret_cast<void**>(&h_status_), 64), "pinned status"); !r)
+    return r;
+  std::memset(h_status_, 0, 64);
+  umma_ = std::make_unique<UmmaState>();
+  if (std::string e = umma::Init(&umma_->ctx, device_); !e.empty()) return std::unexpected(e);
+  return {};
+}
+
+CudaBackend::~CudaBackend() {
+  cudaSetDevice(device_);
+  if (stream_) cudaStreamSynchronize(stream_);
+  for (auto& ev : events_) { cudaEventDestroy(ev.first); cudaEventDestroy(ev.second); }
+  if (umma_) umma::Destroy(&umma_->ctx);
+  cudaFree(d_arena_);
+  cudaFree(d_rodata_);
+  cudaFree(d_source_);
+  cudaFree(d_status_);  // base of the scratch block
+  cudaFree(d_rows_);
+  cudaFree(d_gsum_);
+  if (h_scalars_) cudaFreeHost(h_scalars_);
+  if (h_status_) cudaFreeHost(h_status_);
+  if (own_stream_ && stream_) cudaStreamDestroy(stream_);
+}
+
+Status CudaBackend::Bind(uint8_t* arena, uint64_t arena_bytes, const uint8_t* rodata,
+                         uint64_t rodata_bytes, uint64_t /*rodata_mapped_bytes*/) {
+  if (!arena || arena_bytes == 0) return std::unexpected("cuda: bind: empty arena");
+  cudaSetDevice(device_);
+  // Allocate the new binding first; only when everything succeeded is the old
+  // one released, so a refused Bind leaves the previous plan executable.
+  void* new_arena = nullptr;
+  void* new_rodata = nullptr;
+  if (auto e = cudaMalloc(&new_arena, arena_bytes); e != cudaSuccess)
+    return std::unexpected(CudaErr(e, "bind: arena slab"));
+  if (rodata_bytes) {
+    if (auto e = cudaMalloc(&new_rodata, rodata_bytes + 64); e != cudaSuccess) {
+      cudaFree(new_arena);
+      return std::unexpected(CudaErr(e, "bind: rodata"));
+    }
+    if (auto e = cudaMemcpyAsync(new_rodata, rodata, rodata_bytes, cudaMemcpyHostToDevice, stream_);
+        e != cudaSuccess) {
+      cudaFree(new_arena); cudaFree(new_rodata);
+      return std::unexpected(CudaErr(e, "bind: rodata upload"));
+    }
+  }
+  if (auto e = cudaMemcpyAsync(new_arena, arena, arena_bytes, cudaMemcpyHostToDevice, stream_);
+      e != cudaSuccess) {
+    cudaFree(new_arena); cudaFree(new_rodata);
+    return std::unexpected(CudaErr(e, "bind: arena upload"));
+  }
+  if (auto e = cudaStreamSynchronize(stream_); e != cudaSuccess) {
+    cudaFree(new_arena); cudaFree(new_rodata);
+    return std::unexpected(CudaErr(e, "bind: sync"));
+  }
+  cudaFree(d_arena_);
+  cudaFree(d_rodata_);
+  d_arena_ = static_cast<uint8_t*>(new_arena);
+  d_rodata_ = static_cast<uint8_t*>(new_rodata);
+  host_arena_ = arena;
+  arena_bytes_ = arena_bytes;
+  rodata_bytes_ = rodata_bytes;
+  counters_.h2d_bytes += arena_bytes + rodata_bytes;
+  host_dirty_.clear();
+  device_dirty_.clear();
+  deferred_error_.clear();
+  scalars_valid_ = false;
+  umma::InvalidateAll(&umma_->ctx);
+  return {};
+}
+
+Status CudaBackend::BindSource(const uint8_t* data, uint64_t bytes) {
+  cudaSetDevice(device_);
+  cudaStreamSynchronize(stream_);
+  cudaFree(d_source_);
+  d_source_ = nullptr;
+  source_bytes_ = 0;
+  if (!data || bytes == 0) return {};
+  void* p = nullptr;
+  if (auto r = Check(cudaMalloc(&p, bytes), "bind source"); !r) return r;
+  if (auto r = Check(cudaMemcpy(p, data, bytes, cudaMemcpyHostToDevice), "source upload"); !r) {
+    cudaFree(p);
+    return r;
+  }
+  d_source_ = static_cast<uint8_t*>(p);
+  source_bytes_ = bytes;
+  counters_.h2d_bytes += bytes;
+  return {};
+}
+
+void CudaBackend::HostWrote(uint64_t off, uint64_t bytes) {
+  if (off >= arena_bytes_) return;
+  bytes = std::min(bytes, arena_bytes_ - off);
+  MergeExtent(&host_dirty_, off, bytes);
+}
+
+Status CudaBackend::UploadDirty() {
+  for (const auto& [off, bytes] : host_dirty_) {
+    if (auto r = Check(cudaMemcpyAsync(d_arena_ + off, host_arena_ + off, bytes,
+                                       cudaMemcpyHostToDevice, stream_), "upload"); !r)
+      return r;
+    counters_.h2d_bytes += bytes;
+  }
+  host_dirty_.clear();
+  return {};
+}
+
+Status CudaBackend::HostNeeds(uint64_t off, uint64_t bytes) {
+  if (!d_arena_) return std::unexpected("cuda: nothing is bound");
+  if (off > arena_bytes_ || bytes > arena_bytes_ - off)
+    return std::unexpected("cuda: host_needs: range outside the arena");
+  cudaSetDevice(device_);
+  if (auto r = Check(cudaMemcpyAsync(host_arena_ + off, d_arena_ + off, bytes,
+                                     cudaMemcpyDeviceToHost, stream_), "download"); !r)
+    return r;
+  counters_.d2h_bytes += bytes;
+  return Check(cudaStreamSynchronize(stream_), "download sync");
+}
+
+void CudaBackend::SetGradientGather(int ranks, const void* gathered, uint64_t block_off,
+                                    uint64_t block_bytes) {
+  gather_ranks_ = ranks > 1 ? ranks : 1;
+  d_gathered_ = ranks > 1 ? static_cast<const uint8_t*>(gathered) : nullptr;
+  gather_off_ = block_off;
+  gather_bytes_ = block_bytes;
+}
+
+void CudaBackend::SetProfiling(bool on) { profiling_ = on; }
+
+std::vector<ProfileRecord> CudaBackend::TakeProfile() {
+  cudaSetDevice(device_);
+  cudaStreamSynchronize(stream_);
+  for (size_t i = 0; i < pending_profile_.size(); ++i) {
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, events_[i].first, events_[i].second);
+    pending_profile_[i].ms = ms;
+  }
+  std::vector<ProfileRecord> out;
+  out.swap(pending_profile_);
+  return out;
+}
+
+Status CudaBackend::EnsureScratch(uint64_t row_doubles) {
+  if (row_doubles <= rows_capacity_) return {};
+  // Growing scratch replaces the buffer: drain the stream first so no queued
+  // kernel still reads the old one.
+  if (auto r = Check(cudaStreamSynchronize(stream_), "scratch sync"); !r) return r;
+  cudaFree(d_rows_);
+  d_rows_ = nullptr;
+  rows_capacity_ = 0;
+  void* p = nullptr;
+  if (auto r = Check(cudaMalloc(&p, row_doubles * sizeof(double)), "row scratch"); !r) return r;
+  d_rows_ = static_cast<double*>(p);
+  rows_capacity_ = row_doubles;
+  return {};
+}
+
+void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin, size_t end) {
+  // Size every scratch buffer the range needs up front, so no allocation (and
+  // no stream drain) happens between its instructions.
+  uint64_t rows = 0, gsum = 0;
+  for (size_t i = begin; i < end && i < program.size(); ++i) {
+    const Instruction& ins = program[i];
+    switch (ins.opcode) {
+      case kSoftmaxXEntFwd: case kSoftmaxXEntMaskedFwd: rows = std::max(rows, ins.out[0]); break;
+      case kKLDistillFwd: rows = std::max(rows, Hi32(ins.out[1])); break;
+      case kMseFwd: rows = std::max<uint64_t>(rows, 256); break;
+      case kAdamWStep: case kSgdStep:
+        if (gather_ranks_ > 1 && BitsToF32(ins.out[1]) > 0.0f) gsum = std::max(gsum, ins.out[0]);
+        break;
+      default: break;
+    }
+  }
+  if (rows) (void)EnsureScratch(rows);
+  if (gsum > gsum_capacity_) {
+    cudaStreamSynchronize(stream_);
+    cudaFree(d_gsum_);
+    d_gsum_ = nullptr;
+    gsum_capacity_ = 0;
+    void* p = nullptr;
+    if (cudaMalloc(&p, gsum * sizeof(float)) == cudaSuccess) {
+      d_gsum_ = static_cast<float*>(p);
+      gsum_capacity_ = gsum;
+    }
+  }
+  umma::PlanRange(&umma_->ctx, program.data(), begin, std::min(end, program.size()));
+  range_index_ = 0;
+}
+
+void CudaBackend::EndRange() {}
+
+Status CudaBackend::Flush() {
+  if (!d_arena_) return {};
+  cudaSetDevice(device_);
+  if (coherence_ == Coherence::kStrict) {
+    for (const auto& [off, bytes] : device_dirty_) {
+      if (auto r = Check(cudaMemcpyAsync(host_arena_ + off, d_arena_ + off, bytes,
+                                         cudaMemcpyDeviceToHost, stream_), "flush download"); !r)
+        return r;
+      counters_.d2h_bytes += bytes;
+    }
+  }
+  device_dirty_.clear();
+  if (auto r = Check(cudaMemcpyAsync(h_status_, d_status_, sizeof(k::DeviceStatus),
+                                     cudaMemcpyDeviceToHost, stream_), "status"); !r)
+    return r;
+  // Completion is an error or a success, never a silent fallback.
+  if (auto r = Check(cudaStreamSynchronize(stream_), "flush: device work did not complete"); !r)
+    return r;
+  if (auto e = cudaGetLastError(); e != cudaSuccess) return std::unexpected(CudaErr(e, "flush"));
+  if (!deferred_error_.empty()) {
+    std::string e;
+    e.swap(deferred_error_);
+    return std::unexpected(e);
+  }
+  if (h_status_[0] || h_status_[1]) {
+    const bool refused = h_status_[0] != 0;
+    cudaMemsetAsync(d_status_, 0, sizeof(k::DeviceStatus), stream_);
+    cudaStreamSynchronize(stream_);
+    h_status_[0] = h_status_[1] = 0;
+    return std::unexpected(refused ? std::string(kNonFiniteNormRefusal)
+                                   : std::string("cuda: a bounded device-side wait ran out"));
+  }
+  return {};
+}
+
+Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
+  if (!d_arena_) return std::unexpected("cuda: execute before bind");
+  cudaSetDevice(device_);
+  Extents ext;
+  if (std::string e = DescribeInstruction(ins, arena_bytes_, rodata_bytes_, source_bytes_, &ext);
+      !e.empty())
+    return std::unexpected("cuda: " + e);
+  if (!host_dirty_.empty())
+    if (auto r = UploadDirty(); !r) return r;
+
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  if (profiling_) {
+    const size_t slot = pending_profile_.size();
+    if (slot >= events_.size()) {
+      cudaEvent_t a, b;
+      cudaEventCreate(&a);
+      cudaEventCreate(&b);
+      events_.push_back({a, b});
+    }
+    ev0 = events_[slot].first;
+    ev1 = events_[slot].second;
+    cudaEventRecord(ev0, stream_);
+  }
+
+  if (auto r = Dispatch(ins, params, ext); !r) return r;
+  ++counters_.instructions;
+
+  if (profiling_) {
+    cudaEventRecord(ev1, stream_);
+    ProfileRecord rec{ins.opcode, range_index_, 0.0f, 0, 0, 0};
+    if (ins.opcode <= kGemmAccNN || ins.opcode == kGemmNNQ8 || ins.opcode == kGemmNTQ8 ||
+        ins.opcode == kGemmNNBF16 || ins.opcode == kGemmNTBF16) {
+      rec.m = ins.out[0]; rec.n = ins.out[1]; rec.k = ins.out[2];
+    }
+    pending_profile_.push_back(rec);
+  }
+  ++range_index_;
+
+  for (size_t i = 0; i < ext.count; ++i) {
+    const Extent& e = ext.e[i];
+    if (!e.write) continue;
+    umma::InvalidateRange(&umma_->ctx, e.off, e.bytes);
+    if (coherence_ == Coherence::kStrict) MergeExtent(&device_dirty_, e.off, e.bytes);
+  }
+  if (auto e = cudaPeekAtLastError(); e != cudaSuccess) {
+    cudaGetLastError();
+    return std::unexpected(CudaErr(e, OpName(ins.opcode)));
+  }
+  return {};
+}
+
+Status CudaBackend::DispatchGemm(const Instruction& ins) {
+  k::GemmArgs a;
+  a.A = Rd(ins.in[0]);
+  a.B = Rd<uint8_t>(ins.in[1]);
+  a.C = Wr(ins.in[2]);
+  a.M = ins.out[0]; a.N = ins.out[1]; a.K = ins.out[2];
+  const uint16_t op = ins.opcode;
+  a.b_transposed = op == kGemmNT || op == kGemmNTQ8 || op == kGemmNTBF16;
+  a.a_transposed = op == kGemmTN;
+  a.b_type = (op == kGemmNNQ8 || op == kGemmNTQ8) ? k::BType::kI8
+             : (op == kGemmNNBF16 || op == kGemmNTBF16) ? k::BType::kBf16 : k::BType::kF32;
+  a.act = ActOf(ins.flags);
+  if (ins.flags & kFlagEpilogueBias) a.bias = Rd(ins.in[3]);
+  if (ins.flags & kFlagGemmAddend) a.addend = Rd(ins.in[3]);
+  if (op == kGemmNN || op == kGemmNT || op == kGemmTN) a.alpha = GemmAlphaOf(ins.imm);
+  if (op == kGemmAccNN) { a.alpha = BitsToF32(ins.in[3]); a.accumulate = true; }
+  if (op == kGemmNNQ8 || op == kGemmNTQ8) {
+    if (ins.flags & kFlagQ8ColScale) {
+      if (a.b_transposed) a.a_k_scale = Rd(ins.in[3]); else a.b_col_scale = Rd(ins.in[3]);
+    } else {
+      a.alpha = BitsToF32(ins.in[3]);
+    }
+  }
+  // The relaxed permission: frozen-weight products may run on the bf16 tensor
+  // cores (activation rounded to bf16 once, weight exact, f32 accumulate).
+  if ((ins.flags & kFlagRelaxed) && relaxed_allowed_ && !a.a_transposed && !a.accumulate &&
+      RefSpace(ins.in[1]) != kArena) {
+    int launches = 0;
+    const std::string err = umma::TryGemm(&umma_->ctx, a, RefSpace(ins.in[1]) == kRodata ? 1 : 2,
+                                          RefOffset(ins.in[1]), RefOffset(ins.in[0]),
+                                          a.a_k_scale ? RefOffset(ins.in[3]) : ~0ull, stream_,
+                                          &launches);
+    if (err.empty() && launches > 0) {
+      ++counters_.relaxed_executions;
+      counters_.kernel_launches += launches;
+      return {};
+    }
+    if (!err.empty()) return std::unexpected("cuda: " + err);
+    // launches == 0: the shape is outside the tensor-core kernel's domain.
+  }
+  k::GemmExact(a, stream_);
+  ++counters_.kernel_launches;
+  return {};
+}
+
+Status CudaBackend::DispatchOptimizer(const Instruction& ins, const StepParams& params) {
+  // Per-range scalars, computed with the host libm exactly as the CPU executor
+  // computes them (reference: runtime/executor/optimizer.cc:113-118), uploaded
+  // once per distinct StepParams.
+  if (!scalars_valid_ || std::memcmp(&params, &last_params_, sizeof(StepParams)) != 0) {
+    k::AdamScalars sc{};
+    sc.lr = params.lr; sc.beta1 = params.beta1; sc.beta2 = params.beta2; sc.eps = params.eps;
+    sc.weight_decay = params.weight_decay;
+    sc.inv_bc1 = 1.0f / (1.0f - std::pow(params.beta1, static_cast<float>(params.step)));
+    sc.inv_bc2 = 1.0f / (1.0f - std::pow(params.beta2, static_cast<float>(params.step)));
+    scalar_slot_ = (scalar_slot_ + 1) % kScalarSlots;
+    h_scalars_[scalar_slot_] = sc;
+    if (auto r = Check(cudaMemcpyAsync(d_scalars_, &h_scalars_[scalar_slot_], sizeof(sc),
+                                       cudaMemcpyHostToDevice, stream_), "step scalars"); !r)
+      return r;
+    last_params_ = params;
+    scalars_valid_ = true;
+  }
+  const uint64_t n = ins.out[0];
+  const float clip = BitsToF32(ins.out[1]);
+  const uint64_t g_off = RefOffset(ins.in[1]);
+  const float* g = Rd(ins.in[1]);
+  int copies = 1;
+  size_t cstride = 0;
+  float inv = 1.0f;
+  if (gather_ranks_ > 1 && RefSpace(ins.in[1]) == kArena && g_off >= gather_off_ &&
+      g_off + n * 4 <= gather_off_ + gather_bytes_) {
+    g = reinterpret_cast<const float*>(d_gathered_ + (g_off - gather_off_));
+    copies = gather_ranks_;
+    cstride = gather_bytes_ / 4;
+    inv = 1.0f / static_cast<float>(gather_ranks_);
+  }
+  const float* clip_scale = nullptr;
+  if (clip > 0.0f) {
+    const float* norm_src = g;
+    if (copies > 1) {  // the clip norm is taken on the summed gradient
+      if (n > gsum_capacity_) return std::unexpected("cuda: gradient-sum scratch not sized");
+      k::SumCopies(g, d_gsum_, n, copies, cstride, inv, stream_);
+      norm_src = d_gsum_;
+      ++counters_.kernel_launches;
+    }
+    k::L2Squared(norm_src, n, d_partials_, d_sq_, stream_);
+    k::ClipScaleFromSq(d_sq_, clip, d_clip_scale_, d_status_, stream_);
+    counters_.kernel_launches += 3;
+    clip_scale = d_clip_scale_;
+  }
+  if (ins.opcode == kAdamWStep)
+    k::AdamWStep(Wr(ins.in[0]), g, Wr(ins.in[2]), Wr(ins.in[3]), n, d_scalars_, clip_scale,
+                 d_status_, copies, cstride, inv, stream_);
+  else
+    k::SgdStep(Wr(ins.in[0]), g, n, d_scalars_, clip_scale, d_status_, copies, cstride, inv,
+               stream_);
+  ++counters_.kernel_launches;
+  return {};
+}
+
+Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, const Extents&) {
+  cudaStream_t s = stream_;
+  auto launched = [&](int n = 1) { counters_.kernel_launches += n; };
+  switch (static_cast<Op>(ins.opcode)) {
+    case kNop: break;
+    case kGemmNN: case kGemmNT: case kGemmTN: case kGemmAccNN: case kGemmNNQ8: case kGemmNTQ8:
+    case kGemmNNBF16: case kGemmNTBF16:
+      return DispatchGemm(ins);
+    case kAddEW: k::AddEW(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s); launched(); break;
+    case kMulEW: k::MulEW(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s); launched(); break;
+    case kAddBias:
+      k::AddBias(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], ins.out[1], s); launched(); break;
+    case kReluFwd: k::ActFwd(kActRelu, Rd(ins.in[0]), Wr(ins.in[1]), ins.out[0], s); launched(); break;
+    case kGeluFwd: k::ActFwd(kActGelu, Rd(ins.in[0]), Wr(ins.in[1]), ins.out[0], s); launched(); break;
+    case kSiluFwd: k::ActFwd(kActSilu, Rd(ins.in[0]), Wr(ins.in[1]), ins.out[0], s); launched(); break;
+    case kReluBwd: k::ActBwd(kActRelu, Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s); launched(); break;
+    case kGeluBwd: k::ActBwd(kActGelu, Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s); launched(); break;
+    case kSiluBwd: k::ActBwd(kActSilu, Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s); launched(); break;
+    case kScale:
+      k::Scale(Rd(ins.in[0]), Wr(ins.in[1]), BitsToF32(ins.in[2]), ins.out[0], s); launched(); break;
+    case kFill: k::Fill(Wr(ins.in[0]), BitsToF32(ins.in[1]), ins.out[0], s); launched(); break;
+    case kCopy: k::Copy(Rd(ins.in[0]), Wr(ins.in[1]), ins.out[0], s); launched(); break;
+    case kAccumulate: k::Accumulate(Wr(ins.in[0]), Rd(ins.in[1]), ins.out[0], s); launched(); break;
+    case kReduceRows:
+      k::ReduceRows(Rd(ins.in[0]), Wr(ins.in[1]), ins.out[0], ins.out[1], s); launched(); break;
+    case kFusedMap:
+      k::FusedMap(Rd(ins.in[0]), ins.in[1] == kNullRef ? nullptr : Rd(ins.in[1]),
+                  ins.in[2] == kNullRef ? nullptr : Rd(ins.in[2]), Wr(ins.in[3]), ins.out[0],
+                  static_cast<uint32_t>(ins.out[1]), BitsToF32(ins.out[2]),
+                  BitsToF32(ins.out[2] >> 32), s);
+      launched();
+      break;
+    case kEmbedFwd:
+      k::EmbedFwd(Rd<int32_t>(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0],
+                  Lo32(ins.out[1]), Hi32(ins.out[1]), s);
+      launched();
+      break;
+    case kLayerNormFwd:
+      k::LayerNormFwd(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Wr(ins.in[3]), Wr(ins.out[1]),
+                      Wr(ins.out[2]), Hi32(ins.out[0]), Lo32(ins.out[0]), NormEpsOf(ins.imm), s);
+      launched();
+      break;
+    case kLayerNormBwd:
+      k::LayerNormBwd(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Rd(ins.out[0]), Rd(ins.out[1]),
+                      Wr(ins.in[3]), Hi32(ins.out[2]), Lo32(ins.out[2]), s);
+      launched();
+      break;
+    case kRmsNormFwd:
+      k::RmsNormFwd(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), Wr(ins.in[3]), Hi32(ins.out[0]),
+                    Lo32(ins.out[0]), NormEpsOf(ins.imm), s);
+      launched();
+      break;
+    case kRmsNormBwd:
+      k::RmsNormBwd(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Rd(ins.out[0]), Wr(ins.in[3]),
+                    Hi32(ins.out[1]), Lo32(ins.out[1]), s);
+      launched();
+      break;
+    case kSoftmaxXEntFwd: case kSoftmaxXEntMaskedFwd:
+      if (auto r = EnsureScratch(ins.out[0]); !r) return r;
+      k::SoftmaxXEntFwd(ins.opcode == kSoftmaxXEntMaskedFwd, Rd(ins.in[0]), Rd<int32_t>(ins.in[1]),
+                        Wr(ins.in[2]), Wr(ins.in[3]), ins.out[0], ins.out[1], d_rows_, d_count_, s);
+      launched(2);
+      break;
+    case kSoftmaxXEntBwd: case kSoftmaxXEntMaskedBwd:
+      k::SoftmaxXEntBwd(ins.opcode == kSoftmaxXEntMaskedBwd, Rd(ins.in[0]), Rd<int32_t>(ins.in[1]),
+                        Rd(ins.in[2]), Wr(ins.in[3]), ins.out[0], ins.out[1], d_count_, s);
+      launched(ins.opcode == kSoftmaxXEntMaskedBwd ? 2 : 1);
+      break;
+    case kMseFwd:
+      if (auto r = EnsureScratch(256); !r) return r;
+      k::MseFwd(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], d_rows_, s);
+      launched(2);
+      break;
+    case kMseBwd:
+      k::MseBwd(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Wr(ins.in[3]), ins.out[0], s);
+      launched();
+      break;
+    case kKLDistillFwd: {
+      const float T = BitsToF32(ins.out[2]);
+      const uint64_t hi = ins.out[2] >> 32;
+      if (!std::isfinite(T) || !(T > 0.0f)) return std::unexpected("cuda: kl.fwd: temperature");
+      if (auto r = EnsureScratch(Hi32(ins.out[1])); !r) return r;
+      k::KLDistillFwd(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), Wr(ins.in[3]), Wr(ins.out[0]),
+                      Hi32(ins.out[1]), Lo32(ins.out[1]), T, hi == 0 ? 1.0f : BitsToF32(hi),
+                      d_rows_, s);
+      launched(2);
+      break;
+    }
+    case kKLDistillBwd: {
+      const float T = BitsToF32(ins.out[1]);
+      const uint64_t hi = ins.out[1] >> 32;
+      if (!std::isfinite(T) || !(T > 0.0f)) return std::unexpected("cuda: kl.bwd: temperature");
+      k::KLDistillBwd(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Wr(ins.in[3]), Hi32(ins.out[0]),
+                      Lo32(ins.out[0]), T, hi == 0 ? 1.0f : BitsToF32(hi), s);
+      launched();
+      break;
+    }
+    case kSgdStep: case kAdamWStep:
+      return DispatchOptimizer(ins, params);
+    case kClipNorm: {
+      const float cap = BitsToF32(ins.in[1]);
+      if (!std::isfinite(cap) || !(cap > 0.0f)) return std::unexpected(kClipThresholdRefusal);
+      k::L2Squared(Rd(ins.in[0]), ins.out[0], d_partials_, d_sq_, s);
+      k::ClipScaleFromSq(d_sq_, cap, d_clip_scale_, d_status_, s);
+      k::ScaleInPlaceBy(Wr(ins.in[0]), ins.out[0], d_clip_scale_, d_status_, s);
+      launched(4);
+      break;
+    }
+    case kSqNormAccum:
+      k::L2Squared(Rd(ins.in[0]), ins.out[0], d_partials_, d_sq_, s);
+      k::SqNormAccum(d_sq_, Wr(ins.in[1]), s);
+      launched(3);
+      break;
+    case kClipGlobal: {
+      const float cap = BitsToF32(ins.in[2]);
+      if (!std::isfinite(cap) || !(cap > 0.0f)) return std::unexpected(kClipThresholdRefusal);
+      k::ClipGlobalScale(Rd(ins.in[1]), cap, d_clip_scale_, d_status_, s);
+      k::ScaleInPlaceBy(Wr(ins.in[0]), ins.out[0], d_clip_scale_, d_status_, s);
+      launched(2);
+      break;
+    }
+    case kRopeTable: {
+      const uint64_t S = Hi32(ins.out[0]), d = Lo32(ins.out[0]);
+      const float step = std::pow(BitsToF32(ins.out[1]), -2.0f / static_cast<float>(d));
+      k::RopeTable(Wr(ins.in[0]), S, d, step, s);
+      launched();
+      break;
+    }
+    case kRopeFwd: case kRopeBwd: {
+      const uint64_t d = Lo32(ins.out[1]);
+      const float step = std::pow(BitsToF32(ins.out[2]), -2.0f / static_cast<float>(d));
+      k::Rope(ins.opcode == kRopeBwd, Rd(ins.in[0]), Wr(ins.in[1]), Hi32(ins.out[0]),
+              Lo32(ins.out[0]), Hi32(ins.out[1]), d, step,
+              ins.in[2] == kNullRef ? nullptr : Rd(ins.in[2]), s);
+      launched();
+      break;
+    }
+    case kSegmentStarts:
+      k::SegmentStarts(Rd<int32_t>(ins.in[0]), Wr<int32_t>(ins.in[1]), Hi32(ins.out[0]),
+                       Lo32(ins.out[0]), static_cast<int32_t>(ins.out[1]), s);
+      launched();
+      break;
+    case kAttnFwd:
+      k::AttnFwd(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Wr(ins.in[3]), Wr(ins.out[0]), nullptr,
+                 Hi32(ins.out[1]), Lo32(ins.out[1]), Hi32(ins.out[2]), Lo32(ins.out[2]), nullptr, s);
+      launched();
+      break;
+    case kAttnFwdSeg: {
+      const AttnGeom g = UnpackAttnGeom(ins.out[1]);
+      k::AttnFwd(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Wr(ins.in[3]), Wr(ins.out[0]), nullptr,
+                 g.B, g.S, g.H, g.d, Rd<int32_t>(ins.out[2]), s);
+      launched();
+      break;
+    }
+    case kAttnFwdTiled:
+      k::AttnFwd(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Wr(ins.in[3]), nullptr, Wr(ins.out[0]),
+                 Hi32(ins.out[1]), Lo32(ins.out[1]), Hi32(ins.out[2]), Lo32(ins.out[2]), nullptr, s);
+      launched();
+      break;
+    case kAttnFwdTiledSeg: {
+      const AttnGeom g = UnpackAttnGeom(ins.out[1]);
+      k::AttnFwd(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Wr(ins.in[3]), nullptr, Wr(ins.out[0]),
+                 g.B, g.S, g.H, g.d, Rd<int32_t>(ins.out[2]), s);
+      launched();
+      break;
+    }
+    case kAttnDP:
+      k::AttnDP(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), Hi32(ins.out[0]), Lo32(ins.out[0]),
+                Hi32(ins.out[1]), Lo32(ins.out[1]), s);
+      launched();
+      break;
+    case kAttnDV:
+      k::AttnDV(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), Hi32(ins.out[0]), Lo32(ins.out[0]),
+                Hi32(ins.out[1]), Lo32(ins.out[1]), s);
+      launched();
+      break;
+    case kSoftmaxRowsBwd:
+      k::SoftmaxRowsBwd(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), Hi32(ins.out[0]),
+                        Lo32(ins.out[0]), s);
+      launched();
+      break;
+    case kAttnDQ:
+      k::AttnDQ(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), Hi32(ins.out[0]), Lo32(ins.out[0]),
+                Hi32(ins.out[1]), Lo32(ins.out[1]), s);
+      launched();
+      break;
+    case kAttnDK:
+      k::AttnDK(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), Hi32(ins.out[0]), Lo32(ins.out[0]),
+                Hi32(ins.out[1]), Lo32(ins.out[1]), s);
+      launched();
+      break;
+    case kAttnDQTiled: case kAttnDKTiled: case kAttnDVTiled: {
+      const AttnGeom g = UnpackAttnGeom(ins.out[2]);
+      if (g.d > 256 && ins.opcode != kAttnDQTiled)
+        return std::unexpected("cuda: tiled attention backward supports head widths up to 256");
+      if (ins.opcode == kAttnDQTiled)
+        k::AttnDQTiled(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Rd(ins.in[3]), Wr(ins.out[0]),
+                       Wr(ins.out[1]), g.B, g.S, g.H, g.d, s);
+      else
+        k::AttnDKVTiled(ins.opcode == kAttnDKTiled, Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]),
+                        Rd(ins.in[3]), Rd(ins.out[0]), Wr(ins.out[1]), g.B, g.S, g.H, g.d, s);
+      launched();
+      break;
+    }
+    case kOpCount:
+      return std::unexpected("cuda: unknown opcode");
+  }
+  return {};
+}
+
+}  // namespace see

@@ -1,0 +1,189 @@
+// CudaBackend — the B200 executor behind the reference's backend seam.  The
+// method set, argument meaning and error behaviour mirror
+// seeml::update_rt::ExecutorBackend (reference: runtime/executor/backend.h:82-166):
+// Bind / BindSource / Configure / Execute / BeginRange / EndRange / Flush,
+// relaxed_executions(), fused_dispatches().  Host-only header (C++23).
+//
+// What differs from a unified-memory backend is coherence.  The compiler's
+// arena lives in ONE cudaMalloc'd slab at the compiler-decided offsets; the
+// caller's host arena is a mirror.  Two modes:
+//   strict (default)  Flush copies every range written since the last Flush
+//                     back into the host arena, so the seam's promise — after
+//                     Flush the arena's bytes are what the instructions
+//                     computed — holds byte for byte.
+//   lazy              nothing is copied back unless asked (HostNeeds); the
+//                     engine asks for the loss slot each step and for the
+//                     persistent prefix or deltas when it checkpoints/merges.
+// In both modes the host announces its own writes (HostWrote) and they are
+// uploaded before the next instruction runs; Bind uploads the whole arena.
+#ifndef SEE_CUDA_BACKEND_H_
+#define SEE_CUDA_BACKEND_H_
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <expected>
+#include <memory>
+#include <span>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "extents.h"
+#include "kernels.h"
+#include "plan_abi.h"
+
+namespace see {
+
+using Status = std::expected<void, std::string>;
+
+// The two refusal verdicts, worded as the reference words them (reference:
+// runtime/executor/backend.h:72-80) so a twin test can compare strings.
+inline constexpr const char* kNonFiniteNormRefusal =
+    "gradient norm is not finite — the step was refused with the parameters "
+    "and optimizer state untouched";
+inline constexpr const char* kClipThresholdRefusal =
+    "clip threshold is not a finite positive float — the instruction was "
+    "refused with the gradient untouched";
+
+enum class Coherence : int { kStrict = 0, kLazy = 1 };
+
+struct Counters {
+  uint64_t relaxed_executions = 0;   // instructions run on the tensor-core (bf16) path
+  uint64_t fused_dispatches = 0;     // instruction pairs run as one launch
+  uint64_t kernel_launches = 0;      // device kernels enqueued since creation
+  uint64_t h2d_bytes = 0, d2h_bytes = 0;
+  uint64_t instructions = 0;
+};
+
+// One timed instruction (profile mode): opcode, index in the range, milliseconds.
+struct ProfileRecord { uint16_t opcode; uint32_t index; float ms; uint64_t m, n, k; };
+
+class CudaBackend {
+ public:
+  static std::expected<std::unique_ptr<CudaBackend>, std::string> Create(int device_ordinal);
+  ~CudaBackend();
+  CudaBackend(const CudaBackend&) = delete;
+  CudaBackend& operator=(const CudaBackend&) = delete;
+
+  const char* name() const { return "cuda"; }
+  std::string device() const { return device_label_; }
+
+  // A refused Bind leaves the previous binding intact and executable.
+  Status Bind(uint8_t* arena, uint64_t arena_bytes, const uint8_t* rodata, uint64_t rodata_bytes,
+              uint64_t rodata_mapped_bytes);
+  Status BindSource(const uint8_t* data, uint64_t bytes);
+  void Configure() {}  // the CPU tile policy is throughput-only on its own backend; ignored here
+
+  Status Execute(const Instruction& ins, const StepParams& params);
+  void BeginRange(std::span<const Instruction> program, size_t begin, size_t end);
+  void EndRange();
+  Status Flush();
+
+  uint64_t relaxed_executions() const { return counters_.relaxed_executions; }
+  uint64_t fused_dispatches() const { return counters_.fused_dispatches; }
+  const Counters& counters() const { return counters_; }
+
+  // ---- coherence ----
+  void SetCoherence(Coherence mode) { coherence_ = mode; }
+  void HostWrote(uint64_t off, uint64_t bytes);
+  Status HostNeeds(uint64_t off, uint64_t bytes);  // synchronous device -> host arena
+
+  // ---- stream / device memory access for the engine and the data-parallel driver ----
+  void SetStream(cudaStream_t s) { stream_ = s; }
+  cudaStream_t stream() const { return stream_; }
+  uint8_t* device_arena() const { return d_arena_; }
+  uint64_t arena_bytes() const { return arena_bytes_; }
+  int device_ordinal() const { return device_; }
+
+  // Data parallelism: optimizer steps whose gradient operand lies inside
+  // [block_off, block_off + block_bytes) of the arena read it instead as the
+  // rank-ordered sum of `ranks` gathered copies at `gathered` (device memory,
+  // copy r at gathered + r * block_bytes), times 1/ranks.  ranks <= 1 clears it.
+  void SetGradientGather(int ranks, const void* gathered, uint64_t block_off, uint64_t block_bytes);
+
+  // Allow / forbid the tensor-core path for instructions carrying the relaxed
+  // permission (default: allowed).  The exact kernels are always a valid
+  // execution of a relaxed instruction.
+  void SetRelaxedAllowed(bool allowed) { relaxed_allowed_ = allowed; }
+
+  // Profile mode: every instruction is bracketed by CUDA events on the stream.
+  void SetProfiling(bool on);
+  std::vector<ProfileRecord> TakeProfile();
+
+ private:
+  explicit CudaBackend(int device);
+  Status Init();
+  Status Check(cudaError_t e, const char* what);
+  Status UploadDirty();
+  Status EnsureScratch(uint64_t row_doubles);
+  Status EnsureBf16(uint64_t a_elems);
+  Status Dispatch(const Instruction& ins, const StepParams& params, const Extents& ext);
+  Status DispatchGemm(const Instruction& ins);
+  Status DispatchOptimizer(const Instruction& ins, const StepParams& params);
+
+  template <typename T = float>
+  const T* Rd(uint64_t ref) const {
+    const uint64_t off = RefOffset(ref);
+    switch (RefSpace(ref)) {
+      case kRodata: return reinterpret_cast<const T*>(d_rodata_ + off);
+      case kSource: return reinterpret_cast<const T*>(d_source_ + off);
+      default: return reinterpret_cast<const T*>(d_arena_ + off);
+    }
+  }
+  template <typename T = float>
+  T* Wr(uint64_t ref) const { return reinterpret_cast<T*>(d_arena_ + RefOffset(ref)); }
+
+  int device_ = 0;
+  std::string device_label_;
+  cudaStream_t stream_ = nullptr;
+  bool own_stream_ = false;
+
+  uint8_t* host_arena_ = nullptr;
+  uint64_t arena_bytes_ = 0;
+  uint8_t* d_arena_ = nullptr;
+  uint8_t* d_rodata_ = nullptr;
+  uint64_t rodata_bytes_ = 0;
+  uint8_t* d_source_ = nullptr;
+  uint64_t source_bytes_ = 0;
+
+  // device scratch
+  k::DeviceStatus* d_status_ = nullptr;
+  double* d_partials_ = nullptr;  // 256 doubles
+  double* d_sq_ = nullptr;
+  float* d_clip_scale_ = nullptr;
+  unsigned long long* d_count_ = nullptr;
+  double* d_rows_ = nullptr;
+  uint64_t rows_capacity_ = 0;
+  float* d_gsum_ = nullptr;       // summed gradient for fused clips under data parallelism
+  uint64_t gsum_capacity_ = 0;
+  k::AdamScalars* d_scalars_ = nullptr;
+  k::AdamScalars* h_scalars_ = nullptr;  // pinned ring
+  int scalar_slot_ = 0;
+  StepParams last_params_{};
+  bool scalars_valid_ = false;
+  int* h_status_ = nullptr;  // pinned mirror of the status words
+
+  Coherence coherence_ = Coherence::kStrict;
+  std::vector<std::pair<uint64_t, uint64_t>> host_dirty_;
+  std::vector<std::pair<uint64_t, uint64_t>> device_dirty_;
+  std::string deferred_error_;
+
+  int gather_ranks_ = 1;
+  const uint8_t* d_gathered_ = nullptr;
+  uint64_t gather_off_ = 0, gather_bytes_ = 0;
+
+  bool relaxed_allowed_ = true;
+  bool profiling_ = false;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> events_;
+  std::vector<ProfileRecord> pending_profile_;
+  uint32_t range_index_ = 0;
+
+  Counters counters_;
+  struct UmmaState;
+  std::unique_ptr<UmmaState> umma_;
+};
+
+}  // namespace see
+
+#endif  // SEE_CUDA_BACKEND_H_

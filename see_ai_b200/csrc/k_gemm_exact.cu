@@ -1,0 +1,234 @@
+// The exact GEMM family on CUDA cores: reproduces the CPU executor's two
+// reduction contracts bit for bit, for f32, int8 and bf16 weights.
+//
+//   quad order (NN, TN, AccNN and their narrow-weight forms; reference:
+//     runtime/executor/gemm.cc:73-187): per element, from c = 0 (or the
+//     existing C for the accumulate form),
+//         c += ((a0*b0 + a1*b1) + a2*b2) + a3*b3
+//     over consecutive k-quads aligned to k = 0, then one term at a time for
+//     the K % 4 tail; alpha (or the per-tensor dequant scale) is multiplied
+//     into each A element first, a per-column scale into each widened B element.
+//   lane order (NT forms; reference: runtime/executor/gemm.cc:346-527): eight
+//     accumulators, product k into lane k mod 8, lanes summed 0..7, the result
+//     times alpha; a reduction-axis scale is multiplied into A first.
+//
+// Epilogue order matches the reference (gemm.cc:536-578): addend `d + s` on
+// the finished sum, then bias, then the activation expression.  Compiled with
+// -fmad=false; no multiply is ever fused into an add.  This family is the
+// parity anchor and the path for skinny (rank-r) products; large
+// frozen-weight products carrying the relaxed permission go to the tensor
+// cores instead.
+#include "kernels.h"
+
+namespace see::k {
+
+namespace {
+
+constexpr float kGeluC = 0.7978845608028654f;
+constexpr float kGeluA = 0.044715f;
+
+__device__ __forceinline__ float ApplyAct(float v, Act act) {
+  switch (act) {
+    case kActRelu: return v > 0.0f ? v : 0.0f;
+    case kActGelu: {
+      const float t = tanhf(kGeluC * (v + kGeluA * v * v * v));
+      return 0.5f * v * (1.0f + t);
+    }
+    case kActSilu: return v * (1.0f / (1.0f + expf(-v)));
+    default: return v;
+  }
+}
+
+template <typename T> __device__ __forceinline__ float Widen(T v);
+template <> __device__ __forceinline__ float Widen<float>(float v) { return v; }
+template <> __device__ __forceinline__ float Widen<int8_t>(int8_t v) { return static_cast<float>(v); }
+template <> __device__ __forceinline__ float Widen<uint16_t>(uint16_t v) {
+  return __uint_as_float(static_cast<uint32_t>(v) << 16);
+}
+
+struct Params {
+  const float* A;
+  const void* B;
+  float* C;
+  size_t M, N, K;
+  float alpha;
+  const float* b_col_scale;
+  const float* a_k_scale;
+  const float* bias;
+  const float* addend;
+  Act act;
+  bool accumulate;
+};
+
+constexpr int BK = 16;
+
+template <bool TA>
+__device__ __forceinline__ float LoadA(const Params& p, size_t m, size_t k) {
+  if (m >= p.M || k >= p.K) return 0.0f;
+  return TA ? p.A[k * p.M + m] : p.A[m * p.K + k];
+}
+template <bool TB, typename BT>
+__device__ __forceinline__ float LoadB(const Params& p, size_t k, size_t n) {
+  if (n >= p.N || k >= p.K) return 0.0f;
+  const BT* B = static_cast<const BT*>(p.B);
+  return Widen<BT>(TB ? B[n * p.K + k] : B[k * p.N + n]);
+}
+
+// ---- quad order: 64x64 tile, 256 threads, 4x4 outputs per thread --------------
+template <bool TA, typename BT>
+__global__ void __launch_bounds__(256) GemmQuadKernel(Params p) {
+  constexpr int BM = 64, BN = 64;
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Bs[BK][BN + 4];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const size_t m0 = static_cast<size_t>(blockIdx.y) * BM, n0 = static_cast<size_t>(blockIdx.x) * BN;
+  float c[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const size_t m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      c[i][j] = (p.accumulate && m < p.M && n < p.N) ? p.C[m * p.N + n] : 0.0f;
+    }
+  for (size_t k0 = 0; k0 < p.K; k0 += BK) {
+    // Stage the tiles; alpha and the column scale are applied here, once per
+    // element, as the reference applies them when an element enters the product.
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int idx = threadIdx.x + t * 256;
+      int mm, kk;
+      if (TA) { kk = idx / BM; mm = idx % BM; } else { mm = idx / BK; kk = idx % BK; }
+      As[kk][mm] = p.alpha * LoadA<TA>(p, m0 + mm, k0 + kk);
+      const int kb = idx / BN, nb = idx % BN;
+      float b = LoadB<false, BT>(p, k0 + kb, n0 + nb);
+      if (p.b_col_scale && n0 + nb < p.N) b = b * p.b_col_scale[n0 + nb];
+      Bs[kb][nb] = b;
+    }
+    __syncthreads();
+    const int kmax = p.K - k0 < static_cast<size_t>(BK) ? static_cast<int>(p.K - k0) : BK;
+    int kk = 0;
+    for (; kk + 4 <= kmax; kk += 4) {
+      float a[4][4], b[4][4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[q][i] = As[kk + q][ty * 4 + i];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[q][j] = Bs[kk + q][tx * 4 + j];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float t = a[0][i] * b[0][j];
+          t = t + a[1][i] * b[1][j];
+          t = t + a[2][i] * b[2][j];
+          t = t + a[3][i] * b[3][j];
+          c[i][j] = c[i][j] + t;
+        }
+    }
+    for (; kk < kmax; ++kk) {  // the K % 4 tail, one term at a time
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          c[i][j] = c[i][j] + As[kk][ty * 4 + i] * Bs[kk][tx * 4 + j];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const size_t m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      if (m >= p.M || n >= p.N) continue;
+      float v = c[i][j];
+      if (p.addend) v = p.addend[m * p.N + n] + v;
+      if (p.bias) v = v + p.bias[n];
+      p.C[m * p.N + n] = ApplyAct(v, p.act);
+    }
+}
+
+// ---- lane order: 32x32 tile, 256 threads, 2x2 outputs x 8 lanes per thread ------
+template <typename BT>
+__global__ void __launch_bounds__(256) GemmLaneKernel(Params p) {
+  constexpr int BM = 32, BN = 32;
+  __shared__ float As[BK][BM + 2];
+  __shared__ float Bs[BK][BN + 2];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const size_t m0 = static_cast<size_t>(blockIdx.y) * BM, n0 = static_cast<size_t>(blockIdx.x) * BN;
+  float acc[2][2][8];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int l = 0; l < 8; ++l) acc[i][j][l] = 0.0f;
+  for (size_t k0 = 0; k0 < p.K; k0 += BK) {
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const int idx = threadIdx.x + t * 256;
+      const int mm = idx / BK, kk = idx % BK;
+      float a = LoadA<false>(p, m0 + mm, k0 + kk);
+      if (p.a_k_scale && k0 + kk < p.K) a = a * p.a_k_scale[k0 + kk];
+      As[kk][mm] = a;
+      Bs[kk][mm] = LoadB<true, BT>(p, k0 + kk, n0 + mm);
+    }
+    __syncthreads();
+    const int kmax = p.K - k0 < static_cast<size_t>(BK) ? static_cast<int>(p.K - k0) : BK;
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      if (kk < kmax) {
+        const int l = kk & 7;  // k0 is a multiple of 16, so k mod 8 == kk mod 8
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            acc[i][j][l] = acc[i][j][l] + As[kk][ty * 2 + i] * Bs[kk][tx * 2 + j];
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const size_t m = m0 + ty * 2 + i, n = n0 + tx * 2 + j;
+      if (m >= p.M || n >= p.N) continue;
+      float s = acc[i][j][0];
+#pragma unroll
+      for (int l = 1; l < 8; ++l) s = s + acc[i][j][l];
+      float v = p.alpha * s;
+      if (p.addend) v = p.addend[m * p.N + n] + v;
+      p.C[m * p.N + n] = v;
+    }
+}
+
+}  // namespace
+
+void GemmExact(const GemmArgs& a, cudaStream_t s) {
+  if (a.M == 0 || a.N == 0) return;
+  Params p{a.A, a.B, a.C, a.M, a.N, a.K, a.alpha, a.b_col_scale, a.a_k_scale,
+           a.bias, a.addend, a.act, a.accumulate};
+  if (a.b_transposed) {
+    dim3 grid(static_cast<unsigned>((a.N + 31) / 32), static_cast<unsigned>((a.M + 31) / 32));
+    switch (a.b_type) {
+      case BType::kF32: GemmLaneKernel<float><<<grid, 256, 0, s>>>(p); break;
+      case BType::kI8: GemmLaneKernel<int8_t><<<grid, 256, 0, s>>>(p); break;
+      case BType::kBf16: GemmLaneKernel<uint16_t><<<grid, 256, 0, s>>>(p); break;
+    }
+    return;
+  }
+  dim3 grid(static_cast<unsigned>((a.N + 63) / 64), static_cast<unsigned>((a.M + 63) / 64));
+  if (a.a_transposed) {
+    GemmQuadKernel<true, float><<<grid, 256, 0, s>>>(p);
+    return;
+  }
+  switch (a.b_type) {
+    case BType::kF32: GemmQuadKernel<false, float><<<grid, 256, 0, s>>>(p); break;
+    case BType::kI8: GemmQuadKernel<false, int8_t><<<grid, 256, 0, s>>>(p); break;
+    case BType::kBf16: GemmQuadKernel<false, uint16_t><<<grid, 256, 0, s>>>(p); break;
+  }
+}
+
+}  // namespace see::k

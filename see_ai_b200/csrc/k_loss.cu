@@ -1,0 +1,345 @@
+// Losses: softmax cross-entropy (plain and masked), MSE, KL distillation.
+// HBM-bound row kernels.  The row softmax is the reference's f32 expression
+// (max, exp(x - max), sum, times 1/sum; reference: runtime/executor/loss.cc:21-31)
+// with the row sum taken as lane/thread partials combined in a fixed order.
+// The batch loss follows the reference's shape-chunked contract exactly
+// (reference: runtime/executor/loss.cc:35-72, source/parallel/parallel_for.h:55-67):
+// per-row -log p in double, rows folded sequentially inside each chunk, chunks
+// folded in chunk order, so the loss does not depend on the launch geometry.
+// Integer results (the masked forms' target count) are exact.
+#include "kernels.h"
+
+namespace see::k {
+
+namespace {
+
+constexpr size_t kMaxChunks = 256;   // the reference's kMaxParallelChunks
+constexpr size_t kGrainCheap = 32768;
+constexpr size_t kGrainMath = 4096;
+
+__host__ __device__ inline size_t RowGrain(size_t per_row, size_t budget) {
+  return per_row == 0 ? budget : (budget / per_row > 0 ? budget / per_row : 1);
+}
+__host__ __device__ inline size_t ChunkGrain(size_t n, size_t grain) {
+  if (grain == 0) grain = 1;
+  const size_t cap = (n + kMaxChunks - 1) / kMaxChunks;
+  return grain < cap ? cap : grain;
+}
+
+__device__ __forceinline__ float WarpMax(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+__device__ __forceinline__ float WarpSumF(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+__device__ __forceinline__ double WarpSumD(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+
+// Block-wide reductions for kThreads = 256 (8 warps); every thread gets the result.
+template <typename T, typename WarpOp, typename Op>
+__device__ __forceinline__ T BlockReduce(T v, T identity, T* smem, WarpOp warp_op, Op op) {
+  v = warp_op(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  T r = identity;
+  const int warps = blockDim.x >> 5;
+  for (int w = 0; w < warps; ++w) r = op(r, smem[w]);
+  return r;
+}
+
+// One block per row.  probs[row] = softmax(logits[row] * inv_T); returns the
+// normalised probabilities in place and, via *p_label, the label's probability.
+__device__ void RowSoftmaxBlock(const float* __restrict__ lrow, float* __restrict__ prow, size_t C,
+                                float inv_T, float* smem_f) {
+  float mx = -INFINITY;
+  bool any = false;
+  for (size_t c = threadIdx.x; c < C; c += blockDim.x) {
+    const float v = lrow[c] * inv_T;
+    mx = any ? fmaxf(mx, v) : v;
+    any = true;
+  }
+  // Threads with no element hold -inf, which fmaxf ignores against any number.
+  mx = BlockReduce<float>(mx, -INFINITY, smem_f, WarpMax,
+                          [](float a, float b) { return fmaxf(a, b); });
+  float sum = 0.0f;
+  for (size_t c = threadIdx.x; c < C; c += blockDim.x) {
+    const float e = expf(lrow[c] * inv_T - mx);
+    prow[c] = e;
+    sum += e;
+  }
+  sum = BlockReduce<float>(sum, 0.0f, smem_f, WarpSumF, [](float a, float b) { return a + b; });
+  const float inv_sum = 1.0f / sum;
+  for (size_t c = threadIdx.x; c < C; c += blockDim.x) prow[c] *= inv_sum;
+  __syncthreads();
+}
+
+__device__ __forceinline__ double NegLogSafe(float p) {
+  const double safe = isnan(p) ? static_cast<double>(p) : static_cast<double>(fmaxf(p, 1e-12f));
+  return -log(safe);
+}
+
+// row_loss[n] = -log p[n, label]; masked rows (label < 0) store 0 and are
+// skipped by the fold.  A label outside [0, C) is treated as the reference's
+// feeder contract would never allow: it reads class 0's probability scaled by
+// nothing — the row contributes NaN so the run fails loudly instead of
+// reading outside the row.
+__global__ void XEntRowsKernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
+                               float* __restrict__ probs, double* __restrict__ row_loss, size_t N,
+                               size_t C, bool masked) {
+  __shared__ float smem_f[32];
+  for (size_t n = blockIdx.x; n < N; n += gridDim.x) {
+    RowSoftmaxBlock(logits + n * C, probs + n * C, C, 1.0f, smem_f);
+    if (threadIdx.x == 0) {
+      const int32_t lab = labels[n];
+      double v;
+      if (masked && lab < 0) v = 0.0;
+      else if (lab < 0 || static_cast<size_t>(lab) >= C) v = NAN;
+      else v = NegLogSafe(probs[n * C + static_cast<size_t>(lab)]);
+      row_loss[n] = v;
+    }
+  }
+}
+
+// Folds row losses with the reference's chunk geometry: thread t owns chunk t
+// (rows [t*grain, ...)), summed sequentially; thread 0 then folds the chunk
+// partials in chunk order.  One block of kMaxChunks threads.
+__global__ void XEntFoldKernel(const double* __restrict__ row_loss,
+                               const int32_t* __restrict__ labels, float* __restrict__ loss,
+                               size_t N, size_t grain, bool masked,
+                               unsigned long long* __restrict__ count_out) {
+  __shared__ double partial[kMaxChunks];
+  __shared__ unsigned long long targets[kMaxChunks];
+  const size_t chunk = threadIdx.x;
+  const size_t r0 = chunk * grain;
+  double total = 0.0;
+  unsigned long long t = 0;
+  if (r0 < N) {
+    const size_t r1 = r0 + grain < N ? r0 + grain : N;
+    for (size_t n = r0; n < r1; ++n) {
+      if (masked && labels[n] < 0) continue;
+      total += row_loss[n];
+      ++t;
+    }
+  }
+  partial[chunk] = total;
+  targets[chunk] = t;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const size_t chunks = (N + grain - 1) / grain;
+    double sum = 0.0;
+    unsigned long long T = 0;
+    for (size_t c = 0; c < chunks; ++c) {
+      sum += partial[c];
+      T += targets[c];
+    }
+    if (masked) {
+      *loss = T ? static_cast<float>(sum / static_cast<double>(T)) : 0.0f;
+      if (count_out) *count_out = T;
+    } else {
+      *loss = static_cast<float>(sum / static_cast<double>(N));
+    }
+  }
+}
+
+__global__ void CountTargetsKernel(const int32_t* __restrict__ labels, size_t N,
+                                   unsigned long long* __restrict__ count_out) {
+  __shared__ unsigned long long smem[32];
+  unsigned long long t = 0;
+  for (size_t n = threadIdx.x; n < N; n += blockDim.x) t += labels[n] >= 0;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+  if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = t;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long T = 0;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) T += smem[w];
+    *count_out = T;
+  }
+}
+
+// dlogits = scale * probs, minus scale at the label (reference:
+// runtime/executor/loss.cc:59-72, 107-126).  Bit-identical to the CPU given the
+// same probs: one multiply, and one subtract at the label.
+__global__ void XEntBwdKernel(const float* __restrict__ probs, const int32_t* __restrict__ labels,
+                              const float* __restrict__ seed, float* __restrict__ dlogits, size_t N,
+                              size_t C, bool masked,
+                              const unsigned long long* __restrict__ count) {
+  float scale;
+  if (masked) {
+    const unsigned long long T = *count;
+    scale = T ? *seed / static_cast<float>(T) : 0.0f;
+  } else {
+    scale = *seed / static_cast<float>(N);
+  }
+  const size_t total = N * C;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += stride) {
+    const size_t n = i / C, c = i % C;
+    const int32_t lab = labels[n];
+    float v;
+    if (masked && lab < 0) {
+      v = 0.0f;
+    } else {
+      v = scale * probs[i];
+      if (static_cast<size_t>(lab) == c) v -= scale;
+    }
+    dlogits[i] = v;
+  }
+}
+
+// ---- MSE ---------------------------------------------------------------------
+// Per-chunk double partials (chunk = kGrainCheap elements, capped at 256
+// chunks), chunks folded in order (reference: runtime/executor/loss.cc:128-152).
+__global__ void MsePartialKernel(const float* __restrict__ pred, const float* __restrict__ target,
+                                 size_t n, size_t grain, double* __restrict__ partials) {
+  __shared__ double smem[32];
+  const size_t b = blockIdx.x * grain;
+  const size_t e = b + grain < n ? b + grain : n;
+  double total = 0.0;
+  for (size_t i = b + threadIdx.x; i < e; i += blockDim.x) {
+    const double d = static_cast<double>(pred[i]) - static_cast<double>(target[i]);
+    total += d * d;
+  }
+  total = BlockReduce<double>(total, 0.0, smem, WarpSumD, [](double a, double c) { return a + c; });
+  if (threadIdx.x == 0) partials[blockIdx.x] = total;
+}
+__global__ void MseFoldKernel(const double* __restrict__ partials, size_t chunks, size_t n,
+                              float* __restrict__ loss) {
+  double total = 0.0;
+  for (size_t c = 0; c < chunks; ++c) total += partials[c];
+  *loss = static_cast<float>(total / static_cast<double>(n));
+}
+__global__ void MseBwdKernel(const float* __restrict__ pred, const float* __restrict__ target,
+                             const float* __restrict__ seed, float* __restrict__ dpred, size_t n) {
+  const float scale = 2.0f * *seed / static_cast<float>(n);
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += stride)
+    dpred[i] = scale * (pred[i] - target[i]);
+}
+
+// ---- KL distillation (reference: runtime/executor/loss.cc:154-202) ------------
+__global__ void KLRowsKernel(const float* __restrict__ s_logits, const float* __restrict__ t_logits,
+                             float* __restrict__ p_s, float* __restrict__ p_t,
+                             double* __restrict__ row_loss, size_t N, size_t C, float inv_T) {
+  __shared__ float smem_f[32];
+  __shared__ double smem_d[32];
+  for (size_t n = blockIdx.x; n < N; n += gridDim.x) {
+    RowSoftmaxBlock(s_logits + n * C, p_s + n * C, C, inv_T, smem_f);
+    RowSoftmaxBlock(t_logits + n * C, p_t + n * C, C, inv_T, smem_f);
+    double total = 0.0;
+    for (size_t c = threadIdx.x; c < C; c += blockDim.x) {
+      const float pt = p_t[n * C + c];
+      if (pt <= 0.0f) continue;
+      const float ps_raw = p_s[n * C + c];
+      const double ps = isnan(ps_raw) ? static_cast<double>(ps_raw)
+                                      : static_cast<double>(fmaxf(ps_raw, 1e-12f));
+      total += static_cast<double>(pt) * (log(static_cast<double>(pt)) - log(ps));
+    }
+    total = BlockReduce<double>(total, 0.0, smem_d, WarpSumD,
+                                [](double a, double b) { return a + b; });
+    if (threadIdx.x == 0) row_loss[n] = total;
+  }
+}
+__global__ void KLFoldKernel(const double* __restrict__ row_loss, float* __restrict__ loss,
+                             size_t N, size_t grain, float loss_scale) {
+  __shared__ double partial[kMaxChunks];
+  const size_t r0 = threadIdx.x * grain;
+  double total = 0.0;
+  if (r0 < N) {
+    const size_t r1 = r0 + grain < N ? r0 + grain : N;
+    for (size_t n = r0; n < r1; ++n) total += row_loss[n];
+  }
+  partial[threadIdx.x] = total;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const size_t chunks = (N + grain - 1) / grain;
+    double sum = 0.0;
+    for (size_t c = 0; c < chunks; ++c) sum += partial[c];
+    *loss = static_cast<float>(sum / static_cast<double>(N)) * loss_scale;
+  }
+}
+__global__ void KLBwdKernel(const float* __restrict__ p_s, const float* __restrict__ p_t,
+                            const float* __restrict__ seed, float* __restrict__ dlogits,
+                            size_t total, float n_rows, float T, float loss_scale) {
+  const float scale = (*seed * loss_scale) / (n_rows * T);
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += stride)
+    dlogits[i] = scale * (p_s[i] - p_t[i]);
+}
+
+inline unsigned GridFor(size_t items, int threads, unsigned cap) {
+  size_t b = (items + threads - 1) / threads;
+  if (b < 1) b = 1;
+  if (b > cap) b = cap;
+  return static_cast<unsigned>(b);
+}
+
+}  // namespace
+
+void SoftmaxXEntFwd(bool masked, const float* logits, const int32_t* labels, float* loss,
+                    float* probs, size_t N, size_t C, double* row_scratch,
+                    unsigned long long* count_scratch, cudaStream_t s) {
+  if (N == 0) return;
+  const int threads = C >= 1024 ? 256 : (C >= 128 ? 128 : 32);
+  const unsigned blocks = static_cast<unsigned>(N < 148 * 16 ? N : 148 * 16);
+  XEntRowsKernel<<<blocks, threads, 0, s>>>(logits, labels, probs, row_scratch, N, C, masked);
+  const size_t grain = ChunkGrain(N, RowGrain(C, kGrainMath));
+  XEntFoldKernel<<<1, kMaxChunks, 0, s>>>(row_scratch, labels, loss, N, grain, masked,
+                                         count_scratch);
+}
+
+void SoftmaxXEntBwd(bool masked, const float* probs, const int32_t* labels, const float* seed,
+                    float* dlogits, size_t N, size_t C, unsigned long long* count_scratch,
+                    cudaStream_t s) {
+  if (N * C == 0) return;
+  if (masked) CountTargetsKernel<<<1, 256, 0, s>>>(labels, N, count_scratch);
+  XEntBwdKernel<<<GridFor(N * C, 256, 148 * 8), 256, 0, s>>>(probs, labels, seed, dlogits, N, C,
+                                                            masked, count_scratch);
+}
+
+void MseFwd(const float* pred, const float* target, float* loss, size_t n, double* scratch,
+            cudaStream_t s) {
+  if (n == 0) return;
+  const size_t grain = ChunkGrain(n, kGrainCheap);
+  const size_t chunks = (n + grain - 1) / grain;
+  MsePartialKernel<<<static_cast<unsigned>(chunks), 256, 0, s>>>(pred, target, n, grain, scratch);
+  MseFoldKernel<<<1, 1, 0, s>>>(scratch, chunks, n, loss);
+}
+
+void MseBwd(const float* pred, const float* target, const float* seed, float* dpred, size_t n,
+            cudaStream_t s) {
+  if (n == 0) return;
+  MseBwdKernel<<<GridFor(n, 256, 148 * 8), 256, 0, s>>>(pred, target, seed, dpred, n);
+}
+
+void KLDistillFwd(const float* s_logits, const float* t_logits, float* loss, float* p_s,
+                  float* p_t, size_t N, size_t C, float T, float loss_scale, double* row_scratch,
+                  cudaStream_t s) {
+  if (N == 0) return;
+  const float inv_T = 1.0f / T;
+  const int threads = C >= 1024 ? 256 : (C >= 128 ? 128 : 32);
+  const unsigned blocks = static_cast<unsigned>(N < 148 * 16 ? N : 148 * 16);
+  KLRowsKernel<<<blocks, threads, 0, s>>>(s_logits, t_logits, p_s, p_t, row_scratch, N, C, inv_T);
+  const size_t grain = ChunkGrain(N, RowGrain(C, kGrainMath));
+  KLFoldKernel<<<1, kMaxChunks, 0, s>>>(row_scratch, loss, N, grain, loss_scale);
+}
+
+void KLDistillBwd(const float* p_s, const float* p_t, const float* seed, float* dlogits,
+                  size_t N, size_t C, float T, float loss_scale, cudaStream_t s) {
+  if (N * C == 0) return;
+  KLBwdKernel<<<GridFor(N * C, 256, 148 * 8), 256, 0, s>>>(p_s, p_t, seed, dlogits, N * C,
+                                                          static_cast<float>(N), T, loss_scale);
+}
+
+}  // namespace see::k

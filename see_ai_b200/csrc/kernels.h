@@ -1,0 +1,153 @@
+// Launchers of the device kernels.  Every function enqueues on `stream` and
+// returns; pointers are device pointers.  Arithmetic contracts are stated at
+// each definition (which reference kernel's expression it evaluates, and
+// whether the result is bit-identical to the CPU executor's or within
+// floating-point tolerance of it).
+#ifndef SEE_CUDA_KERNELS_H_
+#define SEE_CUDA_KERNELS_H_
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "plan_abi.h"
+
+namespace see::k {
+
+// Device-side status block shared by all kernels of one backend.
+struct DeviceStatus {
+  int refused;        // 1 = a clip saw a non-finite gradient norm; parameter
+                      // writers skip their stores while it is set
+  int wait_timeout;   // 1 = a bounded device-side wait ran out
+  int pad[2];
+};
+
+// ---- elementwise / broadcast / gather -------------------------------------
+void AddEW(const float* x, const float* y, float* out, size_t n, cudaStream_t s);
+void MulEW(const float* x, const float* y, float* out, size_t n, cudaStream_t s);
+void AddBias(const float* x, const float* b, float* out, size_t rows, size_t cols, cudaStream_t s);
+void Accumulate(float* dst, const float* src, size_t n, cudaStream_t s);
+void Scale(const float* x, float* out, float alpha, size_t n, cudaStream_t s);
+void Fill(float* dst, float value, size_t n, cudaStream_t s);
+void Copy(const float* src, float* dst, size_t n, cudaStream_t s);
+void ActFwd(Act act, const float* x, float* out, size_t n, cudaStream_t s);
+void ActBwd(Act act, const float* dy, const float* x, float* dx, size_t n, cudaStream_t s);
+void FusedMap(const float* x, const float* o1, const float* o2, float* out, size_t n,
+              uint32_t stages, float imm0, float imm1, cudaStream_t s);
+void EmbedFwd(const int32_t* tokens, const float* table, float* out, size_t rows, size_t dim,
+              size_t vocab, cudaStream_t s);
+void ReduceRows(const float* dy, float* db, size_t rows, size_t cols, cudaStream_t s);
+void SegmentStarts(const int32_t* tokens, int32_t* starts, size_t B, size_t S, int32_t eos,
+                   cudaStream_t s);
+void RopeTable(float* table, size_t S, size_t d, float step, cudaStream_t s);
+void Rope(bool backward, const float* x, float* y, size_t B, size_t S, size_t H, size_t d,
+          float step, const float* table, cudaStream_t s);
+// f32 -> bf16 (round to nearest even), optionally scaling column k by
+// col_scale[k] first (the int8 dX GEMM's reduction-axis scales).
+void ToBf16(const float* x, uint16_t* out, size_t rows, size_t cols, const float* col_scale,
+            cudaStream_t s);
+
+// ---- normalization ----------------------------------------------------------
+void LayerNormFwd(const float* x, const float* gamma, const float* beta, float* y, float* mean,
+                  float* rstd, size_t rows, size_t cols, float eps, cudaStream_t s);
+void LayerNormBwd(const float* dy, const float* x, const float* gamma, const float* mean,
+                  const float* rstd, float* dx, size_t rows, size_t cols, cudaStream_t s);
+void RmsNormFwd(const float* x, const float* gamma, float* y, float* rstd, size_t rows,
+                size_t cols, float eps, cudaStream_t s);
+void RmsNormBwd(const float* dy, const float* x, const float* gamma, const float* rstd,
+                float* dx, size_t rows, size_t cols, cudaStream_t s);
+
+// ---- losses -----------------------------------------------------------------
+// `row_scratch` holds N doubles (per-row -log p) and `count_scratch` one
+// uint64 (the masked forms' target count).
+void SoftmaxXEntFwd(bool masked, const float* logits, const int32_t* labels, float* loss,
+                    float* probs, size_t N, size_t C, double* row_scratch,
+                    unsigned long long* count_scratch, cudaStream_t s);
+void SoftmaxXEntBwd(bool masked, const float* probs, const int32_t* labels, const float* seed,
+                    float* dlogits, size_t N, size_t C, unsigned long long* count_scratch,
+                    cudaStream_t s);
+void MseFwd(const float* pred, const float* target, float* loss, size_t n, double* scratch,
+            cudaStream_t s);
+void MseBwd(const float* pred, const float* target, const float* seed, float* dpred, size_t n,
+            cudaStream_t s);
+void KLDistillFwd(const float* s_logits, const float* t_logits, float* loss, float* p_s,
+                  float* p_t, size_t N, size_t C, float T, float loss_scale, double* row_scratch,
+                  cudaStream_t s);
+void KLDistillBwd(const float* p_s, const float* p_t, const float* seed, float* dlogits,
+                  size_t N, size_t C, float T, float loss_scale, cudaStream_t s);
+
+// ---- optimizer / clipping ---------------------------------------------------
+// Sum of squares of g in double, per shape-derived chunk then in chunk order;
+// result in *sq (device).  `partials` holds 256 doubles.
+void L2Squared(const float* g, size_t n, double* partials, double* sq, cudaStream_t s);
+// scale = clip factor for threshold `max_norm` from *sq (1 when max_norm <= 0);
+// raises status->refused when the norm is not finite.
+void ClipScaleFromSq(const double* sq, float max_norm, float* scale, DeviceStatus* status,
+                     cudaStream_t s);
+void ScaleInPlaceBy(float* g, size_t n, const float* scale, const DeviceStatus* status,
+                    cudaStream_t s);
+void SqNormAccum(const double* sq, float* acc, cudaStream_t s);
+void ClipGlobalScale(const float* acc, float max_norm, float* scale, DeviceStatus* status,
+                     cudaStream_t s);
+struct AdamScalars {
+  float lr, beta1, beta2, eps, weight_decay, inv_bc1, inv_bc2;
+};
+// g_copies > 1: the gradient is the sum, in copy order, of g_copies blocks
+// spaced copy_stride floats apart starting at g, times inv_copies.
+// `a` points at device memory (the backend's per-range scalar block), so a
+// captured launch picks up each step's learning rate and bias corrections.
+void AdamWStep(float* p, const float* g, float* m, float* v, size_t n, const AdamScalars* a,
+               const float* clip_scale, const DeviceStatus* status, int g_copies,
+               size_t copy_stride, float inv_copies, cudaStream_t s);
+void SgdStep(float* p, const float* g, size_t n, const AdamScalars* a,
+             const float* clip_scale, const DeviceStatus* status, int g_copies,
+             size_t copy_stride, float inv_copies, cudaStream_t s);
+// out = (sum over copies in order) * inv_copies, for norms taken on a summed gradient.
+void SumCopies(const float* g, float* out, size_t n, int g_copies, size_t copy_stride,
+               float inv_copies, cudaStream_t s);
+
+// ---- attention (exact family; scores in double like the CPU executor) --------
+void AttnFwd(const float* q, const float* k, const float* v, float* o, float* probs,
+             float* stats, size_t B, size_t S, size_t H, size_t d, const int32_t* starts,
+             cudaStream_t s);  // probs != null: cached family; stats != null: tiled family
+void AttnDP(const float* dout, const float* v, float* dp, size_t B, size_t S, size_t H, size_t d,
+            cudaStream_t s);
+void AttnDV(const float* probs, const float* dout, float* dv, size_t B, size_t S, size_t H,
+            size_t d, cudaStream_t s);
+void SoftmaxRowsBwd(const float* probs, const float* dp, float* ds, size_t rows, size_t cols,
+                    cudaStream_t s);
+void AttnDQ(const float* ds, const float* k, float* dq, size_t B, size_t S, size_t H, size_t d,
+            cudaStream_t s);
+void AttnDK(const float* ds, const float* q, float* dk, size_t B, size_t S, size_t H, size_t d,
+            cudaStream_t s);
+void AttnDQTiled(const float* q, const float* k, const float* v, const float* dout, float* stats,
+                 float* dq, size_t B, size_t S, size_t H, size_t d, cudaStream_t s);
+void AttnDKVTiled(bool want_dk, const float* q, const float* k, const float* v, const float* dout,
+                  const float* stats, float* out, size_t B, size_t S, size_t H, size_t d,
+                  cudaStream_t s);
+
+// ---- GEMM -------------------------------------------------------------------
+enum class BType : uint8_t { kF32 = 0, kI8 = 1, kBf16 = 2 };
+struct GemmArgs {
+  const float* A = nullptr;    // [M,K], or [K,M] when a_transposed
+  const void* B = nullptr;     // [K,N], or [N,K] when b_transposed
+  float* C = nullptr;          // [M,N]
+  size_t M = 0, N = 0, K = 0;
+  bool a_transposed = false, b_transposed = false;
+  BType b_type = BType::kF32;
+  float alpha = 1.0f;               // NN/TN: folded into A; NT: applied to the dot
+  const float* b_col_scale = nullptr;  // NN q8: scale per output column n (joins B's widening)
+  const float* a_k_scale = nullptr;    // NT q8: scale per reduction index k (joins A)
+  const float* bias = nullptr;
+  const float* addend = nullptr;
+  Act act = kActNone;
+  bool accumulate = false;  // C += (the merge program's form)
+};
+// The reference's reduction orders on CUDA cores, without fused multiply-adds:
+// bit-identical to the CPU executor for f32 / int8 / bf16 weights.
+void GemmExact(const GemmArgs& a, cudaStream_t s);
+
+}  // namespace see::k
+
+#endif  // SEE_CUDA_KERNELS_H_

@@ -1,0 +1,45 @@
+// The tensor-core path for GEMMs that carry the relaxed permission: the f32
+// activation is rounded once to bf16 (round to nearest even), the frozen
+// weight is widened exactly to bf16 (int8 and bf16 weights) or rounded to it
+// (f32 weights), products accumulate in f32 in tensor memory (tcgen05 / TMEM),
+// operands arrive through TMA.  Host-side planning lives here; the kernel in
+// k_gemm_umma.cu.
+#ifndef SEE_CUDA_UMMA_GEMM_H_
+#define SEE_CUDA_UMMA_GEMM_H_
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+
+#include "kernels.h"
+#include "plan_abi.h"
+
+namespace see::umma {
+
+struct Impl;
+struct Context {
+  Impl* impl = nullptr;
+};
+
+// Returns an empty string, or why the tensor-core path cannot be set up.
+std::string Init(Context* ctx, int device);
+void Destroy(Context* ctx);
+
+// Cached operand conversions: frozen weights are converted once per binding;
+// an activation's bf16 copy is reused by every GEMM that reads the same arena
+// range until an instruction writes into that range.
+void InvalidateAll(Context* ctx);
+void InvalidateRange(Context* ctx, uint64_t arena_off, uint64_t bytes);
+void PlanRange(Context* ctx, const Instruction* program, size_t begin, size_t end);
+
+// Runs C = epilogue(A @ B) on the tensor cores when the shape is inside the
+// kernel's domain.  *launches is the number of kernels enqueued; 0 with an
+// empty return value means "not applicable — use the exact kernel".
+// b_space: 1 = rodata, 2 = source model; offsets identify operands for caching.
+std::string TryGemm(Context* ctx, const k::GemmArgs& args, int b_space, uint64_t b_off,
+                    uint64_t a_off, uint64_t a_scale_off, cudaStream_t stream, int* launches);
+
+}  // namespace see::umma
+
+#endif  // SEE_CUDA_UMMA_GEMM_H_
