@@ -29,8 +29,10 @@ see::StepParams ToParams(const see_step_params* p) {
 
 int Fail(see_cuda_backend* h, const std::string& msg) {
   h->error = msg;
-  return msg == see::kNonFiniteNormRefusal || msg == see::kClipThresholdRefusal ? SEE_REFUSED
-                                                                                 : SEE_ERROR;
+  // A refusal may arrive prefixed with the failing instruction's index.
+  const bool refused = msg.find(see::kNonFiniteNormRefusal) != std::string::npos ||
+                       msg.find(see::kClipThresholdRefusal) != std::string::npos;
+  return refused ? SEE_REFUSED : SEE_ERROR;
 }
 
 }  // namespace

@@ -85,7 +85,7 @@ Status CudaBackend::Init() {
     return r;
   std::memset(h_status_, 0, 64);
   umma_ = std::make_unique<UmmaState>();
-  if (std::string e = umma::Init(&umma_->ctx, device_); !e.empty()) return std::unexpected(e);
+  if (std::string e = umma::Init(&umma_->ctx, device_, d_status_); !e.empty()) return std::unexpected(e);
   return {};
 }
 

@@ -1,0 +1,348 @@
+// The tensor-core GEMM for frozen-weight products that carry the relaxed
+// permission (reference: source/plan/instruction.h:356-382; the reference's own
+// relaxed kernels are runtime/executor/metal_backend.mm:1385-1449):
+//
+//     C[M,N] = epilogue( A_bf16[M,K] . B_bf16[N,K]^T )       f32 accumulate
+//
+// Blackwell-native: operands arrive by TMA (cp.async.bulk.tensor, 128-byte
+// swizzle) into a 3-stage shared-memory ring, one elected thread issues
+// tcgen05.mma (cta_group::1, kind::f16, M=128 x N=128 x K=16) with the
+// accumulator in tensor memory, tcgen05.commit hands ring slots back to the
+// producer, and four epilogue warps read the accumulator with tcgen05.ld and
+// apply scale / addend / bias / activation on the way to HBM.  One CTA per
+// 128x128 output tile, two CTAs resident per SM so one tile's epilogue
+// overlaps another's main loop.  Tensor-pipe bound for long K; for K <= 1024
+// the f32 output write is a comparable term (the arena is f32 by contract).
+//
+// Every wait on an mbarrier is bounded; a wait that runs out raises
+// DeviceStatus::wait_timeout, the CTA stops issuing work, frees its tensor
+// memory and returns, and the host reports the condition at its next flush.
+#include <cuda.h>
+
+#include "kernels.h"
+#include "umma_kernel.h"
+
+namespace see::k {
+
+namespace {
+
+constexpr uint32_t kBlockM = umma_cfg::kBlockM;
+constexpr uint32_t kBlockN = umma_cfg::kBlockN;
+constexpr uint32_t kBlockK = umma_cfg::kBlockK;   // 64 bf16 = one 128-byte swizzle row
+constexpr uint32_t kStages = umma_cfg::kStages;
+constexpr uint32_t kUmmaK = 16;
+constexpr uint32_t kATileBytes = kBlockM * kBlockK * 2;
+constexpr uint32_t kBTileBytes = kBlockN * kBlockK * 2;
+constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
+constexpr uint32_t kTmemCols = kBlockN;           // f32 accumulator columns
+constexpr uint32_t kThreads = 192;                // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr uint32_t kWaitLimit = 1u << 22;
+
+constexpr float kGeluC = 0.7978845608028654f;
+constexpr float kGeluA = 0.044715f;
+
+__device__ __forceinline__ uint32_t SmemAddr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void MbarInit(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(SmemAddr(bar)), "r"(count));
+}
+__device__ __forceinline__ void MbarExpectTx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemAddr(bar)),
+               "r"(bytes)
+               : "memory");
+}
+// Bounded wait: false when the limit ran out.
+__device__ __forceinline__ bool MbarWait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = SmemAddr(bar);
+  for (uint32_t it = 0; it < kWaitLimit; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void TmaLoad2D(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                          int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      ::"r"(SmemAddr(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(SmemAddr(bar)), "r"(x),
+      "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: start address
+// (>>4), leading byte offset 1 (unused for swizzled K-major), stride byte offset
+// 1024 (>>4 = 64: eight 128-byte rows per swizzle atom), descriptor version 1,
+// layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t MakeSmemDesc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::f16: D = f32, A = B = bf16, both K-major.
+__device__ __forceinline__ uint32_t MakeInstrDesc(uint32_t m, uint32_t n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+__device__ __forceinline__ void UmmaBf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void UmmaCommit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(SmemAddr(bar))
+               : "memory");
+}
+__device__ __forceinline__ void TmemLoad32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+__device__ __forceinline__ float ApplyAct(float v, int act) {
+  switch (act) {
+    case kActRelu: return v > 0.0f ? v : 0.0f;
+    case kActGelu: {
+      const float t = tanhf(kGeluC * (v + kGeluA * v * v * v));
+      return 0.5f * v * (1.0f + t);
+    }
+    case kActSilu: return v * (1.0f / (1.0f + expf(-v)));
+    default: return v;
+  }
+}
+
+struct __align__(8) Barriers {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full;
+  uint32_t tmem_base;
+  volatile uint32_t abort;  // set by a role whose wait ran out; the epilogue then stores nothing
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
+UmmaGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               UmmaEpilogue ep) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the swizzle pattern and the descriptors' base offset assume it.
+  uint8_t* smem = smem_raw + ((1024u - (SmemAddr(smem_raw) & 1023u)) & 1023u);
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + kStages * kStageBytes);
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t m0 = blockIdx.y * kBlockM, n0 = blockIdx.x * kBlockN;
+  const uint32_t k_blocks = (ep.K + kBlockK - 1) / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < kStages; ++s) {
+      MbarInit(&bars->full[s], 1);
+      MbarInit(&bars->empty[s], 1);
+    }
+    MbarInit(&bars->tmem_full, 1);
+    bars->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(SmemAddr(&bars->tmem_base)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---- TMA producer ----
+    if (lane == 0) {
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        const uint32_t s = kb % kStages, round = kb / kStages;
+        if (round > 0 && !MbarWait(&bars->empty[s], (round - 1) & 1)) {
+          ep.status->wait_timeout = 1;
+          bars->abort = 1;
+          break;
+        }
+        uint8_t* a_dst = smem + s * kStageBytes;
+        uint8_t* b_dst = a_dst + kATileBytes;
+        MbarExpectTx(&bars->full[s], kStageBytes);
+        TmaLoad2D(a_dst, &map_a, &bars->full[s], static_cast<int32_t>(kb * kBlockK),
+                  static_cast<int32_t>(m0));
+        TmaLoad2D(b_dst, &map_b, &bars->full[s], static_cast<int32_t>(kb * kBlockK),
+                  static_cast<int32_t>(n0));
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    if (lane == 0) {
+      const uint32_t idesc = MakeInstrDesc(kBlockM, kBlockN);
+      bool ok = true;
+      for (uint32_t kb = 0; kb < k_blocks && ok; ++kb) {
+        const uint32_t s = kb % kStages, round = kb / kStages;
+        if (!MbarWait(&bars->full[s], round & 1)) {
+          ep.status->wait_timeout = 1;
+          bars->abort = 1;
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = SmemAddr(smem + s * kStageBytes);
+        const uint64_t desc_a = MakeSmemDesc(a_addr);
+        const uint64_t desc_b = MakeSmemDesc(a_addr + kATileBytes);
+#pragma unroll
+        for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k) {
+          // advance 16 bf16 = 32 bytes inside the 128-byte swizzle row: +2 in >>4 units
+          UmmaBf16(tmem_base, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+        }
+        UmmaCommit(&bars->empty[s]);  // the slot is free once these MMAs have read it
+      }
+      UmmaCommit(&bars->tmem_full);   // accumulator complete (or abandoned on timeout)
+    }
+  } else {
+    // ---- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----
+    const uint32_t quarter = warp & 3;
+    bool ok = MbarWait(&bars->tmem_full, 0);
+    if (!ok && lane == 0) ep.status->wait_timeout = 1;
+    if (bars->abort) ok = false;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t row = m0 + quarter * 32 + lane;
+    if (ok && k_blocks > 0) {
+#pragma unroll 1
+      for (uint32_t c0 = 0; c0 < kBlockN; c0 += 32) {
+        uint32_t r[32];
+        TmemLoad32(tmem_base + ((quarter * 32) << 16) + c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < ep.M) {
+          const uint32_t n_base = n0 + c0;
+          float* crow = ep.C + static_cast<size_t>(row) * ep.N + n_base;
+          const float* drow = ep.addend ? ep.addend + static_cast<size_t>(row) * ep.N + n_base : nullptr;
+#pragma unroll
+          for (uint32_t j = 0; j < 32; j += 4) {
+            if (n_base + j >= ep.N) break;   // N % 4 == 0: a float4 is all in or all out
+            float v[4];
+#pragma unroll
+            for (uint32_t t = 0; t < 4; ++t) {
+              float x = __uint_as_float(r[j + t]);
+              const uint32_t n = n_base + j + t;
+              x = ep.col_scale ? x * __ldg(ep.col_scale + n) : x * ep.alpha;
+              if (drow) x = drow[j + t] + x;
+              if (ep.bias) x = x + __ldg(ep.bias + n);
+              v[t] = ApplyAct(x, ep.act);
+            }
+            *reinterpret_cast<float4*>(crow + j) = make_float4(v[0], v[1], v[2], v[3]);
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+// Weight conversion to the K-major bf16 layout [N][K] the kernel consumes.
+// transpose = true: src is [K][N] (the NN forms); false: src is [N][K].
+template <typename T> __device__ __forceinline__ uint16_t ToBf16Bits(T v);
+template <> __device__ __forceinline__ uint16_t ToBf16Bits<int8_t>(int8_t v) {
+  return static_cast<uint16_t>(__float_as_uint(static_cast<float>(v)) >> 16);  // exact
+}
+template <> __device__ __forceinline__ uint16_t ToBf16Bits<uint16_t>(uint16_t v) { return v; }
+template <> __device__ __forceinline__ uint16_t ToBf16Bits<float>(float f) {
+  uint32_t b = __float_as_uint(f);
+  if ((b & 0x7FFFFFFFu) > 0x7F800000u) return static_cast<uint16_t>((b >> 16) | 0x0040u);
+  b += 0x7FFFu + ((b >> 16) & 1u);
+  return static_cast<uint16_t>(b >> 16);
+}
+
+template <typename T>
+__global__ void WeightToBf16Kernel(const T* __restrict__ src, uint16_t* __restrict__ dst, uint32_t N,
+                                   uint32_t K, bool transpose) {
+  __shared__ uint16_t tile[32][33];
+  const uint32_t bx = blockIdx.x * 32, by = blockIdx.y * 32;
+  if (!transpose) {  // src [N][K] -> dst [N][K]
+    for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
+      const uint32_t n = by + i, k = bx + threadIdx.x;
+      if (n < N && k < K) dst[static_cast<size_t>(n) * K + k] = ToBf16Bits<T>(src[static_cast<size_t>(n) * K + k]);
+    }
+    return;
+  }
+  // src [K][N]: bx indexes n, by indexes k
+  for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
+    const uint32_t k = by + i, n = bx + threadIdx.x;
+    if (k < K && n < N) tile[i][threadIdx.x] = ToBf16Bits<T>(src[static_cast<size_t>(k) * N + n]);
+  }
+  __syncthreads();
+  for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
+    const uint32_t n = bx + i, k = by + threadIdx.x;
+    if (k < K && n < N) dst[static_cast<size_t>(n) * K + k] = tile[threadIdx.x][i];
+  }
+}
+
+}  // namespace
+
+size_t UmmaSmemBytes() { return kStages * kStageBytes + sizeof(Barriers) + 1024; }
+
+cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
+                           const UmmaEpilogue& ep, cudaStream_t s) {
+  static bool configured = false;
+  const size_t smem = UmmaSmemBytes();
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(UmmaGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  dim3 grid((ep.N + kBlockN - 1) / kBlockN, (ep.M + kBlockM - 1) / kBlockM);
+  UmmaGemmKernel<<<grid, kThreads, smem, s>>>(map_a, map_b, ep);
+  return cudaGetLastError();
+}
+
+void WeightToBf16(const void* src, BType type, uint16_t* dst, uint32_t N, uint32_t K,
+                  bool transpose, cudaStream_t s) {
+  dim3 block(32, 8);
+  dim3 grid = transpose ? dim3((N + 31) / 32, (K + 31) / 32) : dim3((K + 31) / 32, (N + 31) / 32);
+  switch (type) {
+    case BType::kI8:
+      WeightToBf16Kernel<int8_t><<<grid, block, 0, s>>>(static_cast<const int8_t*>(src), dst, N, K, transpose);
+      break;
+    case BType::kBf16:
+      WeightToBf16Kernel<uint16_t><<<grid, block, 0, s>>>(static_cast<const uint16_t*>(src), dst, N, K, transpose);
+      break;
+    case BType::kF32:
+      WeightToBf16Kernel<float><<<grid, block, 0, s>>>(static_cast<const float*>(src), dst, N, K, transpose);
+      break;
+  }
+}
+
+}  // namespace see::k

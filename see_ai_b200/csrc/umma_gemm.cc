@@ -1,11 +1,182 @@
 #include "umma_gemm.h"
+
+#include <cuda.h>
+
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <tuple>
+#include <vector>
+
+#include "umma_kernel.h"
+
 namespace see::umma {
-struct Impl {};
-std::string Init(Context*, int) { return {}; }
-void Destroy(Context*) {}
-void InvalidateAll(Context*) {}
-void InvalidateRange(Context*, uint64_t, uint64_t) {}
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// A cached K-major bf16 copy of a frozen weight: key = (space, byte offset,
+// N, K, transposed source, element type).
+using WeightKey = std::tuple<int, uint64_t, uint64_t, uint64_t, bool, int>;
+
+struct ActCopy {   // a bf16 copy of an arena activation [M, K]
+  uint64_t a_off = ~0ull, scale_off = ~0ull, M = 0, K = 0;
+  bool valid = false;
+  uint16_t* buf = nullptr;
+  uint64_t capacity = 0;  // elements
+  uint64_t last_use = 0;
+};
+
+constexpr int kActSlots = 4;
+
+}  // namespace
+
+struct Impl {
+  int device = 0;
+  EncodeTiledFn encode = nullptr;
+  std::map<WeightKey, uint16_t*> weights;
+  ActCopy acts[kActSlots];
+  uint64_t tick = 0;
+  k::DeviceStatus* status = nullptr;  // the backend's device status block (not owned)
+};
+
+std::string Init(Context* ctx, int device, k::DeviceStatus* status) {
+  auto* impl = new Impl;
+  impl->device = device;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres{};
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+    delete impl;
+    return "cuda: the driver does not provide cuTensorMapEncodeTiled (TMA descriptors)";
+  }
+  impl->encode = reinterpret_cast<EncodeTiledFn>(fn);
+  impl->status = status;
+  ctx->impl = impl;
+  return {};
+}
+
+void Destroy(Context* ctx) {
+  if (!ctx->impl) return;
+  InvalidateAll(ctx);
+  for (auto& a : ctx->impl->acts) cudaFree(a.buf);
+  delete ctx->impl;
+  ctx->impl = nullptr;
+}
+
+void InvalidateAll(Context* ctx) {
+  if (!ctx->impl) return;
+  for (auto& [key, buf] : ctx->impl->weights) cudaFree(buf);
+  ctx->impl->weights.clear();
+  for (auto& a : ctx->impl->acts) a.valid = false;
+}
+
+void InvalidateRange(Context* ctx, uint64_t off, uint64_t bytes) {
+  if (!ctx->impl) return;
+  for (auto& a : ctx->impl->acts) {
+    if (!a.valid) continue;
+    const uint64_t a_bytes = a.M * a.K * 4;
+    if (off < a.a_off + a_bytes && a.a_off < off + bytes) a.valid = false;
+  }
+}
+
 void PlanRange(Context*, const Instruction*, size_t, size_t) {}
-std::string TryGemm(Context*, const k::GemmArgs&, int, uint64_t, uint64_t, uint64_t, cudaStream_t,
-                    int* launches) { *launches = 0; return {}; }
+
+static bool EncodeBf16Map(Impl* impl, CUtensorMap* map, const void* base, uint64_t rows,
+                          uint64_t cols, uint32_t box_rows) {
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {k::umma_cfg::kBlockK, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return impl->encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                      strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_off,
+                    uint64_t a_off, uint64_t a_scale_off, cudaStream_t stream, int* launches) {
+  *launches = 0;
+  Impl* impl = ctx->impl;
+  if (!impl) return {};
+  // The kernel's domain: K a multiple of 8 (16-byte global strides for TMA), N a
+  // multiple of 4 (float4 stores), enough rows to fill a 128-row tile, no
+  // transposed A, no accumulate form.  Anything else runs on the exact kernels.
+  if (a.a_transposed || a.accumulate) return {};
+  if (a.K % 8 != 0 || a.N % 4 != 0 || a.K < 64 || a.N < 16 || a.M < 64) return {};
+  if (a.M > 0xFFFFFFFFull || a.N > 0xFFFFFFFFull || a.K > 0xFFFFFFFFull) return {};
+  if ((reinterpret_cast<uintptr_t>(a.C) & 15) || (a.addend && (reinterpret_cast<uintptr_t>(a.addend) & 15)))
+    return {};
+
+  // ---- the weight, K-major bf16 [N][K], converted once per binding ----
+  const WeightKey key{b_space, b_off, a.N, a.K, !a.b_transposed, static_cast<int>(a.b_type)};
+  uint16_t* w = nullptr;
+  if (auto it = impl->weights.find(key); it != impl->weights.end()) {
+    w = it->second;
+  } else {
+    void* p = nullptr;
+    if (cudaMalloc(&p, a.N * a.K * 2) != cudaSuccess) return "tensor-core path: weight copy allocation failed";
+    w = static_cast<uint16_t*>(p);
+    k::WeightToBf16(a.B, a.b_type, w, static_cast<uint32_t>(a.N), static_cast<uint32_t>(a.K),
+                    /*transpose=*/!a.b_transposed, stream);
+    ++*launches;
+    impl->weights.emplace(key, w);
+  }
+
+  // ---- the activation, bf16 [M][K], reused while its arena range is unwritten ----
+  ActCopy* slot = nullptr;
+  for (auto& c : impl->acts)
+    if (c.valid && c.a_off == a_off && c.scale_off == a_scale_off && c.M == a.M && c.K == a.K)
+      slot = &c;
+  if (!slot) {
+    slot = &impl->acts[0];
+    for (auto& c : impl->acts) {
+      if (!c.valid) { slot = &c; break; }
+      if (c.last_use < slot->last_use) slot = &c;
+    }
+    const uint64_t need = a.M * a.K;
+    if (slot->capacity < need) {
+      // Replacing the buffer: queued kernels may still read the old one.
+      cudaStreamSynchronize(stream);
+      cudaFree(slot->buf);
+      slot->buf = nullptr;
+      slot->capacity = 0;
+      void* p = nullptr;
+      if (cudaMalloc(&p, need * 2) != cudaSuccess) return "tensor-core path: activation copy allocation failed";
+      slot->buf = static_cast<uint16_t*>(p);
+      slot->capacity = need;
+    }
+    k::ToBf16(a.A, slot->buf, a.M, a.K, a.a_k_scale, stream);
+    ++*launches;
+    slot->a_off = a_off; slot->scale_off = a_scale_off; slot->M = a.M; slot->K = a.K;
+    slot->valid = true;
+  }
+  slot->last_use = ++impl->tick;
+
+  CUtensorMap map_a, map_b;
+  if (!EncodeBf16Map(impl, &map_a, slot->buf, a.M, a.K, k::umma_cfg::kBlockM) ||
+      !EncodeBf16Map(impl, &map_b, w, a.N, a.K, k::umma_cfg::kBlockN))
+    return "tensor-core path: cuTensorMapEncodeTiled refused the operand layout";
+
+  k::UmmaEpilogue ep{};
+  ep.C = a.C;
+  ep.addend = a.addend;
+  ep.bias = a.bias;
+  ep.col_scale = a.b_col_scale;
+  ep.alpha = a.alpha;
+  ep.act = static_cast<int>(a.act);
+  ep.M = static_cast<uint32_t>(a.M);
+  ep.N = static_cast<uint32_t>(a.N);
+  ep.K = static_cast<uint32_t>(a.K);
+  ep.status = impl->status;
+  if (cudaError_t e = k::UmmaGemmLaunch(map_a, map_b, ep, stream); e != cudaSuccess)
+    return std::string("tensor-core GEMM launch: ") + cudaGetErrorString(e);
+  ++*launches;
+  return {};
+}
+
 }  // namespace see::umma

@@ -23,7 +23,8 @@ struct Context {
 };
 
 // Returns an empty string, or why the tensor-core path cannot be set up.
-std::string Init(Context* ctx, int device);
+// `status` is the backend's device status block; a bounded wait that runs out is raised there.
+std::string Init(Context* ctx, int device, k::DeviceStatus* status);
 void Destroy(Context* ctx);
 
 // Cached operand conversions: frozen weights are converted once per binding;

@@ -1,0 +1,41 @@
+// Interface between the tensor-core GEMM kernel (k_gemm_umma.cu) and its host
+// planner (umma_gemm.cc).
+#ifndef SEE_CUDA_UMMA_KERNEL_H_
+#define SEE_CUDA_UMMA_KERNEL_H_
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "kernels.h"
+
+namespace see::k {
+
+namespace umma_cfg {
+constexpr uint32_t kBlockM = 128, kBlockN = 128, kBlockK = 64, kStages = 3;
+}
+
+struct UmmaEpilogue {
+  float* C;                 // [M, N] f32
+  const float* addend;      // [M, N] or null:  v = d + v
+  const float* bias;        // [N] or null:     v = v + bias[n]
+  const float* col_scale;   // [N] or null:     v = acc * col_scale[n]   (else acc * alpha)
+  float alpha;
+  int act;
+  uint32_t M, N, K;
+  DeviceStatus* status;
+};
+
+size_t UmmaSmemBytes();
+// map_a: bf16 [M, K] row-major, box {64, 128}, 128-byte swizzle; map_b: bf16 [N, K] likewise.
+cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
+                           const UmmaEpilogue& ep, cudaStream_t s);
+// dst[N][K] (bf16 bits) from src [K][N] (transpose) or [N][K]; int8 and bf16 widen exactly.
+void WeightToBf16(const void* src, BType type, uint16_t* dst, uint32_t N, uint32_t K,
+                  bool transpose, cudaStream_t s);
+
+}  // namespace see::k
+
+#endif  // SEE_CUDA_UMMA_KERNEL_H_
