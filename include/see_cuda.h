@@ -98,13 +98,79 @@ int see_cuda_set_gradient_gather(see_cuda_backend* h, int ranks, const void* gat
                                  uint64_t block_offset, uint64_t block_bytes);
 /* Profile mode: CUDA-event pairs around every instruction (the profiler hook,
  * reference: runtime/profiler/kernel_profile.h:25-72).  take_profile fills up
- * to `capacity` records {opcode, index, ms, m, n, k} and returns the count. */
+ * to `capacity` records and returns the count. */
 typedef struct see_profile_record {
-  uint16_t opcode; uint16_t pad; uint32_t index; float ms; uint32_t pad2;
+  uint16_t opcode; uint16_t pad; uint32_t index;
+  float ms;        /* the whole instruction */
+  float kernel_ms; /* the tensor-core GEMM kernel alone, 0 when the instruction did not use it */
   uint64_t m, n, k;
 } see_profile_record;
 int see_cuda_set_profiling(see_cuda_backend* h, int on);
 int64_t see_cuda_take_profile(see_cuda_backend* h, see_profile_record* out, uint64_t capacity);
+
+/* ---- The dispatcher: UpdateEngine over the CUDA backend ----------------------
+ * Mirrors the hot-path surface of seeml::update_rt::UpdateEngine (reference:
+ * runtime/dispatcher/update_engine.h:211-367).  The engine owns the device slab
+ * (zeroed, persistent image at offset 0 — reference: runtime/loader/
+ * plan_loader.cc:251-288); the host moves bytes only through the calls below. */
+typedef struct see_engine see_engine;
+
+int see_engine_create(int device_ordinal, see_engine** out); /* error: see_cuda_create_error() */
+void see_engine_destroy(see_engine* h);
+const char* see_engine_last_error(see_engine* h);
+/* The engine's backend, for the see_cuda_* knobs (stream, counters, gradient
+ * gather, profiling).  Borrowed: do not destroy it. */
+see_cuda_backend* see_engine_backend(see_engine* h);
+
+/* LoadFromMemory — reference: update_engine.h:227-243, update_engine.cc:211-301:
+ * seal, version window, section bounds, every instruction's operand extents.
+ * A refused load keeps the previous plan bound. */
+int see_engine_load(see_engine* h, const uint8_t* plan, uint64_t bytes);
+/* BindSourceModel — reference: update_engine.h:245-252. */
+int see_engine_bind_source(see_engine* h, const uint8_t* data, uint64_t bytes);
+/* Copies the decoded 320-byte plan header (reference: source/plan/schema.h:298-386). */
+int see_engine_header(see_engine* h, void* out_320_bytes);
+
+/* One batch into the I/O slots — what BatchPipeline::NextBatch's memcpy does
+ * (reference: runtime/pipeline/batch_pipeline.h:43-57, update_engine.cc:853),
+ * here a pinned double-buffered host->device copy. */
+int see_engine_stage_batch(see_engine* h, const void* input, uint64_t input_bytes,
+                           const void* labels, uint64_t label_bytes);
+/* ExecuteTrainProgram as two ranges split where the optimizer phase begins
+ * (reference: update_engine.cc:318-364; runtime/profiler/step_timings.h:37-59),
+ * so a data-parallel driver can exchange gradients between them.
+ * advance_step != 0 moves the 1-indexed AdamW timestep first. */
+int see_engine_train_forward_backward(see_engine* h, int advance_step);
+int see_engine_train_optimizer(see_engine* h);
+/* ExecuteStepProgram (gradient accumulation) — reference: update_engine.cc:318-323. */
+int see_engine_step_program(see_engine* h);
+/* LossValue — reference: update_engine.cc:366-368.  Also surfaces a refusal. */
+int see_engine_read_loss(see_engine* h, float* loss);
+/* Evaluate one staged batch: eval program, loss, and the accuracy tally
+ * (rows judged, argmax hits; reference: update_engine.cc:432-580) on device. */
+int see_engine_evaluate(see_engine* h, float* loss, uint64_t* rows, uint64_t* correct);
+/* RunMerge + the finiteness scan of every delta — reference: update_engine.cc:1028-1063. */
+int see_engine_run_merge(see_engine* h, int* all_finite);
+/* Arena access for checkpoints, gate snapshots and commit (reference:
+ * update_engine.cc:763, 1148-1159, 1172-1235). */
+int see_engine_read_arena(see_engine* h, uint64_t offset, uint64_t bytes, void* dst);
+int see_engine_write_arena(see_engine* h, uint64_t offset, uint64_t bytes, const void* src);
+
+uint64_t see_engine_step(see_engine* h);
+int see_engine_set_step(see_engine* h, uint64_t step);      /* resume */
+int see_engine_set_horizon(see_engine* h, uint64_t steps);  /* the run's length, for the schedule */
+/* EffectiveLr — reference: update_engine.cc:370-391. */
+float see_engine_effective_lr(see_engine* h);
+/* Replay each range as a CUDA graph after its first eager execution. */
+int see_engine_set_use_graphs(see_engine* h, int on);
+/* StepProfiler — reference: runtime/profiler/step_timings.h:69-131 — with CUDA
+ * events: forward / backward / optimizer milliseconds accumulated per step. */
+int see_engine_set_phase_timing(see_engine* h, int on);
+int see_engine_take_timings(see_engine* h, float* forward_ms, float* backward_ms,
+                            float* optimizer_ms, uint64_t* steps);
+/* The contiguous arena block holding every optimizer step's gradient operand
+ * (reference: compiler/backend/allocation/arena_binder.cc:56-77 binds them back to back). */
+int see_engine_gradient_block(see_engine* h, uint64_t* offset, uint64_t* bytes);
 
 #ifdef __cplusplus
 }

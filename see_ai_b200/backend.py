@@ -47,7 +47,7 @@ class Counters(ctypes.Structure):
 
 class ProfileRecord(ctypes.Structure):
     _fields_ = [("opcode", ctypes.c_uint16), ("pad", ctypes.c_uint16), ("index", ctypes.c_uint32),
-                ("ms", ctypes.c_float), ("pad2", ctypes.c_uint32), ("m", ctypes.c_uint64),
+                ("ms", ctypes.c_float), ("kernel_ms", ctypes.c_float), ("m", ctypes.c_uint64),
                 ("n", ctypes.c_uint64), ("k", ctypes.c_uint64)]
 
 
@@ -229,4 +229,4 @@ class CudaBackend:
     def take_profile(self, capacity: int = 65536):
         arr = (ProfileRecord * capacity)()
         n = self.lib.see_cuda_take_profile(self.h, arr, capacity)
-        return [(r.opcode, r.index, r.ms, r.m, r.n, r.k) for r in arr[:n]]
+        return [(r.opcode, r.index, r.ms, r.m, r.n, r.k, r.kernel_ms) for r in arr[:n]]

@@ -1,4 +1,5 @@
-// extern "C" face of CudaBackend: one forwarding function per seam member.
+// extern "C" face of CudaBackend and UpdateEngine: one forwarding function per
+// member of the seam it mirrors.
 #include "../../include/see_cuda.h"
 
 #include <cstring>
@@ -7,11 +8,19 @@
 #include <string>
 
 #include "cuda_backend.h"
+#include "engine.h"
 
 struct see_cuda_backend {
-  std::unique_ptr<see::CudaBackend> backend;
+  see::CudaBackend* backend = nullptr;          // borrowed when owned is empty
+  std::unique_ptr<see::CudaBackend> owned;
   std::string error;
   std::string device;
+};
+
+struct see_engine {
+  std::unique_ptr<see::UpdateEngine> engine;
+  see_cuda_backend backend_view;                // a borrowed view of the engine's backend
+  std::string error;
 };
 
 namespace {
@@ -27,13 +36,21 @@ see::StepParams ToParams(const see_step_params* p) {
   return s;
 }
 
-int Fail(see_cuda_backend* h, const std::string& msg) {
-  h->error = msg;
+int CodeOf(const std::string& msg) {
   // A refusal may arrive prefixed with the failing instruction's index.
   const bool refused = msg.find(see::kNonFiniteNormRefusal) != std::string::npos ||
                        msg.find(see::kClipThresholdRefusal) != std::string::npos;
   return refused ? SEE_REFUSED : SEE_ERROR;
 }
+int Fail(see_cuda_backend* h, const std::string& msg) {
+  h->error = msg;
+  return CodeOf(msg);
+}
+int Fail(see_engine* h, const std::string& msg) {
+  h->error = msg;
+  return CodeOf(msg);
+}
+int Done(see_engine* h, const see::Status& r) { return r ? SEE_OK : Fail(h, r.error()); }
 
 }  // namespace
 
@@ -48,7 +65,8 @@ int see_cuda_create(int device_ordinal, see_cuda_backend** out) {
     return SEE_ERROR;
   }
   auto* h = new see_cuda_backend;
-  h->backend = std::move(*b);
+  h->owned = std::move(*b);
+  h->backend = h->owned.get();
   h->device = h->backend->device();
   *out = h;
   return SEE_OK;
@@ -56,7 +74,9 @@ int see_cuda_create(int device_ordinal, see_cuda_backend** out) {
 
 const char* see_cuda_create_error(void) { return g_create_error.c_str(); }
 
-void see_cuda_destroy(see_cuda_backend* h) { delete h; }
+void see_cuda_destroy(see_cuda_backend* h) {
+  if (h && h->owned) delete h;  // a borrowed view belongs to its engine
+}
 
 const char* see_cuda_name(see_cuda_backend* h) { return h->backend->name(); }
 const char* see_cuda_device(see_cuda_backend* h) { return h->device.c_str(); }
@@ -174,10 +194,92 @@ int64_t see_cuda_take_profile(see_cuda_backend* h, see_profile_record* out, uint
   uint64_t n = 0;
   for (const auto& r : recs) {
     if (n >= capacity) break;
-    out[n] = see_profile_record{r.opcode, 0, r.index, r.ms, 0, r.m, r.n, r.k};
+    out[n] = see_profile_record{r.opcode, 0, r.index, r.ms, r.kernel_ms, r.m, r.n, r.k};
     ++n;
   }
   return static_cast<int64_t>(n);
+}
+
+// ---- the engine ---------------------------------------------------------------------
+
+int see_engine_create(int device_ordinal, see_engine** out) {
+  if (!out) return SEE_ERROR;
+  *out = nullptr;
+  auto e = see::UpdateEngine::Create(device_ordinal);
+  if (!e) {
+    g_create_error = e.error();
+    return SEE_ERROR;
+  }
+  auto* h = new see_engine;
+  h->engine = std::move(*e);
+  h->backend_view.backend = &h->engine->backend();
+  h->backend_view.device = h->engine->backend().device();
+  *out = h;
+  return SEE_OK;
+}
+
+void see_engine_destroy(see_engine* h) { delete h; }
+const char* see_engine_last_error(see_engine* h) { return h->error.c_str(); }
+see_cuda_backend* see_engine_backend(see_engine* h) { return &h->backend_view; }
+
+int see_engine_load(see_engine* h, const uint8_t* plan, uint64_t bytes) {
+  return Done(h, h->engine->LoadFromMemory(plan, bytes));
+}
+int see_engine_bind_source(see_engine* h, const uint8_t* data, uint64_t bytes) {
+  return Done(h, h->engine->BindSourceModel(data, bytes));
+}
+int see_engine_header(see_engine* h, void* out_320_bytes) {
+  std::memcpy(out_320_bytes, &h->engine->header(), sizeof(see::PlanHeader));
+  return SEE_OK;
+}
+int see_engine_stage_batch(see_engine* h, const void* input, uint64_t input_bytes,
+                           const void* labels, uint64_t label_bytes) {
+  return Done(h, h->engine->StageBatch(input, input_bytes, labels, label_bytes));
+}
+int see_engine_train_forward_backward(see_engine* h, int advance_step) {
+  return Done(h, h->engine->TrainForwardBackward(advance_step != 0));
+}
+int see_engine_train_optimizer(see_engine* h) { return Done(h, h->engine->TrainOptimizer()); }
+int see_engine_step_program(see_engine* h) { return Done(h, h->engine->StepProgram()); }
+int see_engine_read_loss(see_engine* h, float* loss) { return Done(h, h->engine->ReadLoss(loss)); }
+int see_engine_evaluate(see_engine* h, float* loss, uint64_t* rows, uint64_t* correct) {
+  see::EvalResult r;
+  if (auto s = h->engine->Evaluate(&r); !s) return Fail(h, s.error());
+  if (loss) *loss = r.loss;
+  if (rows) *rows = r.rows;
+  if (correct) *correct = r.correct;
+  return SEE_OK;
+}
+int see_engine_run_merge(see_engine* h, int* all_finite) {
+  bool finite = false;
+  if (auto s = h->engine->RunMerge(&finite); !s) return Fail(h, s.error());
+  if (all_finite) *all_finite = finite ? 1 : 0;
+  return SEE_OK;
+}
+int see_engine_read_arena(see_engine* h, uint64_t offset, uint64_t bytes, void* dst) {
+  return Done(h, h->engine->ReadArena(offset, bytes, dst));
+}
+int see_engine_write_arena(see_engine* h, uint64_t offset, uint64_t bytes, const void* src) {
+  return Done(h, h->engine->WriteArena(offset, bytes, src));
+}
+uint64_t see_engine_step(see_engine* h) { return h->engine->step(); }
+int see_engine_set_step(see_engine* h, uint64_t step) { h->engine->SetStep(step); return SEE_OK; }
+int see_engine_set_horizon(see_engine* h, uint64_t steps) { h->engine->SetHorizon(steps); return SEE_OK; }
+float see_engine_effective_lr(see_engine* h) { return h->engine->EffectiveLr(); }
+int see_engine_set_use_graphs(see_engine* h, int on) { h->engine->SetUseGraphs(on != 0); return SEE_OK; }
+int see_engine_set_phase_timing(see_engine* h, int on) { h->engine->SetPhaseTiming(on != 0); return SEE_OK; }
+int see_engine_take_timings(see_engine* h, float* forward_ms, float* backward_ms,
+                            float* optimizer_ms, uint64_t* steps) {
+  const see::StepTimings t = h->engine->TakeTimings();
+  if (forward_ms) *forward_ms = t.forward;
+  if (backward_ms) *backward_ms = t.backward;
+  if (optimizer_ms) *optimizer_ms = t.optimizer;
+  if (steps) *steps = t.steps;
+  return SEE_OK;
+}
+int see_engine_gradient_block(see_engine* h, uint64_t* offset, uint64_t* bytes) {
+  h->engine->GradientBlock(offset, bytes);
+  return SEE_OK;
 }
 
 }  // extern "C"

@@ -93,6 +93,7 @@ CudaBackend::~CudaBackend() {
   cudaSetDevice(device_);
   if (stream_) cudaStreamSynchronize(stream_);
   for (auto& ev : events_) { cudaEventDestroy(ev.first); cudaEventDestroy(ev.second); }
+  for (auto& ev : kernel_events_) { cudaEventDestroy(ev.first); cudaEventDestroy(ev.second); }
   if (umma_) umma::Destroy(&umma_->ctx);
   cudaFree(d_arena_);
   cudaFree(d_rodata_);
@@ -148,6 +149,75 @@ Status CudaBackend::Bind(uint8_t* arena, uint64_t arena_bytes, const uint8_t* ro
   deferred_error_.clear();
   scalars_valid_ = false;
   umma::InvalidateAll(&umma_->ctx);
+  return {};
+}
+
+Status CudaBackend::BindDeviceImage(uint64_t arena_bytes, const uint8_t* prefix,
+                                    uint64_t prefix_bytes, const uint8_t* rodata,
+                                    uint64_t rodata_bytes) {
+  if (arena_bytes == 0 || prefix_bytes > arena_bytes)
+    return std::unexpected("cuda: bind: bad arena image");
+  cudaSetDevice(device_);
+  void* new_arena = nullptr;
+  void* new_rodata = nullptr;
+  auto fail = [&](cudaError_t e, const char* what) -> Status {
+    cudaFree(new_arena);
+    cudaFree(new_rodata);
+    return std::unexpected(CudaErr(e, what));
+  };
+  if (auto e = cudaMalloc(&new_arena, arena_bytes); e != cudaSuccess) return fail(e, "bind: arena slab");
+  if (auto e = cudaMemsetAsync(new_arena, 0, arena_bytes, stream_); e != cudaSuccess)
+    return fail(e, "bind: arena clear");
+  if (prefix_bytes)
+    if (auto e = cudaMemcpyAsync(new_arena, prefix, prefix_bytes, cudaMemcpyHostToDevice, stream_);
+        e != cudaSuccess)
+      return fail(e, "bind: persistent image upload");
+  if (rodata_bytes) {
+    if (auto e = cudaMalloc(&new_rodata, rodata_bytes + 64); e != cudaSuccess) return fail(e, "bind: rodata");
+    if (auto e = cudaMemcpyAsync(new_rodata, rodata, rodata_bytes, cudaMemcpyHostToDevice, stream_);
+        e != cudaSuccess)
+      return fail(e, "bind: rodata upload");
+  }
+  if (auto e = cudaStreamSynchronize(stream_); e != cudaSuccess) return fail(e, "bind: sync");
+  cudaFree(d_arena_);
+  cudaFree(d_rodata_);
+  d_arena_ = static_cast<uint8_t*>(new_arena);
+  d_rodata_ = static_cast<uint8_t*>(new_rodata);
+  host_arena_ = nullptr;
+  arena_bytes_ = arena_bytes;
+  rodata_bytes_ = rodata_bytes;
+  coherence_ = Coherence::kLazy;
+  counters_.h2d_bytes += prefix_bytes + rodata_bytes;
+  host_dirty_.clear();
+  device_dirty_.clear();
+  deferred_error_.clear();
+  scalars_valid_ = false;
+  umma::InvalidateAll(&umma_->ctx);
+  return {};
+}
+
+Status CudaBackend::ReadArena(uint64_t off, uint64_t bytes, void* dst) {
+  if (!d_arena_) return std::unexpected("cuda: nothing is bound");
+  if (off > arena_bytes_ || bytes > arena_bytes_ - off)
+    return std::unexpected("cuda: read: range outside the arena");
+  cudaSetDevice(device_);
+  if (auto r = Check(cudaMemcpyAsync(dst, d_arena_ + off, bytes, cudaMemcpyDeviceToHost, stream_),
+                     "read"); !r)
+    return r;
+  counters_.d2h_bytes += bytes;
+  return Check(cudaStreamSynchronize(stream_), "read sync");
+}
+
+Status CudaBackend::WriteArena(uint64_t off, uint64_t bytes, const void* src) {
+  if (!d_arena_) return std::unexpected("cuda: nothing is bound");
+  if (off > arena_bytes_ || bytes > arena_bytes_ - off)
+    return std::unexpected("cuda: write: range outside the arena");
+  cudaSetDevice(device_);
+  if (auto r = Check(cudaMemcpyAsync(d_arena_ + off, src, bytes, cudaMemcpyHostToDevice, stream_),
+                     "write"); !r)
+    return r;
+  counters_.h2d_bytes += bytes;
+  umma::InvalidateRange(&umma_->ctx, off, bytes);
   return {};
 }
 
@@ -216,6 +286,11 @@ std::vector<ProfileRecord> CudaBackend::TakeProfile() {
     float ms = 0.0f;
     cudaEventElapsedTime(&ms, events_[i].first, events_[i].second);
     pending_profile_[i].ms = ms;
+    if (pending_profile_[i].has_kernel) {
+      float kms = 0.0f;
+      cudaEventElapsedTime(&kms, kernel_events_[i].first, kernel_events_[i].second);
+      pending_profile_[i].kernel_ms = kms;
+    }
   }
   std::vector<ProfileRecord> out;
   out.swap(pending_profile_);
@@ -266,6 +341,9 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
     }
   }
   umma::PlanRange(&umma_->ctx, program.data(), begin, std::min(end, program.size()));
+  // Cached bf16 activation copies do not outlive a range: a range replayed as a
+  // CUDA graph must contain every conversion it depends on.
+  umma::InvalidateRange(&umma_->ctx, 0, arena_bytes_);
   range_index_ = 0;
 }
 
@@ -324,7 +402,12 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
       cudaEventCreate(&a);
       cudaEventCreate(&b);
       events_.push_back({a, b});
+      cudaEvent_t c, d;
+      cudaEventCreate(&c);
+      cudaEventCreate(&d);
+      kernel_events_.push_back({c, d});
     }
+    umma::SetProfileEvents(&umma_->ctx, kernel_events_[slot].first, kernel_events_[slot].second);
     ev0 = events_[slot].first;
     ev1 = events_[slot].second;
     cudaEventRecord(ev0, stream_);
@@ -336,6 +419,7 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   if (profiling_) {
     cudaEventRecord(ev1, stream_);
     ProfileRecord rec{ins.opcode, range_index_, 0.0f, 0, 0, 0};
+    rec.has_kernel = umma::ProfileEventsUsed(&umma_->ctx);
     if (ins.opcode <= kGemmAccNN || ins.opcode == kGemmNNQ8 || ins.opcode == kGemmNTQ8 ||
         ins.opcode == kGemmNNBF16 || ins.opcode == kGemmNTBF16) {
       rec.m = ins.out[0]; rec.n = ins.out[1]; rec.k = ins.out[2];
@@ -402,17 +486,35 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
   return {};
 }
 
+k::AdamScalars CudaBackend::ScalarsOf(const StepParams& params) {
+  k::AdamScalars sc{};
+  sc.lr = params.lr; sc.beta1 = params.beta1; sc.beta2 = params.beta2; sc.eps = params.eps;
+  sc.weight_decay = params.weight_decay;
+  sc.inv_bc1 = 1.0f / (1.0f - std::pow(params.beta1, static_cast<float>(params.step)));
+  sc.inv_bc2 = 1.0f / (1.0f - std::pow(params.beta2, static_cast<float>(params.step)));
+  return sc;
+}
+
+void CudaBackend::SetCapturing(bool on) {
+  capturing_ = on;
+  scalars_valid_ = false;  // the first optimizer instruction re-uploads (into the graph)
+}
+
+void CudaBackend::UpdateReplayScalars(const StepParams& params) {
+  h_scalars_[0] = ScalarsOf(params);
+  scalars_valid_ = false;
+}
+
 Status CudaBackend::DispatchOptimizer(const Instruction& ins, const StepParams& params) {
   // Per-range scalars, computed with the host libm exactly as the CPU executor
   // computes them (reference: runtime/executor/optimizer.cc:113-118), uploaded
   // once per distinct StepParams.
   if (!scalars_valid_ || std::memcmp(&params, &last_params_, sizeof(StepParams)) != 0) {
-    k::AdamScalars sc{};
-    sc.lr = params.lr; sc.beta1 = params.beta1; sc.beta2 = params.beta2; sc.eps = params.eps;
-    sc.weight_decay = params.weight_decay;
-    sc.inv_bc1 = 1.0f / (1.0f - std::pow(params.beta1, static_cast<float>(params.step)));
-    sc.inv_bc2 = 1.0f / (1.0f - std::pow(params.beta2, static_cast<float>(params.step)));
-    scalar_slot_ = (scalar_slot_ + 1) % kScalarSlots;
+    const k::AdamScalars sc = ScalarsOf(params);
+    // Slot 0 is the replay slot: a copy captured into a CUDA graph reads it at
+    // every replay, after UpdateReplayScalars rewrote it.  Eager uploads rotate
+    // through the other slots so a pending copy is never overwritten.
+    scalar_slot_ = capturing_ ? 0 : 1 + (scalar_slot_ % (kScalarSlots - 1));
     h_scalars_[scalar_slot_] = sc;
     if (auto r = Check(cudaMemcpyAsync(d_scalars_, &h_scalars_[scalar_slot_], sizeof(sc),
                                        cudaMemcpyHostToDevice, stream_), "step scalars"); !r)

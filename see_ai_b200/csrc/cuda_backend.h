@@ -57,7 +57,9 @@ struct Counters {
 };
 
 // One timed instruction (profile mode): opcode, index in the range, milliseconds.
-struct ProfileRecord { uint16_t opcode; uint32_t index; float ms; uint64_t m, n, k; };
+// kernel_ms > 0 only for instructions that ran on the tensor-core GEMM: the
+// kernel alone, without the operand conversions that ms also covers.
+struct ProfileRecord { uint16_t opcode; uint32_t index; float ms; uint64_t m, n, k; float kernel_ms = 0.0f; bool has_kernel = false; };
 
 class CudaBackend {
  public:
@@ -73,6 +75,18 @@ class CudaBackend {
   Status Bind(uint8_t* arena, uint64_t arena_bytes, const uint8_t* rodata, uint64_t rodata_bytes,
               uint64_t rodata_mapped_bytes);
   Status BindSource(const uint8_t* data, uint64_t bytes);
+  // The engine's form of Bind: the slab is created on the device as the
+  // runtime's arena is created on the host — zeroed, then the persistent image
+  // copied to offset 0 (reference: runtime/loader/plan_loader.cc:251-288) — with
+  // no host mirror at all.  Coherence is then lazy by construction: the engine
+  // moves bytes with ReadArena / WriteArena.
+  Status BindDeviceImage(uint64_t arena_bytes, const uint8_t* prefix, uint64_t prefix_bytes,
+                         const uint8_t* rodata, uint64_t rodata_bytes);
+  // Synchronous device -> dst.  Orders after everything enqueued so far.
+  Status ReadArena(uint64_t off, uint64_t bytes, void* dst);
+  // Asynchronous src -> device on the backend's stream; `src` must stay valid
+  // until the stream has passed the copy (pinned memory for true overlap).
+  Status WriteArena(uint64_t off, uint64_t bytes, const void* src);
   void Configure() {}  // the CPU tile policy is throughput-only on its own backend; ignored here
 
   Status Execute(const Instruction& ins, const StepParams& params);
@@ -106,6 +120,14 @@ class CudaBackend {
   // permission (default: allowed).  The exact kernels are always a valid
   // execution of a relaxed instruction.
   void SetRelaxedAllowed(bool allowed) { relaxed_allowed_ = allowed; }
+
+  // CUDA-graph support for the engine.  While capturing, the per-range scalar
+  // upload is recorded from a fixed pinned slot; before each replay the engine
+  // rewrites that slot with the step's scalars (UpdateReplayScalars), so the
+  // captured copy delivers the current learning rate and bias corrections.
+  void SetCapturing(bool on);
+  void UpdateReplayScalars(const StepParams& params);
+  static k::AdamScalars ScalarsOf(const StepParams& params);
 
   // Profile mode: every instruction is bracketed by CUDA events on the stream.
   void SetProfiling(bool on);
@@ -162,6 +184,7 @@ class CudaBackend {
   int scalar_slot_ = 0;
   StepParams last_params_{};
   bool scalars_valid_ = false;
+  bool capturing_ = false;
   int* h_status_ = nullptr;  // pinned mirror of the status words
 
   Coherence coherence_ = Coherence::kStrict;
@@ -176,6 +199,7 @@ class CudaBackend {
   bool relaxed_allowed_ = true;
   bool profiling_ = false;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> events_;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> kernel_events_;
   std::vector<ProfileRecord> pending_profile_;
   uint32_t range_index_ = 0;
 

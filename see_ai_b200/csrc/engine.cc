@@ -1,0 +1,428 @@
+#include "engine.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstddef>
+#include <cstring>
+
+#include "extents.h"
+
+namespace see {
+
+// ---- the seal -------------------------------------------------------------------
+namespace {
+
+constexpr uint64_t kFnvOffset = 0xcbf29ce484222325ull;
+constexpr uint64_t kFnvPrime = 0x100000001b3ull;
+constexpr size_t kHashChunk = size_t{1} << 20;
+constexpr size_t kMaxChunks = 256;
+
+uint64_t MixWord(uint64_t state, uint64_t word) {
+  for (int b = 0; b < 8; ++b) {
+    state ^= (word >> (8 * b)) & 0xff;
+    state *= kFnvPrime;
+  }
+  return state;
+}
+
+// Eight interleaved FNV-1a lanes; byte i feeds lane i mod 8; bytes inside
+// [skip_begin, skip_end) are read as zero.
+uint64_t StripedFnv(const uint8_t* data, size_t size, size_t base, size_t skip_begin,
+                    size_t skip_end) {
+  uint64_t lane[8];
+  for (size_t l = 0; l < 8; ++l) lane[l] = kFnvOffset ^ (0x9E3779B97F4A7C15ull * (l + 1));
+  for (size_t i = 0; i < size; ++i) {
+    const size_t at = base + i;
+    const uint8_t byte = (at >= skip_begin && at < skip_end) ? 0 : data[i];
+    lane[i % 8] ^= byte;
+    lane[i % 8] *= kFnvPrime;
+  }
+  uint64_t h = kFnvOffset;
+  for (size_t l = 0; l < 8; ++l) h = MixWord(h, lane[l]);
+  return MixWord(h, size);
+}
+
+}  // namespace
+
+uint64_t PlanSelfHash(const uint8_t* plan, size_t size, size_t hash_offset) {
+  const size_t cap = (size + kMaxChunks - 1) / kMaxChunks;
+  const size_t grain = std::max(kHashChunk, std::max<size_t>(cap, 1));
+  uint64_t h = kFnvOffset;
+  if (size == 0) {
+    h = MixWord(h, StripedFnv(plan, 0, 0, hash_offset, hash_offset + 8));
+  } else {
+    for (size_t b = 0; b < size; b += grain) {
+      const size_t e = std::min(b + grain, size);
+      h = MixWord(h, StripedFnv(plan + b, e - b, b, hash_offset, hash_offset + 8));
+    }
+  }
+  return MixWord(h, size);
+}
+
+PhaseBoundaries ScanPhases(const std::vector<Instruction>& train) {
+  PhaseBoundaries p{train.size(), train.size()};
+  for (size_t i = 0; i < train.size(); ++i) {
+    const uint16_t op = train[i].opcode;
+    if (op == kSoftmaxXEntFwd || op == kSoftmaxXEntMaskedFwd || op == kMseFwd || op == kKLDistillFwd)
+      p.bwd_begin = i + 1;
+    if ((op == kClipNorm || op == kSqNormAccum || op == kClipGlobal || op == kSgdStep ||
+         op == kAdamWStep) && p.opt_begin == train.size())
+      p.opt_begin = i;
+  }
+  if (p.opt_begin < p.bwd_begin) p.opt_begin = p.bwd_begin;
+  return p;
+}
+
+// ---- lifecycle ---------------------------------------------------------------------
+
+std::expected<std::unique_ptr<UpdateEngine>, std::string> UpdateEngine::Create(int device) {
+  auto backend = CudaBackend::Create(device);
+  if (!backend) return std::unexpected(backend.error());
+  std::unique_ptr<UpdateEngine> e(new UpdateEngine);
+  e->backend_ = std::move(*backend);
+  for (auto& ev : e->ev_)
+    if (cudaEventCreate(&ev) != cudaSuccess) return std::unexpected("cuda: event creation failed");
+  for (auto& ev : e->staged_)
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess)
+      return std::unexpected("cuda: event creation failed");
+  void* p = nullptr;
+  if (cudaMalloc(&p, 4 * sizeof(unsigned long long)) != cudaSuccess)
+    return std::unexpected("cuda: tally allocation failed");
+  e->d_tally_ = static_cast<unsigned long long*>(p);
+  return e;
+}
+
+void UpdateEngine::DropGraphs() {
+  for (GraphSlot* g : {&g_fwdbwd_, &g_opt_, &g_eval_, &g_step_}) {
+    if (g->exec) cudaGraphExecDestroy(g->exec);
+    g->exec = nullptr;
+    g->runs = 0;
+  }
+}
+
+UpdateEngine::~UpdateEngine() {
+  if (backend_) cudaStreamSynchronize(backend_->stream());
+  DropGraphs();
+  for (auto& ev : ev_) if (ev) cudaEventDestroy(ev);
+  for (auto& ev : staged_) if (ev) cudaEventDestroy(ev);
+  if (pinned_) cudaFreeHost(pinned_);
+  cudaFree(d_tally_);
+}
+
+const std::vector<Instruction>& UpdateEngine::program(int which) const {
+  switch (which) {
+    case 1: return eval_;
+    case 2: return merge_;
+    case 3: return step_prog_;
+    default: return train_;
+  }
+}
+
+Status UpdateEngine::LoadFromMemory(const uint8_t* plan, uint64_t size) {
+  if (size < sizeof(PlanHeader)) return std::unexpected("engine: plan is truncated");
+  PlanHeader h;
+  std::memcpy(&h, plan, sizeof(h));
+  if (h.magic != kSeeuMagic) return std::unexpected("engine: not a .seeu plan");
+  if (h.version < kSeeuOldestReadable || h.version > kSeeuVersion)
+    return std::unexpected("engine: unsupported plan version " + std::to_string(h.version));
+  if (PlanSelfHash(plan, size, offsetof(PlanHeader, plan_hash)) != h.plan_hash)
+    return std::unexpected("engine: plan integrity check failed (plan_hash)");
+  auto range_ok = [&](uint64_t off, uint64_t bytes) { return off <= size && bytes <= size - off; };
+  auto decode = [&](uint64_t off, uint64_t count, std::vector<Instruction>* out) -> bool {
+    if (count > size / sizeof(Instruction) || !range_ok(off, count * sizeof(Instruction))) return false;
+    out->resize(count);
+    if (count) std::memcpy(out->data(), plan + off, count * sizeof(Instruction));
+    return true;
+  };
+  std::vector<Instruction> train, eval, merge, step;
+  if (!decode(h.train_instr_offset, h.train_instr_count, &train) ||
+      !decode(h.eval_instr_offset, h.eval_instr_count, &eval) ||
+      !decode(h.merge_instr_offset, h.merge_instr_count, &merge) ||
+      !decode(h.step_instr_offset, h.step_instr_count, &step) ||
+      !range_ok(h.rodata_offset, h.rodata_size) ||
+      !range_ok(h.persist_init_offset, h.persist_init_size) ||
+      h.emit_count > size / sizeof(EmitEntry) ||
+      !range_ok(h.emit_table_offset, h.emit_count * sizeof(EmitEntry)))
+    return std::unexpected("engine: a plan section lies outside the file");
+  if (h.persist_init_size != h.persistent_size || h.persistent_size > h.arena_size)
+    return std::unexpected("engine: persistent image does not match the header");
+  if (h.arena_size == 0) return std::unexpected("engine: empty arena");
+  auto slot_ok = [&](uint64_t ref, uint64_t bytes) {
+    return ref == kNullRef || (RefSpace(ref) == kArena && ref % 4 == 0 && ref <= h.arena_size &&
+                               bytes <= h.arena_size - ref);
+  };
+  if (!slot_ok(h.input_ref, h.input_floats * 4) || !slot_ok(h.label_ref, h.label_bytes) ||
+      !slot_ok(h.loss_ref, 4))
+    return std::unexpected("engine: an I/O slot lies outside the arena");
+  // Every operand of every instruction is proven inside its address space once,
+  // here; source refs are checked again at execution against the bound file.
+  const uint64_t arena_alloc = (h.arena_size + kArenaAlignment - 1) / kArenaAlignment * kArenaAlignment;
+  const std::pair<const char*, const std::vector<Instruction>*> sections[] = {
+      {"train", &train}, {"eval", &eval}, {"merge", &merge}, {"step", &step}};
+  for (const auto& [name, prog] : sections) {
+    for (size_t i = 0; i < prog->size(); ++i) {
+      Extents ext;
+      const std::string e = DescribeInstruction((*prog)[i], h.arena_size, h.rodata_size,
+                                                /*source_bytes=*/uint64_t{1} << 48, &ext);
+      if (!e.empty())
+        return std::unexpected(std::string("engine: ") + name + " instruction " + std::to_string(i) +
+                               ": " + e);
+    }
+  }
+  // The optimizer steps' gradient operands, as one block.
+  uint64_t g_lo = ~0ull, g_hi = 0;
+  const auto& opt_prog = step.empty() ? train : step;
+  for (const Instruction& ins : opt_prog)
+    if (ins.opcode == kAdamWStep || ins.opcode == kSgdStep) {
+      g_lo = std::min(g_lo, RefOffset(ins.in[1]));
+      g_hi = std::max(g_hi, RefOffset(ins.in[1]) + ins.out[0] * 4);
+    }
+
+  if (auto r = backend_->BindDeviceImage(arena_alloc, plan + h.persist_init_offset,
+                                         h.persist_init_size, plan + h.rodata_offset, h.rodata_size);
+      !r)
+    return r;  // the previous plan, if any, stays bound
+
+  DropGraphs();
+  header_ = h;
+  train_ = std::move(train);
+  eval_ = std::move(eval);
+  merge_ = std::move(merge);
+  step_prog_ = std::move(step);
+  emit_.resize(h.emit_count);
+  if (h.emit_count) std::memcpy(emit_.data(), plan + h.emit_table_offset, h.emit_count * sizeof(EmitEntry));
+  phases_ = ScanPhases(train_);
+  grad_off_ = g_lo == ~0ull ? 0 : g_lo;
+  grad_bytes_ = g_lo == ~0ull ? 0 : g_hi - g_lo;
+  step_ = 0;
+  horizon_ = h.default_steps;
+  eval_probs_ref_ = eval_labels_ref_ = kNullRef;
+  for (const Instruction& ins : eval_)
+    if (ins.opcode == kSoftmaxXEntFwd || ins.opcode == kSoftmaxXEntMaskedFwd) {
+      eval_probs_ref_ = ins.in[3];
+      eval_labels_ref_ = ins.in[1];
+      eval_rows_ = ins.out[0];
+      eval_cols_ = ins.out[1];
+    }
+  const uint64_t stage = (h.input_ref == kNullRef ? 0 : h.input_floats * 4) +
+                         (h.label_ref == kNullRef ? 0 : h.label_bytes);
+  if (stage > pinned_bytes_) {
+    if (pinned_) cudaFreeHost(pinned_);
+    pinned_ = nullptr;
+    pinned_bytes_ = 0;
+    void* p = nullptr;
+    if (cudaMallocHost(&p, 2 * stage) != cudaSuccess)
+      return std::unexpected("engine: pinned staging allocation failed");
+    pinned_ = static_cast<uint8_t*>(p);
+    pinned_bytes_ = stage;
+  }
+  loaded_ = true;
+  return {};
+}
+
+Status UpdateEngine::BindSourceModel(const uint8_t* data, uint64_t bytes) {
+  return backend_->BindSource(data, bytes);
+}
+
+// reference: runtime/dispatcher/update_engine.cc:370-391
+float UpdateEngine::EffectiveLr() const {
+  const float base = header_.lr;
+  if (header_.lr_schedule != 1) return base;
+  if (header_.warmup_steps > 0 && step_ <= header_.warmup_steps)
+    return base * static_cast<float>(step_) / static_cast<float>(header_.warmup_steps);
+  const uint64_t run = horizon_;
+  const uint64_t horizon = run > header_.warmup_steps ? run - header_.warmup_steps : 0;
+  const float floor = base * header_.min_lr_factor;
+  if (horizon == 0 || step_ - header_.warmup_steps >= horizon) return floor;
+  const float t = static_cast<float>(step_ - header_.warmup_steps) / static_cast<float>(horizon);
+  constexpr float kPi = 3.14159265358979323846f;
+  return floor + (base - floor) * 0.5f * (1.0f + std::cos(kPi * t));
+}
+
+StepParams UpdateEngine::MakeParams() const {
+  StepParams p;
+  p.lr = EffectiveLr();
+  p.beta1 = header_.beta1; p.beta2 = header_.beta2; p.eps = header_.eps;
+  p.weight_decay = header_.weight_decay;
+  p.step = step_;
+  return p;
+}
+
+Status UpdateEngine::StageBatch(const void* input, uint64_t input_bytes, const void* labels,
+                                uint64_t label_bytes) {
+  if (!loaded_) return std::unexpected("engine: no plan is loaded");
+  const uint64_t want_in = header_.input_ref == kNullRef ? 0 : header_.input_floats * 4;
+  const uint64_t want_lab = header_.label_ref == kNullRef ? 0 : header_.label_bytes;
+  if (input_bytes != want_in || label_bytes != want_lab)
+    return std::unexpected("engine: batch size does not match the plan's I/O slots");
+  // Double-buffered pinned staging: wait until the copy that last used this
+  // half has been consumed, fill it, enqueue the async upload.
+  uint8_t* buf = pinned_ + static_cast<uint64_t>(pinned_slot_) * pinned_bytes_;
+  cudaEventSynchronize(staged_[pinned_slot_]);
+  if (want_in) std::memcpy(buf, input, want_in);
+  if (want_lab) std::memcpy(buf + want_in, labels, want_lab);
+  if (want_in)
+    if (auto r = backend_->WriteArena(RefOffset(header_.input_ref), want_in, buf); !r) return r;
+  if (want_lab)
+    if (auto r = backend_->WriteArena(RefOffset(header_.label_ref), want_lab, buf + want_in); !r)
+      return r;
+  cudaEventRecord(staged_[pinned_slot_], backend_->stream());
+  pinned_slot_ ^= 1;
+  return {};
+}
+
+Status UpdateEngine::RunRange(const std::vector<Instruction>& prog, size_t begin, size_t end,
+                              GraphSlot* slot, float* phase_ms) {
+  if (!loaded_) return std::unexpected("engine: no plan is loaded");
+  if (begin >= end) return {};
+  const StepParams params = MakeParams();
+  cudaStream_t s = backend_->stream();
+  if (phase_ms) cudaEventRecord(ev_[0], s);
+  const std::span<const Instruction> span(prog.data(), prog.size());
+  Status result{};
+  if (use_graphs_ && slot && slot->exec) {
+    backend_->UpdateReplayScalars(params);
+    if (auto e = cudaGraphLaunch(slot->exec, s); e != cudaSuccess)
+      return std::unexpected(std::string("engine: graph launch: ") + cudaGetErrorString(e));
+  } else {
+    backend_->BeginRange(span, begin, end);
+    const bool capture = use_graphs_ && slot && slot->runs >= 1;
+    cudaGraph_t graph = nullptr;
+    if (capture) {
+      backend_->SetCapturing(true);
+      if (auto e = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal); e != cudaSuccess) {
+        backend_->SetCapturing(false);
+        return std::unexpected(std::string("engine: begin capture: ") + cudaGetErrorString(e));
+      }
+    }
+    for (size_t i = begin; i < end; ++i) {
+      if (auto r = backend_->Execute(prog[i], params); !r) {
+        result = std::unexpected("instruction " + std::to_string(i) + ": " + r.error());
+        break;
+      }
+    }
+    if (capture) {
+      const cudaError_t e = cudaStreamEndCapture(s, &graph);
+      backend_->SetCapturing(false);
+      if (e != cudaSuccess || !graph) {
+        if (result) result = std::unexpected(std::string("engine: end capture: ") + cudaGetErrorString(e));
+      } else if (result) {
+        cudaGraphExec_t exec = nullptr;
+        if (auto ie = cudaGraphInstantiate(&exec, graph, 0); ie != cudaSuccess) {
+          result = std::unexpected(std::string("engine: graph instantiate: ") + cudaGetErrorString(ie));
+        } else {
+          slot->exec = exec;
+          backend_->UpdateReplayScalars(params);
+          if (auto le = cudaGraphLaunch(exec, s); le != cudaSuccess)
+            result = std::unexpected(std::string("engine: graph launch: ") + cudaGetErrorString(le));
+        }
+      }
+      if (graph) cudaGraphDestroy(graph);
+    }
+    if (slot) ++slot->runs;
+    backend_->EndRange();
+  }
+  if (phase_ms) {
+    cudaEventRecord(ev_[1], s);
+    cudaEventSynchronize(ev_[1]);
+    cudaEventElapsedTime(phase_ms, ev_[0], ev_[1]);
+  }
+  return result;
+}
+
+Status UpdateEngine::TrainForwardBackward(bool advance) {
+  if (advance) ++step_;
+  if (step_ == 0) step_ = 1;  // AdamW's timestep is 1-indexed
+  if (!phase_timing_) return RunRange(train_, 0, phases_.opt_begin, &g_fwdbwd_, nullptr);
+  // Phase timing splits forward from backward at the loss (two ranges, no graph).
+  float f = 0, b = 0;
+  if (auto r = RunRange(train_, 0, phases_.bwd_begin, nullptr, &f); !r) return r;
+  if (auto r = RunRange(train_, phases_.bwd_begin, phases_.opt_begin, nullptr, &b); !r) return r;
+  timings_.forward += f;
+  timings_.backward += b;
+  return {};
+}
+
+Status UpdateEngine::TrainOptimizer() {
+  float o = 0;
+  auto r = RunRange(train_, phases_.opt_begin, train_.size(), phase_timing_ ? nullptr : &g_opt_,
+                    phase_timing_ ? &o : nullptr);
+  if (phase_timing_) {
+    timings_.optimizer += o;
+    if (step_prog_.empty()) ++timings_.steps;
+  }
+  return r;
+}
+
+Status UpdateEngine::StepProgram() {
+  float o = 0;
+  auto r = RunRange(step_prog_, 0, step_prog_.size(), phase_timing_ ? nullptr : &g_step_,
+                    phase_timing_ ? &o : nullptr);
+  if (phase_timing_) {
+    timings_.optimizer += o;
+    ++timings_.steps;
+  }
+  return r;
+}
+
+StepTimings UpdateEngine::TakeTimings() {
+  StepTimings t = timings_;
+  timings_ = StepTimings{};
+  return t;
+}
+
+Status UpdateEngine::ReadLoss(float* loss) {
+  if (header_.loss_ref == kNullRef) return std::unexpected("engine: the plan has no loss slot");
+  if (auto r = backend_->ReadArena(RefOffset(header_.loss_ref), 4, loss); !r) return r;
+  return backend_->Flush();  // surfaces a refusal raised on the device
+}
+
+Status UpdateEngine::Evaluate(EvalResult* out) {
+  if (auto r = RunRange(eval_, 0, eval_.size(), &g_eval_, nullptr); !r) return r;
+  cudaStream_t s = backend_->stream();
+  cudaMemsetAsync(d_tally_, 0, 4 * sizeof(unsigned long long), s);
+  if (eval_probs_ref_ != kNullRef) {
+    const float* probs = reinterpret_cast<const float*>(backend_->device_arena() + RefOffset(eval_probs_ref_));
+    const int32_t* labels = reinterpret_cast<const int32_t*>(backend_->device_arena() + RefOffset(eval_labels_ref_));
+    k::ArgmaxTally(probs, labels, eval_rows_, eval_cols_, d_tally_, s);
+  }
+  unsigned long long tally[4] = {0, 0, 0, 0};
+  if (auto e = cudaMemcpyAsync(tally, d_tally_, sizeof(tally), cudaMemcpyDeviceToHost, s); e != cudaSuccess)
+    return std::unexpected(std::string("engine: tally read: ") + cudaGetErrorString(e));
+  if (auto r = ReadLoss(&out->loss); !r) return r;
+  out->rows = tally[0];
+  out->correct = tally[1];
+  return {};
+}
+
+Status UpdateEngine::RunMerge(bool* all_finite) {
+  if (auto r = RunRange(merge_, 0, merge_.size(), nullptr, nullptr); !r) return r;
+  cudaStream_t s = backend_->stream();
+  cudaMemsetAsync(d_tally_, 0, 4 * sizeof(unsigned long long), s);
+  for (const EmitEntry& e : emit_) {
+    if (e.arena_offset > header_.arena_size || e.byte_size > header_.arena_size - e.arena_offset)
+      return std::unexpected("engine: an emit entry lies outside the arena");
+    k::CountNonFinite(reinterpret_cast<const float*>(backend_->device_arena() + e.arena_offset),
+                      e.byte_size / 4, d_tally_, s);
+  }
+  unsigned long long tally[4] = {0, 0, 0, 0};
+  if (auto e = cudaMemcpyAsync(tally, d_tally_, sizeof(tally), cudaMemcpyDeviceToHost, s); e != cudaSuccess)
+    return std::unexpected(std::string("engine: tally read: ") + cudaGetErrorString(e));
+  if (auto r = backend_->Flush(); !r) return r;
+  if (all_finite) *all_finite = tally[2] == 0;
+  return {};
+}
+
+Status UpdateEngine::WriteArena(uint64_t off, uint64_t bytes, const void* src) {
+  if (auto r = backend_->WriteArena(off, bytes, src); !r) return r;
+  // The source is the caller's (pageable) memory: finish the copy before returning.
+  if (auto e = cudaStreamSynchronize(backend_->stream()); e != cudaSuccess)
+    return std::unexpected(std::string("engine: write: ") + cudaGetErrorString(e));
+  return {};
+}
+
+Status UpdateEngine::WritePersistent(const void* src) {
+  return WriteArena(0, header_.persistent_size, src);
+}
+
+}  // namespace see

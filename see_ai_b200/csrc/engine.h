@@ -1,0 +1,131 @@
+// UpdateEngine — the dispatcher over the CUDA executor: loads a sealed plan,
+// owns the device slab, runs the plan's programs as ranges through
+// CudaBackend exactly as the reference engine runs them through its backend,
+// and keeps the host-side scalars (timestep, scheduled learning rate) the
+// way the reference does.  Mirrors the hot-path surface of
+// seeml::update_rt::UpdateEngine (reference: runtime/dispatcher/update_engine.h:211-367;
+// ExecuteRange update_engine.cc:325-364; EffectiveLr :370-391; the train loop
+// :817-924; Evaluate :432-580; RunMerge :1028-1063).  What the reference does
+// on the host over unified memory — the accuracy argmax over the probabilities,
+// the finiteness scan of the merged deltas — runs here on the device, so only
+// scalars cross the bus.
+#ifndef SEE_CUDA_ENGINE_H_
+#define SEE_CUDA_ENGINE_H_
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <expected>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "cuda_backend.h"
+#include "plan_abi.h"
+
+namespace see {
+
+// Chunked, striped FNV-1a over a plan blob with its own hash field read as
+// zero (reference: source/identity/hash.h:80-161).
+uint64_t PlanSelfHash(const uint8_t* plan, size_t size, size_t hash_offset);
+
+struct PhaseBoundaries { size_t bwd_begin = 0, opt_begin = 0; };
+// reference: runtime/profiler/step_timings.h:37-59
+PhaseBoundaries ScanPhases(const std::vector<Instruction>& train);
+
+struct StepTimings {   // milliseconds on the device, by CUDA events
+  float forward = 0, backward = 0, optimizer = 0;
+  uint64_t steps = 0;
+};
+
+struct EvalResult {
+  float loss = 0;
+  uint64_t rows = 0;      // loss-target rows scored
+  uint64_t correct = 0;   // argmax == label among them (first maximum wins)
+};
+
+class UpdateEngine {
+ public:
+  static std::expected<std::unique_ptr<UpdateEngine>, std::string> Create(int device);
+  ~UpdateEngine();
+
+  // Decodes and verifies the plan (seal, version window, section bounds, every
+  // instruction's operands), creates the slab — zeroed, persistent image at
+  // offset 0 — and uploads the frozen weights.  A refused load keeps the
+  // previously loaded plan bound and usable.
+  Status LoadFromMemory(const uint8_t* plan, uint64_t size);
+  Status BindSourceModel(const uint8_t* data, uint64_t bytes);
+
+  const PlanHeader& header() const { return header_; }
+  CudaBackend& backend() { return *backend_; }
+  uint64_t step() const { return step_; }
+  void SetStep(uint64_t s) { step_ = s; }
+  void SetHorizon(uint64_t steps) { horizon_ = steps; }
+  float EffectiveLr() const;
+
+  // Copies one batch into the plan's I/O slots (host -> device, asynchronous
+  // from an internal pinned double buffer).
+  Status StageBatch(const void* input, uint64_t input_bytes, const void* labels,
+                    uint64_t label_bytes);
+  // One execution of the train program.  With grad accumulation the caller
+  // runs it G times and then StepProgram().  `advance` moves the 1-indexed
+  // timestep first (once per optimizer step).
+  Status TrainForwardBackward(bool advance);   // [0, opt_begin)
+  Status TrainOptimizer();                     // [opt_begin, end)
+  Status StepProgram();
+  Status ReadLoss(float* loss);
+  // Evaluation: the eval program, the loss, and the accuracy tally on device.
+  Status Evaluate(EvalResult* out);
+  // Merge: every adapter's delta, then a device-side finiteness scan.
+  Status RunMerge(bool* all_finite);
+
+  Status ReadArena(uint64_t off, uint64_t bytes, void* dst) { return backend_->ReadArena(off, bytes, dst); }
+  Status WriteArena(uint64_t off, uint64_t bytes, const void* src);
+  Status ReadPersistent(void* dst) { return backend_->ReadArena(0, header_.persistent_size, dst); }
+  Status WritePersistent(const void* src);
+
+  // Replays each phase as a CUDA graph after its first eager execution.
+  void SetUseGraphs(bool on) { use_graphs_ = on; }
+  void SetPhaseTiming(bool on) { phase_timing_ = on; }
+  StepTimings TakeTimings();
+  // The contiguous arena block holding every optimizer step's gradient
+  // operand (what data parallelism exchanges between backward and optimizer).
+  void GradientBlock(uint64_t* off, uint64_t* bytes) const { *off = grad_off_; *bytes = grad_bytes_; }
+  uint64_t train_instructions() const { return train_.size(); }
+  const std::vector<Instruction>& program(int which) const;  // 0 train, 1 eval, 2 merge, 3 step
+
+ private:
+  UpdateEngine() = default;
+  struct GraphSlot {
+    cudaGraphExec_t exec = nullptr;
+    int runs = 0;
+  };
+  Status RunRange(const std::vector<Instruction>& prog, size_t begin, size_t end, GraphSlot* slot,
+                  float* phase_ms);
+  StepParams MakeParams() const;
+  void DropGraphs();
+
+  std::unique_ptr<CudaBackend> backend_;
+  PlanHeader header_{};
+  std::vector<Instruction> train_, eval_, merge_, step_prog_;
+  std::vector<EmitEntry> emit_;
+  PhaseBoundaries phases_;
+  uint64_t step_ = 0, horizon_ = 0;
+  uint64_t grad_off_ = 0, grad_bytes_ = 0;
+  bool use_graphs_ = false, phase_timing_ = false;
+  GraphSlot g_fwdbwd_, g_opt_, g_eval_, g_step_;
+  uint8_t* pinned_ = nullptr;        // staging double buffer
+  uint64_t pinned_bytes_ = 0;
+  int pinned_slot_ = 0;
+  cudaEvent_t staged_[2] = {nullptr, nullptr};
+  cudaEvent_t ev_[4] = {nullptr, nullptr, nullptr, nullptr};
+  StepTimings timings_;
+  unsigned long long* d_tally_ = nullptr;  // {rows, correct, nonfinite}
+  // where the eval program's loss-forward leaves its probabilities
+  uint64_t eval_probs_ref_ = kNullRef, eval_labels_ref_ = kNullRef, eval_rows_ = 0, eval_cols_ = 0;
+  bool loaded_ = false;
+};
+
+}  // namespace see
+
+#endif  // SEE_CUDA_ENGINE_H_

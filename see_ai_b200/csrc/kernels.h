@@ -127,6 +127,13 @@ void AttnDKVTiled(bool want_dk, const float* q, const float* k, const float* v, 
                   const float* stats, float* out, size_t B, size_t S, size_t H, size_t d,
                   cudaStream_t s);
 
+// ---- evaluation / merge tails (integer tallies, exact) -------------------------
+// tally[0] += rows with label >= 0, tally[1] += those whose argmax == label.
+void ArgmaxTally(const float* probs, const int32_t* labels, size_t N, size_t C,
+                 unsigned long long* tally, cudaStream_t s);
+// tally[2] += count of non-finite elements.
+void CountNonFinite(const float* x, size_t n, unsigned long long* tally, cudaStream_t s);
+
 // ---- GEMM -------------------------------------------------------------------
 enum class BType : uint8_t { kF32 = 0, kI8 = 1, kBf16 = 2 };
 struct GemmArgs {

@@ -42,6 +42,8 @@ struct Impl {
   ActCopy acts[kActSlots];
   uint64_t tick = 0;
   k::DeviceStatus* status = nullptr;  // the backend's device status block (not owned)
+  cudaEvent_t prof_before = nullptr, prof_after = nullptr;
+  bool prof_used = false;
 };
 
 std::string Init(Context* ctx, int device, k::DeviceStatus* status) {
@@ -84,7 +86,39 @@ void InvalidateRange(Context* ctx, uint64_t off, uint64_t bytes) {
   }
 }
 
-void PlanRange(Context*, const Instruction*, size_t, size_t) {}
+// Sizes every activation-copy slot for the largest relaxed GEMM of the range
+// before the range starts, so no allocation (and no stream drain) can fall
+// between its instructions — a requirement for replaying the range as a graph.
+void PlanRange(Context* ctx, const Instruction* program, size_t begin, size_t end) {
+  Impl* impl = ctx->impl;
+  if (!impl) return;
+  uint64_t need = 0;
+  for (size_t i = begin; i < end; ++i) {
+    const Instruction& ins = program[i];
+    if (!(ins.flags & kFlagRelaxed)) continue;
+    switch (ins.opcode) {
+      case kGemmNN: case kGemmNT: case kGemmNNQ8: case kGemmNTQ8: case kGemmNNBF16: case kGemmNTBF16:
+        need = std::max(need, ins.out[0] * ins.out[2]);
+        break;
+      default: break;
+    }
+  }
+  if (need == 0) return;
+  bool drained = false;
+  for (auto& slot : impl->acts) {
+    if (slot.capacity >= need) continue;
+    if (!drained) { cudaDeviceSynchronize(); drained = true; }
+    cudaFree(slot.buf);
+    slot.buf = nullptr;
+    slot.capacity = 0;
+    slot.valid = false;
+    void* p = nullptr;
+    if (cudaMalloc(&p, need * 2) == cudaSuccess) {
+      slot.buf = static_cast<uint16_t*>(p);
+      slot.capacity = need;
+    }
+  }
+}
 
 static bool EncodeBf16Map(Impl* impl, CUtensorMap* map, const void* base, uint64_t rows,
                           uint64_t cols, uint32_t box_rows) {
@@ -173,10 +207,31 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
   ep.N = static_cast<uint32_t>(a.N);
   ep.K = static_cast<uint32_t>(a.K);
   ep.status = impl->status;
+  if (impl->prof_before) cudaEventRecord(impl->prof_before, stream);
   if (cudaError_t e = k::UmmaGemmLaunch(map_a, map_b, ep, stream); e != cudaSuccess)
     return std::string("tensor-core GEMM launch: ") + cudaGetErrorString(e);
+  if (impl->prof_after) {
+    cudaEventRecord(impl->prof_after, stream);
+    impl->prof_used = true;
+    impl->prof_before = impl->prof_after = nullptr;
+  }
   ++*launches;
   return {};
+}
+
+void SetProfileEvents(Context* ctx, cudaEvent_t before, cudaEvent_t after) {
+  if (!ctx->impl) return;
+  ctx->impl->prof_before = before;
+  ctx->impl->prof_after = after;
+  ctx->impl->prof_used = false;
+}
+
+bool ProfileEventsUsed(Context* ctx) {
+  if (!ctx->impl) return false;
+  const bool used = ctx->impl->prof_used;
+  ctx->impl->prof_used = false;
+  ctx->impl->prof_before = ctx->impl->prof_after = nullptr;
+  return used;
 }
 
 }  // namespace see::umma

@@ -41,6 +41,12 @@ void PlanRange(Context* ctx, const Instruction* program, size_t begin, size_t en
 std::string TryGemm(Context* ctx, const k::GemmArgs& args, int b_space, uint64_t b_off,
                     uint64_t a_off, uint64_t a_scale_off, cudaStream_t stream, int* launches);
 
+// Profile mode: the next tensor-core launch records `before` / `after` around
+// the kernel itself (not the operand conversions).  Returns whether a launch
+// consumed them since the last call.
+void SetProfileEvents(Context* ctx, cudaEvent_t before, cudaEvent_t after);
+bool ProfileEventsUsed(Context* ctx);
+
 }  // namespace see::umma
 
 #endif  // SEE_CUDA_UMMA_GEMM_H_

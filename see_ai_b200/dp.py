@@ -1,0 +1,90 @@
+"""Single-node data parallelism for update plans: one process per GPU, the
+batch's sequences sharded across ranks, ONE exchange per optimizer step.
+
+The reference has no distributed path at all (its only parallelism is threads
+inside one process).  What shards naturally: every opcode is per-row or
+per-sequence, and the only cross-row reductions are the loss mean and the
+trainable-parameter gradients, which the compiler binds back to back in the
+arena (reference: compiler/backend/allocation/arena_binder.cc:56-77).  So each
+rank runs the plan compiled for global_rows / N rows, and between the backward
+sweep and the first optimizer instruction (the phase boundary of reference
+runtime/profiler/step_timings.h:37-59) the ranks all-gather that one gradient
+block over NCCL into their own HBM.  The AdamW kernel then sums the N copies in
+rank order 0..N-1 and multiplies by the exact power of two 1/N — the same bits
+on every rank and on every run, which a ring all-reduce does not promise.
+Adapters and moments therefore stay replicated bit for bit.
+
+No peer memory is read by any kernel here: remote gradients arrive through the
+collective into local memory first.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+
+
+def shard_rows(global_rows: int, seq_len: int, world: int, rank: int) -> Tuple[int, int]:
+    """Rows [begin, end) of each global batch that `rank` trains on.  Token
+    plans shard whole sequences (reference: runtime/loader/plan_loader.cc:226-228:
+    batch % seq_len == 0); feature plans shard rows."""
+    unit = seq_len if seq_len else 1
+    units = global_rows // unit
+    if global_rows % unit or units % world:
+        raise ValueError(f"{global_rows} rows of {unit}-row units do not split over {world} ranks")
+    per = units // world * unit
+    return rank * per, (rank + 1) * per
+
+
+def fixed_order_mean(copies: Sequence[np.ndarray]) -> np.ndarray:
+    """The reduction the optimizer kernel applies to gathered gradients: a
+    left-to-right f32 sum in rank order, then one multiply by 1/N."""
+    acc = copies[0].astype(np.float32).copy()
+    for c in copies[1:]:
+        acc = (acc + c.astype(np.float32)).astype(np.float32)
+    return (acc * np.float32(1.0 / len(copies))).astype(np.float32)
+
+
+class _DeviceView:
+    """Exposes a raw device range to torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None}
+
+
+class GradientExchange:
+    """Owns the gather buffer and performs the per-step all-gather on the
+    engine's stream (torch.distributed, NCCL backend)."""
+
+    def __init__(self, engine, group=None):
+        import torch
+        import torch.distributed as dist
+        self.dist = dist
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        off, nbytes = engine.gradient_block()
+        self.off, self.nbytes = off, nbytes
+        self.gathered = torch.empty(self.world * nbytes, dtype=torch.uint8, device="cuda")
+        base = engine.backend.device_arena()
+        self.local = torch.as_tensor(_DeviceView(base + off, nbytes), device="cuda")
+        self._loss = torch.zeros(1, dtype=torch.float32, device="cuda")
+        if self.world > 1:
+            engine.backend.set_gradient_gather(self.world, self.gathered.data_ptr(), off, nbytes)
+
+    def exchange(self):
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.gathered, self.local, group=self.group)
+
+    def mean_loss(self, local_loss: float) -> float:
+        """Mean of the shard losses in rank order (each shard's loss is already a
+        mean over its own rows, and shards are equal-sized)."""
+        import torch
+        if self.world == 1:
+            return local_loss
+        mine = torch.tensor([local_loss], dtype=torch.float32, device="cuda")
+        allv = torch.empty(self.world, dtype=torch.float32, device="cuda")
+        self.dist.all_gather_into_tensor(allv, mine, group=self.group)
+        return float(fixed_order_mean([allv[i:i + 1].cpu().numpy() for i in range(self.world)])[0])
