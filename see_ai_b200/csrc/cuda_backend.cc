@@ -101,6 +101,7 @@ CudaBackend::~CudaBackend() {
   cudaFree(d_status_);  // base of the scratch block
   cudaFree(d_rows_);
   cudaFree(d_gsum_);
+  cudaFree(d_split_);
   if (h_scalars_) cudaFreeHost(h_scalars_);
   if (h_status_) cudaFreeHost(h_status_);
   if (own_stream_ && stream_) cudaStreamDestroy(stream_);
@@ -315,10 +316,15 @@ Status CudaBackend::EnsureScratch(uint64_t row_doubles) {
 void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin, size_t end) {
   // Size every scratch buffer the range needs up front, so no allocation (and
   // no stream drain) happens between its instructions.
-  uint64_t rows = 0, gsum = 0;
+  uint64_t rows = 0, gsum = 0, split = 0;
   for (size_t i = begin; i < end && i < program.size(); ++i) {
     const Instruction& ins = program[i];
     switch (ins.opcode) {
+      case kGemmTN: {
+        const uint64_t chunks = k::SplitKChunks(ins.out[0], ins.out[1], ins.out[2]);
+        if (chunks > 1) split = std::max(split, chunks * ins.out[0] * ins.out[1]);
+        break;
+      }
       case kSoftmaxXEntFwd: case kSoftmaxXEntMaskedFwd: rows = std::max(rows, ins.out[0]); break;
       case kKLDistillFwd: rows = std::max(rows, Hi32(ins.out[1])); break;
       case kMseFwd: rows = std::max<uint64_t>(rows, 256); break;
@@ -329,6 +335,17 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
     }
   }
   if (rows) (void)EnsureScratch(rows);
+  if (split > split_capacity_) {
+    cudaStreamSynchronize(stream_);
+    cudaFree(d_split_);
+    d_split_ = nullptr;
+    split_capacity_ = 0;
+    void* p = nullptr;
+    if (cudaMalloc(&p, split * sizeof(float)) == cudaSuccess) {
+      d_split_ = static_cast<float*>(p);
+      split_capacity_ = split;
+    }
+  }
   if (gsum > gsum_capacity_) {
     cudaStreamSynchronize(stream_);
     cudaFree(d_gsum_);
@@ -481,6 +498,10 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
     if (!err.empty()) return std::unexpected("cuda: " + err);
     // launches == 0: the shape is outside the tensor-core kernel's domain.
   }
+  // The split-K scratch is sized per range (BeginRange); an instruction executed
+  // outside any range simply runs unsplit.
+  a.split_scratch = d_split_;
+  a.split_scratch_floats = split_capacity_;
   k::GemmExact(a, stream_);
   ++counters_.kernel_launches;
   return {};

@@ -177,6 +177,8 @@ class CudaBackend {
   unsigned long long* d_count_ = nullptr;
   double* d_rows_ = nullptr;
   uint64_t rows_capacity_ = 0;
+  float* d_split_ = nullptr;      // split-K partial sums of the adapter-gradient GEMMs
+  uint64_t split_capacity_ = 0;   // floats
   float* d_gsum_ = nullptr;       // summed gradient for fused clips under data parallelism
   uint64_t gsum_capacity_ = 0;
   k::AdamScalars* d_scalars_ = nullptr;

@@ -58,6 +58,12 @@ struct Params {
   const float* addend;
   Act act;
   bool accumulate;
+  // Split-K (long reductions into small outputs): block z reduces k in
+  // [z * k_chunk, (z + 1) * k_chunk) with the quad order inside the chunk and
+  // writes its raw sums to partials[z][M][N]; a second kernel folds the chunks
+  // in chunk order.  k_chunk is a multiple of 16, so quads stay aligned to k = 0.
+  size_t k_chunk;
+  float* partials;
 };
 
 constexpr int BK = 16;
@@ -90,7 +96,9 @@ __global__ void __launch_bounds__(256) GemmQuadKernel(Params p) {
       const size_t m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
       c[i][j] = (p.accumulate && m < p.M && n < p.N) ? p.C[m * p.N + n] : 0.0f;
     }
-  for (size_t k0 = 0; k0 < p.K; k0 += BK) {
+  const size_t k_begin = p.k_chunk ? static_cast<size_t>(blockIdx.z) * p.k_chunk : 0;
+  const size_t k_end = p.k_chunk ? (k_begin + p.k_chunk < p.K ? k_begin + p.k_chunk : p.K) : p.K;
+  for (size_t k0 = k_begin; k0 < k_end; k0 += BK) {
     // Stage the tiles; alpha and the column scale are applied here, once per
     // element, as the reference applies them when an element enters the product.
 #pragma unroll
@@ -105,7 +113,7 @@ __global__ void __launch_bounds__(256) GemmQuadKernel(Params p) {
       Bs[kb][nb] = b;
     }
     __syncthreads();
-    const int kmax = p.K - k0 < static_cast<size_t>(BK) ? static_cast<int>(p.K - k0) : BK;
+    const int kmax = k_end - k0 < static_cast<size_t>(BK) ? static_cast<int>(k_end - k0) : BK;
     int kk = 0;
     for (; kk + 4 <= kmax; kk += 4) {
       float a[4][4], b[4][4];
@@ -143,10 +151,27 @@ __global__ void __launch_bounds__(256) GemmQuadKernel(Params p) {
       const size_t m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
       if (m >= p.M || n >= p.N) continue;
       float v = c[i][j];
+      if (p.partials) {
+        p.partials[(static_cast<size_t>(blockIdx.z) * p.M + m) * p.N + n] = v;
+        continue;
+      }
       if (p.addend) v = p.addend[m * p.N + n] + v;
       if (p.bias) v = v + p.bias[n];
       p.C[m * p.N + n] = ApplyAct(v, p.act);
     }
+}
+
+// Folds split-K partials in chunk order, then the epilogue.
+__global__ void SplitKFoldKernel(Params p, size_t chunks) {
+  const size_t total = p.M * p.N;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += stride) {
+    float v = p.partials[i];
+    for (size_t z = 1; z < chunks; ++z) v = v + p.partials[z * total + i];
+    if (p.addend) v = p.addend[i] + v;
+    if (p.bias) v = v + p.bias[i % p.N];
+    p.C[i] = ApplyAct(v, p.act);
+  }
 }
 
 // ---- lane order: 32x32 tile, 256 threads, 2x2 outputs x 8 lanes per thread ------
@@ -206,10 +231,16 @@ __global__ void __launch_bounds__(256) GemmLaneKernel(Params p) {
 
 }  // namespace
 
+size_t SplitKChunks(size_t M, size_t N, size_t K) {
+  const size_t tiles = ((M + 63) / 64) * ((N + 63) / 64);
+  if (K < 4 * kSplitKChunk || tiles >= 148) return 1;
+  return (K + kSplitKChunk - 1) / kSplitKChunk;
+}
+
 void GemmExact(const GemmArgs& a, cudaStream_t s) {
   if (a.M == 0 || a.N == 0) return;
   Params p{a.A, a.B, a.C, a.M, a.N, a.K, a.alpha, a.b_col_scale, a.a_k_scale,
-           a.bias, a.addend, a.act, a.accumulate};
+           a.bias, a.addend, a.act, a.accumulate, 0, nullptr};
   if (a.b_transposed) {
     dim3 grid(static_cast<unsigned>((a.N + 31) / 32), static_cast<unsigned>((a.M + 31) / 32));
     switch (a.b_type) {
@@ -221,6 +252,21 @@ void GemmExact(const GemmArgs& a, cudaStream_t s) {
   }
   dim3 grid(static_cast<unsigned>((a.N + 63) / 64), static_cast<unsigned>((a.M + 63) / 64));
   if (a.a_transposed) {
+    // Adapter gradients: a [rank x width] or [width x rank] result reduced over
+    // every row of the batch.  With few output tiles and a long K the chunks go
+    // to separate blocks (fixed geometry: a pure function of the shape).
+    const size_t chunks = SplitKChunks(a.M, a.N, a.K);
+    if (chunks > 1 && a.split_scratch && !a.accumulate &&
+        chunks * a.M * a.N <= a.split_scratch_floats) {
+      p.k_chunk = kSplitKChunk;
+      p.partials = a.split_scratch;
+      grid.z = static_cast<unsigned>(chunks);
+      GemmQuadKernel<true, float><<<grid, 256, 0, s>>>(p);
+      size_t blocks = (a.M * a.N + 255) / 256;
+      if (blocks > 1184) blocks = 1184;
+      SplitKFoldKernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(p, chunks);
+      return;
+    }
     GemmQuadKernel<true, float><<<grid, 256, 0, s>>>(p);
     return;
   }

@@ -150,7 +150,14 @@ struct GemmArgs {
   const float* addend = nullptr;
   Act act = kActNone;
   bool accumulate = false;  // C += (the merge program's form)
+  // Scratch for the split-K form of the transposed-A product (optional).
+  float* split_scratch = nullptr;
+  size_t split_scratch_floats = 0;
 };
+// K is cut into chunks of kSplitKChunk when the transposed-A product has fewer
+// output tiles than SMs and K >= 4 chunks; 1 means "not split".
+constexpr size_t kSplitKChunk = 256;
+size_t SplitKChunks(size_t M, size_t N, size_t K);
 // The reference's reduction orders on CUDA cores, without fused multiply-adds:
 // bit-identical to the CPU executor for f32 / int8 / bf16 weights.
 void GemmExact(const GemmArgs& a, cudaStream_t s);

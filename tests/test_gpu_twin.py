@@ -110,3 +110,40 @@ def test_unknown_opcode_and_out_of_bounds_are_errors_not_faults():
         be.run([P.Instr(P.Op.COPY, 0, 0, (P.RODATA_BIT, 0), (4, 0, 0))])
     be.run([P.Instr(P.Op.NOP)])  # and the backend is still usable
     be.close()
+
+
+def test_split_k_adapter_gradients_fixed_order():
+    """Transposed-A products with a small output and a long reduction (the LoRA
+    dA / dB shapes: K = batch rows) run split over K in fixed 256-row chunks.
+    Not the CPU's bits, but held to the reference's own GEMM accuracy metric
+    (|got - want| / (1 + sum|a_k b_k|) < 2e-6; reference:
+    test/runtime/executor/kernels_test.cc:1803-1822) and identical run to run."""
+    rng = np.random.default_rng(77)
+    from tests.test_oracle_pinned import Arena
+    for (M, N, K) in [(16, 96, 4096), (200, 16, 3000), (8, 8, 1024)]:
+        a = Arena(rng)
+        At = a.alloc(K * M, "normal"); Bm = a.alloc(K * N, "normal"); D = a.alloc(M * N, "normal")
+        o1, o2 = a.alloc(M * N), a.alloc(M * N)
+        prog = [P.Instr(P.Op.GEMM_TN, 0, P.f32_bits(2.0), (At, Bm, o1, P.NULL_REF), (M, N, K)),
+                P.Instr(P.Op.GEMM_TN, P.FLAG_GEMM_ADDEND, 0, (At, Bm, o2, D), (M, N, K))]
+        arena, ro = a.build()
+        cpu = arena.copy()
+        ref = oracle.OracleExecutor()
+        ref.bind(cpu, ro)
+        ref.run(prog)
+        runs = []
+        for _ in range(2):
+            gpu = arena.copy()
+            be = B.CudaBackend(0)
+            be.bind(gpu, ro)
+            be.run(prog)
+            be.close()
+            runs.append(gpu)
+        assert np.array_equal(runs[0], runs[1])
+        A_np = arena[At:At + 4 * K * M].view(np.float32).astype(np.float64).reshape(K, M)
+        B_np = arena[Bm:Bm + 4 * K * N].view(np.float32).astype(np.float64).reshape(K, N)
+        mag = np.abs(A_np).T @ np.abs(B_np)
+        for off, scale in ((o1, 2.0), (o2, 1.0)):
+            got = runs[0][off:off + 4 * M * N].view(np.float32).astype(np.float64).reshape(M, N)
+            want = cpu[off:off + 4 * M * N].view(np.float32).astype(np.float64).reshape(M, N)
+            assert (np.abs(got - want) / (1.0 + scale * mag)).max() < 2e-6
