@@ -108,6 +108,25 @@ typedef struct see_profile_record {
 int see_cuda_set_profiling(see_cuda_backend* h, int on);
 int64_t see_cuda_take_profile(see_cuda_backend* h, see_profile_record* out, uint64_t capacity);
 
+/* ---- Softmax cross-entropy forward without any allocation ----------------------
+ * No counterpart in the reference (its CPU kernel keeps its partial sums on the
+ * stack; reference: runtime/executor/loss.cc:35-57).  For callers that may not
+ * call cudaMalloc — a plugin inside a host whose pool already owns the device's
+ * memory, a loop where allocation after start-up is forbidden, or the caller's
+ * own stream capture.  Same arithmetic and kernels as the kSoftmaxXEntFwd
+ * instruction; the per-row scratch is a fixed array inside the library, so
+ * `rows` is limited to see_cuda_static_max_rows() (65536) and larger batches are
+ * refused with SEE_ERROR.  logits [rows, classes], labels [rows] (i32), loss [1]
+ * and probs [rows, classes] are DEVICE pointers; the work is enqueued on
+ * `cuda_stream`.  The first call on a device looks up the array's address — make
+ * it before any stream capture.  All calls share the array: calls that can
+ * overlap on the GPU race.  masked != 0 selects the form that ignores labels of -1. */
+int see_cuda_xent_forward_static(const float* logits, const int32_t* labels, float* loss,
+                                 float* probs, uint64_t rows, uint64_t classes, int masked,
+                                 void* cuda_stream);
+uint64_t see_cuda_static_max_rows(void);
+const char* see_cuda_static_last_error(void);
+
 /* ---- The dispatcher: UpdateEngine over the CUDA backend ----------------------
  * Mirrors the hot-path surface of seeml::update_rt::UpdateEngine (reference:
  * runtime/dispatcher/update_engine.h:211-367).  The engine owns the device slab

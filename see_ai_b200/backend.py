@@ -30,6 +30,7 @@ EXPORTED_SYMBOLS = [
     "see_cuda_host_needs", "see_cuda_counters_get", "see_cuda_set_stream",
     "see_cuda_device_arena", "see_cuda_set_relaxed_allowed", "see_cuda_set_gradient_gather",
     "see_cuda_set_profiling", "see_cuda_take_profile",
+    "see_cuda_xent_forward_static", "see_cuda_static_max_rows", "see_cuda_static_last_error",
 ]
 
 
@@ -99,8 +100,24 @@ def load_library() -> ctypes.CDLL:
     lib.see_cuda_set_profiling.argtypes = [vp, i32]
     lib.see_cuda_take_profile.argtypes = [vp, ctypes.POINTER(ProfileRecord), u64]
     lib.see_cuda_take_profile.restype = ctypes.c_int64
+    lib.see_cuda_xent_forward_static.argtypes = [vp, vp, vp, vp, u64, u64, i32, vp]
+    lib.see_cuda_static_max_rows.restype = u64
+    lib.see_cuda_static_last_error.restype = ctypes.c_char_p
     _lib = lib
     return lib
+
+
+def xent_forward_static(logits_ptr: int, labels_ptr: int, loss_ptr: int, probs_ptr: int,
+                        rows: int, classes: int, masked: bool = False, stream: int = 0) -> None:
+    """Softmax cross-entropy forward over DEVICE pointers with no allocation:
+    the scratch is a fixed array inside the library (at most
+    see_cuda_static_max_rows() rows).  For callers that may not call cudaMalloc."""
+    lib = load_library()
+    rc = lib.see_cuda_xent_forward_static(ctypes.c_void_p(logits_ptr), ctypes.c_void_p(labels_ptr),
+                                          ctypes.c_void_p(loss_ptr), ctypes.c_void_p(probs_ptr),
+                                          rows, classes, int(masked), ctypes.c_void_p(stream))
+    if rc != SEE_OK:
+        raise BackendError(lib.see_cuda_static_last_error().decode())
 
 
 def program_bytes(program) -> bytes:
