@@ -30,6 +30,7 @@ CU_SOURCES = {
     "k_gemm_exact.cu": ["-fmad=false"],
     "k_gemm_umma.cu": [],
     "k_eval.cu": [],
+    "k_attn_umma.cu": [],
     "k_no_alloc.cu": ["-fmad=false"],
 }
 CC_SOURCES = ["extents.cc", "cuda_backend.cc", "c_api.cc", "umma_gemm.cc", "engine.cc"]

@@ -1,0 +1,43 @@
+// Interface of the tensor-core attention kernels (k_attn_umma.cu) to their
+// host planner (umma_attn.cc).
+#ifndef SEE_CUDA_ATTN_UMMA_H_
+#define SEE_CUDA_ATTN_UMMA_H_
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "kernels.h"
+
+namespace see::k {
+
+struct AttnUmmaArgs {
+  uint32_t B, S, H, d;
+  float inv_sqrt_d;
+  float* out;       // O / dQ / dK / dV, f32 [B*S, H*d]
+  float* stats;     // f32 [B*H*S, 4]: score max, 1/denominator, delta, start
+  DeviceStatus* status;
+};
+
+// f32 [B*S, H*d] (heads interleaved along the row) -> bf16 per (sequence, head):
+// rows [B*H][S][d] and/or cols [B*H][d][S]; either destination may be null.
+void PackHeads(const float* x, uint16_t* rows, uint16_t* cols, uint32_t B, uint32_t S, uint32_t H,
+               uint32_t d, cudaStream_t s);
+
+// Row-layout maps: dims {d, S, B*H}, box {64, 128, 1}; column-layout maps:
+// dims {S, d, B*H}, box {64, d, 1}; bf16, 128-byte swizzle.  d is 64 or 128.
+cudaError_t AttnFwdUmma(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& vt,
+                        const AttnUmmaArgs& a, cudaStream_t s);
+cudaError_t AttnDQUmma(const CUtensorMap& q, const CUtensorMap& dout, const CUtensorMap& k,
+                       const CUtensorMap& v, const CUtensorMap& kt, const AttnUmmaArgs& a,
+                       cudaStream_t s);
+// t = dO columns for dV, Q columns for dK.
+cudaError_t AttnDKVUmma(bool want_dk, const CUtensorMap& k, const CUtensorMap& v, const CUtensorMap& q,
+                        const CUtensorMap& dout, const CUtensorMap& t, const AttnUmmaArgs& a,
+                        cudaStream_t s);
+
+}  // namespace see::k
+
+#endif  // SEE_CUDA_ATTN_UMMA_H_

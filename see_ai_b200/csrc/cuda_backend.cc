@@ -736,6 +736,16 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
       break;
     }
     case kAttnFwdTiled:
+      if ((ins.flags & kFlagRelaxed) && relaxed_allowed_) {
+        umma::AttentionOperands op{Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), nullptr,
+                                   RefOffset(ins.in[0]), RefOffset(ins.in[1]), RefOffset(ins.in[2]), 0,
+                                   Wr(ins.out[0]), Wr(ins.in[3]),
+                                   Hi32(ins.out[1]), Lo32(ins.out[1]), Hi32(ins.out[2]), Lo32(ins.out[2])};
+        int n = 0;
+        if (std::string e = umma::TryAttention(&umma_->ctx, ins.opcode, op, s, &n); !e.empty())
+          return std::unexpected("cuda: " + e);
+        if (n > 0) { ++counters_.relaxed_executions; launched(n); break; }
+      }
       k::AttnFwd(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Wr(ins.in[3]), nullptr, Wr(ins.out[0]),
                  Hi32(ins.out[1]), Lo32(ins.out[1]), Hi32(ins.out[2]), Lo32(ins.out[2]), nullptr, s);
       launched();
@@ -774,6 +784,16 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
       break;
     case kAttnDQTiled: case kAttnDKTiled: case kAttnDVTiled: {
       const AttnGeom g = UnpackAttnGeom(ins.out[2]);
+      if ((ins.flags & kFlagRelaxed) && relaxed_allowed_) {
+        umma::AttentionOperands op{Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Rd(ins.in[3]),
+                                   RefOffset(ins.in[0]), RefOffset(ins.in[1]), RefOffset(ins.in[2]),
+                                   RefOffset(ins.in[3]), Wr(ins.out[0]), Wr(ins.out[1]),
+                                   g.B, g.S, g.H, g.d};
+        int n = 0;
+        if (std::string e = umma::TryAttention(&umma_->ctx, ins.opcode, op, s, &n); !e.empty())
+          return std::unexpected("cuda: " + e);
+        if (n > 0) { ++counters_.relaxed_executions; launched(n); break; }
+      }
       if (g.d > 256 && ins.opcode != kAttnDQTiled)
         return std::unexpected("cuda: tiled attention backward supports head widths up to 256");
       if (ins.opcode == kAttnDQTiled)

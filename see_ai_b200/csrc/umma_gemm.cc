@@ -3,11 +3,13 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <map>
 #include <tuple>
 #include <vector>
 
+#include "attn_umma.h"
 #include "umma_kernel.h"
 
 namespace see::umma {
@@ -33,6 +35,13 @@ struct ActCopy {   // a bf16 copy of an arena activation [M, K]
 
 constexpr int kActSlots = 4;
 
+// Packed bf16 copies of attention operands: role (Q, K, V, dO) x layout (rows, cols).
+struct PackSlot {
+  uint16_t* buf = nullptr;
+  uint64_t src_off = ~0ull, elems = 0;
+  bool valid = false;
+};
+
 }  // namespace
 
 struct Impl {
@@ -42,6 +51,8 @@ struct Impl {
   ActCopy acts[kActSlots];
   uint64_t tick = 0;
   k::DeviceStatus* status = nullptr;  // the backend's device status block (not owned)
+  PackSlot pack[4][2];
+  uint64_t pack_capacity = 0;   // elements per slot
   cudaEvent_t prof_before = nullptr, prof_after = nullptr;
   bool prof_used = false;
 };
@@ -66,6 +77,8 @@ void Destroy(Context* ctx) {
   if (!ctx->impl) return;
   InvalidateAll(ctx);
   for (auto& a : ctx->impl->acts) cudaFree(a.buf);
+  for (auto& role : ctx->impl->pack)
+    for (auto& slot : role) cudaFree(slot.buf);
   delete ctx->impl;
   ctx->impl = nullptr;
 }
@@ -75,6 +88,8 @@ void InvalidateAll(Context* ctx) {
   for (auto& [key, buf] : ctx->impl->weights) cudaFree(buf);
   ctx->impl->weights.clear();
   for (auto& a : ctx->impl->acts) a.valid = false;
+  for (auto& role : ctx->impl->pack)
+    for (auto& slot : role) slot.valid = false;
 }
 
 void InvalidateRange(Context* ctx, uint64_t off, uint64_t bytes) {
@@ -84,6 +99,10 @@ void InvalidateRange(Context* ctx, uint64_t off, uint64_t bytes) {
     const uint64_t a_bytes = a.M * a.K * 4;
     if (off < a.a_off + a_bytes && a.a_off < off + bytes) a.valid = false;
   }
+  for (auto& role : ctx->impl->pack)
+    for (auto& slot : role)
+      if (slot.valid && off < slot.src_off + slot.elems * 4 && slot.src_off < off + bytes)
+        slot.valid = false;
 }
 
 // Sizes every activation-copy slot for the largest relaxed GEMM of the range
@@ -102,6 +121,29 @@ void PlanRange(Context* ctx, const Instruction* program, size_t begin, size_t en
         break;
       default: break;
     }
+  }
+  uint64_t attn = 0;
+  for (size_t i = begin; i < end; ++i) {
+    const Instruction& ins = program[i];
+    if (!(ins.flags & kFlagRelaxed)) continue;
+    if (ins.opcode == kAttnFwdTiled)
+      attn = std::max(attn, Hi32(ins.out[1]) * Lo32(ins.out[1]) * Hi32(ins.out[2]) * Lo32(ins.out[2]));
+    if (ins.opcode == kAttnDQTiled || ins.opcode == kAttnDKTiled || ins.opcode == kAttnDVTiled) {
+      const AttnGeom g = UnpackAttnGeom(ins.out[2]);
+      attn = std::max(attn, g.B * g.S * g.H * g.d);
+    }
+  }
+  if (attn > impl->pack_capacity) {
+    cudaDeviceSynchronize();
+    for (auto& role : impl->pack)
+      for (auto& slot : role) {
+        cudaFree(slot.buf);
+        slot.buf = nullptr;
+        slot.valid = false;
+        void* p = nullptr;
+        if (cudaMalloc(&p, attn * 2) == cudaSuccess) slot.buf = static_cast<uint16_t*>(p);
+      }
+    impl->pack_capacity = attn;
   }
   if (need == 0) return;
   bool drained = false;
@@ -215,6 +257,87 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
     impl->prof_used = true;
     impl->prof_before = impl->prof_after = nullptr;
   }
+  ++*launches;
+  return {};
+}
+
+namespace {
+
+bool EncodeHeads(Impl* impl, CUtensorMap* map, const void* base, uint64_t inner, uint64_t mid,
+                 uint64_t outer, uint32_t box_mid) {
+  const cuuint64_t dims[3] = {inner, mid, outer};
+  const cuuint64_t strides[2] = {inner * 2, inner * mid * 2};
+  const cuuint32_t box[3] = {64, box_mid, 1};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  return impl->encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims,
+                      strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands& op,
+                         cudaStream_t stream, int* launches) {
+  *launches = 0;
+  Impl* impl = ctx->impl;
+  if (!impl) return {};
+  if ((op.d != 64 && op.d != 128) || op.S % 8 != 0 || op.S < 16 || op.S > 0x7FFFFFFF ||
+      op.B * op.H > 65535 || op.B * op.H == 0)
+    return {};
+  if ((reinterpret_cast<uintptr_t>(op.out) & 15) || (reinterpret_cast<uintptr_t>(op.stats) & 15))
+    return {};
+  const uint64_t elems = op.B * op.S * op.H * op.d;
+  if (elems > impl->pack_capacity) return {};   // executed outside a planned range
+  for (auto& role : impl->pack)
+    for (auto& slot : role)
+      if (!slot.buf) return "tensor-core attention: packed-operand allocation failed";
+  const bool fwd = opcode == kAttnFwdTiled, dq = opcode == kAttnDQTiled,
+             dk = opcode == kAttnDKTiled, dv = opcode == kAttnDVTiled;
+  if (!fwd && !dq && !dk && !dv) return {};
+  enum { Q = 0, K = 1, V = 2, DO = 3 };
+  const float* src[4] = {op.q, op.k, op.v, op.dout};
+  const uint64_t off[4] = {op.q_off, op.k_off, op.v_off, op.dout_off};
+  bool rows[4] = {false, false, false, false}, cols[4] = {false, false, false, false};
+  if (fwd) { rows[Q] = rows[K] = true; cols[V] = true; }
+  if (dq) { rows[Q] = rows[DO] = rows[K] = rows[V] = true; cols[K] = true; }
+  if (dk) { rows[K] = rows[V] = rows[Q] = rows[DO] = true; cols[Q] = true; }
+  if (dv) { rows[K] = rows[Q] = true; cols[DO] = true; }
+  for (int r = 0; r < 4; ++r) {
+    PackSlot& sr = impl->pack[r][0];
+    PackSlot& sc = impl->pack[r][1];
+    const bool do_rows = rows[r] && !(sr.valid && sr.src_off == off[r] && sr.elems == elems);
+    const bool do_cols = cols[r] && !(sc.valid && sc.src_off == off[r] && sc.elems == elems);
+    if (!do_rows && !do_cols) continue;
+    k::PackHeads(src[r], do_rows ? sr.buf : nullptr, do_cols ? sc.buf : nullptr,
+                 static_cast<uint32_t>(op.B), static_cast<uint32_t>(op.S),
+                 static_cast<uint32_t>(op.H), static_cast<uint32_t>(op.d), stream);
+    ++*launches;
+    if (do_rows) { sr.valid = true; sr.src_off = off[r]; sr.elems = elems; }
+    if (do_cols) { sc.valid = true; sc.src_off = off[r]; sc.elems = elems; }
+  }
+  const uint64_t BH = op.B * op.H;
+  CUtensorMap mr[4], mc[4];
+  for (int r = 0; r < 4; ++r) {
+    if (rows[r] && !EncodeHeads(impl, &mr[r], impl->pack[r][0].buf, op.d, op.S, BH, 128))
+      return "tensor-core attention: cuTensorMapEncodeTiled refused a row layout";
+    if (cols[r] && !EncodeHeads(impl, &mc[r], impl->pack[r][1].buf, op.S, op.d, BH,
+                                static_cast<uint32_t>(op.d)))
+      return "tensor-core attention: cuTensorMapEncodeTiled refused a column layout";
+  }
+  k::AttnUmmaArgs a{};
+  a.B = static_cast<uint32_t>(op.B); a.S = static_cast<uint32_t>(op.S);
+  a.H = static_cast<uint32_t>(op.H); a.d = static_cast<uint32_t>(op.d);
+  a.inv_sqrt_d = 1.0f / std::sqrt(static_cast<float>(op.d));
+  a.out = op.out;
+  a.stats = op.stats;
+  a.status = impl->status;
+  cudaError_t e = cudaSuccess;
+  if (fwd) e = k::AttnFwdUmma(mr[Q], mr[K], mc[V], a, stream);
+  if (dq) e = k::AttnDQUmma(mr[Q], mr[DO], mr[K], mr[V], mc[K], a, stream);
+  if (dk) e = k::AttnDKVUmma(true, mr[K], mr[V], mr[Q], mr[DO], mc[Q], a, stream);
+  if (dv) e = k::AttnDKVUmma(false, mr[K], mr[K], mr[Q], mr[Q], mc[DO], a, stream);
+  if (e != cudaSuccess) return std::string("tensor-core attention launch: ") + cudaGetErrorString(e);
   ++*launches;
   return {};
 }

@@ -41,6 +41,21 @@ void PlanRange(Context* ctx, const Instruction* program, size_t begin, size_t en
 std::string TryGemm(Context* ctx, const k::GemmArgs& args, int b_space, uint64_t b_off,
                     uint64_t a_off, uint64_t a_scale_off, cudaStream_t stream, int* launches);
 
+// Runs one tiled attention opcode (kAttnFwdTiled / kAttnDQTiled / kAttnDKTiled /
+// kAttnDVTiled) on the tensor cores when the geometry is inside the kernels'
+// domain (head width 64 or 128, sequence length a multiple of 8).  Operands are
+// device pointers into the arena; the *_off arguments are their arena offsets,
+// used to reuse packed bf16 copies between the backward opcodes of one layer.
+// *launches == 0 with an empty return value means "not applicable".
+struct AttentionOperands {
+  const float* q; const float* k; const float* v; const float* dout;
+  uint64_t q_off, k_off, v_off, dout_off;
+  float* stats; float* out;
+  uint64_t B, S, H, d;
+};
+std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands& op,
+                         cudaStream_t stream, int* launches);
+
 // Profile mode: the next tensor-core launch records `before` / `after` around
 // the kernel itself (not the operand conversions).  Returns whether a launch
 // consumed them since the last call.
