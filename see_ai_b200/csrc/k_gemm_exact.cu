@@ -15,9 +15,13 @@
 // Epilogue order matches the reference (gemm.cc:536-578): addend `d + s` on
 // the finished sum, then bias, then the activation expression.  Compiled with
 // -fmad=false; no multiply is ever fused into an add.  This family is the
-// parity anchor and the path for skinny (rank-r) products; large
-// frozen-weight products carrying the relaxed permission go to the tensor
-// cores instead.
+// parity anchor and the path for the rank-r adapter products, whose outputs are
+// 8-16 wide (or tall): the block tile comes in three shapes (64x64, 256x16,
+// 16x256 for the quad order; 32x32, 64x16, 16x64 for the lane order) picked
+// from the output shape, so a skinny product wastes no lanes.  A tile shape
+// changes which thread owns an element, never the element's arithmetic.
+// Large frozen-weight products carrying the relaxed permission go to the
+// tensor cores instead.
 #include "kernels.h"
 
 namespace see::k {
@@ -67,6 +71,7 @@ struct Params {
 };
 
 constexpr int BK = 16;
+constexpr int kThreads = 256;
 
 template <bool TA>
 __device__ __forceinline__ float LoadA(const Params& p, size_t m, size_t k) {
@@ -80,13 +85,13 @@ __device__ __forceinline__ float LoadB(const Params& p, size_t k, size_t n) {
   return Widen<BT>(TB ? B[n * p.K + k] : B[k * p.N + n]);
 }
 
-// ---- quad order: 64x64 tile, 256 threads, 4x4 outputs per thread --------------
-template <bool TA, typename BT>
-__global__ void __launch_bounds__(256) GemmQuadKernel(Params p) {
-  constexpr int BM = 64, BN = 64;
+// ---- quad order: BM x BN tile (BM * BN = 4096), 256 threads, 4x4 outputs per thread ----
+template <bool TA, typename BT, int BM, int BN>
+__global__ void __launch_bounds__(kThreads) GemmQuadKernel(Params p) {
+  static_assert(BM * BN == 16 * kThreads, "4x4 outputs per thread");
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
-  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int tx = threadIdx.x % (BN / 4), ty = threadIdx.x / (BN / 4);
   const size_t m0 = static_cast<size_t>(blockIdx.y) * BM, n0 = static_cast<size_t>(blockIdx.x) * BN;
   float c[4][4];
 #pragma unroll
@@ -102,11 +107,13 @@ __global__ void __launch_bounds__(256) GemmQuadKernel(Params p) {
     // Stage the tiles; alpha and the column scale are applied here, once per
     // element, as the reference applies them when an element enters the product.
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const int idx = threadIdx.x + t * 256;
+    for (int idx = threadIdx.x; idx < BM * BK; idx += kThreads) {
       int mm, kk;
       if (TA) { kk = idx / BM; mm = idx % BM; } else { mm = idx / BK; kk = idx % BK; }
       As[kk][mm] = p.alpha * LoadA<TA>(p, m0 + mm, k0 + kk);
+    }
+#pragma unroll
+    for (int idx = threadIdx.x; idx < BK * BN; idx += kThreads) {
       const int kb = idx / BN, nb = idx % BN;
       float b = LoadB<false, BT>(p, k0 + kb, n0 + nb);
       if (p.b_col_scale && n0 + nb < p.N) b = b * p.b_col_scale[n0 + nb];
@@ -174,13 +181,13 @@ __global__ void SplitKFoldKernel(Params p, size_t chunks) {
   }
 }
 
-// ---- lane order: 32x32 tile, 256 threads, 2x2 outputs x 8 lanes per thread ------
-template <typename BT>
-__global__ void __launch_bounds__(256) GemmLaneKernel(Params p) {
-  constexpr int BM = 32, BN = 32;
+// ---- lane order: BM x BN tile (BM * BN = 1024), 256 threads, 2x2 outputs x 8 lanes ------
+template <typename BT, int BM, int BN>
+__global__ void __launch_bounds__(kThreads) GemmLaneKernel(Params p) {
+  static_assert(BM * BN == 4 * kThreads, "2x2 outputs per thread");
   __shared__ float As[BK][BM + 2];
   __shared__ float Bs[BK][BN + 2];
-  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int tx = threadIdx.x % (BN / 2), ty = threadIdx.x / (BN / 2);
   const size_t m0 = static_cast<size_t>(blockIdx.y) * BM, n0 = static_cast<size_t>(blockIdx.x) * BN;
   float acc[2][2][8];
 #pragma unroll
@@ -191,13 +198,16 @@ __global__ void __launch_bounds__(256) GemmLaneKernel(Params p) {
       for (int l = 0; l < 8; ++l) acc[i][j][l] = 0.0f;
   for (size_t k0 = 0; k0 < p.K; k0 += BK) {
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const int idx = threadIdx.x + t * 256;
+    for (int idx = threadIdx.x; idx < BM * BK; idx += kThreads) {
       const int mm = idx / BK, kk = idx % BK;
       float a = LoadA<false>(p, m0 + mm, k0 + kk);
       if (p.a_k_scale && k0 + kk < p.K) a = a * p.a_k_scale[k0 + kk];
       As[kk][mm] = a;
-      Bs[kk][mm] = LoadB<true, BT>(p, k0 + kk, n0 + mm);
+    }
+#pragma unroll
+    for (int idx = threadIdx.x; idx < BN * BK; idx += kThreads) {
+      const int nn = idx / BK, kk = idx % BK;
+      Bs[kk][nn] = LoadB<true, BT>(p, k0 + kk, n0 + nn);
     }
     __syncthreads();
     const int kmax = p.K - k0 < static_cast<size_t>(BK) ? static_cast<int>(p.K - k0) : BK;
@@ -229,11 +239,40 @@ __global__ void __launch_bounds__(256) GemmLaneKernel(Params p) {
     }
 }
 
+unsigned Blocks(size_t extent, size_t tile) { return static_cast<unsigned>((extent + tile - 1) / tile); }
+
+template <bool TA, typename BT>
+void LaunchQuad(const Params& p, unsigned z, cudaStream_t s) {
+  if (p.N <= 16) {
+    GemmQuadKernel<TA, BT, 256, 16><<<dim3(Blocks(p.N, 16), Blocks(p.M, 256), z), kThreads, 0, s>>>(p);
+  } else if (p.M <= 16) {
+    GemmQuadKernel<TA, BT, 16, 256><<<dim3(Blocks(p.N, 256), Blocks(p.M, 16), z), kThreads, 0, s>>>(p);
+  } else {
+    GemmQuadKernel<TA, BT, 64, 64><<<dim3(Blocks(p.N, 64), Blocks(p.M, 64), z), kThreads, 0, s>>>(p);
+  }
+}
+
+template <typename BT>
+void LaunchLane(const Params& p, cudaStream_t s) {
+  if (p.N <= 16) {
+    GemmLaneKernel<BT, 64, 16><<<dim3(Blocks(p.N, 16), Blocks(p.M, 64)), kThreads, 0, s>>>(p);
+  } else if (p.M <= 16) {
+    GemmLaneKernel<BT, 16, 64><<<dim3(Blocks(p.N, 64), Blocks(p.M, 16)), kThreads, 0, s>>>(p);
+  } else {
+    GemmLaneKernel<BT, 32, 32><<<dim3(Blocks(p.N, 32), Blocks(p.M, 32)), kThreads, 0, s>>>(p);
+  }
+}
+
+size_t QuadTiles(size_t M, size_t N) {
+  if (N <= 16) return static_cast<size_t>(Blocks(M, 256)) * Blocks(N, 16);
+  if (M <= 16) return static_cast<size_t>(Blocks(N, 256)) * Blocks(M, 16);
+  return static_cast<size_t>(Blocks(M, 64)) * Blocks(N, 64);
+}
+
 }  // namespace
 
 size_t SplitKChunks(size_t M, size_t N, size_t K) {
-  const size_t tiles = ((M + 63) / 64) * ((N + 63) / 64);
-  if (K < 4 * kSplitKChunk || tiles >= 148) return 1;
+  if (K < 4 * kSplitKChunk || QuadTiles(M, N) >= 148) return 1;
   return (K + kSplitKChunk - 1) / kSplitKChunk;
 }
 
@@ -242,15 +281,13 @@ void GemmExact(const GemmArgs& a, cudaStream_t s) {
   Params p{a.A, a.B, a.C, a.M, a.N, a.K, a.alpha, a.b_col_scale, a.a_k_scale,
            a.bias, a.addend, a.act, a.accumulate, 0, nullptr};
   if (a.b_transposed) {
-    dim3 grid(static_cast<unsigned>((a.N + 31) / 32), static_cast<unsigned>((a.M + 31) / 32));
     switch (a.b_type) {
-      case BType::kF32: GemmLaneKernel<float><<<grid, 256, 0, s>>>(p); break;
-      case BType::kI8: GemmLaneKernel<int8_t><<<grid, 256, 0, s>>>(p); break;
-      case BType::kBf16: GemmLaneKernel<uint16_t><<<grid, 256, 0, s>>>(p); break;
+      case BType::kF32: LaunchLane<float>(p, s); break;
+      case BType::kI8: LaunchLane<int8_t>(p, s); break;
+      case BType::kBf16: LaunchLane<uint16_t>(p, s); break;
     }
     return;
   }
-  dim3 grid(static_cast<unsigned>((a.N + 63) / 64), static_cast<unsigned>((a.M + 63) / 64));
   if (a.a_transposed) {
     // Adapter gradients: a [rank x width] or [width x rank] result reduced over
     // every row of the batch.  With few output tiles and a long K the chunks go
@@ -260,20 +297,19 @@ void GemmExact(const GemmArgs& a, cudaStream_t s) {
         chunks * a.M * a.N <= a.split_scratch_floats) {
       p.k_chunk = kSplitKChunk;
       p.partials = a.split_scratch;
-      grid.z = static_cast<unsigned>(chunks);
-      GemmQuadKernel<true, float><<<grid, 256, 0, s>>>(p);
+      LaunchQuad<true, float>(p, static_cast<unsigned>(chunks), s);
       size_t blocks = (a.M * a.N + 255) / 256;
       if (blocks > 1184) blocks = 1184;
       SplitKFoldKernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(p, chunks);
       return;
     }
-    GemmQuadKernel<true, float><<<grid, 256, 0, s>>>(p);
+    LaunchQuad<true, float>(p, 1, s);
     return;
   }
   switch (a.b_type) {
-    case BType::kF32: GemmQuadKernel<false, float><<<grid, 256, 0, s>>>(p); break;
-    case BType::kI8: GemmQuadKernel<false, int8_t><<<grid, 256, 0, s>>>(p); break;
-    case BType::kBf16: GemmQuadKernel<false, uint16_t><<<grid, 256, 0, s>>>(p); break;
+    case BType::kF32: LaunchQuad<false, float>(p, 1, s); break;
+    case BType::kI8: LaunchQuad<false, int8_t>(p, 1, s); break;
+    case BType::kBf16: LaunchQuad<false, uint16_t>(p, 1, s); break;
   }
 }
 

@@ -230,32 +230,50 @@ UmmaGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (!ok && lane == 0) ep.status->wait_timeout = 1;
     if (bars->abort) ok = false;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t row = m0 + quarter * 32 + lane;
     if (ok && k_blocks > 0) {
+      // The accumulator arrives one row per thread; HBM wants one row per warp
+      // access.  Each warp turns its 32 x 128 slab through shared memory: the
+      // operand ring is idle by now (tmem_full fires after the last MMA has read
+      // it), so the slab lives there.  16-byte chunks are XOR-swizzled with the
+      // row so both the row-per-thread writes and the row-per-warp reads are
+      // bank-conflict free.  Only this warp touches its slab: __syncwarp suffices.
+      float* slab = reinterpret_cast<float*>(smem + quarter * (32 * kBlockN * 4));
 #pragma unroll 1
       for (uint32_t c0 = 0; c0 < kBlockN; c0 += 32) {
         uint32_t r[32];
         TmemLoad32(tmem_base + ((quarter * 32) << 16) + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < ep.M) {
-          const uint32_t n_base = n0 + c0;
-          float* crow = ep.C + static_cast<size_t>(row) * ep.N + n_base;
-          const float* drow = ep.addend ? ep.addend + static_cast<size_t>(row) * ep.N + n_base : nullptr;
 #pragma unroll
-          for (uint32_t j = 0; j < 32; j += 4) {
-            if (n_base + j >= ep.N) break;   // N % 4 == 0: a float4 is all in or all out
-            float v[4];
-#pragma unroll
-            for (uint32_t t = 0; t < 4; ++t) {
-              float x = __uint_as_float(r[j + t]);
-              const uint32_t n = n_base + j + t;
-              x = ep.col_scale ? x * __ldg(ep.col_scale + n) : x * ep.alpha;
-              if (drow) x = drow[j + t] + x;
-              if (ep.bias) x = x + __ldg(ep.bias + n);
-              v[t] = ApplyAct(x, ep.act);
-            }
-            *reinterpret_cast<float4*>(crow + j) = make_float4(v[0], v[1], v[2], v[3]);
+        for (uint32_t q = 0; q < 8; ++q) {
+          const uint32_t chunk = ((c0 >> 2) + q) ^ lane;   // 32 chunks of 4 floats per row
+          *reinterpret_cast<uint4*>(slab + lane * kBlockN + chunk * 4) =
+              make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+        }
+      }
+      __syncwarp();
+      // Lane l owns columns n0 + 4l .. 4l+3 of every row: its scale / bias are loop invariants.
+      const uint32_t n = n0 + lane * 4;
+      if (n < ep.N) {   // N % 4 == 0: a float4 is all in or all out
+        float4 scale = make_float4(ep.alpha, ep.alpha, ep.alpha, ep.alpha);
+        if (ep.col_scale) scale = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n));
+        float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ep.bias) bias = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
+        const uint32_t row0 = m0 + quarter * 32;
+        const uint32_t rows = row0 < ep.M ? (ep.M - row0 < 32 ? ep.M - row0 : 32) : 0;
+#pragma unroll 4
+        for (uint32_t rr = 0; rr < rows; ++rr) {
+          const float4 acc = *reinterpret_cast<const float4*>(slab + rr * kBlockN + ((lane ^ rr) * 4));
+          const size_t at = static_cast<size_t>(row0 + rr) * ep.N + n;
+          float4 v = make_float4(acc.x * scale.x, acc.y * scale.y, acc.z * scale.z, acc.w * scale.w);
+          if (ep.addend) {
+            const float4 d = __ldg(reinterpret_cast<const float4*>(ep.addend + at));
+            v = make_float4(d.x + v.x, d.y + v.y, d.z + v.z, d.w + v.w);
           }
+          if (ep.bias) v = make_float4(v.x + bias.x, v.y + bias.y, v.z + bias.z, v.w + bias.w);
+          if (ep.act != kActNone)
+            v = make_float4(ApplyAct(v.x, ep.act), ApplyAct(v.y, ep.act), ApplyAct(v.z, ep.act),
+                            ApplyAct(v.w, ep.act));
+          *reinterpret_cast<float4*>(ep.C + at) = v;
         }
       }
     }

@@ -185,8 +185,9 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
   if (a.a_transposed || a.accumulate) return {};
   if (a.K % 8 != 0 || a.N % 4 != 0 || a.K < 64 || a.N < 16 || a.M < 64) return {};
   if (a.M > 0xFFFFFFFFull || a.N > 0xFFFFFFFFull || a.K > 0xFFFFFFFFull) return {};
-  if ((reinterpret_cast<uintptr_t>(a.C) & 15) || (a.addend && (reinterpret_cast<uintptr_t>(a.addend) & 15)))
-    return {};
+  auto misaligned = [](const void* p) { return p && (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+  if (misaligned(a.C) || misaligned(a.addend) || misaligned(a.bias) || misaligned(a.b_col_scale))
+    return {};   // the epilogue moves float4s
 
   // ---- the weight, K-major bf16 [N][K], converted once per binding ----
   const WeightKey key{b_space, b_off, a.N, a.K, !a.b_transposed, static_cast<int>(a.b_type)};

@@ -98,7 +98,8 @@ def seeded_programs():
     f = P.f32_bits
 
     # GEMM family over odd shapes, every flag the opcodes admit.
-    for (M, N, K) in [(1, 1, 1), (3, 5, 7), (37, 29, 131), (8, 64, 13), (65, 33, 66)]:
+    for (M, N, K) in [(1, 1, 1), (3, 5, 7), (37, 29, 131), (8, 64, 13), (65, 33, 66),
+                      (300, 16, 70), (12, 300, 70)]:
         a = Arena(rng)
         A = a.alloc(M * K, "normal"); At = a.alloc(K * M, "normal")
         B = a.alloc(K * N, "normal"); Bt = a.alloc(N * K, "normal")
