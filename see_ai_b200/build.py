@@ -28,6 +28,7 @@ CU_SOURCES = {
     "k_optim.cu": ["-fmad=false"],
     "k_attention.cu": ["-fmad=false"],
     "k_gemm_exact.cu": ["-fmad=false"],
+    "k_gemm_skinny.cu": ["-fmad=false"],
     "k_gemm_umma.cu": [],
     "k_eval.cu": [],
     "k_attn_umma.cu": [],
@@ -51,7 +52,7 @@ def _stale(obj: str, deps) -> bool:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
-    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".h")]
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "see_cuda.h"))
     jobs = []
     objs = []

@@ -17,58 +17,18 @@
 // -fmad=false; no multiply is ever fused into an add.  This family is the
 // parity anchor and the path for the rank-r adapter products, whose outputs are
 // 8-16 wide (or tall): the block tile comes in three shapes (64x64, 256x16,
-// 16x256 for the quad order; 32x32, 64x16, 16x64 for the lane order) picked
+// 16x256 for the quad order; 64x32, 128x16, 16x128 for the lane order) picked
 // from the output shape, so a skinny product wastes no lanes.  A tile shape
 // changes which thread owns an element, never the element's arithmetic.
 // Large frozen-weight products carrying the relaxed permission go to the
 // tensor cores instead.
-#include "kernels.h"
+#include "gemm_exact_common.cuh"
 
 namespace see::k {
 
 namespace {
 
-constexpr float kGeluC = 0.7978845608028654f;
-constexpr float kGeluA = 0.044715f;
-
-__device__ __forceinline__ float ApplyAct(float v, Act act) {
-  switch (act) {
-    case kActRelu: return v > 0.0f ? v : 0.0f;
-    case kActGelu: {
-      const float t = tanhf(kGeluC * (v + kGeluA * v * v * v));
-      return 0.5f * v * (1.0f + t);
-    }
-    case kActSilu: return v * (1.0f / (1.0f + expf(-v)));
-    default: return v;
-  }
-}
-
-template <typename T> __device__ __forceinline__ float Widen(T v);
-template <> __device__ __forceinline__ float Widen<float>(float v) { return v; }
-template <> __device__ __forceinline__ float Widen<int8_t>(int8_t v) { return static_cast<float>(v); }
-template <> __device__ __forceinline__ float Widen<uint16_t>(uint16_t v) {
-  return __uint_as_float(static_cast<uint32_t>(v) << 16);
-}
-
-struct Params {
-  const float* A;
-  const void* B;
-  float* C;
-  size_t M, N, K;
-  float alpha;
-  const float* b_col_scale;
-  const float* a_k_scale;
-  const float* bias;
-  const float* addend;
-  Act act;
-  bool accumulate;
-  // Split-K (long reductions into small outputs): block z reduces k in
-  // [z * k_chunk, (z + 1) * k_chunk) with the quad order inside the chunk and
-  // writes its raw sums to partials[z][M][N]; a second kernel folds the chunks
-  // in chunk order.  k_chunk is a multiple of 16, so quads stay aligned to k = 0.
-  size_t k_chunk;
-  float* partials;
-};
+using namespace exact;
 
 constexpr int BK = 16;
 constexpr int kThreads = 256;
@@ -89,8 +49,8 @@ __device__ __forceinline__ float LoadB(const Params& p, size_t k, size_t n) {
 template <bool TA, typename BT, int BM, int BN>
 __global__ void __launch_bounds__(kThreads) GemmQuadKernel(Params p) {
   static_assert(BM * BN == 16 * kThreads, "4x4 outputs per thread");
-  __shared__ float As[BK][BM + 4];
-  __shared__ float Bs[BK][BN + 4];
+  __shared__ __align__(16) float As[BK][BM + 4];
+  __shared__ __align__(16) float Bs[BK][BN + 4];
   const int tx = threadIdx.x % (BN / 4), ty = threadIdx.x / (BN / 4);
   const size_t m0 = static_cast<size_t>(blockIdx.y) * BM, n0 = static_cast<size_t>(blockIdx.x) * BN;
   float c[4][4];
@@ -101,16 +61,37 @@ __global__ void __launch_bounds__(kThreads) GemmQuadKernel(Params p) {
       const size_t m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
       c[i][j] = (p.accumulate && m < p.M && n < p.N) ? p.C[m * p.N + n] : 0.0f;
     }
+  const bool a_vec = (reinterpret_cast<uintptr_t>(p.A) & 15) == 0 && ((TA ? p.M : p.K) & 3) == 0;
   const size_t k_begin = p.k_chunk ? static_cast<size_t>(blockIdx.z) * p.k_chunk : 0;
   const size_t k_end = p.k_chunk ? (k_begin + p.k_chunk < p.K ? k_begin + p.k_chunk : p.K) : p.K;
   for (size_t k0 = k_begin; k0 < k_end; k0 += BK) {
     // Stage the tiles; alpha and the column scale are applied here, once per
     // element, as the reference applies them when an element enters the product.
+    if (a_vec) {  // 16-byte global loads along A's contiguous axis
 #pragma unroll
-    for (int idx = threadIdx.x; idx < BM * BK; idx += kThreads) {
-      int mm, kk;
-      if (TA) { kk = idx / BM; mm = idx % BM; } else { mm = idx / BK; kk = idx % BK; }
-      As[kk][mm] = p.alpha * LoadA<TA>(p, m0 + mm, k0 + kk);
+      for (int idx = threadIdx.x; idx < BM * BK / 4; idx += kThreads) {
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (TA) {
+          const int kk = idx / (BM / 4), mm = (idx % (BM / 4)) * 4;
+          if (m0 + mm < p.M && k0 + kk < p.K)
+            v = *reinterpret_cast<const float4*>(p.A + (k0 + kk) * p.M + m0 + mm);
+          *reinterpret_cast<float4*>(&As[kk][mm]) =
+              make_float4(p.alpha * v.x, p.alpha * v.y, p.alpha * v.z, p.alpha * v.w);
+        } else {
+          const int mm = idx / (BK / 4), kk = (idx % (BK / 4)) * 4;
+          if (m0 + mm < p.M && k0 + kk < p.K)
+            v = *reinterpret_cast<const float4*>(p.A + (m0 + mm) * p.K + k0 + kk);
+          As[kk][mm] = p.alpha * v.x; As[kk + 1][mm] = p.alpha * v.y;
+          As[kk + 2][mm] = p.alpha * v.z; As[kk + 3][mm] = p.alpha * v.w;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int idx = threadIdx.x; idx < BM * BK; idx += kThreads) {
+        int mm, kk;
+        if (TA) { kk = idx / BM; mm = idx % BM; } else { mm = idx / BK; kk = idx % BK; }
+        As[kk][mm] = p.alpha * LoadA<TA>(p, m0 + mm, k0 + kk);
+      }
     }
 #pragma unroll
     for (int idx = threadIdx.x; idx < BK * BN; idx += kThreads) {
@@ -125,11 +106,11 @@ __global__ void __launch_bounds__(kThreads) GemmQuadKernel(Params p) {
     for (; kk + 4 <= kmax; kk += 4) {
       float a[4][4], b[4][4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) a[q][i] = As[kk + q][ty * 4 + i];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) b[q][j] = Bs[kk + q][tx * 4 + j];
+      for (int q = 0; q < 4; ++q) {  // one 16-byte shared load per operand row
+        const float4 av = *reinterpret_cast<const float4*>(&As[kk + q][ty * 4]);
+        const float4 bv = *reinterpret_cast<const float4*>(&Bs[kk + q][tx * 4]);
+        a[q][0] = av.x; a[q][1] = av.y; a[q][2] = av.z; a[q][3] = av.w;
+        b[q][0] = bv.x; b[q][1] = bv.y; b[q][2] = bv.z; b[q][3] = bv.w;
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i)
@@ -150,6 +131,30 @@ __global__ void __launch_bounds__(kThreads) GemmQuadKernel(Params p) {
           c[i][j] = c[i][j] + As[kk][ty * 4 + i] * Bs[kk][tx * 4 + j];
     }
     __syncthreads();
+  }
+  // Whole 16-byte rows of the thread's 4x4 block when the layout allows it.
+  const size_t nq = n0 + tx * 4;
+  const bool vec = !p.partials && (p.N & 3) == 0 && nq + 3 < p.N &&
+                   (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(p.addend) & 15) == 0;
+  if (vec) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const size_t m = m0 + ty * 4 + i;
+      if (m >= p.M) continue;
+      float v[4] = {c[i][0], c[i][1], c[i][2], c[i][3]};
+      if (p.addend) {
+        const float4 d = *reinterpret_cast<const float4*>(p.addend + m * p.N + nq);
+        v[0] = d.x + v[0]; v[1] = d.y + v[1]; v[2] = d.z + v[2]; v[3] = d.w + v[3];
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (p.bias) v[j] = v[j] + p.bias[nq + j];
+        v[j] = ApplyAct(v[j], p.act);
+      }
+      *reinterpret_cast<float4*>(p.C + m * p.N + nq) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    return;
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -173,36 +178,65 @@ __global__ void SplitKFoldKernel(Params p, size_t chunks) {
   const size_t total = p.M * p.N;
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += stride) {
-    float v = p.partials[i];
-    for (size_t z = 1; z < chunks; ++z) v = v + p.partials[z * total + i];
+    // Sixteen independent loads at a time, added in chunk order.
+    float v = 0.0f;
+    for (size_t z0 = 0; z0 < chunks; z0 += 16) {
+      float part[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        part[u] = z0 + u < chunks ? p.partials[(z0 + u) * total + i] : 0.0f;
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        if (z0 + u == 0) v = part[0];
+        else if (z0 + u < chunks) v = v + part[u];
+      }
+    }
     if (p.addend) v = p.addend[i] + v;
     if (p.bias) v = v + p.bias[i % p.N];
     p.C[i] = ApplyAct(v, p.act);
   }
 }
 
-// ---- lane order: BM x BN tile (BM * BN = 1024), 256 threads, 2x2 outputs x 8 lanes ------
+// ---- lane order: BM x BN tile (BM * BN = 2048), 256 threads, 4x2 outputs x 8 lanes -----
 template <typename BT, int BM, int BN>
 __global__ void __launch_bounds__(kThreads) GemmLaneKernel(Params p) {
-  static_assert(BM * BN == 4 * kThreads, "2x2 outputs per thread");
-  __shared__ float As[BK][BM + 2];
-  __shared__ float Bs[BK][BN + 2];
+  static_assert(BM * BN == 8 * kThreads, "4x2 outputs per thread");
+  __shared__ __align__(16) float As[BK][BM + 4];
+  __shared__ __align__(16) float Bs[BK][BN + 4];
   const int tx = threadIdx.x % (BN / 2), ty = threadIdx.x / (BN / 2);
   const size_t m0 = static_cast<size_t>(blockIdx.y) * BM, n0 = static_cast<size_t>(blockIdx.x) * BN;
-  float acc[2][2][8];
+  float acc[4][2][8];
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int l = 0; l < 8; ++l) acc[i][j][l] = 0.0f;
+  const bool a_vec = (p.K & 3) == 0 && (reinterpret_cast<uintptr_t>(p.A) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(p.a_k_scale) & 15) == 0;
   for (size_t k0 = 0; k0 < p.K; k0 += BK) {
+    if (a_vec) {  // 16-byte global loads along k
 #pragma unroll
-    for (int idx = threadIdx.x; idx < BM * BK; idx += kThreads) {
-      const int mm = idx / BK, kk = idx % BK;
-      float a = LoadA<false>(p, m0 + mm, k0 + kk);
-      if (p.a_k_scale && k0 + kk < p.K) a = a * p.a_k_scale[k0 + kk];
-      As[kk][mm] = a;
+      for (int idx = threadIdx.x; idx < BM * BK / 4; idx += kThreads) {
+        const int mm = idx / (BK / 4), kk = (idx % (BK / 4)) * 4;
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (m0 + mm < p.M && k0 + kk < p.K) {
+          v = *reinterpret_cast<const float4*>(p.A + (m0 + mm) * p.K + k0 + kk);
+          if (p.a_k_scale) {
+            const float4 sc = *reinterpret_cast<const float4*>(p.a_k_scale + k0 + kk);
+            v.x = v.x * sc.x; v.y = v.y * sc.y; v.z = v.z * sc.z; v.w = v.w * sc.w;
+          }
+        }
+        As[kk][mm] = v.x; As[kk + 1][mm] = v.y; As[kk + 2][mm] = v.z; As[kk + 3][mm] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int idx = threadIdx.x; idx < BM * BK; idx += kThreads) {
+        const int mm = idx / BK, kk = idx % BK;
+        float a = LoadA<false>(p, m0 + mm, k0 + kk);
+        if (p.a_k_scale && k0 + kk < p.K) a = a * p.a_k_scale[k0 + kk];
+        As[kk][mm] = a;
+      }
     }
 #pragma unroll
     for (int idx = threadIdx.x; idx < BN * BK; idx += kThreads) {
@@ -215,20 +249,46 @@ __global__ void __launch_bounds__(kThreads) GemmLaneKernel(Params p) {
     for (int kk = 0; kk < BK; ++kk) {
       if (kk < kmax) {
         const int l = kk & 7;  // k0 is a multiple of 16, so k mod 8 == kk mod 8
+        const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+        const float2 bv = *reinterpret_cast<const float2*>(&Bs[kk][tx * 2]);
+        const float a[4] = {av.x, av.y, av.z, av.w};
+        const float b[2] = {bv.x, bv.y};
 #pragma unroll
-        for (int i = 0; i < 2; ++i)
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
-          for (int j = 0; j < 2; ++j)
-            acc[i][j][l] = acc[i][j][l] + As[kk][ty * 2 + i] * Bs[kk][tx * 2 + j];
+          for (int j = 0; j < 2; ++j) acc[i][j][l] = acc[i][j][l] + a[i] * b[j];
       }
     }
     __syncthreads();
   }
+  const size_t np = n0 + tx * 2;
+  if ((p.N & 1) == 0 && np + 1 < p.N && (reinterpret_cast<uintptr_t>(p.C) & 7) == 0 &&
+      (reinterpret_cast<uintptr_t>(p.addend) & 7) == 0) {  // 8-byte pairs
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < 4; ++i) {
+      const size_t m = m0 + ty * 4 + i;
+      if (m >= p.M) continue;
+      float v[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float s = acc[i][j][0];
+#pragma unroll
+        for (int l = 1; l < 8; ++l) s = s + acc[i][j][l];
+        v[j] = p.alpha * s;
+      }
+      if (p.addend) {
+        const float2 d = *reinterpret_cast<const float2*>(p.addend + m * p.N + np);
+        v[0] = d.x + v[0]; v[1] = d.y + v[1];
+      }
+      *reinterpret_cast<float2*>(p.C + m * p.N + np) = make_float2(v[0], v[1]);
+    }
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
-      const size_t m = m0 + ty * 2 + i, n = n0 + tx * 2 + j;
+      const size_t m = m0 + ty * 4 + i, n = n0 + tx * 2 + j;
       if (m >= p.M || n >= p.N) continue;
       float s = acc[i][j][0];
 #pragma unroll
@@ -255,11 +315,11 @@ void LaunchQuad(const Params& p, unsigned z, cudaStream_t s) {
 template <typename BT>
 void LaunchLane(const Params& p, cudaStream_t s) {
   if (p.N <= 16) {
-    GemmLaneKernel<BT, 64, 16><<<dim3(Blocks(p.N, 16), Blocks(p.M, 64)), kThreads, 0, s>>>(p);
+    GemmLaneKernel<BT, 128, 16><<<dim3(Blocks(p.N, 16), Blocks(p.M, 128)), kThreads, 0, s>>>(p);
   } else if (p.M <= 16) {
-    GemmLaneKernel<BT, 16, 64><<<dim3(Blocks(p.N, 64), Blocks(p.M, 16)), kThreads, 0, s>>>(p);
+    GemmLaneKernel<BT, 16, 128><<<dim3(Blocks(p.N, 128), Blocks(p.M, 16)), kThreads, 0, s>>>(p);
   } else {
-    GemmLaneKernel<BT, 32, 32><<<dim3(Blocks(p.N, 32), Blocks(p.M, 32)), kThreads, 0, s>>>(p);
+    GemmLaneKernel<BT, 64, 32><<<dim3(Blocks(p.N, 32), Blocks(p.M, 64)), kThreads, 0, s>>>(p);
   }
 }
 
@@ -281,6 +341,7 @@ void GemmExact(const GemmArgs& a, cudaStream_t s) {
   Params p{a.A, a.B, a.C, a.M, a.N, a.K, a.alpha, a.b_col_scale, a.a_k_scale,
            a.bias, a.addend, a.act, a.accumulate, 0, nullptr};
   if (a.b_transposed) {
+    if (a.b_type == BType::kF32 && (SkinnyReduce(p, true, s) || SkinnyExpand(p, true, s))) return;
     switch (a.b_type) {
       case BType::kF32: LaunchLane<float>(p, s); break;
       case BType::kI8: LaunchLane<int8_t>(p, s); break;
@@ -297,7 +358,7 @@ void GemmExact(const GemmArgs& a, cudaStream_t s) {
         chunks * a.M * a.N <= a.split_scratch_floats) {
       p.k_chunk = kSplitKChunk;
       p.partials = a.split_scratch;
-      LaunchQuad<true, float>(p, static_cast<unsigned>(chunks), s);
+      if (!SkinnyTnPartials(p, chunks, s)) LaunchQuad<true, float>(p, static_cast<unsigned>(chunks), s);
       size_t blocks = (a.M * a.N + 255) / 256;
       if (blocks > 1184) blocks = 1184;
       SplitKFoldKernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(p, chunks);
@@ -306,6 +367,7 @@ void GemmExact(const GemmArgs& a, cudaStream_t s) {
     LaunchQuad<true, float>(p, 1, s);
     return;
   }
+  if (a.b_type == BType::kF32 && (SkinnyReduce(p, false, s) || SkinnyExpand(p, false, s))) return;
   switch (a.b_type) {
     case BType::kF32: LaunchQuad<false, float>(p, 1, s); break;
     case BType::kI8: LaunchQuad<false, int8_t>(p, 1, s); break;

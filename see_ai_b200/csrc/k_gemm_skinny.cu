@@ -1,0 +1,464 @@
+// Shape-specialised exact kernels for the rank-r adapter products of a LoRA
+// update.  A decoder step runs six of them per adapted projection, each moving
+// one [rows x width] activation through HBM for a few hundred MFLOP, so they
+// are streaming kernels: the wide operand is read once with 16-byte loads
+// straight into registers, the rank-r operand lives in shared memory or
+// registers, and there is no block-wide barrier inside the stream.
+//
+// Arithmetic per output element is the CPU executor's, operation for operation
+// (reference: runtime/executor/gemm.cc:73-187 quad order, :346-527 lane
+// order); compiled with -fmad=false.  Only the assignment of elements to
+// threads differs from the general tile kernels.
+#include "gemm_exact_common.cuh"
+
+namespace see::k::exact {
+
+namespace {
+
+// One quad of the quad order for four neighbouring columns:
+//   c[j] += ((a0*w0[j] + a1*w1[j]) + a2*w2[j]) + a3*w3[j]
+__device__ __forceinline__ void QuadStep(float (&c)[4], float a0, float a1, float a2, float a3,
+                                         const float4& w0, const float4& w1, const float4& w2,
+                                         const float4& w3) {
+  const float b0[4] = {w0.x, w0.y, w0.z, w0.w};
+  const float b1[4] = {w1.x, w1.y, w1.z, w1.w};
+  const float b2[4] = {w2.x, w2.y, w2.z, w2.w};
+  const float b3[4] = {w3.x, w3.y, w3.z, w3.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float t = a0 * b0[j];
+    t = t + a1 * b1[j];
+    t = t + a2 * b2[j];
+    t = t + a3 * b3[j];
+    c[j] = c[j] + t;
+  }
+}
+
+// ---- reduce: C[M, N = 4G] = A[M, K] * W, K long --------------------------------------
+// A warp owns 2 * 32 / G rows; lane = (row pair, column group g) holds the
+// outputs C[row, 4g .. 4g+3] of two rows, so every 16 bytes of W read from shared
+// memory feed two rows.  The lanes of a row read the same 16 bytes of A (one
+// broadcast load); a row is consumed a 128-byte line (32 k) at a time, eight
+// loads in flight per row.  W is staged in shared memory kChunkK reduction steps
+// at a time, in the layout it has in memory: [k][N] for the quad order (W is
+// [K, N]); [n][k] for the lane order (W is [N, K]), where row n starts at
+// n * kWnStride + 4 * (n / 4) floats so that the four column groups of a warp
+// read four different bank groups.
+constexpr int kReduceThreads = 256;
+constexpr int kReduceRows = 2;   // rows per thread
+constexpr int kChunkK = 512;
+constexpr int kWnStride = kChunkK + 16;
+
+__device__ __forceinline__ int WnRow(int n) { return n * kWnStride + 4 * (n >> 2); }
+
+template <int G, bool kLane>
+__global__ void __launch_bounds__(kReduceThreads) ReduceKernel(Params p) {
+  constexpr int N = 4 * G;
+  constexpr int kRowsPerWarp = 32 / G;  // per row slot; a warp covers kReduceRows of these
+  constexpr int kRowsPerBlock = kReduceRows * kRowsPerWarp * (kReduceThreads / 32);
+  __shared__ __align__(16) float Wsm[N * kWnStride];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane % G;
+  const float* B = static_cast<const float*>(p.B);
+  size_t row[kReduceRows];
+  bool live[kReduceRows];
+  const float* xrow[kReduceRows];
+#pragma unroll
+  for (int r = 0; r < kReduceRows; ++r) {
+    row[r] = static_cast<size_t>(blockIdx.x) * kRowsPerBlock +
+             (warp * kReduceRows + r) * kRowsPerWarp + lane / G;
+    live[r] = row[r] < p.M;
+    xrow[r] = p.A + (live[r] ? row[r] : 0) * p.K;
+  }
+
+  float c[kReduceRows][4];       // quad order
+  float acc[kReduceRows][4][8];  // lane order
+#pragma unroll
+  for (int r = 0; r < kReduceRows; ++r)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      c[r][j] = 0.0f;
+#pragma unroll
+      for (int l = 0; l < 8; ++l) acc[r][j][l] = 0.0f;
+    }
+
+  for (size_t kc0 = 0; kc0 < p.K; kc0 += kChunkK) {
+    const int kc = p.K - kc0 < static_cast<size_t>(kChunkK) ? static_cast<int>(p.K - kc0) : kChunkK;
+    __syncthreads();
+    if (kLane) {
+      const int per_row = kc / 4;
+      for (int idx = threadIdx.x; idx < N * per_row; idx += kReduceThreads) {
+        const int n = idx / per_row, kq = idx % per_row;
+        *reinterpret_cast<float4*>(&Wsm[WnRow(n) + 4 * kq]) =
+            *reinterpret_cast<const float4*>(B + static_cast<size_t>(n) * p.K + kc0 + 4 * kq);
+      }
+    } else {
+      const float4* src = reinterpret_cast<const float4*>(B + kc0 * N);
+      for (int idx = threadIdx.x; idx < kc * G; idx += kReduceThreads)
+        reinterpret_cast<float4*>(Wsm)[idx] = src[idx];
+    }
+    __syncthreads();
+    if (!live[0]) continue;  // rows ascend with r: a dead first row means a dead thread
+    for (int k = 0; k < kc; k += 32) {
+      float4 x[kReduceRows][8];
+#pragma unroll
+      for (int r = 0; r < kReduceRows; ++r)
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          x[r][q] = k + 4 * q < kc ? *reinterpret_cast<const float4*>(xrow[r] + kc0 + k + 4 * q)
+                                   : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int kq = k + 4 * q;
+        if (kq < kc) {
+          if (kLane) {
+            // Product k goes to accumulator k mod 8; kc0 and k are multiples of 32.
+            const int l0 = (q & 1) * 4;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float4 w = *reinterpret_cast<const float4*>(&Wsm[WnRow(4 * g + j) + kq]);
+#pragma unroll
+              for (int r = 0; r < kReduceRows; ++r) {
+                acc[r][j][l0 + 0] = acc[r][j][l0 + 0] + x[r][q].x * w.x;
+                acc[r][j][l0 + 1] = acc[r][j][l0 + 1] + x[r][q].y * w.y;
+                acc[r][j][l0 + 2] = acc[r][j][l0 + 2] + x[r][q].z * w.z;
+                acc[r][j][l0 + 3] = acc[r][j][l0 + 3] + x[r][q].w * w.w;
+              }
+            }
+          } else {
+            const float4 w0 = *reinterpret_cast<const float4*>(&Wsm[(kq + 0) * N + 4 * g]);
+            const float4 w1 = *reinterpret_cast<const float4*>(&Wsm[(kq + 1) * N + 4 * g]);
+            const float4 w2 = *reinterpret_cast<const float4*>(&Wsm[(kq + 2) * N + 4 * g]);
+            const float4 w3 = *reinterpret_cast<const float4*>(&Wsm[(kq + 3) * N + 4 * g]);
+#pragma unroll
+            for (int r = 0; r < kReduceRows; ++r)
+              QuadStep(c[r], p.alpha * x[r][q].x, p.alpha * x[r][q].y, p.alpha * x[r][q].z,
+                       p.alpha * x[r][q].w, w0, w1, w2, w3);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kReduceRows; ++r) {
+    if (!live[r]) continue;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (kLane) {
+        float s = acc[r][j][0];
+#pragma unroll
+        for (int l = 1; l < 8; ++l) s = s + acc[r][j][l];
+        v[j] = p.alpha * s;
+      } else {
+        v[j] = c[r][j];
+      }
+    }
+    const size_t o = row[r] * N + 4 * g;
+    if (p.addend) {
+      const float4 d = *reinterpret_cast<const float4*>(p.addend + o);
+      v[0] = d.x + v[0]; v[1] = d.y + v[1]; v[2] = d.z + v[2]; v[3] = d.w + v[3];
+    }
+    if (!kLane) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (p.bias) v[j] = v[j] + p.bias[4 * g + j];
+        v[j] = ApplyAct(v[j], p.act);
+      }
+    }
+    *reinterpret_cast<float4*>(p.C + o) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+}
+
+template <int G>
+void LaunchReduce(const Params& p, bool lane_order, cudaStream_t s) {
+  constexpr int kRowsPerBlock = kReduceRows * (32 / G) * (kReduceThreads / 32);
+  const unsigned blocks = static_cast<unsigned>((p.M + kRowsPerBlock - 1) / kRowsPerBlock);
+  if (lane_order) ReduceKernel<G, true><<<blocks, kReduceThreads, 0, s>>>(p);
+  else ReduceKernel<G, false><<<blocks, kReduceThreads, 0, s>>>(p);
+}
+
+}  // namespace
+
+bool SkinnyReduce(const Params& p, bool lane_order, cudaStream_t s) {
+  if (p.N != 4 && p.N != 8 && p.N != 16) return false;
+  if (p.K < 64 || (p.K & 3) != 0 || p.M < 256) return false;
+  if (p.accumulate || p.b_col_scale || p.a_k_scale || p.partials) return false;
+  if (lane_order && (p.bias || p.act != kActNone)) return false;
+  if (!Aligned16(p.A) || !Aligned16(p.B) || !Aligned16(p.C) || !Aligned16(p.addend)) return false;
+  switch (p.N) {
+    case 4: LaunchReduce<1>(p, lane_order, s); break;
+    case 8: LaunchReduce<2>(p, lane_order, s); break;
+    default: LaunchReduce<4>(p, lane_order, s); break;
+  }
+  return true;
+}
+
+namespace {
+
+// ---- expand: C[M, N] = addend + A[M, K] * W with K = rank (4..16) ---------------------
+// A thread owns four neighbouring columns for kExpandRows consecutive rows and
+// keeps its K x 4 slice of W in registers.  The block's rows of A (kExpandRows x
+// K floats) are staged in shared memory once and read back as broadcasts.  Rows
+// go four at a time: the four 16-byte addend loads are issued before any
+// arithmetic, so each thread keeps 64 bytes of the stream in flight.  The kernel
+// moves 32 bytes per 2K multiply-adds.
+constexpr int kExpandThreads = 64;
+constexpr int kExpandRows = 32;
+constexpr int kExpandBatch = 4;
+
+template <int K, bool kLane>
+__global__ void __launch_bounds__(kExpandThreads) ExpandKernel(Params p) {
+  __shared__ __align__(16) float As[kExpandRows][K];
+  const size_t r0 = static_cast<size_t>(blockIdx.y) * kExpandRows;
+  const int rows = p.M - r0 < static_cast<size_t>(kExpandRows) ? static_cast<int>(p.M - r0) : kExpandRows;
+  {
+    const float4* src = reinterpret_cast<const float4*>(p.A + r0 * K);
+    for (int idx = threadIdx.x; idx < rows * K / 4; idx += kExpandThreads)
+      reinterpret_cast<float4*>(&As[0][0])[idx] = src[idx];
+  }
+  __syncthreads();
+  const size_t n = (static_cast<size_t>(blockIdx.x) * kExpandThreads + threadIdx.x) * 4;
+  if (n >= p.N) return;
+  const float* B = static_cast<const float*>(p.B);
+  float w[K][4];
+  if (kLane) {  // W is [N, K]
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int kq = 0; kq < K; kq += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(B + (n + j) * K + kq);
+        w[kq][j] = t.x; w[kq + 1][j] = t.y; w[kq + 2][j] = t.z; w[kq + 3][j] = t.w;
+      }
+  } else {      // W is [K, N]
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const float4 t = *reinterpret_cast<const float4*>(B + static_cast<size_t>(k) * p.N + n);
+      w[k][0] = t.x; w[k][1] = t.y; w[k][2] = t.z; w[k][3] = t.w;
+    }
+  }
+  float bias[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (p.bias) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) bias[j] = p.bias[n + j];
+  }
+  for (int mb = 0; mb < rows; mb += kExpandBatch) {
+    float4 d[kExpandBatch];
+#pragma unroll
+    for (int u = 0; u < kExpandBatch; ++u)
+      d[u] = (p.addend && mb + u < rows)
+                 ? *reinterpret_cast<const float4*>(p.addend + (r0 + mb + u) * p.N + n)
+                 : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int u = 0; u < kExpandBatch; ++u) {
+      if (mb + u >= rows) break;
+      float a[K];
+#pragma unroll
+      for (int kq = 0; kq < K; kq += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(&As[mb + u][kq]);
+        a[kq] = t.x; a[kq + 1] = t.y; a[kq + 2] = t.z; a[kq + 3] = t.w;
+      }
+      float v[4];
+      if (kLane) {
+        // Product k into accumulator k mod 8, from zero; accumulators summed 0..7.
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float acc[8];
+#pragma unroll
+          for (int l = 0; l < 8; ++l) acc[l] = 0.0f;
+#pragma unroll
+          for (int k = 0; k < K; ++k) acc[k & 7] = acc[k & 7] + a[k] * w[k][j];
+          float s = acc[0];
+#pragma unroll
+          for (int l = 1; l < 8; ++l) s = s + acc[l];
+          v[j] = p.alpha * s;
+        }
+      } else {
+#pragma unroll
+        for (int kq = 0; kq < K; ++kq) a[kq] = p.alpha * a[kq];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float c = 0.0f;
+#pragma unroll
+          for (int kq = 0; kq < K; kq += 4) {
+            float t = a[kq] * w[kq][j];
+            t = t + a[kq + 1] * w[kq + 1][j];
+            t = t + a[kq + 2] * w[kq + 2][j];
+            t = t + a[kq + 3] * w[kq + 3][j];
+            c = c + t;
+          }
+          v[j] = c;
+        }
+      }
+      if (p.addend) {
+        v[0] = d[u].x + v[0]; v[1] = d[u].y + v[1]; v[2] = d[u].z + v[2]; v[3] = d[u].w + v[3];
+      }
+      if (!kLane) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (p.bias) v[j] = v[j] + bias[j];
+          v[j] = ApplyAct(v[j], p.act);
+        }
+      }
+      *reinterpret_cast<float4*>(p.C + (r0 + mb + u) * p.N + n) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+  }
+}
+
+template <int K>
+void LaunchExpand(const Params& p, bool lane_order, cudaStream_t s) {
+  const dim3 grid(static_cast<unsigned>((p.N / 4 + kExpandThreads - 1) / kExpandThreads),
+                  static_cast<unsigned>((p.M + kExpandRows - 1) / kExpandRows));
+  if (lane_order) ExpandKernel<K, true><<<grid, kExpandThreads, 0, s>>>(p);
+  else ExpandKernel<K, false><<<grid, kExpandThreads, 0, s>>>(p);
+}
+
+}  // namespace
+
+bool SkinnyExpand(const Params& p, bool lane_order, cudaStream_t s) {
+  if (p.K != 4 && p.K != 8 && p.K != 12 && p.K != 16) return false;
+  if ((p.N & 3) != 0 || p.N < 64 || p.M < 64) return false;
+  if (p.M > 65535u * static_cast<size_t>(kExpandRows)) return false;
+  if (p.accumulate || p.b_col_scale || p.a_k_scale || p.partials) return false;
+  if (lane_order && (p.bias || p.act != kActNone)) return false;
+  if (!Aligned16(p.A) || !Aligned16(p.B) || !Aligned16(p.C) || !Aligned16(p.addend)) return false;
+  switch (p.K) {
+    case 4: LaunchExpand<4>(p, lane_order, s); break;
+    case 8: LaunchExpand<8>(p, lane_order, s); break;
+    case 12: LaunchExpand<12>(p, lane_order, s); break;
+    default: LaunchExpand<16>(p, lane_order, s); break;
+  }
+  return true;
+}
+
+namespace {
+
+// ---- transposed-A partials: C = A^T * B over one K chunk, output <= 16 wide or tall ----
+// C[i, j] = sum_k (alpha * A[k, i]) * B[k, j].  One operand is `wide` (its rows
+// are W floats, streamed once with 8-byte loads), the other `narrow` (rows of
+// R floats, R in {4, 8, 12, 16}).  A block takes one chunk of kTnChunk reduction
+// rows and one segment of 2 * kTnThreads wide columns; the chunk's narrow rows
+// are staged in shared memory transposed, Ns[r][k], so the four k of a quad
+// come back in one 16-byte broadcast load.  Each thread holds the R x 2 partial
+// sums of its two wide columns and walks the chunk in quad order, exactly as
+// the general kernel does.  Wide rows are fetched sixteen at a time into one of
+// two register buffers, the next sixteen in flight while these are consumed.
+constexpr int kTnThreads = 128;
+constexpr int kTnChunk = 256;
+constexpr int kTnStage = 16;
+static_assert(kTnChunk == kSplitKChunk, "the chunk geometry is part of the result");
+
+template <bool kWideA, int R>
+__global__ void __launch_bounds__(kTnThreads) TnPartialKernel(Params p) {
+  __shared__ __align__(16) float Ns[R][kTnChunk + 4];
+  const size_t W = kWideA ? p.M : p.N;
+  const float* wide = kWideA ? p.A : static_cast<const float*>(p.B);
+  const float* narrow = kWideA ? static_cast<const float*>(p.B) : p.A;
+  const size_t k0 = static_cast<size_t>(blockIdx.z) * kTnChunk;
+  const int len = p.K - k0 < static_cast<size_t>(kTnChunk) ? static_cast<int>(p.K - k0) : kTnChunk;
+  for (int idx = threadIdx.x; idx < len * R; idx += kTnThreads) {
+    const int m = idx / R, r = idx % R;
+    const float v = narrow[(k0 + m) * R + r];
+    Ns[r][m] = kWideA ? v : p.alpha * v;
+  }
+  __syncthreads();
+  const size_t w0 = (static_cast<size_t>(blockIdx.x) * kTnThreads + threadIdx.x) * 2;
+  if (w0 >= W) return;
+  float acc[R][2];
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r][0] = acc[r][1] = 0.0f;
+  const float* wp = wide + k0 * W + w0;
+
+  auto load = [&](float2 (&buf)[kTnStage], int m0) {
+#pragma unroll
+    for (int u = 0; u < kTnStage; ++u) {
+      buf[u] = m0 + u < len ? *reinterpret_cast<const float2*>(wp + static_cast<size_t>(m0 + u) * W)
+                            : make_float2(0.0f, 0.0f);
+      if (kWideA) { buf[u].x = p.alpha * buf[u].x; buf[u].y = p.alpha * buf[u].y; }
+    }
+  };
+  auto consume = [&](const float2 (&buf)[kTnStage], int m0) {
+#pragma unroll
+    for (int q = 0; q < kTnStage / 4; ++q) {
+      const int m = m0 + 4 * q;
+      if (m + 4 <= len) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const float4 nv = *reinterpret_cast<const float4*>(&Ns[r][m]);
+          float t = nv.x * buf[4 * q].x;
+          t = t + nv.y * buf[4 * q + 1].x;
+          t = t + nv.z * buf[4 * q + 2].x;
+          t = t + nv.w * buf[4 * q + 3].x;
+          acc[r][0] = acc[r][0] + t;
+          float u = nv.x * buf[4 * q].y;
+          u = u + nv.y * buf[4 * q + 1].y;
+          u = u + nv.z * buf[4 * q + 2].y;
+          u = u + nv.w * buf[4 * q + 3].y;
+          acc[r][1] = acc[r][1] + u;
+        }
+      } else {  // the K % 4 tail (last chunk only), one term at a time
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (m + i < len) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              acc[r][0] = acc[r][0] + Ns[r][m + i] * buf[4 * q + i].x;
+              acc[r][1] = acc[r][1] + Ns[r][m + i] * buf[4 * q + i].y;
+            }
+          }
+        }
+      }
+    }
+  };
+  float2 buf0[kTnStage], buf1[kTnStage];
+  load(buf0, 0);
+  for (int m0 = 0; m0 < len; m0 += 2 * kTnStage) {
+    if (m0 + kTnStage < len) load(buf1, m0 + kTnStage);
+    consume(buf0, m0);
+    if (m0 + kTnStage < len) {
+      if (m0 + 2 * kTnStage < len) load(buf0, m0 + 2 * kTnStage);
+      consume(buf1, m0 + kTnStage);
+    }
+  }
+  float* out = p.partials + static_cast<size_t>(blockIdx.z) * p.M * p.N;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    if (kWideA) {
+      out[w0 * p.N + r] = acc[r][0];
+      out[(w0 + 1) * p.N + r] = acc[r][1];
+    } else {
+      *reinterpret_cast<float2*>(out + static_cast<size_t>(r) * p.N + w0) =
+          make_float2(acc[r][0], acc[r][1]);
+    }
+  }
+}
+
+template <bool kWideA>
+bool LaunchTn(const Params& p, int R, dim3 grid, cudaStream_t s) {
+  switch (R) {
+    case 4: TnPartialKernel<kWideA, 4><<<grid, kTnThreads, 0, s>>>(p); return true;
+    case 8: TnPartialKernel<kWideA, 8><<<grid, kTnThreads, 0, s>>>(p); return true;
+    case 12: TnPartialKernel<kWideA, 12><<<grid, kTnThreads, 0, s>>>(p); return true;
+    case 16: TnPartialKernel<kWideA, 16><<<grid, kTnThreads, 0, s>>>(p); return true;
+    default: return false;
+  }
+}
+
+}  // namespace
+
+bool SkinnyTnPartials(const Params& p, size_t chunks, cudaStream_t s) {
+  if (p.k_chunk != static_cast<size_t>(kTnChunk) || !p.partials || chunks > 65535) return false;
+  const bool wide_a = p.N <= 16;
+  if (!wide_a && p.M > 16) return false;
+  const size_t W = wide_a ? p.M : p.N;
+  const int R = static_cast<int>(wide_a ? p.N : p.M);
+  if ((W & 1) != 0 || W < 64) return false;
+  const void* wide = wide_a ? static_cast<const void*>(p.A) : p.B;
+  if ((reinterpret_cast<uintptr_t>(wide) & 7) != 0 || (reinterpret_cast<uintptr_t>(p.partials) & 7) != 0)
+    return false;
+  const dim3 grid(static_cast<unsigned>((W / 2 + kTnThreads - 1) / kTnThreads), 1,
+                  static_cast<unsigned>(chunks));
+  return wide_a ? LaunchTn<true>(p, R, grid, s) : LaunchTn<false>(p, R, grid, s);
+}
+
+}  // namespace see::k::exact

@@ -109,6 +109,86 @@ __global__ void XEntRowsKernel(const float* __restrict__ logits, const int32_t* 
   }
 }
 
+// The same row softmax for wide rows (4096 <= C <= 32768, C % 4 == 0): one
+// 1024-thread block per row with the whole row in registers (eight 16-byte
+// vectors per thread), so the logits are read from HBM once and the
+// probabilities written once.  The next row is copied into shared memory
+// asynchronously (cp.async) while the current one is reduced, each thread
+// fetching exactly the chunks it will later read itself, so no barrier guards
+// the buffer.  Same expressions per element as RowSoftmaxBlock; the row sum is
+// folded as thread partials (ascending index), warp shuffles, then warps in order.
+constexpr int kWideThreads = 1024;
+constexpr int kWideVecs = 8;
+
+__device__ __forceinline__ void CpAsync16(void* smem, const void* gmem) {
+  const unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+
+__global__ void __launch_bounds__(kWideThreads, 1)
+XEntRowsWideKernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
+                   float* __restrict__ probs, double* __restrict__ row_loss, size_t N, size_t C,
+                   bool masked) {
+  extern __shared__ __align__(16) float4 row_smem[];
+  __shared__ float smem_f[32];
+  const int C4 = static_cast<int>(C / 4);
+  const int tid = threadIdx.x;
+  auto prefetch = [&](size_t n) {
+    const float4* lrow = reinterpret_cast<const float4*>(logits + n * C);
+#pragma unroll
+    for (int i = 0; i < kWideVecs; ++i) {
+      const int c4 = i * kWideThreads + tid;
+      if (c4 < C4) CpAsync16(&row_smem[c4], &lrow[c4]);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (blockIdx.x < N) prefetch(blockIdx.x);
+  for (size_t n = blockIdx.x; n < N; n += gridDim.x) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    float4 x[kWideVecs];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kWideVecs; ++i) {
+      const int c4 = i * kWideThreads + tid;
+      if (c4 < C4) {
+        x[i] = row_smem[c4];
+        mx = fmaxf(fmaxf(mx, x[i].x), fmaxf(x[i].y, fmaxf(x[i].z, x[i].w)));
+      }
+    }
+    if (n + gridDim.x < N) prefetch(n + gridDim.x);
+    mx = BlockReduce<float>(mx, -INFINITY, smem_f, WarpMax,
+                            [](float a, float b) { return fmaxf(a, b); });
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kWideVecs; ++i) {
+      if (i * kWideThreads + tid < C4) {
+        x[i].x = expf(x[i].x - mx); sum += x[i].x;
+        x[i].y = expf(x[i].y - mx); sum += x[i].y;
+        x[i].z = expf(x[i].z - mx); sum += x[i].z;
+        x[i].w = expf(x[i].w - mx); sum += x[i].w;
+      }
+    }
+    sum = BlockReduce<float>(sum, 0.0f, smem_f, WarpSumF, [](float a, float b) { return a + b; });
+    const float inv_sum = 1.0f / sum;
+    float4* prow = reinterpret_cast<float4*>(probs + n * C);
+#pragma unroll
+    for (int i = 0; i < kWideVecs; ++i) {
+      const int c4 = i * kWideThreads + tid;
+      if (c4 < C4)
+        prow[c4] = make_float4(x[i].x * inv_sum, x[i].y * inv_sum, x[i].z * inv_sum, x[i].w * inv_sum);
+    }
+    __syncthreads();  // the row's stores are visible to thread 0 below
+    if (tid == 0) {
+      const int32_t lab = labels[n];
+      double v;
+      if (masked && lab < 0) v = 0.0;
+      else if (lab < 0 || static_cast<size_t>(lab) >= C) v = NAN;
+      else v = NegLogSafe(probs[n * C + static_cast<size_t>(lab)]);
+      row_loss[n] = v;
+    }
+  }
+}
+
 // Folds row losses with the reference's chunk geometry: thread t owns chunk t
 // (rows [t*grain, ...)), summed sequentially; thread 0 then folds the chunk
 // partials in chunk order.  One block of kMaxChunks threads.
@@ -194,6 +274,45 @@ __global__ void XEntBwdKernel(const float* __restrict__ probs, const int32_t* __
       if (static_cast<size_t>(lab) == c) v -= scale;
     }
     dlogits[i] = v;
+  }
+}
+
+// The same for rows of whole 16-byte vectors: blockIdx.y walks rows, so the
+// label and the row index are per-block values, not a division per element.
+__global__ void XEntBwdRowsKernel(const float* __restrict__ probs, const int32_t* __restrict__ labels,
+                                  const float* __restrict__ seed, float* __restrict__ dlogits,
+                                  size_t N, size_t C, bool masked,
+                                  const unsigned long long* __restrict__ count) {
+  float scale;
+  if (masked) {
+    const unsigned long long T = *count;
+    scale = T ? *seed / static_cast<float>(T) : 0.0f;
+  } else {
+    scale = *seed / static_cast<float>(N);
+  }
+  const size_t C4 = C / 4;
+  for (size_t n = blockIdx.y; n < N; n += gridDim.y) {
+    const int32_t lab = labels[n];
+    const float4* prow = reinterpret_cast<const float4*>(probs + n * C);
+    float4* drow = reinterpret_cast<float4*>(dlogits + n * C);
+    const bool off = masked && lab < 0;
+    for (size_t c4 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; c4 < C4;
+         c4 += static_cast<size_t>(gridDim.x) * blockDim.x) {
+      float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (!off) {
+        const float4 pr = prow[c4];
+        v = make_float4(scale * pr.x, scale * pr.y, scale * pr.z, scale * pr.w);
+        if (lab >= 0 && static_cast<size_t>(lab) / 4 == c4) {
+          switch (lab & 3) {
+            case 0: v.x -= scale; break;
+            case 1: v.y -= scale; break;
+            case 2: v.z -= scale; break;
+            default: v.w -= scale; break;
+          }
+        }
+      }
+      drow[c4] = v;
+    }
   }
 }
 
@@ -291,9 +410,28 @@ void SoftmaxXEntFwd(bool masked, const float* logits, const int32_t* labels, flo
                     float* probs, size_t N, size_t C, double* row_scratch,
                     unsigned long long* count_scratch, cudaStream_t s) {
   if (N == 0) return;
-  const int threads = C >= 1024 ? 256 : (C >= 128 ? 128 : 32);
-  const unsigned blocks = static_cast<unsigned>(N < 148 * 16 ? N : 148 * 16);
-  XEntRowsKernel<<<blocks, threads, 0, s>>>(logits, labels, probs, row_scratch, N, C, masked);
+  const bool wide = C >= 4096 && C <= static_cast<size_t>(4 * kWideThreads * kWideVecs) &&
+                    (C & 3) == 0 && ((reinterpret_cast<uintptr_t>(logits) |
+                                      reinterpret_cast<uintptr_t>(probs)) & 15) == 0;
+  if (wide) {
+    // Raising a kernel's dynamic shared-memory limit is a per-device setting of
+    // the function, not an allocation; done on first use per device.
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      cudaFuncSetAttribute(XEntRowsWideKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           4 * kWideThreads * kWideVecs * static_cast<int>(sizeof(float)));
+      configured[dev] = true;
+    }
+    const unsigned blocks = static_cast<unsigned>(N < 148 * 4 ? N : 148 * 4);
+    XEntRowsWideKernel<<<blocks, kWideThreads, C * sizeof(float), s>>>(logits, labels, probs,
+                                                                       row_scratch, N, C, masked);
+  } else {
+    const int threads = C >= 1024 ? 256 : (C >= 128 ? 128 : 32);
+    const unsigned blocks = static_cast<unsigned>(N < 148 * 16 ? N : 148 * 16);
+    XEntRowsKernel<<<blocks, threads, 0, s>>>(logits, labels, probs, row_scratch, N, C, masked);
+  }
   const size_t grain = ChunkGrain(N, RowGrain(C, kGrainMath));
   XEntFoldKernel<<<1, kMaxChunks, 0, s>>>(row_scratch, labels, loss, N, grain, masked,
                                          count_scratch);
@@ -304,6 +442,14 @@ void SoftmaxXEntBwd(bool masked, const float* probs, const int32_t* labels, cons
                     cudaStream_t s) {
   if (N * C == 0) return;
   if (masked) CountTargetsKernel<<<1, 256, 0, s>>>(labels, N, count_scratch);
+  if (C >= 1024 && (C & 3) == 0 &&
+      ((reinterpret_cast<uintptr_t>(probs) | reinterpret_cast<uintptr_t>(dlogits)) & 15) == 0) {
+    const size_t per_row = (C / 4 + 255) / 256;
+    const dim3 grid(static_cast<unsigned>(per_row < 64 ? per_row : 64),
+                    static_cast<unsigned>(N < 65535 ? N : 65535));
+    XEntBwdRowsKernel<<<grid, 256, 0, s>>>(probs, labels, seed, dlogits, N, C, masked, count_scratch);
+    return;
+  }
   XEntBwdKernel<<<GridFor(N * C, 256, 148 * 8), 256, 0, s>>>(probs, labels, seed, dlogits, N, C,
                                                             masked, count_scratch);
 }

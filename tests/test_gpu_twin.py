@@ -120,7 +120,7 @@ def test_split_k_adapter_gradients_fixed_order():
     test/runtime/executor/kernels_test.cc:1803-1822) and identical run to run."""
     rng = np.random.default_rng(77)
     from tests.test_oracle_pinned import Arena
-    for (M, N, K) in [(16, 96, 4096), (200, 16, 3000), (8, 8, 1024)]:
+    for (M, N, K) in [(16, 96, 4096), (200, 16, 3000), (8, 8, 1024), (16, 64, 1027), (70, 12, 1030)]:
         a = Arena(rng)
         At = a.alloc(K * M, "normal"); Bm = a.alloc(K * N, "normal"); D = a.alloc(M * N, "normal")
         o1, o2 = a.alloc(M * N), a.alloc(M * N)

@@ -99,7 +99,9 @@ def seeded_programs():
 
     # GEMM family over odd shapes, every flag the opcodes admit.
     for (M, N, K) in [(1, 1, 1), (3, 5, 7), (37, 29, 131), (8, 64, 13), (65, 33, 66),
-                      (300, 16, 70), (12, 300, 70)]:
+                      (300, 16, 70), (12, 300, 70),
+                      # the adapter-product shapes: narrow outputs over a long K, rank-K expansions
+                      (300, 16, 68), (260, 8, 600), (257, 4, 64), (70, 64, 12), (100, 96, 16), (64, 128, 8)]:
         a = Arena(rng)
         A = a.alloc(M * K, "normal"); At = a.alloc(K * M, "normal")
         B = a.alloc(K * N, "normal"); Bt = a.alloc(N * K, "normal")
@@ -134,7 +136,7 @@ def seeded_programs():
         out.append((f"gemm_{M}x{N}x{K}", prog, *a.build()))
 
     # Elementwise, fused map, reductions, losses, optimizers, clips.
-    for n_rows, n_cols in [(1, 1), (5, 3), (33, 130), (300, 17)]:
+    for n_rows, n_cols in [(1, 1), (5, 3), (33, 130), (300, 17), (9, 4100), (3, 32000)]:
         a = Arena(rng)
         n = n_rows * n_cols
         x = a.alloc(n, "normal"); y = a.alloc(n, "normal"); z = a.alloc(n, "normal")
