@@ -37,30 +37,57 @@ constexpr uint32_t kSubTileBytes = 128 * 64 * 2;   // [128 rows][64 bf16], swizz
 constexpr uint32_t kPBytes = 2 * kSubTileBytes;    // P / dS tile: 128 x 128 bf16
 
 // ---- packing: f32 [B*S, H*d] -> bf16 [B*H][S][d] (rows) and [B*H][d][S] (cols) ----
-__global__ void PackHeadsKernel(const float* __restrict__ x, uint16_t* __restrict__ rows,
-                                uint16_t* __restrict__ cols, uint32_t B, uint32_t S, uint32_t H,
-                                uint32_t d) {
-  __shared__ uint16_t tile[32][33];
-  const uint32_t bh = blockIdx.z, b = bh / H, h = bh % H;
-  const uint32_t s0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
-  const size_t D = static_cast<size_t>(H) * d;
-  for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
-    const uint32_t s = s0 + i, c = c0 + threadIdx.x;
-    uint16_t v = 0;
-    if (s < S && c < d) {
-      const float f = x[(static_cast<size_t>(b) * S + s) * D + static_cast<size_t>(h) * d + c];
-      uint32_t u = __float_as_uint(f);
-      if ((u & 0x7FFFFFFFu) > 0x7F800000u) v = static_cast<uint16_t>((u >> 16) | 0x0040u);
-      else { u += 0x7FFFu + ((u >> 16) & 1u); v = static_cast<uint16_t>(u >> 16); }
-      if (rows) rows[(static_cast<size_t>(bh) * S + s) * d + c] = v;
+// One block packs 64 positions of one (sequence, head): 16-byte loads of the f32
+// rows, 8-byte stores of the bf16 row layout straight from registers, and the
+// column layout through a shared-memory transpose, again as 8-byte stores (four
+// positions of one feature).  Reads the source once for both layouts.
+__device__ __forceinline__ uint32_t Bf16Bits(float f) {   // round to nearest even; NaN stays NaN
+  uint32_t u = __float_as_uint(f);
+  if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (u >> 16) | 0x0040u;
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return u >> 16;
+}
+
+constexpr uint32_t kPackPos = 64;
+
+template <int D>
+__global__ void __launch_bounds__(256)
+PackHeadsKernel(const float* __restrict__ x, uint16_t* __restrict__ rows, uint16_t* __restrict__ cols,
+                uint32_t S, uint32_t H) {
+  __shared__ uint16_t tile[kPackPos][D + 2];   // odd word stride: conflict-free transpose reads
+  const uint32_t bh = blockIdx.y, b = bh / H, h = bh % H;
+  const uint32_t s0 = blockIdx.x * kPackPos;
+  const size_t HD = static_cast<size_t>(H) * D;
+  constexpr uint32_t kVecPerRow = D / 4;
+  for (uint32_t idx = threadIdx.x; idx < kPackPos * kVecPerRow; idx += 256) {
+    const uint32_t i = idx / kVecPerRow, c = (idx % kVecPerRow) * 4;
+    const uint32_t s = s0 + i;
+    uint32_t lo = 0, hi = 0;
+    if (s < S) {
+      const float4 f = *reinterpret_cast<const float4*>(
+          x + (static_cast<size_t>(b) * S + s) * HD + static_cast<size_t>(h) * D + c);
+      lo = Bf16Bits(f.x) | (Bf16Bits(f.y) << 16);
+      hi = Bf16Bits(f.z) | (Bf16Bits(f.w) << 16);
+      if (rows)
+        *reinterpret_cast<uint2*>(rows + (static_cast<size_t>(bh) * S + s) * D + c) = make_uint2(lo, hi);
     }
-    tile[i][threadIdx.x] = v;
+    *reinterpret_cast<uint32_t*>(&tile[i][c]) = lo;
+    *reinterpret_cast<uint32_t*>(&tile[i][c + 2]) = hi;
   }
   if (!cols) return;
   __syncthreads();
-  for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
-    const uint32_t c = c0 + i, s = s0 + threadIdx.x;
-    if (s < S && c < d) cols[(static_cast<size_t>(bh) * d + c) * S + s] = tile[threadIdx.x][i];
+  constexpr uint32_t kGroups = kPackPos / 4;   // groups of four positions
+  for (uint32_t idx = threadIdx.x; idx < D * kGroups; idx += 256) {
+    const uint32_t c = idx / kGroups, i = (idx % kGroups) * 4;
+    const uint32_t s = s0 + i;
+    if (s + 4 <= S) {
+      const uint32_t lo = tile[i][c] | (static_cast<uint32_t>(tile[i + 1][c]) << 16);
+      const uint32_t hi = tile[i + 2][c] | (static_cast<uint32_t>(tile[i + 3][c]) << 16);
+      *reinterpret_cast<uint2*>(cols + (static_cast<size_t>(bh) * D + c) * S + s) = make_uint2(lo, hi);
+    } else {
+      for (uint32_t t = 0; t < 4 && s + t < S; ++t)
+        cols[(static_cast<size_t>(bh) * D + c) * S + s + t] = tile[i + t][c];
+    }
   }
 }
 
@@ -584,8 +611,9 @@ static cudaError_t Configure(Kernel kernel, size_t smem) {
 
 void PackHeads(const float* x, uint16_t* rows, uint16_t* cols, uint32_t B, uint32_t S, uint32_t H,
                uint32_t d, cudaStream_t s) {
-  dim3 grid((d + 31) / 32, (S + 31) / 32, B * H), block(32, 8);
-  PackHeadsKernel<<<grid, block, 0, s>>>(x, rows, cols, B, S, H, d);
+  const dim3 grid((S + kPackPos - 1) / kPackPos, B * H);
+  if (d == 64) PackHeadsKernel<64><<<grid, 256, 0, s>>>(x, rows, cols, S, H);
+  else PackHeadsKernel<128><<<grid, 256, 0, s>>>(x, rows, cols, S, H);
 }
 
 cudaError_t AttnFwdUmma(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& vt,

@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstring>
 #include <map>
+#include <set>
 #include <tuple>
 #include <vector>
 
@@ -35,11 +36,17 @@ struct ActCopy {   // a bf16 copy of an arena activation [M, K]
 
 constexpr int kActSlots = 4;
 
-// Packed bf16 copies of attention operands: role (Q, K, V, dO) x layout (rows, cols).
-struct PackSlot {
-  uint16_t* buf = nullptr;
+// Packed bf16 copies of one attention operand (a Q, K, V or dO activation), in
+// both layouts the kernels read: rows [B*H][S][d] and cols [B*H][d][S].  Made
+// once, by one kernel, the first time any attention instruction of the range
+// reads the operand; the forward's copies serve the backward of the same step
+// unless an instruction overwrote the source in between.
+struct PackEntry {
+  uint16_t* rows = nullptr;
+  uint16_t* cols = nullptr;
   uint64_t src_off = ~0ull, elems = 0;
   bool valid = false;
+  uint64_t last_use = 0;
 };
 
 }  // namespace
@@ -51,8 +58,8 @@ struct Impl {
   ActCopy acts[kActSlots];
   uint64_t tick = 0;
   k::DeviceStatus* status = nullptr;  // the backend's device status block (not owned)
-  PackSlot pack[4][2];
-  uint64_t pack_capacity = 0;   // elements per slot
+  std::vector<PackEntry> packs;
+  uint64_t pack_capacity = 0;   // elements per layout of an entry
   cudaEvent_t prof_before = nullptr, prof_after = nullptr;
   bool prof_used = false;
 };
@@ -77,8 +84,7 @@ void Destroy(Context* ctx) {
   if (!ctx->impl) return;
   InvalidateAll(ctx);
   for (auto& a : ctx->impl->acts) cudaFree(a.buf);
-  for (auto& role : ctx->impl->pack)
-    for (auto& slot : role) cudaFree(slot.buf);
+  for (auto& e : ctx->impl->packs) { cudaFree(e.rows); cudaFree(e.cols); }
   delete ctx->impl;
   ctx->impl = nullptr;
 }
@@ -88,8 +94,7 @@ void InvalidateAll(Context* ctx) {
   for (auto& [key, buf] : ctx->impl->weights) cudaFree(buf);
   ctx->impl->weights.clear();
   for (auto& a : ctx->impl->acts) a.valid = false;
-  for (auto& role : ctx->impl->pack)
-    for (auto& slot : role) slot.valid = false;
+  for (auto& e : ctx->impl->packs) e.valid = false;
 }
 
 void InvalidateRange(Context* ctx, uint64_t off, uint64_t bytes) {
@@ -99,10 +104,8 @@ void InvalidateRange(Context* ctx, uint64_t off, uint64_t bytes) {
     const uint64_t a_bytes = a.M * a.K * 4;
     if (off < a.a_off + a_bytes && a.a_off < off + bytes) a.valid = false;
   }
-  for (auto& role : ctx->impl->pack)
-    for (auto& slot : role)
-      if (slot.valid && off < slot.src_off + slot.elems * 4 && slot.src_off < off + bytes)
-        slot.valid = false;
+  for (auto& e : ctx->impl->packs)
+    if (e.valid && off < e.src_off + e.elems * 4 && e.src_off < off + bytes) e.valid = false;
 }
 
 // Sizes every activation-copy slot for the largest relaxed GEMM of the range
@@ -122,28 +125,53 @@ void PlanRange(Context* ctx, const Instruction* program, size_t begin, size_t en
       default: break;
     }
   }
+  // Attention operands: one pack entry per distinct source of the range, within
+  // a budget of one eighth of the device's memory (least recently used entries
+  // are recycled beyond that), never fewer than the four one instruction needs.
   uint64_t attn = 0;
+  std::set<uint64_t> sources;
   for (size_t i = begin; i < end; ++i) {
     const Instruction& ins = program[i];
     if (!(ins.flags & kFlagRelaxed)) continue;
-    if (ins.opcode == kAttnFwdTiled)
+    if (ins.opcode == kAttnFwdTiled) {
       attn = std::max(attn, Hi32(ins.out[1]) * Lo32(ins.out[1]) * Hi32(ins.out[2]) * Lo32(ins.out[2]));
+      for (int j = 0; j < 3; ++j) sources.insert(ins.in[j]);
+    }
     if (ins.opcode == kAttnDQTiled || ins.opcode == kAttnDKTiled || ins.opcode == kAttnDVTiled) {
       const AttnGeom g = UnpackAttnGeom(ins.out[2]);
       attn = std::max(attn, g.B * g.S * g.H * g.d);
+      for (int j = 0; j < 4; ++j) sources.insert(ins.in[j]);
     }
   }
-  if (attn > impl->pack_capacity) {
-    cudaDeviceSynchronize();
-    for (auto& role : impl->pack)
-      for (auto& slot : role) {
-        cudaFree(slot.buf);
-        slot.buf = nullptr;
-        slot.valid = false;
-        void* p = nullptr;
-        if (cudaMalloc(&p, attn * 2) == cudaSuccess) slot.buf = static_cast<uint16_t*>(p);
+  if (attn > 0) {
+    size_t free_b = 0, total_b = 0;
+    cudaMemGetInfo(&free_b, &total_b);
+    const uint64_t per_entry = attn * 4;   // two bf16 layouts
+    const uint64_t by_budget = std::max<uint64_t>(4, (total_b / 8) / per_entry);
+    const size_t want = static_cast<size_t>(
+        std::min<uint64_t>(std::max<uint64_t>(4, sources.size()), by_budget));
+    if (attn > impl->pack_capacity || want > impl->packs.size()) {
+      cudaDeviceSynchronize();
+      const uint64_t cap = std::max(attn, impl->pack_capacity);
+      if (attn > impl->pack_capacity) {
+        for (auto& e : impl->packs) { cudaFree(e.rows); cudaFree(e.cols); }
+        impl->packs.clear();
       }
-    impl->pack_capacity = attn;
+      while (impl->packs.size() < want) {
+        PackEntry e;
+        void* pr = nullptr;
+        void* pc = nullptr;
+        if (cudaMalloc(&pr, cap * 2) != cudaSuccess || cudaMalloc(&pc, cap * 2) != cudaSuccess) {
+          cudaFree(pr);
+          cudaGetLastError();
+          break;
+        }
+        e.rows = static_cast<uint16_t*>(pr);
+        e.cols = static_cast<uint16_t*>(pc);
+        impl->packs.push_back(e);
+      }
+      impl->pack_capacity = cap;
+    }
   }
   if (need == 0) return;
   bool drained = false;
@@ -290,40 +318,48 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
     return {};
   const uint64_t elems = op.B * op.S * op.H * op.d;
   if (elems > impl->pack_capacity) return {};   // executed outside a planned range
-  for (auto& role : impl->pack)
-    for (auto& slot : role)
-      if (!slot.buf) return "tensor-core attention: packed-operand allocation failed";
+  if (impl->packs.size() < 4) return "tensor-core attention: packed-operand allocation failed";
   const bool fwd = opcode == kAttnFwdTiled, dq = opcode == kAttnDQTiled,
              dk = opcode == kAttnDKTiled, dv = opcode == kAttnDVTiled;
   if (!fwd && !dq && !dk && !dv) return {};
   enum { Q = 0, K = 1, V = 2, DO = 3 };
   const float* src[4] = {op.q, op.k, op.v, op.dout};
   const uint64_t off[4] = {op.q_off, op.k_off, op.v_off, op.dout_off};
-  bool rows[4] = {false, false, false, false}, cols[4] = {false, false, false, false};
-  if (fwd) { rows[Q] = rows[K] = true; cols[V] = true; }
-  if (dq) { rows[Q] = rows[DO] = rows[K] = rows[V] = true; cols[K] = true; }
-  if (dk) { rows[K] = rows[V] = rows[Q] = rows[DO] = true; cols[Q] = true; }
-  if (dv) { rows[K] = rows[Q] = true; cols[DO] = true; }
+  bool used[4] = {true, true, true, !fwd};
+  if (dv) used[V] = false;
+  for (int r = 0; r < 4; ++r)
+    if (used[r] && (reinterpret_cast<uintptr_t>(src[r]) & 15)) return {};
+  const uint64_t now = ++impl->tick;
+  PackEntry* ent[4] = {nullptr, nullptr, nullptr, nullptr};
   for (int r = 0; r < 4; ++r) {
-    PackSlot& sr = impl->pack[r][0];
-    PackSlot& sc = impl->pack[r][1];
-    const bool do_rows = rows[r] && !(sr.valid && sr.src_off == off[r] && sr.elems == elems);
-    const bool do_cols = cols[r] && !(sc.valid && sc.src_off == off[r] && sc.elems == elems);
-    if (!do_rows && !do_cols) continue;
-    k::PackHeads(src[r], do_rows ? sr.buf : nullptr, do_cols ? sc.buf : nullptr,
-                 static_cast<uint32_t>(op.B), static_cast<uint32_t>(op.S),
-                 static_cast<uint32_t>(op.H), static_cast<uint32_t>(op.d), stream);
+    if (!used[r]) continue;
+    for (auto& e : impl->packs)
+      if (e.valid && e.src_off == off[r] && e.elems == elems) { ent[r] = &e; break; }
+    if (ent[r]) { ent[r]->last_use = now; continue; }
+    PackEntry* victim = nullptr;
+    for (auto& e : impl->packs) {
+      if (e.last_use == now) continue;   // taken by this instruction
+      if (!e.valid) { victim = &e; break; }
+      if (!victim || e.last_use < victim->last_use) victim = &e;
+    }
+    if (!victim) return "tensor-core attention: no pack entry free";
+    k::PackHeads(src[r], victim->rows, victim->cols, static_cast<uint32_t>(op.B),
+                 static_cast<uint32_t>(op.S), static_cast<uint32_t>(op.H),
+                 static_cast<uint32_t>(op.d), stream);
     ++*launches;
-    if (do_rows) { sr.valid = true; sr.src_off = off[r]; sr.elems = elems; }
-    if (do_cols) { sc.valid = true; sc.src_off = off[r]; sc.elems = elems; }
+    victim->valid = true;
+    victim->src_off = off[r];
+    victim->elems = elems;
+    victim->last_use = now;
+    ent[r] = victim;
   }
   const uint64_t BH = op.B * op.H;
   CUtensorMap mr[4], mc[4];
   for (int r = 0; r < 4; ++r) {
-    if (rows[r] && !EncodeHeads(impl, &mr[r], impl->pack[r][0].buf, op.d, op.S, BH, 128))
+    if (!used[r]) continue;
+    if (!EncodeHeads(impl, &mr[r], ent[r]->rows, op.d, op.S, BH, 128))
       return "tensor-core attention: cuTensorMapEncodeTiled refused a row layout";
-    if (cols[r] && !EncodeHeads(impl, &mc[r], impl->pack[r][1].buf, op.S, op.d, BH,
-                                static_cast<uint32_t>(op.d)))
+    if (!EncodeHeads(impl, &mc[r], ent[r]->cols, op.S, op.d, BH, static_cast<uint32_t>(op.d)))
       return "tensor-core attention: cuTensorMapEncodeTiled refused a column layout";
   }
   k::AttnUmmaArgs a{};
