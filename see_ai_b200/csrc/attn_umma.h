@@ -26,17 +26,18 @@ struct AttnUmmaArgs {
 void PackHeads(const float* x, uint16_t* rows, uint16_t* cols, uint32_t B, uint32_t S, uint32_t H,
                uint32_t d, cudaStream_t s);
 
-// Row-layout maps: dims {d, S, B*H}, box {64, 128, 1}; column-layout maps:
-// dims {S, d, B*H}, box {64, d, 1}; bf16, 128-byte swizzle.  d is 64 or 128.
-cudaError_t AttnFwdUmma(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& vt,
+// Row-layout maps: dims {d, S, B*H}, box {64, 128, 1} (a CTA's own 128 rows) or
+// {64, 64, 1} (`_half`: the 64 positions of one step); column-layout maps: dims
+// {S, d, B*H}, box {64, d, 1}; bf16, 128-byte swizzle.  d is 64 or 128.
+cudaError_t AttnFwdUmma(const CUtensorMap& q, const CUtensorMap& k_half, const CUtensorMap& vt,
                         const AttnUmmaArgs& a, cudaStream_t s);
-cudaError_t AttnDQUmma(const CUtensorMap& q, const CUtensorMap& dout, const CUtensorMap& k,
-                       const CUtensorMap& v, const CUtensorMap& kt, const AttnUmmaArgs& a,
+cudaError_t AttnDQUmma(const CUtensorMap& q, const CUtensorMap& dout, const CUtensorMap& k_half,
+                       const CUtensorMap& v_half, const CUtensorMap& kt, const AttnUmmaArgs& a,
                        cudaStream_t s);
-// t = dO columns for dV, Q columns for dK.
-cudaError_t AttnDKVUmma(bool want_dk, const CUtensorMap& k, const CUtensorMap& v, const CUtensorMap& q,
-                        const CUtensorMap& dout, const CUtensorMap& t, const AttnUmmaArgs& a,
-                        cudaStream_t s);
+// t = dO columns for dV, Q columns for dK.  dV ignores v and dout_half.
+cudaError_t AttnDKVUmma(bool want_dk, const CUtensorMap& k, const CUtensorMap& v,
+                        const CUtensorMap& q_half, const CUtensorMap& dout_half, const CUtensorMap& t,
+                        const AttnUmmaArgs& a, cudaStream_t s);
 
 }  // namespace see::k
 

@@ -12,14 +12,16 @@
 // accumulator in tensor memory, and the softmax / softmax-backward arithmetic
 // runs in f32 registers on values read with tcgen05.ld; P and dS go back to
 // shared memory as bf16 for the second product.  Statistics are exact f32
-// reductions of the bf16 products: two passes over the key tiles (first the
-// row statistics, then the normalised probabilities), so no accumulator is
-// ever rescaled.  128 threads per CTA, one query row (or key row) per thread;
-// thread 0 issues TMA and MMA.  Every mbarrier wait is bounded; a wait that
-// runs out raises DeviceStatus::wait_timeout and the CTA stores nothing.
+// reductions of the bf16 products: two walks over the keys (first the row
+// statistics, then the products), so no accumulator is ever rescaled.
 //
-// Tensor-pipe bound by FLOP count; this first version serialises load, MMA
-// and softmax inside a CTA and relies on co-resident CTAs for overlap.
+// A CTA is 128 threads, one query row (or key row) per thread, and takes the
+// other axis 64 positions per step, which keeps its footprint at 48-72 KB of
+// shared memory and 128-256 columns of tensor memory: two to four CTAs share an
+// SM and fill each other's load, MMA and exp latencies.  Thread 0 issues TMA
+// and MMA; one tcgen05.commit per step covers the step's first product(s) and
+// the previous step's second product.  Every mbarrier wait is bounded; a wait
+// that runs out raises DeviceStatus::wait_timeout and the CTA stores nothing.
 #include <cuda.h>
 
 #include "attn_umma.h"
@@ -92,66 +94,68 @@ PackHeadsKernel(const float* __restrict__ x, uint16_t* __restrict__ rows, uint16
 }
 
 struct Ctl {
-  uint64_t load[2];
-  uint64_t mma;
+  uint64_t bar_a;   // operands of the step's first product(s) have landed
+  uint64_t bar_b;   // operand of the step's second product has landed
+  uint64_t mma;     // the tensor core finished everything issued so far
   uint32_t tmem_base;
   uint32_t pad;
 };
 
-// Loads a [128 rows][D] tile of a row-layout tensor ({d, S, BH} map) as D/64 sub-tiles.
-template <int D>
-__device__ __forceinline__ void LoadRowTile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar,
-                                            uint32_t row0, uint32_t bh) {
-#pragma unroll
-  for (int kb = 0; kb < D / 64; ++kb)
-    TmaLoad3D(dst + kb * kSubTileBytes, map, bar, kb * 64, static_cast<int32_t>(row0),
-              static_cast<int32_t>(bh));
-}
-// Loads a [D rows][128 positions] tile of a column-layout tensor ({S, d, BH} map) as two
-// sub-tiles of [D][64].
-template <int D>
-__device__ __forceinline__ void LoadColTile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar,
-                                            uint32_t pos0, uint32_t bh) {
-#pragma unroll
-  for (int kb = 0; kb < 2; ++kb)
-    TmaLoad3D(dst + kb * (D * 128), map, bar, static_cast<int32_t>(pos0 + kb * 64), 0,
-              static_cast<int32_t>(bh));
+constexpr uint32_t kHalf = 64;                    // keys (or queries) per step
+constexpr uint32_t kHalfTileBytes = 128 * 64 * 2; // P / dS step tile: [128 rows][64] bf16, swizzled
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ float Exp2Approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
-// acc[128 x 128] (+)= A[128 rows][D] . B[128 rows][D]^T, both row tiles in shared memory.
-template <int D>
+// Loads [R rows][D] of a row-layout tensor ({d, S, BH} map with box {64, R}) as D/64
+// sub-tiles of R * 128 bytes.
+template <int D, int R>
+__device__ __forceinline__ void LoadRows(uint8_t* dst, const CUtensorMap* map, uint64_t* bar,
+                                         uint32_t row0, uint32_t bh) {
+#pragma unroll
+  for (int kb = 0; kb < D / 64; ++kb)
+    TmaLoad3D(dst + kb * (R * 128), map, bar, kb * 64, static_cast<int32_t>(row0),
+              static_cast<int32_t>(bh));
+}
+// Loads [D rows][64 positions] of a column-layout tensor ({S, d, BH} map with box {64, D}).
+__device__ __forceinline__ void LoadColsHalf(uint8_t* dst, const CUtensorMap* map, uint64_t* bar,
+                                             uint32_t pos0, uint32_t bh) {
+  TmaLoad3D(dst, map, bar, static_cast<int32_t>(pos0), 0, static_cast<int32_t>(bh));
+}
+
+// acc[128 x NB] = A[128 rows][D] . B[NB rows][D]^T, both row tiles in shared memory.
+template <int D, int NB>
 __device__ __forceinline__ void MmaRowRow(uint32_t tmem, const uint8_t* a, const uint8_t* b) {
-  const uint32_t idesc = MakeInstrDesc(128, 128);
+  const uint32_t idesc = MakeInstrDesc(128, NB);
 #pragma unroll
   for (int kb = 0; kb < D / 64; ++kb) {
-    const uint64_t da = MakeSmemDesc(SmemAddr(a + kb * kSubTileBytes));
-    const uint64_t db = MakeSmemDesc(SmemAddr(b + kb * kSubTileBytes));
+    const uint64_t da = MakeSmemDesc(SmemAddr(a + kb * (128 * 128)));
+    const uint64_t db = MakeSmemDesc(SmemAddr(b + kb * (NB * 128)));
 #pragma unroll
     for (int k = 0; k < 4; ++k) UmmaBf16(tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
   }
 }
-// acc[128 x D] (+)= P[128 rows][128] . T[D rows][128]^T  (P: two [128][64] sub-tiles;
-// T: two [D][64] sub-tiles).  `accumulate` = 0 starts a fresh accumulator.
+// acc[128 x D] (+)= P[128 rows][64] . T[D rows][64]^T.  `accumulate` = 0 starts afresh.
 template <int D>
 __device__ __forceinline__ void MmaPT(uint32_t tmem, const uint8_t* p, const uint8_t* t,
                                       uint32_t accumulate) {
   const uint32_t idesc = MakeInstrDesc(128, D);
+  const uint64_t da = MakeSmemDesc(SmemAddr(p));
+  const uint64_t db = MakeSmemDesc(SmemAddr(t));
 #pragma unroll
-  for (int kb = 0; kb < 2; ++kb) {
-    const uint64_t da = MakeSmemDesc(SmemAddr(p + kb * kSubTileBytes));
-    const uint64_t db = MakeSmemDesc(SmemAddr(t + kb * (D * 128)));
-#pragma unroll
-    for (int k = 0; k < 4; ++k)
-      UmmaBf16(tmem, da + 2 * k, db + 2 * k, idesc, (accumulate | kb | k) != 0 ? 1u : 0u);
-  }
+  for (int k = 0; k < 4; ++k)
+    UmmaBf16(tmem, da + 2 * k, db + 2 * k, idesc, (accumulate | k) != 0 ? 1u : 0u);
 }
 
-// Writes 32 consecutive values of this thread's row (columns c0 .. c0+31 of a 128-wide
-// tile) into the swizzled bf16 tile P.
+// Writes 32 consecutive values of this thread's row (columns c0 .. c0+31 of the 64-wide
+// step tile) into the swizzled bf16 tile.
 __device__ __forceinline__ void StoreRowChunk(uint8_t* p_tile, uint32_t row, uint32_t c0,
                                               const float (&v)[32]) {
-  uint8_t* sub = p_tile + (c0 >> 6) * kSubTileBytes;
-  const uint32_t chunk0 = (c0 & 63) >> 3;   // first 16-byte chunk (8 bf16) of the four
+  const uint32_t chunk0 = c0 >> 3;   // first 16-byte chunk (8 bf16) of the four
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
     uint4 w;
@@ -159,7 +163,7 @@ __device__ __forceinline__ void StoreRowChunk(uint8_t* p_tile, uint32_t row, uin
     w.y = PackBf16x2(v[8 * q + 2], v[8 * q + 3]);
     w.z = PackBf16x2(v[8 * q + 4], v[8 * q + 5]);
     w.w = PackBf16x2(v[8 * q + 6], v[8 * q + 7]);
-    *reinterpret_cast<uint4*>(sub + Sw128Offset(row, chunk0 + q)) = w;
+    *reinterpret_cast<uint4*>(p_tile + Sw128Offset(row, chunk0 + q)) = w;
   }
 }
 
@@ -167,7 +171,41 @@ __device__ __forceinline__ uint8_t* AlignSmem(uint8_t* raw) {
   return raw + ((1024u - (SmemAddr(raw) & 1023u)) & 1023u);
 }
 
+// Stores this thread's output row (D accumulator columns starting at t_out) times `scale`.
+template <int D>
+__device__ __forceinline__ void StoreOutRow(uint32_t t_out, float* o, bool live, float scale) {
+#pragma unroll 1
+  for (uint32_t c0 = 0; c0 < D; c0 += 32) {
+    uint32_t r[32];
+    TmemLoad32(t_out + c0, r);   // warp-collective: every thread loads, live rows store
+    TmemWaitLd();
+    if (live) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(o + c0 + j) =
+            make_float4(__uint_as_float(r[j]) * scale, __uint_as_float(r[j + 1]) * scale,
+                        __uint_as_float(r[j + 2]) * scale, __uint_as_float(r[j + 3]) * scale);
+    }
+  }
+}
+
+// After a wait ran out: give copies that may still be in flight towards this CTA's
+// shared memory a bounded time to land before the CTA retires.
+__device__ __forceinline__ void DrainDelay() {
+  for (int i = 0; i < 64; ++i) __nanosleep(2000);
+}
+
+constexpr uint32_t TmemColsFor(uint32_t need) { return need <= 128 ? 128 : (need <= 256 ? 256 : 512); }
+
 // ---- forward -------------------------------------------------------------------------
+// A CTA owns 128 query rows of one (sequence, head) and walks the keys 64 at a
+// time, twice: the first walk finds each row's score maximum, the second forms
+// p = exp(s - max), sums it, and accumulates the unnormalised O = p V on the
+// tensor core; O is divided by the sum on the way out.  Per step: S = Q K_h^T
+// (128 x 64, tensor memory columns 0..63), read back one row per thread, P
+// written to shared memory as bf16, O += P V_h (columns 64..64+D).  Small
+// footprint on purpose (48 KB of shared memory and 128 tensor-memory columns
+// for d = 64): four CTAs share an SM and cover each other's waits.
 template <int D>
 __global__ void __launch_bounds__(128)
 AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -175,21 +213,23 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw);             // barriers first, tiles 1024-aligned after
   uint8_t* smem = AlignSmem(smem_raw + sizeof(Ctl));
-  constexpr uint32_t kRowTile = 128 * D * 2, kColTile = D * 256;
+  constexpr uint32_t kQBytes = 128 * D * 2, kKBytes = 64 * D * 2, kVBytes = D * 128;
   uint8_t* q_s = smem;
-  uint8_t* stage_s = q_s + kRowTile;                       // 2 x (K row tile + Vt col tile)
-  uint8_t* p_s = stage_s + 2 * (kRowTile + kColTile);
-  constexpr uint32_t kTmemCols = 256;                      // S: 0..127, O: 128..128+D-1
+  uint8_t* k_s = q_s + kQBytes;
+  uint8_t* v_s = k_s + kKBytes;
+  uint8_t* p_s = v_s + kVBytes;
+  constexpr uint32_t kTmemCols = TmemColsFor(64 + D);
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5;
   const uint32_t n_qt = (a.S + kTile - 1) / kTile;
   const uint32_t it = n_qt - 1 - blockIdx.x;               // heaviest tiles first
   const uint32_t bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
-  const uint32_t n_kt = it + 1;
-  const uint32_t total = 2 * n_kt;
+  const uint32_t all_h = (a.S + kHalf - 1) / kHalf;
+  const uint32_t n_h = 2 * (it + 1) < all_h ? 2 * (it + 1) : all_h;
+  const uint32_t total = 2 * n_h;
 
   if (tid == 0) {
-    MbarInit(&ctl->load[0], 1); MbarInit(&ctl->load[1], 1); MbarInit(&ctl->mma, 1);
+    MbarInit(&ctl->bar_a, 1); MbarInit(&ctl->bar_b, 1); MbarInit(&ctl->mma, 1);
     MbarInitFence();
   }
   if (warp == 0) TmemAlloc(&ctl->tmem_base, kTmemCols);
@@ -198,68 +238,59 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   TcFenceAfter();
   const uint32_t tmem = ctl->tmem_base;
   const uint32_t t_s = tmem + ((warp * 32) << 16);
-  const uint32_t t_o = t_s + 128;
+  const uint32_t t_o = t_s + 64;
 
-  auto issue_load = [&](uint32_t ld) {
-    const uint32_t jt = ld % n_kt, st = ld & 1;
-    const bool second = ld >= n_kt;
-    uint8_t* k_dst = stage_s + st * (kRowTile + kColTile);
-    uint32_t bytes = kRowTile + (second ? kColTile : 0) + (ld == 0 ? kRowTile : 0);
-    MbarExpectTx(&ctl->load[st], bytes);
-    if (ld == 0) LoadRowTile<D>(q_s, &map_q, &ctl->load[st], it * kTile, bh);
-    LoadRowTile<D>(k_dst, &map_k, &ctl->load[st], jt * kTile, bh);
-    if (second) LoadColTile<D>(k_dst + kRowTile, &map_vt, &ctl->load[st], jt * kTile, bh);
+  auto issue_a = [&](uint32_t t) {
+    MbarExpectTx(&ctl->bar_a, kKBytes + (t == 0 ? kQBytes : 0));
+    if (t == 0) LoadRows<D, 128>(q_s, &map_q, &ctl->bar_a, it * kTile, bh);
+    LoadRows<D, 64>(k_s, &map_k, &ctl->bar_a, (t % n_h) * kHalf, bh);
+  };
+  auto issue_b = [&](uint32_t jh) {
+    MbarExpectTx(&ctl->bar_b, kVBytes);
+    LoadColsHalf(v_s, &map_vt, &ctl->bar_b, jh * kHalf, bh);
   };
 
   const uint32_t row = it * kTile + tid;                   // this thread's query row
-  float m = -INFINITY, l = 0.0f, inv_l = 0.0f;
-  uint32_t mma_phase = 0;
+  const float c1 = a.inv_sqrt_d * kLog2e;
+  float raw_max = -INFINITY, m = 0.0f, m2 = 0.0f, l = 0.0f;
+  uint32_t b_phase = 0;
   int failed = 0;
-  if (tid == 0) issue_load(0);
+  if (tid == 0) issue_a(0);
 
-  for (uint32_t ld = 0; ld < total; ++ld) {
-    const uint32_t jt = ld % n_kt, st = ld & 1;
-    const bool second = ld >= n_kt;
-    uint8_t* k_s = stage_s + st * (kRowTile + kColTile);
-    if (tid == 0 && ld + 1 < total) issue_load(ld + 1);
-    if (!MbarWait(&ctl->load[st], (ld >> 1) & 1)) failed = 1;
-    if (tid == 0) {
+  for (uint32_t t = 0; t < total; ++t) {
+    const uint32_t jh = t % n_h;
+    const bool second = t >= n_h;
+    if (tid == 0) {   // only the issuing thread needs the operands' arrival
+      if (!MbarWait(&ctl->bar_a, t & 1)) failed = 1;
       TcFenceAfter();
-      MmaRowRow<D>(tmem, q_s, k_s);
+      if (!failed) MmaRowRow<D, 64>(tmem, q_s, k_s);
       UmmaCommit(&ctl->mma);
     }
-    if (!MbarWait(&ctl->mma, mma_phase)) failed = 1;
-    mma_phase ^= 1;
+    // This commit also covers the previous step's O += P V, so p_s, v_s and k_s
+    // are all free again once it arrives.
+    if (!MbarWait(&ctl->mma, t & 1)) failed = 1;
     TcFenceAfter();
-    if (ld == n_kt) inv_l = 1.0f / l;                      // statistics complete
-    const uint32_t key0 = jt * kTile;
+    if (tid == 0 && !failed) {
+      if (t + 1 < total) issue_a(t + 1);
+      if (second) issue_b(jh);
+    }
+    if (t == n_h) { m = raw_max * a.inv_sqrt_d; m2 = m * kLog2e; }
+    const uint32_t key0 = jh * kHalf;
 #pragma unroll 1
-    for (uint32_t c0 = 0; c0 < kTile; c0 += 32) {
+    for (uint32_t c0 = 0; c0 < kHalf; c0 += 32) {
       uint32_t r[32];
       TmemLoad32(t_s + c0, r);
       TmemWaitLd();
-      float v[32];
       if (!second) {
-        float tile_max = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float s = __uint_as_float(r[j]) * a.inv_sqrt_d;
-          v[j] = (key0 + c0 + j <= row) ? s : -INFINITY;
-          tile_max = fmaxf(tile_max, v[j]);
-        }
-        const float m_new = fmaxf(m, tile_max);
-        if (m_new > -INFINITY) {
-          float sum = 0.0f;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) sum += __expf(v[j] - m_new);
-          l = l * __expf(m - m_new) + sum;
-          m = m_new;
-        }
+        for (int j = 0; j < 32; ++j)
+          if (key0 + c0 + j <= row) raw_max = fmaxf(raw_max, __uint_as_float(r[j]));
       } else {
+        float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          const float s = __uint_as_float(r[j]) * a.inv_sqrt_d;
-          v[j] = (key0 + c0 + j <= row) ? __expf(s - m) * inv_l : 0.0f;
+          v[j] = (key0 + c0 + j <= row) ? Exp2Approx(fmaf(__uint_as_float(r[j]), c1, -m2)) : 0.0f;
+          l += v[j];
         }
         StoreRowChunk(p_s, tid, c0, v);
       }
@@ -267,39 +298,26 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     if (second) FenceProxyAsync();
     TcFenceBefore();
     if (__syncthreads_or(failed)) { failed = 1; break; }
-    if (second) {
-      if (tid == 0) {
-        TcFenceAfter();
-        MmaPT<D>(tmem + 128, p_s, k_s + kRowTile, jt != 0);
-        UmmaCommit(&ctl->mma);
-      }
-      if (!MbarWait(&ctl->mma, mma_phase)) failed = 1;
-      mma_phase ^= 1;
+    if (second && tid == 0) {
+      if (!MbarWait(&ctl->bar_b, b_phase)) failed = 1;
+      b_phase ^= 1;
       TcFenceAfter();
+      if (!failed) MmaPT<D>(tmem + 64, p_s, v_s, jh != 0);
     }
   }
+  if (tid == 0) UmmaCommit(&ctl->mma);
+  if (!failed && !MbarWait(&ctl->mma, total & 1)) failed = 1;
+  TcFenceAfter();
   failed = __syncthreads_or(failed);
   if (failed) {
     if (tid == 0) a.status->wait_timeout = 1;
+    DrainDelay();
   } else {
-    // tcgen05.ld is warp-collective: every thread loads, only rows inside the
-    // sequence store.
     const bool live = row < a.S;
     const size_t HD = static_cast<size_t>(a.H) * D;
     float* o = a.out + (static_cast<size_t>(b) * a.S + (live ? row : 0)) * HD + static_cast<size_t>(h) * D;
-#pragma unroll 1
-    for (uint32_t c0 = 0; c0 < D; c0 += 32) {
-      uint32_t r[32];
-      TmemLoad32(t_o + c0, r);
-      TmemWaitLd();
-      if (live) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(o + c0 + j) =
-              make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                          __uint_as_float(r[j + 3]));
-      }
-    }
+    const float inv_l = 1.0f / l;
+    StoreOutRow<D>(t_o, o, live, inv_l);
     if (live) {
       float* st = a.stats + (static_cast<size_t>(bh) * a.S + row) * kAttnStatsWidth;
       *reinterpret_cast<float4*>(st) = make_float4(m, inv_l, 0.0f, 0.0f);
@@ -314,10 +332,11 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 }
 
 // ---- dQ (and delta) --------------------------------------------------------------------
-// Per query tile: pass 1 accumulates delta_i = sum_j P_ij dP_ij, pass 2 forms
-// dS = P (dP - delta) / sqrt(d) and accumulates dQ = dS K.  NS = shared-memory
-// stages for the per-key-tile operands (K rows, V rows, K columns).
-template <int D, int NS>
+// Per 128 query rows, the keys 64 at a time, twice: the first walk accumulates
+// delta_i = sum_j P_ij dP_ij, the second forms dS = P (dP - delta) / sqrt(d) and
+// accumulates dQ = dS K.  Per step S = Q K_h^T (columns 0..63) and dP = dO V_h^T
+// (64..127); dQ lives in columns 128..128+D.
+template <int D>
 __global__ void __launch_bounds__(128)
 AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                  const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -325,22 +344,25 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw);
   uint8_t* smem = AlignSmem(smem_raw + sizeof(Ctl));
-  constexpr uint32_t kRowTile = 128 * D * 2, kColTile = D * 256;
-  constexpr uint32_t kStage = 2 * kRowTile + kColTile;
+  constexpr uint32_t kFull = 128 * D * 2, kHalfRows = 64 * D * 2, kCols = D * 128;
   uint8_t* q_s = smem;
-  uint8_t* do_s = q_s + kRowTile;
-  uint8_t* stage_s = do_s + kRowTile;
-  uint8_t* p_s = stage_s + NS * kStage;
-  constexpr uint32_t kTmemCols = 512;                      // S 0..127, dP 128..255, dQ 256..
+  uint8_t* do_s = q_s + kFull;
+  uint8_t* k_s = do_s + kFull;
+  uint8_t* v_s = k_s + kHalfRows;
+  uint8_t* kt_s = v_s + kHalfRows;
+  uint8_t* p_s = kt_s + kCols;
+  constexpr uint32_t kTmemCols = TmemColsFor(128 + D);
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5;
   const uint32_t n_qt = (a.S + kTile - 1) / kTile;
   const uint32_t it = n_qt - 1 - blockIdx.x;
   const uint32_t bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
-  const uint32_t n_kt = it + 1, total = 2 * n_kt;
+  const uint32_t all_h = (a.S + kHalf - 1) / kHalf;
+  const uint32_t n_h = 2 * (it + 1) < all_h ? 2 * (it + 1) : all_h;
+  const uint32_t total = 2 * n_h;
 
   if (tid == 0) {
-    MbarInit(&ctl->load[0], 1); MbarInit(&ctl->load[1], 1); MbarInit(&ctl->mma, 1);
+    MbarInit(&ctl->bar_a, 1); MbarInit(&ctl->bar_b, 1); MbarInit(&ctl->mma, 1);
     MbarInitFence();
   }
   if (warp == 0) TmemAlloc(&ctl->tmem_base, kTmemCols);
@@ -350,98 +372,96 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   const uint32_t tmem = ctl->tmem_base;
   const uint32_t t_lane = tmem + ((warp * 32) << 16);
 
-  auto issue_load = [&](uint32_t ld) {
-    const uint32_t jt = ld % n_kt, st = ld % NS;
-    const bool second = ld >= n_kt;
-    uint8_t* dst = stage_s + st * kStage;
-    const uint32_t bytes = 2 * kRowTile + (second ? kColTile : 0) + (ld == 0 ? 2 * kRowTile : 0);
-    MbarExpectTx(&ctl->load[st], bytes);
-    if (ld == 0) {
-      LoadRowTile<D>(q_s, &map_q, &ctl->load[st], it * kTile, bh);
-      LoadRowTile<D>(do_s, &map_do, &ctl->load[st], it * kTile, bh);
+  auto issue_a = [&](uint32_t t) {
+    MbarExpectTx(&ctl->bar_a, 2 * kHalfRows + (t == 0 ? 2 * kFull : 0));
+    if (t == 0) {
+      LoadRows<D, 128>(q_s, &map_q, &ctl->bar_a, it * kTile, bh);
+      LoadRows<D, 128>(do_s, &map_do, &ctl->bar_a, it * kTile, bh);
     }
-    LoadRowTile<D>(dst, &map_k, &ctl->load[st], jt * kTile, bh);
-    LoadRowTile<D>(dst + kRowTile, &map_v, &ctl->load[st], jt * kTile, bh);
-    if (second) LoadColTile<D>(dst + 2 * kRowTile, &map_kt, &ctl->load[st], jt * kTile, bh);
+    LoadRows<D, 64>(k_s, &map_k, &ctl->bar_a, (t % n_h) * kHalf, bh);
+    LoadRows<D, 64>(v_s, &map_v, &ctl->bar_a, (t % n_h) * kHalf, bh);
+  };
+  auto issue_b = [&](uint32_t jh) {
+    MbarExpectTx(&ctl->bar_b, kCols);
+    LoadColsHalf(kt_s, &map_kt, &ctl->bar_b, jh * kHalf, bh);
   };
 
   const uint32_t row = it * kTile + tid;
   const bool live = row < a.S;
   float* st_row = a.stats + (static_cast<size_t>(bh) * a.S + (live ? row : 0)) * kAttnStatsWidth;
-  const float m = live ? st_row[0] : 0.0f;
+  const float c1 = a.inv_sqrt_d * kLog2e;
+  const float m2 = live ? st_row[0] * kLog2e : 0.0f;
   const float inv_l = live ? st_row[1] : 0.0f;
   float delta = 0.0f;
-  uint32_t mma_phase = 0;
+  uint32_t b_phase = 0;
   int failed = 0;
-  if (tid == 0) issue_load(0);
+  if (tid == 0) issue_a(0);
 
-  for (uint32_t ld = 0; ld < total; ++ld) {
-    const uint32_t jt = ld % n_kt, st = ld % NS;
-    const bool second = ld >= n_kt;
-    uint8_t* k_s = stage_s + st * kStage;
-    if (NS == 2 && tid == 0 && ld + 1 < total) issue_load(ld + 1);
-    if (!MbarWait(&ctl->load[st], (ld / NS) & 1)) failed = 1;
+  for (uint32_t t = 0; t < total; ++t) {
+    const uint32_t jh = t % n_h;
+    const bool second = t >= n_h;
     if (tid == 0) {
+      if (!MbarWait(&ctl->bar_a, t & 1)) failed = 1;
       TcFenceAfter();
-      MmaRowRow<D>(tmem, q_s, k_s);                        // S  = Q K^T
-      MmaRowRow<D>(tmem + 128, do_s, k_s + kRowTile);      // dP = dO V^T
-      UmmaCommit(&ctl->mma);
+      if (!failed) {
+        MmaRowRow<D, 64>(tmem, q_s, k_s);          // S  = Q K_h^T
+        MmaRowRow<D, 64>(tmem + 64, do_s, v_s);    // dP = dO V_h^T
+      }
+      UmmaCommit(&ctl->mma);   // also covers the previous step's dQ += dS K_h
     }
-    if (!MbarWait(&ctl->mma, mma_phase)) failed = 1;
-    mma_phase ^= 1;
+    if (!MbarWait(&ctl->mma, t & 1)) failed = 1;
     TcFenceAfter();
-    const uint32_t key0 = jt * kTile;
+    if (tid == 0 && !failed) {
+      if (t + 1 < total) issue_a(t + 1);
+      if (second) issue_b(jh);
+    }
+    __syncwarp();
+    const uint32_t key0 = jh * kHalf;
 #pragma unroll 1
-    for (uint32_t c0 = 0; c0 < kTile; c0 += 32) {
+    for (uint32_t c0 = 0; c0 < kHalf; c0 += 32) {
       uint32_t rs[32], rp[32];
       TmemLoad32(t_lane + c0, rs);
-      TmemLoad32(t_lane + 128 + c0, rp);
+      TmemLoad32(t_lane + 64 + c0, rp);
       TmemWaitLd();
-      float v[32];
+      if (!second) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float s = __uint_as_float(rs[j]) * a.inv_sqrt_d;
-        const float p = (key0 + c0 + j <= row) ? __expf(s - m) * inv_l : 0.0f;
-        const float dp = __uint_as_float(rp[j]);
-        if (!second) delta += p * dp;
-        v[j] = p * (dp - delta) * a.inv_sqrt_d;
+        for (int j = 0; j < 32; ++j) {
+          const float p = (key0 + c0 + j <= row)
+                              ? Exp2Approx(fmaf(__uint_as_float(rs[j]), c1, -m2)) * inv_l : 0.0f;
+          delta = fmaf(p, __uint_as_float(rp[j]), delta);
+        }
+      } else {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float p = (key0 + c0 + j <= row)
+                              ? Exp2Approx(fmaf(__uint_as_float(rs[j]), c1, -m2)) * inv_l : 0.0f;
+          v[j] = p * (__uint_as_float(rp[j]) - delta) * a.inv_sqrt_d;
+        }
+        StoreRowChunk(p_s, tid, c0, v);
       }
-      if (second) StoreRowChunk(p_s, tid, c0, v);
     }
     if (second) FenceProxyAsync();
     TcFenceBefore();
     if (__syncthreads_or(failed)) { failed = 1; break; }
-    if (second) {
-      if (tid == 0) {
-        TcFenceAfter();
-        MmaPT<D>(tmem + 256, p_s, k_s + 2 * kRowTile, jt != 0);   // dQ += dS K
-        UmmaCommit(&ctl->mma);
-      }
-      if (!MbarWait(&ctl->mma, mma_phase)) failed = 1;
-      mma_phase ^= 1;
+    if (second && tid == 0) {
+      if (!MbarWait(&ctl->bar_b, b_phase)) failed = 1;
+      b_phase ^= 1;
       TcFenceAfter();
+      if (!failed) MmaPT<D>(tmem + 128, p_s, kt_s, jh != 0);   // dQ += dS K_h
     }
-    if (NS == 1 && tid == 0 && ld + 1 < total) issue_load(ld + 1);
   }
+  if (tid == 0) UmmaCommit(&ctl->mma);
+  if (!failed && !MbarWait(&ctl->mma, total & 1)) failed = 1;
+  TcFenceAfter();
   failed = __syncthreads_or(failed);
   if (failed) {
     if (tid == 0) a.status->wait_timeout = 1;
+    DrainDelay();
   } else {
     const size_t HD = static_cast<size_t>(a.H) * D;
     float* o = a.out + (static_cast<size_t>(b) * a.S + (live ? row : 0)) * HD + static_cast<size_t>(h) * D;
-#pragma unroll 1
-    for (uint32_t c0 = 0; c0 < D; c0 += 32) {
-      uint32_t r[32];
-      TmemLoad32(t_lane + 256 + c0, r);
-      TmemWaitLd();
-      if (live) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(o + c0 + j) =
-              make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                          __uint_as_float(r[j + 3]));
-      }
-    }
+    StoreOutRow<D>(t_lane + 128, o, live, 1.0f);
     if (live) st_row[2] = delta;
   }
   TcFenceBefore();
@@ -453,11 +473,13 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 }
 
 // ---- dK / dV ---------------------------------------------------------------------------
-// Per key tile, over the query tiles at or below the diagonal, in the
-// transposed frame: S^T = K Q^T (one key row per thread, query index along the
-// columns), P^T from the stats rows of those queries; dV += P^T dO, or
-// dS^T = P^T (dP^T - delta) / sqrt(d) with dP^T = V dO^T and dK += dS^T Q.
-template <int D, bool kWantDK, int NS>
+// Per 128 key rows, over the queries at or below the diagonal 64 at a time, in
+// the transposed frame (one key row per thread, query index along the columns):
+// S^T = K Q_h^T; P^T from the stats rows of those queries, folded into one
+// number per query, M = max * log2(e) - log2(1/denominator), so that
+// P^T = 2^(s * log2(e)/sqrt(d) - M).  dV += P^T dO_h, or
+// dS^T = P^T (dP^T - delta) / sqrt(d) with dP^T = V dO_h^T and dK += dS^T Q_h.
+template <int D, bool kWantDK>
 __global__ void __launch_bounds__(128)
 AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                   const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
@@ -465,24 +487,26 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw);
   uint8_t* smem = AlignSmem(smem_raw + sizeof(Ctl));
-  constexpr uint32_t kRowTile = 128 * D * 2, kColTile = D * 256;
-  constexpr uint32_t kStage = (kWantDK ? 2 : 1) * kRowTile + kColTile;
+  constexpr uint32_t kFull = 128 * D * 2, kHalfRows = 64 * D * 2, kCols = D * 128;
   uint8_t* k_s = smem;
-  uint8_t* v_s = k_s + kRowTile;                            // used by dK only
-  uint8_t* stage_s = v_s + (kWantDK ? kRowTile : 0);
-  uint8_t* p_s = stage_s + NS * kStage;
-  float* stat_s = reinterpret_cast<float*>(p_s + kPBytes);  // m[128], 1/l[128], delta[128]
-  constexpr uint32_t kOutCol = kWantDK ? 256 : 128;
-  constexpr uint32_t kTmemCols = kWantDK ? 512 : 256;
+  uint8_t* v_s = k_s + kFull;                                // dK only
+  uint8_t* q_s = v_s + (kWantDK ? kFull : 0);
+  uint8_t* do_s = q_s + kHalfRows;                           // dK only
+  uint8_t* t_s = do_s + (kWantDK ? kHalfRows : 0);
+  uint8_t* p_s = t_s + kCols;
+  float* stat_s = reinterpret_cast<float*>(p_s + kHalfTileBytes);   // M[64], delta[64]
+  constexpr uint32_t kOutCol = kWantDK ? 128 : 64;
+  constexpr uint32_t kTmemCols = TmemColsFor(kOutCol + D);
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5;
-  const uint32_t n_qt = (a.S + kTile - 1) / kTile;
   const uint32_t jt = blockIdx.x;                          // key tile; low tiles have the most work
   const uint32_t bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
-  const uint32_t total = n_qt - jt;
+  const uint32_t all_h = (a.S + kHalf - 1) / kHalf;
+  const uint32_t h0 = 2 * jt;                              // first query step: the diagonal
+  const uint32_t total = all_h - h0;
 
   if (tid == 0) {
-    MbarInit(&ctl->load[0], 1); MbarInit(&ctl->load[1], 1); MbarInit(&ctl->mma, 1);
+    MbarInit(&ctl->bar_a, 1); MbarInit(&ctl->bar_b, 1); MbarInit(&ctl->mma, 1);
     MbarInitFence();
   }
   if (warp == 0) TmemAlloc(&ctl->tmem_base, kTmemCols);
@@ -492,63 +516,81 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
   const uint32_t tmem = ctl->tmem_base;
   const uint32_t t_lane = tmem + ((warp * 32) << 16);
 
-  auto issue_load = [&](uint32_t ld) {
-    const uint32_t it = jt + ld, st = ld % NS;
-    uint8_t* dst = stage_s + st * kStage;
-    const uint32_t bytes = kStage + (ld == 0 ? (kWantDK ? 2 : 1) * kRowTile : 0);
-    MbarExpectTx(&ctl->load[st], bytes);
-    if (ld == 0) {
-      LoadRowTile<D>(k_s, &map_k, &ctl->load[st], jt * kTile, bh);
-      if (kWantDK) LoadRowTile<D>(v_s, &map_v, &ctl->load[st], jt * kTile, bh);
+  auto issue_a = [&](uint32_t t) {
+    constexpr uint32_t kPer = (kWantDK ? 2 : 1) * kHalfRows, kOnce = (kWantDK ? 2 : 1) * kFull;
+    MbarExpectTx(&ctl->bar_a, kPer + (t == 0 ? kOnce : 0));
+    if (t == 0) {
+      LoadRows<D, 128>(k_s, &map_k, &ctl->bar_a, jt * kTile, bh);
+      if (kWantDK) LoadRows<D, 128>(v_s, &map_v, &ctl->bar_a, jt * kTile, bh);
     }
-    LoadRowTile<D>(dst, &map_q, &ctl->load[st], it * kTile, bh);
-    if (kWantDK) LoadRowTile<D>(dst + kRowTile, &map_do, &ctl->load[st], it * kTile, bh);
-    LoadColTile<D>(dst + (kWantDK ? 2 : 1) * kRowTile, &map_t, &ctl->load[st], it * kTile, bh);
+    LoadRows<D, 64>(q_s, &map_q, &ctl->bar_a, (h0 + t) * kHalf, bh);
+    if (kWantDK) LoadRows<D, 64>(do_s, &map_do, &ctl->bar_a, (h0 + t) * kHalf, bh);
+  };
+  auto issue_b = [&](uint32_t t) {
+    MbarExpectTx(&ctl->bar_b, kCols);
+    LoadColsHalf(t_s, &map_t, &ctl->bar_b, (h0 + t) * kHalf, bh);
   };
 
   const uint32_t key = jt * kTile + tid;                    // this thread's key row
-  uint32_t mma_phase = 0;
+  const float c1 = a.inv_sqrt_d * kLog2e;
   int failed = 0;
-  if (tid == 0) issue_load(0);
+  if (tid == 0) issue_a(0);
 
-  for (uint32_t ld = 0; ld < total; ++ld) {
-    const uint32_t it = jt + ld, st = ld % NS;
-    uint8_t* q_s = stage_s + st * kStage;
-    if (NS == 2 && tid == 0 && ld + 1 < total) issue_load(ld + 1);
-    {  // stats rows of this query tile (zeros past the end of the sequence)
-      const uint32_t qi = it * kTile + tid;
-      float4 sv = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (qi < a.S)
-        sv = *reinterpret_cast<const float4*>(a.stats + (static_cast<size_t>(bh) * a.S + qi) * kAttnStatsWidth);
-      stat_s[tid] = sv.x; stat_s[128 + tid] = sv.y; stat_s[256 + tid] = sv.z;
+  for (uint32_t t = 0; t < total; ++t) {
+    const uint32_t q0 = (h0 + t) * kHalf;
+    if (tid < kHalf) {   // this step's queries (the previous step's readers passed a barrier)
+      const uint32_t qi = q0 + tid;
+      float M = INFINITY, dl = 0.0f;   // past the end of the sequence: P = 2^-inf = 0
+      if (qi < a.S) {
+        const float4 sv = *reinterpret_cast<const float4*>(
+            a.stats + (static_cast<size_t>(bh) * a.S + qi) * kAttnStatsWidth);
+        M = sv.x * kLog2e - log2f(sv.y);
+        dl = sv.z;
+      }
+      stat_s[tid] = M;
+      stat_s[kHalf + tid] = dl;
     }
-    __syncthreads();
-    if (!MbarWait(&ctl->load[st], (ld / NS) & 1)) failed = 1;
     if (tid == 0) {
+      if (!MbarWait(&ctl->bar_a, t & 1)) failed = 1;
       TcFenceAfter();
-      MmaRowRow<D>(tmem, k_s, q_s);                              // S^T  = K Q^T
-      if (kWantDK) MmaRowRow<D>(tmem + 128, v_s, q_s + kRowTile); // dP^T = V dO^T
-      UmmaCommit(&ctl->mma);
+      if (!failed) {
+        MmaRowRow<D, 64>(tmem, k_s, q_s);                          // S^T  = K Q_h^T
+        if (kWantDK) MmaRowRow<D, 64>(tmem + 64, v_s, do_s);       // dP^T = V dO_h^T
+      }
+      UmmaCommit(&ctl->mma);   // also covers the previous step's second product
     }
-    if (!MbarWait(&ctl->mma, mma_phase)) failed = 1;
-    mma_phase ^= 1;
+    __syncthreads();           // stat_s is written
+    if (!MbarWait(&ctl->mma, t & 1)) failed = 1;
     TcFenceAfter();
-    const uint32_t q0 = it * kTile;
+    if (tid == 0 && !failed) {
+      if (t + 1 < total) issue_a(t + 1);
+      issue_b(t);
+    }
+    __syncwarp();
+    const bool diagonal = q0 < jt * kTile + kTile;   // some (key, query) pairs are masked
 #pragma unroll 1
-    for (uint32_t c0 = 0; c0 < kTile; c0 += 32) {
+    for (uint32_t c0 = 0; c0 < kHalf; c0 += 32) {
       uint32_t rs[32], rp[32];
       TmemLoad32(t_lane + c0, rs);
-      if (kWantDK) TmemLoad32(t_lane + 128 + c0, rp);
+      if (kWantDK) TmemLoad32(t_lane + 64 + c0, rp);
       TmemWaitLd();
       float v[32];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const uint32_t qi = q0 + c0 + j;
-        const float s = __uint_as_float(rs[j]) * a.inv_sqrt_d;
-        const bool ok = key <= qi && qi < a.S;
-        const float p = ok ? __expf(s - stat_s[c0 + j]) * stat_s[128 + c0 + j] : 0.0f;
-        if (kWantDK) v[j] = p * (__uint_as_float(rp[j]) - stat_s[256 + c0 + j]) * a.inv_sqrt_d;
-        else v[j] = p;
+      for (int j4 = 0; j4 < 32; j4 += 4) {
+        const float4 M4 = *reinterpret_cast<const float4*>(&stat_s[c0 + j4]);
+        const float Mv[4] = {M4.x, M4.y, M4.z, M4.w};
+        float dv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (kWantDK) {
+          const float4 d4 = *reinterpret_cast<const float4*>(&stat_s[kHalf + c0 + j4]);
+          dv[0] = d4.x; dv[1] = d4.y; dv[2] = d4.z; dv[3] = d4.w;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = j4 + u;
+          float p = Exp2Approx(fmaf(__uint_as_float(rs[j]), c1, -Mv[u]));
+          if (diagonal && key > q0 + c0 + j) p = 0.0f;
+          v[j] = kWantDK ? p * (__uint_as_float(rp[j]) - dv[u]) * a.inv_sqrt_d : p;
+        }
       }
       StoreRowChunk(p_s, tid, c0, v);
     }
@@ -556,35 +598,23 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     TcFenceBefore();
     if (__syncthreads_or(failed)) { failed = 1; break; }
     if (tid == 0) {
+      if (!MbarWait(&ctl->bar_b, t & 1)) failed = 1;
       TcFenceAfter();
-      MmaPT<D>(tmem + kOutCol, p_s, q_s + (kWantDK ? 2 : 1) * kRowTile, ld != 0);
-      UmmaCommit(&ctl->mma);
+      if (!failed) MmaPT<D>(tmem + kOutCol, p_s, t_s, t != 0);
     }
-    if (!MbarWait(&ctl->mma, mma_phase)) failed = 1;
-    mma_phase ^= 1;
-    TcFenceAfter();
-    if (NS == 1 && tid == 0 && ld + 1 < total) issue_load(ld + 1);
   }
+  if (tid == 0) UmmaCommit(&ctl->mma);
+  if (!failed && !MbarWait(&ctl->mma, total & 1)) failed = 1;
+  TcFenceAfter();
   failed = __syncthreads_or(failed);
   if (failed) {
     if (tid == 0) a.status->wait_timeout = 1;
+    DrainDelay();
   } else {
     const bool live = key < a.S;
     const size_t HD = static_cast<size_t>(a.H) * D;
     float* o = a.out + (static_cast<size_t>(b) * a.S + (live ? key : 0)) * HD + static_cast<size_t>(h) * D;
-#pragma unroll 1
-    for (uint32_t c0 = 0; c0 < D; c0 += 32) {
-      uint32_t r[32];
-      TmemLoad32(t_lane + kOutCol + c0, r);
-      TmemWaitLd();
-      if (live) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(o + c0 + j) =
-              make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                          __uint_as_float(r[j + 3]));
-      }
-    }
+    StoreOutRow<D>(t_lane + kOutCol, o, live, 1.0f);
   }
   TcFenceBefore();
   __syncthreads();
@@ -596,12 +626,11 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 
 }  // namespace
 
-
-size_t AttnFwdSmem(int d) { return 128 * d * 2 + 2 * (128 * d * 2 + d * 256) + kPBytes + 1024; }
-size_t AttnDQSmem(int d, int ns) { return 2 * 128 * d * 2 + ns * (2 * 128 * d * 2 + d * 256) + kPBytes + 1024; }
-size_t AttnDKVSmem(int d, bool dk, int ns) {
-  const size_t row = 128 * d * 2, col = d * 256;
-  return (dk ? 2 : 1) * row + ns * ((dk ? 2 : 1) * row + col) + kPBytes + 3 * 128 * 4 + 1024;
+size_t AttnFwdSmem(int d) { return 128 * d * 2 + 64 * d * 2 + d * 128 + kHalfTileBytes + 1152; }
+size_t AttnDQSmem(int d) { return 2 * 128 * d * 2 + 2 * 64 * d * 2 + d * 128 + kHalfTileBytes + 1152; }
+size_t AttnDKVSmem(int d, bool dk) {
+  const size_t full = 128 * d * 2, half = 64 * d * 2, cols = d * 128;
+  return (dk ? 2 : 1) * (full + half) + cols + kHalfTileBytes + 2 * kHalf * 4 + 1152;
 }
 
 template <typename Kernel>
@@ -616,57 +645,55 @@ void PackHeads(const float* x, uint16_t* rows, uint16_t* cols, uint32_t B, uint3
   else PackHeadsKernel<128><<<grid, 256, 0, s>>>(x, rows, cols, S, H);
 }
 
-cudaError_t AttnFwdUmma(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& vt,
+cudaError_t AttnFwdUmma(const CUtensorMap& q, const CUtensorMap& k_half, const CUtensorMap& vt,
                         const AttnUmmaArgs& a, cudaStream_t s) {
   dim3 grid((a.S + kTile - 1) / kTile, a.B * a.H);
   const size_t smem = AttnFwdSmem(a.d);
   cudaError_t e;
   if (a.d == 64) {
     if ((e = Configure(AttnFwdUmmaKernel<64>, smem)) != cudaSuccess) return e;
-    AttnFwdUmmaKernel<64><<<grid, 128, smem, s>>>(q, k, vt, a);
+    AttnFwdUmmaKernel<64><<<grid, 128, smem, s>>>(q, k_half, vt, a);
   } else {
     if ((e = Configure(AttnFwdUmmaKernel<128>, smem)) != cudaSuccess) return e;
-    AttnFwdUmmaKernel<128><<<grid, 128, smem, s>>>(q, k, vt, a);
+    AttnFwdUmmaKernel<128><<<grid, 128, smem, s>>>(q, k_half, vt, a);
   }
   return cudaGetLastError();
 }
 
-cudaError_t AttnDQUmma(const CUtensorMap& q, const CUtensorMap& dout, const CUtensorMap& k,
-                       const CUtensorMap& v, const CUtensorMap& kt, const AttnUmmaArgs& a,
+cudaError_t AttnDQUmma(const CUtensorMap& q, const CUtensorMap& dout, const CUtensorMap& k_half,
+                       const CUtensorMap& v_half, const CUtensorMap& kt, const AttnUmmaArgs& a,
                        cudaStream_t s) {
   dim3 grid((a.S + kTile - 1) / kTile, a.B * a.H);
+  const size_t smem = AttnDQSmem(a.d);
   cudaError_t e;
   if (a.d == 64) {
-    const size_t smem = AttnDQSmem(64, 2);
-    if ((e = Configure(AttnDQUmmaKernel<64, 2>, smem)) != cudaSuccess) return e;
-    AttnDQUmmaKernel<64, 2><<<grid, 128, smem, s>>>(q, dout, k, v, kt, a);
+    if ((e = Configure(AttnDQUmmaKernel<64>, smem)) != cudaSuccess) return e;
+    AttnDQUmmaKernel<64><<<grid, 128, smem, s>>>(q, dout, k_half, v_half, kt, a);
   } else {
-    const size_t smem = AttnDQSmem(128, 1);
-    if ((e = Configure(AttnDQUmmaKernel<128, 1>, smem)) != cudaSuccess) return e;
-    AttnDQUmmaKernel<128, 1><<<grid, 128, smem, s>>>(q, dout, k, v, kt, a);
+    if ((e = Configure(AttnDQUmmaKernel<128>, smem)) != cudaSuccess) return e;
+    AttnDQUmmaKernel<128><<<grid, 128, smem, s>>>(q, dout, k_half, v_half, kt, a);
   }
   return cudaGetLastError();
 }
 
-cudaError_t AttnDKVUmma(bool want_dk, const CUtensorMap& k, const CUtensorMap& v, const CUtensorMap& q,
-                        const CUtensorMap& dout, const CUtensorMap& t, const AttnUmmaArgs& a,
-                        cudaStream_t s) {
+cudaError_t AttnDKVUmma(bool want_dk, const CUtensorMap& k, const CUtensorMap& v,
+                        const CUtensorMap& q_half, const CUtensorMap& dout_half, const CUtensorMap& t,
+                        const AttnUmmaArgs& a, cudaStream_t s) {
   dim3 grid((a.S + kTile - 1) / kTile, a.B * a.H);
   cudaError_t e;
-#define SEE_LAUNCH_DKV(D, DK, NS)                                                      \
+#define SEE_LAUNCH_DKV(D, DK)                                                          \
   do {                                                                                 \
-    const size_t smem = AttnDKVSmem(D, DK, NS);                                        \
-    if ((e = Configure(AttnDKVUmmaKernel<D, DK, NS>, smem)) != cudaSuccess) return e;  \
-    AttnDKVUmmaKernel<D, DK, NS><<<grid, 128, smem, s>>>(k, v, q, dout, t, a);        \
+    const size_t smem = AttnDKVSmem(D, DK);                                            \
+    if ((e = Configure(AttnDKVUmmaKernel<D, DK>, smem)) != cudaSuccess) return e;      \
+    AttnDKVUmmaKernel<D, DK><<<grid, 128, smem, s>>>(k, v, q_half, dout_half, t, a);   \
   } while (0)
   if (a.d == 64) {
-    if (want_dk) SEE_LAUNCH_DKV(64, true, 2); else SEE_LAUNCH_DKV(64, false, 2);
+    if (want_dk) SEE_LAUNCH_DKV(64, true); else SEE_LAUNCH_DKV(64, false);
   } else {
-    if (want_dk) SEE_LAUNCH_DKV(128, true, 1); else SEE_LAUNCH_DKV(128, false, 2);
+    if (want_dk) SEE_LAUNCH_DKV(128, true); else SEE_LAUNCH_DKV(128, false);
   }
 #undef SEE_LAUNCH_DKV
   return cudaGetLastError();
 }
-
 
 }  // namespace see::k

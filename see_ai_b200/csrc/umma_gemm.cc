@@ -354,10 +354,11 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
     ent[r] = victim;
   }
   const uint64_t BH = op.B * op.H;
-  CUtensorMap mr[4], mc[4];
+  CUtensorMap mr[4], mh[4], mc[4];   // rows (box 128), rows (box 64), cols
   for (int r = 0; r < 4; ++r) {
     if (!used[r]) continue;
-    if (!EncodeHeads(impl, &mr[r], ent[r]->rows, op.d, op.S, BH, 128))
+    if (!EncodeHeads(impl, &mr[r], ent[r]->rows, op.d, op.S, BH, 128) ||
+        !EncodeHeads(impl, &mh[r], ent[r]->rows, op.d, op.S, BH, 64))
       return "tensor-core attention: cuTensorMapEncodeTiled refused a row layout";
     if (!EncodeHeads(impl, &mc[r], ent[r]->cols, op.S, op.d, BH, static_cast<uint32_t>(op.d)))
       return "tensor-core attention: cuTensorMapEncodeTiled refused a column layout";
@@ -370,10 +371,10 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
   a.stats = op.stats;
   a.status = impl->status;
   cudaError_t e = cudaSuccess;
-  if (fwd) e = k::AttnFwdUmma(mr[Q], mr[K], mc[V], a, stream);
-  if (dq) e = k::AttnDQUmma(mr[Q], mr[DO], mr[K], mr[V], mc[K], a, stream);
-  if (dk) e = k::AttnDKVUmma(true, mr[K], mr[V], mr[Q], mr[DO], mc[Q], a, stream);
-  if (dv) e = k::AttnDKVUmma(false, mr[K], mr[K], mr[Q], mr[Q], mc[DO], a, stream);
+  if (fwd) e = k::AttnFwdUmma(mr[Q], mh[K], mc[V], a, stream);
+  if (dq) e = k::AttnDQUmma(mr[Q], mr[DO], mh[K], mh[V], mc[K], a, stream);
+  if (dk) e = k::AttnDKVUmma(true, mr[K], mr[V], mh[Q], mh[DO], mc[Q], a, stream);
+  if (dv) e = k::AttnDKVUmma(false, mr[K], mr[K], mh[Q], mh[Q], mc[DO], a, stream);
   if (e != cudaSuccess) return std::string("tensor-core attention launch: ") + cudaGetErrorString(e);
   ++*launches;
   return {};
