@@ -37,6 +37,56 @@ def shard_rows(global_rows: int, seq_len: int, world: int, rank: int) -> Tuple[i
     return rank * per, (rank + 1) * per
 
 
+def scan_phases(train) -> Tuple[int, int]:
+    """(bwd_begin, opt_begin) of a train section: the instruction after the loss
+    forward, and the first clip / optimizer instruction (the engine's phase
+    scan, mirrored for hosts that drive the backend seam themselves; reference:
+    runtime/profiler/step_timings.h:37-59)."""
+    from . import plan as P
+    Op = P.Op
+    n = len(train)
+    bwd, opt = n, n
+    for i, ins in enumerate(train):
+        if ins.opcode in (Op.XENT_FWD, Op.XENT_MASKED_FWD, Op.MSE_FWD, Op.KL_FWD):
+            bwd = i + 1
+        if ins.opcode in (Op.CLIP_NORM, Op.SQNORM_ACCUM, Op.CLIP_GLOBAL, Op.SGD_STEP,
+                          Op.ADAMW_STEP) and opt == n:
+            opt = i
+    return bwd, max(opt, bwd)
+
+
+def gradient_block(plan) -> Tuple[int, int]:
+    """(arena offset, bytes) of the block spanning every optimizer instruction's
+    gradient operand: what the ranks exchange once per step."""
+    from . import plan as P
+    prog = plan.section("step") or plan.section("train")
+    lo, hi = None, 0
+    for ins in prog:
+        if ins.opcode in (P.Op.ADAMW_STEP, P.Op.SGD_STEP):
+            off = ins.ins[1] & ~(P.RODATA_BIT | P.SOURCE_BIT)
+            lo = off if lo is None else min(lo, off)
+            hi = max(hi, off + ins.out[0] * 4)
+    return (0, 0) if lo is None else (lo, hi - lo)
+
+
+def host_exchange(arena: np.ndarray, off: int, nbytes: int, group=None) -> None:
+    """The exchange on host memory over any torch.distributed backend (gloo on
+    CPU): all-gather the block, fold the copies in rank order, write the mean
+    back in place.  The device path does the same with the gather landing in HBM
+    and the fold inside the optimizer kernel; this form serves hosts that keep
+    the arena in their own memory, and the CPU tests."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    if world == 1 or nbytes == 0:
+        return
+    mine = torch.from_numpy(arena[off:off + nbytes].copy())
+    copies = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(copies, mine, group=group)
+    mean = fixed_order_mean([c.numpy().view(np.float32) for c in copies])
+    arena[off:off + nbytes] = mean.view(np.uint8)
+
+
 def fixed_order_mean(copies: Sequence[np.ndarray]) -> np.ndarray:
     """The reduction the optimizer kernel applies to gathered gradients: a
     left-to-right f32 sum in rank order, then one multiply by 1/N."""
