@@ -289,6 +289,207 @@ UmmaGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// ---- persistent form -------------------------------------------------------------------
+// One CTA per SM walks 128 x 256 output tiles t = blockIdx.x, blockIdx.x +
+// gridDim.x, ... (tiles of one row block are neighbours, so concurrent CTAs
+// share A in L2).  The wider tile is what the shared-memory fill rate asks for:
+// a 128 x 128 tile moves 32 KB per 128x128x64 block of math (64 FLOP per byte
+// from L2), which tops out near 12-13 TB/s of L2 traffic well below the tensor
+// peak; 128 x 256 moves 48 KB per twice the math (85 FLOP per byte).  The
+// operand ring keeps flowing across tile boundaries, the accumulator is
+// double-buffered in tensor memory (2 x 256 columns: all of it), and the
+// epilogue warps own a staging slab, so tile i's epilogue (128 KB of f32) runs
+// under tile i+1's main loop.  What the one-tile kernel pays per tile — barrier
+// set-up, tensor-memory allocation, the first TMA round trip, CTA launch and
+// retirement — is paid once per SM.
+constexpr uint32_t kPBlockN = 256;
+constexpr uint32_t kPStages = 3;
+constexpr uint32_t kPBTileBytes = kPBlockN * kBlockK * 2;
+constexpr uint32_t kPStageBytes = kATileBytes + kPBTileBytes;
+constexpr uint32_t kPTmemCols = 2 * kPBlockN;
+constexpr uint32_t kSlabBytes = 32 * 128 * 4;   // one epilogue warp's 32 x 128 f32
+
+struct __align__(8) PBarriers {
+  uint64_t full[kPStages];
+  uint64_t empty[kPStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  volatile uint32_t abort;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
+                         const __grid_constant__ CUtensorMap map_b, UmmaEpilogue ep) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (SmemAddr(smem_raw) & 1023u)) & 1023u);
+  uint8_t* slabs = smem + kPStages * kPStageBytes;
+  PBarriers* bars = reinterpret_cast<PBarriers*>(slabs + 4 * kSlabBytes);
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t k_blocks = (ep.K + kBlockK - 1) / kBlockK;
+  const uint32_t tiles_n = (ep.N + kPBlockN - 1) / kPBlockN;
+  const uint32_t tiles_m = (ep.M + kBlockM - 1) / kBlockM;
+  const uint32_t total_tiles = tiles_m * tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < kPStages; ++s) {
+      MbarInit(&bars->full[s], 1);
+      MbarInit(&bars->empty[s], 1);
+    }
+    for (uint32_t b = 0; b < 2; ++b) {
+      MbarInit(&bars->tmem_full[b], 1);
+      MbarInit(&bars->tmem_empty[b], 4);   // one arrival per epilogue warp
+    }
+    bars->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(SmemAddr(&bars->tmem_base)), "r"(kPTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---- TMA producer ----
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const uint32_t m0 = (t / tiles_n) * kBlockM, n0 = (t % tiles_n) * kPBlockN;
+        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
+          const uint32_t s = it % kPStages, round = it / kPStages;
+          if (round > 0 && !MbarWait(&bars->empty[s], (round - 1) & 1)) {
+            ep.status->wait_timeout = 1;
+            bars->abort = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + s * kPStageBytes;
+          MbarExpectTx(&bars->full[s], kPStageBytes);
+          TmaLoad2D(a_dst, &map_a, &bars->full[s], static_cast<int32_t>(kb * kBlockK),
+                    static_cast<int32_t>(m0));
+          // B's 256 rows as two 128-row boxes, back to back: one [256][64] tile.
+          TmaLoad2D(a_dst + kATileBytes, &map_b, &bars->full[s], static_cast<int32_t>(kb * kBlockK),
+                    static_cast<int32_t>(n0));
+          TmaLoad2D(a_dst + kATileBytes + kBTileBytes, &map_b, &bars->full[s],
+                    static_cast<int32_t>(kb * kBlockK), static_cast<int32_t>(n0 + kBlockN));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    if (lane == 0) {
+      const uint32_t idesc = MakeInstrDesc(kBlockM, kPBlockN);
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
+        const uint32_t buf = lt & 1, use = lt >> 1;
+        if (use > 0 && !MbarWait(&bars->tmem_empty[buf], (use - 1) & 1)) {
+          ep.status->wait_timeout = 1;
+          bars->abort = 1;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc = tmem_base + buf * kPBlockN;
+        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
+          const uint32_t s = it % kPStages, round = it / kPStages;
+          if (!MbarWait(&bars->full[s], round & 1)) {
+            ep.status->wait_timeout = 1;
+            bars->abort = 1;
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = SmemAddr(smem + s * kPStageBytes);
+          const uint64_t desc_a = MakeSmemDesc(a_addr);
+          const uint64_t desc_b = MakeSmemDesc(a_addr + kATileBytes);
+#pragma unroll
+          for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k)
+            UmmaBf16(acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          UmmaCommit(&bars->empty[s]);
+        }
+        UmmaCommit(&bars->tmem_full[buf]);   // accumulator complete (or abandoned on timeout)
+      }
+    }
+  } else {
+    // ---- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----
+    const uint32_t quarter = warp & 3;
+    float* slab = reinterpret_cast<float*>(slabs + quarter * kSlabBytes);
+    uint32_t lt = 0;
+    for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++lt) {
+      const uint32_t buf = lt & 1, use = lt >> 1;
+      const uint32_t m0 = (t / tiles_n) * kBlockM, n0 = (t % tiles_n) * kPBlockN;
+      bool ok = MbarWait(&bars->tmem_full[buf], use & 1);
+      if (!ok && lane == 0) { ep.status->wait_timeout = 1; bars->abort = 1; }
+      if (bars->abort) ok = false;
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t row0 = m0 + quarter * 32;
+      const uint32_t rows = row0 < ep.M ? (ep.M - row0 < 32 ? ep.M - row0 : 32) : 0;
+#pragma unroll 1
+      for (uint32_t half = 0; half < 2; ++half) {   // 128 columns at a time through the slab
+#pragma unroll 1
+        for (uint32_t c0 = 0; c0 < 128; c0 += 32) {
+          uint32_t r[32];
+          TmemLoad32(tmem_base + ((quarter * 32) << 16) + buf * kPBlockN + half * 128 + c0, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (uint32_t q = 0; q < 8; ++q) {
+            const uint32_t chunk = ((c0 >> 2) + q) ^ lane;   // 32 chunks of 4 floats per row
+            *reinterpret_cast<uint4*>(slab + lane * 128 + chunk * 4) =
+                make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+          }
+        }
+        if (half == 1) asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        // The accumulator buffer is read out: hand it back before the slow part.
+        if (half == 1 && lane == 0)
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];"
+                       ::"r"(SmemAddr(&bars->tmem_empty[buf])) : "memory");
+        const uint32_t n = n0 + half * 128 + lane * 4;
+        if (n < ep.N) {   // N % 4 == 0: a float4 is all in or all out
+          float4 scale = make_float4(ep.alpha, ep.alpha, ep.alpha, ep.alpha);
+          if (ep.col_scale) scale = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n));
+          float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (ep.bias) bias = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
+#pragma unroll 4
+          for (uint32_t rr = 0; rr < rows; ++rr) {
+            const float4 acc = *reinterpret_cast<const float4*>(slab + rr * 128 + ((lane ^ rr) * 4));
+            const size_t at = static_cast<size_t>(row0 + rr) * ep.N + n;
+            float4 v = make_float4(acc.x * scale.x, acc.y * scale.y, acc.z * scale.z, acc.w * scale.w);
+            if (ep.addend) {
+              const float4 d = __ldg(reinterpret_cast<const float4*>(ep.addend + at));
+              v = make_float4(d.x + v.x, d.y + v.y, d.z + v.z, d.w + v.w);
+            }
+            if (ep.bias) v = make_float4(v.x + bias.x, v.y + bias.y, v.z + bias.z, v.w + bias.w);
+            if (ep.act != kActNone)
+              v = make_float4(ApplyAct(v.x, ep.act), ApplyAct(v.y, ep.act), ApplyAct(v.z, ep.act),
+                              ApplyAct(v.w, ep.act));
+            *reinterpret_cast<float4*>(ep.C + at) = v;
+          }
+        }
+        __syncwarp();   // the slab is rewritten next
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kPTmemCols)
+                 : "memory");
+  }
+}
+
 // Weight conversion to the K-major bf16 layout [N][K] the kernel consumes.
 // transpose = true: src is [K][N] (the NN forms); false: src is [N][K].
 template <typename T> __device__ __forceinline__ uint16_t ToBf16Bits(T v);
@@ -330,18 +531,37 @@ __global__ void WeightToBf16Kernel(const T* __restrict__ src, uint16_t* __restri
 }  // namespace
 
 size_t UmmaSmemBytes() { return kStages * kStageBytes + sizeof(Barriers) + 1024; }
+static size_t UmmaPersistentSmemBytes() {
+  return kPStages * kPStageBytes + 4 * kSlabBytes + sizeof(PBarriers) + 1024;
+}
 
 cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
                            const UmmaEpilogue& ep, cudaStream_t s) {
   static bool configured = false;
-  const size_t smem = UmmaSmemBytes();
+  static int sm_count[64] = {};
+  const size_t smem = UmmaSmemBytes(), psmem = UmmaPersistentSmemBytes();
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(UmmaGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(UmmaGemmPersistentKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(psmem));
+    if (e != cudaSuccess) return e;
     configured = true;
   }
-  dim3 grid((ep.N + kBlockN - 1) / kBlockN, (ep.M + kBlockM - 1) / kBlockM);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && sm_count[dev] == 0)
+    cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+  const uint32_t sms = (dev >= 0 && dev < 64 && sm_count[dev] > 0) ? sm_count[dev] : 148;
+  const uint32_t tiles_n = (ep.N + kBlockN - 1) / kBlockN, tiles_m = (ep.M + kBlockM - 1) / kBlockM;
+  const uint32_t ptiles_n = (ep.N + kPBlockN - 1) / kPBlockN;
+  if (static_cast<uint64_t>(ptiles_n) * tiles_m > 2ull * sms) {
+    // Enough tiles for every SM to amortise its set-up over several.
+    UmmaGemmPersistentKernel<<<sms, kThreads, psmem, s>>>(map_a, map_b, ep);
+    return cudaGetLastError();
+  }
+  dim3 grid(tiles_n, tiles_m);
   UmmaGemmKernel<<<grid, kThreads, smem, s>>>(map_a, map_b, ep);
   return cudaGetLastError();
 }
