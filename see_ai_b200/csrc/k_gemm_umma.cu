@@ -298,16 +298,19 @@ UmmaGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // peak; 128 x 256 moves 48 KB per twice the math (85 FLOP per byte).  The
 // operand ring keeps flowing across tile boundaries, the accumulator is
 // double-buffered in tensor memory (2 x 256 columns: all of it), and the
-// epilogue warps own a staging slab, so tile i's epilogue (128 KB of f32) runs
+// epilogue warps own a small staging slab, so tile i's epilogue (128 KB of f32) runs
 // under tile i+1's main loop.  What the one-tile kernel pays per tile — barrier
 // set-up, tensor-memory allocation, the first TMA round trip, CTA launch and
 // retirement — is paid once per SM.
 constexpr uint32_t kPBlockN = 256;
 constexpr uint32_t kPStages = 3;
+constexpr uint32_t kPThreads = 320;   // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
+constexpr uint32_t kPEpiWarps = 8;
 constexpr uint32_t kPBTileBytes = kPBlockN * kBlockK * 2;
 constexpr uint32_t kPStageBytes = kATileBytes + kPBTileBytes;
 constexpr uint32_t kPTmemCols = 2 * kPBlockN;
-constexpr uint32_t kSlabBytes = 32 * 128 * 4;   // one epilogue warp's 32 x 128 f32
+constexpr uint32_t kSlabCols = 64;
+constexpr uint32_t kSlabBytes = 32 * kSlabCols * 4;   // one epilogue warp's 32 x 64 f32
 
 struct __align__(8) PBarriers {
   uint64_t full[kPStages];
@@ -318,13 +321,13 @@ struct __align__(8) PBarriers {
   volatile uint32_t abort;
 };
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kPThreads, 1)
 UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
                          const __grid_constant__ CUtensorMap map_b, UmmaEpilogue ep) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (SmemAddr(smem_raw) & 1023u)) & 1023u);
   uint8_t* slabs = smem + kPStages * kPStageBytes;
-  PBarriers* bars = reinterpret_cast<PBarriers*>(slabs + 4 * kSlabBytes);
+  PBarriers* bars = reinterpret_cast<PBarriers*>(slabs + kPEpiWarps * kSlabBytes);
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t k_blocks = (ep.K + kBlockK - 1) / kBlockK;
@@ -339,7 +342,7 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
     }
     for (uint32_t b = 0; b < 2; ++b) {
       MbarInit(&bars->tmem_full[b], 1);
-      MbarInit(&bars->tmem_empty[b], 4);   // one arrival per epilogue warp
+      MbarInit(&bars->tmem_empty[b], kPEpiWarps);   // one arrival per epilogue warp
     }
     bars->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -362,6 +365,17 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
       bool ok = true;
       for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const uint32_t m0 = (t / tiles_n) * kBlockM, n0 = (t % tiles_n) * kPBlockN;
+        // Ask L2 for the A rows of this CTA's next tile now, so that its loads
+        // find them there instead of paying an HBM round trip inside the ring.
+        if (t + gridDim.x < total_tiles && k_blocks <= 64) {   // (a long K would only thrash L2)
+          const uint32_t next_m0 = ((t + gridDim.x) / tiles_n) * kBlockM;
+          if (next_m0 != m0)
+            for (uint32_t kb = 0; kb < k_blocks; ++kb)
+              asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                           ::"l"(reinterpret_cast<uint64_t>(&map_a)),
+                             "r"(static_cast<int32_t>(kb * kBlockK)), "r"(static_cast<int32_t>(next_m0))
+                           : "memory");
+        }
         for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
           const uint32_t s = it % kPStages, round = it / kPStages;
           if (round > 0 && !MbarWait(&bars->empty[s], (round - 1) & 1)) {
@@ -418,9 +432,11 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
       }
     }
   } else {
-    // ---- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----
-    const uint32_t quarter = warp & 3;
-    float* slab = reinterpret_cast<float*>(slabs + quarter * kSlabBytes);
+    // ---- epilogue: warps 2..9.  TMEM lane quarter = warp % 4 (the hardware's
+    // rule); the two warps of a quarter split the tile's 256 columns in half.
+    const uint32_t quarter = warp & 3, col_half = (warp - 2) >> 2;
+    float* slab = reinterpret_cast<float*>(slabs + (warp - 2) * kSlabBytes);
+    const uint32_t sub = lane >> 4, cl = lane & 15;
     uint32_t lt = 0;
     for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++lt) {
       const uint32_t buf = lt & 1, use = lt >> 1;
@@ -433,35 +449,42 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t row0 = m0 + quarter * 32;
       const uint32_t rows = row0 < ep.M ? (ep.M - row0 < 32 ? ep.M - row0 : 32) : 0;
+      // 64 columns at a time through the slab.  A thread writes its accumulator
+      // row as sixteen 16-byte chunks, chunk index XOR-ed with the row; the warp
+      // then reads two rows per instruction (lanes 0-15 one row, 16-31 the next),
+      // 512 contiguous bytes of C per store instruction.  Conflict-free both ways.
+      const uint32_t t_row = tmem_base + ((quarter * 32) << 16) + buf * kPBlockN + col_half * 128;
 #pragma unroll 1
-      for (uint32_t half = 0; half < 2; ++half) {   // 128 columns at a time through the slab
-#pragma unroll 1
-        for (uint32_t c0 = 0; c0 < 128; c0 += 32) {
-          uint32_t r[32];
-          TmemLoad32(tmem_base + ((quarter * 32) << 16) + buf * kPBlockN + half * 128 + c0, r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-          for (uint32_t q = 0; q < 8; ++q) {
-            const uint32_t chunk = ((c0 >> 2) + q) ^ lane;   // 32 chunks of 4 floats per row
-            *reinterpret_cast<uint4*>(slab + lane * 128 + chunk * 4) =
-                make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
-          }
+      for (uint32_t pass = 0; pass < 2; ++pass) {
+        uint32_t ra[32], rb[32];
+        TmemLoad32(t_row + pass * kSlabCols, ra);
+        TmemLoad32(t_row + pass * kSlabCols + 32, rb);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (pass == 1) {
+          // The accumulator buffer is read out: hand it back before the slow part.
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0)
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];"
+                         ::"r"(SmemAddr(&bars->tmem_empty[buf])) : "memory");
         }
-        if (half == 1) asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+#pragma unroll
+        for (uint32_t q = 0; q < 8; ++q) {
+          *reinterpret_cast<uint4*>(slab + lane * kSlabCols + ((q ^ (lane & 15)) * 4)) =
+              make_uint4(ra[4 * q], ra[4 * q + 1], ra[4 * q + 2], ra[4 * q + 3]);
+          *reinterpret_cast<uint4*>(slab + lane * kSlabCols + (((q + 8) ^ (lane & 15)) * 4)) =
+              make_uint4(rb[4 * q], rb[4 * q + 1], rb[4 * q + 2], rb[4 * q + 3]);
+        }
         __syncwarp();
-        // The accumulator buffer is read out: hand it back before the slow part.
-        if (half == 1 && lane == 0)
-          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];"
-                       ::"r"(SmemAddr(&bars->tmem_empty[buf])) : "memory");
-        const uint32_t n = n0 + half * 128 + lane * 4;
+        const uint32_t n = n0 + col_half * 128 + pass * kSlabCols + cl * 4;
         if (n < ep.N) {   // N % 4 == 0: a float4 is all in or all out
           float4 scale = make_float4(ep.alpha, ep.alpha, ep.alpha, ep.alpha);
           if (ep.col_scale) scale = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n));
           float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
           if (ep.bias) bias = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
 #pragma unroll 4
-          for (uint32_t rr = 0; rr < rows; ++rr) {
-            const float4 acc = *reinterpret_cast<const float4*>(slab + rr * 128 + ((lane ^ rr) * 4));
+          for (uint32_t rr = sub; rr < rows; rr += 2) {
+            const float4 acc = *reinterpret_cast<const float4*>(slab + rr * kSlabCols + ((cl ^ (rr & 15)) * 4));
             const size_t at = static_cast<size_t>(row0 + rr) * ep.N + n;
             float4 v = make_float4(acc.x * scale.x, acc.y * scale.y, acc.z * scale.z, acc.w * scale.w);
             if (ep.addend) {
@@ -532,7 +555,7 @@ __global__ void WeightToBf16Kernel(const T* __restrict__ src, uint16_t* __restri
 
 size_t UmmaSmemBytes() { return kStages * kStageBytes + sizeof(Barriers) + 1024; }
 static size_t UmmaPersistentSmemBytes() {
-  return kPStages * kPStageBytes + 4 * kSlabBytes + sizeof(PBarriers) + 1024;
+  return kPStages * kPStageBytes + kPEpiWarps * kSlabBytes + sizeof(PBarriers) + 1024;
 }
 
 cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
@@ -558,7 +581,7 @@ cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
   const uint32_t ptiles_n = (ep.N + kPBlockN - 1) / kPBlockN;
   if (static_cast<uint64_t>(ptiles_n) * tiles_m > 2ull * sms) {
     // Enough tiles for every SM to amortise its set-up over several.
-    UmmaGemmPersistentKernel<<<sms, kThreads, psmem, s>>>(map_a, map_b, ep);
+    UmmaGemmPersistentKernel<<<sms, kPThreads, psmem, s>>>(map_a, map_b, ep);
     return cudaGetLastError();
   }
   dim3 grid(tiles_n, tiles_m);
