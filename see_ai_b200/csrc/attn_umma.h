@@ -19,6 +19,7 @@ struct AttnUmmaArgs {
   float* out;       // O / dQ / dK / dV, f32 [B*S, H*d]
   float* stats;     // f32 [B*H*S, 4]: score max, 1/denominator, delta, start
   DeviceStatus* status;
+  Shadow shadow;    // optional bf16 copy of `out` (cols = H*d) for the GEMM that reads it next
 };
 
 // f32 [B*S, H*d] (heads interleaved along the row) -> bf16 per (sequence, head):

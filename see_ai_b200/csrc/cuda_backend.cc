@@ -362,9 +362,82 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
   // CUDA graph must contain every conversion it depends on.
   umma::InvalidateRange(&umma_->ctx, 0, arena_bytes_);
   range_index_ = 0;
+  PlanShadows(program, begin, std::min(end, program.size()));
 }
 
-void CudaBackend::EndRange() {}
+void CudaBackend::EndRange() { shadow_plan_.clear(); }
+
+namespace {
+
+bool IsShadowProducer(uint16_t op) {
+  switch (op) {
+    case kAddEW: case kReluFwd: case kGeluFwd: case kSiluFwd: case kReluBwd: case kGeluBwd:
+    case kSiluBwd: case kLayerNormFwd: case kSoftmaxXEntBwd: case kSoftmaxXEntMaskedBwd:
+    case kAttnFwdTiled: case kAttnDQTiled: case kAttnDKTiled: case kAttnDVTiled:
+      return true;
+    default:
+      return false;
+  }
+}
+
+}  // namespace
+
+// For every relaxed GEMM of the range whose A operand is an arena tensor, finds
+// the instruction that last writes that tensor; if it writes exactly that
+// tensor and can emit a bf16 copy, marks it.  Only an optimisation hint: the
+// copy is published under the usual key and dies with any later write into the
+// range (InvalidateRange), so a missed or spurious mark cannot change a result.
+void CudaBackend::PlanShadows(std::span<const Instruction> program, size_t begin, size_t end) {
+  shadow_plan_.assign(end > begin ? end - begin : 0, ShadowPlan{});
+  if (!relaxed_allowed_ || end <= begin) return;
+  std::vector<Extents> ext(end - begin);
+  for (size_t i = begin; i < end; ++i)
+    if (!DescribeInstruction(program[i], arena_bytes_, rodata_bytes_, source_bytes_, &ext[i - begin]).empty())
+      ext[i - begin].count = 0;
+  for (size_t j = begin; j < end; ++j) {
+    const Instruction& g = program[j];
+    const uint16_t op = g.opcode;
+    const bool gemm = op == kGemmNN || op == kGemmNT || op == kGemmNNQ8 || op == kGemmNTQ8 ||
+                      op == kGemmNNBF16 || op == kGemmNTBF16;
+    if (!gemm || !(g.flags & kFlagRelaxed) || RefSpace(g.in[1]) == kArena ||
+        RefSpace(g.in[0]) != kArena)
+      continue;
+    const uint64_t M = g.out[0], N = g.out[1], K = g.out[2];
+    if (K % 8 != 0 || N % 4 != 0 || K < 64 || N < 16 || M < 64) continue;   // TryGemm's domain
+    ShadowPlan want;
+    want.want = true;
+    want.a_off = RefOffset(g.in[0]);
+    want.M = M;
+    want.K = K;
+    if (op == kGemmNTQ8 && (g.flags & kFlagQ8ColScale)) {
+      want.scale_ref = g.in[3];
+      want.scale_off = RefOffset(g.in[3]);
+    }
+    const uint64_t bytes = M * K * 4;
+    for (size_t i = j; i-- > begin;) {
+      const Extents& e = ext[i - begin];
+      bool touches = false, exact = false;
+      for (size_t x = 0; x < e.count; ++x) {
+        if (!e.e[x].write) continue;
+        if (e.e[x].off < want.a_off + bytes && want.a_off < e.e[x].off + e.e[x].bytes) {
+          touches = true;
+          exact = e.e[x].off == want.a_off && e.e[x].bytes == bytes;
+        }
+      }
+      if (!touches) continue;
+      ShadowPlan& slot = shadow_plan_[i - begin];
+      if (exact && IsShadowProducer(program[i].opcode) && !slot.want) slot = want;
+      break;
+    }
+  }
+}
+
+const k::Shadow* CudaBackend::ShadowFor(uint64_t out_ref, uint64_t elems) const {
+  if (!cur_shadow_.dst || RefSpace(out_ref) != kArena || RefOffset(out_ref) != cur_plan_.a_off ||
+      elems != cur_plan_.M * cur_plan_.K)
+    return nullptr;
+  return &cur_shadow_;
+}
 
 Status CudaBackend::Flush() {
   if (!d_arena_) return {};
@@ -430,6 +503,17 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
     cudaEventRecord(ev0, stream_);
   }
 
+  cur_shadow_ = k::Shadow{};
+  shadow_written_ = false;
+  if (range_index_ < shadow_plan_.size() && shadow_plan_[range_index_].want) {
+    cur_plan_ = shadow_plan_[range_index_];
+    if (uint16_t* buf = umma::ReserveShadow(&umma_->ctx, cur_plan_.M * cur_plan_.K)) {
+      cur_shadow_.dst = buf;
+      cur_shadow_.k_scale = cur_plan_.scale_ref == kNullRef ? nullptr : Rd(cur_plan_.scale_ref);
+      cur_shadow_.cols = cur_plan_.K;
+    }
+  }
+
   if (auto r = Dispatch(ins, params, ext); !r) return r;
   ++counters_.instructions;
 
@@ -451,6 +535,9 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
     umma::InvalidateRange(&umma_->ctx, e.off, e.bytes);
     if (coherence_ == Coherence::kStrict) MergeExtent(&device_dirty_, e.off, e.bytes);
   }
+  if (shadow_written_)   // after the instruction's own writes have invalidated the range
+    umma::CommitShadow(&umma_->ctx, cur_shadow_.dst, cur_plan_.a_off, cur_plan_.scale_off,
+                       cur_plan_.M, cur_plan_.K);
   if (auto e = cudaPeekAtLastError(); e != cudaSuccess) {
     cudaGetLastError();
     return std::unexpected(CudaErr(e, OpName(ins.opcode)));
@@ -589,16 +676,44 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
     case kGemmNN: case kGemmNT: case kGemmTN: case kGemmAccNN: case kGemmNNQ8: case kGemmNTQ8:
     case kGemmNNBF16: case kGemmNTBF16:
       return DispatchGemm(ins);
-    case kAddEW: k::AddEW(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s); launched(); break;
+    case kAddEW:
+      shadow_written_ = k::AddEW(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s,
+                                 ShadowFor(ins.in[2], ins.out[0]));
+      launched();
+      break;
     case kMulEW: k::MulEW(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s); launched(); break;
     case kAddBias:
       k::AddBias(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], ins.out[1], s); launched(); break;
-    case kReluFwd: k::ActFwd(kActRelu, Rd(ins.in[0]), Wr(ins.in[1]), ins.out[0], s); launched(); break;
-    case kGeluFwd: k::ActFwd(kActGelu, Rd(ins.in[0]), Wr(ins.in[1]), ins.out[0], s); launched(); break;
-    case kSiluFwd: k::ActFwd(kActSilu, Rd(ins.in[0]), Wr(ins.in[1]), ins.out[0], s); launched(); break;
-    case kReluBwd: k::ActBwd(kActRelu, Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s); launched(); break;
-    case kGeluBwd: k::ActBwd(kActGelu, Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s); launched(); break;
-    case kSiluBwd: k::ActBwd(kActSilu, Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s); launched(); break;
+    case kReluFwd:
+      shadow_written_ = k::ActFwd(kActRelu, Rd(ins.in[0]), Wr(ins.in[1]), ins.out[0], s,
+                                  ShadowFor(ins.in[1], ins.out[0]));
+      launched();
+      break;
+    case kGeluFwd:
+      shadow_written_ = k::ActFwd(kActGelu, Rd(ins.in[0]), Wr(ins.in[1]), ins.out[0], s,
+                                  ShadowFor(ins.in[1], ins.out[0]));
+      launched();
+      break;
+    case kSiluFwd:
+      shadow_written_ = k::ActFwd(kActSilu, Rd(ins.in[0]), Wr(ins.in[1]), ins.out[0], s,
+                                  ShadowFor(ins.in[1], ins.out[0]));
+      launched();
+      break;
+    case kReluBwd:
+      shadow_written_ = k::ActBwd(kActRelu, Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s,
+                                  ShadowFor(ins.in[2], ins.out[0]));
+      launched();
+      break;
+    case kGeluBwd:
+      shadow_written_ = k::ActBwd(kActGelu, Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s,
+                                  ShadowFor(ins.in[2], ins.out[0]));
+      launched();
+      break;
+    case kSiluBwd:
+      shadow_written_ = k::ActBwd(kActSilu, Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s,
+                                  ShadowFor(ins.in[2], ins.out[0]));
+      launched();
+      break;
     case kScale:
       k::Scale(Rd(ins.in[0]), Wr(ins.in[1]), BitsToF32(ins.in[2]), ins.out[0], s); launched(); break;
     case kFill: k::Fill(Wr(ins.in[0]), BitsToF32(ins.in[1]), ins.out[0], s); launched(); break;
@@ -619,8 +734,10 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
       launched();
       break;
     case kLayerNormFwd:
-      k::LayerNormFwd(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Wr(ins.in[3]), Wr(ins.out[1]),
-                      Wr(ins.out[2]), Hi32(ins.out[0]), Lo32(ins.out[0]), NormEpsOf(ins.imm), s);
+      shadow_written_ = k::LayerNormFwd(
+          Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Wr(ins.in[3]), Wr(ins.out[1]), Wr(ins.out[2]),
+          Hi32(ins.out[0]), Lo32(ins.out[0]), NormEpsOf(ins.imm), s,
+          ShadowFor(ins.in[3], Hi32(ins.out[0]) * Lo32(ins.out[0])));
       launched();
       break;
     case kLayerNormBwd:
@@ -645,8 +762,9 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
       launched(2);
       break;
     case kSoftmaxXEntBwd: case kSoftmaxXEntMaskedBwd:
-      k::SoftmaxXEntBwd(ins.opcode == kSoftmaxXEntMaskedBwd, Rd(ins.in[0]), Rd<int32_t>(ins.in[1]),
-                        Rd(ins.in[2]), Wr(ins.in[3]), ins.out[0], ins.out[1], d_count_, s);
+      shadow_written_ = k::SoftmaxXEntBwd(
+          ins.opcode == kSoftmaxXEntMaskedBwd, Rd(ins.in[0]), Rd<int32_t>(ins.in[1]), Rd(ins.in[2]),
+          Wr(ins.in[3]), ins.out[0], ins.out[1], d_count_, s, ShadowFor(ins.in[3], ins.out[0] * ins.out[1]));
       launched(ins.opcode == kSoftmaxXEntMaskedBwd ? 2 : 1);
       break;
     case kMseFwd:
@@ -740,11 +858,20 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
         umma::AttentionOperands op{Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), nullptr,
                                    RefOffset(ins.in[0]), RefOffset(ins.in[1]), RefOffset(ins.in[2]), 0,
                                    Wr(ins.out[0]), Wr(ins.in[3]),
-                                   Hi32(ins.out[1]), Lo32(ins.out[1]), Hi32(ins.out[2]), Lo32(ins.out[2])};
+                                   Hi32(ins.out[1]), Lo32(ins.out[1]), Hi32(ins.out[2]), Lo32(ins.out[2]),
+                                   k::Shadow{}};
+        const uint64_t elems = op.B * op.S * op.H * op.d;
+        const k::Shadow* sh = ShadowFor(ins.in[3], elems);
+        if (sh && sh->cols == op.H * op.d && k::ShadowUsable(sh, op.out, elems)) op.shadow = *sh;
         int n = 0;
         if (std::string e = umma::TryAttention(&umma_->ctx, ins.opcode, op, s, &n); !e.empty())
           return std::unexpected("cuda: " + e);
-        if (n > 0) { ++counters_.relaxed_executions; launched(n); break; }
+        if (n > 0) {
+          shadow_written_ = op.shadow.dst != nullptr;
+          ++counters_.relaxed_executions;
+          launched(n);
+          break;
+        }
       }
       k::AttnFwd(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Wr(ins.in[3]), nullptr, Wr(ins.out[0]),
                  Hi32(ins.out[1]), Lo32(ins.out[1]), Hi32(ins.out[2]), Lo32(ins.out[2]), nullptr, s);
@@ -788,11 +915,19 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
         umma::AttentionOperands op{Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Rd(ins.in[3]),
                                    RefOffset(ins.in[0]), RefOffset(ins.in[1]), RefOffset(ins.in[2]),
                                    RefOffset(ins.in[3]), Wr(ins.out[0]), Wr(ins.out[1]),
-                                   g.B, g.S, g.H, g.d};
+                                   g.B, g.S, g.H, g.d, k::Shadow{}};
+        const uint64_t elems = g.B * g.S * g.H * g.d;
+        const k::Shadow* sh = ShadowFor(ins.out[1], elems);
+        if (sh && sh->cols == g.H * g.d && k::ShadowUsable(sh, op.out, elems)) op.shadow = *sh;
         int n = 0;
         if (std::string e = umma::TryAttention(&umma_->ctx, ins.opcode, op, s, &n); !e.empty())
           return std::unexpected("cuda: " + e);
-        if (n > 0) { ++counters_.relaxed_executions; launched(n); break; }
+        if (n > 0) {
+          shadow_written_ = op.shadow.dst != nullptr;
+          ++counters_.relaxed_executions;
+          launched(n);
+          break;
+        }
       }
       if (g.d > 256 && ins.opcode != kAttnDQTiled)
         return std::unexpected("cuda: tiled attention backward supports head widths up to 256");

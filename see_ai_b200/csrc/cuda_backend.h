@@ -205,6 +205,20 @@ class CudaBackend {
   std::vector<ProfileRecord> pending_profile_;
   uint32_t range_index_ = 0;
 
+  // Producer-side bf16 conversion (k::Shadow): for each instruction of the
+  // current range, whether its output is the A operand of a later relaxed GEMM,
+  // and under which key that GEMM will look the copy up.
+  struct ShadowPlan {
+    bool want = false;
+    uint64_t a_off = 0, M = 0, K = 0, scale_off = ~0ull, scale_ref = kNullRef;
+  };
+  void PlanShadows(std::span<const Instruction> program, size_t begin, size_t end);
+  const k::Shadow* ShadowFor(uint64_t out_ref, uint64_t elems) const;
+  std::vector<ShadowPlan> shadow_plan_;
+  ShadowPlan cur_plan_;
+  k::Shadow cur_shadow_;
+  bool shadow_written_ = false;
+
   Counters counters_;
   struct UmmaState;
   std::unique_ptr<UmmaState> umma_;

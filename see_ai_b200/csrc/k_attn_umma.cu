@@ -26,6 +26,7 @@
 
 #include "attn_umma.h"
 #include "kernels.h"
+#include "shadow.cuh"
 #include "umma_device.cuh"
 
 namespace see::k {
@@ -171,21 +172,39 @@ __device__ __forceinline__ uint8_t* AlignSmem(uint8_t* raw) {
   return raw + ((1024u - (SmemAddr(raw) & 1023u)) & 1023u);
 }
 
-// Stores this thread's output row (D accumulator columns starting at t_out) times `scale`.
+// Stores a warp's 32 output rows (D accumulator columns starting at t_out, one row per
+// thread, times the thread's `scale`).  The rows turn through a per-warp slab of shared
+// memory (the operand tiles are idle by now) so that HBM sees whole rows: 16-byte chunks
+// XOR-swizzled with the row, conflict-free both for the row-per-thread writes and the
+// row-per-(half-)warp reads.  `out0` points at (first row, this head's first column) of
+// the [B*S, H*d] tensor, `flat0` is that element's index (for the bf16 shadow), `col0`
+// its column, `rows_live` how many of the 32 rows exist.
 template <int D>
-__device__ __forceinline__ void StoreOutRow(uint32_t t_out, float* o, bool live, float scale) {
+__device__ __forceinline__ void StoreOutRows(uint32_t t_out, float* slab, uint32_t lane, float scale,
+                                             float* out0, size_t pitch, uint32_t rows_live,
+                                             const Shadow& sh, size_t flat0, uint32_t col0) {
+  constexpr uint32_t kChunks = D / 4;          // 16-byte chunks per row: 16 or 32
+  constexpr uint32_t kRowsPerPass = 32 / kChunks;
 #pragma unroll 1
   for (uint32_t c0 = 0; c0 < D; c0 += 32) {
     uint32_t r[32];
-    TmemLoad32(t_out + c0, r);   // warp-collective: every thread loads, live rows store
+    TmemLoad32(t_out + c0, r);
     TmemWaitLd();
-    if (live) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        *reinterpret_cast<float4*>(o + c0 + j) =
-            make_float4(__uint_as_float(r[j]) * scale, __uint_as_float(r[j + 1]) * scale,
-                        __uint_as_float(r[j + 2]) * scale, __uint_as_float(r[j + 3]) * scale);
+    for (uint32_t q = 0; q < 8; ++q) {
+      const uint32_t chunk = ((c0 >> 2) + q) ^ (lane & (kChunks - 1));
+      *reinterpret_cast<float4*>(slab + lane * D + chunk * 4) =
+          make_float4(__uint_as_float(r[4 * q]) * scale, __uint_as_float(r[4 * q + 1]) * scale,
+                      __uint_as_float(r[4 * q + 2]) * scale, __uint_as_float(r[4 * q + 3]) * scale);
     }
+  }
+  __syncwarp();
+  const uint32_t sub = lane / kChunks, cl = lane % kChunks;
+#pragma unroll 4
+  for (uint32_t rr = sub; rr < rows_live; rr += kRowsPerPass) {
+    const float4 v = *reinterpret_cast<const float4*>(slab + rr * D + ((cl ^ (rr & (kChunks - 1))) * 4));
+    *reinterpret_cast<float4*>(out0 + rr * pitch + cl * 4) = v;
+    if (sh.dst) ShadowStore4(sh, (flat0 + rr * pitch + cl * 4) / 4, col0 + cl * 4, v);
   }
 }
 
@@ -315,9 +334,12 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   } else {
     const bool live = row < a.S;
     const size_t HD = static_cast<size_t>(a.H) * D;
-    float* o = a.out + (static_cast<size_t>(b) * a.S + (live ? row : 0)) * HD + static_cast<size_t>(h) * D;
+    const uint32_t row0w = it * kTile + warp * 32;
+    const uint32_t rows_live = row0w < a.S ? (a.S - row0w < 32 ? a.S - row0w : 32) : 0;
+    const size_t flat0 = (static_cast<size_t>(b) * a.S + row0w) * HD + static_cast<size_t>(h) * D;
     const float inv_l = 1.0f / l;
-    StoreOutRow<D>(t_o, o, live, inv_l);
+    StoreOutRows<D>(t_o, reinterpret_cast<float*>(smem) + warp * 32 * D, tid & 31, inv_l,
+                    a.out + flat0, HD, rows_live, a.shadow, flat0, h * D);
     if (live) {
       float* st = a.stats + (static_cast<size_t>(bh) * a.S + row) * kAttnStatsWidth;
       *reinterpret_cast<float4*>(st) = make_float4(m, inv_l, 0.0f, 0.0f);
@@ -460,8 +482,11 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     DrainDelay();
   } else {
     const size_t HD = static_cast<size_t>(a.H) * D;
-    float* o = a.out + (static_cast<size_t>(b) * a.S + (live ? row : 0)) * HD + static_cast<size_t>(h) * D;
-    StoreOutRow<D>(t_lane + 128, o, live, 1.0f);
+    const uint32_t row0w = it * kTile + warp * 32;
+    const uint32_t rows_live = row0w < a.S ? (a.S - row0w < 32 ? a.S - row0w : 32) : 0;
+    const size_t flat0 = (static_cast<size_t>(b) * a.S + row0w) * HD + static_cast<size_t>(h) * D;
+    StoreOutRows<D>(t_lane + 128, reinterpret_cast<float*>(smem) + warp * 32 * D, tid & 31, 1.0f,
+                    a.out + flat0, HD, rows_live, a.shadow, flat0, h * D);
     if (live) st_row[2] = delta;
   }
   TcFenceBefore();
@@ -611,10 +636,12 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     if (tid == 0) a.status->wait_timeout = 1;
     DrainDelay();
   } else {
-    const bool live = key < a.S;
     const size_t HD = static_cast<size_t>(a.H) * D;
-    float* o = a.out + (static_cast<size_t>(b) * a.S + (live ? key : 0)) * HD + static_cast<size_t>(h) * D;
-    StoreOutRow<D>(t_lane + kOutCol, o, live, 1.0f);
+    const uint32_t row0w = jt * kTile + warp * 32;
+    const uint32_t rows_live = row0w < a.S ? (a.S - row0w < 32 ? a.S - row0w : 32) : 0;
+    const size_t flat0 = (static_cast<size_t>(b) * a.S + row0w) * HD + static_cast<size_t>(h) * D;
+    StoreOutRows<D>(t_lane + kOutCol, reinterpret_cast<float*>(smem) + warp * 32 * D, tid & 31, 1.0f,
+                    a.out + flat0, HD, rows_live, a.shadow, flat0, h * D);
   }
   TcFenceBefore();
   __syncthreads();

@@ -6,6 +6,7 @@
 // are bit-identical to the CPU executor's; tanh / exp based activations agree
 // to libm-vs-CUDA-libm differences (a few ulp).
 #include "kernels.h"
+#include "shadow.cuh"
 
 namespace see::k {
 
@@ -52,17 +53,20 @@ __device__ __forceinline__ float SiluGrad(float dy, float x) {
 
 // ---- generic maps -------------------------------------------------------------
 template <typename F>
-__global__ void Map1(const float* __restrict__ x, float* __restrict__ out, size_t n, bool vec, F f) {
+__global__ void Map1(const float* __restrict__ x, float* __restrict__ out, size_t n, bool vec, F f,
+                     Shadow sh) {
   const size_t tid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   if (vec) {
     const size_t n4 = n / 4;
     const float4* x4 = reinterpret_cast<const float4*>(x);
     float4* o4 = reinterpret_cast<float4*>(out);
+    ShadowCursor cur(sh, tid, stride);
     for (size_t i = tid; i < n4; i += stride) {
       float4 a = x4[i];
       a.x = f(a.x); a.y = f(a.y); a.z = f(a.z); a.w = f(a.w);
       o4[i] = a;
+      if (sh.dst) { ShadowStore4(sh, i, cur.col(), a); cur.advance(); }
     }
     for (size_t i = n4 * 4 + tid; i < n; i += stride) out[i] = f(x[i]);
   } else {
@@ -72,7 +76,7 @@ __global__ void Map1(const float* __restrict__ x, float* __restrict__ out, size_
 
 // out may alias x or y exactly (in-place accumulate); never partially.
 template <typename F>
-__global__ void Map2(const float* x, const float* y, float* out, size_t n, bool vec, F f) {
+__global__ void Map2(const float* x, const float* y, float* out, size_t n, bool vec, F f, Shadow sh) {
   const size_t tid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   if (vec) {
@@ -80,11 +84,13 @@ __global__ void Map2(const float* x, const float* y, float* out, size_t n, bool 
     const float4* x4 = reinterpret_cast<const float4*>(x);
     const float4* y4 = reinterpret_cast<const float4*>(y);
     float4* o4 = reinterpret_cast<float4*>(out);
+    ShadowCursor cur(sh, tid, stride);
     for (size_t i = tid; i < n4; i += stride) {
       const float4 a = x4[i], b = y4[i];
       float4 r;
       r.x = f(a.x, b.x); r.y = f(a.y, b.y); r.z = f(a.z, b.z); r.w = f(a.w, b.w);
       o4[i] = r;
+      if (sh.dst) { ShadowStore4(sh, i, cur.col(), r); cur.advance(); }
     }
     for (size_t i = n4 * 4 + tid; i < n; i += stride) out[i] = f(x[i], y[i]);
   } else {
@@ -104,16 +110,24 @@ struct GeluBwdF { __device__ float operator()(float dy, float x) const { return 
 struct SiluBwdF { __device__ float operator()(float dy, float x) const { return SiluGrad(dy, x); } };
 
 template <typename F>
-void LaunchMap1(const float* x, float* out, size_t n, cudaStream_t s, F f) {
-  if (n == 0) return;
+bool LaunchMap1(const float* x, float* out, size_t n, cudaStream_t s, F f,
+                const Shadow* shadow = nullptr) {
+  if (n == 0) return false;
   const bool vec = Aligned16(x) && Aligned16(out);
-  Map1<<<BlocksFor(vec ? (n + 3) / 4 : n), kThreads, 0, s>>>(x, out, n, vec, f);
+  const bool shadowed = vec && ShadowUsable(shadow, out, n);
+  Map1<<<BlocksFor(vec ? (n + 3) / 4 : n), kThreads, 0, s>>>(x, out, n, vec, f,
+                                                              shadowed ? *shadow : Shadow{});
+  return shadowed;
 }
 template <typename F>
-void LaunchMap2(const float* x, const float* y, float* out, size_t n, cudaStream_t s, F f) {
-  if (n == 0) return;
+bool LaunchMap2(const float* x, const float* y, float* out, size_t n, cudaStream_t s, F f,
+                const Shadow* shadow = nullptr) {
+  if (n == 0) return false;
   const bool vec = Aligned16(x) && Aligned16(y) && Aligned16(out);
-  Map2<<<BlocksFor(vec ? (n + 3) / 4 : n), kThreads, 0, s>>>(x, y, out, n, vec, f);
+  const bool shadowed = vec && ShadowUsable(shadow, out, n);
+  Map2<<<BlocksFor(vec ? (n + 3) / 4 : n), kThreads, 0, s>>>(x, y, out, n, vec, f,
+                                                              shadowed ? *shadow : Shadow{});
+  return shadowed;
 }
 
 __global__ void FillKernel(float* __restrict__ dst, float value, size_t n, bool vec) {
@@ -331,8 +345,9 @@ __global__ void ToBf16Kernel(const float* __restrict__ x, uint16_t* __restrict__
 
 }  // namespace
 
-void AddEW(const float* x, const float* y, float* out, size_t n, cudaStream_t s) {
-  LaunchMap2(x, y, out, n, s, AddF{});
+bool AddEW(const float* x, const float* y, float* out, size_t n, cudaStream_t s,
+           const Shadow* shadow) {
+  return LaunchMap2(x, y, out, n, s, AddF{}, shadow);
 }
 void MulEW(const float* x, const float* y, float* out, size_t n, cudaStream_t s) {
   LaunchMap2(x, y, out, n, s, MulF{});
@@ -358,21 +373,24 @@ void AddBias(const float* x, const float* b, float* out, size_t rows, size_t col
   AddBiasKernel<<<BlocksFor(vec ? rows * cols / 4 : rows * cols), kThreads, 0, s>>>(
       x, b, out, rows, cols, vec);
 }
-void ActFwd(Act act, const float* x, float* out, size_t n, cudaStream_t s) {
+bool ActFwd(Act act, const float* x, float* out, size_t n, cudaStream_t s, const Shadow* shadow) {
   switch (act) {
-    case kActRelu: LaunchMap1(x, out, n, s, ReluF{}); break;
-    case kActGelu: LaunchMap1(x, out, n, s, GeluF{}); break;
-    case kActSilu: LaunchMap1(x, out, n, s, SiluF{}); break;
-    case kActNone: LaunchMap1(x, out, n, s, IdF{}); break;
+    case kActRelu: return LaunchMap1(x, out, n, s, ReluF{}, shadow);
+    case kActGelu: return LaunchMap1(x, out, n, s, GeluF{}, shadow);
+    case kActSilu: return LaunchMap1(x, out, n, s, SiluF{}, shadow);
+    case kActNone: return LaunchMap1(x, out, n, s, IdF{}, shadow);
   }
+  return false;
 }
-void ActBwd(Act act, const float* dy, const float* x, float* dx, size_t n, cudaStream_t s) {
+bool ActBwd(Act act, const float* dy, const float* x, float* dx, size_t n, cudaStream_t s,
+            const Shadow* shadow) {
   switch (act) {
-    case kActRelu: LaunchMap2(dy, x, dx, n, s, ReluBwdF{}); break;
-    case kActGelu: LaunchMap2(dy, x, dx, n, s, GeluBwdF{}); break;
-    case kActSilu: LaunchMap2(dy, x, dx, n, s, SiluBwdF{}); break;
+    case kActRelu: return LaunchMap2(dy, x, dx, n, s, ReluBwdF{}, shadow);
+    case kActGelu: return LaunchMap2(dy, x, dx, n, s, GeluBwdF{}, shadow);
+    case kActSilu: return LaunchMap2(dy, x, dx, n, s, SiluBwdF{}, shadow);
     case kActNone: break;
   }
+  return false;
 }
 void FusedMap(const float* x, const float* o1, const float* o2, float* out, size_t n,
               uint32_t stages, float imm0, float imm1, cudaStream_t s) {

@@ -8,6 +8,7 @@
 // folded in chunk order, so the loss does not depend on the launch geometry.
 // Integer results (the masked forms' target count) are exact.
 #include "kernels.h"
+#include "shadow.cuh"
 
 namespace see::k {
 
@@ -282,7 +283,7 @@ __global__ void XEntBwdKernel(const float* __restrict__ probs, const int32_t* __
 __global__ void XEntBwdRowsKernel(const float* __restrict__ probs, const int32_t* __restrict__ labels,
                                   const float* __restrict__ seed, float* __restrict__ dlogits,
                                   size_t N, size_t C, bool masked,
-                                  const unsigned long long* __restrict__ count) {
+                                  const unsigned long long* __restrict__ count, Shadow sh) {
   float scale;
   if (masked) {
     const unsigned long long T = *count;
@@ -312,6 +313,7 @@ __global__ void XEntBwdRowsKernel(const float* __restrict__ probs, const int32_t
         }
       }
       drow[c4] = v;
+      if (sh.dst) ShadowStore4(sh, n * C4 + c4, static_cast<uint32_t>(c4 * 4), v);
     }
   }
 }
@@ -437,21 +439,24 @@ void SoftmaxXEntFwd(bool masked, const float* logits, const int32_t* labels, flo
                                          count_scratch);
 }
 
-void SoftmaxXEntBwd(bool masked, const float* probs, const int32_t* labels, const float* seed,
+bool SoftmaxXEntBwd(bool masked, const float* probs, const int32_t* labels, const float* seed,
                     float* dlogits, size_t N, size_t C, unsigned long long* count_scratch,
-                    cudaStream_t s) {
-  if (N * C == 0) return;
+                    cudaStream_t s, const Shadow* shadow) {
+  if (N * C == 0) return false;
   if (masked) CountTargetsKernel<<<1, 256, 0, s>>>(labels, N, count_scratch);
   if (C >= 1024 && (C & 3) == 0 &&
       ((reinterpret_cast<uintptr_t>(probs) | reinterpret_cast<uintptr_t>(dlogits)) & 15) == 0) {
     const size_t per_row = (C / 4 + 255) / 256;
     const dim3 grid(static_cast<unsigned>(per_row < 64 ? per_row : 64),
                     static_cast<unsigned>(N < 65535 ? N : 65535));
-    XEntBwdRowsKernel<<<grid, 256, 0, s>>>(probs, labels, seed, dlogits, N, C, masked, count_scratch);
-    return;
+    const bool shadowed = ShadowUsable(shadow, dlogits, N * C) && shadow->cols == C;
+    XEntBwdRowsKernel<<<grid, 256, 0, s>>>(probs, labels, seed, dlogits, N, C, masked, count_scratch,
+                                           shadowed ? *shadow : Shadow{});
+    return shadowed;
   }
   XEntBwdKernel<<<GridFor(N * C, 256, 148 * 8), 256, 0, s>>>(probs, labels, seed, dlogits, N, C,
                                                             masked, count_scratch);
+  return false;
 }
 
 void MseFwd(const float* pred, const float* target, float* loss, size_t n, double* scratch,

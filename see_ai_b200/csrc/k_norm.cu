@@ -8,6 +8,7 @@
 // survives the cast to float.  Compiled with -fmad=false so the output
 // expressions round like the reference's.
 #include "kernels.h"
+#include "shadow.cuh"
 
 namespace see::k {
 
@@ -24,7 +25,7 @@ __device__ __forceinline__ double WarpSum(double v) {
 __global__ void LayerNormFwdKernel(const float* __restrict__ x, const float* __restrict__ gamma,
                                    const float* __restrict__ beta, float* __restrict__ y,
                                    float* __restrict__ mean, float* __restrict__ rstd,
-                                   size_t rows, size_t cols, float eps) {
+                                   size_t rows, size_t cols, float eps, Shadow sh) {
   const size_t r = blockIdx.x * static_cast<size_t>(kWarpsPerBlock) + threadIdx.x / 32;
   const int lane = threadIdx.x & 31;
   if (r >= rows) return;
@@ -45,7 +46,12 @@ __global__ void LayerNormFwdKernel(const float* __restrict__ x, const float* __r
     rstd[r] = rs;
   }
   float* yr = y + r * cols;
-  for (size_t c = lane; c < cols; c += 32) yr[c] = (xr[c] - mu) * rs * gamma[c] + beta[c];
+  for (size_t c = lane; c < cols; c += 32) {
+    const float v = (xr[c] - mu) * rs * gamma[c] + beta[c];
+    yr[c] = v;
+    if (sh.dst)   // the bf16 copy for the GEMM that reads y next
+      sh.dst[r * cols + c] = static_cast<uint16_t>(ShadowBf16(sh.k_scale ? v * sh.k_scale[c] : v));
+  }
 }
 
 __global__ void LayerNormBwdKernel(const float* __restrict__ dy, const float* __restrict__ x,
@@ -121,11 +127,14 @@ inline unsigned RowBlocks(size_t rows) {
 
 }  // namespace
 
-void LayerNormFwd(const float* x, const float* gamma, const float* beta, float* y, float* mean,
-                  float* rstd, size_t rows, size_t cols, float eps, cudaStream_t s) {
-  if (rows == 0) return;
-  LayerNormFwdKernel<<<RowBlocks(rows), kWarpsPerBlock * 32, 0, s>>>(x, gamma, beta, y, mean, rstd,
-                                                                     rows, cols, eps);
+bool LayerNormFwd(const float* x, const float* gamma, const float* beta, float* y, float* mean,
+                  float* rstd, size_t rows, size_t cols, float eps, cudaStream_t s,
+                  const Shadow* shadow) {
+  if (rows == 0) return false;
+  const bool shadowed = shadow && shadow->dst && shadow->cols == cols;
+  LayerNormFwdKernel<<<RowBlocks(rows), kWarpsPerBlock * 32, 0, s>>>(
+      x, gamma, beta, y, mean, rstd, rows, cols, eps, shadowed ? *shadow : Shadow{});
+  return shadowed;
 }
 void LayerNormBwd(const float* dy, const float* x, const float* gamma, const float* mean,
                   const float* rstd, float* dx, size_t rows, size_t cols, cudaStream_t s) {

@@ -23,16 +23,38 @@ struct DeviceStatus {
   int pad[2];
 };
 
+// An optional second output of a producer kernel: a bf16 copy of the tensor it
+// writes, laid out [rows][cols] like the tensor, for the tensor-core GEMM that
+// reads the tensor next (it would otherwise re-read the f32 values just to
+// round them).  dst[i] = bf16_rne(v[i] * (k_scale ? k_scale[i % cols] : 1)) —
+// the rounding the GEMM's own conversion pass applies.  Producers honour it on
+// their 16-byte vector paths only (ShadowUsable), and ignore it otherwise.
+struct Shadow {
+  uint16_t* dst = nullptr;
+  const float* k_scale = nullptr;   // per-column factor of the consumer (or null)
+  size_t cols = 0;
+};
+inline bool ShadowUsable(const Shadow* sh, const void* out, size_t n) {
+  return sh && sh->dst && sh->cols != 0 && sh->cols % 4 == 0 && n % sh->cols == 0 &&
+         (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+         (reinterpret_cast<uintptr_t>(sh->dst) & 7) == 0 &&
+         (reinterpret_cast<uintptr_t>(sh->k_scale) & 15) == 0;
+}
+
 // ---- elementwise / broadcast / gather -------------------------------------
-void AddEW(const float* x, const float* y, float* out, size_t n, cudaStream_t s);
+// Launchers that take a Shadow return true when they wrote it.
+bool AddEW(const float* x, const float* y, float* out, size_t n, cudaStream_t s,
+           const Shadow* shadow = nullptr);
 void MulEW(const float* x, const float* y, float* out, size_t n, cudaStream_t s);
 void AddBias(const float* x, const float* b, float* out, size_t rows, size_t cols, cudaStream_t s);
 void Accumulate(float* dst, const float* src, size_t n, cudaStream_t s);
 void Scale(const float* x, float* out, float alpha, size_t n, cudaStream_t s);
 void Fill(float* dst, float value, size_t n, cudaStream_t s);
 void Copy(const float* src, float* dst, size_t n, cudaStream_t s);
-void ActFwd(Act act, const float* x, float* out, size_t n, cudaStream_t s);
-void ActBwd(Act act, const float* dy, const float* x, float* dx, size_t n, cudaStream_t s);
+bool ActFwd(Act act, const float* x, float* out, size_t n, cudaStream_t s,
+            const Shadow* shadow = nullptr);
+bool ActBwd(Act act, const float* dy, const float* x, float* dx, size_t n, cudaStream_t s,
+            const Shadow* shadow = nullptr);
 void FusedMap(const float* x, const float* o1, const float* o2, float* out, size_t n,
               uint32_t stages, float imm0, float imm1, cudaStream_t s);
 void EmbedFwd(const int32_t* tokens, const float* table, float* out, size_t rows, size_t dim,
@@ -49,8 +71,9 @@ void ToBf16(const float* x, uint16_t* out, size_t rows, size_t cols, const float
             cudaStream_t s);
 
 // ---- normalization ----------------------------------------------------------
-void LayerNormFwd(const float* x, const float* gamma, const float* beta, float* y, float* mean,
-                  float* rstd, size_t rows, size_t cols, float eps, cudaStream_t s);
+bool LayerNormFwd(const float* x, const float* gamma, const float* beta, float* y, float* mean,
+                  float* rstd, size_t rows, size_t cols, float eps, cudaStream_t s,
+                  const Shadow* shadow = nullptr);
 void LayerNormBwd(const float* dy, const float* x, const float* gamma, const float* mean,
                   const float* rstd, float* dx, size_t rows, size_t cols, cudaStream_t s);
 void RmsNormFwd(const float* x, const float* gamma, float* y, float* rstd, size_t rows,
@@ -64,9 +87,9 @@ void RmsNormBwd(const float* dy, const float* x, const float* gamma, const float
 void SoftmaxXEntFwd(bool masked, const float* logits, const int32_t* labels, float* loss,
                     float* probs, size_t N, size_t C, double* row_scratch,
                     unsigned long long* count_scratch, cudaStream_t s);
-void SoftmaxXEntBwd(bool masked, const float* probs, const int32_t* labels, const float* seed,
+bool SoftmaxXEntBwd(bool masked, const float* probs, const int32_t* labels, const float* seed,
                     float* dlogits, size_t N, size_t C, unsigned long long* count_scratch,
-                    cudaStream_t s);
+                    cudaStream_t s, const Shadow* shadow = nullptr);
 void MseFwd(const float* pred, const float* target, float* loss, size_t n, double* scratch,
             cudaStream_t s);
 void MseBwd(const float* pred, const float* target, const float* seed, float* dpred, size_t n,

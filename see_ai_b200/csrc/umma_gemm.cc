@@ -34,7 +34,7 @@ struct ActCopy {   // a bf16 copy of an arena activation [M, K]
   uint64_t last_use = 0;
 };
 
-constexpr int kActSlots = 4;
+constexpr int kActSlots = 8;
 
 // Packed bf16 copies of one attention operand (a Q, K, V or dO activation), in
 // both layouts the kernels read: rows [B*H][S][d] and cols [B*H][d][S].  Made
@@ -290,6 +290,33 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
   return {};
 }
 
+uint16_t* ReserveShadow(Context* ctx, uint64_t elems) {
+  Impl* impl = ctx->impl;
+  if (!impl) return nullptr;
+  ActCopy* slot = nullptr;
+  for (auto& c : impl->acts) {
+    if (c.capacity < elems || !c.buf) continue;
+    if (!c.valid) { slot = &c; break; }
+    if (!slot || c.last_use < slot->last_use) slot = &c;
+  }
+  if (!slot) return nullptr;
+  slot->valid = false;
+  slot->last_use = ++impl->tick;   // not the next victim while its producer runs
+  return slot->buf;
+}
+
+void CommitShadow(Context* ctx, uint16_t* buf, uint64_t a_off, uint64_t a_scale_off, uint64_t M,
+                  uint64_t K) {
+  Impl* impl = ctx->impl;
+  if (!impl || !buf) return;
+  for (auto& c : impl->acts) {
+    if (c.buf != buf) continue;
+    c.a_off = a_off; c.scale_off = a_scale_off; c.M = M; c.K = K;
+    c.valid = true;
+    c.last_use = ++impl->tick;
+  }
+}
+
 namespace {
 
 bool EncodeHeads(Impl* impl, CUtensorMap* map, const void* base, uint64_t inner, uint64_t mid,
@@ -370,6 +397,7 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
   a.out = op.out;
   a.stats = op.stats;
   a.status = impl->status;
+  a.shadow = op.shadow;
   cudaError_t e = cudaSuccess;
   if (fwd) e = k::AttnFwdUmma(mr[Q], mh[K], mc[V], a, stream);
   if (dq) e = k::AttnDQUmma(mr[Q], mr[DO], mh[K], mh[V], mc[K], a, stream);

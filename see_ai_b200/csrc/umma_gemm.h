@@ -41,6 +41,17 @@ void PlanRange(Context* ctx, const Instruction* program, size_t begin, size_t en
 std::string TryGemm(Context* ctx, const k::GemmArgs& args, int b_space, uint64_t b_off,
                     uint64_t a_off, uint64_t a_scale_off, cudaStream_t stream, int* launches);
 
+// Producer-side conversion: the instruction that writes a tensor a relaxed GEMM
+// reads next can emit the bf16 copy itself (k::Shadow) and spare the GEMM's
+// conversion pass the f32 re-read.  ReserveShadow picks an activation slot and
+// returns its buffer (null when none can hold M x K); after the producing
+// instruction's own write extents have gone through InvalidateRange, CommitShadow
+// publishes the slot under the key TryGemm looks up (arena offset, scale offset,
+// M, K).  A reservation that is not committed is simply reused later.
+uint16_t* ReserveShadow(Context* ctx, uint64_t elems);
+void CommitShadow(Context* ctx, uint16_t* buf, uint64_t a_off, uint64_t a_scale_off, uint64_t M,
+                  uint64_t K);
+
 // Runs one tiled attention opcode (kAttnFwdTiled / kAttnDQTiled / kAttnDKTiled /
 // kAttnDVTiled) on the tensor cores when the geometry is inside the kernels'
 // domain (head width 64 or 128, sequence length a multiple of 8).  Operands are
@@ -52,6 +63,7 @@ struct AttentionOperands {
   uint64_t q_off, k_off, v_off, dout_off;
   float* stats; float* out;
   uint64_t B, S, H, d;
+  k::Shadow shadow;   // optional bf16 copy of `out`
 };
 std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands& op,
                          cudaStream_t stream, int* launches);
