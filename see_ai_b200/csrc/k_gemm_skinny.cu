@@ -35,46 +35,59 @@ __device__ __forceinline__ void QuadStep(float (&c)[4], float a0, float a1, floa
 }
 
 // ---- reduce: C[M, N = 4G] = A[M, K] * W, K long --------------------------------------
-// A warp owns 2 * 32 / G rows; lane = (row pair, column group g) holds the
-// outputs C[row, 4g .. 4g+3] of two rows, so every 16 bytes of W read from shared
-// memory feed two rows.  The lanes of a row read the same 16 bytes of A (one
-// broadcast load); a row is consumed a 128-byte line (32 k) at a time, eight
-// loads in flight per row.  W is staged in shared memory kChunkK reduction steps
-// at a time, in the layout it has in memory: [k][N] for the quad order (W is
-// [K, N]); [n][k] for the lane order (W is [N, K]), where row n starts at
-// n * kWnStride + 4 * (n / 4) floats so that the four column groups of a warp
-// read four different bank groups.
+// A warp owns R * 32 / G rows; lane = (row slot, column group g) holds the outputs
+// C[row, 4g .. 4g+3] of R rows, so every 16 bytes of W read from shared memory
+// feed R rows.  The lanes of a row read the same 16 bytes of A (one broadcast
+// load).  A row is consumed 16 k at a time from one of two register buffers, the
+// next 16 k already in flight while these are multiplied.  All of W sits in
+// shared memory (dynamic, K <= kReduceMaxK), in the layout it has in memory:
+// [k][N] for the quad order (W is [K, N]); [n][k] for the lane order (W is
+// [N, K]), where row n starts at n * (K + 16) + 4 * (n / 4) floats so that the
+// four column groups of a warp read four different bank groups.
 constexpr int kReduceThreads = 256;
-constexpr int kReduceRows = 2;   // rows per thread
-constexpr int kChunkK = 512;
-constexpr int kWnStride = kChunkK + 16;
+constexpr size_t kReduceMaxK = 3072;
 
-__device__ __forceinline__ int WnRow(int n) { return n * kWnStride + 4 * (n >> 2); }
-
-template <int G, bool kLane>
+template <int G, bool kLane, int R, int Q>
 __global__ void __launch_bounds__(kReduceThreads) ReduceKernel(Params p) {
   constexpr int N = 4 * G;
-  constexpr int kRowsPerWarp = 32 / G;  // per row slot; a warp covers kReduceRows of these
-  constexpr int kRowsPerBlock = kReduceRows * kRowsPerWarp * (kReduceThreads / 32);
-  __shared__ __align__(16) float Wsm[N * kWnStride];
+  constexpr int kRowsPerWarp = 32 / G;  // per row slot; a warp covers R of these
+  constexpr int kRowsPerBlock = R * kRowsPerWarp * (kReduceThreads / 32);
+  extern __shared__ __align__(16) float Wsm[];
+  const int K = static_cast<int>(p.K);
+  const int wn_stride = K + 16;
+  auto wn_row = [&](int n) { return n * wn_stride + 4 * (n >> 2); };
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane % G;
   const float* B = static_cast<const float*>(p.B);
-  size_t row[kReduceRows];
-  bool live[kReduceRows];
-  const float* xrow[kReduceRows];
+  size_t row[R];
+  bool live[R];
+  const float* xrow[R];
 #pragma unroll
-  for (int r = 0; r < kReduceRows; ++r) {
-    row[r] = static_cast<size_t>(blockIdx.x) * kRowsPerBlock +
-             (warp * kReduceRows + r) * kRowsPerWarp + lane / G;
+  for (int r = 0; r < R; ++r) {
+    row[r] = static_cast<size_t>(blockIdx.x) * kRowsPerBlock + (warp * R + r) * kRowsPerWarp + lane / G;
     live[r] = row[r] < p.M;
     xrow[r] = p.A + (live[r] ? row[r] : 0) * p.K;
   }
 
-  float c[kReduceRows][4];       // quad order
-  float acc[kReduceRows][4][8];  // lane order
+  if (kLane) {
+    const int per_row = K / 4;
+    for (int idx = threadIdx.x; idx < N * per_row; idx += kReduceThreads) {
+      const int n = idx / per_row, kq = idx % per_row;
+      *reinterpret_cast<float4*>(&Wsm[wn_row(n) + 4 * kq]) =
+          *reinterpret_cast<const float4*>(B + static_cast<size_t>(n) * p.K + 4 * kq);
+    }
+  } else {
+    const float4* src = reinterpret_cast<const float4*>(B);
+    for (int idx = threadIdx.x; idx < K * G; idx += kReduceThreads)
+      reinterpret_cast<float4*>(Wsm)[idx] = src[idx];
+  }
+  __syncthreads();
+  if (!live[0]) return;  // rows ascend with r: a dead first row means a dead thread
+
+  float c[R][4];       // quad order
+  float acc[R][4][8];  // lane order
 #pragma unroll
-  for (int r = 0; r < kReduceRows; ++r)
+  for (int r = 0; r < R; ++r)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       c[r][j] = 0.0f;
@@ -82,65 +95,59 @@ __global__ void __launch_bounds__(kReduceThreads) ReduceKernel(Params p) {
       for (int l = 0; l < 8; ++l) acc[r][j][l] = 0.0f;
     }
 
-  for (size_t kc0 = 0; kc0 < p.K; kc0 += kChunkK) {
-    const int kc = p.K - kc0 < static_cast<size_t>(kChunkK) ? static_cast<int>(p.K - kc0) : kChunkK;
-    __syncthreads();
-    if (kLane) {
-      const int per_row = kc / 4;
-      for (int idx = threadIdx.x; idx < N * per_row; idx += kReduceThreads) {
-        const int n = idx / per_row, kq = idx % per_row;
-        *reinterpret_cast<float4*>(&Wsm[WnRow(n) + 4 * kq]) =
-            *reinterpret_cast<const float4*>(B + static_cast<size_t>(n) * p.K + kc0 + 4 * kq);
-      }
-    } else {
-      const float4* src = reinterpret_cast<const float4*>(B + kc0 * N);
-      for (int idx = threadIdx.x; idx < kc * G; idx += kReduceThreads)
-        reinterpret_cast<float4*>(Wsm)[idx] = src[idx];
-    }
-    __syncthreads();
-    if (!live[0]) continue;  // rows ascend with r: a dead first row means a dead thread
-    for (int k = 0; k < kc; k += 32) {
-      float4 x[kReduceRows][8];
+  auto load = [&](float4 (&buf)[R][Q], int k) {
 #pragma unroll
-      for (int r = 0; r < kReduceRows; ++r)
+    for (int r = 0; r < R; ++r)
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
-          x[r][q] = k + 4 * q < kc ? *reinterpret_cast<const float4*>(xrow[r] + kc0 + k + 4 * q)
-                                   : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      for (int q = 0; q < Q; ++q) buf[r][q] = *reinterpret_cast<const float4*>(xrow[r] + k + 4 * q);
+  };
+  auto consume = [&](const float4 (&buf)[R][Q], int k) {
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const int kq = k + 4 * q;
-        if (kq < kc) {
-          if (kLane) {
-            // Product k goes to accumulator k mod 8; kc0 and k are multiples of 32.
-            const int l0 = (q & 1) * 4;
+    for (int q = 0; q < Q; ++q) {
+      const int kq = k + 4 * q;
+      if (kLane) {
+        // Product k goes to accumulator k mod 8; k is a multiple of 8.
+        const int l0 = (q & 1) * 4;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float4 w = *reinterpret_cast<const float4*>(&Wsm[WnRow(4 * g + j) + kq]);
+        for (int j = 0; j < 4; ++j) {
+          const float4 w = *reinterpret_cast<const float4*>(&Wsm[wn_row(4 * g + j) + kq]);
 #pragma unroll
-              for (int r = 0; r < kReduceRows; ++r) {
-                acc[r][j][l0 + 0] = acc[r][j][l0 + 0] + x[r][q].x * w.x;
-                acc[r][j][l0 + 1] = acc[r][j][l0 + 1] + x[r][q].y * w.y;
-                acc[r][j][l0 + 2] = acc[r][j][l0 + 2] + x[r][q].z * w.z;
-                acc[r][j][l0 + 3] = acc[r][j][l0 + 3] + x[r][q].w * w.w;
-              }
-            }
-          } else {
-            const float4 w0 = *reinterpret_cast<const float4*>(&Wsm[(kq + 0) * N + 4 * g]);
-            const float4 w1 = *reinterpret_cast<const float4*>(&Wsm[(kq + 1) * N + 4 * g]);
-            const float4 w2 = *reinterpret_cast<const float4*>(&Wsm[(kq + 2) * N + 4 * g]);
-            const float4 w3 = *reinterpret_cast<const float4*>(&Wsm[(kq + 3) * N + 4 * g]);
-#pragma unroll
-            for (int r = 0; r < kReduceRows; ++r)
-              QuadStep(c[r], p.alpha * x[r][q].x, p.alpha * x[r][q].y, p.alpha * x[r][q].z,
-                       p.alpha * x[r][q].w, w0, w1, w2, w3);
+          for (int r = 0; r < R; ++r) {
+            acc[r][j][l0 + 0] = acc[r][j][l0 + 0] + buf[r][q].x * w.x;
+            acc[r][j][l0 + 1] = acc[r][j][l0 + 1] + buf[r][q].y * w.y;
+            acc[r][j][l0 + 2] = acc[r][j][l0 + 2] + buf[r][q].z * w.z;
+            acc[r][j][l0 + 3] = acc[r][j][l0 + 3] + buf[r][q].w * w.w;
           }
+        }
+      } else {
+        const float4 w0 = *reinterpret_cast<const float4*>(&Wsm[(kq + 0) * N + 4 * g]);
+        const float4 w1 = *reinterpret_cast<const float4*>(&Wsm[(kq + 1) * N + 4 * g]);
+        const float4 w2 = *reinterpret_cast<const float4*>(&Wsm[(kq + 2) * N + 4 * g]);
+        const float4 w3 = *reinterpret_cast<const float4*>(&Wsm[(kq + 3) * N + 4 * g]);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          if (p.alpha == 1.0f)   // 1.0f * x == x: the multiply changes no bit
+            QuadStep(c[r], buf[r][q].x, buf[r][q].y, buf[r][q].z, buf[r][q].w, w0, w1, w2, w3);
+          else
+            QuadStep(c[r], p.alpha * buf[r][q].x, p.alpha * buf[r][q].y, p.alpha * buf[r][q].z,
+                     p.alpha * buf[r][q].w, w0, w1, w2, w3);
         }
       }
     }
+  };
+  constexpr int kStep = 4 * Q;   // k per register buffer (8 or 16; K % 16 == 0)
+  float4 xa[R][Q], xb[R][Q];
+  load(xa, 0);
+  for (int k = 0; k < K; k += 2 * kStep) {
+    if (k + kStep < K) load(xb, k + kStep);
+    consume(xa, k);
+    if (k + kStep < K) {
+      if (k + 2 * kStep < K) load(xa, k + 2 * kStep);
+      consume(xb, k + kStep);
+    }
   }
 #pragma unroll
-  for (int r = 0; r < kReduceRows; ++r) {
+  for (int r = 0; r < R; ++r) {
     if (!live[r]) continue;
     float v[4];
 #pragma unroll
@@ -170,28 +177,43 @@ __global__ void __launch_bounds__(kReduceThreads) ReduceKernel(Params p) {
   }
 }
 
-template <int G>
-void LaunchReduce(const Params& p, bool lane_order, cudaStream_t s) {
-  constexpr int kRowsPerBlock = kReduceRows * (32 / G) * (kReduceThreads / 32);
+template <int G, bool kLane, int R, int Q>
+bool LaunchReduceAs(const Params& p, cudaStream_t s) {
+  constexpr int N = 4 * G;
+  constexpr int kRowsPerBlock = R * (32 / G) * (kReduceThreads / 32);
+  const size_t smem = (kLane ? N * (p.K + 16) + 16 : p.K * N) * sizeof(float);
+  static size_t configured = 0;   // per instantiation; raising the limit is idempotent
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(ReduceKernel<G, kLane, R, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kReduceMaxK * N * sizeof(float) + 2048)) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    configured = kReduceMaxK * N * sizeof(float) + 2048;
+  }
   const unsigned blocks = static_cast<unsigned>((p.M + kRowsPerBlock - 1) / kRowsPerBlock);
-  if (lane_order) ReduceKernel<G, true><<<blocks, kReduceThreads, 0, s>>>(p);
-  else ReduceKernel<G, false><<<blocks, kReduceThreads, 0, s>>>(p);
+  ReduceKernel<G, kLane, R, Q><<<blocks, kReduceThreads, smem, s>>>(p);
+  return true;
+}
+
+template <int G>
+bool LaunchReduce(const Params& p, bool lane_order, cudaStream_t s) {
+  return lane_order ? LaunchReduceAs<G, true, 2, 4>(p, s) : LaunchReduceAs<G, false, 2, 4>(p, s);
 }
 
 }  // namespace
 
 bool SkinnyReduce(const Params& p, bool lane_order, cudaStream_t s) {
   if (p.N != 4 && p.N != 8 && p.N != 16) return false;
-  if (p.K < 64 || (p.K & 3) != 0 || p.M < 256) return false;
+  if (p.K < 64 || (p.K & 15) != 0 || p.K > kReduceMaxK || p.M < 256) return false;
   if (p.accumulate || p.b_col_scale || p.a_k_scale || p.partials) return false;
   if (lane_order && (p.bias || p.act != kActNone)) return false;
   if (!Aligned16(p.A) || !Aligned16(p.B) || !Aligned16(p.C) || !Aligned16(p.addend)) return false;
   switch (p.N) {
-    case 4: LaunchReduce<1>(p, lane_order, s); break;
-    case 8: LaunchReduce<2>(p, lane_order, s); break;
-    default: LaunchReduce<4>(p, lane_order, s); break;
+    case 4: return LaunchReduce<1>(p, lane_order, s);
+    case 8: return LaunchReduce<2>(p, lane_order, s);
+    default: return LaunchReduce<4>(p, lane_order, s);
   }
-  return true;
 }
 
 namespace {
