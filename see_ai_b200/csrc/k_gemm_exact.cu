@@ -173,28 +173,42 @@ __global__ void __launch_bounds__(kThreads) GemmQuadKernel(Params p) {
     }
 }
 
-// Folds split-K partials in chunk order, then the epilogue.
-__global__ void SplitKFoldKernel(Params p, size_t chunks) {
+// Folds split-K partials, then the epilogue.  Fixed two-level order: the chunks
+// are cut into eight consecutive groups; warp w of a block sums group w in chunk
+// order (for 32 neighbouring outputs, one per lane, so every load is a full
+// 128-byte line), and the eight group sums are then added in group order.  The
+// grouping is a function of the chunk count alone.
+constexpr int kFoldGroups = 8;
+__global__ void __launch_bounds__(32 * kFoldGroups) SplitKFoldKernel(Params p, size_t chunks) {
+  __shared__ float group_sum[kFoldGroups][32];
   const size_t total = p.M * p.N;
-  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += stride) {
-    // Sixteen independent loads at a time, added in chunk order.
-    float v = 0.0f;
-    for (size_t z0 = 0; z0 < chunks; z0 += 16) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const size_t i = static_cast<size_t>(blockIdx.x) * 32 + lane;
+  const size_t per = (chunks + kFoldGroups - 1) / kFoldGroups;
+  const size_t z_begin = w * per, z_end = z_begin + per < chunks ? z_begin + per : chunks;
+  float v = 0.0f;
+  if (i < total) {
+    for (size_t z0 = z_begin; z0 < z_end; z0 += 16) {   // sixteen independent loads at a time
       float part[16];
 #pragma unroll
       for (int u = 0; u < 16; ++u)
-        part[u] = z0 + u < chunks ? p.partials[(z0 + u) * total + i] : 0.0f;
+        part[u] = z0 + u < z_end ? p.partials[(z0 + u) * total + i] : 0.0f;
 #pragma unroll
       for (int u = 0; u < 16; ++u) {
-        if (z0 + u == 0) v = part[0];
-        else if (z0 + u < chunks) v = v + part[u];
+        if (z0 + u == z_begin) v = part[u];
+        else if (z0 + u < z_end) v = v + part[u];
       }
     }
-    if (p.addend) v = p.addend[i] + v;
-    if (p.bias) v = v + p.bias[i % p.N];
-    p.C[i] = ApplyAct(v, p.act);
   }
+  group_sum[w][lane] = v;
+  __syncthreads();
+  if (w != 0 || i >= total) return;
+  v = group_sum[0][lane];
+  for (int gi = 1; gi < kFoldGroups; ++gi)
+    if (static_cast<size_t>(gi) * per < chunks) v = v + group_sum[gi][lane];
+  if (p.addend) v = p.addend[i] + v;
+  if (p.bias) v = v + p.bias[i % p.N];
+  p.C[i] = ApplyAct(v, p.act);
 }
 
 // ---- lane order: BM x BN tile (BM * BN = 2048), 256 threads, 4x2 outputs x 8 lanes -----
@@ -359,9 +373,8 @@ void GemmExact(const GemmArgs& a, cudaStream_t s) {
       p.k_chunk = kSplitKChunk;
       p.partials = a.split_scratch;
       if (!SkinnyTnPartials(p, chunks, s)) LaunchQuad<true, float>(p, static_cast<unsigned>(chunks), s);
-      size_t blocks = (a.M * a.N + 255) / 256;
-      if (blocks > 1184) blocks = 1184;
-      SplitKFoldKernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(p, chunks);
+      const size_t blocks = (a.M * a.N + 31) / 32;
+      SplitKFoldKernel<<<static_cast<unsigned>(blocks), 32 * kFoldGroups, 0, s>>>(p, chunks);
       return;
     }
     LaunchQuad<true, float>(p, 1, s);
