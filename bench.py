@@ -170,7 +170,7 @@ def run_reference(args):
                          "kind": info["kind"], "sample": info["sample"]},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 # ---- our arm ---------------------------------------------------------------------------
@@ -303,7 +303,7 @@ def run_cuda(args):
         tps, info = cpu_sample(1, 0)
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": info["cores"],
                                 "kind": info["kind"], "sample": info["sample"]}
-    print(json.dumps(line))
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -317,10 +317,26 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    # stdout carries exactly one JSON line.  Libraries underneath (NCCL's version
+    # banner, for one) write to file descriptor 1 behind Python's back, so the
+    # descriptor itself is pointed at stderr for the run and the line goes to a
+    # saved copy of the real stdout.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
     else:
         run_cuda(args)
+
+
+_RESULT_FD = None
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    os.write(_RESULT_FD if _RESULT_FD is not None else 1, data)
 
 
 if __name__ == "__main__":

@@ -345,9 +345,17 @@ size_t QuadTiles(size_t M, size_t N) {
 
 }  // namespace
 
+size_t SplitKChunkRows(size_t M, size_t N, size_t K) {
+  const size_t tiles = QuadTiles(M, N);
+  size_t rows = kSplitKChunk;
+  while (rows > 32 && ((K + rows - 1) / rows) * tiles < 296) rows /= 2;
+  return rows;
+}
+
 size_t SplitKChunks(size_t M, size_t N, size_t K) {
   if (K < 4 * kSplitKChunk || QuadTiles(M, N) >= 148) return 1;
-  return (K + kSplitKChunk - 1) / kSplitKChunk;
+  const size_t rows = SplitKChunkRows(M, N, K);
+  return (K + rows - 1) / rows;
 }
 
 void GemmExact(const GemmArgs& a, cudaStream_t s) {
@@ -370,7 +378,7 @@ void GemmExact(const GemmArgs& a, cudaStream_t s) {
     const size_t chunks = SplitKChunks(a.M, a.N, a.K);
     if (chunks > 1 && a.split_scratch && !a.accumulate &&
         chunks * a.M * a.N <= a.split_scratch_floats) {
-      p.k_chunk = kSplitKChunk;
+      p.k_chunk = SplitKChunkRows(a.M, a.N, a.K);
       p.partials = a.split_scratch;
       if (!SkinnyTnPartials(p, chunks, s)) LaunchQuad<true, float>(p, static_cast<unsigned>(chunks), s);
       const size_t blocks = (a.M * a.N + 31) / 32;

@@ -358,7 +358,7 @@ namespace {
 // ---- transposed-A partials: C = A^T * B over one K chunk, output <= 16 wide or tall ----
 // C[i, j] = sum_k (alpha * A[k, i]) * B[k, j].  One operand is `wide` (its rows
 // are W floats, streamed once with 8-byte loads), the other `narrow` (rows of
-// R floats, R in {4, 8, 12, 16}).  A block takes one chunk of kTnChunk reduction
+// R floats, R in {4, 8, 12, 16}).  A block takes one chunk of p.k_chunk reduction
 // rows and one segment of 2 * kTnThreads wide columns; the chunk's narrow rows
 // are staged in shared memory transposed, Ns[r][k], so the four k of a quad
 // come back in one 16-byte broadcast load.  Each thread holds the R x 2 partial
@@ -368,7 +368,7 @@ namespace {
 constexpr int kTnThreads = 128;
 constexpr int kTnChunk = 256;
 constexpr int kTnStage = 16;
-static_assert(kTnChunk == kSplitKChunk, "the chunk geometry is part of the result");
+static_assert(kTnChunk == kSplitKChunk, "the staging buffer holds the largest chunk");
 
 template <bool kWideA, int R>
 __global__ void __launch_bounds__(kTnThreads) TnPartialKernel(Params p) {
@@ -376,8 +376,8 @@ __global__ void __launch_bounds__(kTnThreads) TnPartialKernel(Params p) {
   const size_t W = kWideA ? p.M : p.N;
   const float* wide = kWideA ? p.A : static_cast<const float*>(p.B);
   const float* narrow = kWideA ? static_cast<const float*>(p.B) : p.A;
-  const size_t k0 = static_cast<size_t>(blockIdx.z) * kTnChunk;
-  const int len = p.K - k0 < static_cast<size_t>(kTnChunk) ? static_cast<int>(p.K - k0) : kTnChunk;
+  const size_t k0 = static_cast<size_t>(blockIdx.z) * p.k_chunk;   // p.k_chunk <= kTnChunk
+  const int len = p.K - k0 < p.k_chunk ? static_cast<int>(p.K - k0) : static_cast<int>(p.k_chunk);
   for (int idx = threadIdx.x; idx < len * R; idx += kTnThreads) {
     const int m = idx / R, r = idx % R;
     const float v = narrow[(k0 + m) * R + r];
@@ -469,7 +469,9 @@ bool LaunchTn(const Params& p, int R, dim3 grid, cudaStream_t s) {
 }  // namespace
 
 bool SkinnyTnPartials(const Params& p, size_t chunks, cudaStream_t s) {
-  if (p.k_chunk != static_cast<size_t>(kTnChunk) || !p.partials || chunks > 65535) return false;
+  if (p.k_chunk == 0 || p.k_chunk > static_cast<size_t>(kTnChunk) || (p.k_chunk & 15) != 0 ||
+      !p.partials || chunks > 65535)
+    return false;
   const bool wide_a = p.N <= 16;
   if (!wide_a && p.M > 16) return false;
   const size_t W = wide_a ? p.M : p.N;

@@ -177,9 +177,13 @@ struct GemmArgs {
   float* split_scratch = nullptr;
   size_t split_scratch_floats = 0;
 };
-// K is cut into chunks of kSplitKChunk when the transposed-A product has fewer
-// output tiles than SMs and K >= 4 chunks; 1 means "not split".
-constexpr size_t kSplitKChunk = 256;
+// The transposed-A product is cut along K when it has fewer output tiles than
+// SMs and K is long: chunks of SplitKChunkRows rows (256, halved down to 32
+// while the partial-sum grid would hold fewer than 296 blocks), a pure function
+// of the shape, so a shape always reduces in the same order.  SplitKChunks is
+// the chunk count; 1 means "not split".
+constexpr size_t kSplitKChunk = 256;   // the largest chunk
+size_t SplitKChunkRows(size_t M, size_t N, size_t K);
 size_t SplitKChunks(size_t M, size_t N, size_t K);
 // The reference's reduction orders on CUDA cores, without fused multiply-adds:
 // bit-identical to the CPU executor for f32 / int8 / bf16 weights.
