@@ -295,22 +295,33 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     }
     if (t == n_h) { m = raw_max * a.inv_sqrt_d; m2 = m * kLog2e; }
     const uint32_t key0 = jh * kHalf;
+    const bool diagonal = key0 + kHalf > it * kTile;   // some keys of this step lie above the diagonal
 #pragma unroll 1
     for (uint32_t c0 = 0; c0 < kHalf; c0 += 32) {
       uint32_t r[32];
       TmemLoad32(t_s + c0, r);
       TmemWaitLd();
       if (!second) {
+        if (diagonal) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (key0 + c0 + j <= row) raw_max = fmaxf(raw_max, __uint_as_float(r[j]));
+          for (int j = 0; j < 32; ++j)
+            if (key0 + c0 + j <= row) raw_max = fmaxf(raw_max, __uint_as_float(r[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) raw_max = fmaxf(raw_max, __uint_as_float(r[j]));
+        }
       } else {
         float v[32];
+        if (diagonal) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          v[j] = (key0 + c0 + j <= row) ? Exp2Approx(fmaf(__uint_as_float(r[j]), c1, -m2)) : 0.0f;
-          l += v[j];
+          for (int j = 0; j < 32; ++j)
+            v[j] = (key0 + c0 + j <= row) ? Exp2Approx(fmaf(__uint_as_float(r[j]), c1, -m2)) : 0.0f;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = Exp2Approx(fmaf(__uint_as_float(r[j]), c1, -m2));
         }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) l += v[j];
         StoreRowChunk(p_s, tid, c0, v);
       }
     }
@@ -412,8 +423,8 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   const bool live = row < a.S;
   float* st_row = a.stats + (static_cast<size_t>(bh) * a.S + (live ? row : 0)) * kAttnStatsWidth;
   const float c1 = a.inv_sqrt_d * kLog2e;
-  const float m2 = live ? st_row[0] * kLog2e : 0.0f;
-  const float inv_l = live ? st_row[1] : 0.0f;
+  // P = 2^(s * log2(e)/sqrt(d) - M) with M = max * log2(e) - log2(1/denominator).
+  const float m2l = live ? st_row[0] * kLog2e - log2f(st_row[1]) : 0.0f;
   float delta = 0.0f;
   uint32_t b_phase = 0;
   int failed = 0;
@@ -439,27 +450,29 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     __syncwarp();
     const uint32_t key0 = jh * kHalf;
+    const bool diagonal = key0 + kHalf > it * kTile;
 #pragma unroll 1
     for (uint32_t c0 = 0; c0 < kHalf; c0 += 32) {
       uint32_t rs[32], rp[32];
       TmemLoad32(t_lane + c0, rs);
       TmemLoad32(t_lane + 64 + c0, rp);
       TmemWaitLd();
+      float pr[32];   // P = exp(s - max) / denominator, zero above the diagonal
+      if (diagonal) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          pr[j] = (key0 + c0 + j <= row) ? Exp2Approx(fmaf(__uint_as_float(rs[j]), c1, -m2l)) : 0.0f;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) pr[j] = Exp2Approx(fmaf(__uint_as_float(rs[j]), c1, -m2l));
+      }
       if (!second) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float p = (key0 + c0 + j <= row)
-                              ? Exp2Approx(fmaf(__uint_as_float(rs[j]), c1, -m2)) * inv_l : 0.0f;
-          delta = fmaf(p, __uint_as_float(rp[j]), delta);
-        }
+        for (int j = 0; j < 32; ++j) delta = fmaf(pr[j], __uint_as_float(rp[j]), delta);
       } else {
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float p = (key0 + c0 + j <= row)
-                              ? Exp2Approx(fmaf(__uint_as_float(rs[j]), c1, -m2)) * inv_l : 0.0f;
-          v[j] = p * (__uint_as_float(rp[j]) - delta) * a.inv_sqrt_d;
-        }
+        for (int j = 0; j < 32; ++j) v[j] = pr[j] * (__uint_as_float(rp[j]) - delta) * a.inv_sqrt_d;
         StoreRowChunk(p_s, tid, c0, v);
       }
     }

@@ -198,7 +198,7 @@ bool LaunchReduceAs(const Params& p, cudaStream_t s) {
 
 template <int G>
 bool LaunchReduce(const Params& p, bool lane_order, cudaStream_t s) {
-  return lane_order ? LaunchReduceAs<G, true, 2, 4>(p, s) : LaunchReduceAs<G, false, 2, 4>(p, s);
+  return lane_order ? LaunchReduceAs<G, true, 2, 2>(p, s) : LaunchReduceAs<G, false, 2, 2>(p, s);
 }
 
 }  // namespace
