@@ -102,6 +102,7 @@ CudaBackend::~CudaBackend() {
   cudaFree(d_rows_);
   cudaFree(d_gsum_);
   cudaFree(d_split_);
+  cudaFree(d_adam_table_);
   if (h_scalars_) cudaFreeHost(h_scalars_);
   if (h_status_) cudaFreeHost(h_status_);
   if (own_stream_ && stream_) cudaStreamDestroy(stream_);
@@ -363,9 +364,82 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
   umma::InvalidateRange(&umma_->ctx, 0, arena_bytes_);
   range_index_ = 0;
   PlanShadows(program, begin, std::min(end, program.size()));
+  PlanAdamGroups(program, begin, std::min(end, program.size()));
 }
 
-void CudaBackend::EndRange() { shadow_plan_.clear(); }
+void CudaBackend::EndRange() {
+  shadow_plan_.clear();
+  adam_group_of_.clear();
+  adam_groups_.clear();
+}
+
+// Consecutive AdamW instructions without a fused clip become one launch over a
+// table of their tensors; the table is uploaded here, before the range (and any
+// graph capture of it) starts.
+void CudaBackend::PlanAdamGroups(std::span<const Instruction> program, size_t begin, size_t end) {
+  adam_group_of_.assign(end > begin ? end - begin : 0, -1);
+  adam_groups_.clear();
+  if (coherence_ == Coherence::kStrict || end <= begin) return;
+  std::vector<k::AdamTensor> table;
+  for (size_t i = begin; i < end;) {
+    size_t j = i;
+    while (j < end && program[j].opcode == kAdamWStep && BitsToF32(program[j].out[1]) <= 0.0f &&
+           program[j].out[0] > 0)
+      ++j;
+    if (j - i < 2) { i = j > i ? j : i + 1; continue; }
+    AdamGroup grp;
+    grp.table_begin = table.size();
+    grp.count = static_cast<int>(j - i);
+    for (size_t t = i; t < j; ++t) {
+      const Instruction& ins = program[t];
+      Extents ext;
+      if (!DescribeInstruction(ins, arena_bytes_, rodata_bytes_, source_bytes_, &ext).empty()) {
+        grp.count = 0;   // a malformed member: leave the run to the per-instruction path
+        break;
+      }
+      k::AdamTensor e{};
+      e.p = Wr(ins.in[0]); e.g = Rd(ins.in[1]); e.m = Wr(ins.in[2]); e.v = Wr(ins.in[3]);
+      e.n = ins.out[0];
+      e.g_copies = 1;
+      const uint64_t g_off = RefOffset(ins.in[1]);
+      if (gather_ranks_ > 1 && RefSpace(ins.in[1]) == kArena && g_off >= gather_off_ &&
+          g_off + e.n * 4 <= gather_off_ + gather_bytes_) {
+        e.g = reinterpret_cast<const float*>(d_gathered_ + (g_off - gather_off_));
+        e.g_copies = gather_ranks_;
+        e.copy_stride = gather_bytes_ / 4;
+      }
+      grp.max_n = std::max<uint64_t>(grp.max_n, e.n);
+      table.push_back(e);
+    }
+    if (grp.count >= 2) {
+      adam_group_of_[i - begin] = static_cast<int32_t>(adam_groups_.size());
+      for (size_t t = i + 1; t < j; ++t) adam_group_of_[t - begin] = -2;
+      adam_groups_.push_back(grp);
+    } else {
+      table.resize(grp.table_begin);
+    }
+    i = j;
+  }
+  if (table.empty()) return;
+  if (table.size() > adam_table_capacity_) {
+    cudaStreamSynchronize(stream_);
+    cudaFree(d_adam_table_);
+    d_adam_table_ = nullptr;
+    adam_table_capacity_ = 0;
+    void* p = nullptr;
+    if (cudaMalloc(&p, table.size() * sizeof(k::AdamTensor)) != cudaSuccess) {
+      cudaGetLastError();
+      adam_group_of_.assign(adam_group_of_.size(), -1);
+      adam_groups_.clear();
+      return;
+    }
+    d_adam_table_ = static_cast<k::AdamTensor*>(p);
+    adam_table_capacity_ = table.size();
+  }
+  // The previous range's launches may still be reading the table.
+  cudaStreamSynchronize(stream_);
+  cudaMemcpy(d_adam_table_, table.data(), table.size() * sizeof(k::AdamTensor), cudaMemcpyHostToDevice);
+}
 
 namespace {
 
@@ -629,6 +703,15 @@ Status CudaBackend::DispatchOptimizer(const Instruction& ins, const StepParams& 
       return r;
     last_params_ = params;
     scalars_valid_ = true;
+  }
+  if (range_index_ < adam_group_of_.size() && adam_group_of_[range_index_] != -1) {
+    const int32_t gi = adam_group_of_[range_index_];
+    if (gi == -2) return {};   // done by the run's first instruction
+    const AdamGroup& grp = adam_groups_[gi];
+    k::AdamWStepMulti(d_adam_table_ + grp.table_begin, grp.count, grp.max_n, d_scalars_, d_status_,
+                      gather_ranks_ > 1 ? 1.0f / static_cast<float>(gather_ranks_) : 1.0f, stream_);
+    ++counters_.kernel_launches;
+    return {};
   }
   const uint64_t n = ins.out[0];
   const float clip = BitsToF32(ins.out[1]);

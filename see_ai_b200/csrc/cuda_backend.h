@@ -205,6 +205,15 @@ class CudaBackend {
   std::vector<ProfileRecord> pending_profile_;
   uint32_t range_index_ = 0;
 
+  // Runs of AdamW instructions issued as one launch (engine / lazy coherence
+  // only: in strict mode every instruction's effect must be visible on its own).
+  struct AdamGroup { size_t table_begin = 0; int count = 0; uint64_t max_n = 0; };
+  void PlanAdamGroups(std::span<const Instruction> program, size_t begin, size_t end);
+  std::vector<int32_t> adam_group_of_;   // per range position: -1 none, -2 member, else group index
+  std::vector<AdamGroup> adam_groups_;
+  k::AdamTensor* d_adam_table_ = nullptr;
+  size_t adam_table_capacity_ = 0;
+
   // Producer-side bf16 conversion (k::Shadow): for each instruction of the
   // current range, whether its output is the A operand of a later relaxed GEMM,
   // and under which key that GEMM will look the copy up.

@@ -44,10 +44,9 @@ __device__ __forceinline__ void QuadStep(float (&c)[4], float a0, float a1, floa
 // [k][N] for the quad order (W is [K, N]); [n][k] for the lane order (W is
 // [N, K]), where row n starts at n * (K + 16) + 4 * (n / 4) floats so that the
 // four column groups of a warp read four different bank groups.
-constexpr int kReduceThreads = 256;
 constexpr size_t kReduceMaxK = 3072;
 
-template <int G, bool kLane, int R, int Q>
+template <int G, bool kLane, int R, int Q, int kReduceThreads>
 __global__ void __launch_bounds__(kReduceThreads) ReduceKernel(Params p) {
   constexpr int N = 4 * G;
   constexpr int kRowsPerWarp = 32 / G;  // per row slot; a warp covers R of these
@@ -177,14 +176,15 @@ __global__ void __launch_bounds__(kReduceThreads) ReduceKernel(Params p) {
   }
 }
 
-template <int G, bool kLane, int R, int Q>
+template <int G, bool kLane, int R, int Q, int kReduceThreads>
 bool LaunchReduceAs(const Params& p, cudaStream_t s) {
   constexpr int N = 4 * G;
   constexpr int kRowsPerBlock = R * (32 / G) * (kReduceThreads / 32);
   const size_t smem = (kLane ? N * (p.K + 16) + 16 : p.K * N) * sizeof(float);
   static size_t configured = 0;   // per instantiation; raising the limit is idempotent
   if (smem > configured) {
-    if (cudaFuncSetAttribute(ReduceKernel<G, kLane, R, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(ReduceKernel<G, kLane, R, Q, kReduceThreads>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(kReduceMaxK * N * sizeof(float) + 2048)) != cudaSuccess) {
       cudaGetLastError();
       return false;
@@ -192,13 +192,22 @@ bool LaunchReduceAs(const Params& p, cudaStream_t s) {
     configured = kReduceMaxK * N * sizeof(float) + 2048;
   }
   const unsigned blocks = static_cast<unsigned>((p.M + kRowsPerBlock - 1) / kRowsPerBlock);
-  ReduceKernel<G, kLane, R, Q><<<blocks, kReduceThreads, smem, s>>>(p);
+  ReduceKernel<G, kLane, R, Q, kReduceThreads><<<blocks, kReduceThreads, smem, s>>>(p);
   return true;
+}
+
+// Eight-warp blocks when there are enough rows to fill the GPU with them,
+// two-warp blocks otherwise (a per-GPU batch of a few thousand rows).
+template <int G, bool kLane>
+bool LaunchReduceSized(const Params& p, cudaStream_t s) {
+  constexpr int kBigRows = 2 * (32 / G) * 8;
+  if ((p.M + kBigRows - 1) / kBigRows >= 148) return LaunchReduceAs<G, kLane, 2, 2, 256>(p, s);
+  return LaunchReduceAs<G, kLane, 2, 2, 64>(p, s);
 }
 
 template <int G>
 bool LaunchReduce(const Params& p, bool lane_order, cudaStream_t s) {
-  return lane_order ? LaunchReduceAs<G, true, 2, 2>(p, s) : LaunchReduceAs<G, false, 2, 2>(p, s);
+  return lane_order ? LaunchReduceSized<G, true>(p, s) : LaunchReduceSized<G, false>(p, s);
 }
 
 }  // namespace
@@ -370,14 +379,14 @@ constexpr int kTnChunk = 256;
 constexpr int kTnStage = 16;
 static_assert(kTnChunk == kSplitKChunk, "the staging buffer holds the largest chunk");
 
-template <bool kWideA, int R>
+template <bool kWideA, int R, int kChunk>
 __global__ void __launch_bounds__(kTnThreads) TnPartialKernel(Params p) {
-  __shared__ __align__(16) float Ns[R][kTnChunk + 4];
+  __shared__ __align__(16) float Ns[R][kChunk + 4];
   const size_t W = kWideA ? p.M : p.N;
   const float* wide = kWideA ? p.A : static_cast<const float*>(p.B);
   const float* narrow = kWideA ? static_cast<const float*>(p.B) : p.A;
-  const size_t k0 = static_cast<size_t>(blockIdx.z) * p.k_chunk;   // p.k_chunk <= kTnChunk
-  const int len = p.K - k0 < p.k_chunk ? static_cast<int>(p.K - k0) : static_cast<int>(p.k_chunk);
+  const size_t k0 = static_cast<size_t>(blockIdx.z) * kChunk;   // kChunk == p.k_chunk
+  const int len = p.K - k0 < static_cast<size_t>(kChunk) ? static_cast<int>(p.K - k0) : kChunk;
   for (int idx = threadIdx.x; idx < len * R; idx += kTnThreads) {
     const int m = idx / R, r = idx % R;
     const float v = narrow[(k0 + m) * R + r];
@@ -455,13 +464,24 @@ __global__ void __launch_bounds__(kTnThreads) TnPartialKernel(Params p) {
   }
 }
 
+template <bool kWideA, int kChunk>
+bool LaunchTnChunk(const Params& p, int R, dim3 grid, cudaStream_t s) {
+  switch (R) {
+    case 4: TnPartialKernel<kWideA, 4, kChunk><<<grid, kTnThreads, 0, s>>>(p); return true;
+    case 8: TnPartialKernel<kWideA, 8, kChunk><<<grid, kTnThreads, 0, s>>>(p); return true;
+    case 12: TnPartialKernel<kWideA, 12, kChunk><<<grid, kTnThreads, 0, s>>>(p); return true;
+    case 16: TnPartialKernel<kWideA, 16, kChunk><<<grid, kTnThreads, 0, s>>>(p); return true;
+    default: return false;
+  }
+}
+
 template <bool kWideA>
 bool LaunchTn(const Params& p, int R, dim3 grid, cudaStream_t s) {
-  switch (R) {
-    case 4: TnPartialKernel<kWideA, 4><<<grid, kTnThreads, 0, s>>>(p); return true;
-    case 8: TnPartialKernel<kWideA, 8><<<grid, kTnThreads, 0, s>>>(p); return true;
-    case 12: TnPartialKernel<kWideA, 12><<<grid, kTnThreads, 0, s>>>(p); return true;
-    case 16: TnPartialKernel<kWideA, 16><<<grid, kTnThreads, 0, s>>>(p); return true;
+  switch (p.k_chunk) {
+    case 256: return LaunchTnChunk<kWideA, 256>(p, R, grid, s);
+    case 128: return LaunchTnChunk<kWideA, 128>(p, R, grid, s);
+    case 64: return LaunchTnChunk<kWideA, 64>(p, R, grid, s);
+    case 32: return LaunchTnChunk<kWideA, 32>(p, R, grid, s);
     default: return false;
   }
 }

@@ -134,6 +134,29 @@ __global__ void AdamWKernel(float* __restrict__ p, const float* __restrict__ g,
   }
 }
 
+// The same update for a table of tensors (one optimizer phase in one launch).
+__global__ void AdamWMultiKernel(const AdamTensor* __restrict__ table,
+                                 const AdamScalars* __restrict__ scalars,
+                                 const DeviceStatus* __restrict__ status, float inv_copies) {
+  if (status->refused) return;
+  const AdamTensor t = table[blockIdx.y];
+  const AdamScalars a = *scalars;
+  const float om_b1 = 1.0f - a.beta1;
+  const float om_b2 = 1.0f - a.beta2;
+  const float inv = t.g_copies > 1 ? inv_copies : 1.0f;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < t.n; i += stride) {
+    const float gi = GatherGrad(t.g, i, t.g_copies, t.copy_stride, inv) * 1.0f;
+    const float mi = a.beta1 * t.m[i] + om_b1 * gi;
+    const float vi = a.beta2 * t.v[i] + om_b2 * gi * gi;
+    t.m[i] = mi;
+    t.v[i] = vi;
+    const float m_hat = mi * a.inv_bc1;
+    const float v_hat = vi * a.inv_bc2;
+    t.p[i] -= a.lr * (m_hat / (sqrtf(v_hat) + a.eps) + a.weight_decay * t.p[i]);
+  }
+}
+
 // reference: runtime/executor/optimizer.cc:91-102
 __global__ void SgdKernel(float* __restrict__ p, const float* __restrict__ g, size_t n,
                           const AdamScalars* __restrict__ scalars,
@@ -200,6 +223,15 @@ void AdamWStep(float* p, const float* g, float* m, float* v, size_t n, const Ada
   if (n == 0) return;
   AdamWKernel<<<GridFor(n), 256, 0, s>>>(p, g, m, v, n, a, clip_scale, status, g_copies,
                                          copy_stride, inv_copies);
+}
+
+void AdamWStepMulti(const AdamTensor* table, int count, uint64_t max_n, const AdamScalars* a,
+                    const DeviceStatus* status, float inv_copies, cudaStream_t s) {
+  if (count <= 0 || max_n == 0) return;
+  size_t bx = (max_n + 255) / 256;
+  if (bx > 64) bx = 64;
+  AdamWMultiKernel<<<dim3(static_cast<unsigned>(bx), static_cast<unsigned>(count)), 256, 0, s>>>(
+      table, a, status, inv_copies);
 }
 
 void SgdStep(float* p, const float* g, size_t n, const AdamScalars* a,

@@ -123,6 +123,16 @@ struct AdamScalars {
 void AdamWStep(float* p, const float* g, float* m, float* v, size_t n, const AdamScalars* a,
                const float* clip_scale, const DeviceStatus* status, int g_copies,
                size_t copy_stride, float inv_copies, cudaStream_t s);
+// A run of AdamW instructions as one launch: blockIdx.y picks the tensor.  Each
+// tensor's arithmetic is AdamWStep's, element for element.
+struct AdamTensor {
+  float* p; const float* g; float* m; float* v;
+  uint64_t n;
+  int32_t g_copies; uint32_t pad;
+  uint64_t copy_stride;
+};
+void AdamWStepMulti(const AdamTensor* table, int count, uint64_t max_n, const AdamScalars* a,
+                    const DeviceStatus* status, float inv_copies, cudaStream_t s);
 void SgdStep(float* p, const float* g, size_t n, const AdamScalars* a,
              const float* clip_scale, const DeviceStatus* status, int g_copies,
              size_t copy_stride, float inv_copies, cudaStream_t s);
