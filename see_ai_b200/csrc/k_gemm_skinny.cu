@@ -68,17 +68,29 @@ __global__ void __launch_bounds__(kReduceThreads) ReduceKernel(Params p) {
     xrow[r] = p.A + (live[r] ? row[r] : 0) * p.K;
   }
 
-  if (kLane) {
-    const int per_row = K / 4;
-    for (int idx = threadIdx.x; idx < N * per_row; idx += kReduceThreads) {
-      const int n = idx / per_row, kq = idx % per_row;
-      *reinterpret_cast<float4*>(&Wsm[wn_row(n) + 4 * kq]) =
-          *reinterpret_cast<const float4*>(B + static_cast<size_t>(n) * p.K + 4 * kq);
+  // Stage W, eight 16-byte loads in flight per thread (the copy is latency-bound
+  // otherwise: every block fetches all of W from L2).
+  {
+    const int per_row = K / 4, total = N * per_row;   // in float4 units; [n][k] and [k][n] alike
+    for (int base = threadIdx.x; base < total; base += 8 * kReduceThreads) {
+      float4 tmp[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int idx = base + u * kReduceThreads;
+        if (idx < total) tmp[u] = reinterpret_cast<const float4*>(B)[idx];
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int idx = base + u * kReduceThreads;
+        if (idx >= total) continue;
+        if (kLane) {   // W is [N][K]: float4 unit idx is (n, kq) = (idx / per_row, idx % per_row)
+          const int n = idx / per_row, kq = idx - n * per_row;
+          *reinterpret_cast<float4*>(&Wsm[wn_row(n) + 4 * kq]) = tmp[u];
+        } else {
+          reinterpret_cast<float4*>(Wsm)[idx] = tmp[u];
+        }
+      }
     }
-  } else {
-    const float4* src = reinterpret_cast<const float4*>(B);
-    for (int idx = threadIdx.x; idx < K * G; idx += kReduceThreads)
-      reinterpret_cast<float4*>(Wsm)[idx] = src[idx];
   }
   __syncthreads();
   if (!live[0]) return;  // rows ascend with r: a dead first row means a dead thread
@@ -202,7 +214,7 @@ template <int G, bool kLane>
 bool LaunchReduceSized(const Params& p, cudaStream_t s) {
   constexpr int kBigRows = 2 * (32 / G) * 8;
   if ((p.M + kBigRows - 1) / kBigRows >= 148) return LaunchReduceAs<G, kLane, 2, 2, 256>(p, s);
-  return LaunchReduceAs<G, kLane, 2, 2, 64>(p, s);
+  return LaunchReduceAs<G, kLane, 1, 2, 64>(p, s);
 }
 
 template <int G>
