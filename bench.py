@@ -35,6 +35,10 @@ sys.path.insert(0, ROOT)
 from see_ai_b200 import plan as P  # noqa: E402
 from see_ai_b200 import synth  # noqa: E402
 
+NCU_TRAFFIC_BYTES = 95.6e6
+NCU_TRAFFIC_NOTE = ("ncu, one 32768x768x768 launch (93 of the step's 143 tensor-core GEMM launches): 51.7 MB read "
+                    "+ 43.9 MB written; algorithmic 152 MB (A bf16 50 MB, W 1 MB, C f32 101 MB), part of C is "
+                    "still in L2 when the kernel ends")
 GLOBAL_SEQS = 64
 SEQ = 512
 METRIC = "update_step_tokens_per_s"
@@ -158,7 +162,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = min(args.steps, 3), min(args.warmup, 1)
+    steps, warmup = min(args.steps, 60), min(args.warmup, 10)   # a step is about 2-10 s of host time
     tps, info = cpu_sample(steps, warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s",
@@ -290,17 +294,20 @@ def run_cuda(args):
                 "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": int(launches_per_step * args.steps),
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "UmmaGemmKernel (tcgen05 bf16, relaxed frozen-weight GEMMs)",
+        "roofline": {"bound": "tensor", "kernel": "UmmaGemmPersistentKernel (tcgen05 bf16, relaxed frozen-weight GEMMs)",
                      "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak if peak else None,
-                     "peak_source": pk["source"] + " (bf16 sustained)", "traffic": None,
+                     "peak_source": pk["source"] + " (bf16 sustained)",
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the most frequent
+                     # shape (ncu capture summarised under profiles/); a constant, not measured here.
+                     "traffic": NCU_TRAFFIC_BYTES, "traffic_note": NCU_TRAFFIC_NOTE,
                      "launches_per_step": gemm_launches, "kernel_ms_per_step": gemm_ms},
         "profile_ms_per_step": {k: round(v, 3) for k, v in sorted(by_op.items(), key=lambda kv: -kv[1])},
         "profiled_step_ms": profiled_ms,
         "loss": {"first": loss0, "last": final_loss},
     }
     if world == 1 and not args.no_cpu_baseline:
-        tps, info = cpu_sample(1, 0)
+        tps, info = cpu_sample(4, 1)   # about 10-25 s of host time
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": info["cores"],
                                 "kind": info["kind"], "sample": info["sample"]}
     emit(line)
