@@ -191,6 +191,17 @@ int see_engine_take_timings(see_engine* h, float* forward_ms, float* backward_ms
  * (reference: compiler/backend/allocation/arena_binder.cc:56-77 binds them back to back). */
 int see_engine_gradient_block(see_engine* h, uint64_t* offset, uint64_t* bytes);
 
+/* Checkpoint / gate snapshot of the persistent prefix (adapters + optimizer moments) without stalling
+ * training; replaces the host copies the reference engine makes of the persistent segment for its gate and
+ * checkpoints (reference: runtime/dispatcher/gate.h:20-49, runtime/dispatcher/update_engine.cc:535-564).
+ * `begin` takes the copy at the current point of the step sequence (device to device on the compute stream)
+ * and downloads it on a second stream while later steps run; `wait` blocks until it is on the host and
+ * copies it to dst (bytes must equal the header's persistent_size).  `restore` is the resume path: the
+ * prefix back into the arena and the optimizer timestep set. */
+int see_engine_snapshot_begin(see_engine* h);
+int see_engine_snapshot_wait(see_engine* h, void* dst, uint64_t bytes);
+int see_engine_restore(see_engine* h, const void* src, uint64_t bytes, uint64_t step);
+
 #ifdef __cplusplus
 }
 #endif

@@ -281,5 +281,12 @@ int see_engine_gradient_block(see_engine* h, uint64_t* offset, uint64_t* bytes) 
   h->engine->GradientBlock(offset, bytes);
   return SEE_OK;
 }
+int see_engine_snapshot_begin(see_engine* h) { return Done(h, h->engine->SnapshotBegin()); }
+int see_engine_snapshot_wait(see_engine* h, void* dst, uint64_t bytes) {
+  return Done(h, h->engine->SnapshotWait(dst, bytes));
+}
+int see_engine_restore(see_engine* h, const void* src, uint64_t bytes, uint64_t step) {
+  return Done(h, h->engine->Restore(src, bytes, step));
+}
 
 }  // extern "C"

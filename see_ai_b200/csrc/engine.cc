@@ -107,6 +107,14 @@ UpdateEngine::~UpdateEngine() {
   for (auto& ev : staged_) if (ev) cudaEventDestroy(ev);
   if (pinned_) cudaFreeHost(pinned_);
   cudaFree(d_tally_);
+  if (copy_stream_) {
+    cudaStreamSynchronize(copy_stream_);
+    cudaStreamDestroy(copy_stream_);
+    cudaEventDestroy(snap_taken_);
+    cudaEventDestroy(snap_done_);
+  }
+  cudaFree(d_snap_);
+  if (h_snap_) cudaFreeHost(h_snap_);
 }
 
 const std::vector<Instruction>& UpdateEngine::program(int which) const {
@@ -423,6 +431,67 @@ Status UpdateEngine::WriteArena(uint64_t off, uint64_t bytes, const void* src) {
 
 Status UpdateEngine::WritePersistent(const void* src) {
   return WriteArena(0, header_.persistent_size, src);
+}
+
+Status UpdateEngine::SnapshotBegin() {
+  if (!loaded_) return std::unexpected("engine: no plan is loaded");
+  const uint64_t bytes = header_.persistent_size;
+  if (bytes == 0) return std::unexpected("engine: the plan has no persistent state");
+  auto fail = [](const char* what, cudaError_t e) -> Status {
+    return std::unexpected(std::string("engine: snapshot: ") + what + ": " + cudaGetErrorString(e));
+  };
+  if (snap_pending_) cudaEventSynchronize(snap_done_);   // the buffers are reused
+  if (bytes > snap_bytes_) {
+    cudaFree(d_snap_);
+    if (h_snap_) cudaFreeHost(h_snap_);
+    d_snap_ = nullptr; h_snap_ = nullptr; snap_bytes_ = 0;
+    void* p = nullptr;
+    if (auto e = cudaMalloc(&p, bytes); e != cudaSuccess) return fail("device buffer", e);
+    d_snap_ = static_cast<uint8_t*>(p);
+    if (auto e = cudaMallocHost(&p, bytes); e != cudaSuccess) return fail("pinned buffer", e);
+    h_snap_ = static_cast<uint8_t*>(p);
+    snap_bytes_ = bytes;
+  }
+  if (!copy_stream_) {
+    if (auto e = cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking); e != cudaSuccess)
+      return fail("copy stream", e);
+    if (auto e = cudaEventCreateWithFlags(&snap_taken_, cudaEventDisableTiming); e != cudaSuccess)
+      return fail("event", e);
+    if (auto e = cudaEventCreateWithFlags(&snap_done_, cudaEventDisableTiming); e != cudaSuccess)
+      return fail("event", e);
+  }
+  cudaStream_t s = backend_->stream();
+  if (auto e = cudaMemcpyAsync(d_snap_, backend_->device_arena(), bytes, cudaMemcpyDeviceToDevice, s);
+      e != cudaSuccess)
+    return fail("copy aside", e);
+  cudaEventRecord(snap_taken_, s);
+  cudaStreamWaitEvent(copy_stream_, snap_taken_, 0);
+  if (auto e = cudaMemcpyAsync(h_snap_, d_snap_, bytes, cudaMemcpyDeviceToHost, copy_stream_);
+      e != cudaSuccess)
+    return fail("download", e);
+  cudaEventRecord(snap_done_, copy_stream_);
+  snap_pending_ = true;
+  return {};
+}
+
+Status UpdateEngine::SnapshotWait(void* dst, uint64_t bytes) {
+  if (!snap_pending_) return std::unexpected("engine: no snapshot was begun");
+  if (bytes != header_.persistent_size)
+    return std::unexpected("engine: a snapshot is persistent_size bytes");
+  if (auto e = cudaEventSynchronize(snap_done_); e != cudaSuccess)
+    return std::unexpected(std::string("engine: snapshot: ") + cudaGetErrorString(e));
+  std::memcpy(dst, h_snap_, bytes);
+  snap_pending_ = false;
+  return {};
+}
+
+Status UpdateEngine::Restore(const void* src, uint64_t bytes, uint64_t step) {
+  if (!loaded_) return std::unexpected("engine: no plan is loaded");
+  if (bytes != header_.persistent_size)
+    return std::unexpected("engine: a restore is persistent_size bytes");
+  if (auto r = WritePersistent(src); !r) return r;
+  step_ = step;
+  return {};
 }
 
 }  // namespace see

@@ -84,6 +84,19 @@ class UpdateEngine {
   Status ReadPersistent(void* dst) { return backend_->ReadArena(0, header_.persistent_size, dst); }
   Status WritePersistent(const void* src);
 
+  // Checkpoint / gate snapshot of the persistent prefix (adapters and optimizer
+  // moments) without stalling training (reference: runtime/dispatcher/gate.h:20-49
+  // keeps the best state; runtime/dispatcher/checkpoint.h saves it).
+  // SnapshotBegin copies the prefix aside on the compute stream — a device-to-
+  // device copy at the current point of the step sequence, so later steps may
+  // overwrite the arena — and moves that copy to pinned host memory on a second
+  // stream while training continues.  SnapshotWait blocks until the bytes are
+  // on the host and copies them to `dst`.  Restore is the inverse for a resume:
+  // the prefix back into the arena, the timestep set.
+  Status SnapshotBegin();
+  Status SnapshotWait(void* dst, uint64_t bytes);
+  Status Restore(const void* src, uint64_t bytes, uint64_t step);
+
   // Replays each phase as a CUDA graph after its first eager execution.
   void SetUseGraphs(bool on) { use_graphs_ = on; }
   void SetPhaseTiming(bool on) { phase_timing_ = on; }
@@ -121,6 +134,13 @@ class UpdateEngine {
   cudaEvent_t ev_[4] = {nullptr, nullptr, nullptr, nullptr};
   StepTimings timings_;
   unsigned long long* d_tally_ = nullptr;  // {rows, correct, nonfinite}
+  // snapshot path
+  uint8_t* d_snap_ = nullptr;
+  uint8_t* h_snap_ = nullptr;
+  uint64_t snap_bytes_ = 0;
+  cudaStream_t copy_stream_ = nullptr;
+  cudaEvent_t snap_taken_ = nullptr, snap_done_ = nullptr;
+  bool snap_pending_ = false;
   // where the eval program's loss-forward leaves its probabilities
   uint64_t eval_probs_ref_ = kNullRef, eval_labels_ref_ = kNullRef, eval_rows_ = 0, eval_cols_ = 0;
   bool loaded_ = false;

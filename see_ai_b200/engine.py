@@ -21,6 +21,7 @@ ENGINE_SYMBOLS = [
     "see_engine_read_arena", "see_engine_write_arena", "see_engine_step", "see_engine_set_step",
     "see_engine_set_horizon", "see_engine_effective_lr", "see_engine_set_use_graphs",
     "see_engine_set_phase_timing", "see_engine_take_timings", "see_engine_gradient_block",
+    "see_engine_snapshot_begin", "see_engine_snapshot_wait", "see_engine_restore",
 ]
 
 _configured = False
@@ -63,6 +64,9 @@ def _lib() -> ctypes.CDLL:
     lib.see_engine_take_timings.argtypes = [vp] + [ctypes.POINTER(ctypes.c_float)] * 3 + \
         [ctypes.POINTER(u64)]
     lib.see_engine_gradient_block.argtypes = [vp, ctypes.POINTER(u64), ctypes.POINTER(u64)]
+    lib.see_engine_snapshot_begin.argtypes = [vp]
+    lib.see_engine_snapshot_wait.argtypes = [vp, vp, u64]
+    lib.see_engine_restore.argtypes = [vp, vp, u64, u64]
     _configured = True
     return lib
 
@@ -200,6 +204,21 @@ class Engine:
         self._check(self.lib.see_engine_take_timings(self.h, ctypes.byref(f), ctypes.byref(b),
                                                      ctypes.byref(o), ctypes.byref(n)))
         return dict(forward_ms=f.value, backward_ms=b.value, optimizer_ms=o.value, steps=n.value)
+
+    def snapshot_begin(self):
+        """Starts an asynchronous copy of the persistent prefix as it is now."""
+        self._check(self.lib.see_engine_snapshot_begin(self.h))
+
+    def snapshot_wait(self) -> np.ndarray:
+        """Blocks until the snapshot begun last is on the host; returns its bytes."""
+        out = np.empty(self.header["persistent_size"], dtype=np.uint8)
+        self._check(self.lib.see_engine_snapshot_wait(self.h, out.ctypes.data_as(ctypes.c_void_p), out.size))
+        return out
+
+    def restore(self, persistent: np.ndarray, step: int):
+        """Resume: the persistent prefix back into the arena, the timestep set."""
+        data = np.ascontiguousarray(persistent, dtype=np.uint8)
+        self._check(self.lib.see_engine_restore(self.h, data.ctypes.data_as(ctypes.c_void_p), data.size, step))
 
     def gradient_block(self) -> Tuple[int, int]:
         off, n = ctypes.c_uint64(), ctypes.c_uint64()
