@@ -304,13 +304,15 @@ UmmaGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // retirement — is paid once per SM.
 constexpr uint32_t kPBlockN = 256;
 constexpr uint32_t kPStages = 3;
-constexpr uint32_t kPThreads = 320;   // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
-constexpr uint32_t kPEpiWarps = 8;
+constexpr uint32_t kPEpiWarps = 16;
+constexpr uint32_t kPThreads = 64 + 32 * kPEpiWarps;   // warp 0 TMA, warp 1 MMA, then the epilogue warps
 constexpr uint32_t kPBTileBytes = kPBlockN * kBlockK * 2;
 constexpr uint32_t kPStageBytes = kATileBytes + kPBTileBytes;
 constexpr uint32_t kPTmemCols = 2 * kPBlockN;
-constexpr uint32_t kSlabCols = 64;
-constexpr uint32_t kSlabBytes = 32 * kSlabCols * 4;   // one epilogue warp's 32 x 64 f32
+constexpr uint32_t kSlabCols = 32;
+constexpr uint32_t kSlabBytes = 32 * kSlabCols * 4;   // one epilogue warp's 32 x 32 f32
+constexpr uint32_t kColsPerEpiWarp = kPBlockN / (kPEpiWarps / 4);
+constexpr uint32_t kEpiPasses = kColsPerEpiWarp / kSlabCols;
 
 struct __align__(8) PBarriers {
   uint64_t full[kPStages];
@@ -432,11 +434,13 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
       }
     }
   } else {
-    // ---- epilogue: warps 2..9.  TMEM lane quarter = warp % 4 (the hardware's
-    // rule); the two warps of a quarter split the tile's 256 columns in half.
-    const uint32_t quarter = warp & 3, col_half = (warp - 2) >> 2;
+    // ---- epilogue warps.  TMEM lane quarter = warp % 4 (the hardware's rule);
+    // the warps of a quarter split the tile's 256 columns between them.
+    const uint32_t quarter = warp & 3, col_group = (warp - 2) >> 2;
     float* slab = reinterpret_cast<float*>(slabs + (warp - 2) * kSlabBytes);
-    const uint32_t sub = lane >> 4, cl = lane & 15;
+    constexpr uint32_t kChunks = kSlabCols / 4;          // 16-byte chunks per slab row
+    constexpr uint32_t kRowsPerInstr = 32 / kChunks;     // rows one store instruction covers
+    const uint32_t sub = lane / kChunks, cl = lane % kChunks;
     uint32_t lt = 0;
     for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++lt) {
       const uint32_t buf = lt & 1, use = lt >> 1;
@@ -449,18 +453,17 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t row0 = m0 + quarter * 32;
       const uint32_t rows = row0 < ep.M ? (ep.M - row0 < 32 ? ep.M - row0 : 32) : 0;
-      // 64 columns at a time through the slab.  A thread writes its accumulator
-      // row as sixteen 16-byte chunks, chunk index XOR-ed with the row; the warp
-      // then reads two rows per instruction (lanes 0-15 one row, 16-31 the next),
-      // 512 contiguous bytes of C per store instruction.  Conflict-free both ways.
-      const uint32_t t_row = tmem_base + ((quarter * 32) << 16) + buf * kPBlockN + col_half * 128;
+      // 32 columns at a time through the slab.  A thread writes its accumulator
+      // row as eight 16-byte chunks, chunk index XOR-ed with the row; the warp
+      // then reads four rows per instruction (eight lanes each): whole 128-byte
+      // lines of C per store instruction.  Conflict-free both ways.
+      const uint32_t t_row = tmem_base + ((quarter * 32) << 16) + buf * kPBlockN + col_group * kColsPerEpiWarp;
 #pragma unroll 1
-      for (uint32_t pass = 0; pass < 2; ++pass) {
-        uint32_t ra[32], rb[32];
+      for (uint32_t pass = 0; pass < kEpiPasses; ++pass) {
+        uint32_t ra[32];
         TmemLoad32(t_row + pass * kSlabCols, ra);
-        TmemLoad32(t_row + pass * kSlabCols + 32, rb);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (pass == 1) {
+        if (pass == kEpiPasses - 1) {
           // The accumulator buffer is read out: hand it back before the slow part.
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
@@ -469,22 +472,20 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
                          ::"r"(SmemAddr(&bars->tmem_empty[buf])) : "memory");
         }
 #pragma unroll
-        for (uint32_t q = 0; q < 8; ++q) {
-          *reinterpret_cast<uint4*>(slab + lane * kSlabCols + ((q ^ (lane & 15)) * 4)) =
+        for (uint32_t q = 0; q < kChunks; ++q)
+          *reinterpret_cast<uint4*>(slab + lane * kSlabCols + ((q ^ (lane & (kChunks - 1))) * 4)) =
               make_uint4(ra[4 * q], ra[4 * q + 1], ra[4 * q + 2], ra[4 * q + 3]);
-          *reinterpret_cast<uint4*>(slab + lane * kSlabCols + (((q + 8) ^ (lane & 15)) * 4)) =
-              make_uint4(rb[4 * q], rb[4 * q + 1], rb[4 * q + 2], rb[4 * q + 3]);
-        }
         __syncwarp();
-        const uint32_t n = n0 + col_half * 128 + pass * kSlabCols + cl * 4;
+        const uint32_t n = n0 + col_group * kColsPerEpiWarp + pass * kSlabCols + cl * 4;
         if (n < ep.N) {   // N % 4 == 0: a float4 is all in or all out
           float4 scale = make_float4(ep.alpha, ep.alpha, ep.alpha, ep.alpha);
           if (ep.col_scale) scale = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n));
           float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
           if (ep.bias) bias = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
 #pragma unroll 4
-          for (uint32_t rr = sub; rr < rows; rr += 2) {
-            const float4 acc = *reinterpret_cast<const float4*>(slab + rr * kSlabCols + ((cl ^ (rr & 15)) * 4));
+          for (uint32_t rr = sub; rr < rows; rr += kRowsPerInstr) {
+            const float4 acc = *reinterpret_cast<const float4*>(
+                slab + rr * kSlabCols + ((cl ^ (rr & (kChunks - 1))) * 4));
             const size_t at = static_cast<size_t>(row0 + rr) * ep.N + n;
             float4 v = make_float4(acc.x * scale.x, acc.y * scale.y, acc.z * scale.z, acc.w * scale.w);
             if (ep.addend) {

@@ -1,6 +1,6 @@
 // LayerNorm / RMSNorm forward and backward.  HBM-bound row kernels: one warp
-// per row, the row streamed twice (sums, then the output) with float4 loads
-// where the row width allows.  Row sums are taken in double like the reference
+// per row; LayerNorm rows of 128..1024 floats (a multiple of 128) are held in
+// registers and read once with 16-byte loads, other widths are streamed twice.  Row sums are taken in double like the reference
 // (reference: runtime/executor/normalization.cc:17-113), in a fixed order —
 // lane-strided partials combined by a shuffle tree — so results are run-to-run
 // identical and independent of the grid; they can differ from the CPU's
@@ -84,6 +84,108 @@ __global__ void LayerNormBwdKernel(const float* __restrict__ dy, const float* __
   }
 }
 
+// Rows of 128 * V floats (V <= 8) held in registers: each lane owns V float4
+// chunks (chunk index lane + 32 i), so the row is read from memory once, with
+// 16-byte accesses.  Same expressions per element as the scalar kernels; the
+// double sums run over a lane's chunks in ascending order, then the shuffle tree.
+template <int V>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+LayerNormFwdVecKernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                      const float* __restrict__ beta, float* __restrict__ y,
+                      float* __restrict__ mean, float* __restrict__ rstd, size_t rows, float eps,
+                      Shadow sh) {
+  constexpr size_t cols = 128 * V;
+  const size_t r = blockIdx.x * static_cast<size_t>(kWarpsPerBlock) + threadIdx.x / 32;
+  const int lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const float4* xr = reinterpret_cast<const float4*>(x + r * cols);
+  float4 xv[V];
+  double sum = 0.0;
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    xv[i] = xr[lane + 32 * i];
+    sum += static_cast<double>(xv[i].x);
+    sum += static_cast<double>(xv[i].y);
+    sum += static_cast<double>(xv[i].z);
+    sum += static_cast<double>(xv[i].w);
+  }
+  sum = WarpSum(sum);
+  const float mu = static_cast<float>(sum / static_cast<double>(cols));
+  double var = 0.0;
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    const float e[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const double d = static_cast<double>(e[j]) - static_cast<double>(mu);
+      var += d * d;
+    }
+  }
+  var = WarpSum(var);
+  const float rs = 1.0f / sqrtf(static_cast<float>(var / static_cast<double>(cols)) + eps);
+  if (lane == 0) {
+    mean[r] = mu;
+    rstd[r] = rs;
+  }
+  float4* yr = reinterpret_cast<float4*>(y + r * cols);
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    const int c4 = lane + 32 * i;
+    const float4 g = __ldg(reinterpret_cast<const float4*>(gamma) + c4);
+    const float4 b = __ldg(reinterpret_cast<const float4*>(beta) + c4);
+    float4 v;
+    v.x = (xv[i].x - mu) * rs * g.x + b.x;
+    v.y = (xv[i].y - mu) * rs * g.y + b.y;
+    v.z = (xv[i].z - mu) * rs * g.z + b.z;
+    v.w = (xv[i].w - mu) * rs * g.w + b.w;
+    yr[c4] = v;
+    if (sh.dst) ShadowStore4(sh, r * (cols / 4) + c4, static_cast<uint32_t>(c4 * 4), v);
+  }
+}
+
+template <int V>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+LayerNormBwdVecKernel(const float* __restrict__ dy, const float* __restrict__ x,
+                      const float* __restrict__ gamma, const float* __restrict__ mean,
+                      const float* __restrict__ rstd, float* __restrict__ dx, size_t rows) {
+  constexpr size_t cols = 128 * V;
+  const size_t r = blockIdx.x * static_cast<size_t>(kWarpsPerBlock) + threadIdx.x / 32;
+  const int lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const float inv_d = 1.0f / static_cast<float>(cols);
+  const float4* dyr = reinterpret_cast<const float4*>(dy + r * cols);
+  const float4* xr = reinterpret_cast<const float4*>(x + r * cols);
+  const float mu = mean[r], rs = rstd[r];
+  float xhat[V][4], g[V][4];
+  double sum_g = 0.0, sum_gx = 0.0;
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    const int c4 = lane + 32 * i;
+    const float4 xv = xr[c4], dv = dyr[c4];
+    const float4 gm = __ldg(reinterpret_cast<const float4*>(gamma) + c4);
+    const float xe[4] = {xv.x, xv.y, xv.z, xv.w}, de[4] = {dv.x, dv.y, dv.z, dv.w},
+                ge[4] = {gm.x, gm.y, gm.z, gm.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      xhat[i][j] = (xe[j] - mu) * rs;
+      g[i][j] = de[j] * ge[j];
+      sum_g += static_cast<double>(g[i][j]);
+      sum_gx += static_cast<double>(g[i][j]) * static_cast<double>(xhat[i][j]);
+    }
+  }
+  sum_g = WarpSum(sum_g);
+  sum_gx = WarpSum(sum_gx);
+  const float mg = static_cast<float>(sum_g) * inv_d;
+  const float mgx = static_cast<float>(sum_gx) * inv_d;
+  float4* dxr = reinterpret_cast<float4*>(dx + r * cols);
+#pragma unroll
+  for (int i = 0; i < V; ++i)
+    dxr[lane + 32 * i] = make_float4(rs * (g[i][0] - mg - xhat[i][0] * mgx), rs * (g[i][1] - mg - xhat[i][1] * mgx),
+                                     rs * (g[i][2] - mg - xhat[i][2] * mgx), rs * (g[i][3] - mg - xhat[i][3] * mgx));
+}
+
+inline bool Vec16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 __global__ void RmsNormFwdKernel(const float* __restrict__ x, const float* __restrict__ gamma,
                                  float* __restrict__ y, float* __restrict__ rstd, size_t rows,
                                  size_t cols, float eps) {
@@ -132,13 +234,37 @@ bool LayerNormFwd(const float* x, const float* gamma, const float* beta, float* 
                   const Shadow* shadow) {
   if (rows == 0) return false;
   const bool shadowed = shadow && shadow->dst && shadow->cols == cols;
-  LayerNormFwdKernel<<<RowBlocks(rows), kWarpsPerBlock * 32, 0, s>>>(
-      x, gamma, beta, y, mean, rstd, rows, cols, eps, shadowed ? *shadow : Shadow{});
+  const Shadow sh = shadowed ? *shadow : Shadow{};
+  if (cols % 128 == 0 && cols <= 1024 && Vec16(x) && Vec16(y) && Vec16(gamma) && Vec16(beta) &&
+      (!shadowed || ShadowUsable(shadow, y, rows * cols))) {
+    const unsigned blocks = RowBlocks(rows);
+#define SEE_LN_FWD(V) \
+    case V: LayerNormFwdVecKernel<V><<<blocks, kWarpsPerBlock * 32, 0, s>>>(x, gamma, beta, y, mean, rstd, rows, eps, sh); break
+    switch (cols / 128) {
+      SEE_LN_FWD(1); SEE_LN_FWD(2); SEE_LN_FWD(3); SEE_LN_FWD(4);
+      SEE_LN_FWD(5); SEE_LN_FWD(6); SEE_LN_FWD(7); SEE_LN_FWD(8);
+    }
+#undef SEE_LN_FWD
+    return shadowed;
+  }
+  LayerNormFwdKernel<<<RowBlocks(rows), kWarpsPerBlock * 32, 0, s>>>(x, gamma, beta, y, mean, rstd,
+                                                                     rows, cols, eps, sh);
   return shadowed;
 }
 void LayerNormBwd(const float* dy, const float* x, const float* gamma, const float* mean,
                   const float* rstd, float* dx, size_t rows, size_t cols, cudaStream_t s) {
   if (rows == 0) return;
+  if (cols % 128 == 0 && cols <= 1024 && Vec16(dy) && Vec16(x) && Vec16(gamma) && Vec16(dx)) {
+    const unsigned blocks = RowBlocks(rows);
+#define SEE_LN_BWD(V) \
+    case V: LayerNormBwdVecKernel<V><<<blocks, kWarpsPerBlock * 32, 0, s>>>(dy, x, gamma, mean, rstd, dx, rows); break
+    switch (cols / 128) {
+      SEE_LN_BWD(1); SEE_LN_BWD(2); SEE_LN_BWD(3); SEE_LN_BWD(4);
+      SEE_LN_BWD(5); SEE_LN_BWD(6); SEE_LN_BWD(7); SEE_LN_BWD(8);
+    }
+#undef SEE_LN_BWD
+    return;
+  }
   LayerNormBwdKernel<<<RowBlocks(rows), kWarpsPerBlock * 32, 0, s>>>(dy, x, gamma, mean, rstd, dx,
                                                                      rows, cols);
 }
