@@ -365,9 +365,12 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
   range_index_ = 0;
   PlanShadows(program, begin, std::min(end, program.size()));
   PlanAdamGroups(program, begin, std::min(end, program.size()));
+  PlanBiasFusions(program, begin, std::min(end, program.size()));
 }
 
 void CudaBackend::EndRange() {
+  bias_fusion_.clear();
+  skip_next_add_bias_ = false;
   shadow_plan_.clear();
   adam_group_of_.clear();
   adam_groups_.clear();
@@ -506,6 +509,73 @@ void CudaBackend::PlanShadows(std::span<const Instruction> program, size_t begin
   }
 }
 
+// Marks GEMM i / kAddBias i+1 pairs whose intermediate tensor R (the GEMM's
+// output, the kAddBias input) nobody needs: every byte of R is overwritten by a
+// later instruction of the range before any instruction reads it.  Proven on
+// the operand extents; a range that ends with part of R unaccounted for keeps
+// the pair as it is.
+void CudaBackend::PlanBiasFusions(std::span<const Instruction> program, size_t begin, size_t end) {
+  bias_fusion_.assign(end > begin ? end - begin : 0, BiasFusion{});
+  if (coherence_ == Coherence::kStrict || !relaxed_allowed_ || end < begin + 2) return;
+  std::vector<Extents> ext(end - begin);
+  for (size_t i = begin; i < end; ++i)
+    if (!DescribeInstruction(program[i], arena_bytes_, rodata_bytes_, source_bytes_, &ext[i - begin]).empty())
+      return;   // a malformed instruction: leave everything as it is
+  using Interval = std::pair<uint64_t, uint64_t>;   // [lo, hi)
+  for (size_t i = begin; i + 1 < end; ++i) {
+    const Instruction& g = program[i];
+    const Instruction& ab = program[i + 1];
+    const uint16_t op = g.opcode;
+    const bool gemm = op == kGemmNN || op == kGemmNT || op == kGemmNNQ8 || op == kGemmNTQ8 ||
+                      op == kGemmNNBF16 || op == kGemmNTBF16;
+    if (!gemm || !(g.flags & kFlagRelaxed) || ab.opcode != kAddBias) continue;
+    if ((g.flags & (kFlagEpilogueBias | kFlagGemmAddend)) || ActOf(g.flags) != kActNone) continue;
+    if (RefSpace(g.in[1]) == kArena || RefSpace(g.in[0]) != kArena || RefSpace(g.in[2]) != kArena ||
+        RefSpace(ab.in[2]) != kArena)
+      continue;
+    const uint64_t M = g.out[0], N = g.out[1], K = g.out[2];
+    if (K % 8 != 0 || N % 4 != 0 || K < 64 || N < 16 || M < 64) continue;   // TryGemm's domain
+    if (ab.in[0] != g.in[2] || ab.out[0] != M || ab.out[1] != N) continue;
+    const uint64_t r_lo = RefOffset(g.in[2]), r_hi = r_lo + M * N * 4;
+    const uint64_t z_lo = RefOffset(ab.in[2]), z_hi = z_lo + M * N * 4;
+    if (z_lo < r_hi && r_lo < z_hi && z_lo != r_lo) continue;   // partial overlap: not a case we take
+    if ((RefOffset(ab.in[1]) & 15) != 0 || (z_lo & 15) != 0) continue;   // the epilogue moves float4s
+    bool dead = z_lo == r_lo;   // in place: R is Z, nothing to prove
+    if (!dead) {
+      std::vector<Interval> unknown{{r_lo, r_hi}};
+      bool read_first = false;
+      for (size_t j = i + 2; j < end && !unknown.empty() && !read_first; ++j) {
+        const Extents& e = ext[j - begin];
+        for (size_t x = 0; x < e.count && !read_first; ++x) {
+          if (e.e[x].space != kArena) continue;
+          const uint64_t lo = e.e[x].off, hi = lo + e.e[x].bytes;
+          if (!e.e[x].write || e.e[x].read)
+            for (const Interval& u : unknown)
+              if (lo < u.second && u.first < hi) { read_first = true; break; }
+        }
+        if (read_first) break;
+        for (size_t x = 0; x < e.count; ++x) {
+          if (e.e[x].space != kArena || !e.e[x].write) continue;
+          const uint64_t lo = e.e[x].off, hi = lo + e.e[x].bytes;
+          std::vector<Interval> rest;
+          for (const Interval& u : unknown) {
+            if (hi <= u.first || u.second <= lo) { rest.push_back(u); continue; }
+            if (u.first < lo) rest.push_back({u.first, lo});
+            if (hi < u.second) rest.push_back({hi, u.second});
+          }
+          unknown.swap(rest);
+        }
+      }
+      dead = !read_first && unknown.empty();
+    }
+    if (!dead) continue;
+    BiasFusion& f = bias_fusion_[i - begin];
+    f.fuse = true;
+    f.bias_ref = ab.in[1];
+    f.out_ref = ab.in[2];
+  }
+}
+
 const k::Shadow* CudaBackend::ShadowFor(uint64_t out_ref, uint64_t elems) const {
   if (!cur_shadow_.dst || RefSpace(out_ref) != kArena || RefOffset(out_ref) != cur_plan_.a_off ||
       elems != cur_plan_.M * cur_plan_.K)
@@ -577,6 +647,7 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
     cudaEventRecord(ev0, stream_);
   }
 
+  if (ins.opcode != kAddBias) skip_next_add_bias_ = false;
   cur_shadow_ = k::Shadow{};
   shadow_written_ = false;
   if (range_index_ < shadow_plan_.size() && shadow_plan_[range_index_].want) {
@@ -646,6 +717,12 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
   // cores (activation rounded to bf16 once, weight exact, f32 accumulate).
   if ((ins.flags & kFlagRelaxed) && relaxed_allowed_ && !a.a_transposed && !a.accumulate &&
       RefSpace(ins.in[1]) != kArena) {
+    const BiasFusion* fuse = range_index_ < bias_fusion_.size() && bias_fusion_[range_index_].fuse
+                                 ? &bias_fusion_[range_index_] : nullptr;
+    if (fuse) {   // the following kAddBias, done in this product's epilogue
+      a.bias = Rd(fuse->bias_ref);
+      a.C = Wr(fuse->out_ref);
+    }
     int launches = 0;
     const std::string err = umma::TryGemm(&umma_->ctx, a, RefSpace(ins.in[1]) == kRodata ? 1 : 2,
                                           RefOffset(ins.in[1]), RefOffset(ins.in[0]),
@@ -654,10 +731,15 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
     if (err.empty() && launches > 0) {
       ++counters_.relaxed_executions;
       counters_.kernel_launches += launches;
+      skip_next_add_bias_ = fuse != nullptr;
       return {};
     }
     if (!err.empty()) return std::unexpected("cuda: " + err);
     // launches == 0: the shape is outside the tensor-core kernel's domain.
+    if (fuse) {
+      a.bias = nullptr;
+      a.C = Wr(ins.in[2]);
+    }
   }
   // The split-K scratch is sized per range (BeginRange); an instruction executed
   // outside any range simply runs unsplit.
@@ -766,6 +848,10 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
       break;
     case kMulEW: k::MulEW(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s); launched(); break;
     case kAddBias:
+      if (skip_next_add_bias_) {   // the preceding product's epilogue already wrote this output
+        skip_next_add_bias_ = false;
+        break;
+      }
       k::AddBias(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], ins.out[1], s); launched(); break;
     case kReluFwd:
       shadow_written_ = k::ActFwd(kActRelu, Rd(ins.in[0]), Wr(ins.in[1]), ins.out[0], s,

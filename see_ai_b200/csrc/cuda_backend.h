@@ -214,6 +214,15 @@ class CudaBackend {
   k::AdamTensor* d_adam_table_ = nullptr;
   size_t adam_table_capacity_ = 0;
 
+  // A relaxed GEMM followed by the kAddBias that consumes its output, when the
+  // un-biased product is provably dead afterwards: the GEMM's epilogue adds the
+  // bias and writes the kAddBias output directly; the kAddBias becomes a no-op.
+  // Engine / lazy coherence only.
+  struct BiasFusion { bool fuse = false; uint64_t bias_ref = kNullRef, out_ref = kNullRef; };
+  void PlanBiasFusions(std::span<const Instruction> program, size_t begin, size_t end);
+  std::vector<BiasFusion> bias_fusion_;   // per range position (of the GEMM)
+  bool skip_next_add_bias_ = false;
+
   // Producer-side bf16 conversion (k::Shadow): for each instruction of the
   // current range, whether its output is the A operand of a later relaxed GEMM,
   // and under which key that GEMM will look the copy up.
