@@ -208,12 +208,182 @@ bool LaunchReduceAs(const Params& p, cudaStream_t s) {
   return true;
 }
 
-// Eight-warp blocks when there are enough rows to fill the GPU with them,
-// two-warp blocks otherwise (a per-GPU batch of a few thousand rows).
+// ---- reduce, few rows: the block's rows of A staged in shared memory ------------------
+// With a few thousand rows per GPU there are only a few warps per SM, and a
+// thread that keeps two 16-k register buffers of its row in flight pays one
+// DRAM round trip per 16 k: the kernel above is latency-bound there.  This one
+// issues ALL of the block's traffic at once with 16-byte asynchronous copies
+// (its rows of A and W, in four k chunks, one commit group each) and computes
+// chunk c while chunks c+1.. are still landing, so the round trip is paid once.
+// Rows of A sit at a stride of K + 4 floats: the row slots of a warp then read
+// distinct bank groups.  Arithmetic per element is the same as above.
+__device__ __forceinline__ void CpAsync16(float* smem_dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<unsigned>(
+                   __cvta_generic_to_shared(smem_dst))), "l"(src) : "memory");
+}
+__device__ __forceinline__ void CpAsyncCommit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void CpAsyncWait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+
+constexpr int kStagedChunks = 4;
+constexpr size_t kStagedMaxSmem = 112 * 1024;   // two blocks per SM
+
+template <int G>
+struct StagedShape {
+  static constexpr int kThreads = G == 4 ? 64 : 32;
+  static constexpr int kRows = (32 / G) * (kThreads / 32);
+};
+
+template <int G, bool kLane>
+__host__ __device__ inline size_t StagedSmemFloats(size_t K) {
+  constexpr int N = 4 * G;
+  return StagedShape<G>::kRows * (K + 4) + (kLane ? N * (K + 16) + 16 : K * N);
+}
+
+template <int G, bool kLane>
+__global__ void __launch_bounds__(StagedShape<G>::kThreads) ReduceStagedKernel(Params p) {
+  constexpr int N = 4 * G;
+  constexpr int kThreads = StagedShape<G>::kThreads, kRows = StagedShape<G>::kRows;
+  constexpr int kRowsPerWarp = 32 / G;
+  extern __shared__ __align__(16) float smem[];
+  const int K = static_cast<int>(p.K);
+  const int xs_stride = K + 4, wn_stride = K + 16;
+  float* Xs = smem;
+  float* Wsm = smem + kRows * xs_stride;
+  auto wn_row = [&](int n) { return n * wn_stride + 4 * (n >> 2); };
+  const float* B = static_cast<const float*>(p.B);
+  const size_t row0 = static_cast<size_t>(blockIdx.x) * kRows;
+  const int rows_live = p.M - row0 < static_cast<size_t>(kRows) ? static_cast<int>(p.M - row0) : kRows;
+  const int ck = ((K / 16 + kStagedChunks - 1) / kStagedChunks) * 16;   // chunk length, a multiple of 16
+
+  {
+    const int sub = threadIdx.x >> 4, seg = threadIdx.x & 15;   // 16 threads copy 256 contiguous bytes
+    constexpr int kSubs = kThreads / 16;
+    for (int c = 0; c < kStagedChunks; ++c) {
+      const int k0 = c * ck;
+      const int len = K - k0 < ck ? (K - k0 > 0 ? K - k0 : 0) : ck;
+      const int per = len / 4;
+      for (int r = sub; r < rows_live; r += kSubs)
+        for (int kq = seg; kq < per; kq += 16)
+          CpAsync16(&Xs[r * xs_stride + k0 + 4 * kq], p.A + (row0 + r) * p.K + k0 + 4 * kq);
+      if (kLane) {
+        for (int n = sub; n < N; n += kSubs)
+          for (int kq = seg; kq < per; kq += 16)
+            CpAsync16(&Wsm[wn_row(n) + k0 + 4 * kq], B + static_cast<size_t>(n) * p.K + k0 + 4 * kq);
+      } else {
+        for (int i = threadIdx.x; i < per * N; i += kThreads)   // rows k0.. of [K][N]: one contiguous run
+          CpAsync16(&Wsm[k0 * N + 4 * i], B + static_cast<size_t>(k0) * N + 4 * i);
+      }
+      CpAsyncCommit();
+    }
+  }
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane % G;
+  const int slot = warp * kRowsPerWarp + lane / G;
+  const bool live = slot < rows_live;
+  const float* xs = Xs + slot * xs_stride;
+  float c[4];
+  float acc[4][8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    c[j] = 0.0f;
+#pragma unroll
+    for (int l = 0; l < 8; ++l) acc[j][l] = 0.0f;
+  }
+  auto chunk = [&](int k0) {
+    const int k1 = k0 + ck < K ? k0 + ck : K;
+    if (!live) return;
+#pragma unroll 2
+    for (int k = k0; k < k1; k += 8) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int kq = k + 4 * q;
+        const float4 x = *reinterpret_cast<const float4*>(xs + kq);
+        if (kLane) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 w = *reinterpret_cast<const float4*>(&Wsm[wn_row(4 * g + j) + kq]);
+            acc[j][4 * q + 0] = acc[j][4 * q + 0] + x.x * w.x;   // product k into accumulator k mod 8
+            acc[j][4 * q + 1] = acc[j][4 * q + 1] + x.y * w.y;
+            acc[j][4 * q + 2] = acc[j][4 * q + 2] + x.z * w.z;
+            acc[j][4 * q + 3] = acc[j][4 * q + 3] + x.w * w.w;
+          }
+        } else {
+          const float4 w0 = *reinterpret_cast<const float4*>(&Wsm[(kq + 0) * N + 4 * g]);
+          const float4 w1 = *reinterpret_cast<const float4*>(&Wsm[(kq + 1) * N + 4 * g]);
+          const float4 w2 = *reinterpret_cast<const float4*>(&Wsm[(kq + 2) * N + 4 * g]);
+          const float4 w3 = *reinterpret_cast<const float4*>(&Wsm[(kq + 3) * N + 4 * g]);
+          if (p.alpha == 1.0f)   // 1.0f * x == x: the multiply changes no bit
+            QuadStep(c, x.x, x.y, x.z, x.w, w0, w1, w2, w3);
+          else
+            QuadStep(c, p.alpha * x.x, p.alpha * x.y, p.alpha * x.z, p.alpha * x.w, w0, w1, w2, w3);
+        }
+      }
+    }
+  };
+  CpAsyncWait<3>(); __syncthreads(); chunk(0);
+  CpAsyncWait<2>(); __syncthreads(); chunk(ck);
+  CpAsyncWait<1>(); __syncthreads(); chunk(2 * ck);
+  CpAsyncWait<0>(); __syncthreads(); chunk(3 * ck);
+  static_assert(kStagedChunks == 4, "the waits above are written out for four chunks");
+  if (!live) return;
+
+  float v[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (kLane) {
+      float s = acc[j][0];
+#pragma unroll
+      for (int l = 1; l < 8; ++l) s = s + acc[j][l];
+      v[j] = p.alpha * s;
+    } else {
+      v[j] = c[j];
+    }
+  }
+  const size_t o = (row0 + slot) * N + 4 * g;
+  if (p.addend) {
+    const float4 d = *reinterpret_cast<const float4*>(p.addend + o);
+    v[0] = d.x + v[0]; v[1] = d.y + v[1]; v[2] = d.z + v[2]; v[3] = d.w + v[3];
+  }
+  if (!kLane) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (p.bias) v[j] = v[j] + p.bias[4 * g + j];
+      v[j] = ApplyAct(v[j], p.act);
+    }
+  }
+  *reinterpret_cast<float4*>(p.C + o) = make_float4(v[0], v[1], v[2], v[3]);
+}
+
+template <int G, bool kLane>
+bool LaunchReduceStaged(const Params& p, cudaStream_t s) {
+  const size_t smem = StagedSmemFloats<G, kLane>(p.K) * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(ReduceStagedKernel<G, kLane>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kStagedMaxSmem)) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    configured = true;
+  }
+  constexpr int kRows = StagedShape<G>::kRows;
+  const unsigned blocks = static_cast<unsigned>((p.M + kRows - 1) / kRows);
+  ReduceStagedKernel<G, kLane><<<blocks, StagedShape<G>::kThreads, smem, s>>>(p);
+  return true;
+}
+
+// Eight-warp streaming blocks when there are enough rows to fill the GPU with
+// them; otherwise (a per-GPU batch of a few thousand rows) the staged kernel,
+// or two-warp streaming blocks when K is too long for its shared memory.
 template <int G, bool kLane>
 bool LaunchReduceSized(const Params& p, cudaStream_t s) {
   constexpr int kBigRows = 2 * (32 / G) * 8;
   if ((p.M + kBigRows - 1) / kBigRows >= 148) return LaunchReduceAs<G, kLane, 2, 2, 256>(p, s);
+  if (StagedSmemFloats<G, kLane>(p.K) * sizeof(float) <= kStagedMaxSmem) return LaunchReduceStaged<G, kLane>(p, s);
   return LaunchReduceAs<G, kLane, 1, 2, 64>(p, s);
 }
 

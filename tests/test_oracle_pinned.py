@@ -101,7 +101,9 @@ def seeded_programs():
     for (M, N, K) in [(1, 1, 1), (3, 5, 7), (37, 29, 131), (8, 64, 13), (65, 33, 66),
                       (300, 16, 70), (12, 300, 70),
                       # the adapter-product shapes: narrow outputs over a long K, rank-K expansions
-                      (300, 16, 80), (260, 8, 608), (257, 4, 64), (70, 64, 12), (100, 96, 16), (64, 128, 8)]:
+                      (300, 16, 80), (260, 8, 608), (257, 4, 64), (70, 64, 12), (100, 96, 16), (64, 128, 8),
+                      # enough rows for each of the three block geometries of the narrow-output kernels
+                      (20000, 16, 80), (9000, 8, 64)]:
         a = Arena(rng)
         A = a.alloc(M * K, "normal"); At = a.alloc(K * M, "normal")
         B = a.alloc(K * N, "normal"); Bt = a.alloc(N * K, "normal")
