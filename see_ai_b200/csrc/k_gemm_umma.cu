@@ -314,6 +314,27 @@ constexpr uint32_t kSlabBytes = 32 * kSlabCols * 4;   // one epilogue warp's 32 
 constexpr uint32_t kColsPerEpiWarp = kPBlockN / (kPEpiWarps / 4);
 constexpr uint32_t kEpiPasses = kColsPerEpiWarp / kSlabCols;
 
+// Tile order of the persistent kernel.  Bands of band_blocks row blocks; inside a
+// band the row block runs fastest.  With band_blocks = 1 the column tile runs
+// fastest: the CTAs of a wave share W (small) and each row block of A is used
+// by neighbouring CTAs.  A vocabulary-wide W (dozens of column tiles) does not
+// stay in L2 next to the C it produces; with a band of 64 row blocks the CTAs of
+// one wave share the band's rows of A and two or three column tiles, and W is
+// streamed from HBM once per band rather than once per row block (measured at
+// 32768 x 32000 x 768: 1.93 ms -> 1.70 ms; bands of 16 / 32 / 128: 1.83 / 1.76 / 1.82).
+constexpr uint32_t kWideBandBlocks = 64;
+constexpr uint32_t kWideTilesN = 32;
+__device__ __forceinline__ void TileCoord(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, uint32_t band_blocks,
+                                          uint32_t* m_block, uint32_t* n_block) {
+  const uint32_t per_band = band_blocks * tiles_n;
+  const uint32_t band = t / per_band, within = t - band * per_band;
+  const uint32_t first = band * band_blocks;
+  const uint32_t height = tiles_m - first < band_blocks ? tiles_m - first : band_blocks;
+  const uint32_t nb = within / height;
+  *m_block = first + (within - nb * height);
+  *n_block = nb;
+}
+
 struct __align__(8) PBarriers {
   uint64_t full[kPStages];
   uint64_t empty[kPStages];
@@ -325,7 +346,8 @@ struct __align__(8) PBarriers {
 
 __global__ void __launch_bounds__(kPThreads, 1)
 UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
-                         const __grid_constant__ CUtensorMap map_b, UmmaEpilogue ep) {
+                         const __grid_constant__ CUtensorMap map_b, UmmaEpilogue ep,
+                         uint32_t band_blocks) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (SmemAddr(smem_raw) & 1023u)) & 1023u);
   uint8_t* slabs = smem + kPStages * kPStageBytes;
@@ -366,11 +388,15 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
       uint32_t it = 0;
       bool ok = true;
       for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const uint32_t m0 = (t / tiles_n) * kBlockM, n0 = (t % tiles_n) * kPBlockN;
+        uint32_t mb, nb;
+        TileCoord(t, tiles_m, tiles_n, band_blocks, &mb, &nb);
+        const uint32_t m0 = mb * kBlockM, n0 = nb * kPBlockN;
         // Ask L2 for the A rows of this CTA's next tile now, so that its loads
         // find them there instead of paying an HBM round trip inside the ring.
         if (t + gridDim.x < total_tiles && k_blocks <= 64) {   // (a long K would only thrash L2)
-          const uint32_t next_m0 = ((t + gridDim.x) / tiles_n) * kBlockM;
+          uint32_t next_mb, next_nb;
+          TileCoord(t + gridDim.x, tiles_m, tiles_n, band_blocks, &next_mb, &next_nb);
+          const uint32_t next_m0 = next_mb * kBlockM;
           if (next_m0 != m0)
             for (uint32_t kb = 0; kb < k_blocks; ++kb)
               asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
@@ -444,7 +470,9 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t lt = 0;
     for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++lt) {
       const uint32_t buf = lt & 1, use = lt >> 1;
-      const uint32_t m0 = (t / tiles_n) * kBlockM, n0 = (t % tiles_n) * kPBlockN;
+      uint32_t mb, nb;
+      TileCoord(t, tiles_m, tiles_n, band_blocks, &mb, &nb);
+      const uint32_t m0 = mb * kBlockM, n0 = nb * kPBlockN;
       bool ok = MbarWait(&bars->tmem_full[buf], use & 1);
       if (!ok && lane == 0) { ep.status->wait_timeout = 1; bars->abort = 1; }
       if (bars->abort) ok = false;
@@ -582,7 +610,8 @@ cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
   const uint32_t ptiles_n = (ep.N + kPBlockN - 1) / kPBlockN;
   if (static_cast<uint64_t>(ptiles_n) * tiles_m > 2ull * sms) {
     // Enough tiles for every SM to amortise its set-up over several.
-    UmmaGemmPersistentKernel<<<sms, kPThreads, psmem, s>>>(map_a, map_b, ep);
+    const uint32_t band = ptiles_n >= kWideTilesN ? kWideBandBlocks : 1u;
+    UmmaGemmPersistentKernel<<<sms, kPThreads, psmem, s>>>(map_a, map_b, ep, band);
     return cudaGetLastError();
   }
   dim3 grid(tiles_n, tiles_m);
