@@ -29,7 +29,7 @@ CU_SOURCES = {
     "k_attention.cu": ["-fmad=false"],
     "k_gemm_exact.cu": ["-fmad=false"],
     "k_gemm_skinny.cu": ["-fmad=false"],
-    "k_gemm_umma.cu": [],
+    "k_gemm_umma.cu": ["-fmad=false"],
     "k_eval.cu": [],
     "k_attn_umma.cu": [],
     "k_no_alloc.cu": ["-fmad=false"],

@@ -366,11 +366,15 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
   PlanShadows(program, begin, std::min(end, program.size()));
   PlanAdamGroups(program, begin, std::min(end, program.size()));
   PlanBiasFusions(program, begin, std::min(end, program.size()));
+  PlanActFusions(program, begin, std::min(end, program.size()));
 }
 
 void CudaBackend::EndRange() {
   bias_fusion_.clear();
   skip_next_add_bias_ = false;
+  act_fusion_.clear();
+  skip_act_at_ = -1;
+  elided_.clear();
   shadow_plan_.clear();
   adam_group_of_.clear();
   adam_groups_.clear();
@@ -576,6 +580,137 @@ void CudaBackend::PlanBiasFusions(std::span<const Instruction> program, size_t b
   }
 }
 
+namespace {
+
+bool IsRelaxedFrozenGemm(const Instruction& g) {
+  const uint16_t op = g.opcode;
+  const bool gemm = op == kGemmNN || op == kGemmNT || op == kGemmNNQ8 || op == kGemmNTQ8 ||
+                    op == kGemmNNBF16 || op == kGemmNTBF16;
+  if (!gemm || !(g.flags & kFlagRelaxed) || RefSpace(g.in[1]) == kArena || RefSpace(g.in[0]) != kArena)
+    return false;
+  const uint64_t M = g.out[0], N = g.out[1], K = g.out[2];
+  return K % 8 == 0 && N % 4 == 0 && K >= 64 && N >= 16 && M >= 64;   // TryGemm's domain
+}
+
+uint64_t GemmScaleKey(const Instruction& g) {
+  return g.opcode == kGemmNTQ8 && (g.flags & kFlagQ8ColScale) ? RefOffset(g.in[3]) : ~0ull;
+}
+
+}  // namespace
+
+// True when every byte of arena range [lo, hi) is overwritten by instructions
+// start.. of the range before anything reads it — except, when `key` is given,
+// relaxed GEMMs whose A operand is exactly that range under that copy key (they
+// take the bf16 copy), and only while nothing has written into the range yet.
+static bool DeadFrom(std::span<const Instruction> program, const std::vector<Extents>& ext, size_t begin,
+                     size_t end, size_t start, uint64_t lo, uint64_t hi, uint64_t key_scale, bool allow_consumers,
+                     uint64_t M, uint64_t K) {
+  using Interval = std::pair<uint64_t, uint64_t>;
+  std::vector<Interval> unknown{{lo, hi}};
+  bool written = false;
+  for (size_t j = start; j < end; ++j) {
+    const Extents& e = ext[j - begin];
+    const Instruction& ins = program[j];
+    for (size_t x = 0; x < e.count; ++x) {
+      if (e.e[x].space != kArena) continue;
+      const uint64_t elo = e.e[x].off, ehi = elo + e.e[x].bytes;
+      if (e.e[x].write && !e.e[x].read) continue;
+      bool hits = false;
+      for (const Interval& u : unknown)
+        if (elo < u.second && u.first < ehi) { hits = true; break; }
+      if (!hits) continue;
+      const bool consumer = allow_consumers && !written && !e.e[x].write && IsRelaxedFrozenGemm(ins) &&
+                            RefOffset(ins.in[0]) == lo && elo == lo && ehi == hi && ins.out[0] == M &&
+                            ins.out[2] == K && GemmScaleKey(ins) == key_scale;
+      if (!consumer) return false;
+    }
+    for (size_t x = 0; x < e.count; ++x) {
+      if (e.e[x].space != kArena || !e.e[x].write) continue;
+      const uint64_t elo = e.e[x].off, ehi = elo + e.e[x].bytes;
+      if (elo < hi && lo < ehi) written = true;
+      std::vector<Interval> rest;
+      for (const Interval& u : unknown) {
+        if (ehi <= u.first || u.second <= elo) { rest.push_back(u); continue; }
+        if (u.first < elo) rest.push_back({u.first, elo});
+        if (ehi < u.second) rest.push_back({ehi, u.second});
+      }
+      unknown.swap(rest);
+    }
+    if (unknown.empty()) return true;
+  }
+  return false;
+}
+
+void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t begin, size_t end) {
+  act_fusion_.assign(end > begin ? end - begin : 0, ActFusion{});
+  if (coherence_ == Coherence::kStrict || !relaxed_allowed_ || end < begin + 3) return;
+  std::vector<Extents> ext(end - begin);
+  for (size_t i = begin; i < end; ++i)
+    if (!DescribeInstruction(program[i], arena_bytes_, rodata_bytes_, source_bytes_, &ext[i - begin]).empty())
+      return;   // a malformed instruction: leave everything as it is
+  auto disjoint = [](uint64_t alo, uint64_t ahi, uint64_t blo, uint64_t bhi) { return ahi <= blo || bhi <= alo; };
+  for (size_t i = begin; i + 1 < end; ++i) {
+    const Instruction& g = program[i];
+    if (!IsRelaxedFrozenGemm(g) || RefSpace(g.in[2]) != kArena) continue;
+    if ((g.flags & (kFlagEpilogueBias | kFlagGemmAddend)) || ActOf(g.flags) != kActNone) continue;
+    const uint64_t M = g.out[0], N = g.out[1], bytes = M * N * 4;
+    size_t next = i + 1;
+    uint64_t z_ref = g.in[2];
+    if (bias_fusion_[i - begin].fuse) {
+      z_ref = bias_fusion_[i - begin].out_ref;
+      next = i + 2;
+    }
+    if (next >= end) continue;
+    const Instruction& act = program[next];
+    const uint16_t aop = act.opcode;
+    const bool fwd = aop == kReluFwd || aop == kGeluFwd || aop == kSiluFwd;
+    const bool bwd = aop == kReluBwd || aop == kGeluBwd || aop == kSiluBwd;
+    if ((!fwd && !bwd) || act.in[0] != z_ref || act.out[0] != M * N) continue;
+    const uint64_t out_ref = fwd ? act.in[1] : act.in[2];
+    if (RefSpace(out_ref) != kArena) continue;
+    const ShadowPlan& sp = shadow_plan_[next - begin];
+    if (!sp.want || sp.a_off != RefOffset(out_ref) || sp.M != M || sp.K != N) continue;
+    if (sp.scale_ref != kNullRef && (sp.scale_off & 15) != 0) continue;
+    const uint64_t z_lo = RefOffset(z_ref), z_hi = z_lo + bytes;
+    const uint64_t o_lo = RefOffset(out_ref), o_hi = o_lo + bytes;
+    ActFusion f;
+    f.act = aop == kReluFwd || aop == kReluBwd ? kActRelu : aop == kGeluFwd || aop == kGeluBwd ? kActGelu : kActSilu;
+    f.act_index = static_cast<uint32_t>(next - begin);
+    if (fwd) {
+      if (!disjoint(z_lo, z_hi, o_lo, o_hi)) continue;
+      if (!DeadFrom(program, ext, begin, end, next + 1, o_lo, o_hi, sp.scale_off, true, M, N)) continue;
+      f.mode = k::kFuseActFwd;
+      f.store_c = true;
+      f.elided[0][0] = o_lo; f.elided[0][1] = o_hi;
+      f.elided_count = 1;
+    } else {
+      if (RefSpace(act.in[1]) != kArena || (RefOffset(act.in[1]) & 15) != 0) continue;
+      const uint64_t x_lo = RefOffset(act.in[1]), x_hi = x_lo + bytes;
+      if (!disjoint(x_lo, x_hi, z_lo, z_hi) || !disjoint(x_lo, x_hi, o_lo, o_hi)) continue;
+      const bool in_place = o_lo == z_lo;
+      if (!in_place && !disjoint(z_lo, z_hi, o_lo, o_hi)) continue;
+      if (!DeadFrom(program, ext, begin, end, next + 1, o_lo, o_hi, sp.scale_off, true, M, N)) continue;
+      f.mode = k::kFuseActBwd;
+      f.x_ref = act.in[1];
+      f.elided[0][0] = o_lo; f.elided[0][1] = o_hi;
+      f.elided_count = 1;
+      if (in_place) {
+        f.store_c = false;
+      } else {
+        f.store_c = !DeadFrom(program, ext, begin, end, next + 1, z_lo, z_hi, ~0ull, false, 0, 0);
+        if (!f.store_c) {
+          f.elided[1][0] = z_lo; f.elided[1][1] = z_hi;
+          f.elided_count = 2;
+        }
+      }
+    }
+    act_fusion_[i - begin] = f;
+    // The GEMM is now the producer of the copy the activation would have made.
+    shadow_plan_[i - begin] = sp;
+    shadow_plan_[next - begin].want = false;
+  }
+}
+
 const k::Shadow* CudaBackend::ShadowFor(uint64_t out_ref, uint64_t elems) const {
   if (!cur_shadow_.dst || RefSpace(out_ref) != kArena || RefOffset(out_ref) != cur_plan_.a_off ||
       elems != cur_plan_.M * cur_plan_.K)
@@ -650,8 +785,39 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   if (ins.opcode != kAddBias) skip_next_add_bias_ = false;
   cur_shadow_ = k::Shadow{};
   shadow_written_ = false;
+  umma::ReleaseReservations(&umma_->ctx);
+  // An activation absorbed by the preceding product: nothing runs and nothing is
+  // written, so the copy the product published under this output's key stays.
+  const bool absorbed = skip_act_at_ == static_cast<int64_t>(range_index_);
+  if (absorbed) skip_act_at_ = -1;
+  if (!elided_.empty() && !absorbed) {
+    for (size_t i = 0; i < ext.count; ++i) {
+      const Extent& e = ext.e[i];
+      if (e.space != kArena || (e.write && !e.read)) continue;
+      bool hits = false;
+      for (const auto& [lo, hi] : elided_)
+        if (e.off < hi && lo < e.off + e.bytes) hits = true;
+      if (!hits) continue;
+      const bool gemm_a = (ins.flags & kFlagRelaxed) && relaxed_allowed_ && RefSpace(ins.in[0]) == kArena &&
+                          RefOffset(ins.in[0]) == e.off && !e.write &&
+                          (ins.opcode == kGemmNN || ins.opcode == kGemmNT || ins.opcode == kGemmNNQ8 ||
+                           ins.opcode == kGemmNTQ8 || ins.opcode == kGemmNNBF16 || ins.opcode == kGemmNTBF16) &&
+                          umma::TouchActCopy(&umma_->ctx, e.off,
+                                             ins.opcode == kGemmNTQ8 && (ins.flags & kFlagQ8ColScale)
+                                                 ? RefOffset(ins.in[3]) : ~0ull,
+                                             ins.out[0], ins.out[2]);
+      if (!gemm_a)
+        return std::unexpected(std::string("cuda: ") + OpName(ins.opcode) +
+                               " reads an activation whose f32 form an epilogue fusion left unwritten");
+    }
+  }
   if (range_index_ < shadow_plan_.size() && shadow_plan_[range_index_].want) {
     cur_plan_ = shadow_plan_[range_index_];
+    if (range_index_ < act_fusion_.size() && act_fusion_[range_index_].mode != 0)
+      // The product reads one copy and writes another: keep its operand's slot.
+      umma::TouchActCopy(&umma_->ctx, RefOffset(ins.in[0]),
+                         ins.opcode == kGemmNTQ8 && (ins.flags & kFlagQ8ColScale) ? RefOffset(ins.in[3]) : ~0ull,
+                         ins.out[0], ins.out[2]);
     if (uint16_t* buf = umma::ReserveShadow(&umma_->ctx, cur_plan_.M * cur_plan_.K)) {
       cur_shadow_.dst = buf;
       cur_shadow_.k_scale = cur_plan_.scale_ref == kNullRef ? nullptr : Rd(cur_plan_.scale_ref);
@@ -659,7 +825,8 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
     }
   }
 
-  if (auto r = Dispatch(ins, params, ext); !r) return r;
+  if (!absorbed)
+    if (auto r = Dispatch(ins, params, ext); !r) return r;
   ++counters_.instructions;
 
   if (profiling_) {
@@ -674,11 +841,20 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   }
   ++range_index_;
 
-  for (size_t i = 0; i < ext.count; ++i) {
+  for (size_t i = 0; i < ext.count && !absorbed; ++i) {
     const Extent& e = ext.e[i];
     if (!e.write) continue;
     umma::InvalidateRange(&umma_->ctx, e.off, e.bytes);
     if (coherence_ == Coherence::kStrict) MergeExtent(&device_dirty_, e.off, e.bytes);
+    if (!elided_.empty() && e.space == kArena) {   // written for real: no longer stale
+      std::vector<std::pair<uint64_t, uint64_t>> rest;
+      for (const auto& [lo, hi] : elided_) {
+        if (e.off + e.bytes <= lo || hi <= e.off) { rest.push_back({lo, hi}); continue; }
+        if (lo < e.off) rest.push_back({lo, e.off});
+        if (e.off + e.bytes < hi) rest.push_back({e.off + e.bytes, hi});
+      }
+      elided_.swap(rest);
+    }
   }
   if (shadow_written_)   // after the instruction's own writes have invalidated the range
     umma::CommitShadow(&umma_->ctx, cur_shadow_.dst, cur_plan_.a_off, cur_plan_.scale_off,
@@ -723,6 +899,16 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
       a.bias = Rd(fuse->bias_ref);
       a.C = Wr(fuse->out_ref);
     }
+    const ActFusion* af = range_index_ < act_fusion_.size() && act_fusion_[range_index_].mode != 0 &&
+                                  cur_shadow_.dst ? &act_fusion_[range_index_] : nullptr;
+    if (af) {   // and the activation after it: its result leaves as the consumer's bf16 operand
+      a.fuse_mode = af->mode;
+      a.fuse_act = af->act;
+      a.fuse_x = af->x_ref == kNullRef ? nullptr : Rd(af->x_ref);
+      a.fuse_shadow = cur_shadow_.dst;
+      a.fuse_shadow_scale = cur_shadow_.k_scale;
+      a.store_c = af->store_c;
+    }
     int launches = 0;
     const std::string err = umma::TryGemm(&umma_->ctx, a, RefSpace(ins.in[1]) == kRodata ? 1 : 2,
                                           RefOffset(ins.in[1]), RefOffset(ins.in[0]),
@@ -732,6 +918,11 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
       ++counters_.relaxed_executions;
       counters_.kernel_launches += launches;
       skip_next_add_bias_ = fuse != nullptr;
+      if (af) {
+        shadow_written_ = true;
+        skip_act_at_ = static_cast<int64_t>(af->act_index);
+        for (int e = 0; e < af->elided_count; ++e) elided_.push_back({af->elided[e][0], af->elided[e][1]});
+      }
       return {};
     }
     if (!err.empty()) return std::unexpected("cuda: " + err);
@@ -740,6 +931,11 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
       a.bias = nullptr;
       a.C = Wr(ins.in[2]);
     }
+    a.fuse_mode = 0;
+    a.fuse_x = nullptr;
+    a.fuse_shadow = nullptr;
+    a.fuse_shadow_scale = nullptr;
+    a.store_c = true;
   }
   // The split-K scratch is sized per range (BeginRange); an instruction executed
   // outside any range simply runs unsplit.

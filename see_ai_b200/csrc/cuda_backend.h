@@ -237,6 +237,28 @@ class CudaBackend {
   k::Shadow cur_shadow_;
   bool shadow_written_ = false;
 
+  // An activation instruction that follows a relaxed GEMM (directly, or after
+  // the kAddBias fused above) and reads its output, done in the GEMM's epilogue
+  // when the activation's f32 output is read by nothing but the relaxed GEMM(s)
+  // that take its bf16 operand copy before every byte of it is overwritten: the
+  // epilogue writes that copy and the f32 tensor is never materialised.  For a
+  // backward activation the GEMM's own output (dy) is left unwritten too when it
+  // is dead.  Engine / lazy coherence only.  elided_ lists the f32 ranges left
+  // stale; any other read of them is refused (a guard behind the static proof).
+  struct ActFusion {
+    int mode = 0;                 // k::kFuseNone / kFuseActFwd / kFuseActBwd
+    Act act = kActNone;
+    uint32_t act_index = 0;       // range position of the absorbed instruction
+    uint64_t x_ref = kNullRef;    // backward: the forward input
+    bool store_c = true;
+    uint64_t elided[2][2] = {{0, 0}, {0, 0}};   // [lo, hi) byte ranges
+    int elided_count = 0;
+  };
+  void PlanActFusions(std::span<const Instruction> program, size_t begin, size_t end);
+  std::vector<ActFusion> act_fusion_;   // per range position (of the GEMM)
+  int64_t skip_act_at_ = -1;
+  std::vector<std::pair<uint64_t, uint64_t>> elided_;
+
   Counters counters_;
   struct UmmaState;
   std::unique_ptr<UmmaState> umma_;

@@ -5,6 +5,7 @@
 // add / mul / bias / scale / relu / accumulate / fill / copy / gather results
 // are bit-identical to the CPU executor's; tanh / exp based activations agree
 // to libm-vs-CUDA-libm differences (a few ulp).
+#include "act_expr.cuh"
 #include "kernels.h"
 #include "shadow.cuh"
 
@@ -24,32 +25,6 @@ inline int BlocksFor(size_t work_items) {
 }
 
 inline bool Aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
-
-// ---- activation expressions (reference: runtime/executor/kernel_policy.h:122-136,
-// runtime/executor/activation.cc:22-75) ---------------------------------------
-constexpr float kGeluC = 0.7978845608028654f;
-constexpr float kGeluA = 0.044715f;
-
-__device__ __forceinline__ float SigmoidExpr(float x) { return 1.0f / (1.0f + expf(-x)); }
-__device__ __forceinline__ float ReluExpr(float x) { return x > 0.0f ? x : 0.0f; }
-__device__ __forceinline__ float GeluExpr(float x) {
-  const float t = tanhf(kGeluC * (x + kGeluA * x * x * x));
-  return 0.5f * x * (1.0f + t);
-}
-__device__ __forceinline__ float SiluExpr(float x) { return x * SigmoidExpr(x); }
-__device__ __forceinline__ float GeluGrad(float dy, float v) {
-  const float u = kGeluC * (v + kGeluA * v * v * v);
-  const float t = tanhf(u);
-  const float one_minus_t2 = 1.0f - t * t;
-  const float tail = one_minus_t2 == 0.0f
-                         ? 0.0f
-                         : 0.5f * v * one_minus_t2 * (kGeluC * (1.0f + 3.0f * kGeluA * v * v));
-  return dy * (0.5f * (1.0f + t) + tail);
-}
-__device__ __forceinline__ float SiluGrad(float dy, float x) {
-  const float s = SigmoidExpr(x);
-  return dy * (s * (1.0f + x * (1.0f - s)));
-}
 
 // ---- generic maps -------------------------------------------------------------
 template <typename F>
@@ -105,7 +80,7 @@ struct IdF { __device__ float operator()(float a) const { return a; } };
 struct ReluF { __device__ float operator()(float a) const { return ReluExpr(a); } };
 struct GeluF { __device__ float operator()(float a) const { return GeluExpr(a); } };
 struct SiluF { __device__ float operator()(float a) const { return SiluExpr(a); } };
-struct ReluBwdF { __device__ float operator()(float dy, float x) const { return x > 0.0f ? dy : 0.0f; } };
+struct ReluBwdF { __device__ float operator()(float dy, float x) const { return ReluGrad(dy, x); } };
 struct GeluBwdF { __device__ float operator()(float dy, float x) const { return GeluGrad(dy, x); } };
 struct SiluBwdF { __device__ float operator()(float dy, float x) const { return SiluGrad(dy, x); } };
 

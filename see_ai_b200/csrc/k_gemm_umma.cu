@@ -19,7 +19,9 @@
 // memory and returns, and the host reports the condition at its next flush.
 #include <cuda.h>
 
+#include "act_expr.cuh"
 #include "kernels.h"
+#include "shadow.cuh"
 #include "umma_kernel.h"
 
 namespace see::k {
@@ -38,8 +40,6 @@ constexpr uint32_t kTmemCols = kBlockN;           // f32 accumulator columns
 constexpr uint32_t kThreads = 192;                // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
 constexpr uint32_t kWaitLimit = 1u << 22;
 
-constexpr float kGeluC = 0.7978845608028654f;
-constexpr float kGeluA = 0.044715f;
 
 __device__ __forceinline__ uint32_t SmemAddr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -126,15 +126,36 @@ __device__ __forceinline__ void TmemLoad32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
 }
 
-__device__ __forceinline__ float ApplyAct(float v, int act) {
-  switch (act) {
-    case kActRelu: return v > 0.0f ? v : 0.0f;
-    case kActGelu: {
-      const float t = tanhf(kGeluC * (v + kGeluA * v * v * v));
-      return 0.5f * v * (1.0f + t);
+__device__ __forceinline__ float ApplyAct(float v, int act) { return ActFwdExpr(act, v); }
+
+// The tail of both epilogues: four neighbouring columns n.. of row (at / N).
+__device__ __forceinline__ void EpilogueStore(const UmmaEpilogue& ep, size_t at, uint32_t n, const float4& acc,
+                                              const float4& scale, const float4& bias) {
+  float4 v = make_float4(acc.x * scale.x, acc.y * scale.y, acc.z * scale.z, acc.w * scale.w);
+  if (ep.addend) {
+    const float4 d = __ldg(reinterpret_cast<const float4*>(ep.addend + at));
+    v = make_float4(d.x + v.x, d.y + v.y, d.z + v.z, d.w + v.w);
+  }
+  if (ep.bias) v = make_float4(v.x + bias.x, v.y + bias.y, v.z + bias.z, v.w + bias.w);
+  if (ep.act != kActNone)
+    v = make_float4(ApplyAct(v.x, ep.act), ApplyAct(v.y, ep.act), ApplyAct(v.z, ep.act),
+                    ApplyAct(v.w, ep.act));
+  if (ep.store_c) *reinterpret_cast<float4*>(ep.C + at) = v;
+  if (ep.fuse_mode != kFuseNone) {
+    float4 g;
+    if (ep.fuse_mode == kFuseActFwd) {
+      g = make_float4(ActFwdExpr(ep.fuse_act, v.x), ActFwdExpr(ep.fuse_act, v.y), ActFwdExpr(ep.fuse_act, v.z),
+                      ActFwdExpr(ep.fuse_act, v.w));
+    } else {
+      const float4 x = __ldg(reinterpret_cast<const float4*>(ep.fuse_x + at));
+      g = make_float4(ActBwdExpr(ep.fuse_act, v.x, x.x), ActBwdExpr(ep.fuse_act, v.y, x.y),
+                      ActBwdExpr(ep.fuse_act, v.z, x.z), ActBwdExpr(ep.fuse_act, v.w, x.w));
     }
-    case kActSilu: return v * (1.0f / (1.0f + expf(-v)));
-    default: return v;
+    Shadow sh;
+    sh.dst = ep.shadow_dst;
+    sh.k_scale = ep.shadow_k_scale;
+    sh.cols = ep.N;
+    ShadowStore4(sh, at / 4, n, g);
   }
 }
 
@@ -264,16 +285,7 @@ UmmaGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (uint32_t rr = 0; rr < rows; ++rr) {
           const float4 acc = *reinterpret_cast<const float4*>(slab + rr * kBlockN + ((lane ^ rr) * 4));
           const size_t at = static_cast<size_t>(row0 + rr) * ep.N + n;
-          float4 v = make_float4(acc.x * scale.x, acc.y * scale.y, acc.z * scale.z, acc.w * scale.w);
-          if (ep.addend) {
-            const float4 d = __ldg(reinterpret_cast<const float4*>(ep.addend + at));
-            v = make_float4(d.x + v.x, d.y + v.y, d.z + v.z, d.w + v.w);
-          }
-          if (ep.bias) v = make_float4(v.x + bias.x, v.y + bias.y, v.z + bias.z, v.w + bias.w);
-          if (ep.act != kActNone)
-            v = make_float4(ApplyAct(v.x, ep.act), ApplyAct(v.y, ep.act), ApplyAct(v.z, ep.act),
-                            ApplyAct(v.w, ep.act));
-          *reinterpret_cast<float4*>(ep.C + at) = v;
+          EpilogueStore(ep, at, n, acc, scale, bias);
         }
       }
     }
@@ -515,16 +527,7 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
             const float4 acc = *reinterpret_cast<const float4*>(
                 slab + rr * kSlabCols + ((cl ^ (rr & (kChunks - 1))) * 4));
             const size_t at = static_cast<size_t>(row0 + rr) * ep.N + n;
-            float4 v = make_float4(acc.x * scale.x, acc.y * scale.y, acc.z * scale.z, acc.w * scale.w);
-            if (ep.addend) {
-              const float4 d = __ldg(reinterpret_cast<const float4*>(ep.addend + at));
-              v = make_float4(d.x + v.x, d.y + v.y, d.z + v.z, d.w + v.w);
-            }
-            if (ep.bias) v = make_float4(v.x + bias.x, v.y + bias.y, v.z + bias.z, v.w + bias.w);
-            if (ep.act != kActNone)
-              v = make_float4(ApplyAct(v.x, ep.act), ApplyAct(v.y, ep.act), ApplyAct(v.z, ep.act),
-                              ApplyAct(v.w, ep.act));
-            *reinterpret_cast<float4*>(ep.C + at) = v;
+            EpilogueStore(ep, at, n, acc, scale, bias);
           }
         }
         __syncwarp();   // the slab is rewritten next

@@ -169,6 +169,7 @@ void CountNonFinite(const float* x, size_t n, unsigned long long* tally, cudaStr
 
 // ---- GEMM -------------------------------------------------------------------
 enum class BType : uint8_t { kF32 = 0, kI8 = 1, kBf16 = 2 };
+constexpr int kFuseNone = 0, kFuseActFwd = 1, kFuseActBwd = 2;   // GemmArgs::fuse_mode
 struct GemmArgs {
   const float* A = nullptr;    // [M,K], or [K,M] when a_transposed
   const void* B = nullptr;     // [K,N], or [N,K] when b_transposed
@@ -183,6 +184,15 @@ struct GemmArgs {
   const float* addend = nullptr;
   Act act = kActNone;
   bool accumulate = false;  // C += (the merge program's form)
+  // Tensor-core path only: a following activation instruction done in the
+  // epilogue (see UmmaEpilogue); its result leaves as the bf16 operand copy
+  // fuse_shadow of the product that consumes it.
+  int fuse_mode = 0;
+  Act fuse_act = kActNone;
+  const float* fuse_x = nullptr;
+  uint16_t* fuse_shadow = nullptr;
+  const float* fuse_shadow_scale = nullptr;
+  bool store_c = true;
   // Scratch for the split-K form of the transposed-A product (optional).
   float* split_scratch = nullptr;
   size_t split_scratch_floats = 0;

@@ -29,6 +29,7 @@ using WeightKey = std::tuple<int, uint64_t, uint64_t, uint64_t, bool, int>;
 struct ActCopy {   // a bf16 copy of an arena activation [M, K]
   uint64_t a_off = ~0ull, scale_off = ~0ull, M = 0, K = 0;
   bool valid = false;
+  bool reserved = false;   // handed to a producer (ReserveShadow) and not yet committed
   uint16_t* buf = nullptr;
   uint64_t capacity = 0;  // elements
   uint64_t last_use = 0;
@@ -238,11 +239,14 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
     if (c.valid && c.a_off == a_off && c.scale_off == a_scale_off && c.M == a.M && c.K == a.K)
       slot = &c;
   if (!slot) {
-    slot = &impl->acts[0];
+    // A slot a producer is writing (this product's own epilogue, when it has
+    // absorbed a following activation) is not a candidate.
     for (auto& c : impl->acts) {
+      if (c.reserved) continue;
       if (!c.valid) { slot = &c; break; }
-      if (c.last_use < slot->last_use) slot = &c;
+      if (!slot || c.last_use < slot->last_use) slot = &c;
     }
+    if (!slot) return "tensor-core path: no activation copy slot free";
     const uint64_t need = a.M * a.K;
     if (slot->capacity < need) {
       // Replacing the buffer: queued kernels may still read the old one.
@@ -278,6 +282,12 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
   ep.N = static_cast<uint32_t>(a.N);
   ep.K = static_cast<uint32_t>(a.K);
   ep.status = impl->status;
+  ep.fuse_mode = a.fuse_mode;
+  ep.fuse_act = static_cast<int>(a.fuse_act);
+  ep.fuse_x = a.fuse_x;
+  ep.shadow_dst = a.fuse_shadow;
+  ep.shadow_k_scale = a.fuse_shadow_scale;
+  ep.store_c = a.store_c ? 1 : 0;
   if (impl->prof_before) cudaEventRecord(impl->prof_before, stream);
   if (cudaError_t e = k::UmmaGemmLaunch(map_a, map_b, ep, stream); e != cudaSuccess)
     return std::string("tensor-core GEMM launch: ") + cudaGetErrorString(e);
@@ -290,17 +300,35 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
   return {};
 }
 
+bool TouchActCopy(Context* ctx, uint64_t a_off, uint64_t a_scale_off, uint64_t M, uint64_t K) {
+  Impl* impl = ctx->impl;
+  if (!impl) return false;
+  for (auto& c : impl->acts)
+    if (c.valid && c.a_off == a_off && c.scale_off == a_scale_off && c.M == M && c.K == K) {
+      c.last_use = ++impl->tick;
+      return true;
+    }
+  return false;
+}
+
+void ReleaseReservations(Context* ctx) {
+  if (!ctx->impl) return;
+  for (auto& c : ctx->impl->acts) c.reserved = false;
+}
+
 uint16_t* ReserveShadow(Context* ctx, uint64_t elems) {
   Impl* impl = ctx->impl;
   if (!impl) return nullptr;
   ActCopy* slot = nullptr;
   for (auto& c : impl->acts) {
+    c.reserved = false;   // one reservation at a time
     if (c.capacity < elems || !c.buf) continue;
     if (!c.valid) { slot = &c; break; }
     if (!slot || c.last_use < slot->last_use) slot = &c;
   }
   if (!slot) return nullptr;
   slot->valid = false;
+  slot->reserved = true;
   slot->last_use = ++impl->tick;   // not the next victim while its producer runs
   return slot->buf;
 }
@@ -313,6 +341,7 @@ void CommitShadow(Context* ctx, uint16_t* buf, uint64_t a_off, uint64_t a_scale_
     if (c.buf != buf) continue;
     c.a_off = a_off; c.scale_off = a_scale_off; c.M = M; c.K = K;
     c.valid = true;
+    c.reserved = false;
     c.last_use = ++impl->tick;
   }
 }

@@ -49,6 +49,11 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& args, int b_space, uint64_t
 // publishes the slot under the key TryGemm looks up (arena offset, scale offset,
 // M, K).  A reservation that is not committed is simply reused later.
 uint16_t* ReserveShadow(Context* ctx, uint64_t elems);
+// True when a valid copy with this key exists; marks it most recently used (so
+// the next ReserveShadow does not take its slot).
+bool TouchActCopy(Context* ctx, uint64_t a_off, uint64_t a_scale_off, uint64_t M, uint64_t K);
+// Drops a reservation that was never committed.
+void ReleaseReservations(Context* ctx);
 void CommitShadow(Context* ctx, uint16_t* buf, uint64_t a_off, uint64_t a_scale_off, uint64_t M,
                   uint64_t K);
 

@@ -26,6 +26,18 @@ struct UmmaEpilogue {
   int act;
   uint32_t M, N, K;
   DeviceStatus* status;
+  // A following activation instruction absorbed into this epilogue.  With v the
+  // value above (after scale, addend, bias, act):
+  //   kFuseActFwd: g = act(v);          kFuseActBwd: g = act'(dy = v, x = fuse_x[m, n]).
+  // g leaves only as the bf16 operand copy of the GEMM that consumes it
+  // (shadow_dst, [M, N], times shadow_k_scale[n] when set); v itself is stored to
+  // C only when store_c is set.
+  int fuse_mode = 0;
+  int fuse_act = 0;
+  const float* fuse_x = nullptr;
+  uint16_t* shadow_dst = nullptr;
+  const float* shadow_k_scale = nullptr;
+  int store_c = 1;
 };
 
 size_t UmmaSmemBytes();

@@ -68,3 +68,94 @@ def test_bias_add_rides_the_gemm_epilogue_only_when_the_product_is_dead(later_re
     # compare launches directly: fused drops exactly the kAddBias kernel.
     saved = c_split.kernel_launches - c_fused.kernel_launches
     assert saved == (0 if later_read else 1)
+
+
+# ---- activation absorbed into the producing GEMM's epilogue ---------------------------
+# GEMM (-> kAddBias) -> activation -> GEMM: when the activation's f32 output is
+# read by nothing but the relaxed GEMM that takes its bf16 copy, the first GEMM's
+# epilogue writes that copy and the activation launches nothing.  Sizes: one that
+# runs the one-tile kernel and one that runs the persistent kernel.
+
+ACT_SIZES = [(256, 128, 192), (4864, 64, 2048)]
+
+
+def _build_act_fwd(rng, M, K, N, read_g_later):
+    a = Arena(rng)
+    x = a.alloc(M * K, "normal")
+    w1 = a.ro_alloc(rng.integers(-127, 128, size=K * N, dtype=np.int8))
+    sc1 = a.ro_alloc((rng.random(N) * 0.01 + 1e-3).astype(np.float32))
+    bias = a.ro_alloc(rng.standard_normal(N).astype(np.float32))
+    N2 = 64
+    w2 = a.ro_alloc(rng.integers(-127, 128, size=N * N2, dtype=np.int8))
+    sc2 = a.ro_alloc((rng.random(N2) * 0.01 + 1e-3).astype(np.float32))
+    r = a.alloc(M * N); z = a.alloc(M * N); g = a.alloc(M * N); keep = a.alloc(M * N)
+    h = a.alloc(M * N2)
+    prog = [
+        P.Instr(Op.GEMM_NN_Q8, REL | CS, 0, (x, w1, r, sc1), (M, N, K)),
+        P.Instr(Op.ADD_BIAS, 0, 0, (r, bias, z, P.NULL_REF), (M, N, 0)),
+        P.Instr(Op.GELU_FWD, 0, 0, (z, g), (M * N, 0, 0)),
+        P.Instr(Op.GEMM_NN_Q8, REL | CS, 0, (g, w2, h, sc2), (M, N2, N)),
+    ]
+    if read_g_later:
+        prog.append(P.Instr(Op.COPY, 0, 0, (g, keep), (M * N, 0, 0)))
+    prog.append(P.Instr(Op.FILL, 0, 0, (r, P.f32_bits(0.0)), (M * N, 0, 0)))
+    prog.append(P.Instr(Op.FILL, 0, 0, (g, P.f32_bits(0.0)), (M * N, 0, 0)))
+    arena, ro = a.build()
+    return prog, arena, ro
+
+
+@pytest.mark.parametrize("size", ACT_SIZES, ids=["one-tile", "persistent"])
+@pytest.mark.parametrize("later_read", [False, True], ids=["dead", "read-later"])
+def test_forward_activation_rides_the_gemm_epilogue_only_when_its_f32_output_is_dead(size, later_read):
+    M, K, N = size
+    prog, arena0, ro = _build_act_fwd(np.random.default_rng(17), M, K, N, later_read)
+    fused, c_fused = _run(prog, arena0, ro, one_range=True)
+    split, c_split = _run(prog, arena0, ro, one_range=False)
+    assert np.isfinite(fused.view(np.float32)).all()
+    assert np.array_equal(fused, split)
+    saved = c_split.kernel_launches - c_fused.kernel_launches
+    # kAddBias in the epilogue (1) and the second GEMM's conversion pass (1) are
+    # saved either way; the activation kernel itself (1) only when g is dead.
+    assert saved == (2 if later_read else 3)
+
+
+def _build_act_bwd(rng, M, K, N, read_dy_later, read_dx_later):
+    a = Arena(rng)
+    up = a.alloc(M * K, "normal")
+    x = a.alloc(M * N, "normal")
+    w1 = a.ro_alloc(rng.integers(-127, 128, size=N * K, dtype=np.int8))      # [N][K]
+    sck = a.ro_alloc((2.0 ** rng.integers(-9, -5, size=K)).astype(np.float32))
+    N2 = 64
+    w2 = a.ro_alloc(rng.integers(-127, 128, size=N2 * N, dtype=np.int8))     # [N2][N]
+    sc2 = a.ro_alloc((rng.random(N) * 0.01 + 1e-3).astype(np.float32))       # per-k scale of the consumer
+    dy = a.alloc(M * N); dx = a.alloc(M * N); keep = a.alloc(M * N); out = a.alloc(M * N2)
+    prog = [
+        P.Instr(Op.GEMM_NT_Q8, REL | CS, 0, (up, w1, dy, sck), (M, N, K)),
+        P.Instr(Op.GELU_BWD, 0, 0, (dy, x, dx, P.NULL_REF), (M * N, 0, 0)),
+        P.Instr(Op.GEMM_NT_Q8, REL | CS, 0, (dx, w2, out, sc2), (M, N2, N)),
+    ]
+    if read_dy_later:
+        prog.append(P.Instr(Op.COPY, 0, 0, (dy, keep), (M * N, 0, 0)))
+    if read_dx_later:
+        prog.append(P.Instr(Op.COPY, 0, 0, (dx, keep), (M * N, 0, 0)))
+    prog.append(P.Instr(Op.FILL, 0, 0, (dy, P.f32_bits(0.0)), (M * N, 0, 0)))
+    prog.append(P.Instr(Op.FILL, 0, 0, (dx, P.f32_bits(0.0)), (M * N, 0, 0)))
+    arena, ro = a.build()
+    return prog, arena, ro
+
+
+@pytest.mark.parametrize("size", ACT_SIZES, ids=["one-tile", "persistent"])
+@pytest.mark.parametrize("case", ["dead", "dy-read-later", "dx-read-later"])
+def test_backward_activation_rides_the_gemm_epilogue(size, case):
+    M, K, N = size
+    prog, arena0, ro = _build_act_bwd(np.random.default_rng(23), M, K, N, case == "dy-read-later",
+                                      case == "dx-read-later")
+    fused, c_fused = _run(prog, arena0, ro, one_range=True)
+    split, c_split = _run(prog, arena0, ro, one_range=False)
+    assert np.isfinite(fused.view(np.float32)).all()
+    assert np.array_equal(fused, split)
+    saved = c_split.kernel_launches - c_fused.kernel_launches
+    # The consumer's conversion pass is saved either way (producer-made copy); the
+    # activation kernel too unless its f32 output is read later.  A dy that is read
+    # later is still written by the epilogue (same launches saved).
+    assert saved == (1 if case == "dx-read-later" else 2)
