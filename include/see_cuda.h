@@ -91,6 +91,9 @@ int see_cuda_counters_get(see_cuda_backend* h, see_cuda_counters* out);
 int see_cuda_set_stream(see_cuda_backend* h, void* cuda_stream);     /* run on the caller's stream */
 void* see_cuda_device_arena(see_cuda_backend* h);                      /* device address of offset 0 */
 int see_cuda_set_relaxed_allowed(see_cuda_backend* h, int allowed);  /* 0: always the exact kernels */
+/* 0: every instruction is its own kernel(s) even in lazy coherence (no bias add or
+ * activation absorbed into a product's epilogue); default 1. */
+int see_cuda_set_epilogue_fusion(see_cuda_backend* h, int enabled);
 /* Data parallelism: optimizer steps read gradients inside [block_offset,
  * block_offset + block_bytes) as the rank-ordered sum of `ranks` gathered
  * copies (device memory, copy r at gathered + r * block_bytes) times 1/ranks. */

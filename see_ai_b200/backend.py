@@ -28,7 +28,8 @@ EXPORTED_SYMBOLS = [
     "see_cuda_begin_range", "see_cuda_execute", "see_cuda_end_range", "see_cuda_flush",
     "see_cuda_run_range", "see_cuda_set_coherence", "see_cuda_host_wrote",
     "see_cuda_host_needs", "see_cuda_counters_get", "see_cuda_set_stream",
-    "see_cuda_device_arena", "see_cuda_set_relaxed_allowed", "see_cuda_set_gradient_gather",
+    "see_cuda_device_arena", "see_cuda_set_relaxed_allowed", "see_cuda_set_epilogue_fusion",
+    "see_cuda_set_gradient_gather",
     "see_cuda_set_profiling", "see_cuda_take_profile",
     "see_cuda_xent_forward_static", "see_cuda_static_max_rows", "see_cuda_static_last_error",
 ]
@@ -96,6 +97,7 @@ def load_library() -> ctypes.CDLL:
     lib.see_cuda_device_arena.argtypes = [vp]
     lib.see_cuda_device_arena.restype = vp
     lib.see_cuda_set_relaxed_allowed.argtypes = [vp, i32]
+    lib.see_cuda_set_epilogue_fusion.argtypes = [vp, i32]
     lib.see_cuda_set_gradient_gather.argtypes = [vp, i32, vp, u64, u64]
     lib.see_cuda_set_profiling.argtypes = [vp, i32]
     lib.see_cuda_take_profile.argtypes = [vp, ctypes.POINTER(ProfileRecord), u64]
@@ -234,6 +236,9 @@ class CudaBackend:
 
     def set_relaxed_allowed(self, allowed: bool):
         self._check(self.lib.see_cuda_set_relaxed_allowed(self.h, int(allowed)))
+
+    def set_epilogue_fusion(self, enabled: bool):
+        self._check(self.lib.see_cuda_set_epilogue_fusion(self.h, int(enabled)))
 
     def set_gradient_gather(self, ranks: int, gathered_ptr: int, block_offset: int,
                             block_bytes: int):

@@ -13,22 +13,44 @@ namespace see::k {
 constexpr float kGeluExprC = 0.7978845608028654f;
 constexpr float kGeluExprA = 0.044715f;
 
+// GELU (tanh form) through the hardware exponential and reciprocal.  With
+// u = c (x + a x^3) and r = 1 / (1 + e^{2u}):  tanh u = 1 - 2r, so
+// 0.5 x (1 + tanh u) = x - x r.  Absolute error a few 1e-7 of |x| (the reference
+// differ's bound for these rows is 1e-5 of the tensor's magnitude); saturates
+// exactly, keeps NaN.  About a dozen instructions, explicit FMAs (these rows are
+// tolerance class, not bit-exact class): what lets a GEMM epilogue absorb the
+// activation without becoming the kernel's critical path.
+__device__ __forceinline__ float Ex2Approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float RcpApprox(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+constexpr float kTwoLog2E = 2.885390081777927f;   // e^{2u} = 2^{u * 2 log2 e}
+
 __device__ __forceinline__ float SigmoidExpr(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float ReluExpr(float x) { return x > 0.0f ? x : 0.0f; }
 __device__ __forceinline__ float GeluExpr(float x) {
-  const float t = tanhf(kGeluExprC * (x + kGeluExprA * x * x * x));
-  return 0.5f * x * (1.0f + t);
+  const float u = x * __fmaf_rn(x * x, kGeluExprC * kGeluExprA, kGeluExprC);
+  const float r = RcpApprox(1.0f + Ex2Approx(u * kTwoLog2E));
+  return __fmaf_rn(-x, r, x);
 }
 __device__ __forceinline__ float SiluExpr(float x) { return x * SigmoidExpr(x); }
 __device__ __forceinline__ float ReluGrad(float dy, float x) { return x > 0.0f ? dy : 0.0f; }
 __device__ __forceinline__ float GeluGrad(float dy, float v) {
-  const float u = kGeluExprC * (v + kGeluExprA * v * v * v);
-  const float t = tanhf(u);
-  const float one_minus_t2 = 1.0f - t * t;
-  const float tail = one_minus_t2 == 0.0f
-                         ? 0.0f
-                         : 0.5f * v * one_minus_t2 * (kGeluExprC * (1.0f + 3.0f * kGeluExprA * v * v));
-  return dy * (0.5f * (1.0f + t) + tail);
+  const float v2 = v * v;
+  const float u = v * __fmaf_rn(v2, kGeluExprC * kGeluExprA, kGeluExprC);
+  const float r = RcpApprox(1.0f + Ex2Approx(u * kTwoLog2E));
+  const float t = __fmaf_rn(-2.0f, r, 1.0f);             // tanh u
+  const float one_minus_t2 = __fmaf_rn(-t, t, 1.0f);
+  const float du = __fmaf_rn(v2, 3.0f * kGeluExprC * kGeluExprA, kGeluExprC);
+  // Saturated: the reference drops the tail rather than multiply 0 by a huge du.
+  const float tail = one_minus_t2 == 0.0f ? 0.0f : (0.5f * v) * one_minus_t2 * du;
+  return dy * (__fmaf_rn(0.5f, t, 0.5f) + tail);
 }
 __device__ __forceinline__ float SiluGrad(float dy, float x) {
   const float s = SigmoidExpr(x);

@@ -178,6 +178,11 @@ int see_cuda_set_relaxed_allowed(see_cuda_backend* h, int allowed) {
   return SEE_OK;
 }
 
+int see_cuda_set_epilogue_fusion(see_cuda_backend* h, int enabled) {
+  h->backend->SetEpilogueFusion(enabled != 0);
+  return SEE_OK;
+}
+
 int see_cuda_set_gradient_gather(see_cuda_backend* h, int ranks, const void* gathered_device,
                                  uint64_t block_offset, uint64_t block_bytes) {
   h->backend->SetGradientGather(ranks, gathered_device, block_offset, block_bytes);

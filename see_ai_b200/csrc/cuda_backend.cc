@@ -520,7 +520,7 @@ void CudaBackend::PlanShadows(std::span<const Instruction> program, size_t begin
 // the pair as it is.
 void CudaBackend::PlanBiasFusions(std::span<const Instruction> program, size_t begin, size_t end) {
   bias_fusion_.assign(end > begin ? end - begin : 0, BiasFusion{});
-  if (coherence_ == Coherence::kStrict || !relaxed_allowed_ || end < begin + 2) return;
+  if (coherence_ == Coherence::kStrict || !relaxed_allowed_ || !epilogue_fusion_ || end < begin + 2) return;
   std::vector<Extents> ext(end - begin);
   for (size_t i = begin; i < end; ++i)
     if (!DescribeInstruction(program[i], arena_bytes_, rodata_bytes_, source_bytes_, &ext[i - begin]).empty())
@@ -598,18 +598,26 @@ uint64_t GemmScaleKey(const Instruction& g) {
 
 }  // namespace
 
-// True when every byte of arena range [lo, hi) is overwritten by instructions
-// start.. of the range before anything reads it — except, when `key` is given,
-// relaxed GEMMs whose A operand is exactly that range under that copy key (they
-// take the bf16 copy), and only while nothing has written into the range yet.
-static bool DeadFrom(std::span<const Instruction> program, const std::vector<Extents>& ext, size_t begin,
-                     size_t end, size_t start, uint64_t lo, uint64_t hi, uint64_t key_scale, bool allow_consumers,
-                     uint64_t M, uint64_t K) {
+// True when every byte of arena range [lo, hi) is overwritten before anything
+// reads it, walking instructions start, start + 1, ... to the end of `ext`
+// (the range, or the whole program under the step-program promise, in which
+// case the walk then wraps to instruction 0 and stops at `wrap_stop`, the
+// instruction that defines the range again in the next pass).  Exception, when
+// `allow_consumers`: relaxed GEMMs of the current range (index < range_end)
+// whose A operand is exactly that range under that copy key — they take the
+// bf16 copy — and only while nothing has written into the range yet.
+struct DeadQuery {
+  uint64_t lo, hi;
+  bool allow_consumers;
+  uint64_t key_scale, M, K;
+};
+static bool DeadFrom(std::span<const Instruction> program, const std::vector<Extents>& ext, size_t ext_base,
+                     size_t range_end, size_t start, bool wrap, size_t wrap_stop, const DeadQuery& q) {
   using Interval = std::pair<uint64_t, uint64_t>;
-  std::vector<Interval> unknown{{lo, hi}};
+  std::vector<Interval> unknown{{q.lo, q.hi}};
   bool written = false;
-  for (size_t j = start; j < end; ++j) {
-    const Extents& e = ext[j - begin];
+  auto step = [&](size_t j, bool in_range) -> int {   // -1 read, 1 all overwritten, 0 go on
+    const Extents& e = ext[j - ext_base];
     const Instruction& ins = program[j];
     for (size_t x = 0; x < e.count; ++x) {
       if (e.e[x].space != kArena) continue;
@@ -619,15 +627,16 @@ static bool DeadFrom(std::span<const Instruction> program, const std::vector<Ext
       for (const Interval& u : unknown)
         if (elo < u.second && u.first < ehi) { hits = true; break; }
       if (!hits) continue;
-      const bool consumer = allow_consumers && !written && !e.e[x].write && IsRelaxedFrozenGemm(ins) &&
-                            RefOffset(ins.in[0]) == lo && elo == lo && ehi == hi && ins.out[0] == M &&
-                            ins.out[2] == K && GemmScaleKey(ins) == key_scale;
-      if (!consumer) return false;
+      const bool consumer = q.allow_consumers && in_range && !written && !e.e[x].write &&
+                            IsRelaxedFrozenGemm(ins) && RefOffset(ins.in[0]) == q.lo && elo == q.lo &&
+                            ehi == q.hi && ins.out[0] == q.M && ins.out[2] == q.K &&
+                            GemmScaleKey(ins) == q.key_scale;
+      if (!consumer) return -1;
     }
     for (size_t x = 0; x < e.count; ++x) {
       if (e.e[x].space != kArena || !e.e[x].write) continue;
       const uint64_t elo = e.e[x].off, ehi = elo + e.e[x].bytes;
-      if (elo < hi && lo < ehi) written = true;
+      if (elo < q.hi && q.lo < ehi) written = true;
       std::vector<Interval> rest;
       for (const Interval& u : unknown) {
         if (ehi <= u.first || u.second <= elo) { rest.push_back(u); continue; }
@@ -636,19 +645,33 @@ static bool DeadFrom(std::span<const Instruction> program, const std::vector<Ext
       }
       unknown.swap(rest);
     }
-    if (unknown.empty()) return true;
-  }
-  return false;
+    return unknown.empty() ? 1 : 0;
+  };
+  const size_t stop = ext_base + ext.size();
+  for (size_t j = start; j < stop; ++j)
+    if (const int r = step(j, j < range_end); r != 0) return r > 0;
+  if (!wrap) return false;   // the range ended with bytes unaccounted for
+  for (size_t j = ext_base; j < wrap_stop; ++j)
+    if (const int r = step(j, false); r != 0) return r > 0;
+  return true;   // reached the instruction that defines the range again
 }
 
 void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t begin, size_t end) {
   act_fusion_.assign(end > begin ? end - begin : 0, ActFusion{});
-  if (coherence_ == Coherence::kStrict || !relaxed_allowed_ || end < begin + 3) return;
-  std::vector<Extents> ext(end - begin);
-  for (size_t i = begin; i < end; ++i)
-    if (!DescribeInstruction(program[i], arena_bytes_, rodata_bytes_, source_bytes_, &ext[i - begin]).empty())
+  if (coherence_ == Coherence::kStrict || !relaxed_allowed_ || !epilogue_fusion_ || end < begin + 3) return;
+  // Under the step-program promise liveness is decided on the whole program.
+  const bool whole = step_program_ != nullptr && program.data() == step_program_;
+  const size_t ext_base = whole ? 0 : begin, ext_end = whole ? program.size() : end;
+  std::vector<Extents> ext(ext_end - ext_base);
+  for (size_t i = ext_base; i < ext_end; ++i)
+    if (!DescribeInstruction(program[i], arena_bytes_, rodata_bytes_, source_bytes_, &ext[i - ext_base]).empty())
       return;   // a malformed instruction: leave everything as it is
   auto disjoint = [](uint64_t alo, uint64_t ahi, uint64_t blo, uint64_t bhi) { return ahi <= blo || bhi <= alo; };
+  auto unobserved = [&](uint64_t lo, uint64_t hi) {
+    for (const auto& [off, bytes] : observed_)
+      if (lo < off + bytes && off < hi) return false;
+    return !(gather_ranks_ > 1 && lo < gather_off_ + gather_bytes_ && gather_off_ < hi);
+  };
   for (size_t i = begin; i + 1 < end; ++i) {
     const Instruction& g = program[i];
     if (!IsRelaxedFrozenGemm(g) || RefSpace(g.in[2]) != kArena) continue;
@@ -673,12 +696,24 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
     if (sp.scale_ref != kNullRef && (sp.scale_off & 15) != 0) continue;
     const uint64_t z_lo = RefOffset(z_ref), z_hi = z_lo + bytes;
     const uint64_t o_lo = RefOffset(out_ref), o_hi = o_lo + bytes;
+    // The walk may leave the range (and wrap) only for bytes nothing outside the
+    // program looks at.
+    auto dead = [&](uint64_t lo, uint64_t hi, bool consumers) {
+      const bool wrap = whole && unobserved(lo, hi);
+      if (whole && !wrap) {   // observed bytes: the proof must close inside the range
+        std::vector<Extents> in_range(ext.begin() + static_cast<long>(begin), ext.begin() + static_cast<long>(end));
+        return DeadFrom(program, in_range, begin, end, next + 1, false, 0,
+                        DeadQuery{lo, hi, consumers, sp.scale_off, M, N});
+      }
+      return DeadFrom(program, ext, ext_base, end, next + 1, wrap, next,
+                      DeadQuery{lo, hi, consumers, sp.scale_off, M, N});
+    };
     ActFusion f;
     f.act = aop == kReluFwd || aop == kReluBwd ? kActRelu : aop == kGeluFwd || aop == kGeluBwd ? kActGelu : kActSilu;
     f.act_index = static_cast<uint32_t>(next - begin);
     if (fwd) {
       if (!disjoint(z_lo, z_hi, o_lo, o_hi)) continue;
-      if (!DeadFrom(program, ext, begin, end, next + 1, o_lo, o_hi, sp.scale_off, true, M, N)) continue;
+      if (!dead(o_lo, o_hi, true)) continue;
       f.mode = k::kFuseActFwd;
       f.store_c = true;
       f.elided[0][0] = o_lo; f.elided[0][1] = o_hi;
@@ -689,7 +724,7 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
       if (!disjoint(x_lo, x_hi, z_lo, z_hi) || !disjoint(x_lo, x_hi, o_lo, o_hi)) continue;
       const bool in_place = o_lo == z_lo;
       if (!in_place && !disjoint(z_lo, z_hi, o_lo, o_hi)) continue;
-      if (!DeadFrom(program, ext, begin, end, next + 1, o_lo, o_hi, sp.scale_off, true, M, N)) continue;
+      if (!dead(o_lo, o_hi, true)) continue;
       f.mode = k::kFuseActBwd;
       f.x_ref = act.in[1];
       f.elided[0][0] = o_lo; f.elided[0][1] = o_hi;
@@ -697,7 +732,7 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
       if (in_place) {
         f.store_c = false;
       } else {
-        f.store_c = !DeadFrom(program, ext, begin, end, next + 1, z_lo, z_hi, ~0ull, false, 0, 0);
+        f.store_c = !dead(z_lo, z_hi, false);
         if (!f.store_c) {
           f.elided[1][0] = z_lo; f.elided[1][1] = z_hi;
           f.elided_count = 2;

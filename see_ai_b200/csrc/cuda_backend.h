@@ -90,6 +90,18 @@ class CudaBackend {
   void Configure() {}  // the CPU tile policy is throughput-only on its own backend; ignored here
 
   Status Execute(const Instruction& ins, const StepParams& params);
+
+  // The caller's promise that `program` (the span later passed to BeginRange) is
+  // a complete update step that it only ever runs from instruction 0 onwards,
+  // pass after pass, and that arena bytes outside `observed` ([offset, bytes)
+  // ranges: persistent state, loss, the gradient block ...) are read by nothing
+  // but that program's instructions.  Scratch tensors of such a program that no
+  // instruction reads before the next pass rewrites them may then be left
+  // unwritten by the epilogue fusions (lazy coherence only).
+  void DeclareStepProgram(const Instruction* program, std::vector<std::pair<uint64_t, uint64_t>> observed) {
+    step_program_ = program;
+    observed_ = std::move(observed);
+  }
   void BeginRange(std::span<const Instruction> program, size_t begin, size_t end);
   void EndRange();
   Status Flush();
@@ -120,6 +132,9 @@ class CudaBackend {
   // permission (default: allowed).  The exact kernels are always a valid
   // execution of a relaxed instruction.
   void SetRelaxedAllowed(bool allowed) { relaxed_allowed_ = allowed; }
+  // Off: no kAddBias or activation is absorbed into a product's epilogue (takes
+  // effect at the next BeginRange).
+  void SetEpilogueFusion(bool enabled) { epilogue_fusion_ = enabled; }
 
   // CUDA-graph support for the engine.  While capturing, the per-range scalar
   // upload is recorded from a fixed pinned slot; before each replay the engine
@@ -199,6 +214,7 @@ class CudaBackend {
   uint64_t gather_off_ = 0, gather_bytes_ = 0;
 
   bool relaxed_allowed_ = true;
+  bool epilogue_fusion_ = true;
   bool profiling_ = false;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> events_;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> kernel_events_;
@@ -255,6 +271,8 @@ class CudaBackend {
     int elided_count = 0;
   };
   void PlanActFusions(std::span<const Instruction> program, size_t begin, size_t end);
+  const Instruction* step_program_ = nullptr;   // see DeclareStepProgram
+  std::vector<std::pair<uint64_t, uint64_t>> observed_;
   std::vector<ActFusion> act_fusion_;   // per range position (of the GEMM)
   int64_t skip_act_at_ = -1;
   std::vector<std::pair<uint64_t, uint64_t>> elided_;

@@ -202,6 +202,18 @@ Status UpdateEngine::LoadFromMemory(const uint8_t* plan, uint64_t size) {
   phases_ = ScanPhases(train_);
   grad_off_ = g_lo == ~0ull ? 0 : g_lo;
   grad_bytes_ = g_lo == ~0ull ? 0 : g_hi - g_lo;
+  // The train program is a complete step that this engine only runs from its
+  // first instruction, pass after pass; outside it only these arena ranges are
+  // ever looked at (checkpoints and the merge / eval programs read the persistent
+  // prefix, ReadLoss the loss slot, the data-parallel exchange and a separate
+  // step program the gradient block).
+  {
+    std::vector<std::pair<uint64_t, uint64_t>> observed;
+    if (header_.persistent_size) observed.push_back({0, header_.persistent_size});
+    if (header_.loss_ref != kNullRef) observed.push_back({RefOffset(header_.loss_ref), 4});
+    if (grad_bytes_) observed.push_back({grad_off_, grad_bytes_});
+    backend_->DeclareStepProgram(train_.data(), std::move(observed));
+  }
   step_ = 0;
   horizon_ = h.default_steps;
   eval_probs_ref_ = eval_labels_ref_ = kNullRef;

@@ -282,12 +282,7 @@ __global__ void RopeKernel(const float* __restrict__ x, float* __restrict__ y, s
   }
 }
 
-__device__ __forceinline__ uint16_t Bf16Rne(float f) {
-  uint32_t b = __float_as_uint(f);
-  if ((b & 0x7FFFFFFFu) > 0x7F800000u) return static_cast<uint16_t>((b >> 16) | 0x0040u);
-  b += 0x7FFFu + ((b >> 16) & 1u);
-  return static_cast<uint16_t>(b >> 16);
-}
+__device__ __forceinline__ uint16_t Bf16Rne(float f) { return static_cast<uint16_t>(ShadowBf16(f)); }
 
 __global__ void ToBf16Kernel(const float* __restrict__ x, uint16_t* __restrict__ out, size_t rows,
                              size_t cols, const float* __restrict__ col_scale, bool vec) {
@@ -305,8 +300,8 @@ __global__ void ToBf16Kernel(const float* __restrict__ x, uint16_t* __restrict__
         a.x *= sc.x; a.y *= sc.y; a.z *= sc.z; a.w *= sc.w;
       }
       uint2 r;
-      r.x = Bf16Rne(a.x) | (static_cast<uint32_t>(Bf16Rne(a.y)) << 16);
-      r.y = Bf16Rne(a.z) | (static_cast<uint32_t>(Bf16Rne(a.w)) << 16);
+      r.x = ShadowBf16x2(a.x, a.y);
+      r.y = ShadowBf16x2(a.z, a.w);
       o2[i] = r;
     }
   } else {

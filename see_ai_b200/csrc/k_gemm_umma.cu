@@ -485,6 +485,25 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
       uint32_t mb, nb;
       TileCoord(t, tiles_m, tiles_n, band_blocks, &mb, &nb);
       const uint32_t m0 = mb * kBlockM, n0 = nb * kPBlockN;
+      if (ep.fuse_mode == kFuseActBwd) {
+        // The absorbed backward activation reads x[m, n] next to every output:
+        // ask L2 for this warp's lines of the NEXT tile now (one 128-byte line per
+        // lane and pass), a whole tile ahead of the loads that use them.
+        auto prefetch_x = [&](uint32_t tile) {
+          uint32_t pmb, pnb;
+          TileCoord(tile, tiles_m, tiles_n, band_blocks, &pmb, &pnb);
+          const uint32_t prow = pmb * kBlockM + quarter * 32 + lane;
+          if (prow >= ep.M) return;
+#pragma unroll
+          for (uint32_t pass = 0; pass < kEpiPasses; ++pass) {
+            const uint32_t pcol = pnb * kPBlockN + col_group * kColsPerEpiWarp + pass * kSlabCols;
+            if (pcol < ep.N)
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(ep.fuse_x + static_cast<size_t>(prow) * ep.N + pcol));
+          }
+        };
+        if (lt == 0) prefetch_x(t);
+        if (t + gridDim.x < total_tiles) prefetch_x(t + gridDim.x);
+      }
       bool ok = MbarWait(&bars->tmem_full[buf], use & 1);
       if (!ok && lane == 0) { ep.status->wait_timeout = 1; bars->abort = 1; }
       if (bars->abort) ok = false;

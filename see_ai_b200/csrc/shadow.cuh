@@ -1,6 +1,6 @@
 // Device side of k::Shadow: the bf16 copy a producer kernel writes next to its
 // f32 output.  Same rounding as the GEMM path's own conversion kernel
-// (round to nearest even, NaN kept quiet), the consumer's per-column factor
+// (round to nearest even), the consumer's per-column factor
 // applied first when it has one.
 #ifndef SEE_CUDA_SHADOW_CUH_
 #define SEE_CUDA_SHADOW_CUH_
@@ -9,11 +9,16 @@
 
 namespace see::k {
 
+// The hardware conversion: round to nearest even, NaN to the canonical quiet NaN.
 __device__ __forceinline__ uint32_t ShadowBf16(float f) {
-  uint32_t b = __float_as_uint(f);
-  if ((b & 0x7FFFFFFFu) > 0x7F800000u) return (b >> 16) | 0x0040u;
-  b += 0x7FFFu + ((b >> 16) & 1u);
-  return b >> 16;
+  uint16_t r;
+  asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(f));
+  return r;
+}
+__device__ __forceinline__ uint32_t ShadowBf16x2(float lo, float hi) {   // lo in bits 0..15
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
 }
 
 // Four consecutive elements of one row: flat index 4 * i4, first column `col`
@@ -25,8 +30,8 @@ __device__ __forceinline__ void ShadowStore4(const Shadow& sh, size_t i4, uint32
     v.x *= sc.x; v.y *= sc.y; v.z *= sc.z; v.w *= sc.w;
   }
   uint2 r;
-  r.x = ShadowBf16(v.x) | (ShadowBf16(v.y) << 16);
-  r.y = ShadowBf16(v.z) | (ShadowBf16(v.w) << 16);
+  r.x = ShadowBf16x2(v.x, v.y);
+  r.y = ShadowBf16x2(v.z, v.w);
   reinterpret_cast<uint2*>(sh.dst)[i4] = r;
 }
 

@@ -159,3 +159,51 @@ def test_backward_activation_rides_the_gemm_epilogue(size, case):
     # activation kernel too unless its f32 output is read later.  A dy that is read
     # later is still written by the epilogue (same launches saved).
     assert saved == (1 if case == "dx-read-later" else 2)
+
+
+# ---- the engine's train program: fusions on a whole decoder step ----------------------
+# The engine declares its train program a complete step, so scratch activations
+# that nothing reads before the next pass rewrites them (GELU outputs, GELU
+# backward outputs) may stay unwritten.  Same adapters, moments and losses, bit for
+# bit, as the same engine with epilogue fusion switched off — eager, while the
+# graphs are captured, and on replay.
+
+def _engine_run(fusion: bool, steps: int = 4):
+    import torch
+    from see_ai_b200 import synth
+    from see_ai_b200.engine import Engine
+    cfg = synth.DecoderConfig(layers=2, d_model=128, heads=2, ffn=512, vocab=512, seq=128, batch_seqs=4,
+                              rank=8, alpha=16.0, targets=("q", "k", "v", "o"), quantized=True,
+                              attention="tiled", lr=1e-2, steps=100, seed=3)
+    blob = synth.build_decoder_plan(cfg)
+    rng = np.random.default_rng(9)
+    stream = torch.cuda.Stream()
+    eng = Engine(0)
+    losses = []
+    with torch.cuda.stream(stream):
+        eng.backend.set_stream(stream.cuda_stream)
+        eng.backend.set_epilogue_fusion(fusion)
+        eng.load(blob)
+        eng.set_horizon(cfg.steps)
+        for _ in range(steps):
+            rec = rng.integers(0, cfg.vocab, size=(cfg.batch_seqs, cfg.seq + 1), dtype=np.int32)
+            eng.stage_batch(np.ascontiguousarray(rec[:, :-1]).reshape(-1),
+                            np.ascontiguousarray(rec[:, 1:]).reshape(-1))
+            eng.train_forward_backward(True)
+            eng.train_optimizer()
+            losses.append(eng.read_loss())
+        persist = np.array(eng.read_persistent(), copy=True)
+        launches = eng.backend.counters().kernel_launches
+    eng.close()
+    return persist, np.array(losses, dtype=np.float32), launches
+
+
+def test_engine_step_with_fusions_is_the_unfused_step_bit_for_bit():
+    p_on, l_on, n_on = _engine_run(True)
+    p_off, l_off, n_off = _engine_run(False)
+    assert np.isfinite(l_on).all()
+    assert np.array_equal(l_on, l_off)
+    assert np.array_equal(p_on, p_off)
+    # Two layers: per eagerly executed pass at least the two GELU forwards and the
+    # two GELU backwards stop launching (plus the bias adds).
+    assert n_off - n_on >= 4
