@@ -130,7 +130,9 @@ __device__ __forceinline__ float ApplyAct(float v, int act) { return ActFwdExpr(
 
 // The tail of both epilogues: four neighbouring columns n.. of row (at / N).
 __device__ __forceinline__ void EpilogueStore(const UmmaEpilogue& ep, size_t at, uint32_t n, const float4& acc,
-                                              const float4& scale, const float4& bias) {
+                                              const float4& scale, const float4& bias,
+                                              bool has_kscale = false,
+                                              float4 kscale = make_float4(1.f, 1.f, 1.f, 1.f)) {
   float4 v = make_float4(acc.x * scale.x, acc.y * scale.y, acc.z * scale.z, acc.w * scale.w);
   if (ep.addend) {
     const float4 d = __ldg(reinterpret_cast<const float4*>(ep.addend + at));
@@ -153,8 +155,9 @@ __device__ __forceinline__ void EpilogueStore(const UmmaEpilogue& ep, size_t at,
     }
     Shadow sh;
     sh.dst = ep.shadow_dst;
-    sh.k_scale = ep.shadow_k_scale;
+    sh.k_scale = has_kscale ? nullptr : ep.shadow_k_scale;
     sh.cols = ep.N;
+    if (has_kscale) g = make_float4(g.x * kscale.x, g.y * kscale.y, g.z * kscale.z, g.w * kscale.w);
     ShadowStore4(sh, at / 4, n, g);
   }
 }
@@ -541,12 +544,15 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
           if (ep.col_scale) scale = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n));
           float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
           if (ep.bias) bias = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
+          float4 kscale = make_float4(1.f, 1.f, 1.f, 1.f);   // the consumer's per-column factor (x * 1 == x)
+          if (ep.fuse_mode != kFuseNone && ep.shadow_k_scale)
+            kscale = __ldg(reinterpret_cast<const float4*>(ep.shadow_k_scale + n));
 #pragma unroll 4
           for (uint32_t rr = sub; rr < rows; rr += kRowsPerInstr) {
             const float4 acc = *reinterpret_cast<const float4*>(
                 slab + rr * kSlabCols + ((cl ^ (rr & (kChunks - 1))) * 4));
             const size_t at = static_cast<size_t>(row0 + rr) * ep.N + n;
-            EpilogueStore(ep, at, n, acc, scale, bias);
+            EpilogueStore(ep, at, n, acc, scale, bias, true, kscale);
           }
         }
         __syncwarp();   // the slab is rewritten next
