@@ -672,6 +672,25 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
       if (lo < off + bytes && off < hi) return false;
     return !(gather_ranks_ > 1 && lo < gather_off_ + gather_bytes_ && gather_off_ < hi);
   };
+  // Is the range dead after instruction `def` (which defines it)?  The walk may
+  // leave the range (and wrap) only for bytes nothing outside the program looks at.
+  auto dead_after = [&](size_t def, const DeadQuery& q) {
+    const bool wrap = whole && unobserved(q.lo, q.hi);
+    if (whole && !wrap) {   // observed bytes: the proof must close inside the range
+      std::vector<Extents> in_range(ext.begin() + static_cast<long>(begin), ext.begin() + static_cast<long>(end));
+      return DeadFrom(program, in_range, begin, end, def + 1, false, 0, q);
+    }
+    return DeadFrom(program, ext, ext_base, end, def + 1, wrap, def, q);
+  };
+  // Producers that can write the bf16 copy alone: the loss gradient, whose f32
+  // form (rows x vocabulary) is the largest tensor of a step.
+  for (size_t i = begin; i < end; ++i) {
+    ShadowPlan& sp = shadow_plan_[i - begin];
+    const uint16_t op = program[i].opcode;
+    if (!sp.want || (op != kSoftmaxXEntBwd && op != kSoftmaxXEntMaskedBwd)) continue;
+    if (sp.scale_ref != kNullRef && (sp.scale_off & 15) != 0) continue;
+    sp.only = dead_after(i, DeadQuery{sp.a_off, sp.a_off + sp.M * sp.K * 4, true, sp.scale_off, sp.M, sp.K});
+  }
   for (size_t i = begin; i + 1 < end; ++i) {
     const Instruction& g = program[i];
     if (!IsRelaxedFrozenGemm(g) || RefSpace(g.in[2]) != kArena) continue;
@@ -696,17 +715,8 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
     if (sp.scale_ref != kNullRef && (sp.scale_off & 15) != 0) continue;
     const uint64_t z_lo = RefOffset(z_ref), z_hi = z_lo + bytes;
     const uint64_t o_lo = RefOffset(out_ref), o_hi = o_lo + bytes;
-    // The walk may leave the range (and wrap) only for bytes nothing outside the
-    // program looks at.
     auto dead = [&](uint64_t lo, uint64_t hi, bool consumers) {
-      const bool wrap = whole && unobserved(lo, hi);
-      if (whole && !wrap) {   // observed bytes: the proof must close inside the range
-        std::vector<Extents> in_range(ext.begin() + static_cast<long>(begin), ext.begin() + static_cast<long>(end));
-        return DeadFrom(program, in_range, begin, end, next + 1, false, 0,
-                        DeadQuery{lo, hi, consumers, sp.scale_off, M, N});
-      }
-      return DeadFrom(program, ext, ext_base, end, next + 1, wrap, next,
-                      DeadQuery{lo, hi, consumers, sp.scale_off, M, N});
+      return dead_after(next, DeadQuery{lo, hi, consumers, sp.scale_off, M, N});
     };
     ActFusion f;
     f.act = aop == kReluFwd || aop == kReluBwd ? kActRelu : aop == kGeluFwd || aop == kGeluBwd ? kActGelu : kActSilu;
@@ -857,6 +867,7 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
       cur_shadow_.dst = buf;
       cur_shadow_.k_scale = cur_plan_.scale_ref == kNullRef ? nullptr : Rd(cur_plan_.scale_ref);
       cur_shadow_.cols = cur_plan_.K;
+      cur_shadow_.only = cur_plan_.only;
     }
   }
 
@@ -891,6 +902,8 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
       elided_.swap(rest);
     }
   }
+  if (shadow_written_ && cur_shadow_.only && (ins.opcode == kSoftmaxXEntBwd || ins.opcode == kSoftmaxXEntMaskedBwd))
+    elided_.push_back({cur_plan_.a_off, cur_plan_.a_off + cur_plan_.M * cur_plan_.K * 4});
   if (shadow_written_)   // after the instruction's own writes have invalidated the range
     umma::CommitShadow(&umma_->ctx, cur_shadow_.dst, cur_plan_.a_off, cur_plan_.scale_off,
                        cur_plan_.M, cur_plan_.K);
@@ -953,7 +966,9 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
       ++counters_.relaxed_executions;
       counters_.kernel_launches += launches;
       skip_next_add_bias_ = fuse != nullptr;
+      if (fuse) ++counters_.fused_dispatches;
       if (af) {
+        ++counters_.fused_dispatches;
         shadow_written_ = true;
         skip_act_at_ = static_cast<int64_t>(af->act_index);
         for (int e = 0; e < af->elided_count; ++e) elided_.push_back({af->elided[e][0], af->elided[e][1]});

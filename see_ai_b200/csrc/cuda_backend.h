@@ -244,6 +244,7 @@ class CudaBackend {
   // and under which key that GEMM will look the copy up.
   struct ShadowPlan {
     bool want = false;
+    bool only = false;   // the f32 tensor itself is dead: the producer may write the copy alone
     uint64_t a_off = 0, M = 0, K = 0, scale_off = ~0ull, scale_ref = kNullRef;
   };
   void PlanShadows(std::span<const Instruction> program, size_t begin, size_t end);

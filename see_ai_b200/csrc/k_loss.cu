@@ -312,7 +312,7 @@ __global__ void XEntBwdRowsKernel(const float* __restrict__ probs, const int32_t
           }
         }
       }
-      drow[c4] = v;
+      if (!sh.only) drow[c4] = v;
       if (sh.dst) ShadowStore4(sh, n * C4 + c4, static_cast<uint32_t>(c4 * 4), v);
     }
   }
@@ -450,8 +450,9 @@ bool SoftmaxXEntBwd(bool masked, const float* probs, const int32_t* labels, cons
     const dim3 grid(static_cast<unsigned>(per_row < 64 ? per_row : 64),
                     static_cast<unsigned>(N < 65535 ? N : 65535));
     const bool shadowed = ShadowUsable(shadow, dlogits, N * C) && shadow->cols == C;
-    XEntBwdRowsKernel<<<grid, 256, 0, s>>>(probs, labels, seed, dlogits, N, C, masked, count_scratch,
-                                           shadowed ? *shadow : Shadow{});
+    Shadow sh = shadowed ? *shadow : Shadow{};
+    if (!shadowed) sh.only = false;
+    XEntBwdRowsKernel<<<grid, 256, 0, s>>>(probs, labels, seed, dlogits, N, C, masked, count_scratch, sh);
     return shadowed;
   }
   XEntBwdKernel<<<GridFor(N * C, 256, 148 * 8), 256, 0, s>>>(probs, labels, seed, dlogits, N, C,

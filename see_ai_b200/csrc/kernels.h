@@ -33,6 +33,9 @@ struct Shadow {
   uint16_t* dst = nullptr;
   const float* k_scale = nullptr;   // per-column factor of the consumer (or null)
   size_t cols = 0;
+  // The f32 output itself is read by nobody (proven by the caller): a producer
+  // that supports it writes the copy alone.  Others ignore the flag.
+  bool only = false;
 };
 inline bool ShadowUsable(const Shadow* sh, const void* out, size_t n) {
   return sh && sh->dst && sh->cols != 0 && sh->cols % 4 == 0 && n % sh->cols == 0 &&

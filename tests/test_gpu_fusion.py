@@ -68,6 +68,7 @@ def test_bias_add_rides_the_gemm_epilogue_only_when_the_product_is_dead(later_re
     # compare launches directly: fused drops exactly the kAddBias kernel.
     saved = c_split.kernel_launches - c_fused.kernel_launches
     assert saved == (0 if later_read else 1)
+    assert c_fused.fused_dispatches == (0 if later_read else 1) and c_split.fused_dispatches == 0
 
 
 # ---- activation absorbed into the producing GEMM's epilogue ---------------------------
@@ -117,6 +118,7 @@ def test_forward_activation_rides_the_gemm_epilogue_only_when_its_f32_output_is_
     # kAddBias in the epilogue (1) and the second GEMM's conversion pass (1) are
     # saved either way; the activation kernel itself (1) only when g is dead.
     assert saved == (2 if later_read else 3)
+    assert c_fused.fused_dispatches == (1 if later_read else 2)   # the bias add, and the activation
 
 
 def _build_act_bwd(rng, M, K, N, read_dy_later, read_dx_later):
@@ -159,6 +161,7 @@ def test_backward_activation_rides_the_gemm_epilogue(size, case):
     # activation kernel too unless its f32 output is read later.  A dy that is read
     # later is still written by the epilogue (same launches saved).
     assert saved == (1 if case == "dx-read-later" else 2)
+    assert c_fused.fused_dispatches == (0 if case == "dx-read-later" else 1)
 
 
 # ---- the engine's train program: fusions on a whole decoder step ----------------------
@@ -194,16 +197,26 @@ def _engine_run(fusion: bool, steps: int = 4):
             losses.append(eng.read_loss())
         persist = np.array(eng.read_persistent(), copy=True)
         launches = eng.backend.counters().kernel_launches
+        # The loss gradient's f32 tensor (rows x vocabulary): read by nothing but the
+        # output projection's backward GEMM, which takes the bf16 copy.
+        train = P.Plan(blob).section("train")
+        xb = next(i for i in train if i.opcode == Op.XENT_BWD)
+        dlogits = np.array(eng.read_arena(xb.ins[3] & ((1 << 56) - 1), 4 * cfg.rows * cfg.vocab), copy=True)
     eng.close()
-    return persist, np.array(losses, dtype=np.float32), launches
+    return persist, np.array(losses, dtype=np.float32), launches, dlogits.view(np.float32)
 
 
 def test_engine_step_with_fusions_is_the_unfused_step_bit_for_bit():
-    p_on, l_on, n_on = _engine_run(True)
-    p_off, l_off, n_off = _engine_run(False)
+    p_on, l_on, n_on, d_on = _engine_run(True)
+    p_off, l_off, n_off, d_off = _engine_run(False)
     assert np.isfinite(l_on).all()
     assert np.array_equal(l_on, l_off)
     assert np.array_equal(p_on, p_off)
     # Two layers: per eagerly executed pass at least the two GELU forwards and the
     # two GELU backwards stop launching (plus the bias adds).
     assert n_off - n_on >= 4
+    # ... and the loss-gradient kernel wrote only the bf16 copy.  The plan computes the
+    # gradient in place over the probabilities, so the f32 tensor still holds what
+    # the forward left there (no negative entry); unfused, it holds the gradient
+    # (negative at every label).
+    assert np.any(d_off < 0) and not np.any(d_on < 0)
