@@ -373,8 +373,10 @@ void CudaBackend::EndRange() {
   bias_fusion_.clear();
   skip_next_add_bias_ = false;
   act_fusion_.clear();
+  loss_fusion_.clear();
   skip_act_at_ = -1;
   elided_.clear();
+  pending_elided_.clear();
   shadow_plan_.clear();
   adam_group_of_.clear();
   adam_groups_.clear();
@@ -658,6 +660,7 @@ static bool DeadFrom(std::span<const Instruction> program, const std::vector<Ext
 
 void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t begin, size_t end) {
   act_fusion_.assign(end > begin ? end - begin : 0, ActFusion{});
+  loss_fusion_.assign(end > begin ? end - begin : 0, LossFusion{});
   if (coherence_ == Coherence::kStrict || !relaxed_allowed_ || !epilogue_fusion_ || end < begin + 3) return;
   // Under the step-program promise liveness is decided on the whole program.
   const bool whole = step_program_ != nullptr && program.data() == step_program_;
@@ -674,13 +677,16 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
   };
   // Is the range dead after instruction `def` (which defines it)?  The walk may
   // leave the range (and wrap) only for bytes nothing outside the program looks at.
-  auto dead_after = [&](size_t def, const DeadQuery& q) {
+  // `last` is the last instruction allowed to read it, `def` the one that defines
+  // it (where a wrapped walk stops: the next pass writes it again there).
+  auto dead_after = [&](size_t last, const DeadQuery& q, size_t def = ~size_t{0}) {
+    if (def == ~size_t{0}) def = last;
     const bool wrap = whole && unobserved(q.lo, q.hi);
     if (whole && !wrap) {   // observed bytes: the proof must close inside the range
       std::vector<Extents> in_range(ext.begin() + static_cast<long>(begin), ext.begin() + static_cast<long>(end));
-      return DeadFrom(program, in_range, begin, end, def + 1, false, 0, q);
+      return DeadFrom(program, in_range, begin, end, last + 1, false, 0, q);
     }
-    return DeadFrom(program, ext, ext_base, end, def + 1, wrap, def, q);
+    return DeadFrom(program, ext, ext_base, end, last + 1, wrap, def, q);
   };
   // Producers that can write the bf16 copy alone: the loss gradient, whose f32
   // form (rows x vocabulary) is the largest tensor of a step.
@@ -690,6 +696,30 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
     if (!sp.want || (op != kSoftmaxXEntBwd && op != kSoftmaxXEntMaskedBwd)) continue;
     if (sp.scale_ref != kNullRef && (sp.scale_off & 15) != 0) continue;
     sp.only = dead_after(i, DeadQuery{sp.a_off, sp.a_off + sp.M * sp.K * 4, true, sp.scale_off, sp.M, sp.K});
+  }
+  // Forward loss, seed fill, backward loss: one row pass when the gradient leaves
+  // as a copy only.
+  for (size_t i = begin; i + 2 < end; ++i) {
+    const Instruction& f = program[i];
+    const Instruction& fill = program[i + 1];
+    const Instruction& b = program[i + 2];
+    if (f.opcode != kSoftmaxXEntFwd || fill.opcode != kFill || fill.out[0] != 1 || b.opcode != kSoftmaxXEntBwd)
+      continue;
+    if (b.in[0] != f.in[3] || b.in[1] != f.in[1] || b.in[2] != fill.in[0] || b.out[0] != f.out[0] ||
+        b.out[1] != f.out[1] || RefSpace(f.in[3]) != kArena)
+      continue;
+    ShadowPlan& sp = shadow_plan_[i + 2 - begin];
+    if (!sp.want || !sp.only || shadow_plan_[i - begin].want) continue;
+    LossFusion lf;
+    lf.fuse = true;
+    lf.seed = BitsToF32(fill.in[1]);
+    lf.bwd_index = static_cast<uint32_t>(i + 2 - begin);
+    lf.probs_lo = RefOffset(f.in[3]);
+    lf.probs_hi = lf.probs_lo + f.out[0] * f.out[1] * 4;
+    lf.store_probs = !dead_after(i + 2, DeadQuery{lf.probs_lo, lf.probs_hi, false, ~0ull, 0, 0}, i);
+    loss_fusion_[i - begin] = lf;
+    shadow_plan_[i - begin] = sp;   // the forward is now the copy's producer
+    sp.want = false;
   }
   for (size_t i = begin; i + 1 < end; ++i) {
     const Instruction& g = program[i];
@@ -835,7 +865,9 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   // written, so the copy the product published under this output's key stays.
   const bool absorbed = skip_act_at_ == static_cast<int64_t>(range_index_);
   if (absorbed) skip_act_at_ = -1;
-  if (!elided_.empty() && !absorbed) {
+  // (A kAddBias done by the preceding product's epilogue reads nothing either.)
+  const bool bias_done = skip_next_add_bias_ && ins.opcode == kAddBias;
+  if (!elided_.empty() && !absorbed && !bias_done) {
     for (size_t i = 0; i < ext.count; ++i) {
       const Extent& e = ext.e[i];
       if (e.space != kArena || (e.write && !e.read)) continue;
@@ -904,6 +936,8 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   }
   if (shadow_written_ && cur_shadow_.only && (ins.opcode == kSoftmaxXEntBwd || ins.opcode == kSoftmaxXEntMaskedBwd))
     elided_.push_back({cur_plan_.a_off, cur_plan_.a_off + cur_plan_.M * cur_plan_.K * 4});
+  elided_.insert(elided_.end(), pending_elided_.begin(), pending_elided_.end());
+  pending_elided_.clear();
   if (shadow_written_)   // after the instruction's own writes have invalidated the range
     umma::CommitShadow(&umma_->ctx, cur_shadow_.dst, cur_plan_.a_off, cur_plan_.scale_off,
                        cur_plan_.M, cur_plan_.K);
@@ -971,7 +1005,8 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
         ++counters_.fused_dispatches;
         shadow_written_ = true;
         skip_act_at_ = static_cast<int64_t>(af->act_index);
-        for (int e = 0; e < af->elided_count; ++e) elided_.push_back({af->elided[e][0], af->elided[e][1]});
+        for (int e = 0; e < af->elided_count; ++e)
+          pending_elided_.push_back({af->elided[e][0], af->elided[e][1]});
       }
       return {};
     }
@@ -1171,11 +1206,29 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
       launched();
       break;
     case kSoftmaxXEntFwd: case kSoftmaxXEntMaskedFwd:
+    {
       if (auto r = EnsureScratch(ins.out[0]); !r) return r;
-      k::SoftmaxXEntFwd(ins.opcode == kSoftmaxXEntMaskedFwd, Rd(ins.in[0]), Rd<int32_t>(ins.in[1]),
-                        Wr(ins.in[2]), Wr(ins.in[3]), ins.out[0], ins.out[1], d_rows_, d_count_, s);
+      const LossFusion* lf = range_index_ < loss_fusion_.size() && loss_fusion_[range_index_].fuse &&
+                                     cur_shadow_.dst ? &loss_fusion_[range_index_] : nullptr;
+      k::XEntFusedBwd fb;
+      if (lf) {
+        fb.shadow = cur_shadow_;
+        fb.seed = lf->seed;
+        fb.store_probs = lf->store_probs;
+      }
+      const bool fused = k::SoftmaxXEntFwd(ins.opcode == kSoftmaxXEntMaskedFwd, Rd(ins.in[0]),
+                                           Rd<int32_t>(ins.in[1]), Wr(ins.in[2]), Wr(ins.in[3]), ins.out[0],
+                                           ins.out[1], d_rows_, d_count_, s, lf ? &fb : nullptr);
       launched(2);
+      if (fused) {   // the backward instruction two places on has been done
+        shadow_written_ = true;
+        skip_act_at_ = static_cast<int64_t>(lf->bwd_index);
+        ++counters_.fused_dispatches;
+        pending_elided_.push_back({cur_plan_.a_off, cur_plan_.a_off + cur_plan_.M * cur_plan_.K * 4});
+        if (!lf->store_probs) pending_elided_.push_back({lf->probs_lo, lf->probs_hi});
+      }
       break;
+    }
     case kSoftmaxXEntBwd: case kSoftmaxXEntMaskedBwd:
       shadow_written_ = k::SoftmaxXEntBwd(
           ins.opcode == kSoftmaxXEntMaskedBwd, Rd(ins.in[0]), Rd<int32_t>(ins.in[1]), Rd(ins.in[2]),

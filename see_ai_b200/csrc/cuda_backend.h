@@ -277,6 +277,20 @@ class CudaBackend {
   std::vector<ActFusion> act_fusion_;   // per range position (of the GEMM)
   int64_t skip_act_at_ = -1;
   std::vector<std::pair<uint64_t, uint64_t>> elided_;
+  std::vector<std::pair<uint64_t, uint64_t>> pending_elided_;   // joins elided_ once the instruction's own writes are accounted
+
+  // kSoftmaxXEntFwd, the one-element kFill of the seed, kSoftmaxXEntBwd: when only
+  // the bf16 copy of the loss gradient is needed, the forward's row pass
+  // produces it (the backward instruction launches nothing); the probabilities
+  // are stored only if something else reads them.
+  struct LossFusion {
+    bool fuse = false;
+    float seed = 1.0f;
+    bool store_probs = true;
+    uint32_t bwd_index = 0;
+    uint64_t probs_lo = 0, probs_hi = 0;
+  };
+  std::vector<LossFusion> loss_fusion_;   // per range position (of the forward)
 
   Counters counters_;
   struct UmmaState;

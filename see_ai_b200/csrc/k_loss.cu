@@ -7,6 +7,7 @@
 // per-row -log p in double, rows folded sequentially inside each chunk, chunks
 // folded in chunk order, so the loss does not depend on the launch geometry.
 // Integer results (the masked forms' target count) are exact.
+#include "act_expr.cuh"
 #include "kernels.h"
 #include "shadow.cuh"
 
@@ -129,9 +130,10 @@ __device__ __forceinline__ void CpAsync16(void* smem, const void* gmem) {
 __global__ void __launch_bounds__(kWideThreads, 1)
 XEntRowsWideKernel(const float* __restrict__ logits, const int32_t* __restrict__ labels,
                    float* __restrict__ probs, double* __restrict__ row_loss, size_t N, size_t C,
-                   bool masked) {
+                   bool masked, Shadow sh, float bwd_scale, bool store_probs) {
   extern __shared__ __align__(16) float4 row_smem[];
   __shared__ float smem_f[32];
+  __shared__ float label_prob;
   const int C4 = static_cast<int>(C / 4);
   const int tid = threadIdx.x;
   auto prefetch = [&](size_t n) {
@@ -159,32 +161,55 @@ XEntRowsWideKernel(const float* __restrict__ logits, const int32_t* __restrict__
     if (n + gridDim.x < N) prefetch(n + gridDim.x);
     mx = BlockReduce<float>(mx, -INFINITY, smem_f, WarpMax,
                             [](float a, float b) { return fmaxf(a, b); });
+    // e^{x - mx} = 2^{x log2 e - mx log2 e} on the hardware exponential: one FMA and
+    // one MUFU per element (libm expf is about twenty instructions, and a
+    // vocabulary-wide row is instruction-bound with it).  Relative error about 1e-6
+    // at the far end of the row, inside the 1e-5 these rows are held to.
+    constexpr float kLog2E = 1.4426950408889634f;
+    const float shift = -mx * kLog2E;
     float sum = 0.0f;
 #pragma unroll
     for (int i = 0; i < kWideVecs; ++i) {
       if (i * kWideThreads + tid < C4) {
-        x[i].x = expf(x[i].x - mx); sum += x[i].x;
-        x[i].y = expf(x[i].y - mx); sum += x[i].y;
-        x[i].z = expf(x[i].z - mx); sum += x[i].z;
-        x[i].w = expf(x[i].w - mx); sum += x[i].w;
+        x[i].x = Ex2Approx(__fmaf_rn(x[i].x, kLog2E, shift)); sum += x[i].x;
+        x[i].y = Ex2Approx(__fmaf_rn(x[i].y, kLog2E, shift)); sum += x[i].y;
+        x[i].z = Ex2Approx(__fmaf_rn(x[i].z, kLog2E, shift)); sum += x[i].z;
+        x[i].w = Ex2Approx(__fmaf_rn(x[i].w, kLog2E, shift)); sum += x[i].w;
       }
     }
     sum = BlockReduce<float>(sum, 0.0f, smem_f, WarpSumF, [](float a, float b) { return a + b; });
     const float inv_sum = 1.0f / sum;
     float4* prow = reinterpret_cast<float4*>(probs + n * C);
+    const int32_t lab = labels[n];
+    const int lab4 = lab >= 0 && static_cast<size_t>(lab) < C ? lab >> 2 : -1;
 #pragma unroll
     for (int i = 0; i < kWideVecs; ++i) {
       const int c4 = i * kWideThreads + tid;
-      if (c4 < C4)
-        prow[c4] = make_float4(x[i].x * inv_sum, x[i].y * inv_sum, x[i].z * inv_sum, x[i].w * inv_sum);
+      if (c4 < C4) {
+        const float4 p = make_float4(x[i].x * inv_sum, x[i].y * inv_sum, x[i].z * inv_sum, x[i].w * inv_sum);
+        if (store_probs) prow[c4] = p;
+        if (c4 == lab4) label_prob = (lab & 3) == 0 ? p.x : (lab & 3) == 1 ? p.y : (lab & 3) == 2 ? p.z : p.w;
+        if (sh.dst) {
+          // The backward instruction's arithmetic on the value it would have read back.
+          float4 v = make_float4(bwd_scale * p.x, bwd_scale * p.y, bwd_scale * p.z, bwd_scale * p.w);
+          if (c4 == lab4) {
+            switch (lab & 3) {
+              case 0: v.x -= bwd_scale; break;
+              case 1: v.y -= bwd_scale; break;
+              case 2: v.z -= bwd_scale; break;
+              default: v.w -= bwd_scale; break;
+            }
+          }
+          ShadowStore4(sh, n * static_cast<size_t>(C4) + c4, static_cast<uint32_t>(c4 * 4), v);
+        }
+      }
     }
-    __syncthreads();  // the row's stores are visible to thread 0 below
+    __syncthreads();  // label_prob is visible to thread 0 below; and the smem buffers are reused
     if (tid == 0) {
-      const int32_t lab = labels[n];
       double v;
       if (masked && lab < 0) v = 0.0;
       else if (lab < 0 || static_cast<size_t>(lab) >= C) v = NAN;
-      else v = NegLogSafe(probs[n * C + static_cast<size_t>(lab)]);
+      else v = NegLogSafe(label_prob);
       row_loss[n] = v;
     }
   }
@@ -408,10 +433,11 @@ inline unsigned GridFor(size_t items, int threads, unsigned cap) {
 
 }  // namespace
 
-void SoftmaxXEntFwd(bool masked, const float* logits, const int32_t* labels, float* loss,
+bool SoftmaxXEntFwd(bool masked, const float* logits, const int32_t* labels, float* loss,
                     float* probs, size_t N, size_t C, double* row_scratch,
-                    unsigned long long* count_scratch, cudaStream_t s) {
-  if (N == 0) return;
+                    unsigned long long* count_scratch, cudaStream_t s, const XEntFusedBwd* fused_bwd) {
+  if (N == 0) return false;
+  bool fused = false;
   const bool wide = C >= 4096 && C <= static_cast<size_t>(4 * kWideThreads * kWideVecs) &&
                     (C & 3) == 0 && ((reinterpret_cast<uintptr_t>(logits) |
                                       reinterpret_cast<uintptr_t>(probs)) & 15) == 0;
@@ -427,8 +453,17 @@ void SoftmaxXEntFwd(bool masked, const float* logits, const int32_t* labels, flo
       configured[dev] = true;
     }
     const unsigned blocks = static_cast<unsigned>(N < 148 * 4 ? N : 148 * 4);
-    XEntRowsWideKernel<<<blocks, kWideThreads, C * sizeof(float), s>>>(logits, labels, probs,
-                                                                       row_scratch, N, C, masked);
+    Shadow sh{};
+    float bwd_scale = 0.0f;
+    bool store_probs = true;
+    if (fused_bwd && !masked && ShadowUsable(&fused_bwd->shadow, probs, N * C) && fused_bwd->shadow.cols == C) {
+      sh = fused_bwd->shadow;
+      bwd_scale = fused_bwd->seed / static_cast<float>(N);   // the backward kernel's own expression
+      store_probs = fused_bwd->store_probs;
+      fused = true;
+    }
+    XEntRowsWideKernel<<<blocks, kWideThreads, C * sizeof(float), s>>>(logits, labels, probs, row_scratch, N, C,
+                                                                       masked, sh, bwd_scale, store_probs);
   } else {
     const int threads = C >= 1024 ? 256 : (C >= 128 ? 128 : 32);
     const unsigned blocks = static_cast<unsigned>(N < 148 * 16 ? N : 148 * 16);
@@ -437,6 +472,7 @@ void SoftmaxXEntFwd(bool masked, const float* logits, const int32_t* labels, flo
   const size_t grain = ChunkGrain(N, RowGrain(C, kGrainMath));
   XEntFoldKernel<<<1, kMaxChunks, 0, s>>>(row_scratch, labels, loss, N, grain, masked,
                                          count_scratch);
+  return fused;
 }
 
 bool SoftmaxXEntBwd(bool masked, const float* probs, const int32_t* labels, const float* seed,

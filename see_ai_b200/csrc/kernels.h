@@ -87,9 +87,20 @@ void RmsNormBwd(const float* dy, const float* x, const float* gamma, const float
 // ---- losses -----------------------------------------------------------------
 // `row_scratch` holds N doubles (per-row -log p) and `count_scratch` one
 // uint64 (the masked forms' target count).
-void SoftmaxXEntFwd(bool masked, const float* logits, const int32_t* labels, float* loss,
+// The backward instruction that follows (dlogits = seed / N * (p - onehot)) can ride
+// the forward's row pass when only its bf16 operand copy is needed: XEntFusedBwd
+// carries the seed the plan fills in between, the copy, and whether the
+// probabilities themselves still have to be stored.  Returns true when the
+// backward was done here (wide rows only); false leaves it to SoftmaxXEntBwd.
+struct XEntFusedBwd {
+  Shadow shadow;
+  float seed = 1.0f;
+  bool store_probs = true;
+};
+bool SoftmaxXEntFwd(bool masked, const float* logits, const int32_t* labels, float* loss,
                     float* probs, size_t N, size_t C, double* row_scratch,
-                    unsigned long long* count_scratch, cudaStream_t s);
+                    unsigned long long* count_scratch, cudaStream_t s,
+                    const XEntFusedBwd* fused_bwd = nullptr);
 bool SoftmaxXEntBwd(bool masked, const float* probs, const int32_t* labels, const float* seed,
                     float* dlogits, size_t N, size_t C, unsigned long long* count_scratch,
                     cudaStream_t s, const Shadow* shadow = nullptr);
