@@ -15,6 +15,26 @@ namespace see::k::exact {
 
 namespace {
 
+// Two-wide FP32 adds.  `add.rn.f32x2` rounds each half exactly as `add.rn.f32`
+// does, and ptxas does not contract a SCALAR multiply into a packed add (it does
+// contract a packed multiply feeding a packed add into a packed FMA, even with
+// -fmad=false, which would break the reference's rounding: so products stay
+// scalar).  Two neighbouring columns then cost two multiplies and one add per k
+// instead of two and two.
+__device__ __forceinline__ unsigned long long Pack2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void Unpack2(unsigned long long v, float* lo, float* hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(*lo), "=f"(*hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long Add2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 // One quad of the quad order for four neighbouring columns:
 //   c[j] += ((a0*w0[j] + a1*w1[j]) + a2*w2[j]) + a3*w3[j]
 __device__ __forceinline__ void QuadStep(float (&c)[4], float a0, float a1, float a2, float a3,
@@ -475,32 +495,35 @@ __global__ void __launch_bounds__(kExpandThreads) ExpandKernel(Params p) {
       if (kLane) {
         // Product k into accumulator k mod 8, from zero; accumulators summed 0..7.
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float acc[8];
+        for (int j = 0; j < 4; j += 2) {   // columns j and j + 1 share each packed add
+          unsigned long long acc[8];
 #pragma unroll
-          for (int l = 0; l < 8; ++l) acc[l] = 0.0f;
+          for (int l = 0; l < 8; ++l) acc[l] = Pack2(0.0f, 0.0f);
 #pragma unroll
-          for (int k = 0; k < K; ++k) acc[k & 7] = acc[k & 7] + a[k] * w[k][j];
-          float s = acc[0];
+          for (int k = 0; k < K; ++k) acc[k & 7] = Add2(acc[k & 7], Pack2(a[k] * w[k][j], a[k] * w[k][j + 1]));
+          unsigned long long s = acc[0];
 #pragma unroll
-          for (int l = 1; l < 8; ++l) s = s + acc[l];
-          v[j] = p.alpha * s;
+          for (int l = 1; l < 8; ++l) s = Add2(s, acc[l]);
+          float s0, s1;
+          Unpack2(s, &s0, &s1);
+          v[j] = p.alpha * s0;
+          v[j + 1] = p.alpha * s1;
         }
       } else {
 #pragma unroll
         for (int kq = 0; kq < K; ++kq) a[kq] = p.alpha * a[kq];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float c = 0.0f;
+        for (int j = 0; j < 4; j += 2) {   // columns j and j + 1 share each packed add
+          unsigned long long c = Pack2(0.0f, 0.0f);
 #pragma unroll
           for (int kq = 0; kq < K; kq += 4) {
-            float t = a[kq] * w[kq][j];
-            t = t + a[kq + 1] * w[kq + 1][j];
-            t = t + a[kq + 2] * w[kq + 2][j];
-            t = t + a[kq + 3] * w[kq + 3][j];
-            c = c + t;
+            unsigned long long t = Pack2(a[kq] * w[kq][j], a[kq] * w[kq][j + 1]);
+            t = Add2(t, Pack2(a[kq + 1] * w[kq + 1][j], a[kq + 1] * w[kq + 1][j + 1]));
+            t = Add2(t, Pack2(a[kq + 2] * w[kq + 2][j], a[kq + 2] * w[kq + 2][j + 1]));
+            t = Add2(t, Pack2(a[kq + 3] * w[kq + 3][j], a[kq + 3] * w[kq + 3][j + 1]));
+            c = Add2(c, t);
           }
-          v[j] = c;
+          Unpack2(c, &v[j], &v[j + 1]);
         }
       }
       if (p.addend) {
