@@ -374,6 +374,8 @@ void CudaBackend::EndRange() {
   skip_next_add_bias_ = false;
   act_fusion_.clear();
   loss_fusion_.clear();
+  add_fusion_.clear();
+  skip_add_at_ = -1;
   skip_act_at_ = -1;
   elided_.clear();
   pending_elided_.clear();
@@ -661,6 +663,7 @@ static bool DeadFrom(std::span<const Instruction> program, const std::vector<Ext
 void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t begin, size_t end) {
   act_fusion_.assign(end > begin ? end - begin : 0, ActFusion{});
   loss_fusion_.assign(end > begin ? end - begin : 0, LossFusion{});
+  add_fusion_.assign(end > begin ? end - begin : 0, AddFusion{});
   if (coherence_ == Coherence::kStrict || !relaxed_allowed_ || !epilogue_fusion_ || end < begin + 3) return;
   // Under the step-program promise liveness is decided on the whole program.
   const bool whole = step_program_ != nullptr && program.data() == step_program_;
@@ -784,6 +787,44 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
     shadow_plan_[i - begin] = sp;
     shadow_plan_[next - begin].want = false;
   }
+  // A following kAddEW as the epilogue's addend.
+  for (size_t i = begin; i + 1 < end; ++i) {
+    const Instruction& g = program[i];
+    if (!IsRelaxedFrozenGemm(g) || RefSpace(g.in[2]) != kArena || act_fusion_[i - begin].mode != 0) continue;
+    if ((g.flags & (kFlagEpilogueBias | kFlagGemmAddend)) || ActOf(g.flags) != kActNone) continue;
+    const uint64_t M = g.out[0], N = g.out[1], bytes = M * N * 4;
+    size_t next = i + 1;
+    uint64_t z_ref = g.in[2];
+    if (bias_fusion_[i - begin].fuse) {
+      z_ref = bias_fusion_[i - begin].out_ref;
+      next = i + 2;
+    }
+    if (next >= end) continue;
+    const Instruction& add = program[next];
+    if (add.opcode != kAddEW || add.out[0] != M * N || shadow_plan_[next - begin].want) continue;
+    uint64_t x_ref;
+    if (add.in[0] == z_ref && add.in[1] != z_ref) x_ref = add.in[1];
+    else if (add.in[1] == z_ref && add.in[0] != z_ref) x_ref = add.in[0];
+    else continue;
+    const uint64_t out_ref = add.in[2];
+    if (RefSpace(x_ref) != kArena || RefSpace(out_ref) != kArena || (RefOffset(x_ref) & 15) != 0 ||
+        (RefOffset(out_ref) & 15) != 0)
+      continue;
+    const uint64_t z_lo = RefOffset(z_ref), z_hi = z_lo + bytes;
+    const uint64_t x_lo = RefOffset(x_ref), x_hi = x_lo + bytes;
+    const uint64_t o_lo = RefOffset(out_ref), o_hi = o_lo + bytes;
+    if (!disjoint(x_lo, x_hi, z_lo, z_hi)) continue;
+    if (o_lo != x_lo && !disjoint(o_lo, o_hi, x_lo, x_hi)) continue;   // in place over x, or apart from it
+    if (o_lo != z_lo && !disjoint(o_lo, o_hi, z_lo, z_hi)) continue;   // likewise for the product
+    if (o_lo != z_lo && !dead_after(next, DeadQuery{z_lo, z_hi, false, ~0ull, 0, 0}, i)) continue;
+    AddFusion af;
+    af.fuse = true;
+    af.x_ref = x_ref;
+    af.out_ref = out_ref;
+    af.add_index = static_cast<uint32_t>(next - begin);
+    if (o_lo != z_lo) { af.z_lo = z_lo; af.z_hi = z_hi; }
+    add_fusion_[i - begin] = af;
+  }
 }
 
 const k::Shadow* CudaBackend::ShadowFor(uint64_t out_ref, uint64_t elems) const {
@@ -866,7 +907,8 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   const bool absorbed = skip_act_at_ == static_cast<int64_t>(range_index_);
   if (absorbed) skip_act_at_ = -1;
   // (A kAddBias done by the preceding product's epilogue reads nothing either.)
-  const bool bias_done = skip_next_add_bias_ && ins.opcode == kAddBias;
+  const bool bias_done = (skip_next_add_bias_ && ins.opcode == kAddBias) ||
+                         skip_add_at_ == static_cast<int64_t>(range_index_);
   if (!elided_.empty() && !absorbed && !bias_done) {
     for (size_t i = 0; i < ext.count; ++i) {
       const Extent& e = ext.e[i];
@@ -981,6 +1023,13 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
       a.bias = Rd(fuse->bias_ref);
       a.C = Wr(fuse->out_ref);
     }
+    const AddFusion* adf = range_index_ < add_fusion_.size() && add_fusion_[range_index_].fuse
+                               ? &add_fusion_[range_index_] : nullptr;
+    if (adf) {   // the kAddEW after it (after the fused kAddBias, if any): the epilogue's addend
+      a.addend = Rd(adf->x_ref);
+      a.addend_after_bias = true;
+      a.C = Wr(adf->out_ref);
+    }
     const ActFusion* af = range_index_ < act_fusion_.size() && act_fusion_[range_index_].mode != 0 &&
                                   cur_shadow_.dst ? &act_fusion_[range_index_] : nullptr;
     if (af) {   // and the activation after it: its result leaves as the consumer's bf16 operand
@@ -1001,6 +1050,11 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
       counters_.kernel_launches += launches;
       skip_next_add_bias_ = fuse != nullptr;
       if (fuse) ++counters_.fused_dispatches;
+      if (adf) {
+        ++counters_.fused_dispatches;
+        skip_add_at_ = static_cast<int64_t>(adf->add_index);
+        if (adf->z_hi > adf->z_lo) pending_elided_.push_back({adf->z_lo, adf->z_hi});
+      }
       if (af) {
         ++counters_.fused_dispatches;
         shadow_written_ = true;
@@ -1014,6 +1068,11 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
     // launches == 0: the shape is outside the tensor-core kernel's domain.
     if (fuse) {
       a.bias = nullptr;
+      a.C = Wr(ins.in[2]);
+    }
+    if (adf) {
+      a.addend = nullptr;
+      a.addend_after_bias = false;
       a.C = Wr(ins.in[2]);
     }
     a.fuse_mode = 0;
@@ -1123,6 +1182,10 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
     case kGemmNNBF16: case kGemmNTBF16:
       return DispatchGemm(ins);
     case kAddEW:
+      if (skip_add_at_ == static_cast<int64_t>(range_index_)) {   // done as the preceding product's addend
+        skip_add_at_ = -1;
+        break;
+      }
       shadow_written_ = k::AddEW(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), ins.out[0], s,
                                  ShadowFor(ins.in[2], ins.out[0]));
       launched();

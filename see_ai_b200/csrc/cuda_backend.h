@@ -292,6 +292,18 @@ class CudaBackend {
   };
   std::vector<LossFusion> loss_fusion_;   // per range position (of the forward)
 
+  // A kAddEW that follows a relaxed GEMM (directly, or after the kAddBias fused
+  // above) and adds another tensor to its output: done as the epilogue's addend
+  // (same f32 add) when the un-summed product is dead afterwards.
+  struct AddFusion {
+    bool fuse = false;
+    uint64_t x_ref = kNullRef, out_ref = kNullRef;
+    uint32_t add_index = 0;
+    uint64_t z_lo = 0, z_hi = 0;   // the product's own range when it stays unwritten
+  };
+  std::vector<AddFusion> add_fusion_;   // per range position (of the GEMM)
+  int64_t skip_add_at_ = -1;            // the absorbed kAddEW (its output IS written, by the product)
+
   Counters counters_;
   struct UmmaState;
   std::unique_ptr<UmmaState> umma_;

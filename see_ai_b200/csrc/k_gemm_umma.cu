@@ -134,11 +134,15 @@ __device__ __forceinline__ void EpilogueStore(const UmmaEpilogue& ep, size_t at,
                                               bool has_kscale = false,
                                               float4 kscale = make_float4(1.f, 1.f, 1.f, 1.f)) {
   float4 v = make_float4(acc.x * scale.x, acc.y * scale.y, acc.z * scale.z, acc.w * scale.w);
-  if (ep.addend) {
+  if (ep.addend && !ep.addend_last) {
     const float4 d = __ldg(reinterpret_cast<const float4*>(ep.addend + at));
     v = make_float4(d.x + v.x, d.y + v.y, d.z + v.z, d.w + v.w);
   }
   if (ep.bias) v = make_float4(v.x + bias.x, v.y + bias.y, v.z + bias.z, v.w + bias.w);
+  if (ep.addend && ep.addend_last) {   // an absorbed kAddEW that followed the kAddBias
+    const float4 d = __ldg(reinterpret_cast<const float4*>(ep.addend + at));
+    v = make_float4(d.x + v.x, d.y + v.y, d.z + v.z, d.w + v.w);
+  }
   if (ep.act != kActNone)
     v = make_float4(ApplyAct(v.x, ep.act), ApplyAct(v.y, ep.act), ApplyAct(v.z, ep.act),
                     ApplyAct(v.w, ep.act));

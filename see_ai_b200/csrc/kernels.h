@@ -207,6 +207,7 @@ struct GemmArgs {
   uint16_t* fuse_shadow = nullptr;
   const float* fuse_shadow_scale = nullptr;
   bool store_c = true;
+  bool addend_after_bias = false;   // tensor-core path: v = addend + (product + bias)
   // Scratch for the split-K form of the transposed-A product (optional).
   float* split_scratch = nullptr;
   size_t split_scratch_floats = 0;

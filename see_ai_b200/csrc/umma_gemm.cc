@@ -288,6 +288,7 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
   ep.shadow_dst = a.fuse_shadow;
   ep.shadow_k_scale = a.fuse_shadow_scale;
   ep.store_c = a.store_c ? 1 : 0;
+  ep.addend_last = a.addend_after_bias ? 1 : 0;
   if (impl->prof_before) cudaEventRecord(impl->prof_before, stream);
   if (cudaError_t e = k::UmmaGemmLaunch(map_a, map_b, ep, stream); e != cudaSuccess)
     return std::string("tensor-core GEMM launch: ") + cudaGetErrorString(e);

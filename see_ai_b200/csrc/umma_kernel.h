@@ -19,7 +19,7 @@ constexpr uint32_t kBlockM = 128, kBlockN = 128, kBlockK = 64, kStages = 3;
 
 struct UmmaEpilogue {
   float* C;                 // [M, N] f32
-  const float* addend;      // [M, N] or null:  v = d + v
+  const float* addend;      // [M, N] or null:  v = d + v (before the bias, or after it when addend_last)
   const float* bias;        // [N] or null:     v = v + bias[n]
   const float* col_scale;   // [N] or null:     v = acc * col_scale[n]   (else acc * alpha)
   float alpha;
@@ -38,6 +38,7 @@ struct UmmaEpilogue {
   uint16_t* shadow_dst = nullptr;
   const float* shadow_k_scale = nullptr;
   int store_c = 1;
+  int addend_last = 0;
 };
 
 size_t UmmaSmemBytes();

@@ -214,3 +214,51 @@ def test_engine_step_with_fusions_is_the_unfused_step_bit_for_bit():
     # Per eagerly executed pass: two bias adds, two GELU forwards, two GELU backwards
     # and the loss backward (done by the loss forward's row pass) are absorbed.
     assert f_off == 0 and f_on >= 7
+
+
+# ---- a following elementwise add as the epilogue's addend ------------------------------
+
+def _build_add(rng, M, K, N, with_bias, product_first, read_later):
+    a = Arena(rng)
+    x = a.alloc(M * K, "normal")
+    w = a.ro_alloc(rng.integers(-127, 128, size=K * N, dtype=np.int8))
+    sc = a.ro_alloc((rng.random(N) * 0.01 + 1e-3).astype(np.float32))
+    bias = a.ro_alloc(rng.standard_normal(N).astype(np.float32))
+    res = a.alloc(M * N, "normal")
+    r = a.alloc(M * N); z = a.alloc(M * N); out = a.alloc(M * N); keep = a.alloc(M * N)
+    prog = [P.Instr(Op.GEMM_NN_Q8, REL | CS, 0, (x, w, r, sc), (M, N, K))]
+    src = r
+    if with_bias:
+        prog.append(P.Instr(Op.ADD_BIAS, 0, 0, (r, bias, z, P.NULL_REF), (M, N, 0)))
+        src = z
+    ops = (src, res) if product_first else (res, src)
+    prog.append(P.Instr(Op.ADD_EW, 0, 0, (ops[0], ops[1], out, P.NULL_REF), (M * N, 0, 0)))
+    if read_later:
+        prog.append(P.Instr(Op.COPY, 0, 0, (src, keep), (M * N, 0, 0)))
+    prog.append(P.Instr(Op.FILL, 0, 0, (r, P.f32_bits(0.0)), (M * N, 0, 0)))
+    prog.append(P.Instr(Op.FILL, 0, 0, (z, P.f32_bits(0.0)), (M * N, 0, 0)))
+    arena, ro = a.build()
+    return prog, arena, ro
+
+
+@pytest.mark.parametrize("size", ACT_SIZES, ids=["one-tile", "persistent"])
+@pytest.mark.parametrize("with_bias", [False, True], ids=["plain", "after-bias"])
+@pytest.mark.parametrize("product_first", [False, True], ids=["x+p", "p+x"])
+def test_following_add_rides_the_gemm_epilogue(size, with_bias, product_first):
+    M, K, N = size
+    prog, arena0, ro = _build_add(np.random.default_rng(31), M, K, N, with_bias, product_first, False)
+    fused, c_fused = _run(prog, arena0, ro, one_range=True)
+    split, c_split = _run(prog, arena0, ro, one_range=False)
+    assert np.isfinite(fused.view(np.float32)).all()
+    assert np.array_equal(fused, split)
+    assert c_split.kernel_launches - c_fused.kernel_launches == (2 if with_bias else 1)
+    assert c_fused.fused_dispatches == (2 if with_bias else 1)
+
+
+def test_following_add_is_left_alone_when_the_product_is_read_later():
+    M, K, N = ACT_SIZES[0]
+    prog, arena0, ro = _build_add(np.random.default_rng(32), M, K, N, False, True, True)
+    fused, c_fused = _run(prog, arena0, ro, one_range=True)
+    split, c_split = _run(prog, arena0, ro, one_range=False)
+    assert np.array_equal(fused, split)
+    assert c_fused.fused_dispatches == 0 and c_split.kernel_launches == c_fused.kernel_launches
