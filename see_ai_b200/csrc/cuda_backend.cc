@@ -825,6 +825,47 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
     if (o_lo != z_lo) { af.z_lo = z_lo; af.z_hi = z_hi; }
     add_fusion_[i - begin] = af;
   }
+  // The same for a LayerNorm backward whose dx is only one term of a sum.
+  for (size_t i = begin; i + 1 < end; ++i) {
+    const Instruction& ln = program[i];
+    const Instruction& add = program[i + 1];
+    if (ln.opcode != kLayerNormBwd || add.opcode != kAddEW || RefSpace(ln.in[3]) != kArena) continue;
+    const uint64_t elems = static_cast<uint64_t>(Hi32(ln.out[2])) * Lo32(ln.out[2]), bytes = elems * 4;
+    if (add.out[0] != elems || shadow_plan_[i - begin].want) continue;
+    const uint64_t z_ref = ln.in[3];
+    uint64_t x_ref;
+    if (add.in[0] == z_ref && add.in[1] != z_ref) x_ref = add.in[1];
+    else if (add.in[1] == z_ref && add.in[0] != z_ref) x_ref = add.in[0];
+    else continue;
+    const uint64_t out_ref = add.in[2];
+    if (RefSpace(x_ref) != kArena || RefSpace(out_ref) != kArena) continue;
+    const uint64_t z_lo = RefOffset(z_ref), z_hi = z_lo + bytes;
+    const uint64_t x_lo = RefOffset(x_ref), x_hi = x_lo + bytes;
+    const uint64_t o_lo = RefOffset(out_ref), o_hi = o_lo + bytes;
+    if (!disjoint(x_lo, x_hi, z_lo, z_hi)) continue;
+    if (o_lo != x_lo && !disjoint(o_lo, o_hi, x_lo, x_hi)) continue;
+    if (o_lo != z_lo && !disjoint(o_lo, o_hi, z_lo, z_hi)) continue;
+    // The kernel reads whole rows of dy and x before it writes the row of the sum:
+    // the sum may lie over either, but not partly.
+    bool partial = false;
+    for (int op = 0; op < 2; ++op) {
+      const uint64_t s_lo = RefOffset(ln.in[op]), s_hi = s_lo + bytes;
+      if (RefSpace(ln.in[op]) == kArena && s_lo != o_lo && !disjoint(o_lo, o_hi, s_lo, s_hi)) partial = true;
+    }
+    if (partial) continue;
+    if (o_lo != z_lo && !dead_after(i + 1, DeadQuery{z_lo, z_hi, false, ~0ull, 0, 0}, i)) continue;
+    AddFusion af;
+    af.fuse = true;
+    af.x_ref = x_ref;
+    af.out_ref = out_ref;
+    af.add_index = static_cast<uint32_t>(i + 1 - begin);
+    if (o_lo != z_lo) { af.z_lo = z_lo; af.z_hi = z_hi; }
+    add_fusion_[i - begin] = af;
+    if (shadow_plan_[i + 1 - begin].want) {   // the kernel makes the sum's copy too
+      shadow_plan_[i - begin] = shadow_plan_[i + 1 - begin];
+      shadow_plan_[i + 1 - begin].want = false;
+    }
+  }
 }
 
 const k::Shadow* CudaBackend::ShadowFor(uint64_t out_ref, uint64_t elems) const {
@@ -1253,11 +1294,23 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
           ShadowFor(ins.in[3], Hi32(ins.out[0]) * Lo32(ins.out[0])));
       launched();
       break;
-    case kLayerNormBwd:
-      k::LayerNormBwd(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Rd(ins.out[0]), Rd(ins.out[1]),
-                      Wr(ins.in[3]), Hi32(ins.out[2]), Lo32(ins.out[2]), s);
+    case kLayerNormBwd: {
+      const AddFusion* adf = range_index_ < add_fusion_.size() && add_fusion_[range_index_].fuse
+                                 ? &add_fusion_[range_index_] : nullptr;
+      const int fused = k::LayerNormBwd(Rd(ins.in[0]), Rd(ins.in[1]), Rd(ins.in[2]), Rd(ins.out[0]),
+                                         Rd(ins.out[1]), Wr(ins.in[3]), Hi32(ins.out[2]), Lo32(ins.out[2]), s,
+                                         adf ? Rd(adf->x_ref) : nullptr, adf ? Wr(adf->out_ref) : nullptr,
+                                         adf ? ShadowFor(adf->out_ref, static_cast<uint64_t>(Hi32(ins.out[2])) *
+                                                                           Lo32(ins.out[2])) : nullptr);
       launched();
+      if (fused) {   // the kAddEW after it has been done
+        shadow_written_ = fused == 2;
+        ++counters_.fused_dispatches;
+        skip_add_at_ = static_cast<int64_t>(adf->add_index);
+        if (adf->z_hi > adf->z_lo) pending_elided_.push_back({adf->z_lo, adf->z_hi});
+      }
       break;
+    }
     case kRmsNormFwd:
       k::RmsNormFwd(Rd(ins.in[0]), Rd(ins.in[1]), Wr(ins.in[2]), Wr(ins.in[3]), Hi32(ins.out[0]),
                     Lo32(ins.out[0]), NormEpsOf(ins.imm), s);

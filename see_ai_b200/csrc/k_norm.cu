@@ -147,7 +147,7 @@ template <int V>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 LayerNormBwdVecKernel(const float* __restrict__ dy, const float* __restrict__ x,
                       const float* __restrict__ gamma, const float* __restrict__ mean,
-                      const float* __restrict__ rstd, float* __restrict__ dx, size_t rows) {
+                      const float* __restrict__ rstd, float* dx, size_t rows, const float* addend, Shadow sh) {
   constexpr size_t cols = 128 * V;
   const size_t r = blockIdx.x * static_cast<size_t>(kWarpsPerBlock) + threadIdx.x / 32;
   const int lane = threadIdx.x & 31;
@@ -178,10 +178,18 @@ LayerNormBwdVecKernel(const float* __restrict__ dy, const float* __restrict__ x,
   const float mg = static_cast<float>(sum_g) * inv_d;
   const float mgx = static_cast<float>(sum_gx) * inv_d;
   float4* dxr = reinterpret_cast<float4*>(dx + r * cols);
+  const float4* adr = addend ? reinterpret_cast<const float4*>(addend + r * cols) : nullptr;
 #pragma unroll
-  for (int i = 0; i < V; ++i)
-    dxr[lane + 32 * i] = make_float4(rs * (g[i][0] - mg - xhat[i][0] * mgx), rs * (g[i][1] - mg - xhat[i][1] * mgx),
-                                     rs * (g[i][2] - mg - xhat[i][2] * mgx), rs * (g[i][3] - mg - xhat[i][3] * mgx));
+  for (int i = 0; i < V; ++i) {
+    float4 v = make_float4(rs * (g[i][0] - mg - xhat[i][0] * mgx), rs * (g[i][1] - mg - xhat[i][1] * mgx),
+                           rs * (g[i][2] - mg - xhat[i][2] * mgx), rs * (g[i][3] - mg - xhat[i][3] * mgx));
+    if (adr) {   // an absorbed kAddEW: the sum it would have written (dx may alias the addend)
+      const float4 a = adr[lane + 32 * i];
+      v = make_float4(a.x + v.x, a.y + v.y, a.z + v.z, a.w + v.w);
+    }
+    dxr[lane + 32 * i] = v;
+    if (sh.dst) ShadowStore4(sh, r * (cols / 4) + lane + 32 * i, static_cast<uint32_t>((lane + 32 * i) * 4), v);
+  }
 }
 
 inline bool Vec16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -251,22 +259,30 @@ bool LayerNormFwd(const float* x, const float* gamma, const float* beta, float* 
                                                                      rows, cols, eps, sh);
   return shadowed;
 }
-void LayerNormBwd(const float* dy, const float* x, const float* gamma, const float* mean,
-                  const float* rstd, float* dx, size_t rows, size_t cols, cudaStream_t s) {
-  if (rows == 0) return;
-  if (cols % 128 == 0 && cols <= 1024 && Vec16(dy) && Vec16(x) && Vec16(gamma) && Vec16(dx)) {
+int LayerNormBwd(const float* dy, const float* x, const float* gamma, const float* mean,
+                  const float* rstd, float* dx, size_t rows, size_t cols, cudaStream_t s,
+                  const float* addend, float* sum_out, const Shadow* sum_shadow) {
+  if (rows == 0) return 0;
+  if (cols % 128 == 0 && cols <= 1024 && Vec16(dy) && Vec16(x) && Vec16(gamma) && Vec16(dx) && Vec16(addend) &&
+      Vec16(sum_out)) {
     const unsigned blocks = RowBlocks(rows);
+    const bool fused = addend != nullptr && sum_out != nullptr;
+    if (fused) dx = sum_out;
+    else addend = nullptr;
+    const Shadow sh = fused && ShadowUsable(sum_shadow, sum_out, rows * cols) && sum_shadow->cols == cols
+                          ? *sum_shadow : Shadow{};
 #define SEE_LN_BWD(V) \
-    case V: LayerNormBwdVecKernel<V><<<blocks, kWarpsPerBlock * 32, 0, s>>>(dy, x, gamma, mean, rstd, dx, rows); break
+    case V: LayerNormBwdVecKernel<V><<<blocks, kWarpsPerBlock * 32, 0, s>>>(dy, x, gamma, mean, rstd, dx, rows, addend, sh); break
     switch (cols / 128) {
       SEE_LN_BWD(1); SEE_LN_BWD(2); SEE_LN_BWD(3); SEE_LN_BWD(4);
       SEE_LN_BWD(5); SEE_LN_BWD(6); SEE_LN_BWD(7); SEE_LN_BWD(8);
     }
 #undef SEE_LN_BWD
-    return;
+    return fused ? (sh.dst ? 2 : 1) : 0;
   }
   LayerNormBwdKernel<<<RowBlocks(rows), kWarpsPerBlock * 32, 0, s>>>(dy, x, gamma, mean, rstd, dx,
                                                                      rows, cols);
+  return 0;
 }
 void RmsNormFwd(const float* x, const float* gamma, float* y, float* rstd, size_t rows,
                 size_t cols, float eps, cudaStream_t s) {

@@ -77,8 +77,14 @@ void ToBf16(const float* x, uint16_t* out, size_t rows, size_t cols, const float
 bool LayerNormFwd(const float* x, const float* gamma, const float* beta, float* y, float* mean,
                   float* rstd, size_t rows, size_t cols, float eps, cudaStream_t s,
                   const Shadow* shadow = nullptr);
-void LayerNormBwd(const float* dy, const float* x, const float* gamma, const float* mean,
-                  const float* rstd, float* dx, size_t rows, size_t cols, cudaStream_t s);
+// With addend and sum_out both given, a following kAddEW rides along: the kernel
+// writes sum_out = addend + dx instead of dx (sum_out may alias addend).  Returns
+// 0: dx was written as usual (the kAddEW still has to run); 1: the sum was
+// written; 2: the sum and its bf16 copy.
+int LayerNormBwd(const float* dy, const float* x, const float* gamma, const float* mean,
+                  const float* rstd, float* dx, size_t rows, size_t cols, cudaStream_t s,
+                  const float* addend = nullptr, float* sum_out = nullptr,
+                  const Shadow* sum_shadow = nullptr);   // the copy the kAddEW would have made of the sum
 void RmsNormFwd(const float* x, const float* gamma, float* y, float* rstd, size_t rows,
                 size_t cols, float eps, cudaStream_t s);
 void RmsNormBwd(const float* dy, const float* x, const float* gamma, const float* rstd,

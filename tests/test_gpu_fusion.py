@@ -262,3 +262,28 @@ def test_following_add_is_left_alone_when_the_product_is_read_later():
     split, c_split = _run(prog, arena0, ro, one_range=False)
     assert np.array_equal(fused, split)
     assert c_fused.fused_dispatches == 0 and c_split.kernel_launches == c_fused.kernel_launches
+
+
+@pytest.mark.parametrize("dx_first", [False, True], ids=["x+dx", "dx+x"])
+@pytest.mark.parametrize("in_place", [False, True], ids=["new", "over-addend"])
+def test_add_after_layernorm_backward_rides_the_kernel(dx_first, in_place):
+    M, D = 512, 256
+    rng = np.random.default_rng(41)
+    a = Arena(rng)
+    x = a.alloc(M * D, "normal"); gamma = a.alloc(D, "normal"); beta = a.alloc(D, "normal")
+    y = a.alloc(M * D); mean = a.alloc(M); rstd = a.alloc(M)
+    dy = a.alloc(M * D, "normal"); res = a.alloc(M * D, "normal")
+    dx = a.alloc(M * D); out = res if in_place else a.alloc(M * D)
+    ops = (dx, res) if dx_first else (res, dx)
+    prog = [
+        P.Instr(Op.LAYERNORM_FWD, 0, P.f32_bits(1e-5), (x, gamma, beta, y), (P.pack2(M, D), mean, rstd)),
+        P.Instr(Op.LAYERNORM_BWD, 0, 0, (dy, x, gamma, dx), (mean, rstd, P.pack2(M, D))),
+        P.Instr(Op.ADD_EW, 0, 0, (ops[0], ops[1], out, P.NULL_REF), (M * D, 0, 0)),
+        P.Instr(Op.FILL, 0, 0, (dx, P.f32_bits(0.0)), (M * D, 0, 0)),
+    ]
+    arena0, ro = a.build()
+    fused, c_fused = _run(prog, arena0, ro, one_range=True)
+    split, c_split = _run(prog, arena0, ro, one_range=False)
+    assert np.isfinite(fused.view(np.float32)).all()
+    assert np.array_equal(fused, split)
+    assert c_split.kernel_launches - c_fused.kernel_launches == 1 and c_fused.fused_dispatches == 1
