@@ -825,6 +825,51 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
     if (o_lo != z_lo) { af.z_lo = z_lo; af.z_hi = z_hi; }
     add_fusion_[i - begin] = af;
   }
+  // The same for the rank-r expand product of an adapter (exact kernels): the
+  // residual add after the adapted projection.
+  for (size_t i = begin; i + 1 < end; ++i) {
+    const Instruction& g = program[i];
+    const Instruction& add = program[i + 1];
+    if ((g.opcode != kGemmNN && g.opcode != kGemmNT) || (g.flags & kFlagRelaxed) || add.opcode != kAddEW) continue;
+    if (RefSpace(g.in[2]) != kArena || shadow_plan_[i + 1 - begin].want) continue;
+    const uint64_t M = g.out[0], N = g.out[1], K = g.out[2], bytes = M * N * 4;
+    if ((K != 4 && K != 8 && K != 12 && K != 16) || (N & 3) != 0 || N < 64 || M < 64) continue;   // the expand kernel's shapes
+    if (add.out[0] != M * N) continue;
+    const uint64_t z_ref = g.in[2];
+    uint64_t x_ref;
+    if (add.in[0] == z_ref && add.in[1] != z_ref) x_ref = add.in[1];
+    else if (add.in[1] == z_ref && add.in[0] != z_ref) x_ref = add.in[0];
+    else continue;
+    const uint64_t out_ref = add.in[2];
+    if (RefSpace(x_ref) != kArena || RefSpace(out_ref) != kArena) continue;
+    const uint64_t z_lo = RefOffset(z_ref), z_hi = z_lo + bytes;
+    const uint64_t x_lo = RefOffset(x_ref), x_hi = x_lo + bytes;
+    const uint64_t o_lo = RefOffset(out_ref), o_hi = o_lo + bytes;
+    if (!disjoint(x_lo, x_hi, z_lo, z_hi) || !disjoint(o_lo, o_hi, z_lo, z_hi)) continue;
+    if (o_lo != x_lo && !disjoint(o_lo, o_hi, x_lo, x_hi)) continue;
+    // The product's own operands must not be overwritten by the sum while other
+    // blocks still read them (the addend it accumulates onto may be the sum's place
+    // exactly: each element is read, then written, by the same thread).
+    bool clash = false;
+    const uint64_t srcs[2] = {g.in[0], (g.flags & kFlagGemmAddend) ? g.in[3] : kNullRef};
+    const uint64_t src_bytes[2] = {M * K * 4, bytes};
+    for (int op = 0; op < 2; ++op)
+      if (srcs[op] != kNullRef && RefSpace(srcs[op]) == kArena &&
+          !disjoint(o_lo, o_hi, RefOffset(srcs[op]), RefOffset(srcs[op]) + src_bytes[op]) &&
+          !(op == 1 && RefOffset(srcs[op]) == o_lo))   // exactly over the addend: read, then written, per element
+        clash = true;
+    if (RefSpace(g.in[1]) == kArena && !disjoint(o_lo, o_hi, RefOffset(g.in[1]), RefOffset(g.in[1]) + K * N * 4))
+      clash = true;
+    if (clash) continue;
+    if (!dead_after(i + 1, DeadQuery{z_lo, z_hi, false, ~0ull, 0, 0}, i)) continue;
+    AddFusion af;
+    af.fuse = true;
+    af.x_ref = x_ref;
+    af.out_ref = out_ref;
+    af.add_index = static_cast<uint32_t>(i + 1 - begin);
+    af.z_lo = z_lo; af.z_hi = z_hi;
+    add_fusion_[i - begin] = af;
+  }
   // The same for a LayerNorm backward whose dx is only one term of a sum.
   for (size_t i = begin; i + 1 < end; ++i) {
     const Instruction& ln = program[i];
@@ -1126,8 +1171,19 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
   // outside any range simply runs unsplit.
   a.split_scratch = d_split_;
   a.split_scratch_floats = split_capacity_;
-  k::GemmExact(a, stream_);
+  const AddFusion* tail = !(ins.flags & kFlagRelaxed) && range_index_ < add_fusion_.size() &&
+                                  add_fusion_[range_index_].fuse ? &add_fusion_[range_index_] : nullptr;
+  if (tail) {   // the kAddEW after a rank-r expand product rides its kernel
+    a.tail_addend = Rd(tail->x_ref);
+    a.tail_out = Wr(tail->out_ref);
+  }
+  const bool tail_done = k::GemmExact(a, stream_);
   ++counters_.kernel_launches;
+  if (tail && tail_done) {
+    ++counters_.fused_dispatches;
+    skip_add_at_ = static_cast<int64_t>(tail->add_index);
+    if (tail->z_hi > tail->z_lo) pending_elided_.push_back({tail->z_lo, tail->z_hi});
+  }
   return {};
 }
 

@@ -49,6 +49,10 @@ struct Params {
   // in chunk order.  k_chunk is a multiple of 16, so quads stay aligned to k = 0.
   size_t k_chunk;
   float* partials;
+  // A following kAddEW done by the expand kernel: tail_out = tail_addend + (what C
+  // would have received); C itself is then not written.
+  const float* tail_addend = nullptr;
+  float* tail_out = nullptr;
 };
 
 inline bool Aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }

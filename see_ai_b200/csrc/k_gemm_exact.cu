@@ -358,18 +358,27 @@ size_t SplitKChunks(size_t M, size_t N, size_t K) {
   return (K + rows - 1) / rows;
 }
 
-void GemmExact(const GemmArgs& a, cudaStream_t s) {
-  if (a.M == 0 || a.N == 0) return;
+bool GemmExact(const GemmArgs& a, cudaStream_t s) {
+  if (a.M == 0 || a.N == 0) return false;
   Params p{a.A, a.B, a.C, a.M, a.N, a.K, a.alpha, a.b_col_scale, a.a_k_scale,
            a.bias, a.addend, a.act, a.accumulate, 0, nullptr};
+  // Only the expand kernel takes the tail add; every other path sees none.
+  Params pt = p;
+  if (a.tail_addend && a.tail_out && Aligned16(a.tail_addend) && Aligned16(a.tail_out)) {
+    pt.tail_addend = a.tail_addend;
+    pt.tail_out = a.tail_out;
+  }
   if (a.b_transposed) {
-    if (a.b_type == BType::kF32 && (SkinnyReduce(p, true, s) || SkinnyExpand(p, true, s))) return;
+    if (a.b_type == BType::kF32) {
+      if (SkinnyReduce(p, true, s)) return false;
+      if (SkinnyExpand(pt, true, s)) return pt.tail_out != nullptr;
+    }
     switch (a.b_type) {
       case BType::kF32: LaunchLane<float>(p, s); break;
       case BType::kI8: LaunchLane<int8_t>(p, s); break;
       case BType::kBf16: LaunchLane<uint16_t>(p, s); break;
     }
-    return;
+    return false;
   }
   if (a.a_transposed) {
     // Adapter gradients: a [rank x width] or [width x rank] result reduced over
@@ -383,17 +392,21 @@ void GemmExact(const GemmArgs& a, cudaStream_t s) {
       if (!SkinnyTnPartials(p, chunks, s)) LaunchQuad<true, float>(p, static_cast<unsigned>(chunks), s);
       const size_t blocks = (a.M * a.N + 31) / 32;
       SplitKFoldKernel<<<static_cast<unsigned>(blocks), 32 * kFoldGroups, 0, s>>>(p, chunks);
-      return;
+      return false;
     }
     LaunchQuad<true, float>(p, 1, s);
-    return;
+    return false;
   }
-  if (a.b_type == BType::kF32 && (SkinnyReduce(p, false, s) || SkinnyExpand(p, false, s))) return;
+  if (a.b_type == BType::kF32) {
+    if (SkinnyReduce(p, false, s)) return false;
+    if (SkinnyExpand(pt, false, s)) return pt.tail_out != nullptr;
+  }
   switch (a.b_type) {
     case BType::kF32: LaunchQuad<false, float>(p, 1, s); break;
     case BType::kI8: LaunchQuad<false, int8_t>(p, 1, s); break;
     case BType::kBf16: LaunchQuad<false, uint16_t>(p, 1, s); break;
   }
+  return false;
 }
 
 }  // namespace see::k

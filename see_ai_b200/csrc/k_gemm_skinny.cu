@@ -440,7 +440,7 @@ constexpr int kExpandThreads = 64;
 constexpr int kExpandRows = 32;
 constexpr int kExpandBatch = 4;
 
-template <int K, bool kLane>
+template <int K, bool kLane, bool kTail>
 __global__ void __launch_bounds__(kExpandThreads) ExpandKernel(Params p) {
   __shared__ __align__(16) float As[kExpandRows][K];
   const size_t r0 = static_cast<size_t>(blockIdx.y) * kExpandRows;
@@ -482,6 +482,14 @@ __global__ void __launch_bounds__(kExpandThreads) ExpandKernel(Params p) {
       d[u] = (p.addend && mb + u < rows)
                  ? *reinterpret_cast<const float4*>(p.addend + (r0 + mb + u) * p.N + n)
                  : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 tail[kTail ? kExpandBatch : 1];   // the absorbed add's other operand, fetched with the addend
+    if (kTail) {
+#pragma unroll
+      for (int u = 0; u < kExpandBatch; ++u)
+        tail[kTail ? u : 0] = mb + u < rows
+                                  ? *reinterpret_cast<const float4*>(p.tail_addend + (r0 + mb + u) * p.N + n)
+                                  : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
 #pragma unroll
     for (int u = 0; u < kExpandBatch; ++u) {
       if (mb + u >= rows) break;
@@ -536,7 +544,13 @@ __global__ void __launch_bounds__(kExpandThreads) ExpandKernel(Params p) {
           v[j] = ApplyAct(v[j], p.act);
         }
       }
-      *reinterpret_cast<float4*>(p.C + (r0 + mb + u) * p.N + n) = make_float4(v[0], v[1], v[2], v[3]);
+      const size_t at = (r0 + mb + u) * p.N + n;
+      if (kTail) {   // the kAddEW that follows, done here (tail_out may alias tail_addend or the addend)
+        const float4 t = tail[kTail ? u : 0];
+        *reinterpret_cast<float4*>(p.tail_out + at) = make_float4(t.x + v[0], t.y + v[1], t.z + v[2], t.w + v[3]);
+      } else {
+        *reinterpret_cast<float4*>(p.C + at) = make_float4(v[0], v[1], v[2], v[3]);
+      }
     }
   }
 }
@@ -545,8 +559,13 @@ template <int K>
 void LaunchExpand(const Params& p, bool lane_order, cudaStream_t s) {
   const dim3 grid(static_cast<unsigned>((p.N / 4 + kExpandThreads - 1) / kExpandThreads),
                   static_cast<unsigned>((p.M + kExpandRows - 1) / kExpandRows));
-  if (lane_order) ExpandKernel<K, true><<<grid, kExpandThreads, 0, s>>>(p);
-  else ExpandKernel<K, false><<<grid, kExpandThreads, 0, s>>>(p);
+  if (p.tail_out) {
+    if (lane_order) ExpandKernel<K, true, true><<<grid, kExpandThreads, 0, s>>>(p);
+    else ExpandKernel<K, false, true><<<grid, kExpandThreads, 0, s>>>(p);
+  } else {
+    if (lane_order) ExpandKernel<K, true, false><<<grid, kExpandThreads, 0, s>>>(p);
+    else ExpandKernel<K, false, false><<<grid, kExpandThreads, 0, s>>>(p);
+  }
 }
 
 }  // namespace

@@ -214,6 +214,11 @@ struct GemmArgs {
   const float* fuse_shadow_scale = nullptr;
   bool store_c = true;
   bool addend_after_bias = false;   // tensor-core path: v = addend + (product + bias)
+  // Exact path, rank-r expand kernel only: a following kAddEW rides along
+  // (tail_out = tail_addend + result; C is not written).  GemmExact returns whether
+  // it did.
+  const float* tail_addend = nullptr;
+  float* tail_out = nullptr;
   // Scratch for the split-K form of the transposed-A product (optional).
   float* split_scratch = nullptr;
   size_t split_scratch_floats = 0;
@@ -228,7 +233,7 @@ size_t SplitKChunkRows(size_t M, size_t N, size_t K);
 size_t SplitKChunks(size_t M, size_t N, size_t K);
 // The reference's reduction orders on CUDA cores, without fused multiply-adds:
 // bit-identical to the CPU executor for f32 / int8 / bf16 weights.
-void GemmExact(const GemmArgs& a, cudaStream_t s);
+bool GemmExact(const GemmArgs& a, cudaStream_t s);
 
 }  // namespace see::k
 

@@ -287,3 +287,26 @@ def test_add_after_layernorm_backward_rides_the_kernel(dx_first, in_place):
     assert np.isfinite(fused.view(np.float32)).all()
     assert np.array_equal(fused, split)
     assert c_split.kernel_launches - c_fused.kernel_launches == 1 and c_fused.fused_dispatches == 1
+
+
+@pytest.mark.parametrize("order", ["nn", "nt"])
+@pytest.mark.parametrize("over_addend", [False, True], ids=["new", "over-addend"])
+def test_add_after_an_adapter_expand_product_rides_the_kernel(order, over_addend):
+    M, N, r = 512, 256, 16
+    rng = np.random.default_rng(43)
+    a = Arena(rng)
+    t = a.alloc(M * r, "normal"); w = a.alloc(r * N, "normal")     # [r][N] (nn) or [N][r] (nt)
+    y = a.alloc(M * N, "normal"); res = a.alloc(M * N, "normal")
+    z = a.alloc(M * N); out = y if over_addend else a.alloc(M * N)
+    op = Op.GEMM_NN if order == "nn" else Op.GEMM_NT
+    prog = [
+        P.Instr(op, P.FLAG_GEMM_ADDEND, P.f32_bits(2.0), (t, w, z, y), (M, N, r)),
+        P.Instr(Op.ADD_EW, 0, 0, (res, z, out, P.NULL_REF), (M * N, 0, 0)),
+        P.Instr(Op.FILL, 0, 0, (z, P.f32_bits(0.0)), (M * N, 0, 0)),
+    ]
+    arena0, ro = a.build()
+    fused, c_fused = _run(prog, arena0, ro, one_range=True)
+    split, c_split = _run(prog, arena0, ro, one_range=False)
+    assert np.isfinite(fused.view(np.float32)).all()
+    assert np.array_equal(fused, split)
+    assert c_split.kernel_launches - c_fused.kernel_launches == 1 and c_fused.fused_dispatches == 1
