@@ -226,12 +226,18 @@ def run_cuda(args):
         c0 = eng.backend.counters()
         step(False, 0)
         loss0 = eng.read_loss()
-        prof = eng.backend.take_profile()
+        prof8 = eng.backend.take_profile(with_absorbed=True)
+        prof = [r[:7] for r in prof8]
         eng.backend.set_profiling(False)
         launches_per_step = eng.backend.counters().kernel_launches - c0.kernel_launches
         gemm_flops = sum(2.0 * m * n * k for (_op, _i, _ms, m, n, k, kms) in prof if kms > 0)
         gemm_ms = sum(kms for (*_r, kms) in prof if kms > 0)
         gemm_launches = sum(1 for (*_r, kms) in prof if kms > 0)
+        # The same over the launches whose epilogue carries no absorbed instruction
+        # (an absorbed GELU or add is HBM work the FLOP count does not see).
+        plain = [(m, n, k, kms) for (_op, _i, _ms, m, n, k, kms, absorbed) in prof8 if kms > 0 and absorbed == 0]
+        plain_flops = sum(2.0 * m * n * k for (m, n, k, _t) in plain)
+        plain_ms = sum(t for (*_s, t) in plain)
         by_op = {}
         for (op, _i, ms, *_rest) in prof:
             by_op[P.OP_NAMES.get(op, str(op))] = by_op.get(P.OP_NAMES.get(op, str(op)), 0.0) + ms
@@ -281,6 +287,7 @@ def run_cuda(args):
     value = tokens * args.steps / (ms_resident * 1e-3)
     e2e = tokens * args.steps / (ms_e2e * 1e-3)
     achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    plain_achieved = plain_flops / (plain_ms * 1e-3) / 1e12 if plain_ms > 0 else 0.0
     peak = pk["bf16_tflops_sustained"]
     h2d = 2 * rows * 4
     line = {
@@ -301,7 +308,14 @@ def run_cuda(args):
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the most frequent
                      # shape (ncu capture summarised under profiles/); a constant, not measured here.
                      "traffic": NCU_TRAFFIC_BYTES, "traffic_note": NCU_TRAFFIC_NOTE,
-                     "launches_per_step": gemm_launches, "kernel_ms_per_step": gemm_ms},
+                     "launches_per_step": gemm_launches, "kernel_ms_per_step": gemm_ms,
+                     # The headline figure counts every launch, including those whose epilogue
+                     # also does a following GELU / GELU backward / add (extra HBM traffic and
+                     # instructions, no extra FLOPs).  `plain` is the same ratio over the
+                     # launches that carry nothing else.
+                     "plain": {"launches_per_step": len(plain), "kernel_ms_per_step": plain_ms,
+                               "achieved": plain_achieved,
+                               "frac": plain_achieved / peak if peak and plain_achieved else None}},
         "profile_ms_per_step": {k: round(v, 3) for k, v in sorted(by_op.items(), key=lambda kv: -kv[1])},
         "profiled_step_ms": profiled_ms,
         "loss": {"first": loss0, "last": final_loss},

@@ -103,7 +103,9 @@ int see_cuda_set_gradient_gather(see_cuda_backend* h, int ranks, const void* gat
  * reference: runtime/profiler/kernel_profile.h:25-72).  take_profile fills up
  * to `capacity` records and returns the count. */
 typedef struct see_profile_record {
-  uint16_t opcode; uint16_t pad; uint32_t index;
+  uint16_t opcode;
+  uint16_t absorbed; /* following instructions this one also did (epilogue fusion) */
+  uint32_t index;
   float ms;        /* the whole instruction */
   float kernel_ms; /* the tensor-core GEMM kernel alone, 0 when the instruction did not use it */
   uint64_t m, n, k;

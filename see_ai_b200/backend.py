@@ -48,7 +48,7 @@ class Counters(ctypes.Structure):
 
 
 class ProfileRecord(ctypes.Structure):
-    _fields_ = [("opcode", ctypes.c_uint16), ("pad", ctypes.c_uint16), ("index", ctypes.c_uint32),
+    _fields_ = [("opcode", ctypes.c_uint16), ("absorbed", ctypes.c_uint16), ("index", ctypes.c_uint32),
                 ("ms", ctypes.c_float), ("kernel_ms", ctypes.c_float), ("m", ctypes.c_uint64),
                 ("n", ctypes.c_uint64), ("k", ctypes.c_uint64)]
 
@@ -248,7 +248,12 @@ class CudaBackend:
     def set_profiling(self, on: bool):
         self._check(self.lib.see_cuda_set_profiling(self.h, int(on)))
 
-    def take_profile(self, capacity: int = 65536):
+    def take_profile(self, capacity: int = 65536, with_absorbed: bool = False):
+        """(opcode, index, ms, m, n, k, kernel_ms) per executed instruction; with
+        `with_absorbed` an eighth field: how many following instructions the
+        instruction also did (epilogue fusion)."""
         arr = (ProfileRecord * capacity)()
         n = self.lib.see_cuda_take_profile(self.h, arr, capacity)
+        if with_absorbed:
+            return [(r.opcode, r.index, r.ms, r.m, r.n, r.k, r.kernel_ms, r.absorbed) for r in arr[:n]]
         return [(r.opcode, r.index, r.ms, r.m, r.n, r.k, r.kernel_ms) for r in arr[:n]]

@@ -199,7 +199,7 @@ int64_t see_cuda_take_profile(see_cuda_backend* h, see_profile_record* out, uint
   uint64_t n = 0;
   for (const auto& r : recs) {
     if (n >= capacity) break;
-    out[n] = see_profile_record{r.opcode, 0, r.index, r.ms, r.kernel_ms, r.m, r.n, r.k};
+    out[n] = see_profile_record{r.opcode, r.absorbed, r.index, r.ms, r.kernel_ms, r.m, r.n, r.k};
     ++n;
   }
   return static_cast<int64_t>(n);

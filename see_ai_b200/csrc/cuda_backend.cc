@@ -1031,6 +1031,7 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
     }
   }
 
+  const uint64_t fused_before = counters_.fused_dispatches;
   if (!absorbed)
     if (auto r = Dispatch(ins, params, ext); !r) return r;
   ++counters_.instructions;
@@ -1039,6 +1040,7 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
     cudaEventRecord(ev1, stream_);
     ProfileRecord rec{ins.opcode, range_index_, 0.0f, 0, 0, 0};
     rec.has_kernel = umma::ProfileEventsUsed(&umma_->ctx);
+    rec.absorbed = static_cast<uint16_t>(counters_.fused_dispatches - fused_before);
     if (ins.opcode <= kGemmAccNN || ins.opcode == kGemmNNQ8 || ins.opcode == kGemmNTQ8 ||
         ins.opcode == kGemmNNBF16 || ins.opcode == kGemmNTBF16) {
       rec.m = ins.out[0]; rec.n = ins.out[1]; rec.k = ins.out[2];

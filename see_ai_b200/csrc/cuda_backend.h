@@ -59,7 +59,10 @@ struct Counters {
 // One timed instruction (profile mode): opcode, index in the range, milliseconds.
 // kernel_ms > 0 only for instructions that ran on the tensor-core GEMM: the
 // kernel alone, without the operand conversions that ms also covers.
-struct ProfileRecord { uint16_t opcode; uint32_t index; float ms; uint64_t m, n, k; float kernel_ms = 0.0f; bool has_kernel = false; };
+struct ProfileRecord {
+  uint16_t opcode; uint32_t index; float ms; uint64_t m, n, k; float kernel_ms = 0.0f; bool has_kernel = false;
+  uint16_t absorbed = 0;   // following instructions this one also did
+};
 
 class CudaBackend {
  public:
