@@ -993,8 +993,10 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   const bool absorbed = skip_act_at_ == static_cast<int64_t>(range_index_);
   if (absorbed) skip_act_at_ = -1;
   // (A kAddBias done by the preceding product's epilogue reads nothing either.)
-  const bool bias_done = (skip_next_add_bias_ && ins.opcode == kAddBias) ||
-                         skip_add_at_ == static_cast<int64_t>(range_index_);
+  // (A kAddEW done by the kernel before it: that kernel's dispatch has already
+  // dropped older copies of the sum's range and may have published the new one.)
+  const bool add_done = skip_add_at_ == static_cast<int64_t>(range_index_);
+  const bool bias_done = (skip_next_add_bias_ && ins.opcode == kAddBias) || add_done;
   if (!elided_.empty() && !absorbed && !bias_done) {
     for (size_t i = 0; i < ext.count; ++i) {
       const Extent& e = ext.e[i];
@@ -1052,7 +1054,7 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   for (size_t i = 0; i < ext.count && !absorbed; ++i) {
     const Extent& e = ext.e[i];
     if (!e.write) continue;
-    umma::InvalidateRange(&umma_->ctx, e.off, e.bytes);
+    if (!add_done) umma::InvalidateRange(&umma_->ctx, e.off, e.bytes);
     if (coherence_ == Coherence::kStrict) MergeExtent(&device_dirty_, e.off, e.bytes);
     if (!elided_.empty() && e.space == kArena) {   // written for real: no longer stale
       std::vector<std::pair<uint64_t, uint64_t>> rest;
@@ -1141,6 +1143,7 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
       if (adf) {
         ++counters_.fused_dispatches;
         skip_add_at_ = static_cast<int64_t>(adf->add_index);
+        umma::InvalidateRange(&umma_->ctx, RefOffset(adf->out_ref), a.M * a.N * 4);
         if (adf->z_hi > adf->z_lo) pending_elided_.push_back({adf->z_lo, adf->z_hi});
       }
       if (af) {
@@ -1184,6 +1187,7 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
   if (tail && tail_done) {
     ++counters_.fused_dispatches;
     skip_add_at_ = static_cast<int64_t>(tail->add_index);
+    umma::InvalidateRange(&umma_->ctx, RefOffset(tail->out_ref), a.M * a.N * 4);
     if (tail->z_hi > tail->z_lo) pending_elided_.push_back({tail->z_lo, tail->z_hi});
   }
   return {};
@@ -1363,6 +1367,8 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
       launched();
       if (fused) {   // the kAddEW after it has been done
         shadow_written_ = fused == 2;
+        umma::InvalidateRange(&umma_->ctx, RefOffset(adf->out_ref),
+                              static_cast<uint64_t>(Hi32(ins.out[2])) * Lo32(ins.out[2]) * 4);
         ++counters_.fused_dispatches;
         skip_add_at_ = static_cast<int64_t>(adf->add_index);
         if (adf->z_hi > adf->z_lo) pending_elided_.push_back({adf->z_lo, adf->z_hi});

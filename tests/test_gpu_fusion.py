@@ -310,3 +310,28 @@ def test_add_after_an_adapter_expand_product_rides_the_kernel(order, over_addend
     assert np.isfinite(fused.view(np.float32)).all()
     assert np.array_equal(fused, split)
     assert c_split.kernel_launches - c_fused.kernel_launches == 1 and c_fused.fused_dispatches == 1
+
+
+def test_layernorm_backward_sum_hands_its_copy_to_the_gemm_that_reads_it():
+    M, D, N = 512, 256, 128
+    rng = np.random.default_rng(47)
+    a = Arena(rng)
+    x = a.alloc(M * D, "normal"); gamma = a.alloc(D, "normal"); beta = a.alloc(D, "normal")
+    y = a.alloc(M * D); mean = a.alloc(M); rstd = a.alloc(M)
+    dy = a.alloc(M * D, "normal"); res = a.alloc(M * D, "normal")
+    dx = a.alloc(M * D); total = a.alloc(M * D); out = a.alloc(M * N)
+    w = a.ro_alloc(rng.integers(-127, 128, size=N * D, dtype=np.int8))
+    sck = a.ro_alloc((2.0 ** rng.integers(-9, -5, size=D)).astype(np.float32))
+    prog = [
+        P.Instr(Op.LAYERNORM_FWD, 0, P.f32_bits(1e-5), (x, gamma, beta, y), (P.pack2(M, D), mean, rstd)),
+        P.Instr(Op.LAYERNORM_BWD, 0, 0, (dy, x, gamma, dx), (mean, rstd, P.pack2(M, D))),
+        P.Instr(Op.ADD_EW, 0, 0, (res, dx, total, P.NULL_REF), (M * D, 0, 0)),
+        P.Instr(Op.GEMM_NT_Q8, REL | CS, 0, (total, w, out, sck), (M, N, D)),
+        P.Instr(Op.FILL, 0, 0, (dx, P.f32_bits(0.0)), (M * D, 0, 0)),
+    ]
+    arena0, ro = a.build()
+    fused, c_fused = _run(prog, arena0, ro, one_range=True)
+    split, c_split = _run(prog, arena0, ro, one_range=False)
+    assert np.array_equal(fused, split)
+    # The add kernel and the GEMM's own conversion pass are both gone.
+    assert c_split.kernel_launches - c_fused.kernel_launches == 2 and c_fused.fused_dispatches == 1
