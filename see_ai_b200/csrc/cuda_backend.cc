@@ -494,10 +494,6 @@ void CudaBackend::PlanShadows(std::span<const Instruction> program, size_t begin
     want.a_off = RefOffset(g.in[0]);
     want.M = M;
     want.K = K;
-    if (op == kGemmNTQ8 && (g.flags & kFlagQ8ColScale)) {
-      want.scale_ref = g.in[3];
-      want.scale_off = RefOffset(g.in[3]);
-    }
     const uint64_t bytes = M * K * 4;
     for (size_t i = j; i-- > begin;) {
       const Extents& e = ext[i - begin];
@@ -597,7 +593,8 @@ bool IsRelaxedFrozenGemm(const Instruction& g) {
 }
 
 uint64_t GemmScaleKey(const Instruction& g) {
-  return g.opcode == kGemmNTQ8 && (g.flags & kFlagQ8ColScale) ? RefOffset(g.in[3]) : ~0ull;
+  (void)g;   // the per-k factor of a transposed int8 product lives in its weight copy, not in the operand copy
+  return ~0ull;
 }
 
 }  // namespace
@@ -1010,8 +1007,7 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
                           (ins.opcode == kGemmNN || ins.opcode == kGemmNT || ins.opcode == kGemmNNQ8 ||
                            ins.opcode == kGemmNTQ8 || ins.opcode == kGemmNNBF16 || ins.opcode == kGemmNTBF16) &&
                           umma::TouchActCopy(&umma_->ctx, e.off,
-                                             ins.opcode == kGemmNTQ8 && (ins.flags & kFlagQ8ColScale)
-                                                 ? RefOffset(ins.in[3]) : ~0ull,
+                                             ~0ull,
                                              ins.out[0], ins.out[2]);
       if (!gemm_a)
         return std::unexpected(std::string("cuda: ") + OpName(ins.opcode) +
@@ -1023,7 +1019,7 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
     if (range_index_ < act_fusion_.size() && act_fusion_[range_index_].mode != 0)
       // The product reads one copy and writes another: keep its operand's slot.
       umma::TouchActCopy(&umma_->ctx, RefOffset(ins.in[0]),
-                         ins.opcode == kGemmNTQ8 && (ins.flags & kFlagQ8ColScale) ? RefOffset(ins.in[3]) : ~0ull,
+                         ~0ull,
                          ins.out[0], ins.out[2]);
     if (uint16_t* buf = umma::ReserveShadow(&umma_->ctx, cur_plan_.M * cur_plan_.K)) {
       cur_shadow_.dst = buf;

@@ -588,22 +588,34 @@ template <> __device__ __forceinline__ uint16_t ToBf16Bits<float>(float f) {
   return static_cast<uint16_t>(b >> 16);
 }
 
+template <typename T> __device__ __forceinline__ float WidenWeight(T v);
+template <> __device__ __forceinline__ float WidenWeight<int8_t>(int8_t v) { return static_cast<float>(v); }
+template <> __device__ __forceinline__ float WidenWeight<uint16_t>(uint16_t v) {
+  return __uint_as_float(static_cast<uint32_t>(v) << 16);
+}
+template <> __device__ __forceinline__ float WidenWeight<float>(float v) { return v; }
+template <typename T>
+__device__ __forceinline__ uint16_t WeightBits(T v, const float* k_scale, uint32_t k) {
+  return k_scale ? ToBf16Bits<float>(WidenWeight<T>(v) * k_scale[k]) : ToBf16Bits<T>(v);
+}
+
 template <typename T>
 __global__ void WeightToBf16Kernel(const T* __restrict__ src, uint16_t* __restrict__ dst, uint32_t N,
-                                   uint32_t K, bool transpose) {
+                                   uint32_t K, bool transpose, const float* __restrict__ k_scale) {
   __shared__ uint16_t tile[32][33];
   const uint32_t bx = blockIdx.x * 32, by = blockIdx.y * 32;
   if (!transpose) {  // src [N][K] -> dst [N][K]
     for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
       const uint32_t n = by + i, k = bx + threadIdx.x;
-      if (n < N && k < K) dst[static_cast<size_t>(n) * K + k] = ToBf16Bits<T>(src[static_cast<size_t>(n) * K + k]);
+      if (n < N && k < K)
+        dst[static_cast<size_t>(n) * K + k] = WeightBits<T>(src[static_cast<size_t>(n) * K + k], k_scale, k);
     }
     return;
   }
   // src [K][N]: bx indexes n, by indexes k
   for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
     const uint32_t k = by + i, n = bx + threadIdx.x;
-    if (k < K && n < N) tile[i][threadIdx.x] = ToBf16Bits<T>(src[static_cast<size_t>(k) * N + n]);
+    if (k < K && n < N) tile[i][threadIdx.x] = WeightBits<T>(src[static_cast<size_t>(k) * N + n], k_scale, k);
   }
   __syncthreads();
   for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
@@ -652,18 +664,18 @@ cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
 }
 
 void WeightToBf16(const void* src, BType type, uint16_t* dst, uint32_t N, uint32_t K,
-                  bool transpose, cudaStream_t s) {
+                  bool transpose, const float* k_scale, cudaStream_t s) {
   dim3 block(32, 8);
   dim3 grid = transpose ? dim3((N + 31) / 32, (K + 31) / 32) : dim3((K + 31) / 32, (N + 31) / 32);
   switch (type) {
     case BType::kI8:
-      WeightToBf16Kernel<int8_t><<<grid, block, 0, s>>>(static_cast<const int8_t*>(src), dst, N, K, transpose);
+      WeightToBf16Kernel<int8_t><<<grid, block, 0, s>>>(static_cast<const int8_t*>(src), dst, N, K, transpose, k_scale);
       break;
     case BType::kBf16:
-      WeightToBf16Kernel<uint16_t><<<grid, block, 0, s>>>(static_cast<const uint16_t*>(src), dst, N, K, transpose);
+      WeightToBf16Kernel<uint16_t><<<grid, block, 0, s>>>(static_cast<const uint16_t*>(src), dst, N, K, transpose, k_scale);
       break;
     case BType::kF32:
-      WeightToBf16Kernel<float><<<grid, block, 0, s>>>(static_cast<const float*>(src), dst, N, K, transpose);
+      WeightToBf16Kernel<float><<<grid, block, 0, s>>>(static_cast<const float*>(src), dst, N, K, transpose, k_scale);
       break;
   }
 }

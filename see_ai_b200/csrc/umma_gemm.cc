@@ -23,8 +23,9 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // A cached K-major bf16 copy of a frozen weight: key = (space, byte offset,
-// N, K, transposed source, element type).
-using WeightKey = std::tuple<int, uint64_t, uint64_t, uint64_t, bool, int>;
+// N, K, transposed source, element type, byte offset of the per-k factor
+// folded into it or ~0).
+using WeightKey = std::tuple<int, uint64_t, uint64_t, uint64_t, bool, int, uint64_t>;
 
 struct ActCopy {   // a bf16 copy of an arena activation [M, K]
   uint64_t a_off = ~0ull, scale_off = ~0ull, M = 0, K = 0;
@@ -219,7 +220,12 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
     return {};   // the epilogue moves float4s
 
   // ---- the weight, K-major bf16 [N][K], converted once per binding ----
-  const WeightKey key{b_space, b_off, a.N, a.K, !a.b_transposed, static_cast<int>(a.b_type)};
+  // A transposed int8 product's per-k factor (C = (A s_k) W^T) is folded into the
+  // weight copy, w[n][k] = bf16(W[n][k] * s[k]), once per binding: the activation
+  // copy is then plain bf16(A), which every producer can write without a table
+  // look-up per element, and which any other consumer of the tensor can share.
+  const WeightKey key{b_space, b_off, a.N, a.K, !a.b_transposed, static_cast<int>(a.b_type),
+                      a.a_k_scale ? a_scale_off : ~0ull};
   uint16_t* w = nullptr;
   if (auto it = impl->weights.find(key); it != impl->weights.end()) {
     w = it->second;
@@ -228,7 +234,7 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
     if (cudaMalloc(&p, a.N * a.K * 2) != cudaSuccess) return "tensor-core path: weight copy allocation failed";
     w = static_cast<uint16_t*>(p);
     k::WeightToBf16(a.B, a.b_type, w, static_cast<uint32_t>(a.N), static_cast<uint32_t>(a.K),
-                    /*transpose=*/!a.b_transposed, stream);
+                    /*transpose=*/!a.b_transposed, a.a_k_scale, stream);
     ++*launches;
     impl->weights.emplace(key, w);
   }
@@ -236,7 +242,7 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
   // ---- the activation, bf16 [M][K], reused while its arena range is unwritten ----
   ActCopy* slot = nullptr;
   for (auto& c : impl->acts)
-    if (c.valid && c.a_off == a_off && c.scale_off == a_scale_off && c.M == a.M && c.K == a.K)
+    if (c.valid && c.a_off == a_off && c.scale_off == ~0ull && c.M == a.M && c.K == a.K)
       slot = &c;
   if (!slot) {
     // A slot a producer is writing (this product's own epilogue, when it has
@@ -259,9 +265,9 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
       slot->buf = static_cast<uint16_t*>(p);
       slot->capacity = need;
     }
-    k::ToBf16(a.A, slot->buf, a.M, a.K, a.a_k_scale, stream);
+    k::ToBf16(a.A, slot->buf, a.M, a.K, nullptr, stream);
     ++*launches;
-    slot->a_off = a_off; slot->scale_off = a_scale_off; slot->M = a.M; slot->K = a.K;
+    slot->a_off = a_off; slot->scale_off = ~0ull; slot->M = a.M; slot->K = a.K;
     slot->valid = true;
   }
   slot->last_use = ++impl->tick;
