@@ -132,15 +132,17 @@ __device__ __forceinline__ float ApplyAct(float v, int act) { return ActFwdExpr(
 __device__ __forceinline__ void EpilogueStore(const UmmaEpilogue& ep, size_t at, uint32_t n, const float4& acc,
                                               const float4& scale, const float4& bias,
                                               bool has_kscale = false,
-                                              float4 kscale = make_float4(1.f, 1.f, 1.f, 1.f)) {
+                                              float4 kscale = make_float4(1.f, 1.f, 1.f, 1.f),
+                                              bool has_side = false,   // the addend / x element, already loaded
+                                              float4 side = make_float4(0.f, 0.f, 0.f, 0.f)) {
   float4 v = make_float4(acc.x * scale.x, acc.y * scale.y, acc.z * scale.z, acc.w * scale.w);
   if (ep.addend && !ep.addend_last) {
-    const float4 d = __ldg(reinterpret_cast<const float4*>(ep.addend + at));
+    const float4 d = has_side ? side : __ldg(reinterpret_cast<const float4*>(ep.addend + at));
     v = make_float4(d.x + v.x, d.y + v.y, d.z + v.z, d.w + v.w);
   }
   if (ep.bias) v = make_float4(v.x + bias.x, v.y + bias.y, v.z + bias.z, v.w + bias.w);
   if (ep.addend && ep.addend_last) {   // an absorbed kAddEW that followed the kAddBias
-    const float4 d = __ldg(reinterpret_cast<const float4*>(ep.addend + at));
+    const float4 d = has_side ? side : __ldg(reinterpret_cast<const float4*>(ep.addend + at));
     v = make_float4(d.x + v.x, d.y + v.y, d.z + v.z, d.w + v.w);
   }
   if (ep.act != kActNone)
@@ -153,7 +155,7 @@ __device__ __forceinline__ void EpilogueStore(const UmmaEpilogue& ep, size_t at,
       g = make_float4(ActFwdExpr(ep.fuse_act, v.x), ActFwdExpr(ep.fuse_act, v.y), ActFwdExpr(ep.fuse_act, v.z),
                       ActFwdExpr(ep.fuse_act, v.w));
     } else {
-      const float4 x = __ldg(reinterpret_cast<const float4*>(ep.fuse_x + at));
+      const float4 x = has_side ? side : __ldg(reinterpret_cast<const float4*>(ep.fuse_x + at));
       g = make_float4(ActBwdExpr(ep.fuse_act, v.x, x.x), ActBwdExpr(ep.fuse_act, v.y, x.y),
                       ActBwdExpr(ep.fuse_act, v.z, x.z), ActBwdExpr(ep.fuse_act, v.w, x.w));
     }
@@ -363,6 +365,12 @@ struct __align__(8) PBarriers {
   volatile uint32_t abort;
 };
 
+// kSideLoads: the epilogue reads a second [M, N] f32 operand beside every output
+// (an addend).  Those loads are then software-pipelined: the four of the NEXT group of rows are in flight
+// while this group is converted and stored, across passes and from before the
+// wait for the accumulator, so a memory round trip is not paid per group with
+// every warp of the CTA waiting on it.
+template <bool kSideLoads>
 __global__ void __launch_bounds__(kPThreads, 1)
 UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
                          const __grid_constant__ CUtensorMap map_b, UmmaEpilogue ep,
@@ -511,55 +519,127 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
         if (lt == 0) prefetch_x(t);
         if (t + gridDim.x < total_tiles) prefetch_x(t + gridDim.x);
       }
+      const uint32_t row0 = m0 + quarter * 32;
+      const uint32_t rows = row0 < ep.M ? (ep.M - row0 < 32 ? ep.M - row0 : 32) : 0;
+      [[maybe_unused]] const float* side_ptr = ep.fuse_mode == kFuseActBwd ? ep.fuse_x : ep.addend;
+      [[maybe_unused]] float4 side_a[4], side_b[4];
+      if constexpr (kSideLoads) {   // the first group's loads fly during the wait for the accumulator
+        const uint32_t n_g = n0 + col_group * kColsPerEpiWarp + cl * 4;
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u) {
+          const uint32_t rr = sub + u * kRowsPerInstr;
+          side_a[u] = rr < rows && n_g < ep.N
+                          ? __ldg(reinterpret_cast<const float4*>(side_ptr + static_cast<size_t>(row0 + rr) * ep.N + n_g))
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
       bool ok = MbarWait(&bars->tmem_full[buf], use & 1);
       if (!ok && lane == 0) { ep.status->wait_timeout = 1; bars->abort = 1; }
       if (bars->abort) ok = false;
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t row0 = m0 + quarter * 32;
-      const uint32_t rows = row0 < ep.M ? (ep.M - row0 < 32 ? ep.M - row0 : 32) : 0;
       // 32 columns at a time through the slab.  A thread writes its accumulator
       // row as eight 16-byte chunks, chunk index XOR-ed with the row; the warp
       // then reads four rows per instruction (eight lanes each): whole 128-byte
       // lines of C per store instruction.  Conflict-free both ways.
       const uint32_t t_row = tmem_base + ((quarter * 32) << 16) + buf * kPBlockN + col_group * kColsPerEpiWarp;
-#pragma unroll 1
-      for (uint32_t pass = 0; pass < kEpiPasses; ++pass) {
-        uint32_t ra[32];
-        TmemLoad32(t_row + pass * kSlabCols, ra);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (pass == kEpiPasses - 1) {
-          // The accumulator buffer is read out: hand it back before the slow part.
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          __syncwarp();
-          if (lane == 0)
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];"
-                         ::"r"(SmemAddr(&bars->tmem_empty[buf])) : "memory");
-        }
-#pragma unroll
-        for (uint32_t q = 0; q < kChunks; ++q)
-          *reinterpret_cast<uint4*>(slab + lane * kSlabCols + ((q ^ (lane & (kChunks - 1))) * 4)) =
-              make_uint4(ra[4 * q], ra[4 * q + 1], ra[4 * q + 2], ra[4 * q + 3]);
-        __syncwarp();
-        const uint32_t n = n0 + col_group * kColsPerEpiWarp + pass * kSlabCols + cl * 4;
-        if (n < ep.N) {   // N % 4 == 0: a float4 is all in or all out
-          float4 scale = make_float4(ep.alpha, ep.alpha, ep.alpha, ep.alpha);
-          if (ep.col_scale) scale = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n));
-          float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (ep.bias) bias = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
-          float4 kscale = make_float4(1.f, 1.f, 1.f, 1.f);   // the consumer's per-column factor (x * 1 == x)
-          if (ep.fuse_mode != kFuseNone && ep.shadow_k_scale)
-            kscale = __ldg(reinterpret_cast<const float4*>(ep.shadow_k_scale + n));
-#pragma unroll 4
-          for (uint32_t rr = sub; rr < rows; rr += kRowsPerInstr) {
-            const float4 acc = *reinterpret_cast<const float4*>(
-                slab + rr * kSlabCols + ((cl ^ (rr & (kChunks - 1))) * 4));
-            const size_t at = static_cast<size_t>(row0 + rr) * ep.N + n;
-            EpilogueStore(ep, at, n, acc, scale, bias, true, kscale);
+      if constexpr (!kSideLoads) {
+  #pragma unroll 1
+        for (uint32_t pass = 0; pass < kEpiPasses; ++pass) {
+          uint32_t ra[32];
+          TmemLoad32(t_row + pass * kSlabCols, ra);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (pass == kEpiPasses - 1) {
+            // The accumulator buffer is read out: hand it back before the slow part.
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0)
+              asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];"
+                           ::"r"(SmemAddr(&bars->tmem_empty[buf])) : "memory");
           }
+  #pragma unroll
+          for (uint32_t q = 0; q < kChunks; ++q)
+            *reinterpret_cast<uint4*>(slab + lane * kSlabCols + ((q ^ (lane & (kChunks - 1))) * 4)) =
+                make_uint4(ra[4 * q], ra[4 * q + 1], ra[4 * q + 2], ra[4 * q + 3]);
+          __syncwarp();
+          const uint32_t n = n0 + col_group * kColsPerEpiWarp + pass * kSlabCols + cl * 4;
+          if (n < ep.N) {   // N % 4 == 0: a float4 is all in or all out
+            float4 scale = make_float4(ep.alpha, ep.alpha, ep.alpha, ep.alpha);
+            if (ep.col_scale) scale = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n));
+            float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (ep.bias) bias = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
+            float4 kscale = make_float4(1.f, 1.f, 1.f, 1.f);   // the consumer's per-column factor (x * 1 == x)
+            if (ep.fuse_mode != kFuseNone && ep.shadow_k_scale)
+              kscale = __ldg(reinterpret_cast<const float4*>(ep.shadow_k_scale + n));
+  #pragma unroll 4
+            for (uint32_t rr = sub; rr < rows; rr += kRowsPerInstr) {
+              const float4 acc = *reinterpret_cast<const float4*>(
+                  slab + rr * kSlabCols + ((cl ^ (rr & (kChunks - 1))) * 4));
+              const size_t at = static_cast<size_t>(row0 + rr) * ep.N + n;
+              EpilogueStore(ep, at, n, acc, scale, bias, true, kscale);
+            }
+          }
+          __syncwarp();   // the slab is rewritten next
         }
-        __syncwarp();   // the slab is rewritten next
+      } else {
+        // Groups of four row steps (two per pass); group g + 1's side operands are
+        // loaded while group g is converted and stored.
+        auto load_group = [&](float4 (&dst)[4], uint32_t grp) {
+          const uint32_t n_g = n0 + col_group * kColsPerEpiWarp + (grp >> 1) * kSlabCols + cl * 4;
+#pragma unroll
+          for (uint32_t u = 0; u < 4; ++u) {
+            const uint32_t rr = sub + ((grp & 1) * 4 + u) * kRowsPerInstr;
+            dst[u] = rr < rows && n_g < ep.N
+                         ? __ldg(reinterpret_cast<const float4*>(side_ptr + static_cast<size_t>(row0 + rr) * ep.N + n_g))
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        };
+#pragma unroll
+        for (uint32_t pass = 0; pass < kEpiPasses; ++pass) {
+          uint32_t ra[32];
+          TmemLoad32(t_row + pass * kSlabCols, ra);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (pass == kEpiPasses - 1) {
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0)
+              asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];"
+                           ::"r"(SmemAddr(&bars->tmem_empty[buf])) : "memory");
+          }
+#pragma unroll
+          for (uint32_t q = 0; q < kChunks; ++q)
+            *reinterpret_cast<uint4*>(slab + lane * kSlabCols + ((q ^ (lane & (kChunks - 1))) * 4)) =
+                make_uint4(ra[4 * q], ra[4 * q + 1], ra[4 * q + 2], ra[4 * q + 3]);
+          __syncwarp();
+          const uint32_t n = n0 + col_group * kColsPerEpiWarp + pass * kSlabCols + cl * 4;
+          float4 scale = make_float4(ep.alpha, ep.alpha, ep.alpha, ep.alpha);
+          float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+          float4 kscale = make_float4(1.f, 1.f, 1.f, 1.f);
+          if (n < ep.N) {
+            if (ep.col_scale) scale = __ldg(reinterpret_cast<const float4*>(ep.col_scale + n));
+            if (ep.bias) bias = __ldg(reinterpret_cast<const float4*>(ep.bias + n));
+            if (ep.fuse_mode != kFuseNone && ep.shadow_k_scale)
+              kscale = __ldg(reinterpret_cast<const float4*>(ep.shadow_k_scale + n));
+          }
+          auto process = [&](const float4 (&sv)[4], uint32_t half) {
+#pragma unroll
+            for (uint32_t u = 0; u < 4; ++u) {
+              const uint32_t rr = sub + (half * 4 + u) * kRowsPerInstr;
+              if (rr < rows && n < ep.N) {
+                const float4 acc = *reinterpret_cast<const float4*>(
+                    slab + rr * kSlabCols + ((cl ^ (rr & (kChunks - 1))) * 4));
+                const size_t at = static_cast<size_t>(row0 + rr) * ep.N + n;
+                EpilogueStore(ep, at, n, acc, scale, bias, true, kscale, true, sv[u]);
+              }
+            }
+          };
+          load_group(side_b, 2 * pass + 1);
+          process(side_a, 0);
+          if (pass + 1 < kEpiPasses) load_group(side_a, 2 * pass + 2);
+          process(side_b, 1);
+          __syncwarp();   // the slab is rewritten next
+        }
       }
     }
   }
@@ -640,7 +720,10 @@ cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
     cudaError_t e = cudaFuncSetAttribute(UmmaGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(UmmaGemmPersistentKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(UmmaGemmPersistentKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(psmem));
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(UmmaGemmPersistentKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(psmem));
     if (e != cudaSuccess) return e;
     configured = true;
@@ -655,7 +738,12 @@ cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
   if (static_cast<uint64_t>(ptiles_n) * tiles_m > 2ull * sms) {
     // Enough tiles for every SM to amortise its set-up over several.
     const uint32_t band = ptiles_n >= kWideTilesN ? kWideBandBlocks : 1u;
-    UmmaGemmPersistentKernel<<<sms, kPThreads, psmem, s>>>(map_a, map_b, ep, band);
+    // (The x of an absorbed backward activation stays on the in-loop loads: that
+    // epilogue is bound by its arithmetic, and the pipelined form measured 8 % slower.)
+    if (ep.addend != nullptr && ep.fuse_mode != kFuseActBwd)
+      UmmaGemmPersistentKernel<true><<<sms, kPThreads, psmem, s>>>(map_a, map_b, ep, band);
+    else
+      UmmaGemmPersistentKernel<false><<<sms, kPThreads, psmem, s>>>(map_a, map_b, ep, band);
     return cudaGetLastError();
   }
   dim3 grid(tiles_n, tiles_m);
