@@ -57,6 +57,71 @@ __device__ __forceinline__ float SiluGrad(float dy, float x) {
   return dy * (s * (1.0f + x * (1.0f - s)));
 }
 
+// ---- the same GELU expressions on two elements at once ---------------------------------
+// Packed FP32 instructions (`fma/mul/add.rn.f32x2`) round each half exactly as
+// their scalar forms do, so a pair computed here has the bits GeluExpr /
+// GeluGrad give each element: the operation sequence below is theirs, one
+// packed instruction per two scalar ones (the exponential and the reciprocal
+// stay per element).  For the GEMM epilogue, where instruction count is the
+// limit.
+using f32x2 = unsigned long long;
+__device__ __forceinline__ f32x2 PackF2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void UnpackF2(f32x2 v, float* lo, float* hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(*lo), "=f"(*hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 Mul2(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 AddF2(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 Fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ f32x2 Splat2(float v) { return PackF2(v, v); }
+
+// r = 1 / (1 + e^{2u}) for both halves, u = v (c + c a v^2); also returns v^2.
+__device__ __forceinline__ f32x2 GeluRcp2(f32x2 v, f32x2* v2_out) {
+  const f32x2 v2 = Mul2(v, v);
+  const f32x2 u = Mul2(v, Fma2(v2, Splat2(kGeluExprC * kGeluExprA), Splat2(kGeluExprC)));
+  float a0, a1;
+  UnpackF2(Mul2(u, Splat2(kTwoLog2E)), &a0, &a1);
+  float d0, d1;
+  UnpackF2(AddF2(Splat2(1.0f), PackF2(Ex2Approx(a0), Ex2Approx(a1))), &d0, &d1);
+  *v2_out = v2;
+  return PackF2(RcpApprox(d0), RcpApprox(d1));
+}
+__device__ __forceinline__ f32x2 GeluExpr2(f32x2 x) {
+  f32x2 x2;
+  const f32x2 r = GeluRcp2(x, &x2);
+  // fma(-x, r, x): the negation is exact, and rounding is sign-symmetric.
+  return Fma2(Mul2(x, Splat2(-1.0f)), r, x);
+}
+__device__ __forceinline__ f32x2 GeluGrad2(f32x2 dy, f32x2 v) {
+  f32x2 v2;
+  const f32x2 r = GeluRcp2(v, &v2);
+  const f32x2 t = Fma2(Splat2(-2.0f), r, Splat2(1.0f));    // tanh u
+  const f32x2 nt = Fma2(Splat2(2.0f), r, Splat2(-1.0f));   // -tanh u, the same bits negated
+  const f32x2 one_minus_t2 = Fma2(nt, t, Splat2(1.0f));
+  const f32x2 du = Fma2(v2, Splat2(3.0f * kGeluExprC * kGeluExprA), Splat2(kGeluExprC));
+  const f32x2 tail0 = Mul2(Mul2(Mul2(Splat2(0.5f), v), one_minus_t2), du);
+  float s0, s1, t0, t1;
+  UnpackF2(one_minus_t2, &s0, &s1);
+  UnpackF2(tail0, &t0, &t1);
+  const f32x2 tail = PackF2(s0 == 0.0f ? 0.0f : t0, s1 == 0.0f ? 0.0f : t1);
+  return Mul2(dy, AddF2(Fma2(Splat2(0.5f), t, Splat2(0.5f)), tail));
+}
+
 __device__ __forceinline__ float ActFwdExpr(int act, float x) {
   switch (act) {
     case kActRelu: return ReluExpr(x);

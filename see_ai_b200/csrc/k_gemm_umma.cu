@@ -152,12 +152,22 @@ __device__ __forceinline__ void EpilogueStore(const UmmaEpilogue& ep, size_t at,
   if (ep.fuse_mode != kFuseNone) {
     float4 g;
     if (ep.fuse_mode == kFuseActFwd) {
-      g = make_float4(ActFwdExpr(ep.fuse_act, v.x), ActFwdExpr(ep.fuse_act, v.y), ActFwdExpr(ep.fuse_act, v.z),
-                      ActFwdExpr(ep.fuse_act, v.w));
+      if (ep.fuse_act == kActGelu) {   // two elements per instruction; the bits of GeluExpr
+        UnpackF2(GeluExpr2(PackF2(v.x, v.y)), &g.x, &g.y);
+        UnpackF2(GeluExpr2(PackF2(v.z, v.w)), &g.z, &g.w);
+      } else {
+        g = make_float4(ActFwdExpr(ep.fuse_act, v.x), ActFwdExpr(ep.fuse_act, v.y),
+                        ActFwdExpr(ep.fuse_act, v.z), ActFwdExpr(ep.fuse_act, v.w));
+      }
     } else {
       const float4 x = has_side ? side : __ldg(reinterpret_cast<const float4*>(ep.fuse_x + at));
-      g = make_float4(ActBwdExpr(ep.fuse_act, v.x, x.x), ActBwdExpr(ep.fuse_act, v.y, x.y),
-                      ActBwdExpr(ep.fuse_act, v.z, x.z), ActBwdExpr(ep.fuse_act, v.w, x.w));
+      if (ep.fuse_act == kActGelu) {   // likewise, the bits of GeluGrad
+        UnpackF2(GeluGrad2(PackF2(v.x, v.y), PackF2(x.x, x.y)), &g.x, &g.y);
+        UnpackF2(GeluGrad2(PackF2(v.z, v.w), PackF2(x.z, x.w)), &g.z, &g.w);
+      } else {
+        g = make_float4(ActBwdExpr(ep.fuse_act, v.x, x.x), ActBwdExpr(ep.fuse_act, v.y, x.y),
+                        ActBwdExpr(ep.fuse_act, v.z, x.z), ActBwdExpr(ep.fuse_act, v.w, x.w));
+      }
     }
     Shadow sh;
     sh.dst = ep.shadow_dst;
@@ -366,7 +376,8 @@ struct __align__(8) PBarriers {
 };
 
 // kSideLoads: the epilogue reads a second [M, N] f32 operand beside every output
-// (an addend).  Those loads are then software-pipelined: the four of the NEXT group of rows are in flight
+// (an addend, or the x of an absorbed backward activation).  Those loads are
+// then software-pipelined: the four of the NEXT group of rows are in flight
 // while this group is converted and stored, across passes and from before the
 // wait for the accumulator, so a memory round trip is not paid per group with
 // every warp of the CTA waiting on it.
@@ -738,9 +749,7 @@ cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
   if (static_cast<uint64_t>(ptiles_n) * tiles_m > 2ull * sms) {
     // Enough tiles for every SM to amortise its set-up over several.
     const uint32_t band = ptiles_n >= kWideTilesN ? kWideBandBlocks : 1u;
-    // (The x of an absorbed backward activation stays on the in-loop loads: that
-    // epilogue is bound by its arithmetic, and the pipelined form measured 8 % slower.)
-    if (ep.addend != nullptr && ep.fuse_mode != kFuseActBwd)
+    if (ep.addend != nullptr || ep.fuse_mode == kFuseActBwd)
       UmmaGemmPersistentKernel<true><<<sms, kPThreads, psmem, s>>>(map_a, map_b, ep, band);
     else
       UmmaGemmPersistentKernel<false><<<sms, kPThreads, psmem, s>>>(map_a, map_b, ep, band);
