@@ -335,3 +335,92 @@ def test_layernorm_backward_sum_hands_its_copy_to_the_gemm_that_reads_it():
     assert np.array_equal(fused, split)
     # The add kernel and the GEMM's own conversion pass are both gone.
     assert c_split.kernel_launches - c_fused.kernel_launches == 2 and c_fused.fused_dispatches == 1
+
+
+# ---- random programs: whatever the planner decides to absorb, the arena ends the same --------
+# Outside the engine a tensor counts as dead only if the range overwrites it, so a
+# fused range must leave EVERY byte as the one-instruction ranges do.  Programs
+# are drawn from products, bias adds, activations (forward and backward), adds,
+# consumers, copies and fills over a handful of same-size buffers, in-place forms
+# included; any refusal by the runtime guard fails the test as well.
+
+def _random_program(rng, M, K, N):
+    a = Arena(rng)
+    x = a.alloc(M * K, "normal")
+    bufs = [a.alloc(M * N, "normal") for _ in range(5)]
+    small = a.alloc(M * 64)
+    w = a.ro_alloc(rng.integers(-127, 128, size=K * N, dtype=np.int8))
+    sc = a.ro_alloc((rng.random(N) * 0.01 + 1e-3).astype(np.float32))
+    bias = a.ro_alloc(rng.standard_normal(N).astype(np.float32))
+    w2 = a.ro_alloc(rng.integers(-127, 128, size=64 * N, dtype=np.int8))
+    sk = a.ro_alloc((2.0 ** rng.integers(-9, -5, size=N)).astype(np.float32))
+    pick = lambda: bufs[int(rng.integers(len(bufs)))]
+    prog = []
+    for _ in range(int(rng.integers(8, 16))):
+        kind = int(rng.integers(8))
+        i, j, k = pick(), pick(), pick()
+        if kind == 0:
+            prog.append(P.Instr(Op.GEMM_NN_Q8, REL | CS, 0, (x, w, j, sc), (M, N, K)))
+        elif kind == 1:
+            prog.append(P.Instr(Op.ADD_BIAS, 0, 0, (i, bias, j, P.NULL_REF), (M, N, 0)))
+        elif kind == 2:
+            prog.append(P.Instr(Op.GELU_FWD, 0, 0, (i, j), (M * N, 0, 0)))
+        elif kind == 3 and k != j and k != i:
+            prog.append(P.Instr(Op.GELU_BWD, 0, 0, (i, k, j, P.NULL_REF), (M * N, 0, 0)))
+        elif kind == 4:
+            prog.append(P.Instr(Op.ADD_EW, 0, 0, (i, k, j, P.NULL_REF), (M * N, 0, 0)))
+        elif kind == 5:
+            prog.append(P.Instr(Op.GEMM_NT_Q8, REL | CS, 0, (i, w2, small, sk), (M, 64, N)))
+        elif kind == 6 and i != j:
+            prog.append(P.Instr(Op.COPY, 0, 0, (i, j), (M * N, 0, 0)))
+        else:
+            prog.append(P.Instr(Op.FILL, 0, 0, (j, P.f32_bits(0.5)), (M * N, 0, 0)))
+        # Products are usually followed by something that can ride their epilogue.
+        if kind == 0 and rng.random() < 0.8:
+            nxt = int(rng.integers(4))
+            o = pick()
+            if nxt == 0:
+                prog.append(P.Instr(Op.ADD_BIAS, 0, 0, (j, bias, o, P.NULL_REF), (M, N, 0)))
+                if rng.random() < 0.7:
+                    o2 = pick()
+                    if rng.random() < 0.5:
+                        prog.append(P.Instr(Op.GELU_FWD, 0, 0, (o, o2), (M * N, 0, 0)))
+                    elif k != o:
+                        prog.append(P.Instr(Op.ADD_EW, 0, 0, (k, o, o2, P.NULL_REF), (M * N, 0, 0)))
+                    if rng.random() < 0.7:
+                        prog.append(P.Instr(Op.GEMM_NT_Q8, REL | CS, 0, (o2, w2, small, sk), (M, 64, N)))
+            elif nxt == 1:
+                prog.append(P.Instr(Op.GELU_FWD, 0, 0, (j, o), (M * N, 0, 0)))
+                prog.append(P.Instr(Op.GEMM_NT_Q8, REL | CS, 0, (o, w2, small, sk), (M, 64, N)))
+            elif nxt == 2 and k != j and k != o:
+                prog.append(P.Instr(Op.GELU_BWD, 0, 0, (j, k, o, P.NULL_REF), (M * N, 0, 0)))
+                prog.append(P.Instr(Op.GEMM_NT_Q8, REL | CS, 0, (o, w2, small, sk), (M, 64, N)))
+            elif k != j:
+                prog.append(P.Instr(Op.ADD_EW, 0, 0, (k, j, o, P.NULL_REF), (M * N, 0, 0)))
+    for b in bufs:   # most buffers end overwritten, so intermediates can be proven dead
+        if rng.random() < 0.7:
+            prog.append(P.Instr(Op.FILL, 0, 0, (b, P.f32_bits(0.25)), (M * N, 0, 0)))
+    arena, ro = a.build()
+    return prog, arena, ro
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_programs_end_with_the_same_arena_fused_or_not(seed):
+    rng = np.random.default_rng(1000 + seed)
+    M, K, N = (256, 128, 128) if seed % 4 else (4864, 64, 2048)
+    prog, arena0, ro = _random_program(rng, M, K, N)
+    fused, c_fused = _run(prog, arena0, ro, one_range=True)
+    split, c_split = _run(prog, arena0, ro, one_range=False)
+    assert np.array_equal(fused, split), [str(i) for i in prog]
+    assert c_split.fused_dispatches == 0
+
+
+def test_the_random_programs_do_exercise_the_fusions():
+    total = 0
+    for seed in range(8, 16):
+        rng = np.random.default_rng(1000 + seed)
+        M, K, N = (256, 128, 128) if seed % 4 else (4864, 64, 2048)
+        prog, arena0, ro = _random_program(rng, M, K, N)
+        _fused, c = _run(prog, arena0, ro, one_range=True)
+        total += c.fused_dispatches
+    assert total >= 5
