@@ -20,6 +20,7 @@ struct AttnUmmaArgs {
   float* stats;     // f32 [B*H*S, 4]: score max, 1/denominator, delta, start
   DeviceStatus* status;
   Shadow shadow;    // optional bf16 copy of `out` (cols = H*d) for the GEMM that reads it next
+  float* out2 = nullptr;   // dK and dV in one walk: dV goes here (out is dK)
 };
 
 // f32 [B*S, H*d] (heads interleaved along the row) -> bf16 per (sequence, head):
@@ -35,10 +36,11 @@ cudaError_t AttnFwdUmma(const CUtensorMap& q, const CUtensorMap& k_half, const C
 cudaError_t AttnDQUmma(const CUtensorMap& q, const CUtensorMap& dout, const CUtensorMap& k_half,
                        const CUtensorMap& v_half, const CUtensorMap& kt, const AttnUmmaArgs& a,
                        cudaStream_t s);
-// t = dO columns for dV, Q columns for dK.  dV ignores v and dout_half.
-cudaError_t AttnDKVUmma(bool want_dk, const CUtensorMap& k, const CUtensorMap& v,
+// mode 0: dV (t = dO columns; v and dout_half ignored); 1: dK (t = Q columns);
+// 2: both in one walk (t = Q columns, t2 = dO columns, a.out = dK, a.out2 = dV; d = 64 only).
+cudaError_t AttnDKVUmma(int mode, const CUtensorMap& k, const CUtensorMap& v,
                         const CUtensorMap& q_half, const CUtensorMap& dout_half, const CUtensorMap& t,
-                        const AttnUmmaArgs& a, cudaStream_t s);
+                        const CUtensorMap& t2, const AttnUmmaArgs& a, cudaStream_t s);
 
 }  // namespace see::k
 

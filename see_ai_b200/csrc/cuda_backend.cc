@@ -376,6 +376,8 @@ void CudaBackend::EndRange() {
   loss_fusion_.clear();
   add_fusion_.clear();
   skip_add_at_ = -1;
+  attn_dv_out_.clear();
+  skip_attn_dv_at_ = -1;
   skip_act_at_ = -1;
   elided_.clear();
   pending_elided_.clear();
@@ -661,6 +663,7 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
   act_fusion_.assign(end > begin ? end - begin : 0, ActFusion{});
   loss_fusion_.assign(end > begin ? end - begin : 0, LossFusion{});
   add_fusion_.assign(end > begin ? end - begin : 0, AddFusion{});
+  attn_dv_out_.assign(end > begin ? end - begin : 0, kNullRef);
   if (coherence_ == Coherence::kStrict || !relaxed_allowed_ || !epilogue_fusion_ || end < begin + 3) return;
   // Under the step-program promise liveness is decided on the whole program.
   const bool whole = step_program_ != nullptr && program.data() == step_program_;
@@ -696,6 +699,35 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
     if (!sp.want || (op != kSoftmaxXEntBwd && op != kSoftmaxXEntMaskedBwd)) continue;
     if (sp.scale_ref != kNullRef && (sp.scale_off & 15) != 0) continue;
     sp.only = dead_after(i, DeadQuery{sp.a_off, sp.a_off + sp.M * sp.K * 4, true, sp.scale_off, sp.M, sp.K});
+  }
+  // dK and dV of the same attention in one walk over the queries.
+  for (size_t i = begin; i + 1 < end; ++i) {
+    const Instruction& dk = program[i];
+    const Instruction& dv = program[i + 1];
+    if (dk.opcode != kAttnDKTiled || dv.opcode != kAttnDVTiled || !(dk.flags & kFlagRelaxed) ||
+        !(dv.flags & kFlagRelaxed))
+      continue;
+    if (dk.in[0] != dv.in[0] || dk.in[1] != dv.in[1] || dk.in[2] != dv.in[2] || dk.in[3] != dv.in[3] ||
+        dk.out[0] != dv.out[0] || dk.out[2] != dv.out[2] || RefSpace(dk.out[1]) != kArena ||
+        RefSpace(dv.out[1]) != kArena)
+      continue;
+    const AttnGeom g = UnpackAttnGeom(dk.out[2]);
+    const uint64_t bytes = g.B * g.S * g.H * g.d * 4;
+    if (g.d != 64 || !disjoint(RefOffset(dk.out[1]), RefOffset(dk.out[1]) + bytes, RefOffset(dv.out[1]),
+                               RefOffset(dv.out[1]) + bytes))
+      continue;
+    // Neither output may lie over an operand the other instruction still reads.
+    bool clash = false;
+    for (int op = 0; op < 4; ++op)
+      if (RefSpace(dk.in[op]) == kArena &&
+          (!disjoint(RefOffset(dk.in[op]), RefOffset(dk.in[op]) + bytes, RefOffset(dk.out[1]),
+                     RefOffset(dk.out[1]) + bytes) ||
+           !disjoint(RefOffset(dk.in[op]), RefOffset(dk.in[op]) + bytes, RefOffset(dv.out[1]),
+                     RefOffset(dv.out[1]) + bytes)))
+        clash = true;
+    if (clash) continue;
+    attn_dv_out_[i - begin] = dv.out[1];
+    shadow_plan_[i + 1 - begin].want = false;   // the pair's dV leaves as f32 only
   }
   // Forward loss, seed fill, backward loss: one row pass when the gradient leaves
   // as a copy only.
@@ -1561,15 +1593,28 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
                                    RefOffset(ins.in[3]), Wr(ins.out[0]), Wr(ins.out[1]),
                                    g.B, g.S, g.H, g.d, k::Shadow{}};
         const uint64_t elems = g.B * g.S * g.H * g.d;
+        if (ins.opcode == kAttnDVTiled && skip_attn_dv_at_ == static_cast<int64_t>(range_index_)) {
+          skip_attn_dv_at_ = -1;   // done by the dK kernel before it
+          ++counters_.relaxed_executions;
+          break;
+        }
         const k::Shadow* sh = ShadowFor(ins.out[1], elems);
         if (sh && sh->cols == g.H * g.d && k::ShadowUsable(sh, op.out, elems)) op.shadow = *sh;
+        if (ins.opcode == kAttnDKTiled && range_index_ < attn_dv_out_.size() &&
+            attn_dv_out_[range_index_] != kNullRef)
+          op.out2 = Wr(attn_dv_out_[range_index_]);
         int n = 0;
-        if (std::string e = umma::TryAttention(&umma_->ctx, ins.opcode, op, s, &n); !e.empty())
+        bool did_second = false;
+        if (std::string e = umma::TryAttention(&umma_->ctx, ins.opcode, op, s, &n, &did_second); !e.empty())
           return std::unexpected("cuda: " + e);
         if (n > 0) {
           shadow_written_ = op.shadow.dst != nullptr;
           ++counters_.relaxed_executions;
           launched(n);
+          if (did_second) {
+            ++counters_.fused_dispatches;
+            skip_attn_dv_at_ = static_cast<int64_t>(range_index_) + 1;
+          }
           break;
         }
       }

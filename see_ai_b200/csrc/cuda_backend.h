@@ -305,6 +305,12 @@ class CudaBackend {
     uint64_t z_lo = 0, z_hi = 0;   // the product's own range when it stays unwritten
   };
   std::vector<AddFusion> add_fusion_;   // per range position (of the GEMM)
+
+  // kAttnDKTiled directly followed by kAttnDVTiled on the same operands (relaxed,
+  // head width 64): one kernel walks the queries once for both.  Per range
+  // position of the dK instruction: the dV output reference, or kNullRef.
+  std::vector<uint64_t> attn_dv_out_;
+  int64_t skip_attn_dv_at_ = -1;
   int64_t skip_add_at_ = -1;            // the absorbed kAddEW (its output IS written, by the product)
 
   Counters counters_;

@@ -517,11 +517,19 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 // number per query, M = max * log2(e) - log2(1/denominator), so that
 // P^T = 2^(s * log2(e)/sqrt(d) - M).  dV += P^T dO_h, or
 // dS^T = P^T (dP^T - delta) / sqrt(d) with dP^T = V dO_h^T and dK += dS^T Q_h.
-template <int D, bool kWantDK>
+// kMode 0: dV alone; 1: dK alone; 2: both in one walk (the plan's kAttnDKTiled /
+// kAttnDVTiled pair on the same operands): S^T and P^T are formed once, dV's
+// product rides the step's second commit, and the second kernel's passes over K,
+// Q and the statistics disappear.  Tensor memory: S^T, dP^T, dK, dV = 4 x 64 columns
+// at d = 64 (the 256 the dK form occupies anyway).
+template <int D, int kMode>
 __global__ void __launch_bounds__(128)
 AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                   const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
-                  const __grid_constant__ CUtensorMap map_t, AttnUmmaArgs a) {
+                  const __grid_constant__ CUtensorMap map_t, const __grid_constant__ CUtensorMap map_t2,
+                  AttnUmmaArgs a) {
+  constexpr bool kWantDK = kMode >= 1;
+  constexpr bool kBoth = kMode == 2;
   extern __shared__ uint8_t smem_raw[];
   Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw);
   uint8_t* smem = AlignSmem(smem_raw + sizeof(Ctl));
@@ -531,10 +539,13 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
   uint8_t* q_s = v_s + (kWantDK ? kFull : 0);
   uint8_t* do_s = q_s + kHalfRows;                           // dK only
   uint8_t* t_s = do_s + (kWantDK ? kHalfRows : 0);
-  uint8_t* p_s = t_s + kCols;
-  float* stat_s = reinterpret_cast<float*>(p_s + kHalfTileBytes);   // M[64], delta[64]
+  uint8_t* t2_s = t_s + kCols;                               // both: dO in the column layout
+  uint8_t* p_s = t2_s + (kBoth ? kCols : 0);
+  uint8_t* p2_s = p_s + kHalfTileBytes;                      // both: P^T beside dS^T
+  float* stat_s = reinterpret_cast<float*>(p2_s + (kBoth ? kHalfTileBytes : 0));   // M[64], delta[64]
   constexpr uint32_t kOutCol = kWantDK ? 128 : 64;
-  constexpr uint32_t kTmemCols = TmemColsFor(kOutCol + D);
+  constexpr uint32_t kOutCol2 = kOutCol + D;                 // both: dV after dK
+  constexpr uint32_t kTmemCols = TmemColsFor(kOutCol + (kBoth ? 2 : 1) * D);
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5;
   const uint32_t jt = blockIdx.x;                          // key tile; low tiles have the most work
@@ -565,8 +576,9 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     if (kWantDK) LoadRows<D, 64>(do_s, &map_do, &ctl->bar_a, (h0 + t) * kHalf, bh);
   };
   auto issue_b = [&](uint32_t t) {
-    MbarExpectTx(&ctl->bar_b, kCols);
+    MbarExpectTx(&ctl->bar_b, (kBoth ? 2 : 1) * kCols);
     LoadColsHalf(t_s, &map_t, &ctl->bar_b, (h0 + t) * kHalf, bh);
+    if (kBoth) LoadColsHalf(t2_s, &map_t2, &ctl->bar_b, (h0 + t) * kHalf, bh);
   };
 
   const uint32_t key = jt * kTile + tid;                    // this thread's key row
@@ -613,6 +625,7 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
       if (kWantDK) TmemLoad32(t_lane + 64 + c0, rp);
       TmemWaitLd();
       float v[32];
+      [[maybe_unused]] float pv[kBoth ? 32 : 1];
 #pragma unroll
       for (int j4 = 0; j4 < 32; j4 += 4) {
         const float4 M4 = *reinterpret_cast<const float4*>(&stat_s[c0 + j4]);
@@ -628,9 +641,11 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
           float p = Exp2Approx(fmaf(__uint_as_float(rs[j]), c1, -Mv[u]));
           if (diagonal && key > q0 + c0 + j) p = 0.0f;
           v[j] = kWantDK ? p * (__uint_as_float(rp[j]) - dv[u]) * a.inv_sqrt_d : p;
+          if (kBoth) pv[kBoth ? j : 0] = p;
         }
       }
       StoreRowChunk(p_s, tid, c0, v);
+      if constexpr (kBoth) StoreRowChunk(p2_s, tid, c0, pv);
     }
     FenceProxyAsync();
     TcFenceBefore();
@@ -638,7 +653,10 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     if (tid == 0) {
       if (!MbarWait(&ctl->bar_b, t & 1)) failed = 1;
       TcFenceAfter();
-      if (!failed) MmaPT<D>(tmem + kOutCol, p_s, t_s, t != 0);
+      if (!failed) {
+        MmaPT<D>(tmem + kOutCol, p_s, t_s, t != 0);                 // dK += dS^T Q_h, or dV += P^T dO_h
+        if (kBoth) MmaPT<D>(tmem + kOutCol2, p2_s, t2_s, t != 0);   // dV += P^T dO_h
+      }
     }
   }
   if (tid == 0) UmmaCommit(&ctl->mma);
@@ -655,6 +673,11 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     const size_t flat0 = (static_cast<size_t>(b) * a.S + row0w) * HD + static_cast<size_t>(h) * D;
     StoreOutRows<D>(t_lane + kOutCol, reinterpret_cast<float*>(smem) + warp * 32 * D, tid & 31, 1.0f,
                     a.out + flat0, HD, rows_live, a.shadow, flat0, h * D);
+    if constexpr (kBoth) {
+      __syncwarp();   // the warp's staging slab is reused
+      StoreOutRows<D>(t_lane + kOutCol2, reinterpret_cast<float*>(smem) + warp * 32 * D, tid & 31, 1.0f,
+                      a.out2 + flat0, HD, rows_live, Shadow{}, flat0, h * D);
+    }
   }
   TcFenceBefore();
   __syncthreads();
@@ -668,9 +691,9 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 
 size_t AttnFwdSmem(int d) { return 128 * d * 2 + 64 * d * 2 + d * 128 + kHalfTileBytes + 1152; }
 size_t AttnDQSmem(int d) { return 2 * 128 * d * 2 + 2 * 64 * d * 2 + d * 128 + kHalfTileBytes + 1152; }
-size_t AttnDKVSmem(int d, bool dk) {
+size_t AttnDKVSmem(int d, int mode) {   // 0: dV, 1: dK, 2: both
   const size_t full = 128 * d * 2, half = 64 * d * 2, cols = d * 128;
-  return (dk ? 2 : 1) * (full + half) + cols + kHalfTileBytes + 2 * kHalf * 4 + 1152;
+  return (mode >= 1 ? 2 : 1) * (full + half) + (mode == 2 ? 2 : 1) * (cols + kHalfTileBytes) + 2 * kHalf * 4 + 1152;
 }
 
 template <typename Kernel>
@@ -716,21 +739,22 @@ cudaError_t AttnDQUmma(const CUtensorMap& q, const CUtensorMap& dout, const CUte
   return cudaGetLastError();
 }
 
-cudaError_t AttnDKVUmma(bool want_dk, const CUtensorMap& k, const CUtensorMap& v,
+cudaError_t AttnDKVUmma(int mode, const CUtensorMap& k, const CUtensorMap& v,
                         const CUtensorMap& q_half, const CUtensorMap& dout_half, const CUtensorMap& t,
-                        const AttnUmmaArgs& a, cudaStream_t s) {
+                        const CUtensorMap& t2, const AttnUmmaArgs& a, cudaStream_t s) {
   dim3 grid((a.S + kTile - 1) / kTile, a.B * a.H);
   cudaError_t e;
-#define SEE_LAUNCH_DKV(D, DK)                                                          \
-  do {                                                                                 \
-    const size_t smem = AttnDKVSmem(D, DK);                                            \
-    if ((e = Configure(AttnDKVUmmaKernel<D, DK>, smem)) != cudaSuccess) return e;      \
-    AttnDKVUmmaKernel<D, DK><<<grid, 128, smem, s>>>(k, v, q_half, dout_half, t, a);   \
+#define SEE_LAUNCH_DKV(D, MODE)                                                              \
+  do {                                                                                       \
+    const size_t smem = AttnDKVSmem(D, MODE);                                                \
+    if ((e = Configure(AttnDKVUmmaKernel<D, MODE>, smem)) != cudaSuccess) return e;          \
+    AttnDKVUmmaKernel<D, MODE><<<grid, 128, smem, s>>>(k, v, q_half, dout_half, t, t2, a);   \
   } while (0)
   if (a.d == 64) {
-    if (want_dk) SEE_LAUNCH_DKV(64, true); else SEE_LAUNCH_DKV(64, false);
-  } else {
-    if (want_dk) SEE_LAUNCH_DKV(128, true); else SEE_LAUNCH_DKV(128, false);
+    if (mode == 2) SEE_LAUNCH_DKV(64, 2); else if (mode == 1) SEE_LAUNCH_DKV(64, 1); else SEE_LAUNCH_DKV(64, 0);
+  } else {   // d = 128: both accumulators would need 384 columns beside S^T and dP^T; not offered
+    if (mode == 2) return cudaErrorInvalidValue;
+    if (mode == 1) SEE_LAUNCH_DKV(128, 1); else SEE_LAUNCH_DKV(128, 0);
   }
 #undef SEE_LAUNCH_DKV
   return cudaGetLastError();

@@ -370,7 +370,8 @@ bool EncodeHeads(Impl* impl, CUtensorMap* map, const void* base, uint64_t inner,
 }  // namespace
 
 std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands& op,
-                         cudaStream_t stream, int* launches) {
+                         cudaStream_t stream, int* launches, bool* did_second) {
+  if (did_second) *did_second = false;
   *launches = 0;
   Impl* impl = ctx->impl;
   if (!impl) return {};
@@ -437,8 +438,12 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
   cudaError_t e = cudaSuccess;
   if (fwd) e = k::AttnFwdUmma(mr[Q], mh[K], mc[V], a, stream);
   if (dq) e = k::AttnDQUmma(mr[Q], mr[DO], mh[K], mh[V], mc[K], a, stream);
-  if (dk) e = k::AttnDKVUmma(true, mr[K], mr[V], mh[Q], mh[DO], mc[Q], a, stream);
-  if (dv) e = k::AttnDKVUmma(false, mr[K], mr[K], mh[Q], mh[Q], mc[DO], a, stream);
+  const bool both = dk && op.out2 != nullptr && op.d == 64 &&
+                    (reinterpret_cast<uintptr_t>(op.out2) & 15) == 0;
+  if (both) a.out2 = op.out2;
+  if (dk) e = k::AttnDKVUmma(both ? 2 : 1, mr[K], mr[V], mh[Q], mh[DO], mc[Q], both ? mc[DO] : mc[Q], a, stream);
+  if (dv) e = k::AttnDKVUmma(0, mr[K], mr[K], mh[Q], mh[Q], mc[DO], mc[DO], a, stream);
+  if (both && e == cudaSuccess && did_second) *did_second = true;
   if (e != cudaSuccess) return std::string("tensor-core attention launch: ") + cudaGetErrorString(e);
   ++*launches;
   return {};

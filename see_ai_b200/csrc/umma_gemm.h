@@ -69,9 +69,13 @@ struct AttentionOperands {
   float* stats; float* out;
   uint64_t B, S, H, d;
   k::Shadow shadow;   // optional bf16 copy of `out`
+  // kAttnDKTiled only: the kAttnDVTiled that follows on the same operands, done in
+  // the same walk (its output; head width 64 only — TryAttention ignores it otherwise
+  // and reports through *did_second).
+  float* out2 = nullptr;
 };
 std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands& op,
-                         cudaStream_t stream, int* launches);
+                         cudaStream_t stream, int* launches, bool* did_second = nullptr);
 
 // Profile mode: the next tensor-core launch records `before` / `after` around
 // the kernel itself (not the operand conversions).  Returns whether a launch

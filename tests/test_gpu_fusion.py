@@ -424,3 +424,33 @@ def test_the_random_programs_do_exercise_the_fusions():
         _fused, c = _run(prog, arena0, ro, one_range=True)
         total += c.fused_dispatches
     assert total >= 5
+
+
+def test_attention_dk_and_dv_share_one_walk():
+    from tests.test_gpu_umma import bf16_round
+    Bq, S, H, d = 2, 384, 2, 64
+    rng = np.random.default_rng(53)
+    a = Arena(rng)
+    td = Bq * S * H * d
+    t = {}
+    for name in ("q", "k", "v", "do"):
+        t[name] = a.alloc(td, bf16_round(rng.standard_normal(td).astype(np.float32) * 0.7))
+    for name in ("o", "dq", "dk", "dv"):
+        t[name] = a.alloc(td)
+    stats = a.alloc(Bq * H * S * 4)
+    bs, hd, geo = P.pack2(Bq, S), P.pack2(H, d), P.pack_attn_geometry(Bq, S, H, d)
+    prog = [
+        P.Instr(Op.ATTN_FWD_TILED, REL, 0, (t["q"], t["k"], t["v"], t["o"]), (stats, bs, hd)),
+        P.Instr(Op.ATTN_DQ_TILED, REL, 0, (t["q"], t["k"], t["v"], t["do"]), (stats, t["dq"], geo)),
+        P.Instr(Op.ATTN_DK_TILED, REL, 0, (t["q"], t["k"], t["v"], t["do"]), (stats, t["dk"], geo)),
+        P.Instr(Op.ATTN_DV_TILED, REL, 0, (t["q"], t["k"], t["v"], t["do"]), (stats, t["dv"], geo)),
+    ]
+    arena0, ro = a.build()
+    fused, c_fused = _run(prog, arena0, ro, one_range=True)
+    split, c_split = _run(prog, arena0, ro, one_range=False)
+    assert np.isfinite(fused.view(np.float32)).all()
+    assert np.array_equal(fused, split)
+    assert c_fused.fused_dispatches == 1 and c_split.fused_dispatches == 0
+    assert c_fused.relaxed_executions == c_split.relaxed_executions == 4
+    dv = fused[t["dv"]:t["dv"] + 4 * td].view(np.float32)
+    assert np.abs(dv).max() > 0
