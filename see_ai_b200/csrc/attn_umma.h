@@ -21,6 +21,7 @@ struct AttnUmmaArgs {
   DeviceStatus* status;
   Shadow shadow;    // optional bf16 copy of `out` (cols = H*d) for the GEMM that reads it next
   float* out2 = nullptr;   // dK and dV in one walk: dV goes here (out is dK)
+  Shadow shadow2;          // and its optional bf16 copy
 };
 
 // f32 [B*S, H*d] (heads interleaved along the row) -> bf16 per (sequence, head):

@@ -377,6 +377,7 @@ void CudaBackend::EndRange() {
   add_fusion_.clear();
   skip_add_at_ = -1;
   attn_dv_out_.clear();
+  attn_dv_shadow_.clear();
   skip_attn_dv_at_ = -1;
   skip_act_at_ = -1;
   elided_.clear();
@@ -664,6 +665,7 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
   loss_fusion_.assign(end > begin ? end - begin : 0, LossFusion{});
   add_fusion_.assign(end > begin ? end - begin : 0, AddFusion{});
   attn_dv_out_.assign(end > begin ? end - begin : 0, kNullRef);
+  attn_dv_shadow_.assign(end > begin ? end - begin : 0, ShadowPlan{});
   if (coherence_ == Coherence::kStrict || !relaxed_allowed_ || !epilogue_fusion_ || end < begin + 3) return;
   // Under the step-program promise liveness is decided on the whole program.
   const bool whole = step_program_ != nullptr && program.data() == step_program_;
@@ -727,7 +729,8 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
         clash = true;
     if (clash) continue;
     attn_dv_out_[i - begin] = dv.out[1];
-    shadow_plan_[i + 1 - begin].want = false;   // the pair's dV leaves as f32 only
+    attn_dv_shadow_[i - begin] = shadow_plan_[i + 1 - begin];   // the pair's kernel makes dV's copy too
+    shadow_plan_[i + 1 - begin].want = false;
   }
   // Forward loss, seed fill, backward loss: one row pass when the gradient leaves
   // as a copy only.
@@ -1024,7 +1027,8 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   // (A kAddBias done by the preceding product's epilogue reads nothing either.)
   // (A kAddEW done by the kernel before it: that kernel's dispatch has already
   // dropped older copies of the sum's range and may have published the new one.)
-  const bool add_done = skip_add_at_ == static_cast<int64_t>(range_index_);
+  const bool add_done = skip_add_at_ == static_cast<int64_t>(range_index_) ||
+                        skip_attn_dv_at_ == static_cast<int64_t>(range_index_);
   const bool bias_done = (skip_next_add_bias_ && ins.opcode == kAddBias) || add_done;
   if (!elided_.empty() && !absorbed && !bias_done) {
     for (size_t i = 0; i < ext.count; ++i) {
@@ -1603,6 +1607,17 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
         if (ins.opcode == kAttnDKTiled && range_index_ < attn_dv_out_.size() &&
             attn_dv_out_[range_index_] != kNullRef)
           op.out2 = Wr(attn_dv_out_[range_index_]);
+        uint16_t* dv_copy = nullptr;
+        if (op.out2 && attn_dv_shadow_[range_index_].want && attn_dv_shadow_[range_index_].scale_ref == kNullRef) {
+          const ShadowPlan& sp2 = attn_dv_shadow_[range_index_];
+          if (sp2.M * sp2.K == elems && sp2.K == g.H * g.d && sp2.a_off == RefOffset(attn_dv_out_[range_index_]))
+            dv_copy = umma::ReserveShadow(&umma_->ctx, elems, /*keep_reserved=*/true);
+          if (dv_copy) {
+            op.shadow2.dst = dv_copy;
+            op.shadow2.cols = sp2.K;
+            if (!k::ShadowUsable(&op.shadow2, op.out2, elems)) { op.shadow2 = k::Shadow{}; dv_copy = nullptr; }
+          }
+        }
         int n = 0;
         bool did_second = false;
         if (std::string e = umma::TryAttention(&umma_->ctx, ins.opcode, op, s, &n, &did_second); !e.empty())
@@ -1614,6 +1629,13 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
           if (did_second) {
             ++counters_.fused_dispatches;
             skip_attn_dv_at_ = static_cast<int64_t>(range_index_) + 1;
+            // dV's range is written now: older copies of it go, the new one is published
+            // (the skipped instruction's own bookkeeping must then leave it alone).
+            const ShadowPlan& sp2 = attn_dv_shadow_[range_index_];
+            umma::InvalidateRange(&umma_->ctx, RefOffset(attn_dv_out_[range_index_]), elems * 4);
+            if (dv_copy) umma::CommitShadow(&umma_->ctx, dv_copy, sp2.a_off, sp2.scale_off, sp2.M, sp2.K);
+          } else if (dv_copy) {
+            umma::ReleaseReservations(&umma_->ctx);
           }
           break;
         }

@@ -310,6 +310,7 @@ class CudaBackend {
   // head width 64): one kernel walks the queries once for both.  Per range
   // position of the dK instruction: the dV output reference, or kNullRef.
   std::vector<uint64_t> attn_dv_out_;
+  std::vector<ShadowPlan> attn_dv_shadow_;   // the dV instruction's copy plan, made by the pair's kernel
   int64_t skip_attn_dv_at_ = -1;
   int64_t skip_add_at_ = -1;            // the absorbed kAddEW (its output IS written, by the product)
 

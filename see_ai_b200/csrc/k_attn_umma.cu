@@ -676,7 +676,7 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     if constexpr (kBoth) {
       __syncwarp();   // the warp's staging slab is reused
       StoreOutRows<D>(t_lane + kOutCol2, reinterpret_cast<float*>(smem) + warp * 32 * D, tid & 31, 1.0f,
-                      a.out2 + flat0, HD, rows_live, Shadow{}, flat0, h * D);
+                      a.out2 + flat0, HD, rows_live, a.shadow2, flat0, h * D);
     }
   }
   TcFenceBefore();

@@ -323,13 +323,13 @@ void ReleaseReservations(Context* ctx) {
   for (auto& c : ctx->impl->acts) c.reserved = false;
 }
 
-uint16_t* ReserveShadow(Context* ctx, uint64_t elems) {
+uint16_t* ReserveShadow(Context* ctx, uint64_t elems, bool keep_reserved) {
   Impl* impl = ctx->impl;
   if (!impl) return nullptr;
   ActCopy* slot = nullptr;
   for (auto& c : impl->acts) {
-    c.reserved = false;   // one reservation at a time
-    if (c.capacity < elems || !c.buf) continue;
+    if (!keep_reserved) c.reserved = false;   // normally one reservation at a time
+    if (c.reserved || c.capacity < elems || !c.buf) continue;
     if (!c.valid) { slot = &c; break; }
     if (!slot || c.last_use < slot->last_use) slot = &c;
   }
@@ -440,7 +440,10 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
   if (dq) e = k::AttnDQUmma(mr[Q], mr[DO], mh[K], mh[V], mc[K], a, stream);
   const bool both = dk && op.out2 != nullptr && op.d == 64 &&
                     (reinterpret_cast<uintptr_t>(op.out2) & 15) == 0;
-  if (both) a.out2 = op.out2;
+  if (both) {
+    a.out2 = op.out2;
+    a.shadow2 = op.shadow2;
+  }
   if (dk) e = k::AttnDKVUmma(both ? 2 : 1, mr[K], mr[V], mh[Q], mh[DO], mc[Q], both ? mc[DO] : mc[Q], a, stream);
   if (dv) e = k::AttnDKVUmma(0, mr[K], mr[K], mh[Q], mh[Q], mc[DO], mc[DO], a, stream);
   if (both && e == cudaSuccess && did_second) *did_second = true;

@@ -48,7 +48,9 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& args, int b_space, uint64_t
 // instruction's own write extents have gone through InvalidateRange, CommitShadow
 // publishes the slot under the key TryGemm looks up (arena offset, scale offset,
 // M, K).  A reservation that is not committed is simply reused later.
-uint16_t* ReserveShadow(Context* ctx, uint64_t elems);
+// keep_reserved: a second reservation beside the one already held (an instruction
+// that writes two tensors).
+uint16_t* ReserveShadow(Context* ctx, uint64_t elems, bool keep_reserved = false);
 // True when a valid copy with this key exists; marks it most recently used (so
 // the next ReserveShadow does not take its slot).
 bool TouchActCopy(Context* ctx, uint64_t a_off, uint64_t a_scale_off, uint64_t M, uint64_t K);
@@ -73,6 +75,7 @@ struct AttentionOperands {
   // the same walk (its output; head width 64 only — TryAttention ignores it otherwise
   // and reports through *did_second).
   float* out2 = nullptr;
+  k::Shadow shadow2;   // optional bf16 copy of `out2`
 };
 std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands& op,
                          cudaStream_t stream, int* launches, bool* did_second = nullptr);
