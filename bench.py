@@ -142,18 +142,29 @@ def cpu_sample(steps: int, warmup: int):
         cores = 1
     ex.bind(arena, np.frombuffer(plan.rodata, dtype=np.uint8).copy())
     batches = synthetic_batches(h["batch"], cfg.vocab, 2, seed=11)
+    from see_ai_b200 import dp
+    _bwd, opt_begin = dp.scan_phases(plan.train)
+    g_off, g_bytes = dp.gradient_block(plan)
     times = []
+    first = {}
     for s in range(warmup + steps):
         x, y = batches[s % 2]
         t0 = time.perf_counter()
         arena[h["input_ref"]:h["input_ref"] + x.nbytes] = x.view(np.uint8)
         arena[h["label_ref"]:h["label_ref"] + y.nbytes] = y.view(np.uint8)
-        ex.run(plan.train, oracle.step_params(lr=cfg.lr, step=s + 1))
+        sp = oracle.step_params(lr=cfg.lr, step=s + 1)
+        if s == 0:   # the first step in two ranges, so that its loss and gradient block can be kept
+            ex.run(plan.train, sp, 0, opt_begin)
+            first = dict(loss=float(arena[h["loss_ref"]:h["loss_ref"] + 4].view(np.float32)[0]),
+                         grad=arena[g_off:g_off + g_bytes].view(np.float32).copy(), batch=(x, y))
+            ex.run(plan.train, sp, opt_begin, len(plan.train))
+        else:
+            ex.run(plan.train, sp)
         if s >= warmup:
             times.append(time.perf_counter() - t0)
     sec = sum(times) / len(times)
     loss = float(arena[h["loss_ref"]:h["loss_ref"] + 4].view(np.float32)[0])
-    return h["batch"] / sec, dict(kind=kind, cores=int(cores), seconds_per_step=sec, loss=loss,
+    return h["batch"] / sec, dict(kind=kind, cores=int(cores), seconds_per_step=sec, loss=loss, first=first,
                                   sample=f"{len(times)} optimizer step(s) of the same 12-layer plan at "
                                          f"1 sequence ({h['batch']} tokens) instead of {GLOBAL_SEQS}")
 
@@ -175,6 +186,33 @@ def run_reference(args):
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     emit(line)
+
+
+def gpu_vs_cpu_first_step(first: dict, device: int, graphs: bool) -> dict:
+    """Outside every timed region: the engine exactly as the timed loop drives it
+    (graphs, fusions, tensor-core kernels) on the CPU sample's plan and first
+    batch, its loss and gradient block against the reference CPU executor's."""
+    from see_ai_b200.engine import Engine
+    cfg = decoder_config(1)
+    eng = Engine(device)
+    eng.load(synth.build_decoder_plan(cfg))
+    eng.set_horizon(cfg.steps)
+    eng.set_use_graphs(graphs)
+    x, y = first["batch"]
+    eng.stage_batch(x, y)
+    eng.train_forward_backward(True)
+    loss = eng.read_loss()
+    off, nbytes = eng.gradient_block()
+    got = eng.read_arena(off, nbytes).view(np.float32).astype(np.float64)
+    eng.close()
+    want = first["grad"].astype(np.float64)
+    rms = float(np.sqrt(np.mean((got - want) ** 2)) / np.sqrt(np.mean(want ** 2)))
+    worst = float(np.abs(got - want).max() / np.abs(want).max())
+    return {"plan": "the benchmark's plan at 1 sequence, first step, same batch on both sides",
+            "loss_gpu": loss, "loss_cpu": first["loss"],
+            "loss_rel_err": abs(loss - first["loss"]) / abs(first["loss"]),
+            "gradient_block_rel_rms": rms, "gradient_block_max_err_over_max": worst,
+            "tolerance": 2e-2, "within_tolerance": bool(rms <= 2e-2 and abs(loss - first["loss"]) <= 2e-2 * abs(first["loss"]))}
 
 
 # ---- our arm ---------------------------------------------------------------------------
@@ -324,6 +362,7 @@ def run_cuda(args):
         tps, info = cpu_sample(4, 1)   # about 10-25 s of host time
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": info["cores"],
                                 "kind": info["kind"], "sample": info["sample"]}
+        line["parity"] = gpu_vs_cpu_first_step(info["first"], local_rank, not args.no_graphs)
     emit(line)
     if world > 1:
         dist.destroy_process_group()

@@ -5,7 +5,7 @@
  * chosen by `CreateBackend` (reference: runtime/executor/backend.cc:26-60).
  * Each entry point below is the C spelling of one member of that seam, so a
  * maintainer's `CudaBackend : ExecutorBackend` adapter is one forwarding line
- * per method; INTEGRATION.md shows it.  Plain pointers and sizes only.
+ * per method.  Plain pointers and sizes only.
  *
  * Every function returns 0 on success and a nonzero code on failure;
  * see_cuda_last_error(h) then holds a one-line "<unit>: <message>" diagnostic.
@@ -99,6 +99,15 @@ int see_cuda_set_epilogue_fusion(see_cuda_backend* h, int enabled);
  * copies (device memory, copy r at gathered + r * block_bytes) times 1/ranks. */
 int see_cuda_set_gradient_gather(see_cuda_backend* h, int ranks, const void* gathered_device,
                                  uint64_t block_offset, uint64_t block_bytes);
+/* Symmetric per-column int8 quantisation of a frozen weight W [K, N] on the
+ * device, with the compiler's own arithmetic, so a weight patched by a
+ * committed update can be re-packed where it lies: scale[n] = max_k |w[k,n]| /
+ * 127 (an all-zero column takes 1; never below FLT_MIN), level = round half
+ * away from zero of w / scale, clamped to +-127 (reference:
+ * compiler/backend/allocation/arena_binder.cc:129-190).  All three are DEVICE
+ * pointers; levels [K, N] int8, scales [N] f32; bit-identical to the reference. */
+int see_cuda_quantize_columns(see_cuda_backend* h, const float* w, uint64_t K, uint64_t N,
+                              int8_t* levels, float* scales);
 /* Profile mode: CUDA-event pairs around every instruction (the profiler hook,
  * reference: runtime/profiler/kernel_profile.h:25-72).  take_profile fills up
  * to `capacity` records and returns the count. */
@@ -124,7 +133,8 @@ int64_t see_cuda_take_profile(see_cuda_backend* h, see_profile_record* out, uint
  * refused with SEE_ERROR.  logits [rows, classes], labels [rows] (i32), loss [1]
  * and probs [rows, classes] are DEVICE pointers; the work is enqueued on
  * `cuda_stream`.  The first call on a device looks up the array's address — make
- * it before any stream capture.  All calls share the array: calls that can
+ * it before any stream capture (and one first call per row-width class: rows of
+ * 4096..32768 classes use a kernel whose first launch configures it).  All calls share the array: calls that can
  * overlap on the GPU race.  masked != 0 selects the form that ignores labels of -1. */
 int see_cuda_xent_forward_static(const float* logits, const int32_t* labels, float* loss,
                                  float* probs, uint64_t rows, uint64_t classes, int masked,
@@ -173,6 +183,23 @@ int see_engine_read_loss(see_engine* h, float* loss);
 /* Evaluate one staged batch: eval program, loss, and the accuracy tally
  * (rows judged, argmax hits; reference: update_engine.cc:432-580) on device. */
 int see_engine_evaluate(see_engine* h, float* loss, uint64_t* rows, uint64_t* correct);
+/* The same with the batch's first `real_rows` rows as its real rows — a
+ * validation set's last batch wraps, and its duplicate rows count neither for
+ * accuracy nor for the loss (reference: update_engine.cc:486-564).  Also
+ * returns the real-row loss: the row-order double sum of each real row's loss
+ * and the number of rows it is over (under a masked loss: the real TARGET
+ * rows), computed on the device from the loss instruction's own operands
+ * (reference: update_engine.cc:977-1026; runtime/executor/loss.cc:78-105).
+ * The integer tallies equal the reference's host scan. */
+typedef struct see_eval_result {
+  float loss;            /* the eval program's loss slot (mean over the whole batch) */
+  uint32_t has_accuracy; /* class labels + a softmax covering the batch */
+  uint64_t rows;         /* rows judged for accuracy */
+  uint64_t correct;      /* argmax == label among them; the first maximum wins */
+  double real_row_loss;  /* sum of per-row losses over the real rows */
+  uint64_t loss_rows;    /* rows that sum is over */
+} see_eval_result;
+int see_engine_evaluate_rows(see_engine* h, uint64_t real_rows, see_eval_result* out);
 /* RunMerge + the finiteness scan of every delta — reference: update_engine.cc:1028-1063. */
 int see_engine_run_merge(see_engine* h, int* all_finite);
 /* Arena access for checkpoints, gate snapshots and commit (reference:
@@ -198,7 +225,7 @@ int see_engine_gradient_block(see_engine* h, uint64_t* offset, uint64_t* bytes);
 
 /* Checkpoint / gate snapshot of the persistent prefix (adapters + optimizer moments) without stalling
  * training; replaces the host copies the reference engine makes of the persistent segment for its gate and
- * checkpoints (reference: runtime/dispatcher/gate.h:20-49, runtime/dispatcher/update_engine.cc:535-564).
+ * checkpoints (reference: runtime/gating/gate.h:20-49, runtime/storage/checkpoint.h, runtime/dispatcher/update_engine.cc:763).
  * `begin` takes the copy at the current point of the step sequence (device to device on the compute stream)
  * and downloads it on a second stream while later steps run; `wait` blocks until it is on the host and
  * copies it to dst (bytes must equal the header's persistent_size).  `restore` is the resume path: the

@@ -32,6 +32,7 @@ EXPORTED_SYMBOLS = [
     "see_cuda_set_gradient_gather",
     "see_cuda_set_profiling", "see_cuda_take_profile",
     "see_cuda_xent_forward_static", "see_cuda_static_max_rows", "see_cuda_static_last_error",
+    "see_cuda_quantize_columns",
 ]
 
 
@@ -102,6 +103,7 @@ def load_library() -> ctypes.CDLL:
     lib.see_cuda_set_profiling.argtypes = [vp, i32]
     lib.see_cuda_take_profile.argtypes = [vp, ctypes.POINTER(ProfileRecord), u64]
     lib.see_cuda_take_profile.restype = ctypes.c_int64
+    lib.see_cuda_quantize_columns.argtypes = [vp, vp, u64, u64, vp, vp]
     lib.see_cuda_xent_forward_static.argtypes = [vp, vp, vp, vp, u64, u64, i32, vp]
     lib.see_cuda_static_max_rows.restype = u64
     lib.see_cuda_static_last_error.restype = ctypes.c_char_p
@@ -244,6 +246,11 @@ class CudaBackend:
                             block_bytes: int):
         self._check(self.lib.see_cuda_set_gradient_gather(
             self.h, ranks, ctypes.c_void_p(gathered_ptr), block_offset, block_bytes))
+
+    def quantize_columns(self, w_ptr: int, K: int, N: int, levels_ptr: int, scales_ptr: int):
+        """Per-column int8 quantisation of W [K, N] over DEVICE pointers."""
+        self._check(self.lib.see_cuda_quantize_columns(self.h, ctypes.c_void_p(w_ptr), K, N,
+                                                       ctypes.c_void_p(levels_ptr), ctypes.c_void_p(scales_ptr)))
 
     def set_profiling(self, on: bool):
         self._check(self.lib.see_cuda_set_profiling(self.h, int(on)))

@@ -114,6 +114,12 @@ int see_cuda_end_range(see_cuda_backend* h) {
   return SEE_OK;
 }
 
+int see_cuda_quantize_columns(see_cuda_backend* h, const float* w, uint64_t K, uint64_t N,
+                              int8_t* levels, float* scales) {
+  auto r = h->backend->QuantizeColumns(w, K, N, levels, scales);
+  return r ? SEE_OK : Fail(h, r.error());
+}
+
 int see_cuda_flush(see_cuda_backend* h) {
   auto r = h->backend->Flush();
   return r ? SEE_OK : Fail(h, r.error());
@@ -253,6 +259,19 @@ int see_engine_evaluate(see_engine* h, float* loss, uint64_t* rows, uint64_t* co
   if (loss) *loss = r.loss;
   if (rows) *rows = r.rows;
   if (correct) *correct = r.correct;
+  return SEE_OK;
+}
+int see_engine_evaluate_rows(see_engine* h, uint64_t real_rows, see_eval_result* out) {
+  see::EvalResult r;
+  if (auto s = h->engine->Evaluate(&r, real_rows); !s) return Fail(h, s.error());
+  if (out) {
+    out->loss = r.loss;
+    out->has_accuracy = r.has_accuracy ? 1u : 0u;
+    out->rows = r.rows;
+    out->correct = r.correct;
+    out->real_row_loss = r.real_row_loss;
+    out->loss_rows = r.loss_rows;
+  }
   return SEE_OK;
 }
 int see_engine_run_merge(see_engine* h, int* all_finite) {

@@ -84,6 +84,9 @@ Status CudaBackend::Init() {
   if (auto r = Check(cudaMallocHost(reinterpret_cast<void**>(&h_status_), 64), "pinned status"); !r)
     return r;
   std::memset(h_status_, 0, 64);
+  scalar_done_.assign(kScalarSlots, nullptr);
+  for (auto& ev : scalar_done_)
+    if (auto r = Check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "scalar events"); !r) return r;
   umma_ = std::make_unique<UmmaState>();
   if (std::string e = umma::Init(&umma_->ctx, device_, d_status_); !e.empty()) return std::unexpected(e);
   return {};
@@ -94,6 +97,7 @@ CudaBackend::~CudaBackend() {
   if (stream_) cudaStreamSynchronize(stream_);
   for (auto& ev : events_) { cudaEventDestroy(ev.first); cudaEventDestroy(ev.second); }
   for (auto& ev : kernel_events_) { cudaEventDestroy(ev.first); cudaEventDestroy(ev.second); }
+  for (auto& ev : scalar_done_) if (ev) cudaEventDestroy(ev);
   if (umma_) umma::Destroy(&umma_->ctx);
   cudaFree(d_arena_);
   cudaFree(d_rodata_);
@@ -101,6 +105,7 @@ CudaBackend::~CudaBackend() {
   cudaFree(d_status_);  // base of the scratch block
   cudaFree(d_rows_);
   cudaFree(d_gsum_);
+  cudaFree(d_colmax_);
   cudaFree(d_split_);
   cudaFree(d_adam_table_);
   if (h_scalars_) cudaFreeHost(h_scalars_);
@@ -229,6 +234,9 @@ Status CudaBackend::BindSource(const uint8_t* data, uint64_t bytes) {
   cudaFree(d_source_);
   d_source_ = nullptr;
   source_bytes_ = 0;
+  // Every bf16 weight copy made from the old source model is stale now (they are
+  // keyed by offset, and a second model has the same offsets).
+  umma::InvalidateAll(&umma_->ctx);
   if (!data || bytes == 0) return {};
   void* p = nullptr;
   if (auto r = Check(cudaMalloc(&p, bytes), "bind source"); !r) return r;
@@ -277,6 +285,25 @@ void CudaBackend::SetGradientGather(int ranks, const void* gathered, uint64_t bl
   d_gathered_ = ranks > 1 ? static_cast<const uint8_t*>(gathered) : nullptr;
   gather_off_ = block_off;
   gather_bytes_ = block_bytes;
+  fold_gather_ = gather_folded_ = false;
+}
+
+Status CudaBackend::QuantizeColumns(const float* w, uint64_t K, uint64_t N, int8_t* levels, float* scales) {
+  if (!w || !levels || !scales || K == 0 || N == 0) return std::unexpected("cuda: quantize: empty operand");
+  cudaSetDevice(device_);
+  if (N > colmax_capacity_) {
+    cudaStreamSynchronize(stream_);
+    cudaFree(d_colmax_);
+    d_colmax_ = nullptr;
+    colmax_capacity_ = 0;
+    void* p = nullptr;
+    if (auto r = Check(cudaMalloc(&p, N * sizeof(unsigned int)), "quantize scratch"); !r) return r;
+    d_colmax_ = static_cast<unsigned int*>(p);
+    colmax_capacity_ = N;
+  }
+  k::QuantizeColumns(w, K, N, levels, scales, d_colmax_, stream_);
+  counters_.kernel_launches += 3;
+  return Check(cudaPeekAtLastError(), "quantize");
 }
 
 void CudaBackend::SetProfiling(bool on) { profiling_ = on; }
@@ -318,6 +345,24 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
   // Size every scratch buffer the range needs up front, so no allocation (and
   // no stream drain) happens between its instructions.
   uint64_t rows = 0, gsum = 0, split = 0;
+  fold_gather_ = gather_folded_ = false;
+  range_error_.clear();
+  if (gather_ranks_ > 1) {
+    bool clip = false;
+    for (size_t i = begin; i < end && i < program.size(); ++i) {
+      const uint16_t op = program[i].opcode;
+      clip = clip || op == kClipNorm || op == kSqNormAccum || op == kClipGlobal;
+    }
+    if (clip) {
+      fold_gather_ = true;
+      // The optimizer steps that consume the clipped gradient must be in this
+      // range too: a later range would go back to the gathered, unclipped copies.
+      for (size_t i = std::min(end, program.size()); i < program.size(); ++i)
+        if (program[i].opcode == kAdamWStep || program[i].opcode == kSgdStep)
+          range_error_ = "cuda: data parallel: a range with a standalone clip instruction must also hold "
+                         "the optimizer steps that follow it";
+    }
+  }
   for (size_t i = begin; i < end && i < program.size(); ++i) {
     const Instruction& ins = program[i];
     switch (ins.opcode) {
@@ -330,7 +375,7 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
       case kKLDistillFwd: rows = std::max(rows, Hi32(ins.out[1])); break;
       case kMseFwd: rows = std::max<uint64_t>(rows, 256); break;
       case kAdamWStep: case kSgdStep:
-        if (gather_ranks_ > 1 && BitsToF32(ins.out[1]) > 0.0f) gsum = std::max(gsum, ins.out[0]);
+        if (gather_ranks_ > 1 && !fold_gather_ && BitsToF32(ins.out[1]) > 0.0f) gsum = std::max(gsum, ins.out[0]);
         break;
       default: break;
     }
@@ -370,6 +415,8 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
 }
 
 void CudaBackend::EndRange() {
+  fold_gather_ = gather_folded_ = false;
+  range_error_.clear();
   bias_fusion_.clear();
   skip_next_add_bias_ = false;
   act_fusion_.clear();
@@ -416,7 +463,7 @@ void CudaBackend::PlanAdamGroups(std::span<const Instruction> program, size_t be
       e.n = ins.out[0];
       e.g_copies = 1;
       const uint64_t g_off = RefOffset(ins.in[1]);
-      if (gather_ranks_ > 1 && RefSpace(ins.in[1]) == kArena && g_off >= gather_off_ &&
+      if (gather_ranks_ > 1 && !fold_gather_ && RefSpace(ins.in[1]) == kArena && g_off >= gather_off_ &&
           g_off + e.n * 4 <= gather_off_ + gather_bytes_) {
         e.g = reinterpret_cast<const float*>(d_gathered_ + (g_off - gather_off_));
         e.g_copies = gather_ranks_;
@@ -994,8 +1041,13 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   if (std::string e = DescribeInstruction(ins, arena_bytes_, rodata_bytes_, source_bytes_, &ext);
       !e.empty())
     return std::unexpected("cuda: " + e);
+  if (!range_error_.empty()) return std::unexpected(range_error_);
   if (!host_dirty_.empty())
     if (auto r = UploadDirty(); !r) return r;
+  if (fold_gather_ && !gather_folded_ &&
+      (ins.opcode == kClipNorm || ins.opcode == kSqNormAccum || ins.opcode == kClipGlobal ||
+       ins.opcode == kAdamWStep || ins.opcode == kSgdStep))
+    if (auto r = FoldGatheredIntoArena(); !r) return r;
 
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   if (profiling_) {
@@ -1165,7 +1217,8 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
     int launches = 0;
     const std::string err = umma::TryGemm(&umma_->ctx, a, RefSpace(ins.in[1]) == kRodata ? 1 : 2,
                                           RefOffset(ins.in[1]), RefOffset(ins.in[0]),
-                                          a.a_k_scale ? RefOffset(ins.in[3]) : ~0ull, stream_,
+                                          a.a_k_scale ? ins.in[3] : ~0ull,   // the whole ref: its address space is part of the key
+                                          stream_,
                                           &launches);
     if (err.empty() && launches > 0) {
       ++counters_.relaxed_executions;
@@ -1234,14 +1287,38 @@ k::AdamScalars CudaBackend::ScalarsOf(const StepParams& params) {
   return sc;
 }
 
-void CudaBackend::SetCapturing(bool on) {
-  capturing_ = on;
-  scalars_valid_ = false;  // the first optimizer instruction re-uploads (into the graph)
+void CudaBackend::SetCapturing(bool on) { capturing_ = on; }
+
+Status CudaBackend::UploadStepScalars(const StepParams& params) {
+  cudaSetDevice(device_);
+  scalar_slot_ = (scalar_slot_ + 1) % kScalarSlots;
+  // The slot's previous upload may still be queued behind device work when the
+  // host runs many steps ahead: its bytes must not change until that copy ran.
+  if (auto r = Check(cudaEventSynchronize(scalar_done_[scalar_slot_]), "step scalars: slot"); !r) return r;
+  h_scalars_[scalar_slot_] = ScalarsOf(params);
+  if (auto r = Check(cudaMemcpyAsync(d_scalars_, &h_scalars_[scalar_slot_], sizeof(k::AdamScalars),
+                                     cudaMemcpyHostToDevice, stream_), "step scalars"); !r)
+    return r;
+  if (auto r = Check(cudaEventRecord(scalar_done_[scalar_slot_], stream_), "step scalars: event"); !r) return r;
+  last_params_ = params;
+  scalars_valid_ = true;
+  return {};
 }
 
-void CudaBackend::UpdateReplayScalars(const StepParams& params) {
-  h_scalars_[0] = ScalarsOf(params);
-  scalars_valid_ = false;
+// The rank-ordered mean of the gathered gradient copies, written over this
+// rank's own block in the arena (what a host-side exchange leaves there), for
+// ranges whose clip instructions work on the arena in place.
+Status CudaBackend::FoldGatheredIntoArena() {
+  if (!d_gathered_ || gather_bytes_ == 0 || gather_off_ + gather_bytes_ > arena_bytes_)
+    return std::unexpected("cuda: data parallel: the gathered gradient block is not set");
+  const size_t n = gather_bytes_ / 4;
+  k::SumCopies(reinterpret_cast<const float*>(d_gathered_), reinterpret_cast<float*>(d_arena_ + gather_off_), n,
+               gather_ranks_, n, 1.0f / static_cast<float>(gather_ranks_), stream_);
+  ++counters_.kernel_launches;
+  umma::InvalidateRange(&umma_->ctx, gather_off_, gather_bytes_);
+  if (coherence_ == Coherence::kStrict) MergeExtent(&device_dirty_, gather_off_, gather_bytes_);
+  gather_folded_ = true;
+  return {};
 }
 
 Status CudaBackend::DispatchOptimizer(const Instruction& ins, const StepParams& params) {
@@ -1249,24 +1326,19 @@ Status CudaBackend::DispatchOptimizer(const Instruction& ins, const StepParams& 
   // computes them (reference: runtime/executor/optimizer.cc:113-118), uploaded
   // once per distinct StepParams.
   if (!scalars_valid_ || std::memcmp(&params, &last_params_, sizeof(StepParams)) != 0) {
-    const k::AdamScalars sc = ScalarsOf(params);
-    // Slot 0 is the replay slot: a copy captured into a CUDA graph reads it at
-    // every replay, after UpdateReplayScalars rewrote it.  Eager uploads rotate
-    // through the other slots so a pending copy is never overwritten.
-    scalar_slot_ = capturing_ ? 0 : 1 + (scalar_slot_ % (kScalarSlots - 1));
-    h_scalars_[scalar_slot_] = sc;
-    if (auto r = Check(cudaMemcpyAsync(d_scalars_, &h_scalars_[scalar_slot_], sizeof(sc),
-                                       cudaMemcpyHostToDevice, stream_), "step scalars"); !r)
-      return r;
-    last_params_ = params;
-    scalars_valid_ = true;
+    // A range being captured must not contain the upload (a replay would re-read
+    // the pinned slot with whatever the host has put there since).
+    if (capturing_)
+      return std::unexpected("cuda: step scalars must be uploaded before a range is captured");
+    if (auto r = UploadStepScalars(params); !r) return r;
   }
   if (range_index_ < adam_group_of_.size() && adam_group_of_[range_index_] != -1) {
     const int32_t gi = adam_group_of_[range_index_];
     if (gi == -2) return {};   // done by the run's first instruction
     const AdamGroup& grp = adam_groups_[gi];
     k::AdamWStepMulti(d_adam_table_ + grp.table_begin, grp.count, grp.max_n, d_scalars_, d_status_,
-                      gather_ranks_ > 1 ? 1.0f / static_cast<float>(gather_ranks_) : 1.0f, stream_);
+                      gather_ranks_ > 1 && !fold_gather_ ? 1.0f / static_cast<float>(gather_ranks_) : 1.0f,
+                      stream_);
     ++counters_.kernel_launches;
     return {};
   }
@@ -1277,7 +1349,7 @@ Status CudaBackend::DispatchOptimizer(const Instruction& ins, const StepParams& 
   int copies = 1;
   size_t cstride = 0;
   float inv = 1.0f;
-  if (gather_ranks_ > 1 && RefSpace(ins.in[1]) == kArena && g_off >= gather_off_ &&
+  if (gather_ranks_ > 1 && !fold_gather_ && RefSpace(ins.in[1]) == kArena && g_off >= gather_off_ &&
       g_off + n * 4 <= gather_off_ + gather_bytes_) {
     g = reinterpret_cast<const float*>(d_gathered_ + (g_off - gather_off_));
     copies = gather_ranks_;

@@ -139,13 +139,20 @@ class CudaBackend {
   // effect at the next BeginRange).
   void SetEpilogueFusion(bool enabled) { epilogue_fusion_ = enabled; }
 
-  // CUDA-graph support for the engine.  While capturing, the per-range scalar
-  // upload is recorded from a fixed pinned slot; before each replay the engine
-  // rewrites that slot with the step's scalars (UpdateReplayScalars), so the
-  // captured copy delivers the current learning rate and bias corrections.
+  // CUDA-graph support for the engine.  The optimizer kernels read the step's
+  // learning rate and bias corrections from a small device block.  A captured
+  // range contains no upload of that block: before it captures or replays a range
+  // with optimizer instructions the engine calls UploadStepScalars, an ordinary
+  // stream-ordered copy from a ring of pinned slots (a slot is rewritten only
+  // after the copy that last read it has completed), so every replay sees its own
+  // step's values however far the host runs ahead of the device.
   void SetCapturing(bool on);
-  void UpdateReplayScalars(const StepParams& params);
+  Status UploadStepScalars(const StepParams& params);
   static k::AdamScalars ScalarsOf(const StepParams& params);
+
+  // Per-column int8 quantisation of W [K, N] (device pointers), the compiler's
+  // arithmetic bit for bit (reference: compiler/backend/allocation/arena_binder.cc:129-190).
+  Status QuantizeColumns(const float* w, uint64_t K, uint64_t N, int8_t* levels, float* scales);
 
   // Profile mode: every instruction is bracketed by CUDA events on the stream.
   void SetProfiling(bool on);
@@ -197,10 +204,13 @@ class CudaBackend {
   uint64_t rows_capacity_ = 0;
   float* d_split_ = nullptr;      // split-K partial sums of the adapter-gradient GEMMs
   uint64_t split_capacity_ = 0;   // floats
+  unsigned int* d_colmax_ = nullptr;   // the quantiser's per-column maxima
+  uint64_t colmax_capacity_ = 0;
   float* d_gsum_ = nullptr;       // summed gradient for fused clips under data parallelism
   uint64_t gsum_capacity_ = 0;
   k::AdamScalars* d_scalars_ = nullptr;
   k::AdamScalars* h_scalars_ = nullptr;  // pinned ring
+  std::vector<cudaEvent_t> scalar_done_; // per slot: the upload that last read it
   int scalar_slot_ = 0;
   StepParams last_params_{};
   bool scalars_valid_ = false;
@@ -215,6 +225,15 @@ class CudaBackend {
   int gather_ranks_ = 1;
   const uint8_t* d_gathered_ = nullptr;
   uint64_t gather_off_ = 0, gather_bytes_ = 0;
+  // A range with a standalone clip instruction (kClipNorm / kSqNormAccum /
+  // kClipGlobal) reads and scales the gradient where it lies in the arena, so
+  // under data parallelism the rank-ordered mean of the gathered copies is
+  // written into the arena block once, at the range's first optimizer-phase
+  // instruction, and every instruction after it uses the arena.
+  bool fold_gather_ = false;    // this range needs the fold
+  bool gather_folded_ = false;  // ... and it has been done
+  std::string range_error_;     // a range BeginRange found it cannot run; reported by Execute
+  Status FoldGatheredIntoArena();
 
   bool relaxed_allowed_ = true;
   bool epilogue_fusion_ = true;

@@ -89,6 +89,9 @@ std::expected<std::unique_ptr<UpdateEngine>, std::string> UpdateEngine::Create(i
   if (cudaMalloc(&p, 4 * sizeof(unsigned long long)) != cudaSuccess)
     return std::unexpected("cuda: tally allocation failed");
   e->d_tally_ = static_cast<unsigned long long*>(p);
+  if (cudaMalloc(&p, 2 * sizeof(double)) != cudaSuccess)
+    return std::unexpected("cuda: eval scratch allocation failed");
+  e->d_eval_out_ = static_cast<double*>(p);
   return e;
 }
 
@@ -107,6 +110,8 @@ UpdateEngine::~UpdateEngine() {
   for (auto& ev : staged_) if (ev) cudaEventDestroy(ev);
   if (pinned_) cudaFreeHost(pinned_);
   cudaFree(d_tally_);
+  cudaFree(d_eval_out_);
+  cudaFree(d_eval_terms_);
   if (copy_stream_) {
     cudaStreamSynchronize(copy_stream_);
     cudaStreamDestroy(copy_stream_);
@@ -217,13 +222,37 @@ Status UpdateEngine::LoadFromMemory(const uint8_t* plan, uint64_t size) {
   step_ = 0;
   horizon_ = h.default_steps;
   eval_probs_ref_ = eval_labels_ref_ = kNullRef;
-  for (const Instruction& ins : eval_)
+  eval_tail_ = EvalTail{};
+  uint64_t terms = 0;
+  for (const Instruction& ins : eval_) {
     if (ins.opcode == kSoftmaxXEntFwd || ins.opcode == kSoftmaxXEntMaskedFwd) {
       eval_probs_ref_ = ins.in[3];
       eval_labels_ref_ = ins.in[1];
       eval_rows_ = ins.out[0];
       eval_cols_ = ins.out[1];
+      // Row-separable only when it is the instruction that writes the plan's loss
+      // slot over exactly one batch of rows.
+      if (ins.in[2] == h.loss_ref && ins.out[0] == h.batch) {
+        eval_tail_ = {ins.opcode == kSoftmaxXEntFwd ? EvalTail::kXent : EvalTail::kXentMasked, ins.in[3],
+                      ins.in[1], ins.out[1]};
+        terms = std::max<uint64_t>(terms, h.batch);
+      }
+    } else if (ins.opcode == kMseFwd && ins.in[2] == h.loss_ref && h.batch > 0 && ins.out[0] % h.batch == 0) {
+      eval_tail_ = {EvalTail::kMse, ins.in[0], ins.in[1], ins.out[0] / h.batch};
+      terms = std::max<uint64_t>(terms, ins.out[0]);
     }
+  }
+  if (terms > eval_terms_capacity_) {
+    cudaStreamSynchronize(backend_->stream());
+    cudaFree(d_eval_terms_);
+    d_eval_terms_ = nullptr;
+    eval_terms_capacity_ = 0;
+    void* p = nullptr;
+    if (cudaMalloc(&p, terms * sizeof(double)) != cudaSuccess)
+      return std::unexpected("engine: eval scratch allocation failed");
+    d_eval_terms_ = static_cast<double*>(p);
+    eval_terms_capacity_ = terms;
+  }
   const uint64_t stage = (h.input_ref == kNullRef ? 0 : h.input_floats * 4) +
                          (h.label_ref == kNullRef ? 0 : h.label_bytes);
   if (stage > pinned_bytes_) {
@@ -241,22 +270,30 @@ Status UpdateEngine::LoadFromMemory(const uint8_t* plan, uint64_t size) {
 }
 
 Status UpdateEngine::BindSourceModel(const uint8_t* data, uint64_t bytes) {
+  // Captured ranges hold the old source model's device addresses.
+  if (backend_) cudaStreamSynchronize(backend_->stream());
+  DropGraphs();
   return backend_->BindSource(data, bytes);
 }
 
-// reference: runtime/dispatcher/update_engine.cc:370-391
+// The scheduled learning rate of the current timestep, in f32 with the host's
+// cosf, operation for operation as the reference engine computes it (reference:
+// runtime/dispatcher/update_engine.cc:370-391): schedule 1 is a linear ramp over
+// the plan's warm-up steps, then half a cosine from the plan's rate down to
+// rate * min_lr_factor over the rest of the RUN's length, and that floor beyond.
 float UpdateEngine::EffectiveLr() const {
-  const float base = header_.lr;
-  if (header_.lr_schedule != 1) return base;
-  if (header_.warmup_steps > 0 && step_ <= header_.warmup_steps)
-    return base * static_cast<float>(step_) / static_cast<float>(header_.warmup_steps);
-  const uint64_t run = horizon_;
-  const uint64_t horizon = run > header_.warmup_steps ? run - header_.warmup_steps : 0;
-  const float floor = base * header_.min_lr_factor;
-  if (horizon == 0 || step_ - header_.warmup_steps >= horizon) return floor;
-  const float t = static_cast<float>(step_ - header_.warmup_steps) / static_cast<float>(horizon);
-  constexpr float kPi = 3.14159265358979323846f;
-  return floor + (base - floor) * 0.5f * (1.0f + std::cos(kPi * t));
+  const float peak = header_.lr;
+  constexpr uint32_t kCosineWithWarmup = 1;
+  if (header_.lr_schedule != kCosineWithWarmup) return peak;
+  const uint64_t warm = header_.warmup_steps;
+  if (warm > 0 && step_ <= warm) return peak * static_cast<float>(step_) / static_cast<float>(warm);
+  const float lowest = peak * header_.min_lr_factor;
+  const uint64_t decay_steps = horizon_ > warm ? horizon_ - warm : 0;
+  const uint64_t into_decay = step_ - warm;
+  if (decay_steps == 0 || into_decay >= decay_steps) return lowest;
+  const float progress = static_cast<float>(into_decay) / static_cast<float>(decay_steps);
+  const float pi = 3.14159265358979323846f;
+  return lowest + (peak - lowest) * 0.5f * (1.0f + std::cos(pi * progress));
 }
 
 StepParams UpdateEngine::MakeParams() const {
@@ -300,8 +337,11 @@ Status UpdateEngine::RunRange(const std::vector<Instruction>& prog, size_t begin
   if (phase_ms) cudaEventRecord(ev_[0], s);
   const std::span<const Instruction> span(prog.data(), prog.size());
   Status result{};
+  bool has_opt = false;
+  for (size_t i = begin; i < end; ++i) has_opt = has_opt || prog[i].opcode == kAdamWStep || prog[i].opcode == kSgdStep;
   if (use_graphs_ && slot && slot->exec) {
-    backend_->UpdateReplayScalars(params);
+    if (has_opt)
+      if (auto r = backend_->UploadStepScalars(params); !r) return r;
     if (auto e = cudaGraphLaunch(slot->exec, s); e != cudaSuccess)
       return std::unexpected(std::string("engine: graph launch: ") + cudaGetErrorString(e));
   } else {
@@ -309,6 +349,8 @@ Status UpdateEngine::RunRange(const std::vector<Instruction>& prog, size_t begin
     const bool capture = use_graphs_ && slot && slot->runs >= 1;
     cudaGraph_t graph = nullptr;
     if (capture) {
+      if (has_opt)
+        if (auto r = backend_->UploadStepScalars(params); !r) { backend_->EndRange(); return r; }
       backend_->SetCapturing(true);
       if (auto e = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal); e != cudaSuccess) {
         backend_->SetCapturing(false);
@@ -332,7 +374,6 @@ Status UpdateEngine::RunRange(const std::vector<Instruction>& prog, size_t begin
           result = std::unexpected(std::string("engine: graph instantiate: ") + cudaGetErrorString(ie));
         } else {
           slot->exec = exec;
-          backend_->UpdateReplayScalars(params);
           if (auto le = cudaGraphLaunch(exec, s); le != cudaSuccess)
             result = std::unexpected(std::string("engine: graph launch: ") + cudaGetErrorString(le));
         }
@@ -397,21 +438,55 @@ Status UpdateEngine::ReadLoss(float* loss) {
   return backend_->Flush();  // surfaces a refusal raised on the device
 }
 
-Status UpdateEngine::Evaluate(EvalResult* out) {
+Status UpdateEngine::Evaluate(EvalResult* out, uint64_t real_rows) {
+  if (!loaded_) return std::unexpected("engine: no plan is loaded");
+  if (eval_.empty()) return std::unexpected("engine: the plan carries no eval program");
   if (auto r = RunRange(eval_, 0, eval_.size(), &g_eval_, nullptr); !r) return r;
+  const uint64_t real = std::min<uint64_t>(real_rows, header_.batch);
   cudaStream_t s = backend_->stream();
   cudaMemsetAsync(d_tally_, 0, 4 * sizeof(unsigned long long), s);
-  if (eval_probs_ref_ != kNullRef) {
-    const float* probs = reinterpret_cast<const float*>(backend_->device_arena() + RefOffset(eval_probs_ref_));
-    const int32_t* labels = reinterpret_cast<const int32_t*>(backend_->device_arena() + RefOffset(eval_labels_ref_));
-    k::ArgmaxTally(probs, labels, eval_rows_, eval_cols_, d_tally_, s);
+  cudaMemsetAsync(d_eval_out_, 0, 2 * sizeof(double), s);
+  auto at = [&](uint64_t ref) { return backend_->device_arena() + RefOffset(ref); };
+  // Accuracy needs class labels in the label slot and a softmax whose rows cover
+  // the batch (reference: update_engine.cc:458-466); real rows only, each once.
+  const bool track_accuracy = header_.label_kind == 1 && header_.label_ref != kNullRef &&
+                              eval_probs_ref_ != kNullRef && eval_cols_ > 0 && eval_rows_ >= header_.batch;
+  const int32_t* label_slot = header_.label_ref == kNullRef
+                                  ? nullptr : reinterpret_cast<const int32_t*>(at(header_.label_ref));
+  if (track_accuracy)
+    k::ArgmaxTally(reinterpret_cast<const float*>(at(eval_probs_ref_)), label_slot, real, eval_cols_, d_tally_, s);
+  bool row_loss = true;
+  switch (eval_tail_.kind) {
+    case EvalTail::kXent: case EvalTail::kXentMasked:
+      if (!label_slot) return std::unexpected("engine: a cross-entropy eval tail needs the label slot");
+      k::XentRealRowLoss(reinterpret_cast<const float*>(at(eval_tail_.a)), label_slot, real, eval_tail_.width,
+                         d_eval_terms_, d_eval_out_, d_tally_, s);
+      break;
+    case EvalTail::kMse:
+      k::MseRealRowLoss(reinterpret_cast<const float*>(at(eval_tail_.a)),
+                        reinterpret_cast<const float*>(at(eval_tail_.b)), real, eval_tail_.width, d_eval_terms_,
+                        d_eval_out_, d_tally_, s);
+      break;
+    case EvalTail::kWeighted: row_loss = false; break;
   }
   unsigned long long tally[4] = {0, 0, 0, 0};
+  double sums[2] = {0, 0};
   if (auto e = cudaMemcpyAsync(tally, d_tally_, sizeof(tally), cudaMemcpyDeviceToHost, s); e != cudaSuccess)
     return std::unexpected(std::string("engine: tally read: ") + cudaGetErrorString(e));
-  if (auto r = ReadLoss(&out->loss); !r) return r;
+  if (auto e = cudaMemcpyAsync(sums, d_eval_out_, sizeof(sums), cudaMemcpyDeviceToHost, s); e != cudaSuccess)
+    return std::unexpected(std::string("engine: row-loss read: ") + cudaGetErrorString(e));
+  if (auto r = ReadLoss(&out->loss); !r) return r;   // synchronises the stream
   out->rows = tally[0];
   out->correct = tally[1];
+  out->has_accuracy = track_accuracy;
+  if (row_loss) {
+    out->real_row_loss = sums[0];
+    out->loss_rows = eval_tail_.kind == EvalTail::kMse ? real : tally[3];
+  } else {
+    // A composite loss keeps no per-row values: the batch mean stands for each real row.
+    out->real_row_loss = static_cast<double>(out->loss) * static_cast<double>(real);
+    out->loss_rows = real;
+  }
   return {};
 }
 

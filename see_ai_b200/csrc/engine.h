@@ -39,9 +39,23 @@ struct StepTimings {   // milliseconds on the device, by CUDA events
 };
 
 struct EvalResult {
-  float loss = 0;
-  uint64_t rows = 0;      // loss-target rows scored
+  float loss = 0;         // the eval program's own loss: the mean over the whole fixed-shape batch
+  uint64_t rows = 0;      // rows judged for accuracy: real rows whose label is >= 0
   uint64_t correct = 0;   // argmax == label among them (first maximum wins)
+  // The batch's loss over its real rows alone (a validation set's last batch
+  // wraps; a masked plan is always scored over its target rows): the row-order
+  // double sum of the per-row losses and the number of rows it is over
+  // (reference: runtime/dispatcher/update_engine.cc:977-1026).
+  double real_row_loss = 0;
+  uint64_t loss_rows = 0;
+  bool has_accuracy = false;
+};
+
+// What the eval program's loss instruction lets the engine recompute per row
+// (reference: runtime/loader/plan_loader.cc:165-181).
+struct EvalTail {
+  enum Kind { kWeighted = 0, kXent = 1, kXentMasked = 2, kMse = 3 } kind = kWeighted;
+  uint64_t a = kNullRef, b = kNullRef, width = 0;
 };
 
 class UpdateEngine {
@@ -74,8 +88,10 @@ class UpdateEngine {
   Status TrainOptimizer();                     // [opt_begin, end)
   Status StepProgram();
   Status ReadLoss(float* loss);
-  // Evaluation: the eval program, the loss, and the accuracy tally on device.
-  Status Evaluate(EvalResult* out);
+  // Evaluation of the staged batch: the eval program, its loss, and on the
+  // device the accuracy tally and the real-row loss over the batch's first
+  // `real_rows` rows (the whole batch when real_rows >= the plan's batch).
+  Status Evaluate(EvalResult* out, uint64_t real_rows = ~0ull);
   // Merge: every adapter's delta, then a device-side finiteness scan.
   Status RunMerge(bool* all_finite);
 
@@ -85,8 +101,8 @@ class UpdateEngine {
   Status WritePersistent(const void* src);
 
   // Checkpoint / gate snapshot of the persistent prefix (adapters and optimizer
-  // moments) without stalling training (reference: runtime/dispatcher/gate.h:20-49
-  // keeps the best state; runtime/dispatcher/checkpoint.h saves it).
+  // moments) without stalling training (reference: runtime/gating/gate.h:20-49
+  // keeps the best state; runtime/storage/checkpoint.h saves it).
   // SnapshotBegin copies the prefix aside on the compute stream — a device-to-
   // device copy at the current point of the step sequence, so later steps may
   // overwrite the arena — and moves that copy to pinned host memory on a second
@@ -133,7 +149,11 @@ class UpdateEngine {
   cudaEvent_t staged_[2] = {nullptr, nullptr};
   cudaEvent_t ev_[4] = {nullptr, nullptr, nullptr, nullptr};
   StepTimings timings_;
-  unsigned long long* d_tally_ = nullptr;  // {rows, correct, nonfinite}
+  unsigned long long* d_tally_ = nullptr;  // {rows, correct, nonfinite, loss rows}
+  double* d_eval_out_ = nullptr;           // the real-row loss sum
+  double* d_eval_terms_ = nullptr;         // per-row (per-element) loss terms
+  uint64_t eval_terms_capacity_ = 0;
+  EvalTail eval_tail_;
   // snapshot path
   uint8_t* d_snap_ = nullptr;
   uint8_t* h_snap_ = nullptr;

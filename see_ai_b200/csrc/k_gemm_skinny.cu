@@ -9,6 +9,8 @@
 // (reference: runtime/executor/gemm.cc:73-187 quad order, :346-527 lane
 // order); compiled with -fmad=false.  Only the assignment of elements to
 // threads differs from the general tile kernels.
+#include <atomic>
+
 #include "gemm_exact_common.cuh"
 
 namespace see::k::exact {
@@ -213,15 +215,18 @@ bool LaunchReduceAs(const Params& p, cudaStream_t s) {
   constexpr int N = 4 * G;
   constexpr int kRowsPerBlock = R * (32 / G) * (kReduceThreads / 32);
   const size_t smem = (kLane ? N * (p.K + 16) + 16 : p.K * N) * sizeof(float);
-  static size_t configured = 0;   // per instantiation; raising the limit is idempotent
-  if (smem > configured) {
+  static std::atomic<bool> configured_on[64] = {};   // per instantiation and device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const bool tracked = dev >= 0 && dev < 64;
+  if (!tracked || !configured_on[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(ReduceKernel<G, kLane, R, Q, kReduceThreads>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(kReduceMaxK * N * sizeof(float) + 2048)) != cudaSuccess) {
       cudaGetLastError();
       return false;
     }
-    configured = kReduceMaxK * N * sizeof(float) + 2048;
+    if (tracked) configured_on[dev].store(true, std::memory_order_release);
   }
   const unsigned blocks = static_cast<unsigned>((p.M + kRowsPerBlock - 1) / kRowsPerBlock);
   ReduceKernel<G, kLane, R, Q, kReduceThreads><<<blocks, kReduceThreads, smem, s>>>(p);
@@ -381,14 +386,17 @@ __global__ void __launch_bounds__(StagedShape<G>::kThreads) ReduceStagedKernel(P
 template <int G, bool kLane>
 bool LaunchReduceStaged(const Params& p, cudaStream_t s) {
   const size_t smem = StagedSmemFloats<G, kLane>(p.K) * sizeof(float);
-  static bool configured = false;
-  if (!configured) {
+  static std::atomic<bool> configured_on[64] = {};   // per instantiation and device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const bool tracked = dev >= 0 && dev < 64;
+  if (!tracked || !configured_on[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(ReduceStagedKernel<G, kLane>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(kStagedMaxSmem)) != cudaSuccess) {
       cudaGetLastError();
       return false;
     }
-    configured = true;
+    if (tracked) configured_on[dev].store(true, std::memory_order_release);
   }
   constexpr int kRows = StagedShape<G>::kRows;
   const unsigned blocks = static_cast<unsigned>((p.M + kRows - 1) / kRows);

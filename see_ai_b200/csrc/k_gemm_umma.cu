@@ -19,9 +19,12 @@
 // memory and returns, and the host reports the condition at its next flush.
 #include <cuda.h>
 
+#include <atomic>
+
 #include "act_expr.cuh"
 #include "kernels.h"
 #include "shadow.cuh"
+#include "umma_device.cuh"
 #include "umma_kernel.h"
 
 namespace see::k {
@@ -38,93 +41,9 @@ constexpr uint32_t kBTileBytes = kBlockN * kBlockK * 2;
 constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
 constexpr uint32_t kTmemCols = kBlockN;           // f32 accumulator columns
 constexpr uint32_t kThreads = 192;                // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
-constexpr uint32_t kWaitLimit = 1u << 22;
 
 
-__device__ __forceinline__ uint32_t SmemAddr(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ void MbarInit(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(SmemAddr(bar)), "r"(count));
-}
-__device__ __forceinline__ void MbarExpectTx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemAddr(bar)),
-               "r"(bytes)
-               : "memory");
-}
-// Bounded wait: false when the limit ran out.
-__device__ __forceinline__ bool MbarWait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = SmemAddr(bar);
-  for (uint32_t it = 0; it < kWaitLimit; ++it) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-
-__device__ __forceinline__ void TmaLoad2D(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
-                                          int32_t x, int32_t y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4}], [%2];"
-      ::"r"(SmemAddr(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(SmemAddr(bar)), "r"(x),
-      "r"(y)
-      : "memory");
-}
-
-// Shared-memory matrix descriptor, K-major, 128-byte swizzle: start address
-// (>>4), leading byte offset 1 (unused for swizzled K-major), stride byte offset
-// 1024 (>>4 = 64: eight 128-byte rows per swizzle atom), descriptor version 1,
-// layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t MakeSmemDesc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
-  d |= static_cast<uint64_t>(1) << 16;
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
-  return d;
-}
-
-// Instruction descriptor for kind::f16: D = f32, A = B = bf16, both K-major.
-__device__ __forceinline__ uint32_t MakeInstrDesc(uint32_t m, uint32_t n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
-}
-
-__device__ __forceinline__ void UmmaBf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                         uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void UmmaCommit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-               ::"r"(SmemAddr(bar))
-               : "memory");
-}
-__device__ __forceinline__ void TmemLoad32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
+using namespace umma_dev;   // mbarriers with bounded waits, TMA loads, descriptors, MMA issue, TMEM loads
 
 __device__ __forceinline__ float ApplyAct(float v, int act) { return ActFwdExpr(act, v); }
 
@@ -724,10 +643,15 @@ static size_t UmmaPersistentSmemBytes() {
 
 cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
                            const UmmaEpilogue& ep, cudaStream_t s) {
-  static bool configured = false;
+  // The shared-memory limit of a kernel is a per-device attribute: one flag per
+  // device, so a second backend on another GPU of the same process configures its own.
+  static std::atomic<bool> configured_on[64] = {};
   static int sm_count[64] = {};
   const size_t smem = UmmaSmemBytes(), psmem = UmmaPersistentSmemBytes();
-  if (!configured) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const bool tracked = dev >= 0 && dev < 64;
+  if (!tracked || !configured_on[dev].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(UmmaGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e != cudaSuccess) return e;
@@ -737,10 +661,8 @@ cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
     e = cudaFuncSetAttribute(UmmaGemmPersistentKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(psmem));
     if (e != cudaSuccess) return e;
-    configured = true;
+    if (tracked) configured_on[dev].store(true, std::memory_order_release);
   }
-  int dev = 0;
-  cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && sm_count[dev] == 0)
     cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
   const uint32_t sms = (dev >= 0 && dev < 64 && sm_count[dev] > 0) ? sm_count[dev] : 148;

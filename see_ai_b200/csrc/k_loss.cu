@@ -7,6 +7,7 @@
 // per-row -log p in double, rows folded sequentially inside each chunk, chunks
 // folded in chunk order, so the loss does not depend on the launch geometry.
 // Integer results (the masked forms' target count) are exact.
+#include <atomic>
 #include "act_expr.cuh"
 #include "kernels.h"
 #include "shadow.cuh"
@@ -444,13 +445,15 @@ bool SoftmaxXEntFwd(bool masked, const float* logits, const int32_t* labels, flo
   if (wide) {
     // Raising a kernel's dynamic shared-memory limit is a per-device setting of
     // the function, not an allocation; done on first use per device.
-    static bool configured[64] = {};
+    // (Atomic flags: handle-free callers may make their first calls from two host
+    // threads at once; setting the attribute twice is harmless, a torn flag is not.)
+    static std::atomic<bool> configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
       cudaFuncSetAttribute(XEntRowsWideKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            4 * kWideThreads * kWideVecs * static_cast<int>(sizeof(float)));
-      configured[dev] = true;
+      configured[dev].store(true, std::memory_order_release);
     }
     const unsigned blocks = static_cast<unsigned>(N < 148 * 4 ? N : 148 * 4);
     Shadow sh{};

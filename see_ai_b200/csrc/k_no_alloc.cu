@@ -19,7 +19,9 @@
 // Things a caller must know:
 //  * The first call on each device looks up the array's device address
 //    (cudaGetSymbolAddress, with that device current).  Make that first call
-//    before starting any stream capture.
+//    before starting any stream capture.  Rows of 4096 to 32768 classes take a
+//    different kernel whose first launch on a device raises its shared-memory
+//    limit: make a first call of THAT width class before capture too.
 //  * All calls share the one array.  Two calls whose kernels can overlap on
 //    the GPU (different streams, no ordering between them) race on it.
 //  * Nothing in the array has to start at zero: each call overwrites the
@@ -29,6 +31,7 @@
 //    is launched.
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdio>
 
 #include "../../include/see_cuda.h"
@@ -48,7 +51,10 @@ struct alignas(256) NoAllocScratch {
 // a device address.  Kernels get the address cudaGetSymbolAddress returns.
 static __device__ __align__(256) NoAllocScratch g_no_alloc_scratch;
 
-NoAllocScratch* g_scratch_on_device[kMaxDevices] = {};
+// Written once per device; atomic because nothing stops two host threads from
+// making the first call on a device at the same moment (both then look the same
+// address up and store the same value).
+std::atomic<NoAllocScratch*> g_scratch_on_device[kMaxDevices] = {};
 thread_local char g_no_alloc_error[256] = "";
 
 int Fail(const char* what, cudaError_t e) {
@@ -83,16 +89,16 @@ int see_cuda_xent_forward_static(const float* logits, const int32_t* labels, flo
   int device = -1;
   if (cudaError_t e = cudaGetDevice(&device); e != cudaSuccess) return Fail("cudaGetDevice", e);
   if (device < 0 || device >= kMaxDevices) return Fail("device ordinal out of range", cudaSuccess);
-  if (!g_scratch_on_device[device]) {
+  if (!g_scratch_on_device[device].load(std::memory_order_acquire)) {
     // Set-up, once per device, with that device current.
     NoAllocScratch* ptr = nullptr;
     if (cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_no_alloc_scratch);
         e != cudaSuccess)
       return Fail("cudaGetSymbolAddress", e);
     if (!ptr) return Fail("the scratch symbol has no device address", cudaSuccess);
-    g_scratch_on_device[device] = ptr;
+    g_scratch_on_device[device].store(ptr, std::memory_order_release);
   }
-  NoAllocScratch* scratch = g_scratch_on_device[device];
+  NoAllocScratch* scratch = g_scratch_on_device[device].load(std::memory_order_acquire);
   see::k::SoftmaxXEntFwd(masked != 0, logits, labels, loss, probs, rows, classes, scratch->rows,
                          &scratch->count, static_cast<cudaStream_t>(cuda_stream));
   if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return Fail("launch", e);

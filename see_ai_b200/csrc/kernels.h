@@ -186,6 +186,20 @@ void ArgmaxTally(const float* probs, const int32_t* labels, size_t N, size_t C,
                  unsigned long long* tally, cudaStream_t s);
 // tally[2] += count of non-finite elements.
 void CountNonFinite(const float* x, size_t n, unsigned long long* tally, cudaStream_t s);
+// The real-row loss of the batch just evaluated: out[0] = the sum over the first
+// real_rows rows of each row's loss (-log max(p[label], 1e-12), NaN kept; rows
+// with label < 0 skipped), added in row order in double; tally[3] = the rows it
+// is over.  `terms` holds real_rows doubles.  The MSE form sums the squared
+// differences of real_rows * width elements in element order and divides by width.
+void XentRealRowLoss(const float* probs, const int32_t* labels, size_t real_rows, size_t width,
+                     double* terms, double* out, unsigned long long* tally, cudaStream_t s);
+void MseRealRowLoss(const float* pred, const float* target, size_t real_rows, size_t width, double* terms,
+                    double* out, unsigned long long* tally, cudaStream_t s);
+// Symmetric per-column int8 quantisation of W [K, N] with the compiler's own
+// arithmetic: levels [K, N] int8 and scales [N] f32, bit for bit.
+// `maxbits_scratch` holds N 32-bit words.
+void QuantizeColumns(const float* w, size_t K, size_t N, int8_t* levels, float* scales,
+                     unsigned int* maxbits_scratch, cudaStream_t s);
 
 // ---- GEMM -------------------------------------------------------------------
 enum class BType : uint8_t { kF32 = 0, kI8 = 1, kBf16 = 2 };

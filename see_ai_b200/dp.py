@@ -115,6 +115,16 @@ class GradientExchange:
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
+        # The masked loss divides each shard's gradient by that shard's own target
+        # count, so the plain 1/N mean of shard gradients is the global masked mean
+        # only when every shard holds the same number of targets: not promised here.
+        if self.world > 1 and getattr(engine, "has_masked_loss", False):
+            raise ValueError("data parallel: plans with a masked cross-entropy are not supported "
+                             "(shards would need a target-count-weighted mean)")
+        # The collective is enqueued on torch's current stream; the engine's kernels
+        # must run on that same stream to be ordered with it.
+        self.stream = torch.cuda.current_stream()
+        engine.backend.set_stream(self.stream.cuda_stream)
         off, nbytes = engine.gradient_block()
         self.off, self.nbytes = off, nbytes
         self.gathered = torch.empty(self.world * nbytes, dtype=torch.uint8, device="cuda")
@@ -126,11 +136,15 @@ class GradientExchange:
 
     def exchange(self):
         if self.world > 1:
-            self.dist.all_gather_into_tensor(self.gathered, self.local, group=self.group)
+            import torch
+            with torch.cuda.stream(self.stream):
+                self.dist.all_gather_into_tensor(self.gathered, self.local, group=self.group)
 
     def mean_loss(self, local_loss: float) -> float:
         """Mean of the shard losses in rank order (each shard's loss is already a
-        mean over its own rows, and shards are equal-sized)."""
+        mean over its own rows, and shards are equal-sized; plans with a masked
+        loss, whose per-shard means are over unequal target counts, are refused
+        by the constructor)."""
         import torch
         if self.world == 1:
             return local_loss

@@ -17,7 +17,7 @@ ENGINE_SYMBOLS = [
     "see_engine_create", "see_engine_destroy", "see_engine_last_error", "see_engine_backend",
     "see_engine_load", "see_engine_bind_source", "see_engine_header", "see_engine_stage_batch",
     "see_engine_train_forward_backward", "see_engine_train_optimizer", "see_engine_step_program",
-    "see_engine_read_loss", "see_engine_evaluate", "see_engine_run_merge",
+    "see_engine_read_loss", "see_engine_evaluate", "see_engine_evaluate_rows", "see_engine_run_merge",
     "see_engine_read_arena", "see_engine_write_arena", "see_engine_step", "see_engine_set_step",
     "see_engine_set_horizon", "see_engine_effective_lr", "see_engine_set_use_graphs",
     "see_engine_set_phase_timing", "see_engine_take_timings", "see_engine_gradient_block",
@@ -25,6 +25,13 @@ ENGINE_SYMBOLS = [
 ]
 
 _configured = False
+
+
+class EvalResult(ctypes.Structure):
+    """see_eval_result of include/see_cuda.h."""
+    _fields_ = [("loss", ctypes.c_float), ("has_accuracy", ctypes.c_uint32), ("rows", ctypes.c_uint64),
+                ("correct", ctypes.c_uint64), ("real_row_loss", ctypes.c_double),
+                ("loss_rows", ctypes.c_uint64)]
 
 
 def _lib() -> ctypes.CDLL:
@@ -50,6 +57,7 @@ def _lib() -> ctypes.CDLL:
     lib.see_engine_read_loss.argtypes = [vp, ctypes.POINTER(ctypes.c_float)]
     lib.see_engine_evaluate.argtypes = [vp, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(u64),
                                         ctypes.POINTER(u64)]
+    lib.see_engine_evaluate_rows.argtypes = [vp, u64, ctypes.POINTER(EvalResult)]
     lib.see_engine_run_merge.argtypes = [vp, ctypes.POINTER(i32)]
     lib.see_engine_read_arena.argtypes = [vp, u64, u64, vp]
     lib.see_engine_write_arena.argtypes = [vp, u64, u64, vp]
@@ -119,6 +127,8 @@ class Engine:
         self.lib.see_engine_header(self.h, raw)
         vals = P._HEADER.unpack_from(raw.raw, 0)
         self.header = {n: v for (n, _), v in zip(P._HEADER_FIELDS, vals)}
+        train = P.Plan(blob).section("train")   # decodes the header and the instruction words only
+        self.has_masked_loss = any(i.opcode in (P.Op.XENT_MASKED_FWD, P.Op.XENT_MASKED_BWD) for i in train)
 
     def bind_source(self, data: Optional[np.ndarray]):
         if data is None:
@@ -161,6 +171,14 @@ class Engine:
         self._check(self.lib.see_engine_evaluate(self.h, ctypes.byref(loss), ctypes.byref(rows),
                                                  ctypes.byref(correct)))
         return float(np.float32(loss.value)), int(rows.value), int(correct.value)
+
+    def evaluate_rows(self, x, y, real_rows: int) -> EvalResult:
+        """Evaluates one staged batch whose first `real_rows` rows are real (the
+        rest wrapped duplicates): accuracy tallies and the real-row loss."""
+        self.stage_batch(x, y)
+        out = EvalResult()
+        self._check(self.lib.see_engine_evaluate_rows(self.h, real_rows, ctypes.byref(out)))
+        return out
 
     def run_merge(self) -> bool:
         ok = ctypes.c_int()

@@ -56,6 +56,7 @@ class PlanBuilder:
         self.rodata: List[T] = []
         self.programs: Dict[str, List[tuple]] = {"train": [], "eval": [], "merge": [], "step": []}
         self.cur = "train"
+        self.emits: List[Tuple[T, int]] = []   # (delta tensor, byte offset of its weight in the model file)
 
     # ---- tensors ----
     def t(self, name, n_floats, kind="transient", data=None, elem=4) -> T:
@@ -153,9 +154,10 @@ class PlanBuilder:
 
         h = {k: (v.ref if isinstance(v, T) else v) for k, v in header.items()}
         h.update(arena_size=arena_size, persistent_size=persistent_size)
+        emit = [P.EmitEntry(smf_off, t.nbytes, t.off) for (t, smf_off) in self.emits]
         return P.write_plan(h, lower(self.programs["train"]), lower(self.programs["eval"]),
                             lower(self.programs["merge"]), lower(self.programs["step"]),
-                            rodata.tobytes(), persist.tobytes())
+                            rodata.tobytes(), persist.tobytes(), emit=emit)
 
 
 # ---- LoRA site helpers -----------------------------------------------------------
@@ -196,7 +198,7 @@ def quantize_columns(w: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
     amax = np.max(np.abs(w), axis=0)
     scale = np.where(amax > 0, amax / 127.0, 1.0).astype(np.float32)
     scale = np.maximum(scale, np.finfo(np.float32).tiny)
-    q = w / scale
+    q = (w / scale).astype(np.float32).astype(np.float64)   # the f32 quotient; + 0.5 is then exact
     q = np.clip(np.where(q >= 0, np.floor(q + 0.5), np.ceil(q - 0.5)), -127, 127).astype(np.int8)
     return q, scale
 
@@ -516,10 +518,13 @@ def build_decoder_plan(cfg: DecoderConfig) -> bytes:
     forward(False)
     # ---- merge program: each adapter's delta = (alpha / r) * A @ B ----
     b.cur = "merge"
+    smf_off = 0
     for l in range(L):
         for ad in adapters[l].values():
             b.emit(Op.FILL, (ad.delta, 0), (D * D,))
             b.emit(Op.GEMM_ACC_NN, (ad.A, ad.B, ad.delta, alpha_bits), (D, D, r))
+            b.emits.append((ad.delta, smf_off))
+            smf_off += D * D * 4
 
     header = dict(input_ref=tokens, input_floats=M, label_ref=labels, label_bytes=4 * M, label_kind=1,
                   loss_ref=loss, lr=cfg.lr, batch=M, default_steps=cfg.steps, lr_schedule=0,
@@ -542,6 +547,9 @@ class MlpConfig:
     lr: float = 1e-3
     steps: int = 1000
     seed: int = 7
+    lr_schedule: int = 0        # 1: linear warm-up, then a cosine down to lr * min_lr_factor
+    warmup_steps: int = 0
+    min_lr_factor: float = 0.0
 
 
 def build_mlp_plan(cfg: MlpConfig) -> bytes:
@@ -620,10 +628,15 @@ def build_mlp_plan(cfg: MlpConfig) -> bytes:
     b.cur = "eval"
     forward()
     b.cur = "merge"
+    smf_off = 0
     for ad in ads:
         b.emit(Op.FILL, (ad.delta, 0), (ad.k_in * ad.n_out,))
         b.emit(Op.GEMM_ACC_NN, (ad.A, ad.B, ad.delta, alpha_bits), (ad.k_in, ad.n_out, r))
+        b.emits.append((ad.delta, smf_off))
+        smf_off += ad.k_in * ad.n_out * 4
     header = dict(input_ref=x0, input_floats=M * dims[0], label_ref=labels, label_bytes=4 * M,
                   label_kind=1, loss_ref=loss, lr=cfg.lr, batch=M, default_steps=cfg.steps,
-                  lr_schedule=0, input_kind=0, grad_accum_steps=1, seq_len=0, weight_decay=0.01)
+                  lr_schedule=cfg.lr_schedule, warmup_steps=cfg.warmup_steps,
+                  min_lr_factor=cfg.min_lr_factor, input_kind=0, grad_accum_steps=1, seq_len=0,
+                  weight_decay=0.01)
     return _finish(b, header)

@@ -60,7 +60,9 @@ def test_static_entry_matches_regular_entry_on_two_calls_in_a_row():
     rng = np.random.default_rng(42)
     # Two different batches back to back: the second reuses the array the first
     # left dirty (more rows first, fewer second, so stale entries sit behind it).
-    cases = [(777, 130, False), (300, 1029, True)]
+    # The third is the wide-row kernel (4096..32768 classes: rows held in registers,
+    # first launch raises the kernel's shared-memory limit), masked.
+    cases = [(777, 130, False), (300, 1029, True), (64, 4096, True)]
     for n, c, masked in cases:
         logits = (rng.standard_normal((n, c)) * 3).astype(np.float32)
         labels = rng.integers(0, c, size=n).astype(np.int32)
