@@ -107,6 +107,7 @@ struct __align__(8) Barriers {
 
 __global__ void __launch_bounds__(kThreads, 2)
 UmmaGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
                UmmaEpilogue ep) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the swizzle pattern and the descriptors' base offset assume it.
@@ -115,7 +116,11 @@ UmmaGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t m0 = blockIdx.y * kBlockM, n0 = blockIdx.x * kBlockN;
-  const uint32_t k_blocks = (ep.K + kBlockK - 1) / kBlockK;
+  // The reduction runs over the main operands' K and then over aux_k_blocks more
+  // 64-wide blocks taken from the second pair of maps (a low-rank term T . B'^T
+  // accumulated into the same tile; see UmmaEpilogue::aux_k_blocks).
+  const uint32_t main_blocks = (ep.K + kBlockK - 1) / kBlockK;
+  const uint32_t k_blocks = main_blocks + ep.aux_k_blocks;
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < kStages; ++s) {
@@ -150,10 +155,10 @@ UmmaGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint8_t* a_dst = smem + s * kStageBytes;
         uint8_t* b_dst = a_dst + kATileBytes;
         MbarExpectTx(&bars->full[s], kStageBytes);
-        TmaLoad2D(a_dst, &map_a, &bars->full[s], static_cast<int32_t>(kb * kBlockK),
-                  static_cast<int32_t>(m0));
-        TmaLoad2D(b_dst, &map_b, &bars->full[s], static_cast<int32_t>(kb * kBlockK),
-                  static_cast<int32_t>(n0));
+        const bool aux = kb >= main_blocks;
+        const int32_t kx = static_cast<int32_t>((aux ? kb - main_blocks : kb) * kBlockK);
+        TmaLoad2D(a_dst, aux ? &map_a2 : &map_a, &bars->full[s], kx, static_cast<int32_t>(m0));
+        TmaLoad2D(b_dst, aux ? &map_b2 : &map_b, &bars->full[s], kx, static_cast<int32_t>(n0));
       }
     }
   } else if (warp == 1) {
@@ -303,7 +308,9 @@ struct __align__(8) PBarriers {
 template <bool kSideLoads>
 __global__ void __launch_bounds__(kPThreads, 1)
 UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
-                         const __grid_constant__ CUtensorMap map_b, UmmaEpilogue ep,
+                         const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_a2,
+                         const __grid_constant__ CUtensorMap map_b2, UmmaEpilogue ep,
                          uint32_t band_blocks) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (SmemAddr(smem_raw) & 1023u)) & 1023u);
@@ -311,7 +318,8 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
   PBarriers* bars = reinterpret_cast<PBarriers*>(slabs + kPEpiWarps * kSlabBytes);
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t k_blocks = (ep.K + kBlockK - 1) / kBlockK;
+  const uint32_t main_blocks = (ep.K + kBlockK - 1) / kBlockK;
+  const uint32_t k_blocks = main_blocks + ep.aux_k_blocks;   // then the low-rank term's blocks
   const uint32_t tiles_n = (ep.N + kPBlockN - 1) / kPBlockN;
   const uint32_t tiles_m = (ep.M + kBlockM - 1) / kBlockM;
   const uint32_t total_tiles = tiles_m * tiles_n;
@@ -355,7 +363,7 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
           TileCoord(t + gridDim.x, tiles_m, tiles_n, band_blocks, &next_mb, &next_nb);
           const uint32_t next_m0 = next_mb * kBlockM;
           if (next_m0 != m0)
-            for (uint32_t kb = 0; kb < k_blocks; ++kb)
+            for (uint32_t kb = 0; kb < main_blocks; ++kb)
               asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
                            ::"l"(reinterpret_cast<uint64_t>(&map_a)),
                              "r"(static_cast<int32_t>(kb * kBlockK)), "r"(static_cast<int32_t>(next_m0))
@@ -371,13 +379,15 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
           }
           uint8_t* a_dst = smem + s * kPStageBytes;
           MbarExpectTx(&bars->full[s], kPStageBytes);
-          TmaLoad2D(a_dst, &map_a, &bars->full[s], static_cast<int32_t>(kb * kBlockK),
-                    static_cast<int32_t>(m0));
+          const bool aux = kb >= main_blocks;
+          const CUtensorMap* ma = aux ? &map_a2 : &map_a;
+          const CUtensorMap* mb_ = aux ? &map_b2 : &map_b;
+          const int32_t kx = static_cast<int32_t>((aux ? kb - main_blocks : kb) * kBlockK);
+          TmaLoad2D(a_dst, ma, &bars->full[s], kx, static_cast<int32_t>(m0));
           // B's 256 rows as two 128-row boxes, back to back: one [256][64] tile.
-          TmaLoad2D(a_dst + kATileBytes, &map_b, &bars->full[s], static_cast<int32_t>(kb * kBlockK),
-                    static_cast<int32_t>(n0));
-          TmaLoad2D(a_dst + kATileBytes + kBTileBytes, &map_b, &bars->full[s],
-                    static_cast<int32_t>(kb * kBlockK), static_cast<int32_t>(n0 + kBlockN));
+          TmaLoad2D(a_dst + kATileBytes, mb_, &bars->full[s], kx, static_cast<int32_t>(n0));
+          TmaLoad2D(a_dst + kATileBytes + kBTileBytes, mb_, &bars->full[s], kx,
+                    static_cast<int32_t>(n0 + kBlockN));
         }
       }
     }
@@ -642,7 +652,12 @@ static size_t UmmaPersistentSmemBytes() {
 }
 
 cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
-                           const UmmaEpilogue& ep, cudaStream_t s) {
+                           const UmmaEpilogue& ep, cudaStream_t s, const CUtensorMap* aux_a,
+                           const CUtensorMap* aux_b) {
+  // Without a low-rank term the second pair of maps is never dereferenced; the
+  // main pair stands in so that the parameters are valid descriptors.
+  const CUtensorMap& map_a2 = ep.aux_k_blocks && aux_a ? *aux_a : map_a;
+  const CUtensorMap& map_b2 = ep.aux_k_blocks && aux_b ? *aux_b : map_b;
   // The shared-memory limit of a kernel is a per-device attribute: one flag per
   // device, so a second backend on another GPU of the same process configures its own.
   static std::atomic<bool> configured_on[64] = {};
@@ -672,13 +687,13 @@ cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
     // Enough tiles for every SM to amortise its set-up over several.
     const uint32_t band = ptiles_n >= kWideTilesN ? kWideBandBlocks : 1u;
     if (ep.addend != nullptr || ep.fuse_mode == kFuseActBwd)
-      UmmaGemmPersistentKernel<true><<<sms, kPThreads, psmem, s>>>(map_a, map_b, ep, band);
+      UmmaGemmPersistentKernel<true><<<sms, kPThreads, psmem, s>>>(map_a, map_b, map_a2, map_b2, ep, band);
     else
-      UmmaGemmPersistentKernel<false><<<sms, kPThreads, psmem, s>>>(map_a, map_b, ep, band);
+      UmmaGemmPersistentKernel<false><<<sms, kPThreads, psmem, s>>>(map_a, map_b, map_a2, map_b2, ep, band);
     return cudaGetLastError();
   }
   dim3 grid(tiles_n, tiles_m);
-  UmmaGemmKernel<<<grid, kThreads, smem, s>>>(map_a, map_b, ep);
+  UmmaGemmKernel<<<grid, kThreads, smem, s>>>(map_a, map_b, map_a2, map_b2, ep);
   return cudaGetLastError();
 }
 

@@ -39,12 +39,20 @@ struct UmmaEpilogue {
   const float* shadow_k_scale = nullptr;
   int store_c = 1;
   int addend_last = 0;
+  // A low-rank term folded into the product: after the main operands' K the
+  // reduction continues over aux_k_blocks blocks of 64 from a second operand
+  // pair, T' [M, 64 * aux_k_blocks] and B' [N, 64 * aux_k_blocks] (bf16, K-major),
+  // so the tile holds A W^T + T' B'^T before the epilogue scales it.  With T' and
+  // B' the three-way bf16 splits of f32 factors (LoraSplit* in kernels.h) the
+  // added term is the f32 product t . b to about 2^-23 of |t| |b|.
+  uint32_t aux_k_blocks = 0;
 };
 
 size_t UmmaSmemBytes();
 // map_a: bf16 [M, K] row-major, box {64, 128}, 128-byte swizzle; map_b: bf16 [N, K] likewise.
 cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
-                           const UmmaEpilogue& ep, cudaStream_t s);
+                           const UmmaEpilogue& ep, cudaStream_t s, const CUtensorMap* aux_a = nullptr,
+                           const CUtensorMap* aux_b = nullptr);
 // dst[N][K] (bf16 bits) from src [K][N] (transpose) or [N][K]; int8 and bf16 widen exactly.
 // k_scale (or null): dst[n][k] = bf16(src * k_scale[k]).
 void WeightToBf16(const void* src, BType type, uint16_t* dst, uint32_t N, uint32_t K,

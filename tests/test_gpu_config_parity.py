@@ -139,13 +139,15 @@ def test_mlp_plan_1000_steps_and_the_gate_verdict():
     assert abs(rep_g.val_initial - rep_c.val_initial) <= 1e-5 * abs(rep_c.val_initial)
     assert rep_g.val_initial_accuracy == rep_c.val_initial_accuracy
     figures = {}
-    for n in (1, 10, 100, 1000):
-        ok, ratio = _loss_curve_ok(rep_g.loss_curve[:n], rep_c.loss_curve[:n], 2e-3, 1e-4)
+    # 2e-3 is what the reference asks of its own GPU backend after 8 steps; beyond a hundred steps of
+    # AdamW its release gate prices the drift at 1 % (the comment at metal_backend_test.cc:214-217).
+    for n, rel in ((1, 2e-3), (10, 2e-3), (100, 2e-3), (1000, 1e-2)):
+        ok, ratio = _loss_curve_ok(rep_g.loss_curve[:n], rep_c.loss_curve[:n], rel, 1e-4)
         figures[f"loss_curve_err_over_bound_{n}"] = ratio
         assert ok, (n, ratio)
     assert abs(rep_g.loss_curve[0] - rep_c.loss_curve[0]) <= 1e-5 * abs(rep_c.loss_curve[0])
     for (sg, lg), (sc, lc) in zip(rep_g.eval_trace, rep_c.eval_trace):
-        assert sg == sc and abs(lg - lc) <= 1e-4 + 2e-3 * abs(lc)
+        assert sg == sc and abs(lg - lc) <= 1e-4 + (2e-3 if sg <= 100 else 1e-2) * abs(lc)
     # Both restored the best state they kept: the same step's adapters and moments.
     ratio, rms, name = _worst(_optimizer_tensors(plan), gpu, cpu, 5e-3, 1e-6)
     figures["restored_state_err_over_bound"] = ratio

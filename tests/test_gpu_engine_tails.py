@@ -265,11 +265,15 @@ def test_data_parallel_standalone_clip_reaches_the_update(case_name):
         ex.bind(a, ro)
         arenas.append(a)
         execs.append(ex)
+    moments = [(i.ins[3], i.out[0]) for i in train[opt:] if i.opcode == Op.ADAMW_STEP]
     for step in range(1, 4):
         shards = [(rng.standard_normal((rows, dim)).astype(np.float32) * 3.0,   # large inputs: the clip must bite
                    rng.integers(0, classes, size=rows).astype(np.int32)) for _ in range(2)]
         sp = oracle.StepParams(case.lr, h["beta1"], h["beta2"], h["eps"], h["weight_decay"], 0, step)
         for r in range(2):
+            # Lockstep: every step starts from the engine's own state on both sides, so that one
+            # step's arithmetic is compared and not the drift AdamW makes of earlier differences.
+            arenas[r][:h["persistent_size"]] = engines[r].read_persistent()
             xb, yb = shards[r]
             engines[r].stage_batch(xb, yb)
             engines[r].train_forward_backward(True)
@@ -285,11 +289,21 @@ def test_data_parallel_standalone_clip_reaches_the_update(case_name):
             engines[r].train_optimizer()
             arenas[r][g_off:g_off + g_bytes] = mean.view(np.uint8)
             execs[r].run(train, sp, opt, len(train))
-    states = [e.read_persistent() for e in engines]
-    assert np.array_equal(states[0], states[1])
-    want = arenas[0][:h["persistent_size"]]
-    # Without the fix the update ignores the clip: the difference is then of the order of the state itself.
-    assert np.allclose(states[0].view(np.float32), want.view(np.float32), rtol=1e-4, atol=1e-6)
+        # What the optimizer range leaves in the gradient block is the CLIPPED MEAN on both sides.
+        got_block = engines[0].read_arena(g_off, g_bytes)
+        ok, ratio = compare(got_block.tobytes(), arenas[0][g_off:g_off + g_bytes].tobytes(), 1e-5, 1e-9)
+        assert ok, (step, ratio)
+        clipped = np.abs(arenas[0][g_off:g_off + g_bytes].view(np.float32)).max()
+        assert clipped < 0.9 * np.abs(mean).max(), "the clip did not bite: the test would prove nothing"
+        states = [e.read_persistent() for e in engines]
+        assert np.array_equal(states[0], states[1])
+        want = arenas[0][:h["persistent_size"]]
+        assert np.allclose(states[0].view(np.float32), want.view(np.float32), rtol=5e-3, atol=1e-6), step
+        # The second moments are the squares of what the optimizer was fed: an update that ignored the
+        # clip would leave them larger by the square of the clip factor.
+        for (off, n) in moments:
+            assert np.allclose(states[0][off:off + 4 * n].view(np.float32), want[off:off + 4 * n].view(np.float32),
+                               rtol=1e-3, atol=1e-12), step
     for e in engines:
         e.close()
 
