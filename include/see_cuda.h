@@ -94,6 +94,9 @@ int see_cuda_set_relaxed_allowed(see_cuda_backend* h, int allowed);  /* 0: alway
 /* 0: every instruction is its own kernel(s) even in lazy coherence (no bias add or
  * activation absorbed into a product's epilogue); default 1. */
 int see_cuda_set_epilogue_fusion(see_cuda_backend* h, int enabled);
+/* 0: an adapter's rank-r expand product stays its own kernel instead of riding the
+ * frozen product's tensor-core reduction (lazy coherence only); default 1. */
+int see_cuda_set_lora_fold(see_cuda_backend* h, int enabled);
 /* Data parallelism: optimizer steps read gradients inside [block_offset,
  * block_offset + block_bytes) as the rank-ordered sum of `ranks` gathered
  * copies (device memory, copy r at gathered + r * block_bytes) times 1/ranks. */

@@ -33,6 +33,7 @@ CU_SOURCES = {
     "k_eval.cu": [],
     "k_attn_umma.cu": [],
     "k_no_alloc.cu": ["-fmad=false"],
+    "k_lora.cu": [],
 }
 CC_SOURCES = ["extents.cc", "cuda_backend.cc", "c_api.cc", "umma_gemm.cc", "engine.cc"]
 

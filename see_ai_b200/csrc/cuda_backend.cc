@@ -108,6 +108,8 @@ CudaBackend::~CudaBackend() {
   cudaFree(d_colmax_);
   cudaFree(d_split_);
   cudaFree(d_adam_table_);
+  FreeLoraRanges();
+  cudaFree(d_lora_t_);
   if (h_scalars_) cudaFreeHost(h_scalars_);
   if (h_status_) cudaFreeHost(h_status_);
   if (own_stream_ && stream_) cudaStreamDestroy(stream_);
@@ -156,6 +158,7 @@ Status CudaBackend::Bind(uint8_t* arena, uint64_t arena_bytes, const uint8_t* ro
   deferred_error_.clear();
   scalars_valid_ = false;
   umma::InvalidateAll(&umma_->ctx);
+  FreeLoraRanges();
   return {};
 }
 
@@ -200,6 +203,7 @@ Status CudaBackend::BindDeviceImage(uint64_t arena_bytes, const uint8_t* prefix,
   deferred_error_.clear();
   scalars_valid_ = false;
   umma::InvalidateAll(&umma_->ctx);
+  FreeLoraRanges();
   return {};
 }
 
@@ -408,13 +412,75 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
   // CUDA graph must contain every conversion it depends on.
   umma::InvalidateRange(&umma_->ctx, 0, arena_bytes_);
   range_index_ = 0;
-  PlanShadows(program, begin, std::min(end, program.size()));
   PlanAdamGroups(program, begin, std::min(end, program.size()));
-  PlanBiasFusions(program, begin, std::min(end, program.size()));
-  PlanActFusions(program, begin, std::min(end, program.size()));
+  auto plan_fusions = [&] {
+    PlanShadows(program, begin, std::min(end, program.size()));
+    PlanBiasFusions(program, begin, std::min(end, program.size()));
+    PlanActFusions(program, begin, std::min(end, program.size()));
+  };
+  plan_fusions();
+  uint64_t fold_rows = 0;
+  for (size_t i = 0; i < lora_fold_.size(); ++i)
+    if (lora_fold_[i].fuse) fold_rows = std::max<uint64_t>(fold_rows, program[begin + i].out[0]);
+  if (auto r = PrepareLoraFolds(program.data(), begin, fold_rows); !r) {   // no memory for the operands: run the plan as written
+    cudaGetLastError();
+    const bool enabled = lora_fold_enabled_;
+    lora_fold_enabled_ = false;
+    plan_fusions();   // again, without the folds (they had taken over some of the add fusions)
+    lora_fold_enabled_ = enabled;
+  }
+}
+
+// Device buffers and the weight table of the folds just planned.
+Status CudaBackend::PrepareLoraFolds(const Instruction* program, size_t begin, uint64_t max_rows) {
+  d_lora_table_ = nullptr;
+  d_lora_w_ = nullptr;
+  if (lora_weights_.empty()) return {};
+  LoraRangeBuffers& rb = lora_ranges_[{program, begin}];
+  const uint64_t w_need = static_cast<uint64_t>(lora_weights_.size()) * lora_max_n_ * lora_max_kx_;
+  const uint64_t t_need = max_rows * lora_max_kx_;
+  if (w_need > rb.weights_capacity || t_need > lora_t_capacity_ || lora_weights_.size() > rb.table_capacity)
+    cudaStreamSynchronize(stream_);   // queued kernels may still read the old buffers
+  auto grow = [&](void** buf, uint64_t* cap, uint64_t need, size_t elem) -> Status {
+    if (need <= *cap) return {};
+    cudaFree(*buf);
+    *buf = nullptr;
+    *cap = 0;
+    if (auto r = Check(cudaMalloc(buf, need * elem), "low-rank fold operands"); !r) return r;
+    *cap = need;
+    return {};
+  };
+  uint64_t table_cap = rb.table_capacity;
+  if (auto r = grow(reinterpret_cast<void**>(&rb.weights), &rb.weights_capacity, w_need, 2); !r) return r;
+  if (auto r = grow(reinterpret_cast<void**>(&d_lora_t_), &lora_t_capacity_, t_need, 2); !r) return r;
+  if (auto r = grow(reinterpret_cast<void**>(&rb.table), &table_cap, lora_weights_.size(), sizeof(k::LoraWeight));
+      !r)
+    return r;
+  rb.table_capacity = table_cap;
+  d_lora_table_ = rb.table;
+  d_lora_w_ = rb.weights;
+  for (size_t i = 0; i < lora_weights_.size(); ++i)
+    lora_weights_[i].dst = d_lora_w_ + static_cast<uint64_t>(i) * lora_max_n_ * lora_max_kx_;
+  // An earlier pass over this range may still be reading the table.
+  cudaStreamSynchronize(stream_);
+  return Check(cudaMemcpy(d_lora_table_, lora_weights_.data(), lora_weights_.size() * sizeof(k::LoraWeight),
+                          cudaMemcpyHostToDevice), "low-rank fold table");
+}
+
+void CudaBackend::FreeLoraRanges() {
+  for (auto& [key, rb] : lora_ranges_) {
+    cudaFree(rb.table);
+    cudaFree(rb.weights);
+  }
+  lora_ranges_.clear();
+  d_lora_table_ = nullptr;
+  d_lora_w_ = nullptr;
 }
 
 void CudaBackend::EndRange() {
+  lora_fold_.clear();
+  lora_skip_.clear();
+  lora_weights_.clear();
   fold_gather_ = gather_folded_ = false;
   range_error_.clear();
   bias_fusion_.clear();
@@ -713,6 +779,10 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
   add_fusion_.assign(end > begin ? end - begin : 0, AddFusion{});
   attn_dv_out_.assign(end > begin ? end - begin : 0, kNullRef);
   attn_dv_shadow_.assign(end > begin ? end - begin : 0, ShadowPlan{});
+  lora_fold_.assign(end > begin ? end - begin : 0, LoraFold{});
+  lora_skip_.assign(end > begin ? end - begin : 0, 0);
+  lora_weights_.clear();
+  lora_max_n_ = lora_max_kx_ = 0;
   if (coherence_ == Coherence::kStrict || !relaxed_allowed_ || !epilogue_fusion_ || end < begin + 3) return;
   // Under the step-program promise liveness is decided on the whole program.
   const bool whole = step_program_ != nullptr && program.data() == step_program_;
@@ -990,6 +1060,199 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
       shadow_plan_[i + 1 - begin].want = false;
     }
   }
+
+  // ---- the adapter's expand product folded into the frozen product (LoraFold) ----
+  if (!lora_fold_enabled_) return;
+  auto overlap = [](uint64_t alo, uint64_t ahi, uint64_t blo, uint64_t bhi) { return alo < bhi && blo < ahi; };
+  auto touches = [&](size_t j, uint64_t lo, uint64_t hi, bool want_write) {   // does instruction j write (read) [lo, hi)?
+    const Extents& e = ext[j - ext_base];
+    for (size_t x = 0; x < e.count; ++x) {
+      if (e.e[x].space != kArena || !overlap(e.e[x].off, e.e[x].off + e.e[x].bytes, lo, hi)) continue;
+      if (want_write ? e.e[x].write : (!e.e[x].write || e.e[x].read)) return true;
+    }
+    return false;
+  };
+  auto rank_ok = [](uint64_t r) { return r == 4 || r == 8 || r == 12 || r == 16; };
+  auto aligned = [](uint64_t ref) { return RefSpace(ref) == kArena && (RefOffset(ref) & 15) == 0; };
+  auto plain_frozen = [&](size_t i) {
+    const Instruction& g = program[i];
+    return IsRelaxedFrozenGemm(g) && RefSpace(g.in[2]) == kArena &&
+           !(g.flags & (kFlagEpilogueBias | kFlagGemmAddend)) && ActOf(g.flags) == kActNone &&
+           !bias_fusion_[i - begin].fuse && act_fusion_[i - begin].mode == 0 && lora_skip_[i - begin] == 0 &&
+           !shadow_plan_[i - begin].want;
+  };
+  // The adapter matrix must hold the same values when the range starts (where its
+  // split copy is made) as where the plan multiplies by it.
+  auto unwritten_before = [&](size_t i, uint64_t lo, uint64_t hi) {
+    for (size_t j = begin; j < i; ++j)
+      if (touches(j, lo, hi, true)) return false;
+    return true;
+  };
+  auto add_weight = [&](const Instruction& g, uint64_t w_ref, uint32_t r, uint32_t n_out, float alpha, bool by_column) {
+    const k::GemmArgs ga = GemmArgsOf(g);
+    k::LoraWeight w{};
+    w.src = Rd(w_ref);
+    w.col_scale = ga.b_col_scale;
+    w.tile_alpha = ga.alpha;
+    w.alpha = alpha;
+    w.n_out = n_out;
+    w.r = r;
+    w.kx = k::LoraSplitColumns(r);
+    w.by_column = by_column ? 1u : 0u;
+    lora_weights_.push_back(w);
+    lora_max_n_ = std::max(lora_max_n_, n_out);
+    lora_max_kx_ = std::max(lora_max_kx_, w.kx);
+    return static_cast<uint32_t>(lora_weights_.size() - 1);
+  };
+  // A kAddEW planned to ride the expand kernel (add_fusion_ at the expand's
+  // position) moves to the frozen product's epilogue, or back to its own kernel.
+  auto take_add = [&](size_t e_abs, LoraFold* f, uint64_t e_out_lo, uint64_t e_out_hi, uint64_t keep_lo[3],
+                      uint64_t keep_hi[3], int keeps) {
+    AddFusion& af = add_fusion_[e_abs - begin];
+    if (!af.fuse) return;
+    bool ok = aligned(af.x_ref) && aligned(af.out_ref) && !shadow_plan_[af.add_index].want;
+    const uint64_t o_lo = RefOffset(af.out_ref), o_hi = o_lo + (e_out_hi - e_out_lo);
+    for (int q = 0; q < keeps && ok; ++q)   // the sum must not land on anything the product still reads
+      if (overlap(o_lo, o_hi, keep_lo[q], keep_hi[q])) ok = false;
+    if (ok) {
+      f->out_ref = af.out_ref;
+      f->addend_ref = af.x_ref;
+      ++f->absorbed;
+      lora_skip_[af.add_index] = 1;                       // the sum is written by the product
+      lora_skip_[e_abs - begin] = 2;                      // the expand's own output never is
+      f->dead[f->dead_count][0] = e_out_lo; f->dead[f->dead_count][1] = e_out_hi; ++f->dead_count;
+    }
+    af = AddFusion{};   // either way the expand kernel no longer runs
+  };
+  for (size_t i = begin; i < end; ++i) {
+    if (!plain_frozen(i) || add_fusion_[i - begin].fuse) continue;
+    const Instruction& g = program[i];
+    const uint64_t M = g.out[0], N = g.out[1];
+    const uint64_t b_lo = RefOffset(g.in[2]), b_hi = b_lo + M * N * 4;
+    const uint64_t x_lo = RefOffset(g.in[0]), x_hi = x_lo + M * g.out[2] * 4;
+    // kind 1: G; D: t = x A; E: out = G.out + s t B
+    if (i + 2 < end) {
+      const Instruction& d = program[i + 1];
+      const Instruction& e = program[i + 2];
+      const uint64_t r = d.out[1];
+      if (d.opcode == kGemmNN && d.flags == 0 && e.opcode == kGemmNN && e.flags == kFlagGemmAddend && rank_ok(r) &&
+          d.out[0] == M && e.out[0] == M && e.out[1] == N && e.out[2] == r && e.in[0] == d.in[2] &&
+          e.in[3] == g.in[2] && aligned(d.in[2]) && aligned(e.in[2]) && RefSpace(e.in[1]) == kArena &&
+          RefSpace(d.in[0]) == kArena && lora_skip_[i + 1 - begin] == 0 && lora_skip_[i + 2 - begin] == 0 &&
+          !shadow_plan_[i + 1 - begin].want && !shadow_plan_[i + 2 - begin].want) {
+        const uint64_t t_lo = RefOffset(d.in[2]), t_hi = t_lo + M * r * 4;
+        const uint64_t dx_lo = RefOffset(d.in[0]), dx_hi = dx_lo + M * d.out[2] * 4;
+        const uint64_t a_lo = RefOffset(d.in[1]), a_hi = a_lo + d.out[2] * r * 4;
+        const uint64_t w_lo = RefOffset(e.in[1]), w_hi = w_lo + r * N * 4;
+        const uint64_t o_lo = RefOffset(e.in[2]), o_hi = o_lo + M * N * 4;
+        const bool a_in_arena = RefSpace(d.in[1]) == kArena;
+        bool ok = !overlap(b_lo, b_hi, dx_lo, dx_hi) && !(a_in_arena && overlap(b_lo, b_hi, a_lo, a_hi)) &&
+                  !overlap(t_lo, t_hi, x_lo, x_hi) && !overlap(t_lo, t_hi, b_lo, b_hi) &&
+                  !overlap(o_lo, o_hi, x_lo, x_hi) && !overlap(o_lo, o_hi, t_lo, t_hi) &&
+                  !overlap(o_lo, o_hi, w_lo, w_hi) && (o_lo == b_lo || !overlap(o_lo, o_hi, b_lo, b_hi)) &&
+                  unwritten_before(i + 2, w_lo, w_hi);
+        if (ok && o_lo != b_lo) ok = dead_after(i + 2, DeadQuery{b_lo, b_hi, false, ~0ull, 0, 0}, i);
+        if (ok) {
+          LoraFold f;
+          f.fuse = true;
+          f.kind = 1;
+          f.down = d;
+          f.t_ref = d.in[2];
+          f.r = static_cast<uint32_t>(r);
+          f.out_ref = e.in[2];
+          f.absorbed = 2;
+          f.weight_slot = add_weight(g, e.in[1], f.r, static_cast<uint32_t>(N), GemmAlphaOf(e.imm), false);
+          if (o_lo != b_lo) { f.dead[0][0] = b_lo; f.dead[0][1] = b_hi; f.dead_count = 1; }
+          lora_skip_[i + 1 - begin] = 1;
+          lora_skip_[i + 2 - begin] = 1;
+          uint64_t keep_lo[3] = {x_lo, t_lo, w_lo}, keep_hi[3] = {x_hi, t_hi, w_hi};
+          take_add(i + 2, &f, o_lo, o_hi, keep_lo, keep_hi, 3);
+          lora_fold_[i - begin] = f;
+          continue;
+        }
+      }
+    }
+    // kind 2: G; E: out = G.out + dT A^T
+    if (i + 1 < end) {
+      const Instruction& e = program[i + 1];
+      const uint64_t r = e.out[2];
+      if (e.opcode == kGemmNT && e.flags == kFlagGemmAddend && rank_ok(r) && e.out[0] == M && e.out[1] == N &&
+          e.in[3] == g.in[2] && aligned(e.in[0]) && aligned(e.in[2]) && RefSpace(e.in[1]) == kArena &&
+          lora_skip_[i + 1 - begin] == 0 && !shadow_plan_[i + 1 - begin].want) {
+        const uint64_t t_lo = RefOffset(e.in[0]), t_hi = t_lo + M * r * 4;
+        const uint64_t w_lo = RefOffset(e.in[1]), w_hi = w_lo + N * r * 4;
+        const uint64_t o_lo = RefOffset(e.in[2]), o_hi = o_lo + M * N * 4;
+        bool ok = !overlap(o_lo, o_hi, x_lo, x_hi) && !overlap(o_lo, o_hi, t_lo, t_hi) &&
+                  !overlap(o_lo, o_hi, w_lo, w_hi) && !overlap(b_lo, b_hi, t_lo, t_hi) &&
+                  (o_lo == b_lo || !overlap(o_lo, o_hi, b_lo, b_hi)) && unwritten_before(i + 1, w_lo, w_hi);
+        if (ok && o_lo != b_lo) ok = dead_after(i + 1, DeadQuery{b_lo, b_hi, false, ~0ull, 0, 0}, i);
+        if (ok) {
+          LoraFold f;
+          f.fuse = true;
+          f.kind = 2;
+          f.t_ref = e.in[0];
+          f.r = static_cast<uint32_t>(r);
+          f.out_ref = e.in[2];
+          f.absorbed = 1;
+          f.weight_slot = add_weight(g, e.in[1], f.r, static_cast<uint32_t>(N), GemmAlphaOf(e.imm), true);
+          if (o_lo != b_lo) { f.dead[0][0] = b_lo; f.dead[0][1] = b_hi; f.dead_count = 1; }
+          lora_skip_[i + 1 - begin] = 1;
+          uint64_t keep_lo[3] = {x_lo, t_lo, w_lo}, keep_hi[3] = {x_hi, t_hi, w_hi};
+          take_add(i + 1, &f, o_lo, o_hi, keep_lo, keep_hi, 3);
+          lora_fold_[i - begin] = f;
+          continue;
+        }
+      }
+    }
+  }
+  // kind 3: E: part = acc + dT A^T; (up to two instructions); G; kAddEW: part + G.out, already planned as G's
+  // epilogue addend: the addend becomes acc and the expand rides the reduction.
+  for (size_t i = begin; i < end; ++i) {
+    AddFusion& af = add_fusion_[i - begin];
+    const Instruction& g = program[i];
+    if (!af.fuse || !IsRelaxedFrozenGemm(g) || RefSpace(g.in[2]) != kArena || lora_fold_[i - begin].fuse ||
+        bias_fusion_[i - begin].fuse || act_fusion_[i - begin].mode != 0 || lora_skip_[i - begin] != 0)
+      continue;
+    if ((g.flags & (kFlagEpilogueBias | kFlagGemmAddend)) || ActOf(g.flags) != kActNone) continue;
+    const uint64_t M = g.out[0], N = g.out[1];
+    const size_t add_abs = begin + af.add_index;
+    for (size_t back = 1; back <= 3 && i >= begin + back; ++back) {
+      const size_t ea = i - back;
+      const Instruction& e = program[ea];
+      const uint64_t r = e.out[2];
+      if (e.opcode != kGemmNT || e.flags != kFlagGemmAddend || !rank_ok(r) || e.out[0] != M || e.out[1] != N ||
+          e.in[2] != af.x_ref || !aligned(e.in[0]) || !aligned(e.in[3]) || RefSpace(e.in[1]) != kArena ||
+          lora_skip_[ea - begin] != 0 || add_fusion_[ea - begin].fuse || shadow_plan_[ea - begin].want)
+        continue;
+      const uint64_t p_lo = RefOffset(e.in[2]), p_hi = p_lo + M * N * 4;       // part
+      const uint64_t t_lo = RefOffset(e.in[0]), t_hi = t_lo + M * r * 4;       // dT
+      const uint64_t w_lo = RefOffset(e.in[1]), w_hi = w_lo + N * r * 4;       // A
+      const uint64_t c_lo = RefOffset(e.in[3]), c_hi = c_lo + M * N * 4;       // acc
+      const uint64_t o_lo = RefOffset(af.out_ref), o_hi = o_lo + M * N * 4;    // the sum
+      const uint64_t x_lo = RefOffset(g.in[0]), x_hi = x_lo + M * g.out[2] * 4;
+      bool ok = true;
+      for (size_t j = ea + 1; j < i && ok; ++j)   // nothing in between looks at part or changes the expand's operands
+        ok = !touches(j, p_lo, p_hi, false) && !touches(j, p_lo, p_hi, true) && !touches(j, t_lo, t_hi, true) &&
+             !touches(j, w_lo, w_hi, true) && !touches(j, c_lo, c_hi, true);
+      ok = ok && !overlap(o_lo, o_hi, t_lo, t_hi) && !overlap(o_lo, o_hi, w_lo, w_hi) &&
+           !overlap(o_lo, o_hi, x_lo, x_hi) && (o_lo == c_lo || !overlap(o_lo, o_hi, c_lo, c_hi)) &&
+           !overlap(p_lo, p_hi, c_lo, c_hi) && !overlap(p_lo, p_hi, x_lo, x_hi) && unwritten_before(i, w_lo, w_hi);
+      if (ok && o_lo != p_lo) ok = dead_after(add_abs, DeadQuery{p_lo, p_hi, false, ~0ull, 0, 0}, ea);
+      if (!ok) continue;
+      LoraFold f;
+      f.fuse = true;
+      f.kind = 3;
+      f.t_ref = e.in[0];
+      f.r = static_cast<uint32_t>(r);
+      f.out_ref = af.out_ref;
+      f.addend_ref = e.in[3];
+      f.absorbed = 1;   // (the kAddEW is counted by the add fusion it already is)
+      f.weight_slot = add_weight(g, e.in[1], f.r, static_cast<uint32_t>(N), GemmAlphaOf(e.imm), true);
+      lora_skip_[ea - begin] = 2;
+      lora_fold_[i - begin] = f;
+      break;
+    }
+  }
 }
 
 const k::Shadow* CudaBackend::ShadowFor(uint64_t out_ref, uint64_t elems) const {
@@ -1074,13 +1337,17 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   umma::ReleaseReservations(&umma_->ctx);
   // An activation absorbed by the preceding product: nothing runs and nothing is
   // written, so the copy the product published under this output's key stays.
-  const bool absorbed = skip_act_at_ == static_cast<int64_t>(range_index_);
-  if (absorbed) skip_act_at_ = -1;
+  const uint8_t lora_skip = range_index_ < lora_skip_.size() ? lora_skip_[range_index_] : 0;
+  const bool absorbed = skip_act_at_ == static_cast<int64_t>(range_index_) || lora_skip == 2;
+  if (skip_act_at_ == static_cast<int64_t>(range_index_)) skip_act_at_ = -1;
+  if (lora_skip == 2)   // an expand product deferred into a later frozen product: its output stays unwritten
+    for (size_t i = 0; i < ext.count; ++i)
+      if (ext.e[i].space == kArena && ext.e[i].write) elided_.push_back({ext.e[i].off, ext.e[i].off + ext.e[i].bytes});
   // (A kAddBias done by the preceding product's epilogue reads nothing either.)
   // (A kAddEW done by the kernel before it: that kernel's dispatch has already
   // dropped older copies of the sum's range and may have published the new one.)
   const bool add_done = skip_add_at_ == static_cast<int64_t>(range_index_) ||
-                        skip_attn_dv_at_ == static_cast<int64_t>(range_index_);
+                        skip_attn_dv_at_ == static_cast<int64_t>(range_index_) || lora_skip == 1;
   const bool bias_done = (skip_next_add_bias_ && ins.opcode == kAddBias) || add_done;
   if (!elided_.empty() && !absorbed && !bias_done) {
     for (size_t i = 0; i < ext.count; ++i) {
@@ -1117,8 +1384,12 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
     }
   }
 
+  if (range_index_ == 0 && !lora_weights_.empty()) {   // every adapter matrix of the range, cut once
+    k::LoraSplitWeights(d_lora_table_, static_cast<int>(lora_weights_.size()), lora_max_n_, stream_);
+    ++counters_.kernel_launches;
+  }
   const uint64_t fused_before = counters_.fused_dispatches;
-  if (!absorbed)
+  if (!absorbed && lora_skip != 1)
     if (auto r = Dispatch(ins, params, ext); !r) return r;
   ++counters_.instructions;
 
@@ -1164,7 +1435,7 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   return {};
 }
 
-Status CudaBackend::DispatchGemm(const Instruction& ins) {
+k::GemmArgs CudaBackend::GemmArgsOf(const Instruction& ins) const {
   k::GemmArgs a;
   a.A = Rd(ins.in[0]);
   a.B = Rd<uint8_t>(ins.in[1]);
@@ -1187,6 +1458,11 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
       a.alpha = BitsToF32(ins.in[3]);
     }
   }
+  return a;
+}
+
+Status CudaBackend::DispatchGemm(const Instruction& ins) {
+  k::GemmArgs a = GemmArgsOf(ins);
   // The relaxed permission: frozen-weight products may run on the bf16 tensor
   // cores (activation rounded to bf16 once, weight exact, f32 accumulate).
   if ((ins.flags & kFlagRelaxed) && relaxed_allowed_ && !a.a_transposed && !a.accumulate &&
@@ -1214,6 +1490,28 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
       a.fuse_shadow_scale = cur_shadow_.k_scale;
       a.store_c = af->store_c;
     }
+    const LoraFold* lf = range_index_ < lora_fold_.size() && lora_fold_[range_index_].fuse
+                             ? &lora_fold_[range_index_] : nullptr;
+    if (lf) {   // the adapter's expand product rides this product's reduction
+      if (lf->kind == 1) {   // its down product t = x A first (the plan has it after this instruction)
+        const k::GemmArgs d = GemmArgsOf(lf->down);
+        k::GemmExact(d, stream_);
+        ++counters_.kernel_launches;
+        umma::InvalidateRange(&umma_->ctx, RefOffset(lf->down.in[2]), d.M * d.N * 4);
+      }
+      if (!k::LoraSplitRows(Rd(lf->t_ref), d_lora_t_, a.M, lf->r, stream_))
+        return std::unexpected("cuda: low-rank fold: the factor cannot be split (rank or alignment)");
+      ++counters_.kernel_launches;
+      const uint32_t kx = k::LoraSplitColumns(lf->r);
+      a.aux_a = d_lora_t_;
+      a.aux_b = d_lora_w_ + static_cast<uint64_t>(lf->weight_slot) * lora_max_n_ * lora_max_kx_;
+      a.aux_k = kx;
+      a.C = Wr(lf->out_ref);
+      if (lf->addend_ref != kNullRef) {
+        a.addend = Rd(lf->addend_ref);
+        a.addend_after_bias = true;
+      }
+    }
     int launches = 0;
     const std::string err = umma::TryGemm(&umma_->ctx, a, RefSpace(ins.in[1]) == kRodata ? 1 : 2,
                                           RefOffset(ins.in[1]), RefOffset(ins.in[0]),
@@ -1238,9 +1536,15 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
         for (int e = 0; e < af->elided_count; ++e)
           pending_elided_.push_back({af->elided[e][0], af->elided[e][1]});
       }
+      if (lf) {
+        counters_.fused_dispatches += lf->absorbed;
+        umma::InvalidateRange(&umma_->ctx, RefOffset(lf->out_ref), a.M * a.N * 4);
+        for (int e = 0; e < lf->dead_count; ++e) pending_elided_.push_back({lf->dead[e][0], lf->dead[e][1]});
+      }
       return {};
     }
     if (!err.empty()) return std::unexpected("cuda: " + err);
+    if (lf) return std::unexpected("cuda: low-rank fold: the tensor-core path refused a product it was planned on");
     // launches == 0: the shape is outside the tensor-core kernel's domain.
     if (fuse) {
       a.bias = nullptr;

@@ -23,6 +23,7 @@
 
 #include <cstdint>
 #include <expected>
+#include <map>
 #include <memory>
 #include <span>
 #include <string>
@@ -138,6 +139,10 @@ class CudaBackend {
   // Off: no kAddBias or activation is absorbed into a product's epilogue (takes
   // effect at the next BeginRange).
   void SetEpilogueFusion(bool enabled) { epilogue_fusion_ = enabled; }
+
+  // Off: the rank-r expand product of an adapter stays its own kernel instead of
+  // riding the frozen product's reduction (takes effect at the next BeginRange).
+  void SetLoraFold(bool enabled) { lora_fold_enabled_ = enabled; }
 
   // CUDA-graph support for the engine.  The optimizer kernels read the step's
   // learning rate and bias corrections from a small device block.  A captured
@@ -332,6 +337,53 @@ class CudaBackend {
   std::vector<ShadowPlan> attn_dv_shadow_;   // the dV instruction's copy plan, made by the pair's kernel
   int64_t skip_attn_dv_at_ = -1;
   int64_t skip_add_at_ = -1;            // the absorbed kAddEW (its output IS written, by the product)
+
+  // The rank-r expand product of an adapter, C' = C + s T B, folded into the
+  // frozen product that makes C (the reference's own GPU backend folds the same
+  // pair: runtime/executor/metal_backend.mm:1155-1316): T and the adapter matrix
+  // are cut into bf16 pieces and appended to the tensor-core reduction
+  // (k_lora.cu), so the expand kernel's read-modify-write of C disappears.  Three
+  // instruction patterns, per range position of the frozen product G:
+  //   kind 1 (forward)   G; D: t = x A; E: out = G.out + s t B      D runs early, inside G's dispatch
+  //   kind 2 (backward)  G; E: out = G.out + dT A^T
+  //   kind 3 (backward)  E: part = acc + dT A^T; ...; G; kAddEW: part + G.out    E never runs
+  // each optionally followed by a kAddEW that the epilogue absorbs as well.
+  // Engine / lazy coherence only; every intermediate left unwritten is proven dead.
+  struct LoraFold {
+    bool fuse = false;
+    int kind = 0;
+    Instruction down{};             // kind 1: the down product, executed by the fold
+    uint64_t t_ref = kNullRef;      // the [M, r] factor whose split copy feeds the reduction
+    uint32_t r = 0;
+    uint32_t weight_slot = 0;       // entry of the range's split-weight table
+    uint64_t out_ref = kNullRef;    // where the sum is written
+    uint64_t addend_ref = kNullRef; // epilogue addend (the absorbed kAddEW's other operand, or kind 3's acc)
+    uint32_t absorbed = 0;          // instructions this dispatch stands for besides G
+    uint64_t dead[3][2] = {{0, 0}, {0, 0}, {0, 0}};   // f32 ranges left unwritten
+    int dead_count = 0;
+  };
+  std::vector<LoraFold> lora_fold_;          // per range position (of G)
+  std::vector<uint8_t> lora_skip_;           // per range position: 1 done by an earlier dispatch, 2 never runs
+  std::vector<k::LoraWeight> lora_weights_;  // the range's adapter matrices (host copy of the table)
+  uint32_t lora_max_n_ = 0, lora_max_kx_ = 0;
+  // The table and the split weights belong to ONE range (a captured range keeps
+  // reading them at every replay), so each (program, begin) has its own pair,
+  // kept until the next Bind; the row operand is scratch shared by all.
+  struct LoraRangeBuffers {
+    k::LoraWeight* table = nullptr;
+    size_t table_capacity = 0;
+    uint16_t* weights = nullptr;   // [entries][max n_out][max kx] bf16
+    uint64_t weights_capacity = 0;
+  };
+  std::map<std::pair<const Instruction*, size_t>, LoraRangeBuffers> lora_ranges_;
+  k::LoraWeight* d_lora_table_ = nullptr;    // the current range's
+  uint16_t* d_lora_w_ = nullptr;
+  uint16_t* d_lora_t_ = nullptr;             // [rows][kx] bf16, reused by every fold
+  uint64_t lora_t_capacity_ = 0;
+  bool lora_fold_enabled_ = true;
+  Status PrepareLoraFolds(const Instruction* program, size_t begin, uint64_t max_rows);
+  void FreeLoraRanges();
+  k::GemmArgs GemmArgsOf(const Instruction& ins) const;
 
   Counters counters_;
   struct UmmaState;

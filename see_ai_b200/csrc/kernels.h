@@ -201,6 +201,26 @@ void MseRealRowLoss(const float* pred, const float* target, size_t real_rows, si
 void QuantizeColumns(const float* w, size_t K, size_t N, int8_t* levels, float* scales,
                      unsigned int* maxbits_scratch, cudaStream_t s);
 
+// ---- low-rank (adapter) term folded into a tensor-core GEMM --------------------
+// The f32 factors of s * T * B are cut into three bf16 pieces each and laid out
+// as extra K columns of the base product (k_lora.cu).  LoraSplitColumns(r) is the
+// width of both operands: 6 r rounded up to a multiple of 64.
+uint32_t LoraSplitColumns(uint32_t r);
+// out [M, LoraSplitColumns(r)] bf16 from t [M, r] f32, r in {4, 8, 12, 16}.
+// False (nothing launched) for another rank or a misaligned pointer.
+bool LoraSplitRows(const float* t, uint16_t* out, size_t M, uint32_t r, cudaStream_t s);
+struct LoraWeight {
+  const float* src;         // the adapter matrix: B [r, n_out], or A [n_out, r] when by_column
+  uint16_t* dst;            // [n_out, kx] bf16
+  const float* col_scale;   // the base product's per-column epilogue scale, or null
+  float tile_alpha;         // ... or its scalar scale
+  float alpha;              // the low-rank term's own factor
+  uint32_t n_out, r, kx;
+  uint32_t by_column;
+};
+// Every entry of a device-resident table in one launch.
+void LoraSplitWeights(const LoraWeight* table, int count, uint32_t max_n_out, cudaStream_t s);
+
 // ---- GEMM -------------------------------------------------------------------
 enum class BType : uint8_t { kF32 = 0, kI8 = 1, kBf16 = 2 };
 constexpr int kFuseNone = 0, kFuseActFwd = 1, kFuseActBwd = 2;   // GemmArgs::fuse_mode
@@ -228,6 +248,11 @@ struct GemmArgs {
   const float* fuse_shadow_scale = nullptr;
   bool store_c = true;
   bool addend_after_bias = false;   // tensor-core path: v = addend + (product + bias)
+  // Tensor-core path only: a low-rank term appended to the reduction (see
+  // UmmaEpilogue::aux_k_blocks): aux_a [M, aux_k] and aux_b [N, aux_k], bf16.
+  const uint16_t* aux_a = nullptr;
+  const uint16_t* aux_b = nullptr;
+  uint32_t aux_k = 0;
   // Exact path, rank-r expand kernel only: a following kAddEW rides along
   // (tail_out = tail_addend + result; C is not written).  GemmExact returns whether
   // it did.

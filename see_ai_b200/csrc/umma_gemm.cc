@@ -272,10 +272,14 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
   }
   slot->last_use = ++impl->tick;
 
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_b, aux_a, aux_b;
   if (!EncodeBf16Map(impl, &map_a, slot->buf, a.M, a.K, k::umma_cfg::kBlockM) ||
       !EncodeBf16Map(impl, &map_b, w, a.N, a.K, k::umma_cfg::kBlockN))
     return "tensor-core path: cuTensorMapEncodeTiled refused the operand layout";
+  const bool has_aux = a.aux_a && a.aux_b && a.aux_k >= 64 && a.aux_k % 64 == 0;
+  if (has_aux && (!EncodeBf16Map(impl, &aux_a, a.aux_a, a.M, a.aux_k, k::umma_cfg::kBlockM) ||
+                  !EncodeBf16Map(impl, &aux_b, a.aux_b, a.N, a.aux_k, k::umma_cfg::kBlockN)))
+    return "tensor-core path: cuTensorMapEncodeTiled refused the low-rank operand layout";
 
   k::UmmaEpilogue ep{};
   ep.C = a.C;
@@ -295,8 +299,11 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
   ep.shadow_k_scale = a.fuse_shadow_scale;
   ep.store_c = a.store_c ? 1 : 0;
   ep.addend_last = a.addend_after_bias ? 1 : 0;
+  ep.aux_k_blocks = has_aux ? a.aux_k / 64 : 0;
   if (impl->prof_before) cudaEventRecord(impl->prof_before, stream);
-  if (cudaError_t e = k::UmmaGemmLaunch(map_a, map_b, ep, stream); e != cudaSuccess)
+  if (cudaError_t e = k::UmmaGemmLaunch(map_a, map_b, ep, stream, has_aux ? &aux_a : nullptr,
+                                        has_aux ? &aux_b : nullptr);
+      e != cudaSuccess)
     return std::string("tensor-core GEMM launch: ") + cudaGetErrorString(e);
   if (impl->prof_after) {
     cudaEventRecord(impl->prof_after, stream);

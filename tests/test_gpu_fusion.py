@@ -171,7 +171,7 @@ def test_backward_activation_rides_the_gemm_epilogue(size, case):
 # bit, as the same engine with epilogue fusion switched off — eager, while the
 # graphs are captured, and on replay.
 
-def _engine_run(fusion: bool, steps: int = 4):
+def _engine_run(fusion: bool, steps: int = 4, lora_fold: bool = False):
     import torch
     from see_ai_b200 import synth
     from see_ai_b200.engine import Engine
@@ -186,6 +186,7 @@ def _engine_run(fusion: bool, steps: int = 4):
     with torch.cuda.stream(stream):
         eng.backend.set_stream(stream.cuda_stream)
         eng.backend.set_epilogue_fusion(fusion)
+        eng.backend.set_lora_fold(lora_fold)
         eng.load(blob)
         eng.set_horizon(cfg.steps)
         for _ in range(steps):
@@ -200,6 +201,24 @@ def _engine_run(fusion: bool, steps: int = 4):
         fused = eng.backend.counters().fused_dispatches
     eng.close()
     return persist, np.array(losses, dtype=np.float32), launches, fused
+
+
+def test_engine_step_with_the_low_rank_fold_stays_within_f32_noise_of_the_step_without():
+    """The adapter expand products riding the frozen products' reductions change
+    the arithmetic of those sums (pieces of the factors on the tensor cores
+    instead of f32 multiply-adds): the step must stay within what such a change
+    of summation order does — far inside the bf16 rounding of the frozen products
+    themselves."""
+    p_on, l_on, n_on, f_on = _engine_run(True, lora_fold=True)
+    p_off, l_off, n_off, f_off = _engine_run(True, lora_fold=False)
+    assert np.isfinite(l_on).all()
+    assert np.allclose(l_on, l_off, rtol=2e-4, atol=0)
+    a, b = p_on.view(np.float32).astype(np.float64), p_off.view(np.float32).astype(np.float64)
+    assert np.sqrt(np.mean((a - b) ** 2)) <= 5e-2 * np.sqrt(np.mean(b ** 2))   # four AdamW steps amplify sign flips
+    # Two layers, four adapters each: eight forward and eight backward expand kernels ride a product.
+    # (The launch count does not fall: a small kernel cuts each factor into pieces where the expand
+    # kernel ran.  What falls is the traffic: the expand read and rewrote the whole [rows, width] sum.)
+    assert f_on - f_off >= 16
 
 
 def test_engine_step_with_fusions_is_the_unfused_step_bit_for_bit():
