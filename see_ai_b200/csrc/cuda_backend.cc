@@ -1114,13 +1114,23 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
     const uint64_t o_lo = RefOffset(af.out_ref), o_hi = o_lo + (e_out_hi - e_out_lo);
     for (int q = 0; q < keeps && ok; ++q)   // the sum must not land on anything the product still reads
       if (overlap(o_lo, o_hi, keep_lo[q], keep_hi[q])) ok = false;
+    // ... and lies exactly over, or apart from, each range the fold leaves unwritten
+    // (the plan often puts the sum where the un-adapted product was).
+    for (int q = 0; q < f->dead_count && ok; ++q)
+      if (overlap(o_lo, o_hi, f->dead[q][0], f->dead[q][1]) && o_lo != f->dead[q][0]) ok = false;
     if (ok) {
       f->out_ref = af.out_ref;
       f->addend_ref = af.x_ref;
       ++f->absorbed;
       lora_skip_[af.add_index] = 1;                       // the sum is written by the product
       lora_skip_[e_abs - begin] = 2;                      // the expand's own output never is
-      f->dead[f->dead_count][0] = e_out_lo; f->dead[f->dead_count][1] = e_out_hi; ++f->dead_count;
+      int kept = 0;
+      for (int q = 0; q < f->dead_count; ++q)             // a range the sum lands on is written after all
+        if (f->dead[q][0] != o_lo) { f->dead[kept][0] = f->dead[q][0]; f->dead[kept][1] = f->dead[q][1]; ++kept; }
+      f->dead_count = kept;
+      if (e_out_lo != o_lo) {
+        f->dead[f->dead_count][0] = e_out_lo; f->dead[f->dead_count][1] = e_out_hi; ++f->dead_count;
+      }
     }
     af = AddFusion{};   // either way the expand kernel no longer runs
   };
@@ -1148,7 +1158,7 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
         const bool a_in_arena = RefSpace(d.in[1]) == kArena;
         bool ok = !overlap(b_lo, b_hi, dx_lo, dx_hi) && !(a_in_arena && overlap(b_lo, b_hi, a_lo, a_hi)) &&
                   !overlap(t_lo, t_hi, x_lo, x_hi) && !overlap(t_lo, t_hi, b_lo, b_hi) &&
-                  !overlap(o_lo, o_hi, x_lo, x_hi) && !overlap(o_lo, o_hi, t_lo, t_hi) &&
+                  !overlap(o_lo, o_hi, t_lo, t_hi) &&
                   !overlap(o_lo, o_hi, w_lo, w_hi) && (o_lo == b_lo || !overlap(o_lo, o_hi, b_lo, b_hi)) &&
                   unwritten_before(i + 2, w_lo, w_hi);
         if (ok && o_lo != b_lo) ok = dead_after(i + 2, DeadQuery{b_lo, b_hi, false, ~0ull, 0, 0}, i);
@@ -1165,8 +1175,10 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
           if (o_lo != b_lo) { f.dead[0][0] = b_lo; f.dead[0][1] = b_hi; f.dead_count = 1; }
           lora_skip_[i + 1 - begin] = 1;
           lora_skip_[i + 2 - begin] = 1;
-          uint64_t keep_lo[3] = {x_lo, t_lo, w_lo}, keep_hi[3] = {x_hi, t_hi, w_hi};
-          take_add(i + 2, &f, o_lo, o_hi, keep_lo, keep_hi, 3);
+          // (The sum may land on the product's own f32 operand: the product reads its bf16 copy,
+          // made before the kernel starts.  Not on t, which the backward sweep reads.)
+          uint64_t keep_lo[3] = {t_lo, w_lo, 0}, keep_hi[3] = {t_hi, w_hi, 0};
+          take_add(i + 2, &f, o_lo, o_hi, keep_lo, keep_hi, 2);
           lora_fold_[i - begin] = f;
           continue;
         }
@@ -1182,8 +1194,9 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
         const uint64_t t_lo = RefOffset(e.in[0]), t_hi = t_lo + M * r * 4;
         const uint64_t w_lo = RefOffset(e.in[1]), w_hi = w_lo + N * r * 4;
         const uint64_t o_lo = RefOffset(e.in[2]), o_hi = o_lo + M * N * 4;
-        bool ok = !overlap(o_lo, o_hi, x_lo, x_hi) && !overlap(o_lo, o_hi, t_lo, t_hi) &&
-                  !overlap(o_lo, o_hi, w_lo, w_hi) && !overlap(b_lo, b_hi, t_lo, t_hi) &&
+        // The sum may reuse the slot of dY or of dT (the plans do): both are read through copies
+        // made before the kernel starts, and the plan's own expand kernel wrote the sum there too.
+        bool ok = !overlap(o_lo, o_hi, w_lo, w_hi) && !overlap(b_lo, b_hi, t_lo, t_hi) &&
                   (o_lo == b_lo || !overlap(o_lo, o_hi, b_lo, b_hi)) && unwritten_before(i + 1, w_lo, w_hi);
         if (ok && o_lo != b_lo) ok = dead_after(i + 1, DeadQuery{b_lo, b_hi, false, ~0ull, 0, 0}, i);
         if (ok) {
@@ -1197,8 +1210,8 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
           f.weight_slot = add_weight(g, e.in[1], f.r, static_cast<uint32_t>(N), GemmAlphaOf(e.imm), true);
           if (o_lo != b_lo) { f.dead[0][0] = b_lo; f.dead[0][1] = b_hi; f.dead_count = 1; }
           lora_skip_[i + 1 - begin] = 1;
-          uint64_t keep_lo[3] = {x_lo, t_lo, w_lo}, keep_hi[3] = {x_hi, t_hi, w_hi};
-          take_add(i + 1, &f, o_lo, o_hi, keep_lo, keep_hi, 3);
+          uint64_t keep_lo[3] = {w_lo, 0, 0}, keep_hi[3] = {w_hi, 0, 0};
+          take_add(i + 1, &f, o_lo, o_hi, keep_lo, keep_hi, 1);
           lora_fold_[i - begin] = f;
           continue;
         }
@@ -1234,8 +1247,7 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
       for (size_t j = ea + 1; j < i && ok; ++j)   // nothing in between looks at part or changes the expand's operands
         ok = !touches(j, p_lo, p_hi, false) && !touches(j, p_lo, p_hi, true) && !touches(j, t_lo, t_hi, true) &&
              !touches(j, w_lo, w_hi, true) && !touches(j, c_lo, c_hi, true);
-      ok = ok && !overlap(o_lo, o_hi, t_lo, t_hi) && !overlap(o_lo, o_hi, w_lo, w_hi) &&
-           !overlap(o_lo, o_hi, x_lo, x_hi) && (o_lo == c_lo || !overlap(o_lo, o_hi, c_lo, c_hi)) &&
+      ok = ok && !overlap(o_lo, o_hi, w_lo, w_hi) && (o_lo == c_lo || !overlap(o_lo, o_hi, c_lo, c_hi)) &&
            !overlap(p_lo, p_hi, c_lo, c_hi) && !overlap(p_lo, p_hi, x_lo, x_hi) && unwritten_before(i, w_lo, w_hi);
       if (ok && o_lo != p_lo) ok = dead_after(add_abs, DeadQuery{p_lo, p_hi, false, ~0ull, 0, 0}, ea);
       if (!ok) continue;

@@ -265,7 +265,6 @@ def test_data_parallel_standalone_clip_reaches_the_update(case_name):
         ex.bind(a, ro)
         arenas.append(a)
         execs.append(ex)
-    moments = [(i.ins[3], i.out[0]) for i in train[opt:] if i.opcode == Op.ADAMW_STEP]
     for step in range(1, 4):
         shards = [(rng.standard_normal((rows, dim)).astype(np.float32) * 3.0,   # large inputs: the clip must bite
                    rng.integers(0, classes, size=rows).astype(np.int32)) for _ in range(2)]
@@ -298,12 +297,15 @@ def test_data_parallel_standalone_clip_reaches_the_update(case_name):
         states = [e.read_persistent() for e in engines]
         assert np.array_equal(states[0], states[1])
         want = arenas[0][:h["persistent_size"]]
-        assert np.allclose(states[0].view(np.float32), want.view(np.float32), rtol=5e-3, atol=1e-6), step
-        # The second moments are the squares of what the optimizer was fed: an update that ignored the
-        # clip would leave them larger by the square of the clip factor.
-        for (off, n) in moments:
-            assert np.allclose(states[0][off:off + 4 * n].view(np.float32), want[off:off + 4 * n].view(np.float32),
-                               rtol=1e-3, atol=1e-12), step
+        # Per optimizer tensor, against that tensor's own scale: AdamW turns a 1e-6 difference in a
+        # gradient element far below the block's maximum into a visible fraction of the learning
+        # rate, so element-wise relative bounds are meaningless here.  An update that ignored the
+        # clip would leave second moments larger by the square of the clip factor (several times).
+        for ins in (i for i in train[opt:] if i.opcode == Op.ADAMW_STEP):
+            for ref in (ins.ins[0], ins.ins[2], ins.ins[3]):
+                ok, ratio = compare(states[0][ref:ref + 4 * ins.out[0]].tobytes(),
+                                    want[ref:ref + 4 * ins.out[0]].tobytes(), 2e-2, 1e-12)
+                assert ok, (step, hex(ref), ratio)
     for e in engines:
         e.close()
 
