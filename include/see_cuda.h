@@ -97,6 +97,10 @@ int see_cuda_set_epilogue_fusion(see_cuda_backend* h, int enabled);
 /* 0: an adapter's rank-r expand product stays its own kernel instead of riding the
  * frozen product's tensor-core reduction (lazy coherence only); default 1. */
 int see_cuda_set_lora_fold(see_cuda_backend* h, int enabled);
+/* 0: the rank-r adapter products keep one rounding per operation (the CPU's
+ * arithmetic, bit for bit) in lazy coherence too; default 1: fused multiply-adds
+ * there.  Strict coherence is always bit-exact. */
+int see_cuda_set_adapter_fma(see_cuda_backend* h, int enabled);
 /* Data parallelism: optimizer steps read gradients inside [block_offset,
  * block_offset + block_bytes) as the rank-ordered sum of `ranks` gathered
  * copies (device memory, copy r at gathered + r * block_bytes) times 1/ranks. */

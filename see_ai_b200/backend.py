@@ -32,7 +32,7 @@ EXPORTED_SYMBOLS = [
     "see_cuda_set_gradient_gather",
     "see_cuda_set_profiling", "see_cuda_take_profile",
     "see_cuda_xent_forward_static", "see_cuda_static_max_rows", "see_cuda_static_last_error",
-    "see_cuda_quantize_columns", "see_cuda_set_lora_fold",
+    "see_cuda_quantize_columns", "see_cuda_set_lora_fold", "see_cuda_set_adapter_fma",
 ]
 
 
@@ -105,6 +105,7 @@ def load_library() -> ctypes.CDLL:
     lib.see_cuda_take_profile.restype = ctypes.c_int64
     lib.see_cuda_quantize_columns.argtypes = [vp, vp, u64, u64, vp, vp]
     lib.see_cuda_set_lora_fold.argtypes = [vp, i32]
+    lib.see_cuda_set_adapter_fma.argtypes = [vp, i32]
     lib.see_cuda_xent_forward_static.argtypes = [vp, vp, vp, vp, u64, u64, i32, vp]
     lib.see_cuda_static_max_rows.restype = u64
     lib.see_cuda_static_last_error.restype = ctypes.c_char_p
@@ -245,6 +246,9 @@ class CudaBackend:
 
     def set_lora_fold(self, enabled: bool):
         self._check(self.lib.see_cuda_set_lora_fold(self.h, int(enabled)))
+
+    def set_adapter_fma(self, enabled: bool):
+        self._check(self.lib.see_cuda_set_adapter_fma(self.h, int(enabled)))
 
     def set_gradient_gather(self, ranks: int, gathered_ptr: int, block_offset: int,
                             block_bytes: int):

@@ -34,6 +34,7 @@ CU_SOURCES = {
     "k_attn_umma.cu": [],
     "k_no_alloc.cu": ["-fmad=false"],
     "k_lora.cu": [],
+    "k_gemm_skinny_fast.cu": [],
 }
 CC_SOURCES = ["extents.cc", "cuda_backend.cc", "c_api.cc", "umma_gemm.cc", "engine.cc"]
 

@@ -1506,7 +1506,8 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
                              ? &lora_fold_[range_index_] : nullptr;
     if (lf) {   // the adapter's expand product rides this product's reduction
       if (lf->kind == 1) {   // its down product t = x A first (the plan has it after this instruction)
-        const k::GemmArgs d = GemmArgsOf(lf->down);
+        k::GemmArgs d = GemmArgsOf(lf->down);
+        d.contract_fma = adapter_fma_;
         k::GemmExact(d, stream_);
         ++counters_.kernel_launches;
         umma::InvalidateRange(&umma_->ctx, RefOffset(lf->down.in[2]), d.M * d.N * 4);
@@ -1583,6 +1584,8 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
     a.tail_addend = Rd(tail->x_ref);
     a.tail_out = Wr(tail->out_ref);
   }
+  // The engine does not observe whether a rank-r product rounded once or twice per term.
+  a.contract_fma = coherence_ == Coherence::kLazy && adapter_fma_;
   const bool tail_done = k::GemmExact(a, stream_);
   ++counters_.kernel_launches;
   if (tail && tail_done) {

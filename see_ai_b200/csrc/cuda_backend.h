@@ -144,6 +144,10 @@ class CudaBackend {
   // riding the frozen product's reduction (takes effect at the next BeginRange).
   void SetLoraFold(bool enabled) { lora_fold_enabled_ = enabled; }
 
+  // Off: the rank-r adapter products keep the CPU's one-rounding-per-operation
+  // arithmetic even in lazy coherence (default on: fused multiply-adds there).
+  void SetAdapterFma(bool enabled) { adapter_fma_ = enabled; }
+
   // CUDA-graph support for the engine.  The optimizer kernels read the step's
   // learning rate and bias corrections from a small device block.  A captured
   // range contains no upload of that block: before it captures or replays a range
@@ -381,6 +385,7 @@ class CudaBackend {
   uint16_t* d_lora_t_ = nullptr;             // [rows][kx] bf16, reused by every fold
   uint64_t lora_t_capacity_ = 0;
   bool lora_fold_enabled_ = true;
+  bool adapter_fma_ = true;
   Status PrepareLoraFolds(const Instruction* program, size_t begin, uint64_t max_rows);
   void FreeLoraRanges();
   k::GemmArgs GemmArgsOf(const Instruction& ins) const;

@@ -72,4 +72,11 @@ bool SkinnyTnPartials(const Params& p, size_t chunks, cudaStream_t s);
 
 }  // namespace see::k::exact
 
+// The same three with multiply-adds contracted (see k_gemm_skinny.cu).
+namespace see::k::fast {
+bool SkinnyReduce(const exact::Params& p, bool lane_order, cudaStream_t s);
+bool SkinnyExpand(const exact::Params& p, bool lane_order, cudaStream_t s);
+bool SkinnyTnPartials(const exact::Params& p, size_t chunks, cudaStream_t s);
+}  // namespace see::k::fast
+
 #endif  // SEE_CUDA_GEMM_EXACT_COMMON_CUH_

@@ -368,10 +368,13 @@ bool GemmExact(const GemmArgs& a, cudaStream_t s) {
     pt.tail_addend = a.tail_addend;
     pt.tail_out = a.tail_out;
   }
+  const auto reduce = a.contract_fma ? fast::SkinnyReduce : exact::SkinnyReduce;
+  const auto expand = a.contract_fma ? fast::SkinnyExpand : exact::SkinnyExpand;
+  const auto tn_partials = a.contract_fma ? fast::SkinnyTnPartials : exact::SkinnyTnPartials;
   if (a.b_transposed) {
     if (a.b_type == BType::kF32) {
-      if (SkinnyReduce(p, true, s)) return false;
-      if (SkinnyExpand(pt, true, s)) return pt.tail_out != nullptr;
+      if (reduce(p, true, s)) return false;
+      if (expand(pt, true, s)) return pt.tail_out != nullptr;
     }
     switch (a.b_type) {
       case BType::kF32: LaunchLane<float>(p, s); break;
@@ -389,7 +392,7 @@ bool GemmExact(const GemmArgs& a, cudaStream_t s) {
         chunks * a.M * a.N <= a.split_scratch_floats) {
       p.k_chunk = SplitKChunkRows(a.M, a.N, a.K);
       p.partials = a.split_scratch;
-      if (!SkinnyTnPartials(p, chunks, s)) LaunchQuad<true, float>(p, static_cast<unsigned>(chunks), s);
+      if (!tn_partials(p, chunks, s)) LaunchQuad<true, float>(p, static_cast<unsigned>(chunks), s);
       const size_t blocks = (a.M * a.N + 31) / 32;
       SplitKFoldKernel<<<static_cast<unsigned>(blocks), 32 * kFoldGroups, 0, s>>>(p, chunks);
       return false;
@@ -398,8 +401,8 @@ bool GemmExact(const GemmArgs& a, cudaStream_t s) {
     return false;
   }
   if (a.b_type == BType::kF32) {
-    if (SkinnyReduce(p, false, s)) return false;
-    if (SkinnyExpand(pt, false, s)) return pt.tail_out != nullptr;
+    if (reduce(p, false, s)) return false;
+    if (expand(pt, false, s)) return pt.tail_out != nullptr;
   }
   switch (a.b_type) {
     case BType::kF32: LaunchQuad<false, float>(p, 1, s); break;

@@ -9,11 +9,24 @@
 // (reference: runtime/executor/gemm.cc:73-187 quad order, :346-527 lane
 // order); compiled with -fmad=false.  Only the assignment of elements to
 // threads differs from the general tile kernels.
+//
+// This file is compiled twice.  As see::k::exact (with -fmad=false) it is the
+// bit-exact form the strict seam uses.  As see::k::fast (through
+// k_gemm_skinny_fast.cu, multiply-adds contracted) it is the form the engine
+// uses where the plan does not observe the bits: the same kernels, the same
+// fixed reduction orders — so still identical run to run — at one instruction
+// per multiply-add instead of two, and within a few 2^-24 of the exact form.
 #include <atomic>
 
 #include "gemm_exact_common.cuh"
 
-namespace see::k::exact {
+#ifndef SEE_SKINNY_NAMESPACE
+#define SEE_SKINNY_NAMESPACE exact
+#endif
+
+namespace see::k::SEE_SKINNY_NAMESPACE {
+
+using namespace see::k::exact;   // Params, ApplyAct, Aligned16 (a no-op in the exact build)
 
 namespace {
 
@@ -422,7 +435,7 @@ bool LaunchReduce(const Params& p, bool lane_order, cudaStream_t s) {
 
 }  // namespace
 
-bool SkinnyReduce(const Params& p, bool lane_order, cudaStream_t s) {
+bool SkinnyReduce(const exact::Params& p, bool lane_order, cudaStream_t s) {
   if (p.N != 4 && p.N != 8 && p.N != 16) return false;
   if (p.K < 64 || (p.K & 15) != 0 || p.K > kReduceMaxK || p.M < 256) return false;
   if (p.accumulate || p.b_col_scale || p.a_k_scale || p.partials) return false;
@@ -578,7 +591,7 @@ void LaunchExpand(const Params& p, bool lane_order, cudaStream_t s) {
 
 }  // namespace
 
-bool SkinnyExpand(const Params& p, bool lane_order, cudaStream_t s) {
+bool SkinnyExpand(const exact::Params& p, bool lane_order, cudaStream_t s) {
   if (p.K != 4 && p.K != 8 && p.K != 12 && p.K != 16) return false;
   if ((p.N & 3) != 0 || p.N < 64 || p.M < 64) return false;
   if (p.M > 65535u * static_cast<size_t>(kExpandRows)) return false;
@@ -720,7 +733,7 @@ bool LaunchTn(const Params& p, int R, dim3 grid, cudaStream_t s) {
 
 }  // namespace
 
-bool SkinnyTnPartials(const Params& p, size_t chunks, cudaStream_t s) {
+bool SkinnyTnPartials(const exact::Params& p, size_t chunks, cudaStream_t s) {
   if (p.k_chunk == 0 || p.k_chunk > static_cast<size_t>(kTnChunk) || (p.k_chunk & 15) != 0 ||
       !p.partials || chunks > 65535)
     return false;
@@ -737,4 +750,4 @@ bool SkinnyTnPartials(const Params& p, size_t chunks, cudaStream_t s) {
   return wide_a ? LaunchTn<true>(p, R, grid, s) : LaunchTn<false>(p, R, grid, s);
 }
 
-}  // namespace see::k::exact
+}  // namespace see::k::SEE_SKINNY_NAMESPACE

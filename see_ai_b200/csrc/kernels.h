@@ -258,6 +258,10 @@ struct GemmArgs {
   // it did.
   const float* tail_addend = nullptr;
   float* tail_out = nullptr;
+  // Exact path: the shape-specialised rank-r kernels may contract multiply-adds
+  // (same reduction order, one rounding per term instead of two).  Set by the
+  // engine; never through the strict seam.
+  bool contract_fma = false;
   // Scratch for the split-K form of the transposed-A product (optional).
   float* split_scratch = nullptr;
   size_t split_scratch_floats = 0;

@@ -190,3 +190,62 @@ def test_pattern_is_left_alone_when_an_intermediate_is_read_later():
     split, c_split = _run(prog, arena0, ro, False)
     assert c_fused.fused_dispatches == 0
     assert np.array_equal(fused, split)
+
+
+def test_adapter_products_with_contracted_multiply_adds():
+    """In lazy coherence the rank-r products run with fused multiply-adds (same
+    kernels and reduction order, one rounding per term instead of two).  Held to
+    the reference's bound for its own GEMMs against a float64 sum, |got - sum| /
+    (1 + sum|a_k b_k|) < 2e-6; identical run to run; and with the knob off the
+    bits of the strict seam."""
+    M, K, r = 4096, 768, 16
+    rng = np.random.default_rng(99)
+    a = Arena(rng)
+    x = a.alloc(M * K, "normal")
+    dy = a.alloc(M * K, "normal")
+    A = a.alloc(K * r, "normal", scale=0.05)        # [K, r]
+    Bt = a.alloc(r * K, "normal", scale=0.05)       # [r, K]: B of an adapter whose width is K
+    t = a.alloc(M * r); dt = a.alloc(M * r); gB = a.alloc(r * K); gA = a.alloc(K * r)
+    s = 2.0
+    prog = [
+        P.Instr(Op.GEMM_NN, 0, 0, (x, A, t, P.NULL_REF), (M, r, K)),                      # t = x A
+        P.Instr(Op.GEMM_NT, 0, P.f32_bits(s), (dy, Bt, dt, P.NULL_REF), (M, r, K)),       # dT = s dY B^T
+        P.Instr(Op.GEMM_TN, 0, P.f32_bits(s), (t, dy, gB, P.NULL_REF), (r, K, M)),        # dB = s t^T dY
+        P.Instr(Op.GEMM_TN, 0, 0, (x, dt, gA, P.NULL_REF), (K, r, M)),                    # dA = x^T dT
+    ]
+    arena0, ro = a.build()
+
+    def run(coherence, fma):
+        arena = arena0.copy()
+        be = B.CudaBackend(0)
+        be.set_coherence(coherence)
+        be.set_adapter_fma(fma)
+        be.bind(arena, ro)
+        be.run(prog)
+        be.host_needs(0, arena.size)
+        be.flush()
+        be.close()
+        return arena
+
+    strict = run(B.COHERENCE_STRICT, True)
+    fast1 = run(B.COHERENCE_LAZY, True)
+    fast2 = run(B.COHERENCE_LAZY, True)
+    lazy_exact = run(B.COHERENCE_LAZY, False)
+    assert np.array_equal(fast1, fast2)
+    assert np.array_equal(lazy_exact, strict)
+    X = _f32(arena0, x, M * K).reshape(M, K); DY = _f32(arena0, dy, M * K).reshape(M, K)
+    Am = _f32(arena0, A, K * r).reshape(K, r); Bm = _f32(arena0, Bt, r * K).reshape(r, K)
+    T = _f32(fast1, t, M * r).reshape(M, r); DT = _f32(fast1, dt, M * r).reshape(M, r)
+    cases = [
+        ("t", T, X @ Am, np.abs(X) @ np.abs(Am)),
+        ("dT", DT, s * (DY @ Bm.T), s * (np.abs(DY) @ np.abs(Bm.T))),
+        ("dB", _f32(fast1, gB, r * K).reshape(r, K), s * (T.T @ DY), s * (np.abs(T.T) @ np.abs(DY))),
+        ("dA", _f32(fast1, gA, K * r).reshape(K, r), X.T @ DT, np.abs(X.T) @ np.abs(DT)),
+    ]
+    differs = False
+    for name, got, want, mag in cases:
+        err = np.abs(got - want) / (1.0 + mag)
+        assert err.max() < 2e-6, (name, err.max())
+    for off, n in ((t, M * r), (dt, M * r), (gB, r * K), (gA, K * r)):
+        differs = differs or not np.array_equal(fast1[off:off + 4 * n], strict[off:off + 4 * n])
+    assert differs, "the contracted kernels gave the exact kernels' bits: did they run?"
