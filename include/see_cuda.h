@@ -37,6 +37,7 @@ typedef struct see_cuda_counters {
   uint64_t kernel_launches;
   uint64_t h2d_bytes, d2h_bytes;
   uint64_t instructions;
+  uint64_t split_executions; /* exact f32 products run as bf16 pieces on the tensor cores */
 } see_cuda_counters;
 
 enum { SEE_OK = 0, SEE_ERROR = 1, SEE_REFUSED = 2 };
@@ -101,6 +102,14 @@ int see_cuda_set_lora_fold(see_cuda_backend* h, int enabled);
  * arithmetic, bit for bit) in lazy coherence too; default 1: fused multiply-adds
  * there.  Strict coherence is always bit-exact. */
 int see_cuda_set_adapter_fma(see_cuda_backend* h, int enabled);
+/* Exact f32 products (kGemmNN / kGemmNT / kGemmTN without the relaxed permission)
+ * of at least 2^26 multiply-adds on the tensor cores: both operands cut into
+ * three bf16 pieces, six piece products over a K axis six times as long, f32
+ * accumulation.  The result is the f32 product to a few 2^-24 of sum|a_k b_k|
+ * (the reference holds its own GEMMs to 2e-6 of that: test/runtime/executor/
+ * kernels_test.cc:1803-1822), not the CPU's bits.  mode -1 (default): in lazy
+ * coherence only; 0: never; 1: in strict coherence too. */
+int see_cuda_set_split_gemm(see_cuda_backend* h, int mode);
 /* Data parallelism: optimizer steps read gradients inside [block_offset,
  * block_offset + block_bytes) as the rank-ordered sum of `ranks` gathered
  * copies (device memory, copy r at gathered + r * block_bytes) times 1/ranks. */

@@ -32,7 +32,7 @@ EXPORTED_SYMBOLS = [
     "see_cuda_set_gradient_gather",
     "see_cuda_set_profiling", "see_cuda_take_profile",
     "see_cuda_xent_forward_static", "see_cuda_static_max_rows", "see_cuda_static_last_error",
-    "see_cuda_quantize_columns", "see_cuda_set_lora_fold", "see_cuda_set_adapter_fma",
+    "see_cuda_quantize_columns", "see_cuda_set_lora_fold", "see_cuda_set_adapter_fma", "see_cuda_set_split_gemm",
 ]
 
 
@@ -45,7 +45,7 @@ class StepParams(ctypes.Structure):
 class Counters(ctypes.Structure):
     _fields_ = [(n, ctypes.c_uint64) for n in
                 ("relaxed_executions", "fused_dispatches", "kernel_launches", "h2d_bytes",
-                 "d2h_bytes", "instructions")]
+                 "d2h_bytes", "instructions", "split_executions")]
 
 
 class ProfileRecord(ctypes.Structure):
@@ -106,6 +106,7 @@ def load_library() -> ctypes.CDLL:
     lib.see_cuda_quantize_columns.argtypes = [vp, vp, u64, u64, vp, vp]
     lib.see_cuda_set_lora_fold.argtypes = [vp, i32]
     lib.see_cuda_set_adapter_fma.argtypes = [vp, i32]
+    lib.see_cuda_set_split_gemm.argtypes = [vp, i32]
     lib.see_cuda_xent_forward_static.argtypes = [vp, vp, vp, vp, u64, u64, i32, vp]
     lib.see_cuda_static_max_rows.restype = u64
     lib.see_cuda_static_last_error.restype = ctypes.c_char_p
@@ -249,6 +250,10 @@ class CudaBackend:
 
     def set_adapter_fma(self, enabled: bool):
         self._check(self.lib.see_cuda_set_adapter_fma(self.h, int(enabled)))
+
+    def set_split_gemm(self, mode: int):
+        """-1: exact f32 products on the tensor cores in lazy coherence only; 0 never; 1 always."""
+        self._check(self.lib.see_cuda_set_split_gemm(self.h, mode))
 
     def set_gradient_gather(self, ranks: int, gathered_ptr: int, block_offset: int,
                             block_bytes: int):

@@ -124,6 +124,11 @@ int see_cuda_set_adapter_fma(see_cuda_backend* h, int enabled) {
   return SEE_OK;
 }
 
+int see_cuda_set_split_gemm(see_cuda_backend* h, int mode) {
+  h->backend->SetSplitGemm(mode);
+  return SEE_OK;
+}
+
 int see_cuda_quantize_columns(see_cuda_backend* h, const float* w, uint64_t K, uint64_t N,
                               int8_t* levels, float* scales) {
   auto r = h->backend->QuantizeColumns(w, K, N, levels, scales);

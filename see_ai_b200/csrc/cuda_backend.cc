@@ -408,6 +408,7 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
     }
   }
   umma::PlanRange(&umma_->ctx, program.data(), begin, std::min(end, program.size()));
+  if (SplitGemmOn()) umma::PlanSplitGemms(&umma_->ctx, program.data(), begin, std::min(end, program.size()));
   // Cached bf16 activation copies do not outlive a range: a range replayed as a
   // CUDA graph must contain every conversion it depends on.
   umma::InvalidateRange(&umma_->ctx, 0, arena_bytes_);
@@ -1573,6 +1574,20 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
     a.fuse_shadow = nullptr;
     a.fuse_shadow_scale = nullptr;
     a.store_c = true;
+  }
+  // Large exact f32 products: bf16 pieces on the tensor cores where the bits are not observed.
+  if (SplitGemmOn() && (ins.opcode == kGemmNN || ins.opcode == kGemmNT || ins.opcode == kGemmTN) &&
+      umma::SplitGemmEligible(a)) {
+    int launches = 0;
+    const std::string err = umma::TrySplitGemm(&umma_->ctx, a,
+                                               RefSpace(ins.in[1]) == kArena ? 0 : (RefSpace(ins.in[1]) == kRodata ? 1 : 2),
+                                               RefOffset(ins.in[1]), stream_, &launches);
+    if (!err.empty()) return std::unexpected("cuda: " + err);
+    if (launches > 0) {
+      counters_.kernel_launches += launches;
+      ++counters_.split_executions;
+      return {};
+    }
   }
   // The split-K scratch is sized per range (BeginRange); an instruction executed
   // outside any range simply runs unsplit.

@@ -55,6 +55,7 @@ struct Counters {
   uint64_t kernel_launches = 0;      // device kernels enqueued since creation
   uint64_t h2d_bytes = 0, d2h_bytes = 0;
   uint64_t instructions = 0;
+  uint64_t split_executions = 0;     // exact f32 products run as bf16 pieces on the tensor cores
 };
 
 // One timed instruction (profile mode): opcode, index in the range, milliseconds.
@@ -147,6 +148,12 @@ class CudaBackend {
   // Off: the rank-r adapter products keep the CPU's one-rounding-per-operation
   // arithmetic even in lazy coherence (default on: fused multiply-adds there).
   void SetAdapterFma(bool enabled) { adapter_fma_ = enabled; }
+
+  // Exact f32 products (kGemmNN / NT / TN without the relaxed permission) above a
+  // size threshold on the tensor cores as six bf16 piece products (umma::TrySplitGemm):
+  // f32-class accuracy, not the CPU's bits.  -1 (default): in lazy coherence only;
+  // 0: never; 1: in strict coherence too.
+  void SetSplitGemm(int mode) { split_gemm_mode_ = mode; }
 
   // CUDA-graph support for the engine.  The optimizer kernels read the step's
   // learning rate and bias corrections from a small device block.  A captured
@@ -386,6 +393,8 @@ class CudaBackend {
   uint64_t lora_t_capacity_ = 0;
   bool lora_fold_enabled_ = true;
   bool adapter_fma_ = true;
+  int split_gemm_mode_ = -1;
+  bool SplitGemmOn() const { return split_gemm_mode_ > 0 || (split_gemm_mode_ < 0 && coherence_ == Coherence::kLazy); }
   Status PrepareLoraFolds(const Instruction* program, size_t begin, uint64_t max_rows);
   void FreeLoraRanges();
   k::GemmArgs GemmArgsOf(const Instruction& ins) const;

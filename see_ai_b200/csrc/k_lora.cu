@@ -96,7 +96,86 @@ __global__ void SplitWeightsKernel(const LoraWeight* __restrict__ table, int cou
   for (uint32_t k = 6 * e.r; k < e.kx; ++k) dst[k] = 0;
 }
 
+// ---- whole matrices: an f32 GEMM on the bf16 tensor cores -------------------------------
+// dst [rows][6 * cols] bf16: six K segments of `cols` each, segment s holding
+// piece kRowPiece[s] (the A side of a product) or kWeightPiece[s] (the B side) of
+// every element, so that A' B'^T over the long K axis is the six-product sum of
+// the header comment.  src is [rows][cols], or [cols][rows] when transposed
+// (then a 32 x 32 tile goes through shared memory so both sides stay coalesced).
+__device__ __forceinline__ int PieceOf(int side, int s) {
+  return side == 0 ? (s == 0 || s == 1 || s == 3 ? 0 : (s == 5 ? 2 : 1))
+                   : (s == 0 || s == 2 || s == 5 ? 0 : (s == 3 ? 2 : 1));
+}
+
+template <int kSide>
+__global__ void SplitMatrixKernel(const float* __restrict__ src, uint16_t* __restrict__ dst, uint32_t rows,
+                                  uint32_t cols) {
+  const size_t quads = static_cast<size_t>(rows) * (cols / 4);
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t q = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; q < quads; q += stride) {
+    const uint32_t row = static_cast<uint32_t>(q / (cols / 4)), c4 = static_cast<uint32_t>(q % (cols / 4)) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(src + static_cast<size_t>(row) * cols + c4);
+    uint16_t p[4][3];
+    Split3(v.x, p[0]); Split3(v.y, p[1]); Split3(v.z, p[2]); Split3(v.w, p[3]);
+    uint16_t* out = dst + static_cast<size_t>(row) * 6 * cols + c4;
+#pragma unroll
+    for (int s = 0; s < 6; ++s) {
+      const int pc = PieceOf(kSide, s);
+      uint2 w;
+      w.x = static_cast<uint32_t>(p[0][pc]) | (static_cast<uint32_t>(p[1][pc]) << 16);
+      w.y = static_cast<uint32_t>(p[2][pc]) | (static_cast<uint32_t>(p[3][pc]) << 16);
+      *reinterpret_cast<uint2*>(out + static_cast<size_t>(s) * cols) = w;
+    }
+  }
+}
+
+// src [cols][rows] -> dst row r, column c = src[c][r].
+template <int kSide>
+__global__ void SplitMatrixTransposedKernel(const float* __restrict__ src, uint16_t* __restrict__ dst,
+                                            uint32_t rows, uint32_t cols) {
+  __shared__ float tile[32][33];
+  const uint32_t r0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
+    const uint32_t c = c0 + i, r = r0 + threadIdx.x;
+    tile[i][threadIdx.x] = c < cols && r < rows ? src[static_cast<size_t>(c) * rows + r] : 0.0f;
+  }
+  __syncthreads();
+  for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
+    const uint32_t r = r0 + i, c = c0 + threadIdx.x;
+    if (r >= rows || c >= cols) continue;
+    uint16_t p[3];
+    Split3(tile[threadIdx.x][i], p);
+    uint16_t* out = dst + static_cast<size_t>(r) * 6 * cols + c;
+#pragma unroll
+    for (int s = 0; s < 6; ++s) out[static_cast<size_t>(s) * cols] = p[PieceOf(kSide, s)];
+  }
+}
+
 }  // namespace
+
+void SplitMatrix(const float* src, uint16_t* dst, size_t rows, size_t cols, bool transposed, int side,
+                 cudaStream_t s) {
+  if (rows == 0 || cols == 0) return;
+  if (transposed) {
+    const dim3 grid(static_cast<unsigned>((rows + 31) / 32), static_cast<unsigned>((cols + 31) / 32));
+    const dim3 block(32, 8);
+    if (side == 0)
+      SplitMatrixTransposedKernel<0><<<grid, block, 0, s>>>(src, dst, static_cast<uint32_t>(rows),
+                                                            static_cast<uint32_t>(cols));
+    else
+      SplitMatrixTransposedKernel<1><<<grid, block, 0, s>>>(src, dst, static_cast<uint32_t>(rows),
+                                                            static_cast<uint32_t>(cols));
+    return;
+  }
+  size_t blocks = (rows * (cols / 4) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (side == 0)
+    SplitMatrixKernel<0><<<static_cast<unsigned>(blocks), 256, 0, s>>>(src, dst, static_cast<uint32_t>(rows),
+                                                                       static_cast<uint32_t>(cols));
+  else
+    SplitMatrixKernel<1><<<static_cast<unsigned>(blocks), 256, 0, s>>>(src, dst, static_cast<uint32_t>(rows),
+                                                                       static_cast<uint32_t>(cols));
+}
 
 uint32_t LoraSplitColumns(uint32_t r) { return (6 * r + 63) / 64 * 64; }
 

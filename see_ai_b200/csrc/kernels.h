@@ -221,6 +221,14 @@ struct LoraWeight {
 // Every entry of a device-resident table in one launch.
 void LoraSplitWeights(const LoraWeight* table, int count, uint32_t max_n_out, cudaStream_t s);
 
+// A whole f32 matrix as its bf16 pieces, dst [rows][6 * cols] (six K segments of
+// `cols`): the operand layout that makes an f32 GEMM a bf16 tensor-core GEMM over
+// K' = 6 K (k_lora.cu).  side 0: the A operand's piece order; 1: the B operand's.
+// src is [rows][cols], or [cols][rows] when `transposed`.  cols % 4 == 0 and 16-byte
+// aligned pointers for the untransposed form.
+void SplitMatrix(const float* src, uint16_t* dst, size_t rows, size_t cols, bool transposed, int side,
+                 cudaStream_t s);
+
 // ---- GEMM -------------------------------------------------------------------
 enum class BType : uint8_t { kF32 = 0, kI8 = 1, kBf16 = 2 };
 constexpr int kFuseNone = 0, kFuseActFwd = 1, kFuseActBwd = 2;   // GemmArgs::fuse_mode

@@ -64,6 +64,11 @@ struct Impl {
   uint64_t pack_capacity = 0;   // elements per layout of an entry
   cudaEvent_t prof_before = nullptr, prof_after = nullptr;
   bool prof_used = false;
+  // bf16 pieces of the operands of exact f32 products (TrySplitGemm)
+  uint16_t* split_a = nullptr;
+  uint16_t* split_b = nullptr;
+  uint64_t split_a_capacity = 0, split_b_capacity = 0;   // elements
+  std::map<WeightKey, uint16_t*> split_weights;          // frozen B operands, once per binding
 };
 
 std::string Init(Context* ctx, int device, k::DeviceStatus* status) {
@@ -87,6 +92,8 @@ void Destroy(Context* ctx) {
   InvalidateAll(ctx);
   for (auto& a : ctx->impl->acts) cudaFree(a.buf);
   for (auto& e : ctx->impl->packs) { cudaFree(e.rows); cudaFree(e.cols); }
+  cudaFree(ctx->impl->split_a);
+  cudaFree(ctx->impl->split_b);
   delete ctx->impl;
   ctx->impl = nullptr;
 }
@@ -95,6 +102,8 @@ void InvalidateAll(Context* ctx) {
   if (!ctx->impl) return;
   for (auto& [key, buf] : ctx->impl->weights) cudaFree(buf);
   ctx->impl->weights.clear();
+  for (auto& [key, buf] : ctx->impl->split_weights) cudaFree(buf);
+  ctx->impl->split_weights.clear();
   for (auto& a : ctx->impl->acts) a.valid = false;
   for (auto& e : ctx->impl->packs) e.valid = false;
 }
@@ -304,6 +313,104 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
   if (cudaError_t e = k::UmmaGemmLaunch(map_a, map_b, ep, stream, has_aux ? &aux_a : nullptr,
                                         has_aux ? &aux_b : nullptr);
       e != cudaSuccess)
+    return std::string("tensor-core GEMM launch: ") + cudaGetErrorString(e);
+  if (impl->prof_after) {
+    cudaEventRecord(impl->prof_after, stream);
+    impl->prof_used = true;
+    impl->prof_before = impl->prof_after = nullptr;
+  }
+  ++*launches;
+  return {};
+}
+
+bool SplitGemmEligible(const k::GemmArgs& a) {
+  if (a.b_type != k::BType::kF32 || a.accumulate || a.b_col_scale || a.a_k_scale) return false;
+  if (a.M < 128 || a.N < 64 || a.K < 64 || (a.N & 3) != 0 || (a.K & 3) != 0) return false;
+  if (a.M * a.N * a.K < (1ull << 26)) return false;   // below ~0.1 GFLOP a launch is latency either way
+  if (a.M > 0x7FFFFFFFull || a.N > 0x7FFFFFFFull || 6 * a.K > 0x7FFFFFFFull) return false;
+  auto misaligned = [](const void* p) { return p && (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+  return !(misaligned(a.A) || misaligned(a.B) || misaligned(a.C) || misaligned(a.addend) || misaligned(a.bias));
+}
+
+static bool GrowSplit(uint16_t** buf, uint64_t* cap, uint64_t need, cudaStream_t stream, bool whole_device = false) {
+  if (need <= *cap) return true;
+  // Queued kernels may still read the old buffer.
+  if (whole_device) cudaDeviceSynchronize(); else cudaStreamSynchronize(stream);
+  cudaFree(*buf);
+  *buf = nullptr;
+  *cap = 0;
+  void* p = nullptr;
+  if (cudaMalloc(&p, need * 2) != cudaSuccess) { cudaGetLastError(); return false; }
+  *buf = static_cast<uint16_t*>(p);
+  *cap = need;
+  return true;
+}
+
+void PlanSplitGemms(Context* ctx, const Instruction* program, size_t begin, size_t end) {
+  Impl* impl = ctx->impl;
+  if (!impl) return;
+  uint64_t need_a = 0, need_b = 0;
+  for (size_t i = begin; i < end; ++i) {
+    const Instruction& ins = program[i];
+    if (ins.opcode != kGemmNN && ins.opcode != kGemmNT && ins.opcode != kGemmTN) continue;
+    const uint64_t M = ins.out[0], N = ins.out[1], K = ins.out[2];
+    if (M < 128 || N < 64 || K < 64 || M * N * K < (1ull << 26)) continue;
+    need_a = std::max(need_a, M * 6 * K);
+    if (RefSpace(ins.in[1]) == kArena) need_b = std::max(need_b, N * 6 * K);
+  }
+  GrowSplit(&impl->split_a, &impl->split_a_capacity, need_a, nullptr, true);
+  GrowSplit(&impl->split_b, &impl->split_b_capacity, need_b, nullptr, true);
+}
+
+std::string TrySplitGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_off,
+                         cudaStream_t stream, int* launches) {
+  *launches = 0;
+  Impl* impl = ctx->impl;
+  if (!impl || !SplitGemmEligible(a)) return {};
+  const uint64_t K6 = 6 * a.K;
+  if (!GrowSplit(&impl->split_a, &impl->split_a_capacity, a.M * K6, stream))
+    return "tensor-core path: operand-piece allocation failed";
+  // A: [M, K], or [K, M] for the transposed-A form.
+  k::SplitMatrix(a.A, impl->split_a, a.M, a.K, a.a_transposed, 0, stream);
+  ++*launches;
+  // B: wanted as [N][K]; stored [N, K] (NT) or [K, N] (NN, TN).
+  uint16_t* b = nullptr;
+  if (b_space != 0) {   // frozen: once per binding
+    const WeightKey key{b_space, b_off, a.N, a.K, !a.b_transposed, 100, ~0ull};
+    if (auto it = impl->split_weights.find(key); it != impl->split_weights.end()) {
+      b = it->second;
+    } else {
+      void* p = nullptr;
+      if (cudaMalloc(&p, a.N * K6 * 2) != cudaSuccess) return "tensor-core path: weight-piece allocation failed";
+      b = static_cast<uint16_t*>(p);
+      k::SplitMatrix(static_cast<const float*>(a.B), b, a.N, a.K, !a.b_transposed, 1, stream);
+      ++*launches;
+      impl->split_weights.emplace(key, b);
+    }
+  } else {
+    if (!GrowSplit(&impl->split_b, &impl->split_b_capacity, a.N * K6, stream))
+      return "tensor-core path: operand-piece allocation failed";
+    b = impl->split_b;
+    k::SplitMatrix(static_cast<const float*>(a.B), b, a.N, a.K, !a.b_transposed, 1, stream);
+    ++*launches;
+  }
+  CUtensorMap map_a, map_b;
+  if (!EncodeBf16Map(impl, &map_a, impl->split_a, a.M, K6, k::umma_cfg::kBlockM) ||
+      !EncodeBf16Map(impl, &map_b, b, a.N, K6, k::umma_cfg::kBlockN))
+    return "tensor-core path: cuTensorMapEncodeTiled refused the operand-piece layout";
+  k::UmmaEpilogue ep{};
+  ep.C = a.C;
+  ep.addend = a.addend;
+  ep.bias = a.bias;
+  ep.col_scale = nullptr;
+  ep.alpha = a.alpha;   // (the exact kernels fold alpha into A or the finished dot; here it scales the tile)
+  ep.act = static_cast<int>(a.act);
+  ep.M = static_cast<uint32_t>(a.M);
+  ep.N = static_cast<uint32_t>(a.N);
+  ep.K = static_cast<uint32_t>(K6);
+  ep.status = impl->status;
+  if (impl->prof_before) cudaEventRecord(impl->prof_before, stream);
+  if (cudaError_t e = k::UmmaGemmLaunch(map_a, map_b, ep, stream); e != cudaSuccess)
     return std::string("tensor-core GEMM launch: ") + cudaGetErrorString(e);
   if (impl->prof_after) {
     cudaEventRecord(impl->prof_after, stream);

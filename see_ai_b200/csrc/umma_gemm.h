@@ -41,6 +41,22 @@ void PlanRange(Context* ctx, const Instruction* program, size_t begin, size_t en
 std::string TryGemm(Context* ctx, const k::GemmArgs& args, int b_space, uint64_t b_off,
                     uint64_t a_off, uint64_t a_scale_off, cudaStream_t stream, int* launches);
 
+// An EXACT f32 product on the tensor cores: both operands cut into three bf16
+// pieces, the six largest piece products summed over a K axis six times as long
+// (k::SplitMatrix), f32 accumulation in tensor memory.  The result is the f32
+// product to a few 2^-24 of sum|a_k b_k| — the accuracy the exact CUDA-core
+// kernels have against a float64 sum, not their bits — at a sixth of the bf16
+// tensor rate instead of the FP32 pipe's.  Takes NN, NT and TN forms with f32
+// operands in any address space; epilogue addend / bias / activation as usual.
+// *launches == 0 with an empty return value: outside the domain (small or odd
+// shapes, narrow outputs), use the exact kernels.
+bool SplitGemmEligible(const k::GemmArgs& args);
+std::string TrySplitGemm(Context* ctx, const k::GemmArgs& args, int b_space, uint64_t b_off,
+                         cudaStream_t stream, int* launches);
+// Sizes the two operand buffers for the largest eligible product of a range
+// (called with the other per-range sizing, before any capture).
+void PlanSplitGemms(Context* ctx, const Instruction* program, size_t begin, size_t end);
+
 // Producer-side conversion: the instruction that writes a tensor a relaxed GEMM
 // reads next can emit the bf16 copy itself (k::Shadow) and spare the GEMM's
 // conversion pass the f32 re-read.  ReserveShadow picks an activation slot and
