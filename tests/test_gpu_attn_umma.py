@@ -99,3 +99,32 @@ def test_permission_withheld_runs_the_exact_family_bit_for_bit_on_exact_ops():
         got = gpu[t[name]:t[name] + 4 * td].view(np.float32)
         want = cpu[t[name]:t[name] + 4 * td].view(np.float32)
         assert np.max(np.abs(got - want)) <= 1e-5 * np.max(np.abs(want)) + 1e-7, name
+
+
+@pytest.mark.parametrize("geom", [(1, 4096, 2, 64), (1, 4096, 1, 128)], ids=["S4096d64", "S4096d128"])
+def test_longest_sweep_sequence_against_the_exact_family_on_the_device(geom):
+    """S = 4096, the attention sweep's longest sequence, at both head widths.
+    The CPU oracle would need minutes here; the device's own exact family (held
+    to the oracle at the sizes above, and independent per (batch, head)) is the
+    reference instead."""
+    Bq, S, H, d = geom
+    rng = np.random.default_rng(S + d)
+    t, prog, arena, ro, td = build(rng, Bq, S, H, d)
+    exact, fast = arena.copy(), arena.copy()
+    be = B.CudaBackend(0)
+    be.set_relaxed_allowed(False)
+    be.bind(exact, ro)
+    be.run(prog(REL))
+    assert be.counters().relaxed_executions == 0
+    be.close()
+    be = B.CudaBackend(0)
+    be.bind(fast, ro)
+    be.run(prog(REL))
+    assert be.counters().relaxed_executions == 4
+    be.close()
+    for name in ("o", "dq", "dk", "dv"):
+        got = fast[t[name]:t[name] + 4 * td].view(np.float32)
+        want = exact[t[name]:t[name] + 4 * td].view(np.float32)
+        assert np.isfinite(got).all(), name
+        err = np.max(np.abs(got - want)) / np.max(np.abs(want))
+        assert err < 1e-2, f"{name}: {err:.3g} of scale"
