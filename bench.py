@@ -292,17 +292,27 @@ def run_plan(args):
         plain_flops = sum(2.0 * m * n * k for (m, n, k, _t) in plain)
         plain_ms = sum(t for (*_s, t) in plain)
         by_op, hbm = {}, {}
-        # The records of the two ranges (forward + backward, optimizer) in program order.
+        # The records of the two ranges (forward + backward, optimizer) in program order.  A kernel
+        # that also did following instructions (an absorbed add, the loss backward inside the loss
+        # forward's row pass) is credited with their bytes too and listed as "<opcode>+absorbed";
+        # the absorbed instructions launch nothing (their records hold event overhead only).
+        hold = None   # the last bandwidth-bound record that absorbed others, still collecting their bytes
         for rec, ins in zip(prof8, train):
-            op, ms = rec[0], rec[2]
+            op, ms, absorbed = rec[0], rec[2], rec[7]
             name = P.OP_NAMES.get(op, str(op))
             by_op[name] = by_op.get(name, 0.0) + ms
             _fl, nbytes = W.algorithmic_work(ins)
-            # (An instruction another kernel absorbed launches nothing: its few microseconds of event
-            # overhead would read as an impossible bandwidth, so it is left out, like one that absorbed others.)
-            if nbytes > 0 and ms > 0 and rec[7] == 0 and nbytes / 1e9 / (ms * 1e-3) < 1.3 * peaks()["hbm_gbs"]:
-                e = hbm.setdefault(name, [0.0, 0.0, 0])
-                e[0] += ms; e[1] += nbytes; e[2] += 1
+            if nbytes <= 0 or ms <= 0:
+                continue
+            launched = nbytes / 1e9 / (ms * 1e-3) < 1.5 * peaks()["hbm_gbs"]
+            if not launched:
+                if hold is not None and hold[1] > 0:
+                    hold[0][1] += nbytes
+                    hold[1] -= 1
+                continue
+            e = hbm.setdefault(name + ("+absorbed" if absorbed else ""), [0.0, 0.0, 0])
+            e[0] += ms; e[1] += nbytes; e[2] += 1
+            hold = [e, absorbed] if absorbed else None
         profiled_ms = sum(by_op.values())
         for _ in range(3 if exchange else 0):
             step(False, 0, time_exchange=True)
