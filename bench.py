@@ -229,6 +229,9 @@ def run_plan(args):
     from see_ai_b200.engine import Engine
 
     wl = W.plan_workload(args.config)
+    reduced = args.config == 4 and (args.layers or args.batch_seqs)
+    if reduced:   # same kernels on a case small enough to sit under a profiler; never a headline number
+        wl = W.Int8DecoderWorkload(layers=args.layers or 12, batch_seqs=args.batch_seqs or 64)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -368,7 +371,7 @@ def run_plan(args):
         "config": {"workload": wl.description, "rows_per_gpu": rows, "parallelism": f"dp{world}",
                    "l2_policy": ("inputs larger than L2 (the step streams >10 GB through HBM)" if args.config == 4 else
                                  "a step's working set is rewritten every step; no separate flush"),
-                   "cuda_graphs": not args.no_graphs},
+                   "cuda_graphs": not args.no_graphs, **({"reduced_case_for_profiling": True} if reduced else {})},
         "e2e": {"value": e2e, "unit": wl.unit + "/s", "h2d_bytes_per_step": h2d * world,
                 "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": int(launches_per_step * args.steps),
@@ -423,7 +426,7 @@ def run_plan(args):
                                       "bandwidth, is what is measured)",
             "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"],
             "peak_source": pk["source"] + " (copy)", "traffic": None, "launches_per_step": int(launches_per_step)}
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and not reduced:
         ups, info = cpu_plan_sample(args.config, 200 if args.config == 1 else 3, 20 if args.config == 1 else 1)
         line["cpu_baseline"] = {"value": ups, "unit": wl.unit + "/s", "cores": info["cores"],
                                 "kind": info["kind"], "sample": info["sample"]}
@@ -591,6 +594,8 @@ def main():
     ap.add_argument("--dtypes", default="", help="config 2: f32,bf16")
     ap.add_argument("--head-dims", default="", help="config 5: 64,128")
     ap.add_argument("--cpu-max-size", type=int, default=1024, help="configs 2 and 5: largest S the CPU arm runs")
+    ap.add_argument("--layers", type=int, default=0, help="config 4 only: a REDUCED case for profiler captures")
+    ap.add_argument("--batch-seqs", type=int, default=0, help="config 4 only: a REDUCED case for profiler captures")
     args = ap.parse_args()
     # stdout carries exactly one JSON line.  Libraries underneath (NCCL's version
     # banner, for one) write to file descriptor 1 behind Python's back, so the

@@ -90,13 +90,16 @@ class SmallDecoderWorkload(PlanWorkload):
 
 
 class Int8DecoderWorkload(PlanWorkload):
-    def __init__(self):
-        super().__init__("decoder_int8", "int8-weight decoder LoRA update: 12 layers, d_model 768, 12 heads, FFN 3072, "
-                         "vocab 32000, seq 512, global batch 64 sequences, LoRA r16 alpha 32 on Q/K/V/O, relaxed bf16 "
-                         "GEMMs, AdamW", "tokens", 64 * 512, 512, "bf16", vocab=32000)
+    def __init__(self, layers: int = 12, batch_seqs: int = 64):
+        self.layers, self.batch_seqs = layers, batch_seqs
+        super().__init__("decoder_int8", f"int8-weight decoder LoRA update: {layers} layers, d_model 768, 12 heads, "
+                         f"FFN 3072, vocab 32000, seq 512, global batch {batch_seqs} sequences, LoRA r16 alpha 32 on "
+                         "Q/K/V/O, relaxed bf16 GEMMs, AdamW", "tokens", batch_seqs * 512, 512, "bf16", vocab=32000)
 
     def build(self, world: int) -> bytes:
-        return synth.build_decoder_plan(int8_decoder_config(64 // world))
+        cfg = int8_decoder_config(self.batch_seqs // world)
+        cfg.layers = self.layers
+        return synth.build_decoder_plan(cfg)
 
 
 def plan_workload(config: int) -> PlanWorkload:
