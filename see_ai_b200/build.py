@@ -35,6 +35,7 @@ CU_SOURCES = {
     "k_no_alloc.cu": ["-fmad=false"],
     "k_lora.cu": [],
     "k_gemm_skinny_fast.cu": [],
+    "k_lora_mma.cu": [],
 }
 CC_SOURCES = ["extents.cc", "cuda_backend.cc", "c_api.cc", "umma_gemm.cc", "engine.cc"]
 

@@ -110,6 +110,7 @@ CudaBackend::~CudaBackend() {
   cudaFree(d_adam_table_);
   FreeLoraRanges();
   cudaFree(d_lora_t_);
+  cudaFree(d_lora_partials_);
   if (h_scalars_) cudaFreeHost(h_scalars_);
   if (h_status_) cudaFreeHost(h_status_);
   if (own_stream_ && stream_) cudaStreamDestroy(stream_);
@@ -420,6 +421,31 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
     PlanActFusions(program, begin, std::min(end, program.size()));
   };
   plan_fusions();
+  uint64_t partial_floats = 0;
+  for (size_t i = 0; i < adapter_bwd_.size(); ++i)
+    if (adapter_bwd_[i].fuse)
+      partial_floats = std::max<uint64_t>(partial_floats,
+                                          k::LoraBackwardPartialFloats(program[begin + i].out[2], adapter_bwd_[i].da.out[0],
+                                                                       program[begin + i].out[1]));
+  if (partial_floats > lora_partials_capacity_) {
+    cudaStreamSynchronize(stream_);
+    cudaFree(d_lora_partials_);
+    d_lora_partials_ = nullptr;
+    lora_partials_capacity_ = 0;
+    void* p = nullptr;
+    if (cudaMalloc(&p, partial_floats * sizeof(float)) == cudaSuccess) {
+      d_lora_partials_ = static_cast<float*>(p);
+      lora_partials_capacity_ = partial_floats;
+    } else {   // no scratch: the three products stay three instructions
+      cudaGetLastError();
+      for (size_t i = 0; i < adapter_bwd_.size(); ++i)
+        if (adapter_bwd_[i].fuse) {
+          adapter_bwd_[i].fuse = false;
+          for (size_t q = i + 1; q < lora_skip_.size() && q <= i + 3; ++q)
+            if (lora_skip_[q] == 1 && (program[begin + q].opcode == kGemmTN)) lora_skip_[q] = 0;
+        }
+    }
+  }
   uint64_t fold_rows = 0;
   for (size_t i = 0; i < lora_fold_.size(); ++i)
     if (lora_fold_[i].fuse) fold_rows = std::max<uint64_t>(fold_rows, program[begin + i].out[0]);
@@ -479,6 +505,7 @@ void CudaBackend::FreeLoraRanges() {
 }
 
 void CudaBackend::EndRange() {
+  adapter_bwd_.clear();
   lora_fold_.clear();
   lora_skip_.clear();
   lora_weights_.clear();
@@ -781,6 +808,7 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
   attn_dv_out_.assign(end > begin ? end - begin : 0, kNullRef);
   attn_dv_shadow_.assign(end > begin ? end - begin : 0, ShadowPlan{});
   lora_fold_.assign(end > begin ? end - begin : 0, LoraFold{});
+  adapter_bwd_.assign(end > begin ? end - begin : 0, AdapterBackward{});
   lora_skip_.assign(end > begin ? end - begin : 0, 0);
   lora_weights_.clear();
   lora_max_n_ = lora_max_kx_ = 0;
@@ -1063,7 +1091,7 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
   }
 
   // ---- the adapter's expand product folded into the frozen product (LoraFold) ----
-  if (!lora_fold_enabled_) return;
+  const bool folds = lora_fold_enabled_;
   auto overlap = [](uint64_t alo, uint64_t ahi, uint64_t blo, uint64_t bhi) { return alo < bhi && blo < ahi; };
   auto touches = [&](size_t j, uint64_t lo, uint64_t hi, bool want_write) {   // does instruction j write (read) [lo, hi)?
     const Extents& e = ext[j - ext_base];
@@ -1135,7 +1163,7 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
     }
     af = AddFusion{};   // either way the expand kernel no longer runs
   };
-  for (size_t i = begin; i < end; ++i) {
+  for (size_t i = begin; i < end && folds; ++i) {
     if (!plain_frozen(i) || add_fusion_[i - begin].fuse) continue;
     const Instruction& g = program[i];
     const uint64_t M = g.out[0], N = g.out[1];
@@ -1221,7 +1249,7 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
   }
   // kind 3: E: part = acc + dT A^T; (up to two instructions); G; kAddEW: part + G.out, already planned as G's
   // epilogue addend: the addend becomes acc and the expand rides the reduction.
-  for (size_t i = begin; i < end; ++i) {
+  for (size_t i = begin; i < end && folds; ++i) {
     AddFusion& af = add_fusion_[i - begin];
     const Instruction& g = program[i];
     if (!af.fuse || !IsRelaxedFrozenGemm(g) || RefSpace(g.in[2]) != kArena || lora_fold_[i - begin].fuse ||
@@ -1265,6 +1293,59 @@ void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t be
       lora_fold_[i - begin] = f;
       break;
     }
+  }
+  // ---- the three activation-streaming backward products of an adapter site in one pass ----
+  //   [j] dT = a dY B^T   [j+1] dB = a t^T dY   [j+2 or j+3] dA = x^T dT
+  if (!adapter_fma_) return;
+  for (size_t j = begin; j + 2 < end; ++j) {
+    const Instruction& dt = program[j];
+    const Instruction& db = program[j + 1];
+    if (dt.opcode != kGemmNT || dt.flags != 0 || db.opcode != kGemmTN || db.flags != 0) continue;
+    if (lora_skip_[j - begin] != 0 || lora_skip_[j + 1 - begin] != 0) continue;
+    const uint64_t M = dt.out[0], r = dt.out[1], N = dt.out[2];
+    if (db.out[0] != r || db.out[1] != N || db.out[2] != M || db.in[1] != dt.in[0]) continue;
+    size_t ja = 0;
+    for (size_t q = j + 2; q < end && q <= j + 3; ++q) {
+      const Instruction& c = program[q];
+      if (c.opcode == kGemmTN && c.flags == 0 && c.out[1] == r && c.out[2] == M && c.in[1] == dt.in[2] &&
+          lora_skip_[q - begin] == 0) {
+        ja = q;
+        break;
+      }
+    }
+    if (ja == 0) continue;
+    const Instruction& da = program[ja];
+    const uint64_t K = da.out[0];
+    if (!k::LoraBackwardSupported(M, N, K, r)) continue;
+    const uint64_t refs[7] = {dt.in[0], da.in[0], db.in[0], dt.in[1], dt.in[2], db.in[2], da.in[2]};
+    const uint64_t bytes[7] = {M * N * 4, M * K * 4, M * r * 4, r * N * 4, M * r * 4, r * N * 4, K * r * 4};
+    bool ok = true;
+    for (int q = 0; q < 7; ++q) ok = ok && aligned(refs[q]);
+    // the three outputs apart from each other and from every operand
+    for (int o = 4; o < 7 && ok; ++o)
+      for (int q = 0; q < 7 && ok; ++q)
+        if (q != o && overlap(RefOffset(refs[o]), RefOffset(refs[o]) + bytes[o], RefOffset(refs[q]),
+                              RefOffset(refs[q]) + bytes[q]))
+          ok = false;
+    // what the plan runs between dT and dA (an expand product, at most) neither changes an operand nor
+    // looks at dB / dA, which exist early now
+    for (size_t q = j + 1; q < ja && ok; ++q) {
+      if (q == j + 1) continue;
+      for (int w = 0; w < 5 && ok; ++w)
+        if (touches(q, RefOffset(refs[w]), RefOffset(refs[w]) + bytes[w], true)) ok = false;
+      for (int o = 5; o < 7 && ok; ++o)
+        if (touches(q, RefOffset(refs[o]), RefOffset(refs[o]) + bytes[o], true) ||
+            touches(q, RefOffset(refs[o]), RefOffset(refs[o]) + bytes[o], false))
+          ok = false;
+    }
+    if (!ok) continue;
+    AdapterBackward ab;
+    ab.fuse = true;
+    ab.db = db;
+    ab.da = da;
+    adapter_bwd_[j - begin] = ab;
+    lora_skip_[j + 1 - begin] = 1;
+    lora_skip_[ja - begin] = 1;
   }
 }
 
@@ -1509,7 +1590,9 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
       if (lf->kind == 1) {   // its down product t = x A first (the plan has it after this instruction)
         k::GemmArgs d = GemmArgsOf(lf->down);
         d.contract_fma = adapter_fma_;
-        k::GemmExact(d, stream_);
+        if (!(adapter_fma_ && lf->down.flags == 0 && k::LoraDownSupported(d.M, d.K, d.N) &&
+              k::LoraDown(d.A, static_cast<const float*>(d.B), d.C, d.M, d.K, d.N, d.alpha, stream_)))
+          k::GemmExact(d, stream_);
         ++counters_.kernel_launches;
         umma::InvalidateRange(&umma_->ctx, RefOffset(lf->down.in[2]), d.M * d.N * 4);
       }
@@ -1574,6 +1657,32 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
     a.fuse_shadow = nullptr;
     a.fuse_shadow_scale = nullptr;
     a.store_c = true;
+  }
+  // An adapter site's three backward products in one pass (this is the first of them).
+  if (range_index_ < adapter_bwd_.size() && adapter_bwd_[range_index_].fuse) {
+    const AdapterBackward& ab = adapter_bwd_[range_index_];
+    k::LoraBackwardArgs b;
+    b.dy = Rd(ins.in[0]); b.B = Rd(ins.in[1]); b.dt = Wr(ins.in[2]);
+    b.t = Rd(ab.db.in[0]); b.dB = Wr(ab.db.in[2]);
+    b.x = Rd(ab.da.in[0]); b.dA = Wr(ab.da.in[2]);
+    b.partials = d_lora_partials_;
+    b.partials_floats = lora_partials_capacity_;
+    b.M = ins.out[0]; b.r = ins.out[1]; b.N = ins.out[2]; b.K = ab.da.out[0];
+    b.alpha_dt = GemmAlphaOf(ins.imm); b.alpha_db = GemmAlphaOf(ab.db.imm); b.alpha_da = GemmAlphaOf(ab.da.imm);
+    if (!k::LoraBackward(b, stream_))
+      return std::unexpected("cuda: the fused adapter backward refused a site it was planned on");
+    counters_.kernel_launches += 3;
+    counters_.fused_dispatches += 2;
+    umma::InvalidateRange(&umma_->ctx, RefOffset(ab.db.in[2]), b.r * b.N * 4);
+    umma::InvalidateRange(&umma_->ctx, RefOffset(ab.da.in[2]), b.K * b.r * 4);
+    return {};
+  }
+  // The forward's down product t = x A on the tensor cores (3xTF32) where the bits are not observed.
+  if (coherence_ == Coherence::kLazy && adapter_fma_ && ins.opcode == kGemmNN && ins.flags == 0 &&
+      RefSpace(ins.in[1]) == kArena && k::LoraDownSupported(a.M, a.K, a.N) &&
+      k::LoraDown(a.A, static_cast<const float*>(a.B), a.C, a.M, a.K, a.N, a.alpha, stream_)) {
+    ++counters_.kernel_launches;
+    return {};
   }
   // Large exact f32 products: bf16 pieces on the tensor cores where the bits are not observed.
   if (SplitGemmOn() && (ins.opcode == kGemmNN || ins.opcode == kGemmNT || ins.opcode == kGemmTN) &&

@@ -393,6 +393,17 @@ class CudaBackend {
   uint64_t lora_t_capacity_ = 0;
   bool lora_fold_enabled_ = true;
   bool adapter_fma_ = true;
+  // The three backward products of an adapter site (dT = a dY B^T, dB = a t^T dY,
+  // dA = x^T dT), which the plan spells as three instructions that each stream a
+  // whole activation, as ONE pass over dY and x (k::LoraBackward).  Per range
+  // position of the dT instruction; the other two are marked done in lora_skip_.
+  struct AdapterBackward {
+    bool fuse = false;
+    Instruction db{}, da{};
+  };
+  std::vector<AdapterBackward> adapter_bwd_;
+  float* d_lora_partials_ = nullptr;
+  uint64_t lora_partials_capacity_ = 0;   // floats
   int split_gemm_mode_ = -1;
   bool SplitGemmOn() const { return split_gemm_mode_ > 0 || (split_gemm_mode_ < 0 && coherence_ == Coherence::kLazy); }
   Status PrepareLoraFolds(const Instruction* program, size_t begin, uint64_t max_rows);

@@ -221,6 +221,31 @@ struct LoraWeight {
 // Every entry of a device-resident table in one launch.
 void LoraSplitWeights(const LoraWeight* table, int count, uint32_t max_n_out, cudaStream_t s);
 
+// ---- the activation-streaming adapter products on the tensor cores (k_lora_mma.cu) -----
+// t = alpha x A for x [M, K], A [K, r]; 3xTF32 (f32-class accuracy, not the CPU's
+// bits).  False (nothing launched) outside the shapes it is built for.
+bool LoraDownSupported(size_t M, size_t K, size_t r);
+bool LoraDown(const float* x, const float* A, float* out, size_t M, size_t K, size_t r, float alpha, cudaStream_t s);
+// The three backward products of one adapter site in one pass over dY and x:
+// dT = alpha_dt dY B^T, dB = alpha_db t^T dY, dA = alpha_da x^T dT.  `partials`
+// holds LoraBackwardPartialFloats(N, K, r) floats of scratch.
+struct LoraBackwardArgs {
+  const float* dy = nullptr;   // [M, N]
+  const float* x = nullptr;    // [M, K]
+  const float* t = nullptr;    // [M, r]
+  const float* B = nullptr;    // [r, N]
+  float* dt = nullptr;         // [M, r]
+  float* dB = nullptr;         // [r, N]
+  float* dA = nullptr;         // [K, r]
+  float* partials = nullptr;
+  size_t partials_floats = 0;
+  size_t M = 0, N = 0, K = 0, r = 0;
+  float alpha_dt = 1.0f, alpha_db = 1.0f, alpha_da = 1.0f;
+};
+bool LoraBackwardSupported(size_t M, size_t N, size_t K, size_t r);
+size_t LoraBackwardPartialFloats(size_t N, size_t K, size_t r);
+bool LoraBackward(const LoraBackwardArgs& args, cudaStream_t s);
+
 // A whole f32 matrix as its bf16 pieces, dst [rows][6 * cols] (six K segments of
 // `cols`): the operand layout that makes an f32 GEMM a bf16 tensor-core GEMM over
 // K' = 6 K (k_lora.cu).  side 0: the A operand's piece order; 1: the B operand's.

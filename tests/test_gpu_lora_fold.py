@@ -249,3 +249,66 @@ def test_adapter_products_with_contracted_multiply_adds():
     for off, n in ((t, M * r), (dt, M * r), (gB, r * K), (gA, K * r)):
         differs = differs or not np.array_equal(fast1[off:off + 4 * n], strict[off:off + 4 * n])
     assert differs, "the contracted kernels gave the exact kernels' bits: did they run?"
+
+
+@pytest.mark.parametrize("shape", [(4096, 768, 16), (4100, 768, 8), (1000, 256, 8)],
+                         ids=["4096x768r16", "4100x768r8-ragged", "1000x256r8"])
+def test_one_pass_adapter_backward_and_tensor_core_down_product(shape):
+    """In lazy coherence the down product t = x A runs as 3xTF32 on the tensor cores,
+    and the three backward products of a site — dT = a dY B^T, dB = a t^T dY,
+    dA = x^T dT, three instructions that each stream an activation — run as one
+    pass over dY and x.  Held to 2e-6 of 1 + sum|a_k b_k| against float64 (the
+    reference's bound for its own GEMMs); identical run to run; the strict seam
+    keeps the exact kernels' bits."""
+    M, D, r = shape
+    rng = np.random.default_rng(M + r)
+    a = Arena(rng)
+    x = a.alloc(M * D, "normal"); dy = a.alloc(M * D, "normal")
+    A = a.alloc(D * r, "normal", scale=0.05); Bm = a.alloc(r * D, "normal", scale=0.05)
+    acc = a.alloc(M * D, "normal")
+    t = a.alloc(M * r); dt = a.alloc(M * r); gB = a.alloc(r * D); gA = a.alloc(D * r); part = a.alloc(M * D)
+    s = 2.0
+    prog = [
+        P.Instr(Op.GEMM_NN, 0, 0, (x, A, t, P.NULL_REF), (M, r, D)),
+        P.Instr(Op.GEMM_NT, 0, P.f32_bits(s), (dy, Bm, dt, P.NULL_REF), (M, r, D)),
+        P.Instr(Op.GEMM_TN, 0, P.f32_bits(s), (t, dy, gB, P.NULL_REF), (r, D, M)),
+        P.Instr(Op.GEMM_NT, ADDEND, 0, (dt, A, part, acc), (M, D, r)),          # what a plan puts in between
+        P.Instr(Op.GEMM_TN, 0, 0, (x, dt, gA, P.NULL_REF), (D, r, M)),
+    ]
+    arena0, ro = a.build()
+
+    def run(coherence, fma=True):
+        arena = arena0.copy()
+        be = B.CudaBackend(0)
+        be.set_coherence(coherence)
+        be.set_adapter_fma(fma)
+        be.bind(arena, ro)
+        be.run(prog)
+        be.host_needs(0, arena.size)
+        be.flush()
+        c = be.counters()
+        be.close()
+        return arena, c
+
+    strict, _ = run(B.COHERENCE_STRICT)
+    fast1, c1 = run(B.COHERENCE_LAZY)
+    fast2, _ = run(B.COHERENCE_LAZY)
+    plain, c0 = run(B.COHERENCE_LAZY, fma=False)
+    assert c1.fused_dispatches == 2 and c0.fused_dispatches == 0
+    assert np.array_equal(fast1, fast2)
+    assert np.array_equal(plain, strict)
+    X = _f32(arena0, x, M * D).reshape(M, D); DY = _f32(arena0, dy, M * D).reshape(M, D)
+    Am = _f32(arena0, A, D * r).reshape(D, r); Bmm = _f32(arena0, Bm, r * D).reshape(r, D)
+    T = _f32(fast1, t, M * r).reshape(M, r); DT = _f32(fast1, dt, M * r).reshape(M, r)
+    cases = [
+        ("t", T, X @ Am, np.abs(X) @ np.abs(Am)),
+        ("dT", DT, s * (DY @ Bmm.T), s * (np.abs(DY) @ np.abs(Bmm.T))),
+        ("dB", _f32(fast1, gB, r * D).reshape(r, D), s * (T.T @ DY), s * (np.abs(T.T) @ np.abs(DY))),
+        ("dA", _f32(fast1, gA, D * r).reshape(D, r), X.T @ DT, np.abs(X.T) @ np.abs(DT)),
+    ]
+    worst = {name: float((np.abs(got - want) / (1.0 + mag)).max()) for name, got, want, mag in cases}
+    assert max(worst.values()) < 2e-6, worst
+    # the expand product in between saw the dT the fused pass wrote
+    want_part = _f32(arena0, acc, M * D).reshape(M, D) + DT @ Am.T
+    got_part = _f32(fast1, part, M * D).reshape(M, D)
+    assert np.abs(got_part - want_part).max() < 1e-4
