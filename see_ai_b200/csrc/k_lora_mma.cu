@@ -45,11 +45,13 @@ __device__ __forceinline__ void CpAsyncWait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
 }
 
-// x = hi + lo with hi the TF32 rounding of x (its low 13 mantissa bits zero) and
-// lo the exact remainder (the tensor core reads lo's leading 11 bits).
+// x = hi + lo with hi = x cut to TF32 (its low 13 mantissa bits cleared) and lo the
+// exact remainder, below 2^-10 |x| (the tensor core reads lo's leading 11 bits, so
+// what is lost is below 2^-21 |x|).  A mask and a subtraction: the rounding
+// conversion instruction runs on the 16-lane special-function pipe and was 30 % of
+// this kernel's issue slots.
 __device__ __forceinline__ void SplitTf32(float x, uint32_t* hi, uint32_t* lo) {
-  uint32_t h;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+  const uint32_t h = __float_as_uint(x) & 0xFFFFE000u;
   *hi = h;
   *lo = __float_as_uint(x - __uint_as_float(h));
 }
@@ -130,12 +132,17 @@ __device__ __forceinline__ void RowsTimesWeight(const float* tile, int stride, W
 }
 
 // ---- forward: t = alpha x A ---------------------------------------------------------------
+// Three row tiles of x in flight per block (the kernel is a stream of 48 KB tiles
+// with a few hundred tensor instructions each: one tile of lookahead left the SM
+// waiting on HBM latency most of the time).
+constexpr int kDownStages = 3;
+
 template <int K, int R>
 struct DownSmem {
   static constexpr int kXStride = K + 8;
-  static constexpr int kAStride = R + 8;     // A is [K][R]: rows k, so a fragment's four k land in four bank groups
+  static constexpr int kAStride = K + 4;     // A^T [R][K]: rows n, so a fragment's eight n land in eight bank groups
   static constexpr int kOutStride = R + 8;
-  static constexpr size_t kFloats = kTileRows * kXStride + static_cast<size_t>(K) * kAStride +
+  static constexpr size_t kFloats = kDownStages * kTileRows * kXStride + static_cast<size_t>(R) * kAStride +
                                     kWarps * kTileRows * R + kTileRows * kOutStride;
 };
 
@@ -146,25 +153,33 @@ LoraDownKernel(const float* __restrict__ x, const float* __restrict__ A, float* 
   using S = DownSmem<K, R>;
   extern __shared__ __align__(16) float smem[];
   float* x_s = smem;
-  float* a_s = x_s + kTileRows * S::kXStride;
-  float* red = a_s + static_cast<size_t>(K) * S::kAStride;
+  float* a_s = x_s + kDownStages * kTileRows * S::kXStride;
+  float* red = a_s + static_cast<size_t>(R) * S::kAStride;
   float* out_s = red + kWarps * kTileRows * R;
-  for (int idx = threadIdx.x; idx < K * R / 4; idx += kThreads) {   // A [K][R], 16 bytes at a time
-    const int k = idx / (R / 4), c = idx - k * (R / 4);
-    *reinterpret_cast<float4*>(a_s + k * S::kAStride + 4 * c) = *reinterpret_cast<const float4*>(A + k * R + 4 * c);
+  for (int idx = threadIdx.x; idx < K * R; idx += kThreads) {   // A [K][R] -> a_s[n][k]
+    const int k = idx / R, n = idx - k * R;
+    a_s[n * S::kAStride + k] = A[idx];
   }
   const size_t tiles = (M + kTileRows - 1) / kTileRows;
-  size_t tile = blockIdx.x;
-  if (tile < tiles) LoadTile<K>(x_s, S::kXStride, x, tile * kTileRows, M);
-  CpAsyncCommit();
-  for (; tile < tiles; tile += gridDim.x) {
-    CpAsyncWait<0>();
-    __syncthreads();
-    RowsTimesWeight<K, R>(x_s, S::kXStride, [&](int n, int k) { return a_s[k * S::kAStride + n]; }, red, out_s,
-                          S::kOutStride, alpha);
-    // (RowsTimesWeight leaves the block synchronised: x_s is free for the next tile.)
-    if (tile + gridDim.x < tiles) LoadTile<K>(x_s, S::kXStride, x, (tile + gridDim.x) * kTileRows, M);
+  // Stage s holds tile blockIdx.x + (i) * gridDim.x for i = s (mod kDownStages); one commit group per tile.
+#pragma unroll
+  for (int i = 0; i < kDownStages - 1; ++i) {
+    const size_t tl = blockIdx.x + static_cast<size_t>(i) * gridDim.x;
+    if (tl < tiles) LoadTile<K>(x_s + i * kTileRows * S::kXStride, S::kXStride, x, tl * kTileRows, M);
     CpAsyncCommit();
+  }
+  int stage = 0;
+  for (size_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    // The tile two ahead goes into the stage the previous iteration finished with.
+    const size_t ahead = tile + static_cast<size_t>(kDownStages - 1) * gridDim.x;
+    const int ahead_stage = (stage + kDownStages - 1) % kDownStages;
+    if (ahead < tiles) LoadTile<K>(x_s + ahead_stage * kTileRows * S::kXStride, S::kXStride, x, ahead * kTileRows, M);
+    CpAsyncCommit();
+    CpAsyncWait<kDownStages - 1>();   // this tile has landed
+    __syncthreads();
+    const float* xs = x_s + stage * kTileRows * S::kXStride;
+    RowsTimesWeight<K, R>(xs, S::kXStride, [&](int n, int k) { return a_s[n * S::kAStride + k]; }, red, out_s,
+                          S::kOutStride, alpha);
     const size_t row0 = tile * kTileRows;
     for (int idx = threadIdx.x; idx < kTileRows * R / 4; idx += kThreads) {
       const int r = idx / (R / 4), c = idx - r * (R / 4);
@@ -172,8 +187,10 @@ LoraDownKernel(const float* __restrict__ x, const float* __restrict__ A, float* 
         *reinterpret_cast<float4*>(out + (row0 + r) * R + 4 * c) =
             *reinterpret_cast<const float4*>(out_s + r * S::kOutStride + 4 * c);
     }
-    __syncthreads();   // out_s is rewritten by the next tile
+    __syncthreads();   // out_s and this stage are rewritten next
+    stage = (stage + 1) % kDownStages;
   }
+  CpAsyncWait<0>();
 }
 
 // ---- backward: dT, and per-block partial sums of dB and dA ------------------------------------
