@@ -16,6 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libsee_cuda.so")
+PROBE = os.path.join(HERE, "see-cuda-plan-probe")   # the seeml-plan-probe-compatible executable over the C ABI
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 
@@ -90,6 +91,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
         run(["g++", "-shared", "-o", LIB] + objs +
             [f"-L{CUDA_HOME}/lib64", "-lcudart_static", "-lrt", "-ldl", "-lpthread",
              "-Wl,--no-undefined"])
+    probe_src = os.path.join(CSRC, "probe_main.cc")
+    if os.path.exists(probe_src) and (jobs or force or _stale(PROBE, [probe_src, LIB] + headers)):
+        run(["g++"] + CXX_FLAGS + [probe_src, os.path.join(OBJ, "extents.cc.o"), "-o", PROBE, f"-L{HERE}",
+                                   "-lsee_cuda", "-Wl,-rpath,$ORIGIN"])
     return LIB
 
 
