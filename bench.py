@@ -317,6 +317,10 @@ def run_plan(args):
             e[0] += ms; e[1] += nbytes; e[2] += 1
             hold = [e, absorbed] if absorbed else None
         profiled_ms = sum(by_op.values())
+        if args.dump_profile and rank == 0:
+            with open(args.dump_profile, "w") as f:
+                json.dump([{"index": i, "op": P.OP_NAMES.get(r[0], str(r[0])), "ms": r[2], "m": r[3], "n": r[4],
+                            "k": r[5], "tensor_kernel_ms": r[6], "absorbed": r[7]} for i, r in enumerate(prof8)], f)
         for _ in range(3 if exchange else 0):
             step(False, 0, time_exchange=True)
 
@@ -594,6 +598,7 @@ def main():
     ap.add_argument("--dtypes", default="", help="config 2: f32,bf16")
     ap.add_argument("--head-dims", default="", help="config 5: 64,128")
     ap.add_argument("--cpu-max-size", type=int, default=1024, help="configs 2 and 5: largest S the CPU arm runs")
+    ap.add_argument("--dump-profile", default="", help="config 4: write the profiled step's per-instruction records here")
     ap.add_argument("--layers", type=int, default=0, help="config 4 only: a REDUCED case for profiler captures")
     ap.add_argument("--batch-seqs", type=int, default=0, help="config 4 only: a REDUCED case for profiler captures")
     args = ap.parse_args()

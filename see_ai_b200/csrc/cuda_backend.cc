@@ -1587,18 +1587,23 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
     const LoraFold* lf = range_index_ < lora_fold_.size() && lora_fold_[range_index_].fuse
                              ? &lora_fold_[range_index_] : nullptr;
     if (lf) {   // the adapter's expand product rides this product's reduction
+      bool pieces_made = false;
       if (lf->kind == 1) {   // its down product t = x A first (the plan has it after this instruction)
         k::GemmArgs d = GemmArgsOf(lf->down);
         d.contract_fma = adapter_fma_;
-        if (!(adapter_fma_ && lf->down.flags == 0 && k::LoraDownSupported(d.M, d.K, d.N) &&
-              k::LoraDown(d.A, static_cast<const float*>(d.B), d.C, d.M, d.K, d.N, d.alpha, stream_)))
-          k::GemmExact(d, stream_);
+        // (the tensor-core form of it leaves t's bf16 cut in the same launch)
+        pieces_made = adapter_fma_ && lf->down.flags == 0 && d.N == lf->r && k::LoraDownSupported(d.M, d.K, d.N) &&
+                      k::LoraDown(d.A, static_cast<const float*>(d.B), d.C, d.M, d.K, d.N, d.alpha, stream_,
+                                  d_lora_t_);
+        if (!pieces_made) k::GemmExact(d, stream_);
         ++counters_.kernel_launches;
         umma::InvalidateRange(&umma_->ctx, RefOffset(lf->down.in[2]), d.M * d.N * 4);
       }
-      if (!k::LoraSplitRows(Rd(lf->t_ref), d_lora_t_, a.M, lf->r, stream_))
-        return std::unexpected("cuda: low-rank fold: the factor cannot be split (rank or alignment)");
-      ++counters_.kernel_launches;
+      if (!pieces_made) {
+        if (!k::LoraSplitRows(Rd(lf->t_ref), d_lora_t_, a.M, lf->r, stream_))
+          return std::unexpected("cuda: low-rank fold: the factor cannot be split (rank or alignment)");
+        ++counters_.kernel_launches;
+      }
       const uint32_t kx = k::LoraSplitColumns(lf->r);
       a.aux_a = d_lora_t_;
       a.aux_b = d_lora_w_ + static_cast<uint64_t>(lf->weight_slot) * lora_max_n_ * lora_max_kx_;

@@ -29,58 +29,33 @@
 // a range into its [N, KX] operand in one launch.  Compiled WITH fused
 // multiply-add: nothing here reproduces a CPU rounding sequence bit for bit.
 #include "kernels.h"
+#include "lora_split.cuh"
 
 namespace see::k {
 
 namespace {
 
-__device__ __forceinline__ uint16_t Bf16Rn(float f) {
-  uint16_t r;
-  asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(f));
-  return r;
-}
-__device__ __forceinline__ float Bf16ToF32(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
-
-// v = p[0] + p[1] + p[2] + (a remainder below 2^-24 |v|); each subtraction is exact.
-__device__ __forceinline__ void Split3(float v, uint16_t (&p)[3]) {
-  p[0] = Bf16Rn(v);
-  const float r1 = v - Bf16ToF32(p[0]);
-  p[1] = Bf16Rn(r1);
-  const float r2 = r1 - Bf16ToF32(p[1]);
-  p[2] = Bf16Rn(r2);
-}
-
-// Which piece each of the six K segments takes from the row factor (side 0) and
-// from the weight factor (side 1): t2 b0, t1 b1, t0 b2, t1 b0, t0 b1, t0 b0.
-__host__ __device__ constexpr int PieceOf(int side, int s) {
-  return side == 0 ? (s == 0 ? 2 : (s == 1 || s == 3 ? 1 : 0))
-                   : (s == 2 ? 2 : (s == 1 || s == 4 ? 1 : 0));
-}
-
-// One thread per row: r values in, KX bf16 out (6 r of them pieces, the rest zero).
+// One thread per (row, four columns of t): 4 values in, their pieces out to the six
+// segments; the threads of a row also zero its padding columns [6 R, KX).
 template <int R>
 __global__ void SplitRowsKernel(const float* __restrict__ t, uint16_t* __restrict__ out, uint32_t M, uint32_t KX) {
-  const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
+  constexpr uint32_t kQuads = R / 4;
+  const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+  const uint32_t row = idx / kQuads, j = (idx - row * kQuads) * 4;
   if (row >= M) return;
-  uint16_t piece[R][3];
-#pragma unroll
-  for (int j = 0; j < R; j += 4) {
-    const float4 v = *reinterpret_cast<const float4*>(t + static_cast<size_t>(row) * R + j);
-    Split3(v.x, piece[j]); Split3(v.y, piece[j + 1]); Split3(v.z, piece[j + 2]); Split3(v.w, piece[j + 3]);
-  }
+  const float4 v = *reinterpret_cast<const float4*>(t + static_cast<size_t>(row) * R + j);
+  uint16_t piece[4][3];
+  Split3(v.x, piece[0]); Split3(v.y, piece[1]); Split3(v.z, piece[2]); Split3(v.w, piece[3]);
   uint16_t* dst = out + static_cast<size_t>(row) * KX;
 #pragma unroll
   for (int s = 0; s < 6; ++s) {
-#pragma unroll
-    for (int j = 0; j < R; j += 4) {
-      const int pc = PieceOf(0, s);
-      uint2 w;
-      w.x = static_cast<uint32_t>(piece[j][pc]) | (static_cast<uint32_t>(piece[j + 1][pc]) << 16);
-      w.y = static_cast<uint32_t>(piece[j + 2][pc]) | (static_cast<uint32_t>(piece[j + 3][pc]) << 16);
-      *reinterpret_cast<uint2*>(dst + s * R + j) = w;
-    }
+    const int pc = PieceOf(0, s);
+    uint2 w;
+    w.x = static_cast<uint32_t>(piece[0][pc]) | (static_cast<uint32_t>(piece[1][pc]) << 16);
+    w.y = static_cast<uint32_t>(piece[2][pc]) | (static_cast<uint32_t>(piece[3][pc]) << 16);
+    *reinterpret_cast<uint2*>(dst + s * R + j) = w;
   }
-  for (uint32_t k = 6 * R; k < KX; k += 4) *reinterpret_cast<uint2*>(dst + k) = make_uint2(0u, 0u);
+  for (uint32_t k = 6 * R + j; k < KX; k += R) *reinterpret_cast<uint2*>(dst + k) = make_uint2(0u, 0u);
 }
 
 // One thread per (entry, output column n): r values of the adapter matrix,
@@ -185,12 +160,12 @@ uint32_t LoraSplitColumns(uint32_t r) { return (6 * r + 63) / 64 * 64; }
 bool LoraSplitRows(const float* t, uint16_t* out, size_t M, uint32_t r, cudaStream_t s) {
   if ((reinterpret_cast<uintptr_t>(t) & 15) != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0) return false;
   const uint32_t KX = LoraSplitColumns(r);
-  const unsigned blocks = static_cast<unsigned>((M + 127) / 128);
+  const unsigned blocks = static_cast<unsigned>((M * (r / 4) + 255) / 256);
   switch (r) {
-    case 4: SplitRowsKernel<4><<<blocks, 128, 0, s>>>(t, out, static_cast<uint32_t>(M), KX); return true;
-    case 8: SplitRowsKernel<8><<<blocks, 128, 0, s>>>(t, out, static_cast<uint32_t>(M), KX); return true;
-    case 12: SplitRowsKernel<12><<<blocks, 128, 0, s>>>(t, out, static_cast<uint32_t>(M), KX); return true;
-    case 16: SplitRowsKernel<16><<<blocks, 128, 0, s>>>(t, out, static_cast<uint32_t>(M), KX); return true;
+    case 4: SplitRowsKernel<4><<<blocks, 256, 0, s>>>(t, out, static_cast<uint32_t>(M), KX); return true;
+    case 8: SplitRowsKernel<8><<<blocks, 256, 0, s>>>(t, out, static_cast<uint32_t>(M), KX); return true;
+    case 12: SplitRowsKernel<12><<<blocks, 256, 0, s>>>(t, out, static_cast<uint32_t>(M), KX); return true;
+    case 16: SplitRowsKernel<16><<<blocks, 256, 0, s>>>(t, out, static_cast<uint32_t>(M), KX); return true;
     default: return false;
   }
 }

@@ -26,6 +26,7 @@
 #include <atomic>
 
 #include "kernels.h"
+#include "lora_split.cuh"
 
 namespace see::k {
 
@@ -132,65 +133,130 @@ __device__ __forceinline__ void RowsTimesWeight(const float* tile, int stride, W
 }
 
 // ---- forward: t = alpha x A ---------------------------------------------------------------
-// Three row tiles of x in flight per block (the kernel is a stream of 48 KB tiles
-// with a few hundred tensor instructions each: one tile of lookahead left the SM
-// waiting on HBM latency most of the time).
-constexpr int kDownStages = 3;
+// A warp owns a 16-row tile over the whole of K: no partial tiles to fold, no
+// block-wide barrier after the prologue.  x goes from global memory straight into
+// the tensor instruction's row fragments: the reduction index inside a 16-wide
+// block of k is permuted (lane t takes columns 4t .. 4t+3: the pairs (4t, 4t+1)
+// and (4t+2, 4t+3) are the (t, t+4) elements of two successive instructions), so
+// that each lane reads its share as one 16-byte load per row and block, four
+// blocks ahead of their use.  A^T sits in shared memory already cut into (hi, lo), read
+// with the same permutation.  Every product term keeps its own accumulator
+// (lo*hi, hi*lo, hi*hi per 8-column group), so successive instructions do not
+// wait on each other; the terms are added small ones first at the end.  With
+// `pieces` set the tile also leaves as the three-way bf16 cut that a base
+// product's reduction takes as extra K columns (lora_split.cuh), which saves the
+// separate pass over t.  (Measured at 32768 x 768, r 16: 30 us, the issue rate of
+// the tensor instruction; the same product as register-tiled f32 multiply-adds on
+// the CUDA cores was bound by shared-memory reads at twice that.)
+constexpr int kDownThreads = 512;
+constexpr int kDownWarps = kDownThreads / 32;
+constexpr int kDownAhead = 4;   // 16-wide k blocks in flight per lane and row
 
 template <int K, int R>
 struct DownSmem {
-  static constexpr int kXStride = K + 8;
-  static constexpr int kAStride = K + 4;     // A^T [R][K]: rows n, so a fragment's eight n land in eight bank groups
-  static constexpr int kOutStride = R + 8;
-  static constexpr size_t kFloats = kDownStages * kTileRows * kXStride + static_cast<size_t>(R) * kAStride +
-                                    kWarps * kTileRows * R + kTileRows * kOutStride;
+  static constexpr int kStride = K + 16;   // rows 16 banks apart: a quarter warp's two rows cover all 32
+  static constexpr size_t kFloats = 2 * static_cast<size_t>(R) * kStride;
 };
 
 template <int K, int R>
-__global__ void __launch_bounds__(kThreads, 1)
-LoraDownKernel(const float* __restrict__ x, const float* __restrict__ A, float* __restrict__ out, size_t M,
-               float alpha) {
+__global__ void __launch_bounds__(kDownThreads, 1)
+LoraDownKernel(const float* __restrict__ x, const float* __restrict__ A, float* __restrict__ out,
+               uint16_t* __restrict__ pieces, uint32_t piece_cols, size_t M, float alpha) {
   using S = DownSmem<K, R>;
   extern __shared__ __align__(16) float smem[];
-  float* x_s = smem;
-  float* a_s = x_s + kDownStages * kTileRows * S::kXStride;
-  float* red = a_s + static_cast<size_t>(R) * S::kAStride;
-  float* out_s = red + kWarps * kTileRows * R;
-  for (int idx = threadIdx.x; idx < K * R; idx += kThreads) {   // A [K][R] -> a_s[n][k]
-    const int k = idx / R, n = idx - k * R;
-    a_s[n * S::kAStride + k] = A[idx];
+  uint32_t* a_hi = reinterpret_cast<uint32_t*>(smem);
+  uint32_t* a_lo = a_hi + static_cast<size_t>(R) * S::kStride;
+  for (int idx = threadIdx.x; idx < K * R; idx += kDownThreads) {   // A [K][R] -> a[n][k], k fastest (bank-free stores)
+    const int n = idx / K, k = idx - n * K;
+    SplitTf32(__ldg(A + k * R + n), &a_hi[n * S::kStride + k], &a_lo[n * S::kStride + k]);
   }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  constexpr int kBlocks = K / 16;
   const size_t tiles = (M + kTileRows - 1) / kTileRows;
-  // Stage s holds tile blockIdx.x + (i) * gridDim.x for i = s (mod kDownStages); one commit group per tile.
+  // Tile order: warp w of block b takes tiles w * gridDim.x + b, + gridDim.x * kDownWarps, ...
+  for (size_t tile = static_cast<size_t>(warp) * gridDim.x + blockIdx.x; tile < tiles;
+       tile += static_cast<size_t>(gridDim.x) * kDownWarps) {
+    const size_t row_a = tile * kTileRows + g, row_b = row_a + 8;
+    const bool in_a = row_a < M, in_b = row_b < M;
+    const float* xa = x + (in_a ? row_a : 0) * K + 4 * t;
+    const float* xb = x + (in_b ? row_b : 0) * K + 4 * t;
+    float c[R / 8][3][4];
 #pragma unroll
-  for (int i = 0; i < kDownStages - 1; ++i) {
-    const size_t tl = blockIdx.x + static_cast<size_t>(i) * gridDim.x;
-    if (tl < tiles) LoadTile<K>(x_s + i * kTileRows * S::kXStride, S::kXStride, x, tl * kTileRows, M);
-    CpAsyncCommit();
-  }
-  int stage = 0;
-  for (size_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-    // The tile two ahead goes into the stage the previous iteration finished with.
-    const size_t ahead = tile + static_cast<size_t>(kDownStages - 1) * gridDim.x;
-    const int ahead_stage = (stage + kDownStages - 1) % kDownStages;
-    if (ahead < tiles) LoadTile<K>(x_s + ahead_stage * kTileRows * S::kXStride, S::kXStride, x, ahead * kTileRows, M);
-    CpAsyncCommit();
-    CpAsyncWait<kDownStages - 1>();   // this tile has landed
-    __syncthreads();
-    const float* xs = x_s + stage * kTileRows * S::kXStride;
-    RowsTimesWeight<K, R>(xs, S::kXStride, [&](int n, int k) { return a_s[n * S::kAStride + k]; }, red, out_s,
-                          S::kOutStride, alpha);
-    const size_t row0 = tile * kTileRows;
-    for (int idx = threadIdx.x; idx < kTileRows * R / 4; idx += kThreads) {
-      const int r = idx / (R / 4), c = idx - r * (R / 4);
-      if (row0 + r < M)
-        *reinterpret_cast<float4*>(out + (row0 + r) * R + 4 * c) =
-            *reinterpret_cast<const float4*>(out_s + r * S::kOutStride + 4 * c);
+    for (int j = 0; j < R / 8; ++j)
+#pragma unroll
+      for (int term = 0; term < 3; ++term) c[j][term][0] = c[j][term][1] = c[j][term][2] = c[j][term][3] = 0.0f;
+    float4 va[kDownAhead], vb[kDownAhead];
+#pragma unroll
+    for (int p = 0; p < kDownAhead; ++p) {
+      va[p] = __ldg(reinterpret_cast<const float4*>(xa + 16 * p));
+      vb[p] = __ldg(reinterpret_cast<const float4*>(xb + 16 * p));
     }
-    __syncthreads();   // out_s and this stage are rewritten next
-    stage = (stage + 1) % kDownStages;
+#pragma unroll 1
+    for (int s0 = 0; s0 < kBlocks; s0 += kDownAhead) {
+#pragma unroll
+      for (int p = 0; p < kDownAhead; ++p) {
+        const int s = s0 + p;
+        const float4 ua = va[p], ub = vb[p];
+        if (s + kDownAhead < kBlocks) {
+          va[p] = __ldg(reinterpret_cast<const float4*>(xa + 16 * (s + kDownAhead)));
+          vb[p] = __ldg(reinterpret_cast<const float4*>(xb + 16 * (s + kDownAhead)));
+        }
+        uint32_t ah0[4], al0[4], ah1[4], al1[4];   // the block's two instructions' row fragments
+        SplitTf32(ua.x, &ah0[0], &al0[0]);
+        SplitTf32(ub.x, &ah0[1], &al0[1]);
+        SplitTf32(ua.y, &ah0[2], &al0[2]);
+        SplitTf32(ub.y, &ah0[3], &al0[3]);
+        SplitTf32(ua.z, &ah1[0], &al1[0]);
+        SplitTf32(ub.z, &ah1[1], &al1[1]);
+        SplitTf32(ua.w, &ah1[2], &al1[2]);
+        SplitTf32(ub.w, &ah1[3], &al1[3]);
+#pragma unroll
+        for (int j = 0; j < R / 8; ++j) {
+          const uint4 h = *reinterpret_cast<const uint4*>(a_hi + (8 * j + g) * S::kStride + 16 * s + 4 * t);
+          const uint4 l = *reinterpret_cast<const uint4*>(a_lo + (8 * j + g) * S::kStride + 16 * s + 4 * t);
+          const uint32_t bh0[2] = {h.x, h.y}, bl0[2] = {l.x, l.y}, bh1[2] = {h.z, h.w}, bl1[2] = {l.z, l.w};
+          Mma1688(c[j][0], al0, bh0);
+          Mma1688(c[j][1], ah0, bl0);
+          Mma1688(c[j][2], ah0, bh0);
+          Mma1688(c[j][0], al1, bh1);
+          Mma1688(c[j][1], ah1, bl1);
+          Mma1688(c[j][2], ah1, bh1);
+        }
+      }
+    }
+    // This lane holds rows g and g + 8, columns 8 j + 2 t and + 1.
+#pragma unroll
+    for (int j = 0; j < R / 8; ++j) {
+      float v[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] = alpha * ((c[j][0][e] + c[j][1][e]) + c[j][2][e]);
+      const int col = 8 * j + 2 * t;
+      if (in_a) *reinterpret_cast<float2*>(out + row_a * R + col) = make_float2(v[0], v[1]);
+      if (in_b) *reinterpret_cast<float2*>(out + row_b * R + col) = make_float2(v[2], v[3]);
+      if (pieces != nullptr) {
+        uint16_t p[4][3];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) Split3(v[e], p[e]);
+#pragma unroll
+        for (int sgm = 0; sgm < 6; ++sgm) {
+          const int pc = PieceOf(0, sgm);
+          if (in_a)
+            *reinterpret_cast<uint32_t*>(pieces + row_a * piece_cols + sgm * R + col) =
+                static_cast<uint32_t>(p[0][pc]) | (static_cast<uint32_t>(p[1][pc]) << 16);
+          if (in_b)
+            *reinterpret_cast<uint32_t*>(pieces + row_b * piece_cols + sgm * R + col) =
+                static_cast<uint32_t>(p[2][pc]) | (static_cast<uint32_t>(p[3][pc]) << 16);
+        }
+      }
+    }
+    if (pieces != nullptr) {   // the padding columns [6 R, piece_cols): each lane of a row's four an equal share
+      for (uint32_t k = 6 * R + 2 * t; k < piece_cols; k += 8) {
+        if (in_a) *reinterpret_cast<uint32_t*>(pieces + row_a * piece_cols + k) = 0u;
+        if (in_b) *reinterpret_cast<uint32_t*>(pieces + row_b * piece_cols + k) = 0u;
+      }
+    }
   }
-  CpAsyncWait<0>();
 }
 
 // ---- backward: dT, and per-block partial sums of dB and dA ------------------------------------
@@ -326,14 +392,26 @@ LoraBackwardKernel(const float* __restrict__ dy, const float* __restrict__ x, co
   }
 }
 
-// out[i] = alpha * (partials[0][i] + partials[1][i] + ...), blocks in order.
-__global__ void FoldPartialsKernel(const float* __restrict__ partials, size_t stride, int blocks, size_t offset,
-                                   size_t n, float alpha, float* __restrict__ out) {
+// dB[i] = alpha_db * (partials[0][i] + partials[1][i] + ...) for i < n_db, dA likewise
+// from the part after it: blocks in order, eight loads in flight per thread.
+__global__ void FoldPartialsKernel(const float* __restrict__ partials, size_t stride, int blocks, size_t n_db,
+                                   size_t n_da, float alpha_db, float alpha_da, float* __restrict__ dB,
+                                   float* __restrict__ dA) {
   const size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
-  if (i >= n) return;
-  float s = partials[offset + i];
-  for (int b = 1; b < blocks; ++b) s += partials[static_cast<size_t>(b) * stride + offset + i];
-  out[i] = alpha * s;
+  if (i >= n_db + n_da) return;
+  const float* p = partials + i;
+  float s = 0.0f;
+  int b = 0;
+  for (; b + 8 <= blocks; b += 8) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = __ldg(p + static_cast<size_t>(b + u) * stride);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) s += v[u];
+  }
+  for (; b < blocks; ++b) s += __ldg(p + static_cast<size_t>(b) * stride);
+  if (i < n_db) dB[i] = alpha_db * s;
+  else dA[i - n_db] = alpha_da * s;
 }
 
 template <typename Kernel>
@@ -366,13 +444,15 @@ int SmCount() {
 }
 
 template <int K, int R>
-bool LaunchDown(const float* x, const float* A, float* out, size_t M, float alpha, cudaStream_t s) {
+bool LaunchDown(const float* x, const float* A, float* out, uint16_t* pieces, uint32_t piece_cols, size_t M,
+                float alpha, cudaStream_t s) {
   static std::atomic<bool> configured[64] = {};
   const size_t smem = DownSmem<K, R>::kFloats * sizeof(float);
   if (!Configure(LoraDownKernel<K, R>, smem, configured)) return false;
+  // One block per SM as soon as there is a tile per SM: the tiles go round the blocks first.
   const size_t tiles = (M + kTileRows - 1) / kTileRows;
   const unsigned grid = static_cast<unsigned>(tiles < static_cast<size_t>(SmCount()) ? tiles : SmCount());
-  LoraDownKernel<K, R><<<grid, kThreads, smem, s>>>(x, A, out, M, alpha);
+  LoraDownKernel<K, R><<<grid, kDownThreads, smem, s>>>(x, A, out, pieces, piece_cols, M, alpha);
   return true;
 }
 
@@ -386,10 +466,9 @@ bool LaunchBackward(const LoraBackwardArgs& a, cudaStream_t s) {
   const size_t stride = static_cast<size_t>(R) * N + static_cast<size_t>(K) * R;
   if (static_cast<size_t>(blocks) * stride > a.partials_floats) return false;
   LoraBackwardKernel<N, K, R><<<blocks, kThreads, smem, s>>>(a.dy, a.x, a.t, a.B, a.dt, a.partials, a.M, a.alpha_dt);
-  FoldPartialsKernel<<<static_cast<unsigned>((static_cast<size_t>(R) * N + 255) / 256), 256, 0, s>>>(
-      a.partials, stride, blocks, 0, static_cast<size_t>(R) * N, a.alpha_db, a.dB);
-  FoldPartialsKernel<<<static_cast<unsigned>((static_cast<size_t>(K) * R + 255) / 256), 256, 0, s>>>(
-      a.partials, stride, blocks, static_cast<size_t>(R) * N, static_cast<size_t>(K) * R, a.alpha_da, a.dA);
+  FoldPartialsKernel<<<static_cast<unsigned>((stride + 127) / 128), 128, 0, s>>>(
+      a.partials, stride, blocks, static_cast<size_t>(R) * N, static_cast<size_t>(K) * R, a.alpha_db, a.alpha_da, a.dB,
+      a.dA);
   return true;
 }
 
@@ -405,11 +484,14 @@ bool LoraDownSupported(size_t M, size_t K, size_t r) {
   return M >= 64 && ((K == 768 && (r == 16 || r == 8)) || (K == 256 && r == 8));
 }
 
-bool LoraDown(const float* x, const float* A, float* out, size_t M, size_t K, size_t r, float alpha, cudaStream_t s) {
-  if (!LoraDownSupported(M, K, r) || !Aligned16(x) || !Aligned16(A) || !Aligned16(out)) return false;
-  if (K == 768 && r == 16) return LaunchDown<768, 16>(x, A, out, M, alpha, s);
-  if (K == 768 && r == 8) return LaunchDown<768, 8>(x, A, out, M, alpha, s);
-  return LaunchDown<256, 8>(x, A, out, M, alpha, s);
+bool LoraDown(const float* x, const float* A, float* out, size_t M, size_t K, size_t r, float alpha, cudaStream_t s,
+              uint16_t* pieces) {
+  if (!LoraDownSupported(M, K, r) || !Aligned16(x) || !Aligned16(A) || !Aligned16(out) || !Aligned16(pieces))
+    return false;
+  const uint32_t cols = LoraSplitColumns(static_cast<uint32_t>(r));
+  if (K == 768 && r == 16) return LaunchDown<768, 16>(x, A, out, pieces, cols, M, alpha, s);
+  if (K == 768 && r == 8) return LaunchDown<768, 8>(x, A, out, pieces, cols, M, alpha, s);
+  return LaunchDown<256, 8>(x, A, out, pieces, cols, M, alpha, s);
 }
 
 bool LoraBackwardSupported(size_t M, size_t N, size_t K, size_t r) {

@@ -223,9 +223,12 @@ void LoraSplitWeights(const LoraWeight* table, int count, uint32_t max_n_out, cu
 
 // ---- the activation-streaming adapter products on the tensor cores (k_lora_mma.cu) -----
 // t = alpha x A for x [M, K], A [K, r]; 3xTF32 (f32-class accuracy, not the CPU's
-// bits).  False (nothing launched) outside the shapes it is built for.
+// bits).  With `pieces` ([M, LoraSplitColumns(r)] bf16) the same launch also writes
+// what LoraSplitRows would make of t.  False (nothing launched) outside the shapes
+// it is built for.
 bool LoraDownSupported(size_t M, size_t K, size_t r);
-bool LoraDown(const float* x, const float* A, float* out, size_t M, size_t K, size_t r, float alpha, cudaStream_t s);
+bool LoraDown(const float* x, const float* A, float* out, size_t M, size_t K, size_t r, float alpha, cudaStream_t s,
+              uint16_t* pieces = nullptr);
 // The three backward products of one adapter site in one pass over dY and x:
 // dT = alpha_dt dY B^T, dB = alpha_db t^T dY, dA = alpha_da x^T dT.  `partials`
 // holds LoraBackwardPartialFloats(N, K, r) floats of scratch.

@@ -86,6 +86,7 @@ def test_probe_trace_agrees_with_the_reference_probes_trace(name):
         got = P.read_trace(open(trace_path, "rb").read())
         want = run["trace"]
         assert [(i, op, len(ext)) for (i, op, _r, ext) in got] == [(i, op, len(ext)) for (i, op, _r, ext) in want]
+        lr = float(np.array([int(lr_bits, 16)], dtype=np.uint32).view(np.float32)[0])
         worst = 0.0
         for (idx, op, _rel, g_ext), (_i, _o, _r2, w_ext) in zip(got, want):
             for (g_off, g_bytes), (w_off, w_bytes) in zip(g_ext, w_ext):
@@ -93,7 +94,13 @@ def test_probe_trace_agrees_with_the_reference_probes_trace(name):
                 # free-running: earlier 1e-7 differences (libm on the device) carry forward, so even the
                 # bit-exact opcodes are held to the differ's default tolerance here (rtol 1e-5, atol 1e-7;
                 # reference: tool/frontier_exec.py:2922-2923)
-                ok, ratio = compare(g_bytes, w_bytes, 1e-5 if op in BIT_EXACT else 1e-4, 1e-7)
+                # An optimizer step moves an element by lr * m / (sqrt(v) + eps); where a gradient is near eps that
+                # quotient magnifies a 1e-7 difference of the gradient, so those extents are allowed 1e-3 of one
+                # update's size (lr) on top of the looser relative bound.
+                if "ADAMW" in P.OP_NAMES[op] or "SGD" in P.OP_NAMES[op]:
+                    ok, ratio = compare(g_bytes, w_bytes, 1e-4, 1e-3 * lr)
+                else:
+                    ok, ratio = compare(g_bytes, w_bytes, 1e-5 if op in BIT_EXACT else 1e-4, 1e-7)
                 worst = max(worst, ratio)
                 assert ok, (idx, P.OP_NAMES[op], ratio)
         image = np.fromfile(out_path, dtype=np.uint8)
