@@ -239,6 +239,23 @@ int see_engine_take_timings(see_engine* h, float* forward_ms, float* backward_ms
  * (reference: compiler/backend/allocation/arena_binder.cc:56-77 binds them back to back). */
 int see_engine_gradient_block(see_engine* h, uint64_t* offset, uint64_t* bytes);
 
+/* Data parallelism, one engine per GPU and process.  No counterpart in the reference (it has no
+ * distributed path); what is exchanged is the gradient block above, once per optimizer step.
+ * see_cuda_exchange_id: a fresh 128-byte communicator id (ncclGetUniqueId; NCCL is resolved from the
+ *   process at run time, error text in see_cuda_create_error()).  One rank makes it and the host hands it
+ *   to the others by whatever channel it has.
+ * see_engine_attach_exchange: a COLLECTIVE call (every rank, same id): joins the communicator and allocates
+ *   the gather buffer.  From then on the step's all-gather runs on the engine's stream between the backward
+ *   range and the optimizer range (inside see_engine_train_optimizer / see_engine_step_program, or earlier
+ *   through see_engine_exchange for a host that wants to time it), and the optimizer kernels sum the
+ *   gathered copies in rank order and scale by 1/world: the same bits on every rank and every run.
+ *   Refused for plans with a masked loss (shards would need a target-count-weighted mean).  world <= 1
+ *   detaches. */
+int see_cuda_exchange_id(uint8_t* out128);
+int see_engine_attach_exchange(see_engine* h, int world, int rank, const uint8_t* id128);
+int see_engine_detach_exchange(see_engine* h);
+int see_engine_exchange(see_engine* h);
+
 /* Checkpoint / gate snapshot of the persistent prefix (adapters + optimizer moments) without stalling
  * training; replaces the host copies the reference engine makes of the persistent segment for its gate and
  * checkpoints (reference: runtime/gating/gate.h:20-49, runtime/storage/checkpoint.h, runtime/dispatcher/update_engine.cc:763).

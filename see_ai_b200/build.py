@@ -38,7 +38,7 @@ CU_SOURCES = {
     "k_gemm_skinny_fast.cu": [],
     "k_lora_mma.cu": [],
 }
-CC_SOURCES = ["extents.cc", "cuda_backend.cc", "c_api.cc", "umma_gemm.cc", "engine.cc"]
+CC_SOURCES = ["extents.cc", "cuda_backend.cc", "c_api.cc", "umma_gemm.cc", "engine.cc", "exchange.cc"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
               "--expt-extended-lambda", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",

@@ -320,6 +320,22 @@ int see_engine_gradient_block(see_engine* h, uint64_t* offset, uint64_t* bytes) 
   h->engine->GradientBlock(offset, bytes);
   return SEE_OK;
 }
+int see_cuda_exchange_id(uint8_t* out128) {
+  if (!out128) return SEE_ERROR;
+  if (auto r = see::MakeExchangeId(out128); !r) {
+    g_create_error = r.error();
+    return SEE_ERROR;
+  }
+  return SEE_OK;
+}
+int see_engine_attach_exchange(see_engine* h, int world, int rank, const uint8_t* id128) {
+  return Done(h, h->engine->AttachExchange(world, rank, id128));
+}
+int see_engine_detach_exchange(see_engine* h) {
+  h->engine->DetachExchange();
+  return SEE_OK;
+}
+int see_engine_exchange(see_engine* h) { return Done(h, h->engine->Exchange()); }
 int see_engine_snapshot_begin(see_engine* h) { return Done(h, h->engine->SnapshotBegin()); }
 int see_engine_snapshot_wait(see_engine* h, void* dst, uint64_t bytes) {
   return Done(h, h->engine->SnapshotWait(dst, bytes));

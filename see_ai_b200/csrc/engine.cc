@@ -265,6 +265,12 @@ Status UpdateEngine::LoadFromMemory(const uint8_t* plan, uint64_t size) {
     pinned_ = static_cast<uint8_t*>(p);
     pinned_bytes_ = stage;
   }
+  // A communicator joined for the previous plan's gradient block does not fit this one.
+  if (exchange_) {
+    exchange_.reset();
+    exchange_pending_ = false;
+    backend_->SetGradientGather(1, nullptr, 0, 0);
+  }
   loaded_ = true;
   return {};
 }
@@ -391,9 +397,54 @@ Status UpdateEngine::RunRange(const std::vector<Instruction>& prog, size_t begin
   return result;
 }
 
+bool UpdateEngine::has_masked_loss() const {
+  for (const Instruction& ins : train_)
+    if (ins.opcode == kSoftmaxXEntMaskedFwd || ins.opcode == kSoftmaxXEntMaskedBwd) return true;
+  return false;
+}
+
+Status UpdateEngine::AttachExchange(int world, int rank, const uint8_t* id) {
+  if (!loaded_) return std::unexpected("engine: no plan is loaded");
+  if (world <= 1) {
+    DetachExchange();
+    return {};
+  }
+  // The masked loss divides each shard's gradient by that shard's own target
+  // count, so the plain 1/N mean of shard gradients is the global masked mean
+  // only when every shard holds the same number of targets: not promised here.
+  if (has_masked_loss())
+    return std::unexpected("engine: data parallel: plans with a masked cross-entropy are not supported "
+                           "(shards would need a target-count-weighted mean)");
+  if (!id) return std::unexpected("engine: data parallel: no communicator id");
+  auto x = GradientExchange::Join(world, rank, id, grad_bytes_);
+  if (!x) return std::unexpected(x.error());
+  DropGraphs();   // the optimizer kernels now read the gathered copies
+  exchange_ = std::move(*x);
+  backend_->SetGradientGather(world, exchange_->gathered(), grad_off_, grad_bytes_);
+  exchange_pending_ = false;
+  return {};
+}
+
+void UpdateEngine::DetachExchange() {
+  if (!exchange_) return;
+  cudaStreamSynchronize(backend_->stream());
+  DropGraphs();
+  backend_->SetGradientGather(1, nullptr, 0, 0);
+  exchange_.reset();
+  exchange_pending_ = false;
+}
+
+Status UpdateEngine::Exchange() {
+  if (!exchange_ || !exchange_pending_) return {};
+  exchange_pending_ = false;
+  const uint8_t* local = static_cast<const uint8_t*>(backend_->device_arena()) + grad_off_;
+  return exchange_->AllGather(local, backend_->stream());
+}
+
 Status UpdateEngine::TrainForwardBackward(bool advance) {
   if (advance) ++step_;
   if (step_ == 0) step_ = 1;  // AdamW's timestep is 1-indexed
+  exchange_pending_ = exchange_ != nullptr;
   if (!phase_timing_) return RunRange(train_, 0, phases_.opt_begin, &g_fwdbwd_, nullptr);
   // Phase timing splits forward from backward at the loss (two ranges, no graph).
   float f = 0, b = 0;
@@ -405,6 +456,7 @@ Status UpdateEngine::TrainForwardBackward(bool advance) {
 }
 
 Status UpdateEngine::TrainOptimizer() {
+  if (auto x = Exchange(); !x) return x;
   float o = 0;
   auto r = RunRange(train_, phases_.opt_begin, train_.size(), phase_timing_ ? nullptr : &g_opt_,
                     phase_timing_ ? &o : nullptr);
@@ -416,6 +468,7 @@ Status UpdateEngine::TrainOptimizer() {
 }
 
 Status UpdateEngine::StepProgram() {
+  if (auto x = Exchange(); !x) return x;
   float o = 0;
   auto r = RunRange(step_prog_, 0, step_prog_.size(), phase_timing_ ? nullptr : &g_step_,
                     phase_timing_ ? &o : nullptr);

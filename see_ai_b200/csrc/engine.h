@@ -21,6 +21,7 @@
 #include <vector>
 
 #include "cuda_backend.h"
+#include "exchange.h"
 #include "plan_abi.h"
 
 namespace see {
@@ -120,6 +121,17 @@ class UpdateEngine {
   // The contiguous arena block holding every optimizer step's gradient
   // operand (what data parallelism exchanges between backward and optimizer).
   void GradientBlock(uint64_t* off, uint64_t* bytes) const { *off = grad_off_; *bytes = grad_bytes_; }
+  // Data parallelism: joins the ranks' communicator (a collective call, same id
+  // on every rank) and from then on all-gathers the gradient block on the step
+  // stream between the backward range and the optimizer range; the optimizer
+  // kernels fold the copies in rank order.  Plans with a masked loss are refused
+  // (each shard's gradient is a mean over its own target count).  Exchange()
+  // enqueues the step's all-gather now (a host that wants to time it); otherwise
+  // TrainOptimizer / StepProgram do it when a backward has run since the last one.
+  Status AttachExchange(int world, int rank, const uint8_t* id);
+  void DetachExchange();
+  Status Exchange();
+  bool has_masked_loss() const;
   uint64_t train_instructions() const { return train_.size(); }
   const std::vector<Instruction>& program(int which) const;  // 0 train, 1 eval, 2 merge, 3 step
 
@@ -163,6 +175,8 @@ class UpdateEngine {
   bool snap_pending_ = false;
   // where the eval program's loss-forward leaves its probabilities
   uint64_t eval_probs_ref_ = kNullRef, eval_labels_ref_ = kNullRef, eval_rows_ = 0, eval_cols_ = 0;
+  std::unique_ptr<GradientExchange> exchange_;
+  bool exchange_pending_ = false;
   bool loaded_ = false;
 };
 

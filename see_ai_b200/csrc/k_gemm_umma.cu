@@ -257,17 +257,25 @@ UmmaGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // under tile i+1's main loop.  What the one-tile kernel pays per tile — barrier
 // set-up, tensor-memory allocation, the first TMA round trip, CTA launch and
 // retirement — is paid once per SM.
-constexpr uint32_t kPBlockN = 256;
-constexpr uint32_t kPStages = 3;
+// The tile width is a template parameter: 256 columns where the product has tiles
+// to spare, 128 where the wide tile would leave SMs without work (a shard of a
+// few thousand rows with a 768-wide output: 96 wide tiles for 148 SMs, against
+// 192 narrow ones; the narrow tile's shorter stage buys a fourth ring slot).
+constexpr uint32_t kPBlockN = 256;                     // the wide tile
+constexpr uint32_t kPMaxStages = 4;
 constexpr uint32_t kPEpiWarps = 16;
 constexpr uint32_t kPThreads = 64 + 32 * kPEpiWarps;   // warp 0 TMA, warp 1 MMA, then the epilogue warps
-constexpr uint32_t kPBTileBytes = kPBlockN * kBlockK * 2;
-constexpr uint32_t kPStageBytes = kATileBytes + kPBTileBytes;
-constexpr uint32_t kPTmemCols = 2 * kPBlockN;
 constexpr uint32_t kSlabCols = 32;
 constexpr uint32_t kSlabBytes = 32 * kSlabCols * 4;   // one epilogue warp's 32 x 32 f32
-constexpr uint32_t kColsPerEpiWarp = kPBlockN / (kPEpiWarps / 4);
-constexpr uint32_t kEpiPasses = kColsPerEpiWarp / kSlabCols;
+template <uint32_t kTN>
+struct PTile {
+  static constexpr uint32_t kStages = kTN == 256 ? 3 : 4;
+  static constexpr uint32_t kBTileBytes = kTN * kBlockK * 2;
+  static constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
+  static constexpr uint32_t kTmemCols = 2 * kTN;
+  static constexpr uint32_t kColsPerEpiWarp = kTN / (kPEpiWarps / 4);
+  static constexpr uint32_t kEpiPasses = kColsPerEpiWarp / kSlabCols;
+};
 
 // Tile order of the persistent kernel.  Bands of band_blocks row blocks; inside a
 // band the row block runs fastest.  With band_blocks = 1 the column tile runs
@@ -291,8 +299,8 @@ __device__ __forceinline__ void TileCoord(uint32_t t, uint32_t tiles_m, uint32_t
 }
 
 struct __align__(8) PBarriers {
-  uint64_t full[kPStages];
-  uint64_t empty[kPStages];
+  uint64_t full[kPMaxStages];
+  uint64_t empty[kPMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
@@ -305,13 +313,16 @@ struct __align__(8) PBarriers {
 // while this group is converted and stored, across passes and from before the
 // wait for the accumulator, so a memory round trip is not paid per group with
 // every warp of the CTA waiting on it.
-template <bool kSideLoads>
+template <bool kSideLoads, uint32_t kTN>
 __global__ void __launch_bounds__(kPThreads, 1)
 UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
                          const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_a2,
                          const __grid_constant__ CUtensorMap map_b2, UmmaEpilogue ep,
                          uint32_t band_blocks) {
+  using T = PTile<kTN>;
+  constexpr uint32_t kPStages = T::kStages, kPStageBytes = T::kStageBytes, kPTmemCols = T::kTmemCols;
+  constexpr uint32_t kColsPerEpiWarp = T::kColsPerEpiWarp, kEpiPasses = T::kEpiPasses;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (SmemAddr(smem_raw) & 1023u)) & 1023u);
   uint8_t* slabs = smem + kPStages * kPStageBytes;
@@ -320,7 +331,7 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t main_blocks = (ep.K + kBlockK - 1) / kBlockK;
   const uint32_t k_blocks = main_blocks + ep.aux_k_blocks;   // then the low-rank term's blocks
-  const uint32_t tiles_n = (ep.N + kPBlockN - 1) / kPBlockN;
+  const uint32_t tiles_n = (ep.N + kTN - 1) / kTN;
   const uint32_t tiles_m = (ep.M + kBlockM - 1) / kBlockM;
   const uint32_t total_tiles = tiles_m * tiles_n;
 
@@ -355,7 +366,7 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
       for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         uint32_t mb, nb;
         TileCoord(t, tiles_m, tiles_n, band_blocks, &mb, &nb);
-        const uint32_t m0 = mb * kBlockM, n0 = nb * kPBlockN;
+        const uint32_t m0 = mb * kBlockM, n0 = nb * kTN;
         // Ask L2 for the A rows of this CTA's next tile now, so that its loads
         // find them there instead of paying an HBM round trip inside the ring.
         if (t + gridDim.x < total_tiles && k_blocks <= 64) {   // (a long K would only thrash L2)
@@ -384,17 +395,18 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
           const CUtensorMap* mb_ = aux ? &map_b2 : &map_b;
           const int32_t kx = static_cast<int32_t>((aux ? kb - main_blocks : kb) * kBlockK);
           TmaLoad2D(a_dst, ma, &bars->full[s], kx, static_cast<int32_t>(m0));
-          // B's 256 rows as two 128-row boxes, back to back: one [256][64] tile.
+          // B's rows as 128-row boxes, back to back: one [kTN][64] tile.
           TmaLoad2D(a_dst + kATileBytes, mb_, &bars->full[s], kx, static_cast<int32_t>(n0));
-          TmaLoad2D(a_dst + kATileBytes + kBTileBytes, mb_, &bars->full[s], kx,
-                    static_cast<int32_t>(n0 + kBlockN));
+          if constexpr (kTN == 256)
+            TmaLoad2D(a_dst + kATileBytes + kBTileBytes, mb_, &bars->full[s], kx,
+                      static_cast<int32_t>(n0 + kBlockN));
         }
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer ----
     if (lane == 0) {
-      const uint32_t idesc = MakeInstrDesc(kBlockM, kPBlockN);
+      const uint32_t idesc = MakeInstrDesc(kBlockM, kTN);
       uint32_t it = 0, lt = 0;
       bool ok = true;
       for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
@@ -405,7 +417,7 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t acc = tmem_base + buf * kPBlockN;
+        const uint32_t acc = tmem_base + buf * kTN;
         for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
           const uint32_t s = it % kPStages, round = it / kPStages;
           if (!MbarWait(&bars->full[s], round & 1)) {
@@ -439,7 +451,7 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t buf = lt & 1, use = lt >> 1;
       uint32_t mb, nb;
       TileCoord(t, tiles_m, tiles_n, band_blocks, &mb, &nb);
-      const uint32_t m0 = mb * kBlockM, n0 = nb * kPBlockN;
+      const uint32_t m0 = mb * kBlockM, n0 = nb * kTN;
       if (ep.fuse_mode == kFuseActBwd) {
         // The absorbed backward activation reads x[m, n] next to every output:
         // ask L2 for this warp's lines of the NEXT tile now (one 128-byte line per
@@ -451,7 +463,7 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
           if (prow >= ep.M) return;
 #pragma unroll
           for (uint32_t pass = 0; pass < kEpiPasses; ++pass) {
-            const uint32_t pcol = pnb * kPBlockN + col_group * kColsPerEpiWarp + pass * kSlabCols;
+            const uint32_t pcol = pnb * kTN + col_group * kColsPerEpiWarp + pass * kSlabCols;
             if (pcol < ep.N)
               asm volatile("prefetch.global.L2 [%0];" ::"l"(ep.fuse_x + static_cast<size_t>(prow) * ep.N + pcol));
           }
@@ -483,7 +495,7 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
       // row as eight 16-byte chunks, chunk index XOR-ed with the row; the warp
       // then reads four rows per instruction (eight lanes each): whole 128-byte
       // lines of C per store instruction.  Conflict-free both ways.
-      const uint32_t t_row = tmem_base + ((quarter * 32) << 16) + buf * kPBlockN + col_group * kColsPerEpiWarp;
+      const uint32_t t_row = tmem_base + ((quarter * 32) << 16) + buf * kTN + col_group * kColsPerEpiWarp;
       if constexpr (!kSideLoads) {
   #pragma unroll 1
         for (uint32_t pass = 0; pass < kEpiPasses; ++pass) {
@@ -647,8 +659,26 @@ __global__ void WeightToBf16Kernel(const T* __restrict__ src, uint16_t* __restri
 }  // namespace
 
 size_t UmmaSmemBytes() { return kStages * kStageBytes + sizeof(Barriers) + 1024; }
+template <uint32_t kTN>
 static size_t UmmaPersistentSmemBytes() {
-  return kPStages * kPStageBytes + kPEpiWarps * kSlabBytes + sizeof(PBarriers) + 1024;
+  return PTile<kTN>::kStages * PTile<kTN>::kStageBytes + kPEpiWarps * kSlabBytes + sizeof(PBarriers) + 1024;
+}
+
+template <bool kSideLoads, uint32_t kTN>
+static cudaError_t ConfigurePersistent() {
+  return cudaFuncSetAttribute(UmmaGemmPersistentKernel<kSideLoads, kTN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(UmmaPersistentSmemBytes<kTN>()));
+}
+
+template <uint32_t kTN>
+static void LaunchPersistent(uint32_t grid, bool side_loads, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                             const CUtensorMap& map_a2, const CUtensorMap& map_b2, const UmmaEpilogue& ep,
+                             uint32_t band, cudaStream_t s) {
+  const size_t smem = UmmaPersistentSmemBytes<kTN>();
+  if (side_loads)
+    UmmaGemmPersistentKernel<true, kTN><<<grid, kPThreads, smem, s>>>(map_a, map_b, map_a2, map_b2, ep, band);
+  else
+    UmmaGemmPersistentKernel<false, kTN><<<grid, kPThreads, smem, s>>>(map_a, map_b, map_a2, map_b2, ep, band);
 }
 
 cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
@@ -662,7 +692,7 @@ cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
   // device, so a second backend on another GPU of the same process configures its own.
   static std::atomic<bool> configured_on[64] = {};
   static int sm_count[64] = {};
-  const size_t smem = UmmaSmemBytes(), psmem = UmmaPersistentSmemBytes();
+  const size_t smem = UmmaSmemBytes();
   int dev = 0;
   cudaGetDevice(&dev);
   const bool tracked = dev >= 0 && dev < 64;
@@ -670,12 +700,10 @@ cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
     cudaError_t e = cudaFuncSetAttribute(UmmaGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(UmmaGemmPersistentKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(psmem));
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(UmmaGemmPersistentKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(psmem));
-    if (e != cudaSuccess) return e;
+    if ((e = ConfigurePersistent<false, 256>()) != cudaSuccess) return e;
+    if ((e = ConfigurePersistent<true, 256>()) != cudaSuccess) return e;
+    if ((e = ConfigurePersistent<false, 128>()) != cudaSuccess) return e;
+    if ((e = ConfigurePersistent<true, 128>()) != cudaSuccess) return e;
     if (tracked) configured_on[dev].store(true, std::memory_order_release);
   }
   if (dev >= 0 && dev < 64 && sm_count[dev] == 0)
@@ -683,13 +711,26 @@ cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
   const uint32_t sms = (dev >= 0 && dev < 64 && sm_count[dev] > 0) ? sm_count[dev] : 148;
   const uint32_t tiles_n = (ep.N + kBlockN - 1) / kBlockN, tiles_m = (ep.M + kBlockM - 1) / kBlockM;
   const uint32_t ptiles_n = (ep.N + kPBlockN - 1) / kPBlockN;
-  if (static_cast<uint64_t>(ptiles_n) * tiles_m > 2ull * sms) {
+  const uint64_t wide = static_cast<uint64_t>(ptiles_n) * tiles_m, narrow = static_cast<uint64_t>(tiles_n) * tiles_m;
+  const bool side_loads = ep.addend != nullptr || ep.fuse_mode == kFuseActBwd;
+  if (wide > 2ull * sms) {
     // Enough tiles for every SM to amortise its set-up over several.
     const uint32_t band = ptiles_n >= kWideTilesN ? kWideBandBlocks : 1u;
-    if (ep.addend != nullptr || ep.fuse_mode == kFuseActBwd)
-      UmmaGemmPersistentKernel<true><<<sms, kPThreads, psmem, s>>>(map_a, map_b, map_a2, map_b2, ep, band);
+    LaunchPersistent<256>(sms, side_loads, map_a, map_b, map_a2, map_b2, ep, band, s);
+    return cudaGetLastError();
+  }
+  if (narrow >= sms / 2) {
+    // A shard-sized product: the persistent kernel's staged, coalesced epilogue on
+    // whichever tile width finishes first, counted in rounds of 128 columns (plus
+    // a quarter tile of fixed cost per round).
+    const uint64_t wide_cost = ((wide + sms - 1) / sms) * (256 + 32);
+    const uint64_t narrow_cost = ((narrow + sms - 1) / sms) * (128 + 32);
+    if (wide_cost <= narrow_cost)
+      LaunchPersistent<256>(static_cast<uint32_t>(wide < sms ? wide : sms), side_loads, map_a, map_b, map_a2, map_b2,
+                            ep, 1u, s);
     else
-      UmmaGemmPersistentKernel<false><<<sms, kPThreads, psmem, s>>>(map_a, map_b, map_a2, map_b2, ep, band);
+      LaunchPersistent<128>(static_cast<uint32_t>(narrow < sms ? narrow : sms), side_loads, map_a, map_b, map_a2,
+                            map_b2, ep, 1u, s);
     return cudaGetLastError();
   }
   dim3 grid(tiles_n, tiles_m);

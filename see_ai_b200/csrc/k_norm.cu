@@ -89,7 +89,7 @@ __global__ void LayerNormBwdKernel(const float* __restrict__ dy, const float* __
 // 16-byte accesses.  Same expressions per element as the scalar kernels; the
 // double sums run over a lane's chunks in ascending order, then the shuffle tree.
 template <int V>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4)
 LayerNormFwdVecKernel(const float* __restrict__ x, const float* __restrict__ gamma,
                       const float* __restrict__ beta, float* __restrict__ y,
                       float* __restrict__ mean, float* __restrict__ rstd, size_t rows, float eps,

@@ -96,49 +96,38 @@ def fixed_order_mean(copies: Sequence[np.ndarray]) -> np.ndarray:
     return (acc * np.float32(1.0 / len(copies))).astype(np.float32)
 
 
-class _DeviceView:
-    """Exposes a raw device range to torch through the CUDA array interface."""
-
-    def __init__(self, ptr: int, nbytes: int):
-        self.__cuda_array_interface__ = {
-            "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None}
-
-
 class GradientExchange:
-    """Owns the gather buffer and performs the per-step all-gather on the
-    engine's stream (torch.distributed, NCCL backend)."""
+    """The per-step exchange of a data-parallel run.  The collective itself lives in the
+    library (see_engine_attach_exchange: an NCCL all-gather on the engine's stream between
+    the backward and the optimizer range, the fold in rank order inside the optimizer
+    kernels); torch.distributed only carries the 128-byte communicator id from rank 0 to
+    the others, and the shard losses for reporting."""
 
     def __init__(self, engine, group=None):
         import torch
         import torch.distributed as dist
+        from . import engine as E
         self.dist = dist
         self.group = group
+        self.engine = engine
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
-        # The masked loss divides each shard's gradient by that shard's own target
-        # count, so the plain 1/N mean of shard gradients is the global masked mean
-        # only when every shard holds the same number of targets: not promised here.
-        if self.world > 1 and getattr(engine, "has_masked_loss", False):
-            raise ValueError("data parallel: plans with a masked cross-entropy are not supported "
-                             "(shards would need a target-count-weighted mean)")
-        # The collective is enqueued on torch's current stream; the engine's kernels
-        # must run on that same stream to be ordered with it.
-        self.stream = torch.cuda.current_stream()
-        engine.backend.set_stream(self.stream.cuda_stream)
-        off, nbytes = engine.gradient_block()
-        self.off, self.nbytes = off, nbytes
-        self.gathered = torch.empty(self.world * nbytes, dtype=torch.uint8, device="cuda")
-        base = engine.backend.device_arena()
-        self.local = torch.as_tensor(_DeviceView(base + off, nbytes), device="cuda")
-        self._loss = torch.zeros(1, dtype=torch.float32, device="cuda")
+        self.off, self.nbytes = engine.gradient_block()
         if self.world > 1:
-            engine.backend.set_gradient_gather(self.world, self.gathered.data_ptr(), off, nbytes)
+            # (refused by the library too; said here before any rank blocks in the collective join)
+            if getattr(engine, "has_masked_loss", False):
+                raise ValueError("data parallel: plans with a masked cross-entropy are not supported "
+                                 "(shards would need a target-count-weighted mean)")
+            box = [E.make_exchange_id() if self.rank == 0 else None]
+            dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0,
+                                       group=group)
+            engine.attach_exchange(self.world, self.rank, box[0])
 
     def exchange(self):
+        """Enqueues the step's all-gather on the engine's stream now; without this call the
+        engine does it at the start of its optimizer range."""
         if self.world > 1:
-            import torch
-            with torch.cuda.stream(self.stream):
-                self.dist.all_gather_into_tensor(self.gathered, self.local, group=self.group)
+            self.engine.exchange()
 
     def mean_loss(self, local_loss: float) -> float:
         """Mean of the shard losses in rank order (each shard's loss is already a

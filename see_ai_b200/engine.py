@@ -22,9 +22,19 @@ ENGINE_SYMBOLS = [
     "see_engine_set_horizon", "see_engine_effective_lr", "see_engine_set_use_graphs",
     "see_engine_set_phase_timing", "see_engine_take_timings", "see_engine_gradient_block",
     "see_engine_snapshot_begin", "see_engine_snapshot_wait", "see_engine_restore",
+    "see_cuda_exchange_id", "see_engine_attach_exchange", "see_engine_detach_exchange", "see_engine_exchange",
 ]
 
 _configured = False
+
+
+def make_exchange_id() -> bytes:
+    """A fresh communicator id for Engine.attach_exchange (made on one rank, handed to all)."""
+    lib = _lib()
+    buf = (ctypes.c_uint8 * 128)()
+    if lib.see_cuda_exchange_id(buf) != 0:
+        raise RuntimeError(lib.see_cuda_create_error().decode())
+    return bytes(buf)
 
 
 class EvalResult(ctypes.Structure):
@@ -72,6 +82,10 @@ def _lib() -> ctypes.CDLL:
     lib.see_engine_take_timings.argtypes = [vp] + [ctypes.POINTER(ctypes.c_float)] * 3 + \
         [ctypes.POINTER(u64)]
     lib.see_engine_gradient_block.argtypes = [vp, ctypes.POINTER(u64), ctypes.POINTER(u64)]
+    lib.see_cuda_exchange_id.argtypes = [vp]
+    lib.see_engine_attach_exchange.argtypes = [vp, ctypes.c_int, ctypes.c_int, vp]
+    lib.see_engine_detach_exchange.argtypes = [vp]
+    lib.see_engine_exchange.argtypes = [vp]
     lib.see_engine_snapshot_begin.argtypes = [vp]
     lib.see_engine_snapshot_wait.argtypes = [vp, vp, u64]
     lib.see_engine_restore.argtypes = [vp, vp, u64, u64]
@@ -242,3 +256,16 @@ class Engine:
         off, n = ctypes.c_uint64(), ctypes.c_uint64()
         self._check(self.lib.see_engine_gradient_block(self.h, ctypes.byref(off), ctypes.byref(n)))
         return int(off.value), int(n.value)
+
+    # -- data parallelism: the NCCL all-gather of the gradient block inside the library --
+    def attach_exchange(self, world: int, rank: int, comm_id: bytes):
+        """Collective over the ranks (same 128-byte id everywhere); world <= 1 detaches."""
+        buf = (ctypes.c_uint8 * 128).from_buffer_copy(comm_id) if comm_id else None
+        self._check(self.lib.see_engine_attach_exchange(self.h, world, rank, buf))
+
+    def detach_exchange(self):
+        self._check(self.lib.see_engine_detach_exchange(self.h))
+
+    def exchange(self):
+        """Enqueues this step's all-gather now (otherwise the optimizer call does it)."""
+        self._check(self.lib.see_engine_exchange(self.h))

@@ -33,8 +33,10 @@ def bf16_round(x: np.ndarray) -> np.ndarray:
     return b.astype(np.uint32).view(np.float32)
 
 
+# The last three are shard-sized: too few 128 x 256 tiles for every SM, so the persistent kernel
+# takes them on 128-wide tiles (or on one wide tile per CTA), ragged edges included.
 SHAPES = [(64, 16, 64), (128, 128, 64), (256, 384, 512), (200, 132, 72), (512, 768, 768),
-          (130, 260, 200), (1000, 64, 3072)]
+          (130, 260, 200), (1000, 64, 3072), (4096, 768, 768), (2500, 780, 320), (9000, 520, 192)]
 
 
 def build_case(rng, M, N, K, pre_round=True):
