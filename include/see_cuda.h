@@ -110,6 +110,10 @@ int see_cuda_set_adapter_fma(see_cuda_backend* h, int enabled);
  * kernels_test.cc:1803-1822), not the CPU's bits.  mode -1 (default): in lazy
  * coherence only; 0: never; 1: in strict coherence too. */
 int see_cuda_set_split_gemm(see_cuda_backend* h, int mode);
+/* Large tensor-core products run on CTA pairs (two SMs per 256 x 256 tile, each loading half of the
+ * weight tile).  Default on; 0 = one CTA per 128 x 256 tile.  Results are identical either way (the same
+ * products in the same order).  Process-wide, not per handle. */
+int see_cuda_set_cta_pairs(int enabled);
 /* Data parallelism: optimizer steps read gradients inside [block_offset,
  * block_offset + block_bytes) as the rank-ordered sum of `ranks` gathered
  * copies (device memory, copy r at gathered + r * block_bytes) times 1/ranks. */

@@ -9,6 +9,7 @@
 
 #include "cuda_backend.h"
 #include "engine.h"
+#include "umma_kernel.h"
 
 struct see_cuda_backend {
   see::CudaBackend* backend = nullptr;          // borrowed when owned is empty
@@ -126,6 +127,11 @@ int see_cuda_set_adapter_fma(see_cuda_backend* h, int enabled) {
 
 int see_cuda_set_split_gemm(see_cuda_backend* h, int mode) {
   h->backend->SetSplitGemm(mode);
+  return SEE_OK;
+}
+
+int see_cuda_set_cta_pairs(int enabled) {
+  see::k::UmmaSetCtaPairs(enabled != 0);
   return SEE_OK;
 }
 

@@ -19,6 +19,8 @@
 // memory and returns, and the host reports the condition at its next flush.
 #include <cuda.h>
 
+#include <utility>
+
 #include <atomic>
 
 #include "act_expr.cuh"
@@ -262,19 +264,28 @@ UmmaGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // few thousand rows with a 768-wide output: 96 wide tiles for 148 SMs, against
 // 192 narrow ones; the narrow tile's shorter stage buys a fourth ring slot).
 constexpr uint32_t kPBlockN = 256;                     // the wide tile
-constexpr uint32_t kPMaxStages = 4;
+constexpr uint32_t kPMaxStages = 5;
 constexpr uint32_t kPEpiWarps = 16;
 constexpr uint32_t kPThreads = 64 + 32 * kPEpiWarps;   // warp 0 TMA, warp 1 MMA, then the epilogue warps
 constexpr uint32_t kSlabCols = 32;
 constexpr uint32_t kSlabBytes = 32 * kSlabCols * 4;   // one epilogue warp's 32 x 32 f32
-template <uint32_t kTN>
+// kPair: two CTAs of a cluster work one 256 x 256 tile (cta_group::2): each loads
+// its own 128 rows of A and its own 128 of B's 256 rows (32 KB per k block instead
+// of 48 KB for the same 128 x 256 of output per CTA), the even CTA issues one
+// 256-row MMA that reads both shared memories, and each CTA's tensor memory
+// receives its own 128 rows.  A third less operand traffic from L2 per flop, and
+// the smaller stage leaves room for five ring slots: the K = 768 shapes of the
+// step were bound by bytes in flight per SM, not by the tensor pipe.
+template <uint32_t kTN, bool kPair>
 struct PTile {
-  static constexpr uint32_t kStages = kTN == 256 ? 3 : 4;
-  static constexpr uint32_t kBTileBytes = kTN * kBlockK * 2;
+  static constexpr uint32_t kStages = kPair ? 5 : (kTN == 256 ? 3 : 4);
+  static constexpr uint32_t kBRows = kPair ? kTN / 2 : kTN;      // rows of B this CTA loads per k block
+  static constexpr uint32_t kBTileBytes = kBRows * kBlockK * 2;
   static constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
   static constexpr uint32_t kTmemCols = 2 * kTN;
   static constexpr uint32_t kColsPerEpiWarp = kTN / (kPEpiWarps / 4);
   static constexpr uint32_t kEpiPasses = kColsPerEpiWarp / kSlabCols;
+  static constexpr uint32_t kRowsPerTile = kPair ? 2 * kBlockM : kBlockM;
 };
 
 // Tile order of the persistent kernel.  Bands of band_blocks row blocks; inside a
@@ -313,14 +324,14 @@ struct __align__(8) PBarriers {
 // while this group is converted and stored, across passes and from before the
 // wait for the accumulator, so a memory round trip is not paid per group with
 // every warp of the CTA waiting on it.
-template <bool kSideLoads, uint32_t kTN>
+template <bool kSideLoads, uint32_t kTN, bool kPair>
 __global__ void __launch_bounds__(kPThreads, 1)
 UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
                          const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_a2,
                          const __grid_constant__ CUtensorMap map_b2, UmmaEpilogue ep,
                          uint32_t band_blocks) {
-  using T = PTile<kTN>;
+  using T = PTile<kTN, kPair>;
   constexpr uint32_t kPStages = T::kStages, kPStageBytes = T::kStageBytes, kPTmemCols = T::kTmemCols;
   constexpr uint32_t kColsPerEpiWarp = T::kColsPerEpiWarp, kEpiPasses = T::kEpiPasses;
   extern __shared__ uint8_t smem_raw[];
@@ -332,8 +343,11 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t main_blocks = (ep.K + kBlockK - 1) / kBlockK;
   const uint32_t k_blocks = main_blocks + ep.aux_k_blocks;   // then the low-rank term's blocks
   const uint32_t tiles_n = (ep.N + kTN - 1) / kTN;
-  const uint32_t tiles_m = (ep.M + kBlockM - 1) / kBlockM;
+  const uint32_t tiles_m = (ep.M + T::kRowsPerTile - 1) / T::kRowsPerTile;
   const uint32_t total_tiles = tiles_m * tiles_n;
+  // A work unit is a CTA, or a CTA pair: `unit` walks the tiles, `cta_rank` is this CTA's half of a pair's tile.
+  const uint32_t cta_rank = kPair ? ClusterCtaRank() : 0u;
+  const uint32_t unit = kPair ? blockIdx.x >> 1 : blockIdx.x, units = kPair ? gridDim.x >> 1 : gridDim.x;
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < kPStages; ++s) {
@@ -342,19 +356,25 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
     }
     for (uint32_t b = 0; b < 2; ++b) {
       MbarInit(&bars->tmem_full[b], 1);
-      MbarInit(&bars->tmem_empty[b], kPEpiWarps);   // one arrival per epilogue warp
+      // one arrival per epilogue warp (of both CTAs of a pair: the even CTA's barrier counts them all)
+      MbarInit(&bars->tmem_empty[b], kPair ? 2 * kPEpiWarps : kPEpiWarps);
     }
     bars->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(SmemAddr(&bars->tmem_base)), "r"(kPTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (kPair) {
+      TmemAllocPair(const_cast<uint32_t*>(&bars->tmem_base), kPTmemCols);
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                   ::"r"(SmemAddr(&bars->tmem_base)), "r"(kPTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if constexpr (kPair) ClusterSync();   // the peer's barriers exist before anything signals them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = bars->tmem_base;
 
@@ -363,16 +383,16 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (uint32_t t = unit; t < total_tiles && ok; t += units) {
         uint32_t mb, nb;
         TileCoord(t, tiles_m, tiles_n, band_blocks, &mb, &nb);
-        const uint32_t m0 = mb * kBlockM, n0 = nb * kTN;
+        const uint32_t m0 = mb * T::kRowsPerTile + cta_rank * kBlockM, n0 = nb * kTN;
         // Ask L2 for the A rows of this CTA's next tile now, so that its loads
         // find them there instead of paying an HBM round trip inside the ring.
-        if (t + gridDim.x < total_tiles && k_blocks <= 64) {   // (a long K would only thrash L2)
+        if (t + units < total_tiles && k_blocks <= 64) {   // (a long K would only thrash L2)
           uint32_t next_mb, next_nb;
-          TileCoord(t + gridDim.x, tiles_m, tiles_n, band_blocks, &next_mb, &next_nb);
-          const uint32_t next_m0 = next_mb * kBlockM;
+          TileCoord(t + units, tiles_m, tiles_n, band_blocks, &next_mb, &next_nb);
+          const uint32_t next_m0 = next_mb * T::kRowsPerTile + cta_rank * kBlockM;
           if (next_m0 != m0)
             for (uint32_t kb = 0; kb < main_blocks; ++kb)
               asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
@@ -389,27 +409,35 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
             break;
           }
           uint8_t* a_dst = smem + s * kPStageBytes;
-          MbarExpectTx(&bars->full[s], kPStageBytes);
           const bool aux = kb >= main_blocks;
           const CUtensorMap* ma = aux ? &map_a2 : &map_a;
           const CUtensorMap* mb_ = aux ? &map_b2 : &map_b;
           const int32_t kx = static_cast<int32_t>((aux ? kb - main_blocks : kb) * kBlockK);
-          TmaLoad2D(a_dst, ma, &bars->full[s], kx, static_cast<int32_t>(m0));
-          // B's rows as 128-row boxes, back to back: one [kTN][64] tile.
-          TmaLoad2D(a_dst + kATileBytes, mb_, &bars->full[s], kx, static_cast<int32_t>(n0));
-          if constexpr (kTN == 256)
-            TmaLoad2D(a_dst + kATileBytes + kBTileBytes, mb_, &bars->full[s], kx,
-                      static_cast<int32_t>(n0 + kBlockN));
+          if constexpr (kPair) {
+            // Both CTAs' bytes are counted on the even CTA's barrier, which alone expects them.
+            if (cta_rank == 0) MbarExpectTx(&bars->full[s], 2 * kPStageBytes);
+            const uint32_t full_bar = MapToCta(SmemAddr(&bars->full[s]), 0);
+            TmaLoad2DPair(a_dst, ma, full_bar, kx, static_cast<int32_t>(m0));
+            TmaLoad2DPair(a_dst + kATileBytes, mb_, full_bar, kx, static_cast<int32_t>(n0 + cta_rank * kBlockN));
+          } else {
+            MbarExpectTx(&bars->full[s], kPStageBytes);
+            TmaLoad2D(a_dst, ma, &bars->full[s], kx, static_cast<int32_t>(m0));
+            // B's rows as 128-row boxes, back to back: one [kTN][64] tile.
+            TmaLoad2D(a_dst + kATileBytes, mb_, &bars->full[s], kx, static_cast<int32_t>(n0));
+            if constexpr (kTN == 256)
+              TmaLoad2D(a_dst + kATileBytes + kBTileBytes, mb_, &bars->full[s], kx,
+                        static_cast<int32_t>(n0 + kBlockN));
+          }
         }
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer ----
-    if (lane == 0) {
-      const uint32_t idesc = MakeInstrDesc(kBlockM, kTN);
+    if (lane == 0 && cta_rank == 0) {   // (a pair's odd CTA issues nothing: its memories are read by the even one's MMAs)
+      const uint32_t idesc = MakeInstrDesc(T::kRowsPerTile, kTN);
       uint32_t it = 0, lt = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
+      for (uint32_t t = unit; t < total_tiles && ok; t += units, ++lt) {
         const uint32_t buf = lt & 1, use = lt >> 1;
         if (use > 0 && !MbarWait(&bars->tmem_empty[buf], (use - 1) & 1)) {
           ep.status->wait_timeout = 1;
@@ -431,11 +459,16 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
           const uint64_t desc_a = MakeSmemDesc(a_addr);
           const uint64_t desc_b = MakeSmemDesc(a_addr + kATileBytes);
 #pragma unroll
-          for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k)
-            UmmaBf16(acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-          UmmaCommit(&bars->empty[s]);
+          for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k) {
+            if constexpr (kPair) UmmaBf16Pair(acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            else UmmaBf16(acc, desc_a + 2 * k, desc_b + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          if constexpr (kPair) UmmaCommitPair(&bars->empty[s]);
+          else UmmaCommit(&bars->empty[s]);
         }
-        UmmaCommit(&bars->tmem_full[buf]);   // accumulator complete (or abandoned on timeout)
+        // accumulator complete (or abandoned on timeout)
+        if constexpr (kPair) UmmaCommitPair(&bars->tmem_full[buf]);
+        else UmmaCommit(&bars->tmem_full[buf]);
       }
     }
   } else {
@@ -447,11 +480,11 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
     constexpr uint32_t kRowsPerInstr = 32 / kChunks;     // rows one store instruction covers
     const uint32_t sub = lane / kChunks, cl = lane % kChunks;
     uint32_t lt = 0;
-    for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++lt) {
+    for (uint32_t t = unit; t < total_tiles; t += units, ++lt) {
       const uint32_t buf = lt & 1, use = lt >> 1;
       uint32_t mb, nb;
       TileCoord(t, tiles_m, tiles_n, band_blocks, &mb, &nb);
-      const uint32_t m0 = mb * kBlockM, n0 = nb * kTN;
+      const uint32_t m0 = mb * T::kRowsPerTile + cta_rank * kBlockM, n0 = nb * kTN;
       if (ep.fuse_mode == kFuseActBwd) {
         // The absorbed backward activation reads x[m, n] next to every output:
         // ask L2 for this warp's lines of the NEXT tile now (one 128-byte line per
@@ -459,7 +492,7 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
         auto prefetch_x = [&](uint32_t tile) {
           uint32_t pmb, pnb;
           TileCoord(tile, tiles_m, tiles_n, band_blocks, &pmb, &pnb);
-          const uint32_t prow = pmb * kBlockM + quarter * 32 + lane;
+          const uint32_t prow = pmb * T::kRowsPerTile + cta_rank * kBlockM + quarter * 32 + lane;
           if (prow >= ep.M) return;
 #pragma unroll
           for (uint32_t pass = 0; pass < kEpiPasses; ++pass) {
@@ -469,7 +502,7 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
           }
         };
         if (lt == 0) prefetch_x(t);
-        if (t + gridDim.x < total_tiles) prefetch_x(t + gridDim.x);
+        if (t + units < total_tiles) prefetch_x(t + units);
       }
       const uint32_t row0 = m0 + quarter * 32;
       const uint32_t rows = row0 < ep.M ? (ep.M - row0 < 32 ? ep.M - row0 : 32) : 0;
@@ -506,9 +539,13 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
             // The accumulator buffer is read out: hand it back before the slow part.
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0)
-              asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];"
-                           ::"r"(SmemAddr(&bars->tmem_empty[buf])) : "memory");
+            if (lane == 0) {
+              if constexpr (kPair)
+                MbarArriveCluster(MapToCta(SmemAddr(&bars->tmem_empty[buf]), 0));
+              else
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];"
+                             ::"r"(SmemAddr(&bars->tmem_empty[buf])) : "memory");
+            }
           }
   #pragma unroll
           for (uint32_t q = 0; q < kChunks; ++q)
@@ -555,9 +592,13 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
           if (pass == kEpiPasses - 1) {
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0)
-              asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];"
-                           ::"r"(SmemAddr(&bars->tmem_empty[buf])) : "memory");
+            if (lane == 0) {
+              if constexpr (kPair)
+                MbarArriveCluster(MapToCta(SmemAddr(&bars->tmem_empty[buf]), 0));
+              else
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];"
+                             ::"r"(SmemAddr(&bars->tmem_empty[buf])) : "memory");
+            }
           }
 #pragma unroll
           for (uint32_t q = 0; q < kChunks; ++q)
@@ -598,11 +639,16 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if constexpr (kPair) ClusterSync();   // neither CTA leaves while the other may still read its memories
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(kPTmemCols)
-                 : "memory");
+    if constexpr (kPair) {
+      TmemFreePair(tmem_base, kPTmemCols);
+    } else {
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"(kPTmemCols)
+                   : "memory");
+    }
   }
 }
 
@@ -659,27 +705,66 @@ __global__ void WeightToBf16Kernel(const T* __restrict__ src, uint16_t* __restri
 }  // namespace
 
 size_t UmmaSmemBytes() { return kStages * kStageBytes + sizeof(Barriers) + 1024; }
-template <uint32_t kTN>
+template <uint32_t kTN, bool kPair>
 static size_t UmmaPersistentSmemBytes() {
-  return PTile<kTN>::kStages * PTile<kTN>::kStageBytes + kPEpiWarps * kSlabBytes + sizeof(PBarriers) + 1024;
+  using T = PTile<kTN, kPair>;
+  return T::kStages * T::kStageBytes + kPEpiWarps * kSlabBytes + sizeof(PBarriers) + 1024;
 }
 
-template <bool kSideLoads, uint32_t kTN>
+template <bool kSideLoads, uint32_t kTN, bool kPair>
 static cudaError_t ConfigurePersistent() {
-  return cudaFuncSetAttribute(UmmaGemmPersistentKernel<kSideLoads, kTN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(UmmaPersistentSmemBytes<kTN>()));
+  return cudaFuncSetAttribute(UmmaGemmPersistentKernel<kSideLoads, kTN, kPair>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(UmmaPersistentSmemBytes<kTN, kPair>()));
+}
+
+// A launch with an optional cluster dimension (2 for the CTA-pair form).
+// (Programmatic dependent launches — the next kernel's set-up run beside this
+// one's tail — were measured on the whole step and cost 1 %: not used.)
+template <typename... KArgs, typename... Args>
+static cudaError_t LaunchClustered(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                   unsigned cluster, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = cluster > 1 ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 template <uint32_t kTN>
-static void LaunchPersistent(uint32_t grid, bool side_loads, const CUtensorMap& map_a, const CUtensorMap& map_b,
-                             const CUtensorMap& map_a2, const CUtensorMap& map_b2, const UmmaEpilogue& ep,
-                             uint32_t band, cudaStream_t s) {
-  const size_t smem = UmmaPersistentSmemBytes<kTN>();
+static cudaError_t LaunchPersistent(uint32_t grid, bool side_loads, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                                    const CUtensorMap& map_a2, const CUtensorMap& map_b2, const UmmaEpilogue& ep,
+                                    uint32_t band, cudaStream_t s) {
+  const size_t smem = UmmaPersistentSmemBytes<kTN, false>();
   if (side_loads)
-    UmmaGemmPersistentKernel<true, kTN><<<grid, kPThreads, smem, s>>>(map_a, map_b, map_a2, map_b2, ep, band);
-  else
-    UmmaGemmPersistentKernel<false, kTN><<<grid, kPThreads, smem, s>>>(map_a, map_b, map_a2, map_b2, ep, band);
+    return LaunchClustered(UmmaGemmPersistentKernel<true, kTN, false>, dim3(grid), dim3(kPThreads), smem, s, 1u, map_a,
+                           map_b, map_a2, map_b2, ep, band);
+  return LaunchClustered(UmmaGemmPersistentKernel<false, kTN, false>, dim3(grid), dim3(kPThreads), smem, s, 1u, map_a,
+                         map_b, map_a2, map_b2, ep, band);
 }
+
+// The CTA-pair form: clusters of two, an even grid.
+static cudaError_t LaunchPairs(uint32_t grid, bool side_loads, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                               const CUtensorMap& map_a2, const CUtensorMap& map_b2, const UmmaEpilogue& ep,
+                               uint32_t band, cudaStream_t s) {
+  const size_t smem = UmmaPersistentSmemBytes<256, true>();
+  if (side_loads)
+    return LaunchClustered(UmmaGemmPersistentKernel<true, 256, true>, dim3(grid & ~1u), dim3(kPThreads), smem, s, 2u,
+                           map_a, map_b, map_a2, map_b2, ep, band);
+  return LaunchClustered(UmmaGemmPersistentKernel<false, 256, true>, dim3(grid & ~1u), dim3(kPThreads), smem, s, 2u,
+                         map_a, map_b, map_a2, map_b2, ep, band);
+}
+
+static std::atomic<bool> g_cta_pairs{true};
+void UmmaSetCtaPairs(bool on) { g_cta_pairs.store(on, std::memory_order_relaxed); }
 
 cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
                            const UmmaEpilogue& ep, cudaStream_t s, const CUtensorMap* aux_a,
@@ -700,10 +785,12 @@ cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
     cudaError_t e = cudaFuncSetAttribute(UmmaGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e != cudaSuccess) return e;
-    if ((e = ConfigurePersistent<false, 256>()) != cudaSuccess) return e;
-    if ((e = ConfigurePersistent<true, 256>()) != cudaSuccess) return e;
-    if ((e = ConfigurePersistent<false, 128>()) != cudaSuccess) return e;
-    if ((e = ConfigurePersistent<true, 128>()) != cudaSuccess) return e;
+    if ((e = ConfigurePersistent<false, 256, false>()) != cudaSuccess) return e;
+    if ((e = ConfigurePersistent<true, 256, false>()) != cudaSuccess) return e;
+    if ((e = ConfigurePersistent<false, 128, false>()) != cudaSuccess) return e;
+    if ((e = ConfigurePersistent<true, 128, false>()) != cudaSuccess) return e;
+    if ((e = ConfigurePersistent<false, 256, true>()) != cudaSuccess) return e;
+    if ((e = ConfigurePersistent<true, 256, true>()) != cudaSuccess) return e;
     if (tracked) configured_on[dev].store(true, std::memory_order_release);
   }
   if (dev >= 0 && dev < 64 && sm_count[dev] == 0)
@@ -716,8 +803,12 @@ cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
   if (wide > 2ull * sms) {
     // Enough tiles for every SM to amortise its set-up over several.
     const uint32_t band = ptiles_n >= kWideTilesN ? kWideBandBlocks : 1u;
-    LaunchPersistent<256>(sms, side_loads, map_a, map_b, map_a2, map_b2, ep, band, s);
-    return cudaGetLastError();
+    // CTA pairs where the reduction is long: measured at 32768 rows, K = 3072 and 32000 gain 9-10 % (a third
+    // less operand traffic per flop), while at K = 768 the epilogue sets the pace and a pair's two epilogues,
+    // which must both finish before the accumulator buffer is free again, cost 5-15 % where they are heavy.
+    if (g_cta_pairs.load(std::memory_order_relaxed) && sms >= 2 && ep.K >= 1536)
+      return LaunchPairs(sms, side_loads, map_a, map_b, map_a2, map_b2, ep, band > 1 ? band / 2 : 1u, s);
+    return LaunchPersistent<256>(sms, side_loads, map_a, map_b, map_a2, map_b2, ep, band, s);
   }
   if (narrow >= sms / 2) {
     // A shard-sized product: the persistent kernel's staged, coalesced epilogue on
@@ -726,16 +817,13 @@ cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
     const uint64_t wide_cost = ((wide + sms - 1) / sms) * (256 + 32);
     const uint64_t narrow_cost = ((narrow + sms - 1) / sms) * (128 + 32);
     if (wide_cost <= narrow_cost)
-      LaunchPersistent<256>(static_cast<uint32_t>(wide < sms ? wide : sms), side_loads, map_a, map_b, map_a2, map_b2,
-                            ep, 1u, s);
-    else
-      LaunchPersistent<128>(static_cast<uint32_t>(narrow < sms ? narrow : sms), side_loads, map_a, map_b, map_a2,
-                            map_b2, ep, 1u, s);
-    return cudaGetLastError();
+      return LaunchPersistent<256>(static_cast<uint32_t>(wide < sms ? wide : sms), side_loads, map_a, map_b, map_a2,
+                                   map_b2, ep, 1u, s);
+    return LaunchPersistent<128>(static_cast<uint32_t>(narrow < sms ? narrow : sms), side_loads, map_a, map_b, map_a2,
+                                 map_b2, ep, 1u, s);
   }
   dim3 grid(tiles_n, tiles_m);
-  UmmaGemmKernel<<<grid, kThreads, smem, s>>>(map_a, map_b, map_a2, map_b2, ep);
-  return cudaGetLastError();
+  return LaunchClustered(UmmaGemmKernel, grid, dim3(kThreads), smem, s, 1u, map_a, map_b, map_a2, map_b2, ep);
 }
 
 void WeightToBf16(const void* src, BType type, uint16_t* dst, uint32_t N, uint32_t K,

@@ -114,6 +114,69 @@ __device__ __forceinline__ void UmmaCommit(uint64_t* bar) {
                ::"r"(SmemAddr(bar))
                : "memory");
 }
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster, one 256-row tile ---------------------
+// The even CTA of the pair (cluster rank 0) issues every MMA; each CTA's shared
+// memory holds its own 128 rows of A and its own half of B's rows, each CTA's
+// tensor memory receives its own 128 rows of the product.
+__device__ __forceinline__ uint32_t ClusterCtaRank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The shared::cluster address of `local` (a shared::cta address) in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t MapToCta(uint32_t local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void ClusterSync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// A tile load whose completion bytes are counted on a barrier of the pair's even CTA
+// (`bar_cluster_addr`: a shared::cluster address); the data lands in the executing
+// CTA's own shared memory only.
+__device__ __forceinline__ void TmaLoad2DPair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                              int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      ::"r"(SmemAddr(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void UmmaBf16Pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair
+// once the MMAs issued so far are complete: one commit per CTA, each naming that
+// CTA's barrier by its shared::cluster address.
+__device__ __forceinline__ void UmmaCommitPair(uint64_t* bar) {
+  const uint32_t local = SmemAddr(bar);
+#pragma unroll
+  for (uint32_t rank = 0; rank < 2; ++rank)
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(MapToCta(local, rank))
+                 : "memory");
+}
+__device__ __forceinline__ void MbarArriveCluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void TmemAllocPair(uint32_t* smem_slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+               ::"r"(SmemAddr(smem_slot)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void TmemFreePair(uint32_t base, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+}
+
 __device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void TcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void TmemWaitLd() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }

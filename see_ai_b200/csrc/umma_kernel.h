@@ -53,6 +53,8 @@ size_t UmmaSmemBytes();
 cudaError_t UmmaGemmLaunch(const CUtensorMap& map_a, const CUtensorMap& map_b,
                            const UmmaEpilogue& ep, cudaStream_t s, const CUtensorMap* aux_a = nullptr,
                            const CUtensorMap* aux_b = nullptr);
+// Large products run on CTA pairs (cta_group::2) by default; off = one CTA per tile.  Process-wide.
+void UmmaSetCtaPairs(bool on);
 // dst[N][K] (bf16 bits) from src [K][N] (transpose) or [N][K]; int8 and bf16 widen exactly.
 // k_scale (or null): dst[n][k] = bf16(src * k_scale[k]).
 void WeightToBf16(const void* src, BType type, uint16_t* dst, uint32_t N, uint32_t K,

@@ -33,6 +33,7 @@ def bf16_round(x: np.ndarray) -> np.ndarray:
     return b.astype(np.uint32).view(np.float32)
 
 
+# (CTA pairs, which need a far larger product, are held to the single-CTA bits by a test below.)
 # The last three are shard-sized: too few 128 x 256 tiles for every SM, so the persistent kernel
 # takes them on 128-wide tiles (or on one wide tile per CTA), ragged edges included.
 SHAPES = [(64, 16, 64), (128, 128, 64), (256, 384, 512), (200, 132, 72), (512, 768, 768),
@@ -108,6 +109,29 @@ def test_tensor_core_gemm_matches_oracle_on_identical_operands(shape):
         scaled = np.abs(got - want) / (1.0 + mags[mag_of[name]])
         assert np.isfinite(got).all(), name
         assert scaled.max() < 2e-6, f"{name}: scaled error {scaled.max():.3g}"
+
+
+def test_cta_pair_tiles_give_the_single_cta_bits():
+    """A product large enough for CTA pairs (two SMs per 256 x 256 tile) computes the same products in the
+    same order as one CTA per 128 x 256 tile: identical bits, ragged edges in both directions included."""
+    M, N, K = 10300, 1028, 1600
+    rng = np.random.default_rng(99)
+    variants, dims, outs, arena, ro, _mags, _mag_of = build_case(rng, M, N, K)
+    prog = [P.Instr(op, fl | REL, 0, ins, dims) for (_n, op, fl, ins) in variants]
+    images = []
+    for pairs in (True, False):
+        img = arena.copy()
+        be = B.CudaBackend(0)
+        be.set_cta_pairs(pairs)
+        be.bind(img, ro)
+        be.run(prog)
+        c = be.counters()
+        be.set_cta_pairs(True)
+        be.close()
+        assert c.relaxed_executions == len(variants)
+        images.append(img)
+    for (name, _op, _fl, _ins), off in zip(variants, outs):
+        assert np.array_equal(images[0][off:off + 4 * M * N], images[1][off:off + 4 * M * N]), name
 
 
 def test_relaxed_rounding_stays_within_plan_tolerance():
