@@ -22,7 +22,7 @@ const char* OpName(uint16_t op) {
 
 namespace {
 
-bool MulOk(uint64_t a, uint64_t b, uint64_t* out) {
+bool ProductFits(uint64_t a, uint64_t b, uint64_t* out) {
   return !__builtin_mul_overflow(a, b, out);
 }
 
@@ -36,7 +36,7 @@ struct Builder {
   void Add(uint64_t ref, uint64_t count, bool write, bool read, uint64_t elem = 4) {
     if (!ok) return;
     uint64_t bytes = 0;
-    if (ref == kNullRef || !MulOk(count, elem, &bytes)) { ok = false; return; }
+    if (ref == kNullRef || !ProductFits(count, elem, &bytes)) { ok = false; return; }
     const Space sp = RefSpace(ref);
     const uint64_t off = RefOffset(ref);
     if (write && sp != kArena) { ok = false; return; }
@@ -64,16 +64,16 @@ std::string DescribeInstruction(const Instruction& ins, uint64_t arena_bytes,
   if (ins.opcode >= kOpCount) return "unknown opcode " + std::to_string(ins.opcode);
   if (ins.flags & ~kKnownFlags) return std::string(OpName(ins.opcode)) + ": unknown flag bits";
   Builder b{ins, {arena_bytes, rodata_bytes, source_bytes}, out};
-  const uint64_t d0 = ins.out[0], d1 = ins.out[1], d2 = ins.out[2];
-  uint64_t mk = 0, kn = 0, mn = 0, nc = 0;
+  const uint64_t dim_a = ins.out[0], dim_b = ins.out[1], dim_c = ins.out[2];
+  uint64_t a_elems = 0, b_elems = 0, c_elems = 0, row_elems = 0;
   auto fail = [&](const char* why = "operand out of bounds or malformed dims") {
     return std::string(OpName(ins.opcode)) + ": " + why;
   };
   auto attn = [&](uint64_t B, uint64_t S, uint64_t H, uint64_t d, uint64_t* td, uint64_t* pn) {
     uint64_t bs = 0, hd = 0, bhs = 0;
     if (B == 0 || S == 0 || H == 0 || d == 0) return false;
-    return MulOk(B, S, &bs) && MulOk(H, d, &hd) && MulOk(bs, hd, td) &&
-           MulOk(bs, H, &bhs) && MulOk(bhs, S, pn);
+    return ProductFits(B, S, &bs) && ProductFits(H, d, &hd) && ProductFits(bs, hd, td) &&
+           ProductFits(bs, H, &bhs) && ProductFits(bhs, S, pn);
   };
 
   switch (static_cast<Op>(ins.opcode)) {
@@ -83,27 +83,27 @@ std::string DescribeInstruction(const Instruction& ins, uint64_t arena_bytes,
     case kGemmNNQ8: case kGemmNTQ8: case kGemmNNBF16: case kGemmNTBF16: {
       const bool q8 = ins.opcode == kGemmNNQ8 || ins.opcode == kGemmNTQ8;
       const bool bf = ins.opcode == kGemmNNBF16 || ins.opcode == kGemmNTBF16;
-      if (!MulOk(d0, d2, &mk) || !MulOk(d2, d1, &kn) || !MulOk(d0, d1, &mn)) return fail();
+      if (!ProductFits(dim_a, dim_c, &a_elems) || !ProductFits(dim_c, dim_b, &b_elems) || !ProductFits(dim_a, dim_b, &c_elems)) return fail();
       if ((q8 || bf) && RefSpace(ins.in[1]) != kRodata) return fail("narrow weight outside rodata");
-      b.R(ins.in[0], mk);
-      b.R(ins.in[1], kn, q8 ? 1 : bf ? 2 : 4);
-      if (ins.opcode == kGemmAccNN) b.RW(ins.in[2], mn); else b.W(ins.in[2], mn);
+      b.R(ins.in[0], a_elems);
+      b.R(ins.in[1], b_elems, q8 ? 1 : bf ? 2 : 4);
+      if (ins.opcode == kGemmAccNN) b.RW(ins.in[2], c_elems); else b.W(ins.in[2], c_elems);
       const bool f32w = ins.opcode == kGemmNN || ins.opcode == kGemmNT || ins.opcode == kGemmTN;
       if (ins.flags & kFlagEpilogueBias) {
         if (ins.opcode != kGemmNN && ins.opcode != kGemmNNBF16) return fail("bias flag on this opcode");
         if (ins.flags & kFlagGemmAddend) return fail("bias and addend share in[3]");
-        b.R(ins.in[3], d1);
+        b.R(ins.in[3], dim_b);
       }
       if ((ins.flags & kFlagActMask) && ins.opcode != kGemmNN && ins.opcode != kGemmNNBF16 &&
           ins.opcode != kGemmNNQ8)
         return fail("activation flag on this opcode");
       if (ins.flags & kFlagGemmAddend) {
         if (!f32w) return fail("addend flag on this opcode");
-        b.R(ins.in[3], mn);
+        b.R(ins.in[3], c_elems);
       }
       if (ins.flags & kFlagQ8ColScale) {
         if (!q8 || RefSpace(ins.in[3]) != kRodata) return fail("column scales");
-        b.R(ins.in[3], ins.opcode == kGemmNTQ8 ? d2 : d1);
+        b.R(ins.in[3], ins.opcode == kGemmNTQ8 ? dim_c : dim_b);
       } else if (q8) {
         const float s = BitsToF32(ins.in[3]);
         if ((ins.in[3] >> 32) != 0 || !std::isfinite(s) || !(s > 0.0f))
@@ -114,113 +114,113 @@ std::string DescribeInstruction(const Instruction& ins, uint64_t arena_bytes,
       break;
     }
     case kAddEW: case kMulEW: case kReluBwd: case kGeluBwd: case kSiluBwd:
-      b.R(ins.in[0], d0); b.R(ins.in[1], d0); b.W(ins.in[2], d0);
+      b.R(ins.in[0], dim_a); b.R(ins.in[1], dim_a); b.W(ins.in[2], dim_a);
       break;
     case kAddBias:
-      if (!MulOk(d0, d1, &mn)) return fail();
-      b.R(ins.in[0], mn); b.R(ins.in[1], d1); b.W(ins.in[2], mn);
+      if (!ProductFits(dim_a, dim_b, &c_elems)) return fail();
+      b.R(ins.in[0], c_elems); b.R(ins.in[1], dim_b); b.W(ins.in[2], c_elems);
       break;
     case kReluFwd: case kGeluFwd: case kSiluFwd: case kCopy:
-      b.R(ins.in[0], d0); b.W(ins.in[1], d0);
+      b.R(ins.in[0], dim_a); b.W(ins.in[1], dim_a);
       break;
     case kScale:
       if (!FiniteImm(ins.in[2])) return fail("scale immediate");
-      b.R(ins.in[0], d0); b.W(ins.in[1], d0);
+      b.R(ins.in[0], dim_a); b.W(ins.in[1], dim_a);
       break;
     case kLayerNormFwd: {
-      const uint64_t rows = Hi32(d0), cols = Lo32(d0);
-      if (!MulOk(rows, cols, &nc) || cols == 0) return fail();
-      b.R(ins.in[0], nc); b.R(ins.in[1], cols); b.R(ins.in[2], cols); b.W(ins.in[3], nc);
+      const uint64_t rows = Hi32(dim_a), cols = Lo32(dim_a);
+      if (!ProductFits(rows, cols, &row_elems) || cols == 0) return fail();
+      b.R(ins.in[0], row_elems); b.R(ins.in[1], cols); b.R(ins.in[2], cols); b.W(ins.in[3], row_elems);
       b.W(ins.out[1], rows); b.W(ins.out[2], rows);
       break;
     }
     case kLayerNormBwd: {
-      const uint64_t rows = Hi32(d2), cols = Lo32(d2);
-      if (!MulOk(rows, cols, &nc) || cols == 0) return fail();
-      b.R(ins.in[0], nc); b.R(ins.in[1], nc); b.R(ins.in[2], cols); b.W(ins.in[3], nc);
+      const uint64_t rows = Hi32(dim_c), cols = Lo32(dim_c);
+      if (!ProductFits(rows, cols, &row_elems) || cols == 0) return fail();
+      b.R(ins.in[0], row_elems); b.R(ins.in[1], row_elems); b.R(ins.in[2], cols); b.W(ins.in[3], row_elems);
       b.R(ins.out[0], rows); b.R(ins.out[1], rows);
       break;
     }
     case kRmsNormFwd: {
-      const uint64_t rows = Hi32(d0), cols = Lo32(d0);
-      if (!MulOk(rows, cols, &nc) || cols == 0) return fail();
-      b.R(ins.in[0], nc); b.R(ins.in[1], cols); b.W(ins.in[2], nc); b.W(ins.in[3], rows);
+      const uint64_t rows = Hi32(dim_a), cols = Lo32(dim_a);
+      if (!ProductFits(rows, cols, &row_elems) || cols == 0) return fail();
+      b.R(ins.in[0], row_elems); b.R(ins.in[1], cols); b.W(ins.in[2], row_elems); b.W(ins.in[3], rows);
       break;
     }
     case kRmsNormBwd: {
-      const uint64_t rows = Hi32(d1), cols = Lo32(d1);
-      if (!MulOk(rows, cols, &nc) || cols == 0) return fail();
-      b.R(ins.in[0], nc); b.R(ins.in[1], nc); b.R(ins.in[2], cols); b.W(ins.in[3], nc);
+      const uint64_t rows = Hi32(dim_b), cols = Lo32(dim_b);
+      if (!ProductFits(rows, cols, &row_elems) || cols == 0) return fail();
+      b.R(ins.in[0], row_elems); b.R(ins.in[1], row_elems); b.R(ins.in[2], cols); b.W(ins.in[3], row_elems);
       b.R(ins.out[0], rows);
       break;
     }
     case kClipNorm:
       if (!FiniteImm(ins.in[1])) return fail("clip threshold");
-      b.RW(ins.in[0], d0);
+      b.RW(ins.in[0], dim_a);
       break;
     case kSqNormAccum:
-      b.R(ins.in[0], d0); b.RW(ins.in[1], 1);
+      b.R(ins.in[0], dim_a); b.RW(ins.in[1], 1);
       break;
     case kClipGlobal:
       if (!FiniteImm(ins.in[2])) return fail("clip threshold");
-      b.RW(ins.in[0], d0); b.R(ins.in[1], 1);
+      b.RW(ins.in[0], dim_a); b.R(ins.in[1], 1);
       break;
     case kReduceRows:
-      if (!MulOk(d0, d1, &mn)) return fail();
-      b.R(ins.in[0], mn); b.W(ins.in[1], d1);
+      if (!ProductFits(dim_a, dim_b, &c_elems)) return fail();
+      b.R(ins.in[0], c_elems); b.W(ins.in[1], dim_b);
       break;
     case kSoftmaxXEntFwd: case kSoftmaxXEntMaskedFwd:
-      if (!MulOk(d0, d1, &nc) || d0 == 0 || d1 == 0) return fail();
-      b.R(ins.in[0], nc); b.R(ins.in[1], d0); b.W(ins.in[2], 1); b.W(ins.in[3], nc);
+      if (!ProductFits(dim_a, dim_b, &row_elems) || dim_a == 0 || dim_b == 0) return fail();
+      b.R(ins.in[0], row_elems); b.R(ins.in[1], dim_a); b.W(ins.in[2], 1); b.W(ins.in[3], row_elems);
       break;
     case kSoftmaxXEntBwd: case kSoftmaxXEntMaskedBwd:
-      if (!MulOk(d0, d1, &nc) || d0 == 0 || d1 == 0) return fail();
-      b.R(ins.in[0], nc); b.R(ins.in[1], d0); b.R(ins.in[2], 1); b.W(ins.in[3], nc);
+      if (!ProductFits(dim_a, dim_b, &row_elems) || dim_a == 0 || dim_b == 0) return fail();
+      b.R(ins.in[0], row_elems); b.R(ins.in[1], dim_a); b.R(ins.in[2], 1); b.W(ins.in[3], row_elems);
       break;
     case kMseFwd:
-      b.R(ins.in[0], d0); b.R(ins.in[1], d0); b.W(ins.in[2], 1);
+      b.R(ins.in[0], dim_a); b.R(ins.in[1], dim_a); b.W(ins.in[2], 1);
       break;
     case kMseBwd:
-      b.R(ins.in[0], d0); b.R(ins.in[1], d0); b.R(ins.in[2], 1); b.W(ins.in[3], d0);
+      b.R(ins.in[0], dim_a); b.R(ins.in[1], dim_a); b.R(ins.in[2], 1); b.W(ins.in[3], dim_a);
       break;
     case kKLDistillFwd:
-      if (!MulOk(Hi32(d1), Lo32(d1), &nc) || nc == 0) return fail();
-      b.R(ins.in[0], nc); b.R(ins.in[1], nc); b.W(ins.in[2], 1); b.W(ins.in[3], nc);
-      b.W(ins.out[0], nc);
+      if (!ProductFits(Hi32(dim_b), Lo32(dim_b), &row_elems) || row_elems == 0) return fail();
+      b.R(ins.in[0], row_elems); b.R(ins.in[1], row_elems); b.W(ins.in[2], 1); b.W(ins.in[3], row_elems);
+      b.W(ins.out[0], row_elems);
       break;
     case kKLDistillBwd:
-      if (!MulOk(Hi32(d0), Lo32(d0), &nc) || nc == 0) return fail();
-      b.R(ins.in[0], nc); b.R(ins.in[1], nc); b.R(ins.in[2], 1); b.W(ins.in[3], nc);
+      if (!ProductFits(Hi32(dim_a), Lo32(dim_a), &row_elems) || row_elems == 0) return fail();
+      b.R(ins.in[0], row_elems); b.R(ins.in[1], row_elems); b.R(ins.in[2], 1); b.W(ins.in[3], row_elems);
       break;
     case kSgdStep:
-      if (!FiniteImm(d1)) return fail("clip word");
-      b.RW(ins.in[0], d0); b.R(ins.in[1], d0);
+      if (!FiniteImm(dim_b)) return fail("clip word");
+      b.RW(ins.in[0], dim_a); b.R(ins.in[1], dim_a);
       break;
     case kAccumulate:
-      b.RW(ins.in[0], d0); b.R(ins.in[1], d0);
+      b.RW(ins.in[0], dim_a); b.R(ins.in[1], dim_a);
       break;
     case kAdamWStep:
-      if (!FiniteImm(d1)) return fail("clip word");
-      b.RW(ins.in[0], d0); b.R(ins.in[1], d0); b.RW(ins.in[2], d0); b.RW(ins.in[3], d0);
+      if (!FiniteImm(dim_b)) return fail("clip word");
+      b.RW(ins.in[0], dim_a); b.R(ins.in[1], dim_a); b.RW(ins.in[2], dim_a); b.RW(ins.in[3], dim_a);
       break;
     case kFill:
-      b.W(ins.in[0], d0);
+      b.W(ins.in[0], dim_a);
       break;
     case kRopeFwd: case kRopeBwd: {
       uint64_t td = 0, pn = 0;
-      if (!attn(Hi32(d0), Lo32(d0), Hi32(d1), Lo32(d1), &td, &pn) || Lo32(d1) % 2) return fail();
-      const float base = BitsToF32(d2);
-      if ((d2 >> 32) != 0 || !std::isfinite(base) || !(base > 1.0f)) return fail("rope base");
+      if (!attn(Hi32(dim_a), Lo32(dim_a), Hi32(dim_b), Lo32(dim_b), &td, &pn) || Lo32(dim_b) % 2) return fail();
+      const float base = BitsToF32(dim_c);
+      if ((dim_c >> 32) != 0 || !std::isfinite(base) || !(base > 1.0f)) return fail("rope base");
       b.R(ins.in[0], td); b.W(ins.in[1], td);
-      if (ins.in[2] != kNullRef) b.R(ins.in[2], Lo32(d0) * Lo32(d1));
+      if (ins.in[2] != kNullRef) b.R(ins.in[2], Lo32(dim_a) * Lo32(dim_b));
       break;
     }
     case kRopeTable: {
-      const uint64_t S = Hi32(d0), d = Lo32(d0);
-      const float base = BitsToF32(d1);
+      const uint64_t S = Hi32(dim_a), d = Lo32(dim_a);
+      const float base = BitsToF32(dim_b);
       uint64_t table = 0;
-      if (S == 0 || d == 0 || d % 2 || (d1 >> 32) != 0 || !std::isfinite(base) ||
-          !(base > 1.0f) || !MulOk(S, d, &table))
+      if (S == 0 || d == 0 || d % 2 || (dim_b >> 32) != 0 || !std::isfinite(base) ||
+          !(base > 1.0f) || !ProductFits(S, d, &table))
         return fail();
       b.W(ins.in[0], table);
       break;
@@ -229,7 +229,7 @@ std::string DescribeInstruction(const Instruction& ins, uint64_t arena_bytes,
       bool uses[3] = {false, false, false};
       int stages = 0;
       for (; stages < 4; ++stages) {
-        const uint8_t st = static_cast<uint8_t>(d1 >> (8 * stages));
+        const uint8_t st = static_cast<uint8_t>(dim_b >> (8 * stages));
         const uint8_t kind = st & 0x0F, arg = (st >> 4) & 3;
         if (kind == kFEnd) break;
         if (kind > kFSilu) return fail("unknown fused stage");
@@ -241,69 +241,69 @@ std::string DescribeInstruction(const Instruction& ins, uint64_t arena_bytes,
         }
       }
       if (stages == 0) return fail("empty fused program");
-      b.R(ins.in[0], d0);
+      b.R(ins.in[0], dim_a);
       for (int s = 1; s <= 2; ++s) {
-        if (uses[s]) b.R(ins.in[s], d0);
+        if (uses[s]) b.R(ins.in[s], dim_a);
         else if (ins.in[s] != kNullRef) return fail("unused fused operand present");
       }
-      b.W(ins.in[3], d0);
+      b.W(ins.in[3], dim_a);
       break;
     }
     case kAttnFwd: {
       uint64_t td = 0, pn = 0;
-      if (!attn(Hi32(d1), Lo32(d1), Hi32(d2), Lo32(d2), &td, &pn)) return fail();
+      if (!attn(Hi32(dim_b), Lo32(dim_b), Hi32(dim_c), Lo32(dim_c), &td, &pn)) return fail();
       b.R(ins.in[0], td); b.R(ins.in[1], td); b.R(ins.in[2], td); b.W(ins.in[3], td);
       b.W(ins.out[0], pn);
       break;
     }
     case kSegmentStarts: {
       uint64_t t = 0;
-      if (Hi32(d0) == 0 || Lo32(d0) == 0 || !MulOk(Hi32(d0), Lo32(d0), &t) || d1 > 0x7FFFFFFFu)
+      if (Hi32(dim_a) == 0 || Lo32(dim_a) == 0 || !ProductFits(Hi32(dim_a), Lo32(dim_a), &t) || dim_b > 0x7FFFFFFFu)
         return fail();
       b.R(ins.in[0], t); b.W(ins.in[1], t);
       break;
     }
     case kAttnFwdSeg: {
-      const AttnGeom g = UnpackAttnGeom(d1);
+      const AttnGeom g = UnpackAttnGeom(dim_b);
       uint64_t td = 0, pn = 0;
       if (!attn(g.B, g.S, g.H, g.d, &td, &pn)) return fail();
       b.R(ins.in[0], td); b.R(ins.in[1], td); b.R(ins.in[2], td); b.W(ins.in[3], td);
-      b.W(ins.out[0], pn); b.R(d2, g.B * g.S);
+      b.W(ins.out[0], pn); b.R(dim_c, g.B * g.S);
       break;
     }
     case kAttnDP: {
       uint64_t td = 0, pn = 0;
-      if (!attn(Hi32(d0), Lo32(d0), Hi32(d1), Lo32(d1), &td, &pn)) return fail();
+      if (!attn(Hi32(dim_a), Lo32(dim_a), Hi32(dim_b), Lo32(dim_b), &td, &pn)) return fail();
       b.R(ins.in[0], td); b.R(ins.in[1], td); b.W(ins.in[2], pn);
       break;
     }
     case kAttnDV: case kAttnDQ: case kAttnDK: {
       uint64_t td = 0, pn = 0;
-      if (!attn(Hi32(d0), Lo32(d0), Hi32(d1), Lo32(d1), &td, &pn)) return fail();
+      if (!attn(Hi32(dim_a), Lo32(dim_a), Hi32(dim_b), Lo32(dim_b), &td, &pn)) return fail();
       b.R(ins.in[0], pn); b.R(ins.in[1], td); b.W(ins.in[2], td);
       break;
     }
     case kSoftmaxRowsBwd:
-      if (!MulOk(Hi32(d0), Lo32(d0), &nc) || Lo32(d0) == 0) return fail();
-      b.R(ins.in[0], nc); b.R(ins.in[1], nc); b.W(ins.in[2], nc);
+      if (!ProductFits(Hi32(dim_a), Lo32(dim_a), &row_elems) || Lo32(dim_a) == 0) return fail();
+      b.R(ins.in[0], row_elems); b.R(ins.in[1], row_elems); b.W(ins.in[2], row_elems);
       break;
     case kAttnFwdTiled: {
       uint64_t td = 0, pn = 0;
-      if (!attn(Hi32(d1), Lo32(d1), Hi32(d2), Lo32(d2), &td, &pn)) return fail();
+      if (!attn(Hi32(dim_b), Lo32(dim_b), Hi32(dim_c), Lo32(dim_c), &td, &pn)) return fail();
       b.R(ins.in[0], td); b.R(ins.in[1], td); b.R(ins.in[2], td); b.W(ins.in[3], td);
-      b.W(ins.out[0], Hi32(d1) * Lo32(d1) * Hi32(d2) * kAttnStatsWidth);
+      b.W(ins.out[0], Hi32(dim_b) * Lo32(dim_b) * Hi32(dim_c) * kAttnStatsWidth);
       break;
     }
     case kAttnFwdTiledSeg: {
-      const AttnGeom g = UnpackAttnGeom(d1);
+      const AttnGeom g = UnpackAttnGeom(dim_b);
       uint64_t td = 0, pn = 0;
       if (!attn(g.B, g.S, g.H, g.d, &td, &pn)) return fail();
       b.R(ins.in[0], td); b.R(ins.in[1], td); b.R(ins.in[2], td); b.W(ins.in[3], td);
-      b.W(ins.out[0], g.B * g.S * g.H * kAttnStatsWidth); b.R(d2, g.B * g.S);
+      b.W(ins.out[0], g.B * g.S * g.H * kAttnStatsWidth); b.R(dim_c, g.B * g.S);
       break;
     }
     case kAttnDQTiled: case kAttnDKTiled: case kAttnDVTiled: {
-      const AttnGeom g = UnpackAttnGeom(d2);
+      const AttnGeom g = UnpackAttnGeom(dim_c);
       uint64_t td = 0, pn = 0;
       if (!attn(g.B, g.S, g.H, g.d, &td, &pn)) return fail();
       b.R(ins.in[0], td); b.R(ins.in[1], td); b.R(ins.in[2], td); b.R(ins.in[3], td);
@@ -313,11 +313,11 @@ std::string DescribeInstruction(const Instruction& ins, uint64_t arena_bytes,
       break;
     }
     case kEmbedFwd: {
-      const uint64_t vocab = Hi32(d1), dim = Lo32(d1);
+      const uint64_t vocab = Hi32(dim_b), dim = Lo32(dim_b);
       uint64_t vd = 0, td = 0;
-      if (!MulOk(vocab, dim, &vd) || !MulOk(d0, dim, &td) || dim == 0) return fail();
+      if (!ProductFits(vocab, dim, &vd) || !ProductFits(dim_a, dim, &td) || dim == 0) return fail();
       if (RefSpace(ins.in[1]) == kArena) return fail("embedding table in the arena");
-      b.R(ins.in[0], d0); b.R(ins.in[1], vd); b.W(ins.in[2], td);
+      b.R(ins.in[0], dim_a); b.R(ins.in[1], vd); b.W(ins.in[2], td);
       break;
     }
     case kOpCount:

@@ -33,21 +33,21 @@ __global__ void LayerNormFwdKernel(const float* __restrict__ x, const float* __r
   double sum = 0.0;
   for (size_t c = lane; c < cols; c += 32) sum += static_cast<double>(xr[c]);
   sum = WarpSum(sum);
-  const float mu = static_cast<float>(sum / static_cast<double>(cols));
+  const float row_mean = static_cast<float>(sum / static_cast<double>(cols));
   double var = 0.0;
   for (size_t c = lane; c < cols; c += 32) {
-    const double d = static_cast<double>(xr[c]) - static_cast<double>(mu);
+    const double d = static_cast<double>(xr[c]) - static_cast<double>(row_mean);
     var += d * d;
   }
   var = WarpSum(var);
-  const float rs = 1.0f / sqrtf(static_cast<float>(var / static_cast<double>(cols)) + eps);
+  const float inv_sigma = 1.0f / sqrtf(static_cast<float>(var / static_cast<double>(cols)) + eps);
   if (lane == 0) {
-    mean[r] = mu;
-    rstd[r] = rs;
+    mean[r] = row_mean;
+    rstd[r] = inv_sigma;
   }
   float* yr = y + r * cols;
   for (size_t c = lane; c < cols; c += 32) {
-    const float v = (xr[c] - mu) * rs * gamma[c] + beta[c];
+    const float v = (xr[c] - row_mean) * inv_sigma * gamma[c] + beta[c];
     yr[c] = v;
     if (sh.dst)   // the bf16 copy for the GEMM that reads y next
       sh.dst[r * cols + c] = static_cast<uint16_t>(ShadowBf16(sh.k_scale ? v * sh.k_scale[c] : v));
@@ -61,26 +61,26 @@ __global__ void LayerNormBwdKernel(const float* __restrict__ dy, const float* __
   const size_t r = blockIdx.x * static_cast<size_t>(kWarpsPerBlock) + threadIdx.x / 32;
   const int lane = threadIdx.x & 31;
   if (r >= rows) return;
-  const float inv_d = 1.0f / static_cast<float>(cols);
+  const float per_col = 1.0f / static_cast<float>(cols);
   const float* dyr = dy + r * cols;
   const float* xr = x + r * cols;
   float* dxr = dx + r * cols;
-  const float mu = mean[r], rs = rstd[r];
-  double sum_g = 0.0, sum_gx = 0.0;
+  const float row_mean = mean[r], inv_sigma = rstd[r];
+  double acc_g = 0.0, acc_gu = 0.0;
   for (size_t c = lane; c < cols; c += 32) {
-    const float xhat = (xr[c] - mu) * rs;
+    const float unit = (xr[c] - row_mean) * inv_sigma;
     const float g = dyr[c] * gamma[c];
-    sum_g += static_cast<double>(g);
-    sum_gx += static_cast<double>(g) * static_cast<double>(xhat);
+    acc_g += static_cast<double>(g);
+    acc_gu += static_cast<double>(g) * static_cast<double>(unit);
   }
-  sum_g = WarpSum(sum_g);
-  sum_gx = WarpSum(sum_gx);
-  const float mg = static_cast<float>(sum_g) * inv_d;
-  const float mgx = static_cast<float>(sum_gx) * inv_d;
+  acc_g = WarpSum(acc_g);
+  acc_gu = WarpSum(acc_gu);
+  const float avg_g = static_cast<float>(acc_g) * per_col;
+  const float avg_gu = static_cast<float>(acc_gu) * per_col;
   for (size_t c = lane; c < cols; c += 32) {
-    const float xhat = (xr[c] - mu) * rs;
+    const float unit = (xr[c] - row_mean) * inv_sigma;
     const float g = dyr[c] * gamma[c];
-    dxr[c] = rs * (g - mg - xhat * mgx);
+    dxr[c] = inv_sigma * (g - avg_g - unit * avg_gu);
   }
 }
 
@@ -110,22 +110,22 @@ LayerNormFwdVecKernel(const float* __restrict__ x, const float* __restrict__ gam
     sum += static_cast<double>(xv[i].w);
   }
   sum = WarpSum(sum);
-  const float mu = static_cast<float>(sum / static_cast<double>(cols));
+  const float row_mean = static_cast<float>(sum / static_cast<double>(cols));
   double var = 0.0;
 #pragma unroll
   for (int i = 0; i < V; ++i) {
     const float e[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const double d = static_cast<double>(e[j]) - static_cast<double>(mu);
+      const double d = static_cast<double>(e[j]) - static_cast<double>(row_mean);
       var += d * d;
     }
   }
   var = WarpSum(var);
-  const float rs = 1.0f / sqrtf(static_cast<float>(var / static_cast<double>(cols)) + eps);
+  const float inv_sigma = 1.0f / sqrtf(static_cast<float>(var / static_cast<double>(cols)) + eps);
   if (lane == 0) {
-    mean[r] = mu;
-    rstd[r] = rs;
+    mean[r] = row_mean;
+    rstd[r] = inv_sigma;
   }
   float4* yr = reinterpret_cast<float4*>(y + r * cols);
 #pragma unroll
@@ -134,10 +134,10 @@ LayerNormFwdVecKernel(const float* __restrict__ x, const float* __restrict__ gam
     const float4 g = __ldg(reinterpret_cast<const float4*>(gamma) + c4);
     const float4 b = __ldg(reinterpret_cast<const float4*>(beta) + c4);
     float4 v;
-    v.x = (xv[i].x - mu) * rs * g.x + b.x;
-    v.y = (xv[i].y - mu) * rs * g.y + b.y;
-    v.z = (xv[i].z - mu) * rs * g.z + b.z;
-    v.w = (xv[i].w - mu) * rs * g.w + b.w;
+    v.x = (xv[i].x - row_mean) * inv_sigma * g.x + b.x;
+    v.y = (xv[i].y - row_mean) * inv_sigma * g.y + b.y;
+    v.z = (xv[i].z - row_mean) * inv_sigma * g.z + b.z;
+    v.w = (xv[i].w - row_mean) * inv_sigma * g.w + b.w;
     yr[c4] = v;
     if (sh.dst) ShadowStore4(sh, r * (cols / 4) + c4, static_cast<uint32_t>(c4 * 4), v);
   }
@@ -152,12 +152,12 @@ LayerNormBwdVecKernel(const float* __restrict__ dy, const float* __restrict__ x,
   const size_t r = blockIdx.x * static_cast<size_t>(kWarpsPerBlock) + threadIdx.x / 32;
   const int lane = threadIdx.x & 31;
   if (r >= rows) return;
-  const float inv_d = 1.0f / static_cast<float>(cols);
+  const float per_col = 1.0f / static_cast<float>(cols);
   const float4* dyr = reinterpret_cast<const float4*>(dy + r * cols);
   const float4* xr = reinterpret_cast<const float4*>(x + r * cols);
-  const float mu = mean[r], rs = rstd[r];
-  float xhat[V][4], g[V][4];
-  double sum_g = 0.0, sum_gx = 0.0;
+  const float row_mean = mean[r], inv_sigma = rstd[r];
+  float unit[V][4], g[V][4];
+  double acc_g = 0.0, acc_gu = 0.0;
 #pragma unroll
   for (int i = 0; i < V; ++i) {
     const int c4 = lane + 32 * i;
@@ -167,22 +167,22 @@ LayerNormBwdVecKernel(const float* __restrict__ dy, const float* __restrict__ x,
                 ge[4] = {gm.x, gm.y, gm.z, gm.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      xhat[i][j] = (xe[j] - mu) * rs;
+      unit[i][j] = (xe[j] - row_mean) * inv_sigma;
       g[i][j] = de[j] * ge[j];
-      sum_g += static_cast<double>(g[i][j]);
-      sum_gx += static_cast<double>(g[i][j]) * static_cast<double>(xhat[i][j]);
+      acc_g += static_cast<double>(g[i][j]);
+      acc_gu += static_cast<double>(g[i][j]) * static_cast<double>(unit[i][j]);
     }
   }
-  sum_g = WarpSum(sum_g);
-  sum_gx = WarpSum(sum_gx);
-  const float mg = static_cast<float>(sum_g) * inv_d;
-  const float mgx = static_cast<float>(sum_gx) * inv_d;
+  acc_g = WarpSum(acc_g);
+  acc_gu = WarpSum(acc_gu);
+  const float avg_g = static_cast<float>(acc_g) * per_col;
+  const float avg_gu = static_cast<float>(acc_gu) * per_col;
   float4* dxr = reinterpret_cast<float4*>(dx + r * cols);
   const float4* adr = addend ? reinterpret_cast<const float4*>(addend + r * cols) : nullptr;
 #pragma unroll
   for (int i = 0; i < V; ++i) {
-    float4 v = make_float4(rs * (g[i][0] - mg - xhat[i][0] * mgx), rs * (g[i][1] - mg - xhat[i][1] * mgx),
-                           rs * (g[i][2] - mg - xhat[i][2] * mgx), rs * (g[i][3] - mg - xhat[i][3] * mgx));
+    float4 v = make_float4(inv_sigma * (g[i][0] - avg_g - unit[i][0] * avg_gu), inv_sigma * (g[i][1] - avg_g - unit[i][1] * avg_gu),
+                           inv_sigma * (g[i][2] - avg_g - unit[i][2] * avg_gu), inv_sigma * (g[i][3] - avg_g - unit[i][3] * avg_gu));
     if (adr) {   // an absorbed kAddEW: the sum it would have written (dx may alias the addend)
       const float4 a = adr[lane + 32 * i];
       v = make_float4(a.x + v.x, a.y + v.y, a.z + v.z, a.w + v.w);
@@ -205,10 +205,10 @@ __global__ void RmsNormFwdKernel(const float* __restrict__ x, const float* __res
   for (size_t c = lane; c < cols; c += 32)
     ss += static_cast<double>(xr[c]) * static_cast<double>(xr[c]);
   ss = WarpSum(ss);
-  const float rs = 1.0f / sqrtf(static_cast<float>(ss / static_cast<double>(cols)) + eps);
-  if (lane == 0) rstd[r] = rs;
+  const float inv_sigma = 1.0f / sqrtf(static_cast<float>(ss / static_cast<double>(cols)) + eps);
+  if (lane == 0) rstd[r] = inv_sigma;
   float* yr = y + r * cols;
-  for (size_t c = lane; c < cols; c += 32) yr[c] = xr[c] * rs * gamma[c];
+  for (size_t c = lane; c < cols; c += 32) yr[c] = xr[c] * inv_sigma * gamma[c];
 }
 
 __global__ void RmsNormBwdKernel(const float* __restrict__ dy, const float* __restrict__ x,
@@ -217,18 +217,18 @@ __global__ void RmsNormBwdKernel(const float* __restrict__ dy, const float* __re
   const size_t r = blockIdx.x * static_cast<size_t>(kWarpsPerBlock) + threadIdx.x / 32;
   const int lane = threadIdx.x & 31;
   if (r >= rows) return;
-  const float inv_d = 1.0f / static_cast<float>(cols);
+  const float per_col = 1.0f / static_cast<float>(cols);
   const float* dyr = dy + r * cols;
   const float* xr = x + r * cols;
   float* dxr = dx + r * cols;
-  const float rs = rstd[r];
-  double sum_gx = 0.0;
+  const float inv_sigma = rstd[r];
+  double acc_gu = 0.0;
   for (size_t c = lane; c < cols; c += 32)
-    sum_gx += static_cast<double>(dyr[c] * gamma[c]) * static_cast<double>(xr[c]);
-  sum_gx = WarpSum(sum_gx);
-  const float mgx = static_cast<float>(sum_gx) * inv_d;
+    acc_gu += static_cast<double>(dyr[c] * gamma[c]) * static_cast<double>(xr[c]);
+  acc_gu = WarpSum(acc_gu);
+  const float avg_gu = static_cast<float>(acc_gu) * per_col;
   for (size_t c = lane; c < cols; c += 32)
-    dxr[c] = rs * (dyr[c] * gamma[c] - xr[c] * rs * rs * mgx);
+    dxr[c] = inv_sigma * (dyr[c] * gamma[c] - xr[c] * inv_sigma * inv_sigma * avg_gu);
 }
 
 inline unsigned RowBlocks(size_t rows) {
