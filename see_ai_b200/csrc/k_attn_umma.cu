@@ -217,14 +217,21 @@ __device__ __forceinline__ void DrainDelay() {
 constexpr uint32_t TmemColsFor(uint32_t need) { return need <= 128 ? 128 : (need <= 256 ? 256 : 512); }
 
 // ---- forward -------------------------------------------------------------------------
-// A CTA owns 128 query rows of one (sequence, head) and walks the keys 64 at a
-// time, twice: the first walk finds each row's score maximum, the second forms
-// p = exp(s - max), sums it, and accumulates the unnormalised O = p V on the
-// tensor core; O is divided by the sum on the way out.  Per step: S = Q K_h^T
-// (128 x 64, tensor memory columns 0..63), read back one row per thread, P
-// written to shared memory as bf16, O += P V_h (columns 64..64+D).  Small
-// footprint on purpose (48 KB of shared memory and 128 tensor-memory columns
-// for d = 64): four CTAs share an SM and cover each other's waits.
+// A CTA owns 128 query rows of one (sequence, head) and walks the keys ONCE, 64 at
+// a time.  Per step: S = Q K_h^T (128 x 64, tensor memory columns 0..63), read back
+// one row per thread; p = 2^(s c - ref) against a per-row reference exponent, P
+// written to shared memory as bf16, O += P V_h (columns 64..64+D) unnormalised.
+// The reference follows the running maximum lazily: it moves (and the row's O
+// and sum are multiplied by 2^(old - new), a read-modify-write of the row's
+// tensor-memory lane) only when a step's maximum exceeds it by more than 2^8, so
+// p stays below 256 — exact in f32 sums, the same relative rounding in bf16 —
+// and most steps rescale nothing.  The true maximum is tracked beside it and the
+// stats row gets {max, 1 / sum relative to that max}, what the backward kernels
+// and the exact family expect.  Small footprint on purpose (48 KB of shared
+// memory and 128 tensor-memory columns for d = 64): four CTAs share an SM and
+// cover each other's waits.
+constexpr float kRescaleSlack = 8.0f;   // log2 units
+
 template <int D>
 __global__ void __launch_bounds__(128)
 AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -244,8 +251,7 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const uint32_t it = n_qt - 1 - blockIdx.x;               // heaviest tiles first
   const uint32_t bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
   const uint32_t all_h = (a.S + kHalf - 1) / kHalf;
-  const uint32_t n_h = 2 * (it + 1) < all_h ? 2 * (it + 1) : all_h;
-  const uint32_t total = 2 * n_h;
+  const uint32_t total = 2 * (it + 1) < all_h ? 2 * (it + 1) : all_h;   // key steps up to the diagonal
 
   if (tid == 0) {
     MbarInit(&ctl->bar_a, 1); MbarInit(&ctl->bar_b, 1); MbarInit(&ctl->mma, 1);
@@ -262,23 +268,22 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   auto issue_a = [&](uint32_t t) {
     MbarExpectTx(&ctl->bar_a, kKBytes + (t == 0 ? kQBytes : 0));
     if (t == 0) LoadRows<D, 128>(q_s, &map_q, &ctl->bar_a, it * kTile, bh);
-    LoadRows<D, 64>(k_s, &map_k, &ctl->bar_a, (t % n_h) * kHalf, bh);
+    LoadRows<D, 64>(k_s, &map_k, &ctl->bar_a, t * kHalf, bh);
   };
-  auto issue_b = [&](uint32_t jh) {
+  auto issue_b = [&](uint32_t t) {
     MbarExpectTx(&ctl->bar_b, kVBytes);
-    LoadColsHalf(v_s, &map_vt, &ctl->bar_b, jh * kHalf, bh);
+    LoadColsHalf(v_s, &map_vt, &ctl->bar_b, t * kHalf, bh);
   };
 
   const uint32_t row = it * kTile + tid;                   // this thread's query row
   const float c1 = a.inv_sqrt_d * kLog2e;
-  float raw_max = -INFINITY, m = 0.0f, m2 = 0.0f, l = 0.0f;
-  uint32_t b_phase = 0;
+  float raw_max = -INFINITY;   // the row's true score maximum so far
+  float ref = -INFINITY;       // the exponent (log2 units) its p, sum and O are relative to
+  float l = 0.0f;
   int failed = 0;
   if (tid == 0) issue_a(0);
 
   for (uint32_t t = 0; t < total; ++t) {
-    const uint32_t jh = t % n_h;
-    const bool second = t >= n_h;
     if (tid == 0) {   // only the issuing thread needs the operands' arrival
       if (!MbarWait(&ctl->bar_a, t & 1)) failed = 1;
       TcFenceAfter();
@@ -286,53 +291,76 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       UmmaCommit(&ctl->mma);
     }
     // This commit also covers the previous step's O += P V, so p_s, v_s and k_s
-    // are all free again once it arrives.
+    // are all free again once it arrives, and O is at rest.
     if (!MbarWait(&ctl->mma, t & 1)) failed = 1;
     TcFenceAfter();
     if (tid == 0 && !failed) {
       if (t + 1 < total) issue_a(t + 1);
-      if (second) issue_b(jh);
+      issue_b(t);
     }
-    if (t == n_h) { m = raw_max * a.inv_sqrt_d; m2 = m * kLog2e; }
-    const uint32_t key0 = jh * kHalf;
+    const uint32_t key0 = t * kHalf;
     const bool diagonal = key0 + kHalf > it * kTile;   // some keys of this step lie above the diagonal
-#pragma unroll 1
-    for (uint32_t c0 = 0; c0 < kHalf; c0 += 32) {
-      uint32_t r[32];
-      TmemLoad32(t_s + c0, r);
+    uint32_t r[64];
+    {
+      uint32_t lo[32], hi[32];
+      TmemLoad32(t_s, lo);
+      TmemLoad32(t_s + 32, hi);
       TmemWaitLd();
-      if (!second) {
-        if (diagonal) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (key0 + c0 + j <= row) raw_max = fmaxf(raw_max, __uint_as_float(r[j]));
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) raw_max = fmaxf(raw_max, __uint_as_float(r[j]));
-        }
-      } else {
-        float v[32];
-        if (diagonal) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            v[j] = (key0 + c0 + j <= row) ? Exp2Approx(fmaf(__uint_as_float(r[j]), c1, -m2)) : 0.0f;
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = Exp2Approx(fmaf(__uint_as_float(r[j]), c1, -m2));
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) l += v[j];
-        StoreRowChunk(p_s, tid, c0, v);
-      }
+      for (int j = 0; j < 32; ++j) { r[j] = lo[j]; r[32 + j] = hi[j]; }
     }
-    if (second) FenceProxyAsync();
+    float step_max = -INFINITY;
+    if (diagonal) {
+#pragma unroll
+      for (int j = 0; j < 64; ++j)
+        if (key0 + j <= row) step_max = fmaxf(step_max, __uint_as_float(r[j]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 64; ++j) step_max = fmaxf(step_max, __uint_as_float(r[j]));
+    }
+    raw_max = fmaxf(raw_max, step_max);
+    const float step_ref = step_max * c1;
+    const bool moves = step_ref > ref + kRescaleSlack;   // always at a row's first live key (ref = -inf)
+    float alpha = 1.0f;
+    if (moves) {
+      alpha = Exp2Approx(ref - step_ref);                // 0 the first time
+      l *= alpha;
+      ref = step_ref;
+    }
+    if (t > 0 && __any_sync(0xFFFFFFFFu, moves)) {       // the warp's rows rescale their O lanes together
+#pragma unroll 1
+      for (uint32_t c0 = 0; c0 < D; c0 += 32) {
+        uint32_t o[32];
+        TmemLoad32(t_o + c0, o);
+        TmemWaitLd();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+        TmemStore32(t_o + c0, o);
+      }
+      TmemWaitSt();
+    }
+#pragma unroll
+    for (uint32_t c0 = 0; c0 < kHalf; c0 += 32) {
+      float v[32];
+      if (diagonal) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          v[j] = (key0 + c0 + j <= row) ? Exp2Approx(fmaf(__uint_as_float(r[c0 + j]), c1, -ref)) : 0.0f;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = Exp2Approx(fmaf(__uint_as_float(r[c0 + j]), c1, -ref));
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) l += v[j];
+      StoreRowChunk(p_s, tid, c0, v);
+    }
+    FenceProxyAsync();
     TcFenceBefore();
     if (__syncthreads_or(failed)) { failed = 1; break; }
-    if (second && tid == 0) {
-      if (!MbarWait(&ctl->bar_b, b_phase)) failed = 1;
-      b_phase ^= 1;
+    if (tid == 0) {
+      if (!MbarWait(&ctl->bar_b, t & 1)) failed = 1;
       TcFenceAfter();
-      if (!failed) MmaPT<D>(tmem + 64, p_s, v_s, jh != 0);
+      if (!failed) MmaPT<D>(tmem + 64, p_s, v_s, t != 0);
     }
   }
   if (tid == 0) UmmaCommit(&ctl->mma);
@@ -352,8 +380,11 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     StoreOutRows<D>(t_o, reinterpret_cast<float*>(smem) + warp * 32 * D, tid & 31, inv_l,
                     a.out + flat0, HD, rows_live, a.shadow, flat0, h * D);
     if (live) {
+      // The stats row speaks of the true maximum: the sum relative to it is l 2^(ref - max c).
+      const float m = raw_max * a.inv_sqrt_d;
+      const float inv_l_at_max = 1.0f / (l * Exp2Approx(ref - raw_max * c1));
       float* st = a.stats + (static_cast<size_t>(bh) * a.S + row) * kAttnStatsWidth;
-      *reinterpret_cast<float4*>(st) = make_float4(m, inv_l, 0.0f, 0.0f);
+      *reinterpret_cast<float4*>(st) = make_float4(m, inv_l_at_max, 0.0f, 0.0f);
     }
   }
   TcFenceBefore();
