@@ -102,6 +102,11 @@ int see_cuda_set_lora_fold(see_cuda_backend* h, int enabled);
  * arithmetic, bit for bit) in lazy coherence too; default 1: fused multiply-adds
  * there.  Strict coherence is always bit-exact. */
 int see_cuda_set_adapter_fma(see_cuda_backend* h, int enabled);
+/* Lazy coherence: the relaxed attention forward keeps a private bf16 copy of its output, and the dQ
+ * instruction of the same attention takes delta_i = sum_j P_ij dP_ij as dO_i . O_i from it and walks
+ * the keys once instead of twice.  Same quantity, another rounding (tolerance class, like every relaxed
+ * attention result).  Default on; 0 keeps the two-walk kernel. */
+int see_cuda_set_attention_one_walk(see_cuda_backend* h, int enabled);
 /* Exact f32 products (kGemmNN / kGemmNT / kGemmTN without the relaxed permission)
  * of at least 2^26 multiply-adds on the tensor cores: both operands cut into
  * three bf16 pieces, six piece products over a K axis six times as long, f32

@@ -22,6 +22,13 @@ struct AttnUmmaArgs {
   Shadow shadow;    // optional bf16 copy of `out` (cols = H*d) for the GEMM that reads it next
   float* out2 = nullptr;   // dK and dV in one walk: dV goes here (out is dK)
   Shadow shadow2;          // and its optional bf16 copy
+  // Forward: a second, private bf16 copy of O ([B*S, H*d]) kept for the dQ of the same
+  // attention (the arena's O is long overwritten by then — its slot usually holds dO).
+  uint16_t* keep = nullptr;
+  // dQ: that copy, and dO in f32.  delta_i = sum_j P_ij dP_ij equals dO_i . O_i, so the
+  // kernel takes it from one row of each and walks the keys once instead of twice.
+  const uint16_t* fwd_keep = nullptr;
+  const float* dout_f32 = nullptr;
 };
 
 // f32 [B*S, H*d] (heads interleaved along the row) -> bf16 per (sequence, head):

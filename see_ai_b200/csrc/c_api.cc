@@ -120,6 +120,11 @@ int see_cuda_set_lora_fold(see_cuda_backend* h, int enabled) {
   return SEE_OK;
 }
 
+int see_cuda_set_attention_one_walk(see_cuda_backend* h, int enabled) {
+  h->backend->SetAttentionOneWalk(enabled != 0);
+  return SEE_OK;
+}
+
 int see_cuda_set_adapter_fma(see_cuda_backend* h, int enabled) {
   h->backend->SetAdapterFma(enabled != 0);
   return SEE_OK;

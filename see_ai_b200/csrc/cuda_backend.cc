@@ -110,6 +110,7 @@ CudaBackend::~CudaBackend() {
   cudaFree(d_adam_table_);
   FreeLoraRanges();
   cudaFree(d_lora_t_);
+  for (uint16_t* p : attn_keep_pool_) cudaFree(p);
   cudaFree(d_lora_partials_);
   if (h_scalars_) cudaFreeHost(h_scalars_);
   if (h_status_) cudaFreeHost(h_status_);
@@ -415,6 +416,7 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
   umma::InvalidateRange(&umma_->ctx, 0, arena_bytes_);
   range_index_ = 0;
   PlanAdamGroups(program, begin, std::min(end, program.size()));
+  PlanAttentionKeeps(program, begin, std::min(end, program.size()));
   auto plan_fusions = [&] {
     PlanShadows(program, begin, std::min(end, program.size()));
     PlanBiasFusions(program, begin, std::min(end, program.size()));
@@ -799,6 +801,51 @@ static bool DeadFrom(std::span<const Instruction> program, const std::vector<Ext
   for (size_t j = ext_base; j < wrap_stop; ++j)
     if (const int r = step(j, false); r != 0) return r > 0;
   return true;   // reached the instruction that defines the range again
+}
+
+// Pairs each relaxed kAttnDQTiled of the range with the kAttnFwdTiled of the same
+// attention earlier in the range (same q, k, v and stats row) and gives the pair a
+// buffer for the forward's bf16 copy of O.  Buffers are allocated here, before any
+// capture; a failed allocation just leaves the pair on the two-walk kernel.
+void CudaBackend::PlanAttentionKeeps(std::span<const Instruction> program, size_t begin, size_t end) {
+  attn_keep_slot_.assign(end > begin ? end - begin : 0, -1);
+  if (coherence_ == Coherence::kStrict || !relaxed_allowed_ || !attn_one_walk_) return;
+  int slots = 0;
+  uint64_t elems = 0;
+  for (size_t i = begin; i < end && i < program.size(); ++i) {
+    const Instruction& dq = program[i];
+    if (dq.opcode != kAttnDQTiled || !(dq.flags & kFlagRelaxed)) continue;
+    const AttnGeom g = UnpackAttnGeom(dq.out[2]);
+    for (size_t j = i; j-- > begin;) {
+      const Instruction& fw = program[j];
+      if (fw.opcode != kAttnFwdTiled || fw.out[0] != dq.out[0]) continue;
+      if ((fw.flags & kFlagRelaxed) && fw.in[0] == dq.in[0] && fw.in[1] == dq.in[1] && fw.in[2] == dq.in[2] &&
+          Hi32(fw.out[1]) == g.B && Lo32(fw.out[1]) == g.S && Hi32(fw.out[2]) == g.H && Lo32(fw.out[2]) == g.d &&
+          attn_keep_slot_[j - begin] < 0) {
+        attn_keep_slot_[j - begin] = attn_keep_slot_[i - begin] = slots++;
+        elems = std::max(elems, g.B * g.S * g.H * g.d);
+      }
+      break;
+    }
+  }
+  if (slots == 0) return;
+  if (elems > attn_keep_elems_) {   // grow: every buffer anew
+    cudaStreamSynchronize(stream_);
+    for (uint16_t* p : attn_keep_pool_) cudaFree(p);
+    attn_keep_pool_.clear();
+    attn_keep_elems_ = elems;
+  }
+  while (static_cast<int>(attn_keep_pool_.size()) < slots) {
+    void* p = nullptr;
+    if (cudaMalloc(&p, attn_keep_elems_ * 2) != cudaSuccess) {
+      cudaGetLastError();
+      break;
+    }
+    attn_keep_pool_.push_back(static_cast<uint16_t*>(p));
+  }
+  for (int& slot : attn_keep_slot_)
+    if (slot >= static_cast<int>(attn_keep_pool_.size())) slot = -1;
+  attn_keep_written_.assign(attn_keep_pool_.size(), 0);
 }
 
 void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t begin, size_t end) {
@@ -2063,10 +2110,16 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
         const uint64_t elems = op.B * op.S * op.H * op.d;
         const k::Shadow* sh = ShadowFor(ins.in[3], elems);
         if (sh && sh->cols == op.H * op.d && k::ShadowUsable(sh, op.out, elems)) op.shadow = *sh;
+        const int keep = range_index_ < attn_keep_slot_.size() ? attn_keep_slot_[range_index_] : -1;
+        if (keep >= 0) {
+          op.keep = attn_keep_pool_[static_cast<size_t>(keep)];
+          attn_keep_written_[static_cast<size_t>(keep)] = 0;
+        }
         int n = 0;
         if (std::string e = umma::TryAttention(&umma_->ctx, ins.opcode, op, s, &n); !e.empty())
           return std::unexpected("cuda: " + e);
         if (n > 0) {
+          if (keep >= 0) attn_keep_written_[static_cast<size_t>(keep)] = 1;
           shadow_written_ = op.shadow.dst != nullptr;
           ++counters_.relaxed_executions;
           launched(n);
@@ -2127,6 +2180,9 @@ Status CudaBackend::Dispatch(const Instruction& ins, const StepParams& params, c
         if (ins.opcode == kAttnDKTiled && range_index_ < attn_dv_out_.size() &&
             attn_dv_out_[range_index_] != kNullRef)
           op.out2 = Wr(attn_dv_out_[range_index_]);
+        if (ins.opcode == kAttnDQTiled && range_index_ < attn_keep_slot_.size() && attn_keep_slot_[range_index_] >= 0 &&
+            attn_keep_written_[static_cast<size_t>(attn_keep_slot_[range_index_])])
+          op.fwd_keep = attn_keep_pool_[static_cast<size_t>(attn_keep_slot_[range_index_])];
         uint16_t* dv_copy = nullptr;
         if (op.out2 && attn_dv_shadow_[range_index_].want && attn_dv_shadow_[range_index_].scale_ref == kNullRef) {
           const ShadowPlan& sp2 = attn_dv_shadow_[range_index_];

@@ -144,6 +144,7 @@ class CudaBackend {
   // Off: the rank-r expand product of an adapter stays its own kernel instead of
   // riding the frozen product's reduction (takes effect at the next BeginRange).
   void SetLoraFold(bool enabled) { lora_fold_enabled_ = enabled; }
+  void SetAttentionOneWalk(bool enabled) { attn_one_walk_ = enabled; }
 
   // Off: the rank-r adapter products keep the CPU's one-rounding-per-operation
   // arithmetic even in lazy coherence (default on: fused multiply-adds there).
@@ -345,6 +346,14 @@ class CudaBackend {
   // head width 64): one kernel walks the queries once for both.  Per range
   // position of the dK instruction: the dV output reference, or kNullRef.
   std::vector<uint64_t> attn_dv_out_;
+  // Relaxed tiled attention: the forward keeps a private bf16 copy of its output for the dQ of the
+  // same attention (per instruction of the range: the pool slot, or -1); a slot is usable by dQ
+  // once the tensor-core forward of this pass has written it.
+  std::vector<int> attn_keep_slot_;
+  std::vector<uint16_t*> attn_keep_pool_;
+  std::vector<uint8_t> attn_keep_written_;
+  uint64_t attn_keep_elems_ = 0;
+  void PlanAttentionKeeps(std::span<const Instruction> program, size_t begin, size_t end);
   std::vector<ShadowPlan> attn_dv_shadow_;   // the dV instruction's copy plan, made by the pair's kernel
   int64_t skip_attn_dv_at_ = -1;
   int64_t skip_add_at_ = -1;            // the absorbed kAddEW (its output IS written, by the product)
@@ -392,6 +401,7 @@ class CudaBackend {
   uint16_t* d_lora_t_ = nullptr;             // [rows][kx] bf16, reused by every fold
   uint64_t lora_t_capacity_ = 0;
   bool lora_fold_enabled_ = true;
+  bool attn_one_walk_ = true;
   bool adapter_fma_ = true;
   // The three backward products of an adapter site (dT = a dY B^T, dB = a t^T dY,
   // dA = x^T dT), which the plan spells as three instructions that each stream a

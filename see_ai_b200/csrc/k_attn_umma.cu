@@ -182,7 +182,8 @@ __device__ __forceinline__ uint8_t* AlignSmem(uint8_t* raw) {
 template <int D>
 __device__ __forceinline__ void StoreOutRows(uint32_t t_out, float* slab, uint32_t lane, float scale,
                                              float* out0, size_t pitch, uint32_t rows_live,
-                                             const Shadow& sh, size_t flat0, uint32_t col0) {
+                                             const Shadow& sh, size_t flat0, uint32_t col0,
+                                             uint16_t* keep = nullptr) {
   constexpr uint32_t kChunks = D / 4;          // 16-byte chunks per row: 16 or 32
   constexpr uint32_t kRowsPerPass = 32 / kChunks;
 #pragma unroll 1
@@ -205,6 +206,9 @@ __device__ __forceinline__ void StoreOutRows(uint32_t t_out, float* slab, uint32
     const float4 v = *reinterpret_cast<const float4*>(slab + rr * D + ((cl ^ (rr & (kChunks - 1))) * 4));
     *reinterpret_cast<float4*>(out0 + rr * pitch + cl * 4) = v;
     if (sh.dst) ShadowStore4(sh, (flat0 + rr * pitch + cl * 4) / 4, col0 + cl * 4, v);
+    if (keep)
+      *reinterpret_cast<uint2*>(keep + flat0 + rr * pitch + cl * 4) =
+          make_uint2(PackBf16x2(v.x, v.y), PackBf16x2(v.z, v.w));
   }
 }
 
@@ -378,7 +382,7 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const size_t flat0 = (static_cast<size_t>(b) * a.S + row0w) * HD + static_cast<size_t>(h) * D;
     const float inv_l = 1.0f / l;
     StoreOutRows<D>(t_o, reinterpret_cast<float*>(smem) + warp * 32 * D, tid & 31, inv_l,
-                    a.out + flat0, HD, rows_live, a.shadow, flat0, h * D);
+                    a.out + flat0, HD, rows_live, a.shadow, flat0, h * D, a.keep);
     if (live) {
       // The stats row speaks of the true maximum: the sum relative to it is l 2^(ref - max c).
       const float m = raw_max * a.inv_sqrt_d;
@@ -396,10 +400,11 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 }
 
 // ---- dQ (and delta) --------------------------------------------------------------------
-// Per 128 query rows, the keys 64 at a time, twice: the first walk accumulates
-// delta_i = sum_j P_ij dP_ij, the second forms dS = P (dP - delta) / sqrt(d) and
-// accumulates dQ = dS K.  Per step S = Q K_h^T (columns 0..63) and dP = dO V_h^T
-// (64..127); dQ lives in columns 128..128+D.
+// Per 128 query rows, the keys 64 at a time.  Per step S = Q K_h^T (columns
+// 0..63) and dP = dO V_h^T (64..127); dS = P (dP - delta) / sqrt(d) goes to shared
+// memory as bf16 and dQ += dS K (columns 128..128+D).  delta_i = sum_j P_ij dP_ij:
+// with the forward's kept copy of O at hand it is dO_i . O_i, one row of each read
+// by the row's thread before the walk; without it a first walk over the keys sums it.
 template <int D>
 __global__ void __launch_bounds__(128)
 AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
@@ -423,7 +428,8 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   const uint32_t bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
   const uint32_t all_h = (a.S + kHalf - 1) / kHalf;
   const uint32_t n_h = 2 * (it + 1) < all_h ? 2 * (it + 1) : all_h;
-  const uint32_t total = 2 * n_h;
+  const bool one_walk = a.fwd_keep != nullptr;
+  const uint32_t total = one_walk ? n_h : 2 * n_h;
 
   if (tid == 0) {
     MbarInit(&ctl->bar_a, 1); MbarInit(&ctl->bar_b, 1); MbarInit(&ctl->mma, 1);
@@ -460,10 +466,28 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint32_t b_phase = 0;
   int failed = 0;
   if (tid == 0) issue_a(0);
+  if (one_walk && live) {   // (under the first loads' flight)
+    const size_t at = (static_cast<size_t>(b) * a.S + row) * (static_cast<size_t>(a.H) * D) + static_cast<size_t>(h) * D;
+    const uint4* orow = reinterpret_cast<const uint4*>(a.fwd_keep + at);     // eight bf16 per load
+    const float4* drow = reinterpret_cast<const float4*>(a.dout_f32 + at);
+#pragma unroll 2
+    for (int c = 0; c < D / 8; ++c) {
+      const uint4 o = orow[c];
+      const float4 g0 = drow[2 * c], g1 = drow[2 * c + 1];
+      delta = fmaf(__uint_as_float(o.x << 16), g0.x, delta);
+      delta = fmaf(__uint_as_float(o.x & 0xFFFF0000u), g0.y, delta);
+      delta = fmaf(__uint_as_float(o.y << 16), g0.z, delta);
+      delta = fmaf(__uint_as_float(o.y & 0xFFFF0000u), g0.w, delta);
+      delta = fmaf(__uint_as_float(o.z << 16), g1.x, delta);
+      delta = fmaf(__uint_as_float(o.z & 0xFFFF0000u), g1.y, delta);
+      delta = fmaf(__uint_as_float(o.w << 16), g1.z, delta);
+      delta = fmaf(__uint_as_float(o.w & 0xFFFF0000u), g1.w, delta);
+    }
+  }
 
   for (uint32_t t = 0; t < total; ++t) {
     const uint32_t jh = t % n_h;
-    const bool second = t >= n_h;
+    const bool second = one_walk || t >= n_h;
     if (tid == 0) {
       if (!MbarWait(&ctl->bar_a, t & 1)) failed = 1;
       TcFenceAfter();

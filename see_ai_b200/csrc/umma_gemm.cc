@@ -550,8 +550,20 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
   a.status = impl->status;
   a.shadow = op.shadow;
   cudaError_t e = cudaSuccess;
-  if (fwd) e = k::AttnFwdUmma(mr[Q], mh[K], mc[V], a, stream);
-  if (dq) e = k::AttnDQUmma(mr[Q], mr[DO], mh[K], mh[V], mc[K], a, stream);
+  if (fwd) {
+    a.keep = op.keep;
+    e = k::AttnFwdUmma(mr[Q], mh[K], mc[V], a, stream);
+    a.keep = nullptr;
+  }
+  if (dq) {
+    if (op.fwd_keep && (reinterpret_cast<uintptr_t>(op.dout) & 15) == 0) {
+      a.fwd_keep = op.fwd_keep;
+      a.dout_f32 = op.dout;
+    }
+    e = k::AttnDQUmma(mr[Q], mr[DO], mh[K], mh[V], mc[K], a, stream);
+    a.fwd_keep = nullptr;
+    a.dout_f32 = nullptr;
+  }
   const bool both = dk && op.out2 != nullptr && op.d == 64 &&
                     (reinterpret_cast<uintptr_t>(op.out2) & 15) == 0;
   if (both) {

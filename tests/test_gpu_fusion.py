@@ -39,10 +39,11 @@ def _build(rng, read_intermediate_later: bool):
     return prog, arena, ro, (r, 4 * M * N)
 
 
-def _run(prog, arena0, ro, one_range: bool):
+def _run(prog, arena0, ro, one_range: bool, one_walk: bool = False):
     arena = arena0.copy()
     be = B.CudaBackend(0)
     be.set_coherence(B.COHERENCE_LAZY)
+    be.set_attention_one_walk(one_walk)   # (its own test below: another rounding of delta, not the same bits)
     be.bind(arena, ro)
     be.set_program(prog)
     if one_range:
@@ -171,7 +172,7 @@ def test_backward_activation_rides_the_gemm_epilogue(size, case):
 # bit, as the same engine with epilogue fusion switched off — eager, while the
 # graphs are captured, and on replay.
 
-def _engine_run(fusion: bool, steps: int = 4, lora_fold: bool = False):
+def _engine_run(fusion: bool, steps: int = 4, lora_fold: bool = False, one_walk: bool = False):
     import torch
     from see_ai_b200 import synth
     from see_ai_b200.engine import Engine
@@ -187,6 +188,7 @@ def _engine_run(fusion: bool, steps: int = 4, lora_fold: bool = False):
         eng.backend.set_stream(stream.cuda_stream)
         eng.backend.set_epilogue_fusion(fusion)
         eng.backend.set_lora_fold(lora_fold)
+        eng.backend.set_attention_one_walk(one_walk)
         eng.load(blob)
         eng.set_horizon(cfg.steps)
         for _ in range(steps):
@@ -219,6 +221,19 @@ def test_engine_step_with_the_low_rank_fold_stays_within_f32_noise_of_the_step_w
     # (The launch count does not fall: a small kernel cuts each factor into pieces where the expand
     # kernel ran.  What falls is the traffic: the expand read and rewrote the whole [rows, width] sum.)
     assert f_on - f_off >= 16
+
+
+def test_engine_step_with_one_walk_dq_stays_within_relaxed_noise_of_the_two_walk_step():
+    """dQ with delta taken as dO . O from the forward's kept bf16 copy of its output (one walk over the
+    keys) against the two-walk kernel that sums P dP: the same quantity in another rounding, on operands
+    that are bf16-rounded either way."""
+    p_on, l_on, _n, _f = _engine_run(True, one_walk=True)
+    p_off, l_off, _n2, _f2 = _engine_run(True, one_walk=False)
+    assert np.isfinite(l_on).all()
+    assert not np.array_equal(p_on, p_off), "the one-walk kernel gave the two-walk bits: did it run?"
+    assert np.allclose(l_on, l_off, rtol=2e-3, atol=0)
+    a, b = p_on.view(np.float32).astype(np.float64), p_off.view(np.float32).astype(np.float64)
+    assert np.sqrt(np.mean((a - b) ** 2)) <= 5e-2 * np.sqrt(np.mean(b ** 2))   # four AdamW steps amplify sign flips
 
 
 def test_engine_step_with_fusions_is_the_unfused_step_bit_for_bit():
@@ -479,3 +494,16 @@ def test_attention_dk_and_dv_share_one_walk():
     assert c_fused.relaxed_executions == c_split.relaxed_executions == 6
     dv = fused[t["dv"]:t["dv"] + 4 * td].view(np.float32)
     assert np.abs(dv).max() > 0
+    # dQ in one walk (delta = dO . O from the forward's kept bf16 copy of O) against the two-walk kernel
+    # (delta = sum P dP): delta itself, dQ, and dK, which reads delta from the stats row.
+    from tests.util import compare
+    walk1, _c = _run(prog, arena0, ro, one_range=True, one_walk=True)
+    assert not np.array_equal(walk1, fused), "the one-walk kernel gave the two-walk bits: did it run?"
+    st1 = walk1[stats:stats + 16 * Bq * H * S].view(np.float32).reshape(-1, 4)
+    st2 = fused[stats:stats + 16 * Bq * H * S].view(np.float32).reshape(-1, 4)
+    assert np.array_equal(st1[:, :2], st2[:, :2])
+    ok, ratio = compare(st1[:, 2].tobytes(), st2[:, 2].tobytes(), 1e-2, 1e-6)
+    assert ok, ("delta", ratio)
+    for name in ("dq", "dk", "dv"):
+        ok, ratio = compare(walk1[t[name]:t[name] + 4 * td], fused[t[name]:t[name] + 4 * td], 1e-2, 1e-6)
+        assert ok, (name, ratio)
