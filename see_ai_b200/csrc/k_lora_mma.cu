@@ -23,6 +23,13 @@
 // holds its own GEMMs to (2e-6 of 1 + sum|a_k b_k|; reference:
 // test/runtime/executor/kernels_test.cc:1803-1822), not the CPU's bits: the
 // strict seam keeps the bit-exact kernels.
+//
+// Both kernels run at the issue rate of the tensor instruction, not at HBM speed
+// (about 5.6 cycles per m16n8k8 and SM).  Two cheaper-looking forms were measured
+// on the bench shapes and are not kept: the same products as two-piece bf16
+// splits on m16n8k16 (half the instructions, each twice as long: no faster), and
+// as register-tiled f32 multiply-adds on the CUDA cores (bound by shared-memory
+// operand reads at twice the time).
 #include <atomic>
 
 #include "kernels.h"
