@@ -102,7 +102,7 @@ int see_cuda_set_lora_fold(see_cuda_backend* h, int enabled);
  * arithmetic, bit for bit) in lazy coherence too; default 1: fused multiply-adds
  * there.  Strict coherence is always bit-exact. */
 int see_cuda_set_adapter_fma(see_cuda_backend* h, int enabled);
-/* Lazy coherence: the relaxed attention forward keeps a private bf16 copy of its output, and the dQ
+/* Lazy coherence: the relaxed attention forward keeps a private f32 copy of its output, and the dQ
  * instruction of the same attention takes delta_i = sum_j P_ij dP_ij as dO_i . O_i from it and walks
  * the keys once instead of twice.  Same quantity, another rounding (tolerance class, like every relaxed
  * attention result).  Default on; 0 keeps the two-walk kernel. */

@@ -22,33 +22,30 @@ struct AttnUmmaArgs {
   Shadow shadow;    // optional bf16 copy of `out` (cols = H*d) for the GEMM that reads it next
   float* out2 = nullptr;   // dK and dV in one walk: dV goes here (out is dK)
   Shadow shadow2;          // and its optional bf16 copy
-  // Forward: a second, private bf16 copy of O ([B*S, H*d]) kept for the dQ of the same
+  // Forward: a second, private copy of O (f32 [B*S, H*d]) kept for the dQ of the same
   // attention (the arena's O is long overwritten by then — its slot usually holds dO).
-  uint16_t* keep = nullptr;
-  // dQ: that copy, and dO in f32.  delta_i = sum_j P_ij dP_ij equals dO_i . O_i, so the
-  // kernel takes it from one row of each and walks the keys once instead of twice.
-  const uint16_t* fwd_keep = nullptr;
+  float* keep = nullptr;
+  // dQ: that copy, and dO in f32.  delta_i = sum_j P_ij dP_ij equals dO_i . O_i (with dO
+  // rounded to bf16 as the tensor core sees it), so the kernel takes it from one row of
+  // each and walks the keys once instead of twice.
+  const float* fwd_keep = nullptr;
   const float* dout_f32 = nullptr;
 };
 
-// f32 [B*S, H*d] (heads interleaved along the row) -> bf16 per (sequence, head):
-// rows [B*H][S][d] and/or cols [B*H][d][S]; either destination may be null.
-void PackHeads(const float* x, uint16_t* rows, uint16_t* cols, uint32_t B, uint32_t S, uint32_t H,
-               uint32_t d, cudaStream_t s);
+// f32 [B*S, H*d] (heads interleaved along the row) -> bf16 rows [B*H][S][d].
+void PackHeads(const float* x, uint16_t* rows, uint32_t B, uint32_t S, uint32_t H, uint32_t d, cudaStream_t s);
 
-// Row-layout maps: dims {d, S, B*H}, box {64, 128, 1} (a CTA's own 128 rows) or
-// {64, 64, 1} (`_half`: the 64 positions of one step); column-layout maps: dims
-// {S, d, B*H}, box {64, d, 1}; bf16, 128-byte swizzle.  d is 64 or 128.
-cudaError_t AttnFwdUmma(const CUtensorMap& q, const CUtensorMap& k_half, const CUtensorMap& vt,
+// Maps over the packed rows: dims {d, S, B*H}, box {64, 128, 1} (a CTA's own 128 rows) or
+// {64, 64, 1} (`_half`: the 64 positions of one step); bf16, 128-byte swizzle.  d is 64 or 128.
+// A `_half` tile serves both as the K-major operand of a product over the head dimension
+// and as the MN-major operand of a product over its 64 positions.
+cudaError_t AttnFwdUmma(const CUtensorMap& q, const CUtensorMap& k_half, const CUtensorMap& v_half,
                         const AttnUmmaArgs& a, cudaStream_t s);
 cudaError_t AttnDQUmma(const CUtensorMap& q, const CUtensorMap& dout, const CUtensorMap& k_half,
-                       const CUtensorMap& v_half, const CUtensorMap& kt, const AttnUmmaArgs& a,
-                       cudaStream_t s);
-// mode 0: dV (t = dO columns; v and dout_half ignored); 1: dK (t = Q columns);
-// 2: both in one walk (t = Q columns, t2 = dO columns, a.out = dK, a.out2 = dV; d = 64 only).
-cudaError_t AttnDKVUmma(int mode, const CUtensorMap& k, const CUtensorMap& v,
-                        const CUtensorMap& q_half, const CUtensorMap& dout_half, const CUtensorMap& t,
-                        const CUtensorMap& t2, const AttnUmmaArgs& a, cudaStream_t s);
+                       const CUtensorMap& v_half, const AttnUmmaArgs& a, cudaStream_t s);
+// mode 0: dV (v ignored); 1: dK; 2: both in one walk (a.out = dK, a.out2 = dV; d = 64 only).
+cudaError_t AttnDKVUmma(int mode, const CUtensorMap& k, const CUtensorMap& v, const CUtensorMap& q_half,
+                        const CUtensorMap& dout_half, const AttnUmmaArgs& a, cudaStream_t s);
 
 }  // namespace see::k
 

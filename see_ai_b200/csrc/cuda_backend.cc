@@ -110,7 +110,7 @@ CudaBackend::~CudaBackend() {
   cudaFree(d_adam_table_);
   FreeLoraRanges();
   cudaFree(d_lora_t_);
-  for (uint16_t* p : attn_keep_pool_) cudaFree(p);
+  for (float* p : attn_keep_pool_) cudaFree(p);
   cudaFree(d_lora_partials_);
   if (h_scalars_) cudaFreeHost(h_scalars_);
   if (h_status_) cudaFreeHost(h_status_);
@@ -805,7 +805,7 @@ static bool DeadFrom(std::span<const Instruction> program, const std::vector<Ext
 
 // Pairs each relaxed kAttnDQTiled of the range with the kAttnFwdTiled of the same
 // attention earlier in the range (same q, k, v and stats row) and gives the pair a
-// buffer for the forward's bf16 copy of O.  Buffers are allocated here, before any
+// buffer for the forward's kept copy of O.  Buffers are allocated here, before any
 // capture; a failed allocation just leaves the pair on the two-walk kernel.
 void CudaBackend::PlanAttentionKeeps(std::span<const Instruction> program, size_t begin, size_t end) {
   attn_keep_slot_.assign(end > begin ? end - begin : 0, -1);
@@ -831,17 +831,17 @@ void CudaBackend::PlanAttentionKeeps(std::span<const Instruction> program, size_
   if (slots == 0) return;
   if (elems > attn_keep_elems_) {   // grow: every buffer anew
     cudaStreamSynchronize(stream_);
-    for (uint16_t* p : attn_keep_pool_) cudaFree(p);
+    for (float* p : attn_keep_pool_) cudaFree(p);
     attn_keep_pool_.clear();
     attn_keep_elems_ = elems;
   }
   while (static_cast<int>(attn_keep_pool_.size()) < slots) {
     void* p = nullptr;
-    if (cudaMalloc(&p, attn_keep_elems_ * 2) != cudaSuccess) {
+    if (cudaMalloc(&p, attn_keep_elems_ * sizeof(float)) != cudaSuccess) {
       cudaGetLastError();
       break;
     }
-    attn_keep_pool_.push_back(static_cast<uint16_t*>(p));
+    attn_keep_pool_.push_back(static_cast<float*>(p));
   }
   for (int& slot : attn_keep_slot_)
     if (slot >= static_cast<int>(attn_keep_pool_.size())) slot = -1;

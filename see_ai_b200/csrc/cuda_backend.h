@@ -346,11 +346,11 @@ class CudaBackend {
   // head width 64): one kernel walks the queries once for both.  Per range
   // position of the dK instruction: the dV output reference, or kNullRef.
   std::vector<uint64_t> attn_dv_out_;
-  // Relaxed tiled attention: the forward keeps a private bf16 copy of its output for the dQ of the
+  // Relaxed tiled attention: the forward keeps a private f32 copy of its output for the dQ of the
   // same attention (per instruction of the range: the pool slot, or -1); a slot is usable by dQ
   // once the tensor-core forward of this pass has written it.
   std::vector<int> attn_keep_slot_;
-  std::vector<uint16_t*> attn_keep_pool_;
+  std::vector<float*> attn_keep_pool_;
   std::vector<uint8_t> attn_keep_written_;
   uint64_t attn_keep_elems_ = 0;
   void PlanAttentionKeeps(std::span<const Instruction> program, size_t begin, size_t end);

@@ -7,7 +7,7 @@
 // delta into the stats row and dQ; dK and dV read the stats row.
 //
 // Blackwell-native: per (sequence, head) the operands are packed once to bf16
-// ([S][d] and [d][S]), tiles arrive by TMA (128-byte swizzle), every product
+// ([S][d]), tiles arrive by TMA (128-byte swizzle), every product
 // (Q K^T, P V, dO V^T, dS K, dS^T Q, P^T dO) is a tcgen05.mma with its
 // accumulator in tensor memory, and the softmax / softmax-backward arithmetic
 // runs in f32 registers on values read with tcgen05.ld; P and dS go back to
@@ -39,11 +39,11 @@ constexpr uint32_t kTile = 128;          // query rows / key rows per tile
 constexpr uint32_t kSubTileBytes = 128 * 64 * 2;   // [128 rows][64 bf16], swizzled
 constexpr uint32_t kPBytes = 2 * kSubTileBytes;    // P / dS tile: 128 x 128 bf16
 
-// ---- packing: f32 [B*S, H*d] -> bf16 [B*H][S][d] (rows) and [B*H][d][S] (cols) ----
-// One block packs 64 positions of one (sequence, head): 16-byte loads of the f32
-// rows, 8-byte stores of the bf16 row layout straight from registers, and the
-// column layout through a shared-memory transpose, again as 8-byte stores (four
-// positions of one feature).  Reads the source once for both layouts.
+// ---- packing: f32 [B*S, H*d] -> bf16 [B*H][S][d] ----------------------------------------
+// One block packs 64 positions of one (sequence, head): 16-byte loads of the f32 rows,
+// 8-byte stores of the bf16 rows.  (Every operand of the kernels below is taken from this
+// one layout: as a K-major tile where the head dimension is the reduction index, as an
+// MN-major tile where the positions are.)
 __device__ __forceinline__ uint32_t Bf16Bits(float f) {   // round to nearest even; NaN stays NaN
   uint32_t u = __float_as_uint(f);
   if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (u >> 16) | 0x0040u;
@@ -55,9 +55,7 @@ constexpr uint32_t kPackPos = 64;
 
 template <int D>
 __global__ void __launch_bounds__(256)
-PackHeadsKernel(const float* __restrict__ x, uint16_t* __restrict__ rows, uint16_t* __restrict__ cols,
-                uint32_t S, uint32_t H) {
-  __shared__ uint16_t tile[kPackPos][D + 2];   // odd word stride: conflict-free transpose reads
+PackHeadsKernel(const float* __restrict__ x, uint16_t* __restrict__ rows, uint32_t S, uint32_t H) {
   const uint32_t bh = blockIdx.y, b = bh / H, h = bh % H;
   const uint32_t s0 = blockIdx.x * kPackPos;
   const size_t HD = static_cast<size_t>(H) * D;
@@ -65,32 +63,11 @@ PackHeadsKernel(const float* __restrict__ x, uint16_t* __restrict__ rows, uint16
   for (uint32_t idx = threadIdx.x; idx < kPackPos * kVecPerRow; idx += 256) {
     const uint32_t i = idx / kVecPerRow, c = (idx % kVecPerRow) * 4;
     const uint32_t s = s0 + i;
-    uint32_t lo = 0, hi = 0;
-    if (s < S) {
-      const float4 f = *reinterpret_cast<const float4*>(
-          x + (static_cast<size_t>(b) * S + s) * HD + static_cast<size_t>(h) * D + c);
-      lo = Bf16Bits(f.x) | (Bf16Bits(f.y) << 16);
-      hi = Bf16Bits(f.z) | (Bf16Bits(f.w) << 16);
-      if (rows)
-        *reinterpret_cast<uint2*>(rows + (static_cast<size_t>(bh) * S + s) * D + c) = make_uint2(lo, hi);
-    }
-    *reinterpret_cast<uint32_t*>(&tile[i][c]) = lo;
-    *reinterpret_cast<uint32_t*>(&tile[i][c + 2]) = hi;
-  }
-  if (!cols) return;
-  __syncthreads();
-  constexpr uint32_t kGroups = kPackPos / 4;   // groups of four positions
-  for (uint32_t idx = threadIdx.x; idx < D * kGroups; idx += 256) {
-    const uint32_t c = idx / kGroups, i = (idx % kGroups) * 4;
-    const uint32_t s = s0 + i;
-    if (s + 4 <= S) {
-      const uint32_t lo = tile[i][c] | (static_cast<uint32_t>(tile[i + 1][c]) << 16);
-      const uint32_t hi = tile[i + 2][c] | (static_cast<uint32_t>(tile[i + 3][c]) << 16);
-      *reinterpret_cast<uint2*>(cols + (static_cast<size_t>(bh) * D + c) * S + s) = make_uint2(lo, hi);
-    } else {
-      for (uint32_t t = 0; t < 4 && s + t < S; ++t)
-        cols[(static_cast<size_t>(bh) * D + c) * S + s + t] = tile[i + t][c];
-    }
+    if (s >= S) continue;
+    const float4 f = *reinterpret_cast<const float4*>(
+        x + (static_cast<size_t>(b) * S + s) * HD + static_cast<size_t>(h) * D + c);
+    *reinterpret_cast<uint2*>(rows + (static_cast<size_t>(bh) * S + s) * D + c) =
+        make_uint2(Bf16Bits(f.x) | (Bf16Bits(f.y) << 16), Bf16Bits(f.z) | (Bf16Bits(f.w) << 16));
   }
 }
 
@@ -122,12 +99,6 @@ __device__ __forceinline__ void LoadRows(uint8_t* dst, const CUtensorMap* map, u
     TmaLoad3D(dst + kb * (R * 128), map, bar, kb * 64, static_cast<int32_t>(row0),
               static_cast<int32_t>(bh));
 }
-// Loads [D rows][64 positions] of a column-layout tensor ({S, d, BH} map with box {64, D}).
-__device__ __forceinline__ void LoadColsHalf(uint8_t* dst, const CUtensorMap* map, uint64_t* bar,
-                                             uint32_t pos0, uint32_t bh) {
-  TmaLoad3D(dst, map, bar, static_cast<int32_t>(pos0), 0, static_cast<int32_t>(bh));
-}
-
 // acc[128 x NB] = A[128 rows][D] . B[NB rows][D]^T, both row tiles in shared memory.
 template <int D, int NB>
 __device__ __forceinline__ void MmaRowRow(uint32_t tmem, const uint8_t* a, const uint8_t* b) {
@@ -140,16 +111,18 @@ __device__ __forceinline__ void MmaRowRow(uint32_t tmem, const uint8_t* a, const
     for (int k = 0; k < 4; ++k) UmmaBf16(tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
   }
 }
-// acc[128 x D] (+)= P[128 rows][64] . T[D rows][64]^T.  `accumulate` = 0 starts afresh.
+// acc[128 x D] (+)= P[128 rows][64] . T with T given as a ROW tile [64 positions][D]
+// (the positions are the reduction index: an MN-major B operand), D / 64 sub-tiles of
+// [64][64] as LoadRows<D, 64> leaves them.
 template <int D>
-__device__ __forceinline__ void MmaPT(uint32_t tmem, const uint8_t* p, const uint8_t* t,
-                                      uint32_t accumulate) {
-  const uint32_t idesc = MakeInstrDesc(128, D);
+__device__ __forceinline__ void MmaPRows(uint32_t tmem, const uint8_t* p, const uint8_t* t_rows,
+                                         uint32_t accumulate) {
+  const uint32_t idesc = MakeInstrDesc(128, D) | kInstrDescBMnMajor;
   const uint64_t da = MakeSmemDesc(SmemAddr(p));
-  const uint64_t db = MakeSmemDesc(SmemAddr(t));
+  const uint32_t tb = SmemAddr(t_rows);
 #pragma unroll
   for (int k = 0; k < 4; ++k)
-    UmmaBf16(tmem, da + 2 * k, db + 2 * k, idesc, (accumulate | k) != 0 ? 1u : 0u);
+    UmmaBf16(tmem, da + 2 * k, MakeSmemDescMn(tb + k * 2048, 64 * 128), idesc, (accumulate | k) != 0 ? 1u : 0u);
 }
 
 // Writes 32 consecutive values of this thread's row (columns c0 .. c0+31 of the 64-wide
@@ -183,7 +156,7 @@ template <int D>
 __device__ __forceinline__ void StoreOutRows(uint32_t t_out, float* slab, uint32_t lane, float scale,
                                              float* out0, size_t pitch, uint32_t rows_live,
                                              const Shadow& sh, size_t flat0, uint32_t col0,
-                                             uint16_t* keep = nullptr) {
+                                             float* keep = nullptr) {
   constexpr uint32_t kChunks = D / 4;          // 16-byte chunks per row: 16 or 32
   constexpr uint32_t kRowsPerPass = 32 / kChunks;
 #pragma unroll 1
@@ -206,9 +179,7 @@ __device__ __forceinline__ void StoreOutRows(uint32_t t_out, float* slab, uint32
     const float4 v = *reinterpret_cast<const float4*>(slab + rr * D + ((cl ^ (rr & (kChunks - 1))) * 4));
     *reinterpret_cast<float4*>(out0 + rr * pitch + cl * 4) = v;
     if (sh.dst) ShadowStore4(sh, (flat0 + rr * pitch + cl * 4) / 4, col0 + cl * 4, v);
-    if (keep)
-      *reinterpret_cast<uint2*>(keep + flat0 + rr * pitch + cl * 4) =
-          make_uint2(PackBf16x2(v.x, v.y), PackBf16x2(v.z, v.w));
+    if (keep) *reinterpret_cast<float4*>(keep + flat0 + rr * pitch + cl * 4) = v;
   }
 }
 
@@ -239,7 +210,7 @@ constexpr float kRescaleSlack = 8.0f;   // log2 units
 template <int D>
 __global__ void __launch_bounds__(128)
 AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                  const __grid_constant__ CUtensorMap map_vt, AttnUmmaArgs a) {
+                  const __grid_constant__ CUtensorMap map_v, AttnUmmaArgs a) {
   extern __shared__ uint8_t smem_raw[];
   Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw);             // barriers first, tiles 1024-aligned after
   uint8_t* smem = AlignSmem(smem_raw + sizeof(Ctl));
@@ -276,7 +247,7 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   };
   auto issue_b = [&](uint32_t t) {
     MbarExpectTx(&ctl->bar_b, kVBytes);
-    LoadColsHalf(v_s, &map_vt, &ctl->bar_b, t * kHalf, bh);
+    LoadRows<D, 64>(v_s, &map_v, &ctl->bar_b, t * kHalf, bh);   // V_h as rows: the MN-major operand of P V
   };
 
   const uint32_t row = it * kTile + tid;                   // this thread's query row
@@ -364,7 +335,7 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     if (tid == 0) {
       if (!MbarWait(&ctl->bar_b, t & 1)) failed = 1;
       TcFenceAfter();
-      if (!failed) MmaPT<D>(tmem + 64, p_s, v_s, t != 0);
+      if (!failed) MmaPRows<D>(tmem + 64, p_s, v_s, t != 0);
     }
   }
   if (tid == 0) UmmaCommit(&ctl->mma);
@@ -409,17 +380,16 @@ template <int D>
 __global__ void __launch_bounds__(128)
 AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                  const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                 const __grid_constant__ CUtensorMap map_kt, AttnUmmaArgs a) {
+                 AttnUmmaArgs a) {
   extern __shared__ uint8_t smem_raw[];
   Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw);
   uint8_t* smem = AlignSmem(smem_raw + sizeof(Ctl));
-  constexpr uint32_t kFull = 128 * D * 2, kHalfRows = 64 * D * 2, kCols = D * 128;
+  constexpr uint32_t kFull = 128 * D * 2, kHalfRows = 64 * D * 2;
   uint8_t* q_s = smem;
   uint8_t* do_s = q_s + kFull;
-  uint8_t* k_s = do_s + kFull;
-  uint8_t* v_s = k_s + kHalfRows;
-  uint8_t* kt_s = v_s + kHalfRows;
-  uint8_t* p_s = kt_s + kCols;
+  uint8_t* k_s = do_s + kFull;          // two buffers: step t's K_h also feeds dQ += dS K_h after the softmax,
+  uint8_t* v_s = k_s + 2 * kHalfRows;   // while step t + 1's is already on its way
+  uint8_t* p_s = v_s + kHalfRows;
   constexpr uint32_t kTmemCols = TmemColsFor(128 + D);
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5;
@@ -448,12 +418,8 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       LoadRows<D, 128>(q_s, &map_q, &ctl->bar_a, it * kTile, bh);
       LoadRows<D, 128>(do_s, &map_do, &ctl->bar_a, it * kTile, bh);
     }
-    LoadRows<D, 64>(k_s, &map_k, &ctl->bar_a, (t % n_h) * kHalf, bh);
+    LoadRows<D, 64>(k_s + (t & 1) * kHalfRows, &map_k, &ctl->bar_a, (t % n_h) * kHalf, bh);
     LoadRows<D, 64>(v_s, &map_v, &ctl->bar_a, (t % n_h) * kHalf, bh);
-  };
-  auto issue_b = [&](uint32_t jh) {
-    MbarExpectTx(&ctl->bar_b, kCols);
-    LoadColsHalf(kt_s, &map_kt, &ctl->bar_b, jh * kHalf, bh);
   };
 
   const uint32_t row = it * kTile + tid;
@@ -463,25 +429,20 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   // P = 2^(s * log2(e)/sqrt(d) - M) with M = max * log2(e) - log2(1/denominator).
   const float m2l = live ? st_row[0] * kLog2e - log2f(st_row[1]) : 0.0f;
   float delta = 0.0f;
-  uint32_t b_phase = 0;
   int failed = 0;
   if (tid == 0) issue_a(0);
   if (one_walk && live) {   // (under the first loads' flight)
     const size_t at = (static_cast<size_t>(b) * a.S + row) * (static_cast<size_t>(a.H) * D) + static_cast<size_t>(h) * D;
-    const uint4* orow = reinterpret_cast<const uint4*>(a.fwd_keep + at);     // eight bf16 per load
+    const float4* orow = reinterpret_cast<const float4*>(a.fwd_keep + at);
     const float4* drow = reinterpret_cast<const float4*>(a.dout_f32 + at);
-#pragma unroll 2
-    for (int c = 0; c < D / 8; ++c) {
-      const uint4 o = orow[c];
-      const float4 g0 = drow[2 * c], g1 = drow[2 * c + 1];
-      delta = fmaf(__uint_as_float(o.x << 16), g0.x, delta);
-      delta = fmaf(__uint_as_float(o.x & 0xFFFF0000u), g0.y, delta);
-      delta = fmaf(__uint_as_float(o.y << 16), g0.z, delta);
-      delta = fmaf(__uint_as_float(o.y & 0xFFFF0000u), g0.w, delta);
-      delta = fmaf(__uint_as_float(o.z << 16), g1.x, delta);
-      delta = fmaf(__uint_as_float(o.z & 0xFFFF0000u), g1.y, delta);
-      delta = fmaf(__uint_as_float(o.w << 16), g1.z, delta);
-      delta = fmaf(__uint_as_float(o.w & 0xFFFF0000u), g1.w, delta);
+    auto as_bf16 = [](float x) { return __uint_as_float(Bf16Bits(x) << 16); };   // dO as the products below see it
+#pragma unroll 4
+    for (int c = 0; c < D / 4; ++c) {
+      const float4 o = orow[c], g = drow[c];
+      delta = fmaf(o.x, as_bf16(g.x), delta);
+      delta = fmaf(o.y, as_bf16(g.y), delta);
+      delta = fmaf(o.z, as_bf16(g.z), delta);
+      delta = fmaf(o.w, as_bf16(g.w), delta);
     }
   }
 
@@ -492,17 +453,14 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       if (!MbarWait(&ctl->bar_a, t & 1)) failed = 1;
       TcFenceAfter();
       if (!failed) {
-        MmaRowRow<D, 64>(tmem, q_s, k_s);          // S  = Q K_h^T
+        MmaRowRow<D, 64>(tmem, q_s, k_s + (t & 1) * kHalfRows);   // S  = Q K_h^T
         MmaRowRow<D, 64>(tmem + 64, do_s, v_s);    // dP = dO V_h^T
       }
       UmmaCommit(&ctl->mma);   // also covers the previous step's dQ += dS K_h
     }
     if (!MbarWait(&ctl->mma, t & 1)) failed = 1;
     TcFenceAfter();
-    if (tid == 0 && !failed) {
-      if (t + 1 < total) issue_a(t + 1);
-      if (second) issue_b(jh);
-    }
+    if (tid == 0 && !failed && t + 1 < total) issue_a(t + 1);
     __syncwarp();
     const uint32_t key0 = jh * kHalf;
     const bool diagonal = key0 + kHalf > it * kTile;
@@ -535,10 +493,8 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     TcFenceBefore();
     if (__syncthreads_or(failed)) { failed = 1; break; }
     if (second && tid == 0) {
-      if (!MbarWait(&ctl->bar_b, b_phase)) failed = 1;
-      b_phase ^= 1;
       TcFenceAfter();
-      if (!failed) MmaPT<D>(tmem + 128, p_s, kt_s, jh != 0);   // dQ += dS K_h
+      MmaPRows<D>(tmem + 128, p_s, k_s + (t & 1) * kHalfRows, jh != 0);   // dQ += dS K_h (K_h as the MN-major operand)
     }
   }
   if (tid == 0) UmmaCommit(&ctl->mma);
@@ -581,21 +537,20 @@ template <int D, int kMode>
 __global__ void __launch_bounds__(128)
 AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                   const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
-                  const __grid_constant__ CUtensorMap map_t, const __grid_constant__ CUtensorMap map_t2,
                   AttnUmmaArgs a) {
   constexpr bool kWantDK = kMode >= 1;
   constexpr bool kBoth = kMode == 2;
   extern __shared__ uint8_t smem_raw[];
   Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw);
   uint8_t* smem = AlignSmem(smem_raw + sizeof(Ctl));
-  constexpr uint32_t kFull = 128 * D * 2, kHalfRows = 64 * D * 2, kCols = D * 128;
+  constexpr uint32_t kFull = 128 * D * 2, kHalfRows = 64 * D * 2;
   uint8_t* k_s = smem;
   uint8_t* v_s = k_s + kFull;                                // dK only
+  // Q_h and dO_h are double-buffered: a step's tiles also feed its second products
+  // (as MN-major operands) after the softmax, while the next step's are on their way.
   uint8_t* q_s = v_s + (kWantDK ? kFull : 0);
-  uint8_t* do_s = q_s + kHalfRows;                           // dK only
-  uint8_t* t_s = do_s + (kWantDK ? kHalfRows : 0);
-  uint8_t* t2_s = t_s + kCols;                               // both: dO in the column layout
-  uint8_t* p_s = t2_s + (kBoth ? kCols : 0);
+  uint8_t* do_s = q_s + 2 * kHalfRows;
+  uint8_t* p_s = do_s + 2 * kHalfRows;
   uint8_t* p2_s = p_s + kHalfTileBytes;                      // both: P^T beside dS^T
   float* stat_s = reinterpret_cast<float*>(p2_s + (kBoth ? kHalfTileBytes : 0));   // M[64], delta[64]
   constexpr uint32_t kOutCol = kWantDK ? 128 : 64;
@@ -621,19 +576,14 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
   const uint32_t t_lane = tmem + ((warp * 32) << 16);
 
   auto issue_a = [&](uint32_t t) {
-    constexpr uint32_t kPer = (kWantDK ? 2 : 1) * kHalfRows, kOnce = (kWantDK ? 2 : 1) * kFull;
+    constexpr uint32_t kPer = 2 * kHalfRows, kOnce = (kWantDK ? 2 : 1) * kFull;
     MbarExpectTx(&ctl->bar_a, kPer + (t == 0 ? kOnce : 0));
     if (t == 0) {
       LoadRows<D, 128>(k_s, &map_k, &ctl->bar_a, jt * kTile, bh);
       if (kWantDK) LoadRows<D, 128>(v_s, &map_v, &ctl->bar_a, jt * kTile, bh);
     }
-    LoadRows<D, 64>(q_s, &map_q, &ctl->bar_a, (h0 + t) * kHalf, bh);
-    if (kWantDK) LoadRows<D, 64>(do_s, &map_do, &ctl->bar_a, (h0 + t) * kHalf, bh);
-  };
-  auto issue_b = [&](uint32_t t) {
-    MbarExpectTx(&ctl->bar_b, (kBoth ? 2 : 1) * kCols);
-    LoadColsHalf(t_s, &map_t, &ctl->bar_b, (h0 + t) * kHalf, bh);
-    if (kBoth) LoadColsHalf(t2_s, &map_t2, &ctl->bar_b, (h0 + t) * kHalf, bh);
+    LoadRows<D, 64>(q_s + (t & 1) * kHalfRows, &map_q, &ctl->bar_a, (h0 + t) * kHalf, bh);
+    LoadRows<D, 64>(do_s + (t & 1) * kHalfRows, &map_do, &ctl->bar_a, (h0 + t) * kHalf, bh);
   };
 
   const uint32_t key = jt * kTile + tid;                    // this thread's key row
@@ -659,18 +609,15 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
       if (!MbarWait(&ctl->bar_a, t & 1)) failed = 1;
       TcFenceAfter();
       if (!failed) {
-        MmaRowRow<D, 64>(tmem, k_s, q_s);                          // S^T  = K Q_h^T
-        if (kWantDK) MmaRowRow<D, 64>(tmem + 64, v_s, do_s);       // dP^T = V dO_h^T
+        MmaRowRow<D, 64>(tmem, k_s, q_s + (t & 1) * kHalfRows);                          // S^T  = K Q_h^T
+        if (kWantDK) MmaRowRow<D, 64>(tmem + 64, v_s, do_s + (t & 1) * kHalfRows);       // dP^T = V dO_h^T
       }
       UmmaCommit(&ctl->mma);   // also covers the previous step's second product
     }
     __syncthreads();           // stat_s is written
     if (!MbarWait(&ctl->mma, t & 1)) failed = 1;
     TcFenceAfter();
-    if (tid == 0 && !failed) {
-      if (t + 1 < total) issue_a(t + 1);
-      issue_b(t);
-    }
+    if (tid == 0 && !failed && t + 1 < total) issue_a(t + 1);
     __syncwarp();
     const bool diagonal = q0 < jt * kTile + kTile;   // some (key, query) pairs are masked
 #pragma unroll 1
@@ -705,13 +652,12 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     FenceProxyAsync();
     TcFenceBefore();
     if (__syncthreads_or(failed)) { failed = 1; break; }
-    if (tid == 0) {
-      if (!MbarWait(&ctl->bar_b, t & 1)) failed = 1;
+    if (tid == 0) {   // the step's own Q_h / dO_h tiles again, now as the MN-major operands
       TcFenceAfter();
-      if (!failed) {
-        MmaPT<D>(tmem + kOutCol, p_s, t_s, t != 0);                 // dK += dS^T Q_h, or dV += P^T dO_h
-        if (kBoth) MmaPT<D>(tmem + kOutCol2, p2_s, t2_s, t != 0);   // dV += P^T dO_h
-      }
+      const uint8_t* qh = q_s + (t & 1) * kHalfRows;
+      const uint8_t* doh = do_s + (t & 1) * kHalfRows;
+      MmaPRows<D>(tmem + kOutCol, p_s, kWantDK ? qh : doh, t != 0);   // dK += dS^T Q_h, or dV += P^T dO_h
+      if (kBoth) MmaPRows<D>(tmem + kOutCol2, p2_s, doh, t != 0);     // dV += P^T dO_h
     }
   }
   if (tid == 0) UmmaCommit(&ctl->mma);
@@ -745,10 +691,10 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 }  // namespace
 
 size_t AttnFwdSmem(int d) { return 128 * d * 2 + 64 * d * 2 + d * 128 + kHalfTileBytes + 1152; }
-size_t AttnDQSmem(int d) { return 2 * 128 * d * 2 + 2 * 64 * d * 2 + d * 128 + kHalfTileBytes + 1152; }
+size_t AttnDQSmem(int d) { return 2 * 128 * d * 2 + 3 * 64 * d * 2 + kHalfTileBytes + 1152; }
 size_t AttnDKVSmem(int d, int mode) {   // 0: dV, 1: dK, 2: both
-  const size_t full = 128 * d * 2, half = 64 * d * 2, cols = d * 128;
-  return (mode >= 1 ? 2 : 1) * (full + half) + (mode == 2 ? 2 : 1) * (cols + kHalfTileBytes) + 2 * kHalf * 4 + 1152;
+  const size_t full = 128 * d * 2, half = 64 * d * 2;
+  return (mode >= 1 ? 2 : 1) * full + 4 * half + (mode == 2 ? 2 : 1) * kHalfTileBytes + 2 * kHalf * 4 + 1152;
 }
 
 template <typename Kernel>
@@ -756,54 +702,52 @@ static cudaError_t Configure(Kernel kernel, size_t smem) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
 }
 
-void PackHeads(const float* x, uint16_t* rows, uint16_t* cols, uint32_t B, uint32_t S, uint32_t H,
-               uint32_t d, cudaStream_t s) {
+void PackHeads(const float* x, uint16_t* rows, uint32_t B, uint32_t S, uint32_t H, uint32_t d, cudaStream_t s) {
   const dim3 grid((S + kPackPos - 1) / kPackPos, B * H);
-  if (d == 64) PackHeadsKernel<64><<<grid, 256, 0, s>>>(x, rows, cols, S, H);
-  else PackHeadsKernel<128><<<grid, 256, 0, s>>>(x, rows, cols, S, H);
+  if (d == 64) PackHeadsKernel<64><<<grid, 256, 0, s>>>(x, rows, S, H);
+  else PackHeadsKernel<128><<<grid, 256, 0, s>>>(x, rows, S, H);
 }
 
-cudaError_t AttnFwdUmma(const CUtensorMap& q, const CUtensorMap& k_half, const CUtensorMap& vt,
+cudaError_t AttnFwdUmma(const CUtensorMap& q, const CUtensorMap& k_half, const CUtensorMap& v_half,
                         const AttnUmmaArgs& a, cudaStream_t s) {
   dim3 grid((a.S + kTile - 1) / kTile, a.B * a.H);
   const size_t smem = AttnFwdSmem(a.d);
   cudaError_t e;
   if (a.d == 64) {
     if ((e = Configure(AttnFwdUmmaKernel<64>, smem)) != cudaSuccess) return e;
-    AttnFwdUmmaKernel<64><<<grid, 128, smem, s>>>(q, k_half, vt, a);
+    AttnFwdUmmaKernel<64><<<grid, 128, smem, s>>>(q, k_half, v_half, a);
   } else {
     if ((e = Configure(AttnFwdUmmaKernel<128>, smem)) != cudaSuccess) return e;
-    AttnFwdUmmaKernel<128><<<grid, 128, smem, s>>>(q, k_half, vt, a);
+    AttnFwdUmmaKernel<128><<<grid, 128, smem, s>>>(q, k_half, v_half, a);
   }
   return cudaGetLastError();
 }
 
 cudaError_t AttnDQUmma(const CUtensorMap& q, const CUtensorMap& dout, const CUtensorMap& k_half,
-                       const CUtensorMap& v_half, const CUtensorMap& kt, const AttnUmmaArgs& a,
-                       cudaStream_t s) {
+                       const CUtensorMap& v_half, const AttnUmmaArgs& a, cudaStream_t s) {
   dim3 grid((a.S + kTile - 1) / kTile, a.B * a.H);
   const size_t smem = AttnDQSmem(a.d);
   cudaError_t e;
   if (a.d == 64) {
     if ((e = Configure(AttnDQUmmaKernel<64>, smem)) != cudaSuccess) return e;
-    AttnDQUmmaKernel<64><<<grid, 128, smem, s>>>(q, dout, k_half, v_half, kt, a);
+    AttnDQUmmaKernel<64><<<grid, 128, smem, s>>>(q, dout, k_half, v_half, a);
   } else {
     if ((e = Configure(AttnDQUmmaKernel<128>, smem)) != cudaSuccess) return e;
-    AttnDQUmmaKernel<128><<<grid, 128, smem, s>>>(q, dout, k_half, v_half, kt, a);
+    AttnDQUmmaKernel<128><<<grid, 128, smem, s>>>(q, dout, k_half, v_half, a);
   }
   return cudaGetLastError();
 }
 
 cudaError_t AttnDKVUmma(int mode, const CUtensorMap& k, const CUtensorMap& v,
-                        const CUtensorMap& q_half, const CUtensorMap& dout_half, const CUtensorMap& t,
-                        const CUtensorMap& t2, const AttnUmmaArgs& a, cudaStream_t s) {
+                        const CUtensorMap& q_half, const CUtensorMap& dout_half, const AttnUmmaArgs& a,
+                        cudaStream_t s) {
   dim3 grid((a.S + kTile - 1) / kTile, a.B * a.H);
   cudaError_t e;
 #define SEE_LAUNCH_DKV(D, MODE)                                                              \
   do {                                                                                       \
     const size_t smem = AttnDKVSmem(D, MODE);                                                \
     if ((e = Configure(AttnDKVUmmaKernel<D, MODE>, smem)) != cudaSuccess) return e;          \
-    AttnDKVUmmaKernel<D, MODE><<<grid, 128, smem, s>>>(k, v, q_half, dout_half, t, t2, a);   \
+    AttnDKVUmmaKernel<D, MODE><<<grid, 128, smem, s>>>(k, v, q_half, dout_half, a);   \
   } while (0)
   if (a.d == 64) {
     if (mode == 2) SEE_LAUNCH_DKV(64, 2); else if (mode == 1) SEE_LAUNCH_DKV(64, 1); else SEE_LAUNCH_DKV(64, 0);

@@ -95,6 +95,23 @@ __device__ __forceinline__ uint64_t MakeSmemDesc(uint32_t smem_addr) {
   return d;
 }
 
+// The same for an MN-major operand under the 128-byte swizzle: the tile is stored
+// [k][64 elements of M or N] (128-byte rows, one per k, eight of them per 1024-byte
+// swizzle atom) — what a TMA load of a row-major [rows = k][columns = n] tensor
+// leaves.  Stride byte offset 1024 (from one group of eight k to the next), leading
+// byte offset = the distance between successive 64-element groups along M / N.
+// Advancing K by 16 adds 16 rows = 2048 bytes to the start address.
+__device__ __forceinline__ uint64_t MakeSmemDescMn(uint32_t smem_addr, uint32_t group_stride_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>((group_stride_bytes >> 4) & 0x3FFF) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+constexpr uint32_t kInstrDescBMnMajor = 1u << 16;   // OR into MakeInstrDesc: B is MN-major
+
 // Instruction descriptor for kind::f16: D = f32, A = B = bf16, both K-major.
 __device__ __forceinline__ uint32_t MakeInstrDesc(uint32_t m, uint32_t n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);

@@ -38,14 +38,13 @@ struct ActCopy {   // a bf16 copy of an arena activation [M, K]
 
 constexpr int kActSlots = 8;
 
-// Packed bf16 copies of one attention operand (a Q, K, V or dO activation), in
-// both layouts the kernels read: rows [B*H][S][d] and cols [B*H][d][S].  Made
+// The packed bf16 copy of one attention operand (a Q, K, V or dO activation):
+// rows [B*H][S][d], the one layout the kernels read.  Made
 // once, by one kernel, the first time any attention instruction of the range
 // reads the operand; the forward's copies serve the backward of the same step
 // unless an instruction overwrote the source in between.
 struct PackEntry {
   uint16_t* rows = nullptr;
-  uint16_t* cols = nullptr;
   uint64_t src_off = ~0ull, elems = 0;
   bool valid = false;
   uint64_t last_use = 0;
@@ -91,7 +90,7 @@ void Destroy(Context* ctx) {
   if (!ctx->impl) return;
   InvalidateAll(ctx);
   for (auto& a : ctx->impl->acts) cudaFree(a.buf);
-  for (auto& e : ctx->impl->packs) { cudaFree(e.rows); cudaFree(e.cols); }
+  for (auto& e : ctx->impl->packs) cudaFree(e.rows);
   cudaFree(ctx->impl->split_a);
   cudaFree(ctx->impl->split_b);
   delete ctx->impl;
@@ -157,7 +156,7 @@ void PlanRange(Context* ctx, const Instruction* program, size_t begin, size_t en
   if (attn > 0) {
     size_t free_b = 0, total_b = 0;
     cudaMemGetInfo(&free_b, &total_b);
-    const uint64_t per_entry = attn * 4;   // two bf16 layouts
+    const uint64_t per_entry = attn * 2;   // bf16
     const uint64_t by_budget = std::max<uint64_t>(4, (total_b / 8) / per_entry);
     const size_t want = static_cast<size_t>(
         std::min<uint64_t>(std::max<uint64_t>(4, sources.size()), by_budget));
@@ -165,20 +164,17 @@ void PlanRange(Context* ctx, const Instruction* program, size_t begin, size_t en
       cudaDeviceSynchronize();
       const uint64_t cap = std::max(attn, impl->pack_capacity);
       if (attn > impl->pack_capacity) {
-        for (auto& e : impl->packs) { cudaFree(e.rows); cudaFree(e.cols); }
+        for (auto& e : impl->packs) cudaFree(e.rows);
         impl->packs.clear();
       }
       while (impl->packs.size() < want) {
         PackEntry e;
         void* pr = nullptr;
-        void* pc = nullptr;
-        if (cudaMalloc(&pr, cap * 2) != cudaSuccess || cudaMalloc(&pc, cap * 2) != cudaSuccess) {
-          cudaFree(pr);
+        if (cudaMalloc(&pr, cap * 2) != cudaSuccess) {
           cudaGetLastError();
           break;
         }
         e.rows = static_cast<uint16_t*>(pr);
-        e.cols = static_cast<uint16_t*>(pc);
         impl->packs.push_back(e);
       }
       impl->pack_capacity = cap;
@@ -521,7 +517,7 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
       if (!victim || e.last_use < victim->last_use) victim = &e;
     }
     if (!victim) return "tensor-core attention: no pack entry free";
-    k::PackHeads(src[r], victim->rows, victim->cols, static_cast<uint32_t>(op.B),
+    k::PackHeads(src[r], victim->rows, static_cast<uint32_t>(op.B),
                  static_cast<uint32_t>(op.S), static_cast<uint32_t>(op.H),
                  static_cast<uint32_t>(op.d), stream);
     ++*launches;
@@ -532,14 +528,12 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
     ent[r] = victim;
   }
   const uint64_t BH = op.B * op.H;
-  CUtensorMap mr[4], mh[4], mc[4];   // rows (box 128), rows (box 64), cols
+  CUtensorMap mr[4], mh[4];   // rows (box 128), rows (box 64)
   for (int r = 0; r < 4; ++r) {
     if (!used[r]) continue;
     if (!EncodeHeads(impl, &mr[r], ent[r]->rows, op.d, op.S, BH, 128) ||
         !EncodeHeads(impl, &mh[r], ent[r]->rows, op.d, op.S, BH, 64))
       return "tensor-core attention: cuTensorMapEncodeTiled refused a row layout";
-    if (!EncodeHeads(impl, &mc[r], ent[r]->cols, op.S, op.d, BH, static_cast<uint32_t>(op.d)))
-      return "tensor-core attention: cuTensorMapEncodeTiled refused a column layout";
   }
   k::AttnUmmaArgs a{};
   a.B = static_cast<uint32_t>(op.B); a.S = static_cast<uint32_t>(op.S);
@@ -552,7 +546,7 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
   cudaError_t e = cudaSuccess;
   if (fwd) {
     a.keep = op.keep;
-    e = k::AttnFwdUmma(mr[Q], mh[K], mc[V], a, stream);
+    e = k::AttnFwdUmma(mr[Q], mh[K], mh[V], a, stream);
     a.keep = nullptr;
   }
   if (dq) {
@@ -560,7 +554,7 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
       a.fwd_keep = op.fwd_keep;
       a.dout_f32 = op.dout;
     }
-    e = k::AttnDQUmma(mr[Q], mr[DO], mh[K], mh[V], mc[K], a, stream);
+    e = k::AttnDQUmma(mr[Q], mr[DO], mh[K], mh[V], a, stream);
     a.fwd_keep = nullptr;
     a.dout_f32 = nullptr;
   }
@@ -570,8 +564,8 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
     a.out2 = op.out2;
     a.shadow2 = op.shadow2;
   }
-  if (dk) e = k::AttnDKVUmma(both ? 2 : 1, mr[K], mr[V], mh[Q], mh[DO], mc[Q], both ? mc[DO] : mc[Q], a, stream);
-  if (dv) e = k::AttnDKVUmma(0, mr[K], mr[K], mh[Q], mh[Q], mc[DO], mc[DO], a, stream);
+  if (dk) e = k::AttnDKVUmma(both ? 2 : 1, mr[K], mr[V], mh[Q], mh[DO], a, stream);
+  if (dv) e = k::AttnDKVUmma(0, mr[K], mr[K], mh[Q], mh[DO], a, stream);
   if (both && e == cudaSuccess && did_second) *did_second = true;
   if (e != cudaSuccess) return std::string("tensor-core attention launch: ") + cudaGetErrorString(e);
   ++*launches;

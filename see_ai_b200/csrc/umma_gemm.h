@@ -92,10 +92,10 @@ struct AttentionOperands {
   // and reports through *did_second).
   float* out2 = nullptr;
   k::Shadow shadow2;   // optional bf16 copy of `out2`
-  // kAttnFwdTiled: where to keep a private bf16 copy of the output for the dQ of the same
+  // kAttnFwdTiled: where to keep a private f32 copy of the output for the dQ of the same
   // attention; kAttnDQTiled: that copy (one walk over the keys instead of two).
-  uint16_t* keep = nullptr;
-  const uint16_t* fwd_keep = nullptr;
+  float* keep = nullptr;
+  const float* fwd_keep = nullptr;
 };
 std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands& op,
                          cudaStream_t stream, int* launches, bool* did_second = nullptr);
