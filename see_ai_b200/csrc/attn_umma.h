@@ -32,11 +32,11 @@ struct AttnUmmaArgs {
   const float* dout_f32 = nullptr;
 };
 
-// f32 [B*S, H*d] (heads interleaved along the row) -> bf16 rows [B*H][S][d].
+// f32 [B*S, H*d] -> bf16, same row-major layout (the operand copy the kernels below read).
 void PackHeads(const float* x, uint16_t* rows, uint32_t B, uint32_t S, uint32_t H, uint32_t d, cudaStream_t s);
 
-// Maps over the packed rows: dims {d, S, B*H}, box {64, 128, 1} (a CTA's own 128 rows) or
-// {64, 64, 1} (`_half`: the 64 positions of one step); bf16, 128-byte swizzle.  d is 64 or 128.
+// Maps over that copy: dims {d, S, H, B}, box {64, 128, 1, 1} (a CTA's own 128 rows) or
+// {64, 64, 1, 1} (`_half`: the 64 positions of one step); bf16, 128-byte swizzle.  d is 64 or 128.
 // A `_half` tile serves both as the K-major operand of a product over the head dimension
 // and as the MN-major operand of a product over its 64 positions.
 cudaError_t AttnFwdUmma(const CUtensorMap& q, const CUtensorMap& k_half, const CUtensorMap& v_half,

@@ -421,6 +421,7 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
     PlanShadows(program, begin, std::min(end, program.size()));
     PlanBiasFusions(program, begin, std::min(end, program.size()));
     PlanActFusions(program, begin, std::min(end, program.size()));
+    PlanAttentionPacks(program, begin, std::min(end, program.size()));
   };
   plan_fusions();
   uint64_t partial_floats = 0;
@@ -846,6 +847,63 @@ void CudaBackend::PlanAttentionKeeps(std::span<const Instruction> program, size_
   for (int& slot : attn_keep_slot_)
     if (slot >= static_cast<int>(attn_keep_pool_.size())) slot = -1;
   attn_keep_written_.assign(attn_keep_pool_.size(), 0);
+}
+
+// After the fusions are planned: for every relaxed GEMM of the range that will run as one
+// tensor-core dispatch, where does its result finally land (its own output, the sum of an
+// absorbed add, the output of a folded low-rank term), and is that tensor read, before
+// anything overwrites it, by a relaxed tiled attention instruction as one of its operands?
+void CudaBackend::PlanAttentionPacks(std::span<const Instruction> program, size_t begin, size_t end) {
+  pack_plan_.assign(end > begin ? end - begin : 0, PackPlan{});
+  if (coherence_ == Coherence::kStrict || !relaxed_allowed_ || !epilogue_fusion_) return;
+  for (size_t i = begin; i < end; ++i) {
+    const Instruction& g = program[i];
+    const bool gemm = g.opcode == kGemmNN || g.opcode == kGemmNT || g.opcode == kGemmNNQ8 || g.opcode == kGemmNTQ8 ||
+                      g.opcode == kGemmNNBF16 || g.opcode == kGemmNTBF16;
+    if (!gemm || !(g.flags & kFlagRelaxed)) continue;
+    const size_t ri = i - begin;
+    if (ri < act_fusion_.size() && act_fusion_[ri].mode != 0) continue;   // its stored value is not the consumer's operand
+    if (ri < lora_skip_.size() && lora_skip_[ri] != 0) continue;
+    uint64_t out = g.in[2];
+    size_t last = i;   // the last instruction this dispatch stands for
+    if (ri < add_fusion_.size() && add_fusion_[ri].fuse) {
+      out = add_fusion_[ri].out_ref;
+      last = std::max(last, begin + add_fusion_[ri].add_index);
+    }
+    if (ri < lora_fold_.size() && lora_fold_[ri].fuse) {
+      out = lora_fold_[ri].out_ref;
+      for (size_t j = i + 1; j < end; ++j)   // the folded expand product: the instruction that names `out` as its output
+        if (program[j].in[2] == out && j - begin < lora_skip_.size() && lora_skip_[j - begin] == 1) last = std::max(last, j);
+    }
+    if (RefSpace(out) != kArena) continue;
+    const uint64_t o_lo = RefOffset(out), o_hi = o_lo + g.out[0] * g.out[1] * 4;
+    for (size_t j = last + 1; j < end; ++j) {
+      const Instruction& at = program[j];
+      const bool fwd = at.opcode == kAttnFwdTiled;
+      const bool bwd = at.opcode == kAttnDQTiled || at.opcode == kAttnDKTiled || at.opcode == kAttnDVTiled;
+      if ((fwd || bwd) && (at.flags & kFlagRelaxed)) {
+        bool reads = false;
+        for (int r = 0; r < (fwd ? 3 : 4); ++r) reads = reads || at.in[r] == out;
+        if (reads) {
+          AttnGeom geo;
+          if (fwd) { geo.B = Hi32(at.out[1]); geo.S = Lo32(at.out[1]); geo.H = Hi32(at.out[2]); geo.d = Lo32(at.out[2]); }
+          else geo = UnpackAttnGeom(at.out[2]);
+          if (geo.B * geo.S == g.out[0] && geo.H * geo.d == g.out[1] && (geo.d == 64 || geo.d == 128) &&
+              geo.S % 8 == 0)
+            pack_plan_[ri] = PackPlan{out, static_cast<uint32_t>(geo.S), static_cast<uint32_t>(geo.H),
+                                      static_cast<uint32_t>(geo.d)};
+          break;
+        }
+      }
+      Extents ex;
+      if (!DescribeInstruction(at, arena_bytes_, rodata_bytes_, source_bytes_, &ex).empty()) break;
+      bool overwritten = false;
+      for (size_t e = 0; e < ex.count; ++e)
+        if (ex.e[e].write && ex.e[e].space == kArena && ex.e[e].off < o_hi && o_lo < ex.e[e].off + ex.e[e].bytes)
+          overwritten = true;
+      if (overwritten) break;
+    }
+  }
 }
 
 void CudaBackend::PlanActFusions(std::span<const Instruction> program, size_t begin, size_t end) {
@@ -1569,6 +1627,10 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   if (shadow_written_)   // after the instruction's own writes have invalidated the range
     umma::CommitShadow(&umma_->ctx, cur_shadow_.dst, cur_plan_.a_off, cur_plan_.scale_off,
                        cur_plan_.M, cur_plan_.K);
+  if (pending_pack_.rows) {
+    umma::CommitPack(&umma_->ctx, pending_pack_.rows, pending_pack_.off, pending_pack_.elems);
+    pending_pack_ = PendingPack{};
+  }
   if (auto e = cudaPeekAtLastError(); e != cudaSuccess) {
     cudaGetLastError();
     return std::unexpected(CudaErr(e, OpName(ins.opcode)));
@@ -1661,6 +1723,12 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
         a.addend_after_bias = true;
       }
     }
+    uint16_t* pack_rows = nullptr;
+    if (range_index_ < pack_plan_.size() && pack_plan_[range_index_].S != 0 && !af &&
+        RefOffset(pack_plan_[range_index_].out_ref) == static_cast<uint64_t>(reinterpret_cast<uint8_t*>(a.C) - d_arena_)) {
+      pack_rows = umma::ReservePack(&umma_->ctx, a.M * a.N);
+      if (pack_rows) a.pack_dst = pack_rows;
+    }
     int launches = 0;
     const std::string err = umma::TryGemm(&umma_->ctx, a, RefSpace(ins.in[1]) == kRodata ? 1 : 2,
                                           RefOffset(ins.in[1]), RefOffset(ins.in[0]),
@@ -1690,8 +1758,11 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
         umma::InvalidateRange(&umma_->ctx, RefOffset(lf->out_ref), a.M * a.N * 4);
         for (int e = 0; e < lf->dead_count; ++e) pending_elided_.push_back({lf->dead[e][0], lf->dead[e][1]});
       }
+      if (pack_rows)   // published once this instruction's own write extents have dropped older copies
+        pending_pack_ = PendingPack{pack_rows, static_cast<uint64_t>(reinterpret_cast<uint8_t*>(a.C) - d_arena_), a.M * a.N};
       return {};
     }
+    a.pack_dst = nullptr;
     if (!err.empty()) return std::unexpected("cuda: " + err);
     if (lf) return std::unexpected("cuda: low-rank fold: the tensor-core path refused a product it was planned on");
     // launches == 0: the shape is outside the tensor-core kernel's domain.

@@ -354,6 +354,19 @@ class CudaBackend {
   std::vector<uint8_t> attn_keep_written_;
   uint64_t attn_keep_elems_ = 0;
   void PlanAttentionKeeps(std::span<const Instruction> program, size_t begin, size_t end);
+  // A tensor-core GEMM whose result a relaxed tiled attention instruction reads as q, k, v or dO
+  // writes that operand's packed bf16 rows in its own epilogue (per instruction of the range:
+  // the attention geometry, S == 0 when not wanted).
+  struct PackPlan {
+    uint64_t out_ref = kNullRef;
+    uint32_t S = 0, H = 0, d = 0;
+  };
+  std::vector<PackPlan> pack_plan_;
+  struct PendingPack {
+    uint16_t* rows = nullptr;
+    uint64_t off = 0, elems = 0;
+  } pending_pack_;
+  void PlanAttentionPacks(std::span<const Instruction> program, size_t begin, size_t end);
   std::vector<ShadowPlan> attn_dv_shadow_;   // the dV instruction's copy plan, made by the pair's kernel
   int64_t skip_attn_dv_at_ = -1;
   int64_t skip_add_at_ = -1;            // the absorbed kAddEW (its output IS written, by the product)

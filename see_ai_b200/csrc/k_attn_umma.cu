@@ -6,8 +6,10 @@
 // writes O and the stats row {score max, 1/denominator, 0, start}; dQ writes
 // delta into the stats row and dQ; dK and dV read the stats row.
 //
-// Blackwell-native: per (sequence, head) the operands are packed once to bf16
-// ([S][d]), tiles arrive by TMA (128-byte swizzle), every product
+// Blackwell-native: the operands are held once as bf16 in the tensors' own
+// row-major layout [B*S, H*d] (written by the kernel that produces the tensor,
+// or converted once), a (sequence, head) tile arrives by one 4-D TMA load
+// (128-byte swizzle), every product
 // (Q K^T, P V, dO V^T, dS K, dS^T Q, P^T dO) is a tcgen05.mma with its
 // accumulator in tensor memory, and the softmax / softmax-backward arithmetic
 // runs in f32 registers on values read with tcgen05.ld; P and dS go back to
@@ -39,11 +41,11 @@ constexpr uint32_t kTile = 128;          // query rows / key rows per tile
 constexpr uint32_t kSubTileBytes = 128 * 64 * 2;   // [128 rows][64 bf16], swizzled
 constexpr uint32_t kPBytes = 2 * kSubTileBytes;    // P / dS tile: 128 x 128 bf16
 
-// ---- packing: f32 [B*S, H*d] -> bf16 [B*H][S][d] ----------------------------------------
-// One block packs 64 positions of one (sequence, head): 16-byte loads of the f32 rows,
-// 8-byte stores of the bf16 rows.  (Every operand of the kernels below is taken from this
-// one layout: as a K-major tile where the head dimension is the reduction index, as an
-// MN-major tile where the positions are.)
+// ---- operand copies: f32 [B*S, H*d] -> bf16, same layout --------------------------------
+// (Every operand tile of the kernels below is cut out of this copy by a 4-D tensor map
+// {d, S, H, B}: 64 head-dimension elements x R positions of one head of one sequence land
+// as [R][128 bytes] — the K-major tile of a product over the head dimension, and through an
+// MN-major descriptor the operand of a product over the positions.)
 __device__ __forceinline__ uint32_t Bf16Bits(float f) {   // round to nearest even; NaN stays NaN
   uint32_t u = __float_as_uint(f);
   if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (u >> 16) | 0x0040u;
@@ -51,22 +53,12 @@ __device__ __forceinline__ uint32_t Bf16Bits(float f) {   // round to nearest ev
   return u >> 16;
 }
 
-constexpr uint32_t kPackPos = 64;
-
-template <int D>
 __global__ void __launch_bounds__(256)
-PackHeadsKernel(const float* __restrict__ x, uint16_t* __restrict__ rows, uint32_t S, uint32_t H) {
-  const uint32_t bh = blockIdx.y, b = bh / H, h = bh % H;
-  const uint32_t s0 = blockIdx.x * kPackPos;
-  const size_t HD = static_cast<size_t>(H) * D;
-  constexpr uint32_t kVecPerRow = D / 4;
-  for (uint32_t idx = threadIdx.x; idx < kPackPos * kVecPerRow; idx += 256) {
-    const uint32_t i = idx / kVecPerRow, c = (idx % kVecPerRow) * 4;
-    const uint32_t s = s0 + i;
-    if (s >= S) continue;
-    const float4 f = *reinterpret_cast<const float4*>(
-        x + (static_cast<size_t>(b) * S + s) * HD + static_cast<size_t>(h) * D + c);
-    *reinterpret_cast<uint2*>(rows + (static_cast<size_t>(bh) * S + s) * D + c) =
+PackRowsKernel(const float* __restrict__ x, uint16_t* __restrict__ rows, size_t quads) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t q = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; q < quads; q += stride) {
+    const float4 f = reinterpret_cast<const float4*>(x)[q];
+    reinterpret_cast<uint2*>(rows)[q] =
         make_uint2(Bf16Bits(f.x) | (Bf16Bits(f.y) << 16), Bf16Bits(f.z) | (Bf16Bits(f.w) << 16));
   }
 }
@@ -89,15 +81,15 @@ __device__ __forceinline__ float Exp2Approx(float x) {
   return y;
 }
 
-// Loads [R rows][D] of a row-layout tensor ({d, S, BH} map with box {64, R}) as D/64
-// sub-tiles of R * 128 bytes.
+// Loads [R positions][D] of head h of sequence b ({d, S, H, B} map with box {64, R, 1, 1}) as
+// D/64 sub-tiles of R * 128 bytes; positions past the end of the sequence arrive as zeros.
 template <int D, int R>
 __device__ __forceinline__ void LoadRows(uint8_t* dst, const CUtensorMap* map, uint64_t* bar,
-                                         uint32_t row0, uint32_t bh) {
+                                         uint32_t row0, uint32_t h, uint32_t b) {
 #pragma unroll
   for (int kb = 0; kb < D / 64; ++kb)
-    TmaLoad3D(dst + kb * (R * 128), map, bar, kb * 64, static_cast<int32_t>(row0),
-              static_cast<int32_t>(bh));
+    TmaLoad4D(dst + kb * (R * 128), map, bar, kb * 64, static_cast<int32_t>(row0), static_cast<int32_t>(h),
+              static_cast<int32_t>(b));
 }
 // acc[128 x NB] = A[128 rows][D] . B[NB rows][D]^T, both row tiles in shared memory.
 template <int D, int NB>
@@ -242,12 +234,12 @@ AttnFwdUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
   auto issue_a = [&](uint32_t t) {
     MbarExpectTx(&ctl->bar_a, kKBytes + (t == 0 ? kQBytes : 0));
-    if (t == 0) LoadRows<D, 128>(q_s, &map_q, &ctl->bar_a, it * kTile, bh);
-    LoadRows<D, 64>(k_s, &map_k, &ctl->bar_a, t * kHalf, bh);
+    if (t == 0) LoadRows<D, 128>(q_s, &map_q, &ctl->bar_a, it * kTile, h, b);
+    LoadRows<D, 64>(k_s, &map_k, &ctl->bar_a, t * kHalf, h, b);
   };
   auto issue_b = [&](uint32_t t) {
     MbarExpectTx(&ctl->bar_b, kVBytes);
-    LoadRows<D, 64>(v_s, &map_v, &ctl->bar_b, t * kHalf, bh);   // V_h as rows: the MN-major operand of P V
+    LoadRows<D, 64>(v_s, &map_v, &ctl->bar_b, t * kHalf, h, b);   // V_h as rows: the MN-major operand of P V
   };
 
   const uint32_t row = it * kTile + tid;                   // this thread's query row
@@ -415,11 +407,11 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   auto issue_a = [&](uint32_t t) {
     MbarExpectTx(&ctl->bar_a, 2 * kHalfRows + (t == 0 ? 2 * kFull : 0));
     if (t == 0) {
-      LoadRows<D, 128>(q_s, &map_q, &ctl->bar_a, it * kTile, bh);
-      LoadRows<D, 128>(do_s, &map_do, &ctl->bar_a, it * kTile, bh);
+      LoadRows<D, 128>(q_s, &map_q, &ctl->bar_a, it * kTile, h, b);
+      LoadRows<D, 128>(do_s, &map_do, &ctl->bar_a, it * kTile, h, b);
     }
-    LoadRows<D, 64>(k_s + (t & 1) * kHalfRows, &map_k, &ctl->bar_a, (t % n_h) * kHalf, bh);
-    LoadRows<D, 64>(v_s, &map_v, &ctl->bar_a, (t % n_h) * kHalf, bh);
+    LoadRows<D, 64>(k_s + (t & 1) * kHalfRows, &map_k, &ctl->bar_a, (t % n_h) * kHalf, h, b);
+    LoadRows<D, 64>(v_s, &map_v, &ctl->bar_a, (t % n_h) * kHalf, h, b);
   };
 
   const uint32_t row = it * kTile + tid;
@@ -579,11 +571,11 @@ AttnDKVUmmaKernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     constexpr uint32_t kPer = 2 * kHalfRows, kOnce = (kWantDK ? 2 : 1) * kFull;
     MbarExpectTx(&ctl->bar_a, kPer + (t == 0 ? kOnce : 0));
     if (t == 0) {
-      LoadRows<D, 128>(k_s, &map_k, &ctl->bar_a, jt * kTile, bh);
-      if (kWantDK) LoadRows<D, 128>(v_s, &map_v, &ctl->bar_a, jt * kTile, bh);
+      LoadRows<D, 128>(k_s, &map_k, &ctl->bar_a, jt * kTile, h, b);
+      if (kWantDK) LoadRows<D, 128>(v_s, &map_v, &ctl->bar_a, jt * kTile, h, b);
     }
-    LoadRows<D, 64>(q_s + (t & 1) * kHalfRows, &map_q, &ctl->bar_a, (h0 + t) * kHalf, bh);
-    LoadRows<D, 64>(do_s + (t & 1) * kHalfRows, &map_do, &ctl->bar_a, (h0 + t) * kHalf, bh);
+    LoadRows<D, 64>(q_s + (t & 1) * kHalfRows, &map_q, &ctl->bar_a, (h0 + t) * kHalf, h, b);
+    LoadRows<D, 64>(do_s + (t & 1) * kHalfRows, &map_do, &ctl->bar_a, (h0 + t) * kHalf, h, b);
   };
 
   const uint32_t key = jt * kTile + tid;                    // this thread's key row
@@ -703,9 +695,9 @@ static cudaError_t Configure(Kernel kernel, size_t smem) {
 }
 
 void PackHeads(const float* x, uint16_t* rows, uint32_t B, uint32_t S, uint32_t H, uint32_t d, cudaStream_t s) {
-  const dim3 grid((S + kPackPos - 1) / kPackPos, B * H);
-  if (d == 64) PackHeadsKernel<64><<<grid, 256, 0, s>>>(x, rows, S, H);
-  else PackHeadsKernel<128><<<grid, 256, 0, s>>>(x, rows, S, H);
+  const size_t quads = static_cast<size_t>(B) * S * H * d / 4;
+  const size_t blocks = (quads + 255) / 256;
+  PackRowsKernel<<<static_cast<unsigned>(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, s>>>(x, rows, quads);
 }
 
 cudaError_t AttnFwdUmma(const CUtensorMap& q, const CUtensorMap& k_half, const CUtensorMap& v_half,

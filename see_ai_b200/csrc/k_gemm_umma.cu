@@ -70,6 +70,12 @@ __device__ __forceinline__ void EpilogueStore(const UmmaEpilogue& ep, size_t at,
     v = make_float4(ApplyAct(v.x, ep.act), ApplyAct(v.y, ep.act), ApplyAct(v.z, ep.act),
                     ApplyAct(v.w, ep.act));
   if (ep.store_c) *reinterpret_cast<float4*>(ep.C + at) = v;
+  if (ep.pack_dst) {   // the bf16 operand copy a tiled attention instruction reads this tensor through
+    uint32_t lo, hi;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(v.y), "f"(v.x));
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(v.w), "f"(v.z));
+    *reinterpret_cast<uint2*>(ep.pack_dst + at) = make_uint2(lo, hi);
+  }
   if (ep.fuse_mode != kFuseNone) {
     float4 g;
     if (ep.fuse_mode == kFuseActFwd) {

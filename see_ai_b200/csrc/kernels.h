@@ -282,6 +282,10 @@ struct GemmArgs {
   const float* fuse_x = nullptr;
   uint16_t* fuse_shadow = nullptr;
   const float* fuse_shadow_scale = nullptr;
+  // Tensor-core path only: the result (what goes to C) also leaves as bf16 in the same
+  // [M, N] layout: the operand copy a tiled attention instruction reads it through, which
+  // saves that instruction's conversion pass.
+  uint16_t* pack_dst = nullptr;
   bool store_c = true;
   bool addend_after_bias = false;   // tensor-core path: v = addend + (product + bias)
   // Tensor-core path only: a low-rank term appended to the reduction (see

@@ -65,6 +65,15 @@ __device__ __forceinline__ void TmaLoad3D(void* smem_dst, const CUtensorMap* map
       "r"(y), "r"(z)
       : "memory");
 }
+__device__ __forceinline__ void TmaLoad4D(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                          int32_t x, int32_t y, int32_t z, int32_t w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(SmemAddr(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(SmemAddr(bar)), "r"(x),
+      "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
 // Tile store shared -> global; rows/columns outside the tensor are clipped.
 __device__ __forceinline__ void TmaStore2D(const CUtensorMap* map, const void* smem_src, int32_t x,
                                            int32_t y) {

@@ -38,8 +38,9 @@ struct ActCopy {   // a bf16 copy of an arena activation [M, K]
 
 constexpr int kActSlots = 8;
 
-// The packed bf16 copy of one attention operand (a Q, K, V or dO activation):
-// rows [B*H][S][d], the one layout the kernels read.  Made
+// The bf16 copy of one attention operand (a Q, K, V or dO activation) in the
+// tensor's own row-major layout [B*S, H*d], which the kernels' 4-D tensor maps cut
+// (sequence, head) tiles out of.  Made
 // once, by one kernel, the first time any attention instruction of the range
 // reads the operand; the forward's copies serve the backward of the same step
 // unless an instruction overwrote the source in between.
@@ -302,6 +303,7 @@ std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_
   ep.fuse_x = a.fuse_x;
   ep.shadow_dst = a.fuse_shadow;
   ep.shadow_k_scale = a.fuse_shadow_scale;
+  ep.pack_dst = a.pack_dst;
   ep.store_c = a.store_c ? 1 : 0;
   ep.addend_last = a.addend_after_bias ? 1 : 0;
   ep.aux_k_blocks = has_aux ? a.aux_k / 64 : 0;
@@ -465,13 +467,15 @@ void CommitShadow(Context* ctx, uint16_t* buf, uint64_t a_off, uint64_t a_scale_
 
 namespace {
 
-bool EncodeHeads(Impl* impl, CUtensorMap* map, const void* base, uint64_t inner, uint64_t mid,
-                 uint64_t outer, uint32_t box_mid) {
-  const cuuint64_t dims[3] = {inner, mid, outer};
-  const cuuint64_t strides[2] = {inner * 2, inner * mid * 2};
-  const cuuint32_t box[3] = {64, box_mid, 1};
-  const cuuint32_t elem[3] = {1, 1, 1};
-  return impl->encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims,
+// {d, S, H, B} over a row-major bf16 [B*S, H*d] tensor: a box is 64 head-dimension elements
+// of `box_rows` positions of one head of one sequence.
+bool EncodeHeads(Impl* impl, CUtensorMap* map, const void* base, uint64_t d, uint64_t S, uint64_t H, uint64_t B,
+                 uint32_t box_rows) {
+  const cuuint64_t dims[4] = {d, S, H, B};
+  const cuuint64_t strides[3] = {H * d * 2, d * 2, S * H * d * 2};
+  const cuuint32_t box[4] = {64, box_rows, 1, 1};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  return impl->encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims,
                       strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -527,12 +531,11 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
     victim->last_use = now;
     ent[r] = victim;
   }
-  const uint64_t BH = op.B * op.H;
   CUtensorMap mr[4], mh[4];   // rows (box 128), rows (box 64)
   for (int r = 0; r < 4; ++r) {
     if (!used[r]) continue;
-    if (!EncodeHeads(impl, &mr[r], ent[r]->rows, op.d, op.S, BH, 128) ||
-        !EncodeHeads(impl, &mh[r], ent[r]->rows, op.d, op.S, BH, 64))
+    if (!EncodeHeads(impl, &mr[r], ent[r]->rows, op.d, op.S, op.H, op.B, 128) ||
+        !EncodeHeads(impl, &mh[r], ent[r]->rows, op.d, op.S, op.H, op.B, 64))
       return "tensor-core attention: cuTensorMapEncodeTiled refused a row layout";
   }
   k::AttnUmmaArgs a{};
@@ -570,6 +573,35 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
   if (e != cudaSuccess) return std::string("tensor-core attention launch: ") + cudaGetErrorString(e);
   ++*launches;
   return {};
+}
+
+uint16_t* ReservePack(Context* ctx, uint64_t elems) {
+  Impl* impl = ctx->impl;
+  if (!impl || elems > impl->pack_capacity) return nullptr;
+  PackEntry* victim = nullptr;
+  for (auto& e : impl->packs) {
+    if (!e.valid) { victim = &e; break; }
+    if (!victim || e.last_use < victim->last_use) victim = &e;
+  }
+  if (!victim) return nullptr;
+  victim->valid = false;
+  victim->last_use = ++impl->tick;
+  return victim->rows;
+}
+
+void CommitPack(Context* ctx, uint16_t* rows, uint64_t src_off, uint64_t elems) {
+  Impl* impl = ctx->impl;
+  if (!impl || !rows) return;
+  for (auto& e : impl->packs) {
+    if (e.rows == rows) {
+      e.valid = true;
+      e.src_off = src_off;
+      e.elems = elems;
+      e.last_use = ++impl->tick;
+    } else if (e.valid && e.src_off == src_off) {
+      e.valid = false;   // an older copy of the same tensor
+    }
+  }
 }
 
 void SetProfileEvents(Context* ctx, cudaEvent_t before, cudaEvent_t after) {

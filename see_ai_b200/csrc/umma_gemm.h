@@ -97,6 +97,12 @@ struct AttentionOperands {
   float* keep = nullptr;
   const float* fwd_keep = nullptr;
 };
+// A producer (a tensor-core GEMM epilogue) can write an attention operand's packed rows
+// itself: ReservePack hands out an entry's buffer (null when none fits `elems`), CommitPack
+// publishes it under the tensor's arena offset once the producing instruction's own write
+// extents have gone through InvalidateRange; TryAttention then finds it and packs nothing.
+uint16_t* ReservePack(Context* ctx, uint64_t elems);
+void CommitPack(Context* ctx, uint16_t* rows, uint64_t src_off, uint64_t elems);
 std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands& op,
                          cudaStream_t stream, int* launches, bool* did_second = nullptr);
 

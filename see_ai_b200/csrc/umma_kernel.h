@@ -46,6 +46,8 @@ struct UmmaEpilogue {
   // B' the three-way bf16 splits of f32 factors (LoraSplit* in kernels.h) the
   // added term is the f32 product t . b to about 2^-23 of |t| |b|.
   uint32_t aux_k_blocks = 0;
+  // The stored value also as bf16 [M, N] (GemmArgs::pack_dst).
+  uint16_t* pack_dst = nullptr;
 };
 
 size_t UmmaSmemBytes();
