@@ -25,11 +25,11 @@ struct AttnUmmaArgs {
   // Forward: a second, private copy of O (f32 [B*S, H*d]) kept for the dQ of the same
   // attention (the arena's O is long overwritten by then — its slot usually holds dO).
   float* keep = nullptr;
-  // dQ: that copy, and dO in f32.  delta_i = sum_j P_ij dP_ij equals dO_i . O_i (with dO
-  // rounded to bf16 as the tensor core sees it), so the kernel takes it from one row of
+  // dQ: that copy, and dO's bf16 operand copy ([B*S, H*d], what the tensor core sees).
+  // delta_i = sum_j P_ij dP_ij equals dO_i . O_i, so the kernel takes it from one row of
   // each and walks the keys once instead of twice.
   const float* fwd_keep = nullptr;
-  const float* dout_f32 = nullptr;
+  const uint16_t* dout_bf16 = nullptr;
 };
 
 // f32 [B*S, H*d] -> bf16, same row-major layout (the operand copy the kernels below read).

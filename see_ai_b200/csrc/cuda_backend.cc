@@ -526,6 +526,9 @@ void CudaBackend::EndRange() {
   skip_act_at_ = -1;
   elided_.clear();
   pending_elided_.clear();
+  deferred_elided_.clear();
+  pack_plan_.clear();
+  pending_pack_ = PendingPack{};
   shadow_plan_.clear();
   adam_group_of_.clear();
   adam_groups_.clear();
@@ -758,7 +761,25 @@ struct DeadQuery {
   uint64_t lo, hi;
   bool allow_consumers;
   uint64_t key_scale, M, K;
+  // Reads of the whole tensor by relaxed tiled attention instructions of the range do not
+  // count: they take the bf16 copy its producer wrote.
+  bool allow_attention = false;
 };
+
+// A relaxed tiled attention instruction whose geometry the tensor-core kernels take, reading
+// the tensor at `off` as one of its operands.
+static bool IsAttentionCopyReader(const Instruction& ins, uint64_t off) {
+  const bool fwd = ins.opcode == kAttnFwdTiled;
+  const bool bwd = ins.opcode == kAttnDQTiled || ins.opcode == kAttnDKTiled || ins.opcode == kAttnDVTiled;
+  if (!(fwd || bwd) || !(ins.flags & kFlagRelaxed)) return false;
+  AttnGeom g;
+  if (fwd) { g.B = Hi32(ins.out[1]); g.S = Lo32(ins.out[1]); g.H = Hi32(ins.out[2]); g.d = Lo32(ins.out[2]); }
+  else g = UnpackAttnGeom(ins.out[2]);
+  if ((g.d != 64 && g.d != 128) || g.S % 8 != 0 || g.S < 16 || g.B * g.H > 65535 || g.B * g.H == 0) return false;
+  for (int r = 0; r < (fwd ? 3 : 4); ++r)
+    if (RefSpace(ins.in[r]) == kArena && RefOffset(ins.in[r]) == off) return true;
+  return false;
+}
 static bool DeadFrom(std::span<const Instruction> program, const std::vector<Extents>& ext, size_t ext_base,
                      size_t range_end, size_t start, bool wrap, size_t wrap_stop, const DeadQuery& q) {
   using Interval = std::pair<uint64_t, uint64_t>;
@@ -779,7 +800,9 @@ static bool DeadFrom(std::span<const Instruction> program, const std::vector<Ext
                             IsRelaxedFrozenGemm(ins) && RefOffset(ins.in[0]) == q.lo && elo == q.lo &&
                             ehi == q.hi && ins.out[0] == q.M && ins.out[2] == q.K &&
                             GemmScaleKey(ins) == q.key_scale;
-      if (!consumer) return -1;
+      const bool copy_reader = q.allow_attention && in_range && !written && !e.e[x].write && elo == q.lo &&
+                               ehi == q.hi && IsAttentionCopyReader(ins, q.lo);
+      if (!consumer && !copy_reader) return -1;
     }
     for (size_t x = 0; x < e.count; ++x) {
       if (e.e[x].space != kArena || !e.e[x].write) continue;
@@ -856,6 +879,18 @@ void CudaBackend::PlanAttentionKeeps(std::span<const Instruction> program, size_
 void CudaBackend::PlanAttentionPacks(std::span<const Instruction> program, size_t begin, size_t end) {
   pack_plan_.assign(end > begin ? end - begin : 0, PackPlan{});
   if (coherence_ == Coherence::kStrict || !relaxed_allowed_ || !epilogue_fusion_) return;
+  // Liveness of the f32 forms, as PlanActFusions decides it: on the whole program under the step-program promise.
+  const bool whole = step_program_ != nullptr && program.data() == step_program_;
+  const size_t ext_base = whole ? 0 : begin, ext_end = whole ? program.size() : end;
+  std::vector<Extents> ext(ext_end - ext_base);
+  bool have_ext = true;
+  for (size_t i = ext_base; i < ext_end && have_ext; ++i)
+    have_ext = DescribeInstruction(program[i], arena_bytes_, rodata_bytes_, source_bytes_, &ext[i - ext_base]).empty();
+  auto unobserved = [&](uint64_t lo, uint64_t hi) {
+    for (const auto& [off, bytes] : observed_)
+      if (lo < off + bytes && off < hi) return false;
+    return !(gather_ranks_ > 1 && lo < gather_off_ + gather_bytes_ && gather_off_ < hi);
+  };
   for (size_t i = begin; i < end; ++i) {
     const Instruction& g = program[i];
     const bool gemm = g.opcode == kGemmNN || g.opcode == kGemmNT || g.opcode == kGemmNNQ8 || g.opcode == kGemmNTQ8 ||
@@ -872,8 +907,10 @@ void CudaBackend::PlanAttentionPacks(std::span<const Instruction> program, size_
     }
     if (ri < lora_fold_.size() && lora_fold_[ri].fuse) {
       out = lora_fold_[ri].out_ref;
-      for (size_t j = i + 1; j < end; ++j)   // the folded expand product: the instruction that names `out` as its output
-        if (program[j].in[2] == out && j - begin < lora_skip_.size() && lora_skip_[j - begin] == 1) last = std::max(last, j);
+      // The instructions this dispatch stands for follow it directly (the down product, the expand
+      // product, an absorbed add): the last of them is the last skipped one before anything else runs.
+      for (size_t j = i + 1; j < end && j - begin < lora_skip_.size() && lora_skip_[j - begin] != 0; ++j)
+        last = std::max(last, j);
     }
     if (RefSpace(out) != kArena) continue;
     const uint64_t o_lo = RefOffset(out), o_hi = o_lo + g.out[0] * g.out[1] * 4;
@@ -888,10 +925,21 @@ void CudaBackend::PlanAttentionPacks(std::span<const Instruction> program, size_
           AttnGeom geo;
           if (fwd) { geo.B = Hi32(at.out[1]); geo.S = Lo32(at.out[1]); geo.H = Hi32(at.out[2]); geo.d = Lo32(at.out[2]); }
           else geo = UnpackAttnGeom(at.out[2]);
-          if (geo.B * geo.S == g.out[0] && geo.H * geo.d == g.out[1] && (geo.d == 64 || geo.d == 128) &&
-              geo.S % 8 == 0)
+          if (geo.B * geo.S == g.out[0] && geo.H * geo.d == g.out[1] && IsAttentionCopyReader(at, o_lo)) {
             pack_plan_[ri] = PackPlan{out, static_cast<uint32_t>(geo.S), static_cast<uint32_t>(geo.H),
-                                      static_cast<uint32_t>(geo.d)};
+                                      static_cast<uint32_t>(geo.d), false, last - begin};
+            // Is the f32 form read by anything else before it is written again?
+            DeadQuery q{o_lo, o_hi, false, 0, 0, 0, true};
+            if (have_ext) {
+              const bool wrap = whole && unobserved(o_lo, o_hi);
+              if (whole && !wrap) {
+                std::vector<Extents> in_range(ext.begin() + static_cast<long>(begin), ext.begin() + static_cast<long>(end));
+                pack_plan_[ri].copy_only = DeadFrom(program, in_range, begin, end, last + 1, false, 0, q);
+              } else {
+                pack_plan_[ri].copy_only = DeadFrom(program, ext, ext_base, end, last + 1, wrap, i, q);
+              }
+            }
+          }
           break;
         }
       }
@@ -1563,7 +1611,9 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
                           umma::TouchActCopy(&umma_->ctx, e.off,
                                              ~0ull,
                                              ins.out[0], ins.out[2]);
-      if (!gemm_a)
+      const bool attn_copy = !e.write && IsAttentionCopyReader(ins, e.off) && relaxed_allowed_ &&
+                             umma::TouchPack(&umma_->ctx, e.off, e.bytes / 4);
+      if (!gemm_a && !attn_copy)
         return std::unexpected(std::string("cuda: ") + OpName(ins.opcode) +
                                " reads an activation whose f32 form an epilogue fusion left unwritten");
     }
@@ -1630,6 +1680,14 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   if (pending_pack_.rows) {
     umma::CommitPack(&umma_->ctx, pending_pack_.rows, pending_pack_.off, pending_pack_.elems);
     pending_pack_ = PendingPack{};
+  }
+  for (size_t i = 0; i < deferred_elided_.size();) {   // (range_index_ has moved past this instruction)
+    if (deferred_elided_[i].after + 1 == range_index_) {
+      elided_.push_back({deferred_elided_[i].lo, deferred_elided_[i].hi});
+      deferred_elided_.erase(deferred_elided_.begin() + static_cast<long>(i));
+    } else {
+      ++i;
+    }
   }
   if (auto e = cudaPeekAtLastError(); e != cudaSuccess) {
     cudaGetLastError();
@@ -1727,7 +1785,10 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
     if (range_index_ < pack_plan_.size() && pack_plan_[range_index_].S != 0 && !af &&
         RefOffset(pack_plan_[range_index_].out_ref) == static_cast<uint64_t>(reinterpret_cast<uint8_t*>(a.C) - d_arena_)) {
       pack_rows = umma::ReservePack(&umma_->ctx, a.M * a.N);
-      if (pack_rows) a.pack_dst = pack_rows;
+      if (pack_rows) {
+        a.pack_dst = pack_rows;
+        if (pack_plan_[range_index_].copy_only) a.store_c = false;
+      }
     }
     int launches = 0;
     const std::string err = umma::TryGemm(&umma_->ctx, a, RefSpace(ins.in[1]) == kRodata ? 1 : 2,
@@ -1758,8 +1819,11 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
         umma::InvalidateRange(&umma_->ctx, RefOffset(lf->out_ref), a.M * a.N * 4);
         for (int e = 0; e < lf->dead_count; ++e) pending_elided_.push_back({lf->dead[e][0], lf->dead[e][1]});
       }
-      if (pack_rows)   // published once this instruction's own write extents have dropped older copies
-        pending_pack_ = PendingPack{pack_rows, static_cast<uint64_t>(reinterpret_cast<uint8_t*>(a.C) - d_arena_), a.M * a.N};
+      if (pack_rows) {   // published once this instruction's own write extents have dropped older copies
+        const uint64_t c_off = static_cast<uint64_t>(reinterpret_cast<uint8_t*>(a.C) - d_arena_);
+        pending_pack_ = PendingPack{pack_rows, c_off, a.M * a.N};
+        if (!a.store_c) deferred_elided_.push_back({pack_plan_[range_index_].last, c_off, c_off + a.M * a.N * 4});
+      }
       return {};
     }
     a.pack_dst = nullptr;

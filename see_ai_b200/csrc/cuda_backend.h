@@ -360,7 +360,15 @@ class CudaBackend {
   struct PackPlan {
     uint64_t out_ref = kNullRef;
     uint32_t S = 0, H = 0, d = 0;
+    // Nothing but attention instructions of this range (which take the copy) reads the
+    // tensor's f32 form before it is written again: the epilogue stores the copy alone.
+    bool copy_only = false;
+    size_t last = 0;   // range index of the last instruction the dispatch stands for
   };
+  // Ranges whose f32 form a dispatch left unwritten, recorded as stale once the instruction
+  // at the given range index (the last one the dispatch stood for) has passed.
+  struct DeferredElision { size_t after; uint64_t lo, hi; };
+  std::vector<DeferredElision> deferred_elided_;
   std::vector<PackPlan> pack_plan_;
   struct PendingPack {
     uint16_t* rows = nullptr;

@@ -426,15 +426,15 @@ AttnDQUmmaKernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   if (one_walk && live) {   // (under the first loads' flight)
     const size_t at = (static_cast<size_t>(b) * a.S + row) * (static_cast<size_t>(a.H) * D) + static_cast<size_t>(h) * D;
     const float4* orow = reinterpret_cast<const float4*>(a.fwd_keep + at);
-    const float4* drow = reinterpret_cast<const float4*>(a.dout_f32 + at);
-    auto as_bf16 = [](float x) { return __uint_as_float(Bf16Bits(x) << 16); };   // dO as the products below see it
+    const uint2* drow = reinterpret_cast<const uint2*>(a.dout_bf16 + at);   // four bf16 per load
 #pragma unroll 4
     for (int c = 0; c < D / 4; ++c) {
-      const float4 o = orow[c], g = drow[c];
-      delta = fmaf(o.x, as_bf16(g.x), delta);
-      delta = fmaf(o.y, as_bf16(g.y), delta);
-      delta = fmaf(o.z, as_bf16(g.z), delta);
-      delta = fmaf(o.w, as_bf16(g.w), delta);
+      const float4 o = orow[c];
+      const uint2 g = drow[c];
+      delta = fmaf(o.x, __uint_as_float(g.x << 16), delta);
+      delta = fmaf(o.y, __uint_as_float(g.x & 0xFFFF0000u), delta);
+      delta = fmaf(o.z, __uint_as_float(g.y << 16), delta);
+      delta = fmaf(o.w, __uint_as_float(g.y & 0xFFFF0000u), delta);
     }
   }
 

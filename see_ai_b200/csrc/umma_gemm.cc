@@ -553,13 +553,13 @@ std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands&
     a.keep = nullptr;
   }
   if (dq) {
-    if (op.fwd_keep && (reinterpret_cast<uintptr_t>(op.dout) & 15) == 0) {
+    if (op.fwd_keep) {
       a.fwd_keep = op.fwd_keep;
-      a.dout_f32 = op.dout;
+      a.dout_bf16 = ent[DO]->rows;
     }
     e = k::AttnDQUmma(mr[Q], mr[DO], mh[K], mh[V], a, stream);
     a.fwd_keep = nullptr;
-    a.dout_f32 = nullptr;
+    a.dout_bf16 = nullptr;
   }
   const bool both = dk && op.out2 != nullptr && op.d == 64 &&
                     (reinterpret_cast<uintptr_t>(op.out2) & 15) == 0;
@@ -587,6 +587,17 @@ uint16_t* ReservePack(Context* ctx, uint64_t elems) {
   victim->valid = false;
   victim->last_use = ++impl->tick;
   return victim->rows;
+}
+
+bool TouchPack(Context* ctx, uint64_t src_off, uint64_t elems) {
+  Impl* impl = ctx->impl;
+  if (!impl) return false;
+  for (auto& e : impl->packs)
+    if (e.valid && e.src_off == src_off && e.elems == elems) {
+      e.last_use = ++impl->tick;
+      return true;
+    }
+  return false;
 }
 
 void CommitPack(Context* ctx, uint16_t* rows, uint64_t src_off, uint64_t elems) {

@@ -103,6 +103,8 @@ struct AttentionOperands {
 // extents have gone through InvalidateRange; TryAttention then finds it and packs nothing.
 uint16_t* ReservePack(Context* ctx, uint64_t elems);
 void CommitPack(Context* ctx, uint16_t* rows, uint64_t src_off, uint64_t elems);
+// True when a valid copy of the tensor at `src_off` exists; marks it most recently used.
+bool TouchPack(Context* ctx, uint64_t src_off, uint64_t elems);
 std::string TryAttention(Context* ctx, uint16_t opcode, const AttentionOperands& op,
                          cudaStream_t stream, int* launches, bool* did_second = nullptr);
 
