@@ -415,6 +415,7 @@ void CudaBackend::BeginRange(std::span<const Instruction> program, size_t begin,
   // CUDA graph must contain every conversion it depends on.
   umma::InvalidateRange(&umma_->ctx, 0, arena_bytes_);
   range_index_ = 0;
+  lora_rows_tag_.valid = false;
   PlanAdamGroups(program, begin, std::min(end, program.size()));
   PlanAttentionKeeps(program, begin, std::min(end, program.size()));
   auto plan_fusions = [&] {
@@ -527,6 +528,7 @@ void CudaBackend::EndRange() {
   elided_.clear();
   pending_elided_.clear();
   deferred_elided_.clear();
+  lora_rows_tag_.valid = false;
   pack_plan_.clear();
   pending_pack_ = PendingPack{};
   shadow_plan_.clear();
@@ -1658,6 +1660,9 @@ Status CudaBackend::Execute(const Instruction& ins, const StepParams& params) {
   for (size_t i = 0; i < ext.count && !absorbed; ++i) {
     const Extent& e = ext.e[i];
     if (!e.write) continue;
+    if (lora_rows_tag_.valid && lora_rows_tag_.producer + 1 != range_index_ && e.space == kArena &&
+        e.off < lora_rows_tag_.off + lora_rows_tag_.M * lora_rows_tag_.r * 4 && lora_rows_tag_.off < e.off + e.bytes)
+      lora_rows_tag_.valid = false;
     if (!add_done) umma::InvalidateRange(&umma_->ctx, e.off, e.bytes);
     if (coherence_ == Coherence::kStrict) MergeExtent(&device_dirty_, e.off, e.bytes);
     if (!elided_.empty() && e.space == kArena) {   // written for real: no longer stale
@@ -1766,6 +1771,11 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
         ++counters_.kernel_launches;
         umma::InvalidateRange(&umma_->ctx, RefOffset(lf->down.in[2]), d.M * d.N * 4);
       }
+      if (!pieces_made && lf->kind != 1 && lora_rows_tag_.valid && lora_rows_tag_.off == RefOffset(lf->t_ref) &&
+          lora_rows_tag_.M == a.M && lora_rows_tag_.r == lf->r)
+        pieces_made = true;   // the adapter backward left dT's cut in the scratch
+      else
+        lora_rows_tag_.valid = false;   // the scratch is rewritten below (or was, by the down product)
       if (!pieces_made) {
         if (!k::LoraSplitRows(Rd(lf->t_ref), d_lora_t_, a.M, lf->r, stream_))
           return std::unexpected("cuda: low-rank fold: the factor cannot be split (rank or alignment)");
@@ -1856,8 +1866,14 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
     b.partials_floats = lora_partials_capacity_;
     b.M = ins.out[0]; b.r = ins.out[1]; b.N = ins.out[2]; b.K = ab.da.out[0];
     b.alpha_dt = GemmAlphaOf(ins.imm); b.alpha_db = GemmAlphaOf(ab.db.imm); b.alpha_da = GemmAlphaOf(ab.da.imm);
+    // dT's bf16 cut in the same pass, for the fold that takes dT A^T a few instructions on.
+    const bool cut = lora_fold_enabled_ && d_lora_t_ != nullptr &&
+                     b.M * k::LoraSplitColumns(static_cast<uint32_t>(b.r)) <= lora_t_capacity_;
+    if (cut) b.dt_pieces = d_lora_t_;
+    lora_rows_tag_.valid = false;
     if (!k::LoraBackward(b, stream_))
       return std::unexpected("cuda: the fused adapter backward refused a site it was planned on");
+    if (cut) lora_rows_tag_ = LoraRowsTag{true, RefOffset(ins.in[2]), b.M, static_cast<uint32_t>(b.r), range_index_};
     counters_.kernel_launches += 3;
     counters_.fused_dispatches += 2;
     umma::InvalidateRange(&umma_->ctx, RefOffset(ab.db.in[2]), b.r * b.N * 4);

@@ -369,6 +369,10 @@ class CudaBackend {
   // at the given range index (the last one the dispatch stood for) has passed.
   struct DeferredElision { size_t after; uint64_t lo, hi; };
   std::vector<DeferredElision> deferred_elided_;
+  // What the shared row-operand scratch of the low-rank folds (d_lora_t_) holds: the bf16 cut of the
+  // [M, r] tensor at `off`, written by the instruction at range index `producer`; any other
+  // instruction that writes into that tensor, or reuses the scratch, ends it.
+  struct LoraRowsTag { bool valid = false; uint64_t off = 0, M = 0; uint32_t r = 0; size_t producer = 0; } lora_rows_tag_;
   std::vector<PackPlan> pack_plan_;
   struct PendingPack {
     uint16_t* rows = nullptr;

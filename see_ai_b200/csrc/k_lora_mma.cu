@@ -280,7 +280,7 @@ template <int N, int K, int R>
 __global__ void __launch_bounds__(kThreads, 1)
 LoraBackwardKernel(const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ t,
                    const float* __restrict__ B, float* __restrict__ dt, float* __restrict__ partials, size_t M,
-                   float alpha_dt) {
+                   float alpha_dt, uint16_t* __restrict__ pieces, uint32_t piece_cols) {
   using S = BackSmem<N, K, R>;
   extern __shared__ __align__(16) float smem[];
   float* dy_s = smem;
@@ -327,6 +327,27 @@ LoraBackwardKernel(const float* __restrict__ dy, const float* __restrict__ x, co
       if (row0 + r < M)
         *reinterpret_cast<float4*>(dt + (row0 + r) * R + 4 * c) =
             *reinterpret_cast<const float4*>(dt_s + r * S::kSmallStride + 4 * c);
+    }
+    if (pieces != nullptr) {   // dT's three-way bf16 cut, for the product that takes dT A^T into its reduction
+      for (int idx = threadIdx.x; idx < kTileRows * R / 2; idx += kThreads) {   // two columns per thread
+        const int r = idx / (R / 2), j = 2 * (idx - r * (R / 2));
+        if (row0 + r >= M) continue;
+        uint16_t p0[3], p1[3];
+        Split3(dt_s[r * S::kSmallStride + j], p0);
+        Split3(dt_s[r * S::kSmallStride + j + 1], p1);
+        uint16_t* dst = pieces + (row0 + r) * piece_cols + j;
+#pragma unroll
+        for (int sg = 0; sg < 6; ++sg) {
+          const int pc = PieceOf(0, sg);
+          *reinterpret_cast<uint32_t*>(dst + sg * R) =
+              static_cast<uint32_t>(p0[pc]) | (static_cast<uint32_t>(p1[pc]) << 16);
+        }
+      }
+      const int pad_pairs = (static_cast<int>(piece_cols) - 6 * R) / 2;   // the padding columns [6 R, piece_cols)
+      for (int idx = threadIdx.x; idx < kTileRows * pad_pairs; idx += kThreads) {
+        const int r = idx / pad_pairs, c = idx - r * pad_pairs;
+        if (row0 + r < M) *reinterpret_cast<uint32_t*>(pieces + (row0 + r) * piece_cols + 6 * R + 2 * c) = 0u;
+      }
     }
     // dB += t^T dY over the tile's 16 rows: A(i, k) = t[k][i], B(k, n) = dY[k][n].
 #pragma unroll
@@ -399,26 +420,41 @@ LoraBackwardKernel(const float* __restrict__ dy, const float* __restrict__ x, co
   }
 }
 
-// dB[i] = alpha_db * (partials[0][i] + partials[1][i] + ...) for i < n_db, dA likewise
-// from the part after it: blocks in order, eight loads in flight per thread.
+// dB[i] = alpha_db * sum over blocks of partials[b][i] for i < n_db, dA likewise from the part
+// after it.  Four lanes share an output: lane q adds its quarter of the blocks in block
+// order (eight loads in flight), then the four sums are added in lane order — a fixed
+// order, so the result is the same from run to run.
 __global__ void FoldPartialsKernel(const float* __restrict__ partials, size_t stride, int blocks, size_t n_db,
                                    size_t n_da, float alpha_db, float alpha_da, float* __restrict__ dB,
                                    float* __restrict__ dA) {
-  const size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
-  if (i >= n_db + n_da) return;
-  const float* p = partials + i;
+  const size_t tid = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  const size_t i = tid >> 2;
+  const int q = static_cast<int>(tid & 3);
+  const bool live = i < n_db + n_da;
+  const int per = (blocks + 3) / 4;
+  const int b0 = q * per, b1 = b0 + per < blocks ? b0 + per : blocks;
   float s = 0.0f;
-  int b = 0;
-  for (; b + 8 <= blocks; b += 8) {
-    float v[8];
+  if (live) {
+    const float* p = partials + i;
+    int b = b0;
+    for (; b + 8 <= b1; b += 8) {
+      float v[8];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) v[u] = __ldg(p + static_cast<size_t>(b + u) * stride);
+      for (int u = 0; u < 8; ++u) v[u] = __ldg(p + static_cast<size_t>(b + u) * stride);
 #pragma unroll
-    for (int u = 0; u < 8; ++u) s += v[u];
+      for (int u = 0; u < 8; ++u) s += v[u];
+    }
+    for (; b < b1; ++b) s += __ldg(p + static_cast<size_t>(b) * stride);
   }
-  for (; b < blocks; ++b) s += __ldg(p + static_cast<size_t>(b) * stride);
-  if (i < n_db) dB[i] = alpha_db * s;
-  else dA[i - n_db] = alpha_da * s;
+  // (lanes 4k .. 4k+3 hold one output's four sums)
+  const float s1 = __shfl_down_sync(0xFFFFFFFFu, s, 1);
+  const float s2 = __shfl_down_sync(0xFFFFFFFFu, s, 2);
+  const float s3 = __shfl_down_sync(0xFFFFFFFFu, s, 3);
+  if (live && q == 0) {
+    const float total = ((s + s1) + s2) + s3;
+    if (i < n_db) dB[i] = alpha_db * total;
+    else dA[i - n_db] = alpha_da * total;
+  }
 }
 
 template <typename Kernel>
@@ -472,8 +508,9 @@ bool LaunchBackward(const LoraBackwardArgs& a, cudaStream_t s) {
   const int blocks = static_cast<int>(tiles < static_cast<size_t>(SmCount()) ? tiles : SmCount());
   const size_t stride = static_cast<size_t>(R) * N + static_cast<size_t>(K) * R;
   if (static_cast<size_t>(blocks) * stride > a.partials_floats) return false;
-  LoraBackwardKernel<N, K, R><<<blocks, kThreads, smem, s>>>(a.dy, a.x, a.t, a.B, a.dt, a.partials, a.M, a.alpha_dt);
-  FoldPartialsKernel<<<static_cast<unsigned>((stride + 127) / 128), 128, 0, s>>>(
+  LoraBackwardKernel<N, K, R><<<blocks, kThreads, smem, s>>>(a.dy, a.x, a.t, a.B, a.dt, a.partials, a.M, a.alpha_dt,
+                                                             a.dt_pieces, LoraSplitColumns(static_cast<uint32_t>(R)));
+  FoldPartialsKernel<<<static_cast<unsigned>((4 * stride + 255) / 256), 256, 0, s>>>(
       a.partials, stride, blocks, static_cast<size_t>(R) * N, static_cast<size_t>(K) * R, a.alpha_db, a.alpha_da, a.dB,
       a.dA);
   return true;
@@ -508,7 +545,7 @@ bool LoraBackwardSupported(size_t M, size_t N, size_t K, size_t r) {
 bool LoraBackward(const LoraBackwardArgs& a, cudaStream_t s) {
   if (!LoraBackwardSupported(a.M, a.N, a.K, a.r)) return false;
   if (!Aligned16(a.dy) || !Aligned16(a.x) || !Aligned16(a.t) || !Aligned16(a.B) || !Aligned16(a.dt) ||
-      !Aligned16(a.partials))
+      !Aligned16(a.partials) || !Aligned16(a.dt_pieces))
     return false;
   if (a.N == 768 && a.r == 16) return LaunchBackward<768, 768, 16>(a, s);
   if (a.N == 768 && a.r == 8) return LaunchBackward<768, 768, 8>(a, s);

@@ -244,6 +244,7 @@ struct LoraBackwardArgs {
   size_t partials_floats = 0;
   size_t M = 0, N = 0, K = 0, r = 0;
   float alpha_dt = 1.0f, alpha_db = 1.0f, alpha_da = 1.0f;
+  uint16_t* dt_pieces = nullptr;   // optional: what LoraSplitRows would make of dt ([M, LoraSplitColumns(r)] bf16)
 };
 bool LoraBackwardSupported(size_t M, size_t N, size_t K, size_t r);
 size_t LoraBackwardPartialFloats(size_t N, size_t K, size_t r);
