@@ -42,10 +42,11 @@ sys.path.insert(0, ROOT)
 from see_ai_b200 import plan as P  # noqa: E402
 from see_ai_b200 import workloads as W  # noqa: E402
 
-NCU_TRAFFIC_BYTES = 109.0e6
-NCU_TRAFFIC_NOTE = ("ncu, one 32768x768x768 launch with its low-rank blocks (the most frequent shape of the step's "
-                    "tensor-core GEMM launches): 60.7 MB read + 48.3 MB written; algorithmic 160 MB (A bf16 50 MB, "
-                    "low-rank operand 8 MB, W 1 MB, C f32 101 MB), part of C is still in L2 when the kernel ends")
+NCU_TRAFFIC_BYTES = 71.5e6
+NCU_TRAFFIC_NOTE = ("ncu, one 32768x768x768 launch with its low-rank blocks and the bf16 operand copy of its result as "
+                    "the only store (the most frequent form of the step's tensor-core GEMM launches): 60.2 MB read + "
+                    "11.3 MB written; algorithmic 109 MB (A bf16 50 MB, low-rank operand 8 MB, W 1 MB, bf16 result "
+                    "50 MB), most of the result is still in L2 when the kernel ends")
 METRIC = "update_step_tokens_per_s"
 
 
