@@ -159,20 +159,28 @@ constexpr int kDownThreads = 512;
 constexpr int kDownWarps = kDownThreads / 32;
 constexpr int kDownAhead = 4;   // 16-wide k blocks in flight per lane and row
 
+//
+// With fewer tiles than warps on the device (a data-parallel rank's share of the rows) the
+// reduction axis is cut instead: `ksplit` warps (a power of two) share a tile, each over its
+// own run of k blocks, and the tile's first warp adds their sums in warp order through
+// shared memory — a fixed order, so a given row count always gives the same bits.
 template <int K, int R>
 struct DownSmem {
   static constexpr int kStride = K + 16;   // rows 16 banks apart: a quarter warp's two rows cover all 32
-  static constexpr size_t kFloats = 2 * static_cast<size_t>(R) * kStride;
+  static constexpr size_t kWeightFloats = 2 * static_cast<size_t>(R) * kStride;
+  static constexpr int kLaneFloats = R / 8 * 4;   // one lane's share of a tile's sums
+  static constexpr size_t kFloats = kWeightFloats + static_cast<size_t>(kDownThreads) * kLaneFloats;
 };
 
-template <int K, int R>
+template <int K, int R, bool kSplitK>
 __global__ void __launch_bounds__(kDownThreads, 1)
 LoraDownKernel(const float* __restrict__ x, const float* __restrict__ A, float* __restrict__ out,
-               uint16_t* __restrict__ pieces, uint32_t piece_cols, size_t M, float alpha) {
+               uint16_t* __restrict__ pieces, uint32_t piece_cols, size_t M, float alpha, int ksplit) {
   using S = DownSmem<K, R>;
   extern __shared__ __align__(16) float smem[];
   uint32_t* a_hi = reinterpret_cast<uint32_t*>(smem);
   uint32_t* a_lo = a_hi + static_cast<size_t>(R) * S::kStride;
+  float* part = smem + S::kWeightFloats;   // [warp][lane][kLaneFloats]
   for (int idx = threadIdx.x; idx < K * R; idx += kDownThreads) {   // A [K][R] -> a[n][k], k fastest (bank-free stores)
     const int n = idx / K, k = idx - n * K;
     SplitTf32(__ldg(A + k * R + n), &a_hi[n * S::kStride + k], &a_lo[n * S::kStride + k]);
@@ -181,11 +189,22 @@ LoraDownKernel(const float* __restrict__ x, const float* __restrict__ A, float* 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   constexpr int kBlocks = K / 16;
   const size_t tiles = (M + kTileRows - 1) / kTileRows;
-  // Tile order: warp w of block b takes tiles w * gridDim.x + b, + gridDim.x * kDownWarps, ...
-  for (size_t tile = static_cast<size_t>(warp) * gridDim.x + blockIdx.x; tile < tiles;
-       tile += static_cast<size_t>(gridDim.x) * kDownWarps) {
+  // Tile order: group w (a warp, or `ksplit` warps) of block b takes tiles w * gridDim.x + b,
+  // + gridDim.x * groups, ...  Every warp makes the same number of trips (the shared-memory
+  // hand-over below has block-wide barriers); a trip past the last tile computes nothing.
+  const int groups = kSplitK ? kDownWarps / ksplit : kDownWarps;
+  const int group = kSplitK ? warp / ksplit : warp;
+  const int member = kSplitK ? warp - group * ksplit : 0;
+  const int kb0 = kSplitK ? member * (kBlocks / ksplit) : 0;
+  const int kb1 = kSplitK ? kb0 + kBlocks / ksplit : kBlocks;
+  const size_t stride = static_cast<size_t>(gridDim.x) * groups;
+  const size_t trips = kSplitK ? (tiles + stride - 1) / stride : 0;
+  size_t trip = 0;
+  for (size_t tile = static_cast<size_t>(group) * gridDim.x + blockIdx.x; kSplitK ? trip < trips : tile < tiles;
+       tile += stride, ++trip) {
+    const bool live = tile < tiles;
     const size_t row_a = tile * kTileRows + g, row_b = row_a + 8;
-    const bool in_a = row_a < M, in_b = row_b < M;
+    const bool in_a = live && row_a < M, in_b = live && row_b < M;
     const float* xa = x + (in_a ? row_a : 0) * K + 4 * t;
     const float* xb = x + (in_b ? row_b : 0) * K + 4 * t;
     float c[R / 8][3][4];
@@ -196,16 +215,18 @@ LoraDownKernel(const float* __restrict__ x, const float* __restrict__ A, float* 
     float4 va[kDownAhead], vb[kDownAhead];
 #pragma unroll
     for (int p = 0; p < kDownAhead; ++p) {
-      va[p] = __ldg(reinterpret_cast<const float4*>(xa + 16 * p));
-      vb[p] = __ldg(reinterpret_cast<const float4*>(xb + 16 * p));
+      if (kSplitK && (!live || kb0 + p >= kb1)) continue;
+      va[p] = __ldg(reinterpret_cast<const float4*>(xa + 16 * (kb0 + p)));
+      vb[p] = __ldg(reinterpret_cast<const float4*>(xb + 16 * (kb0 + p)));
     }
 #pragma unroll 1
-    for (int s0 = 0; s0 < kBlocks; s0 += kDownAhead) {
+    for (int s0 = kb0; s0 < (kSplitK && !live ? kb0 : kb1); s0 += kDownAhead) {
 #pragma unroll
       for (int p = 0; p < kDownAhead; ++p) {
         const int s = s0 + p;
+        if (kSplitK && s >= kb1) break;
         const float4 ua = va[p], ub = vb[p];
-        if (s + kDownAhead < kBlocks) {
+        if (s + kDownAhead < kb1) {
           va[p] = __ldg(reinterpret_cast<const float4*>(xa + 16 * (s + kDownAhead)));
           vb[p] = __ldg(reinterpret_cast<const float4*>(xb + 16 * (s + kDownAhead)));
         }
@@ -233,6 +254,32 @@ LoraDownKernel(const float* __restrict__ x, const float* __restrict__ A, float* 
       }
     }
     // This lane holds rows g and g + 8, columns 8 j + 2 t and + 1.
+    if (kSplitK) {
+      float* mine = part + (static_cast<size_t>(warp) * 32 + lane) * S::kLaneFloats;
+      if (member != 0) {
+#pragma unroll
+        for (int j = 0; j < R / 8; ++j)
+          *reinterpret_cast<float4*>(mine + 4 * j) =
+              make_float4((c[j][0][0] + c[j][1][0]) + c[j][2][0], (c[j][0][1] + c[j][1][1]) + c[j][2][1],
+                          (c[j][0][2] + c[j][1][2]) + c[j][2][2], (c[j][0][3] + c[j][1][3]) + c[j][2][3]);
+      }
+      __syncthreads();
+      if (member == 0) {
+#pragma unroll
+        for (int j = 0; j < R / 8; ++j) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) c[j][0][e] = (c[j][0][e] + c[j][1][e]) + c[j][2][e];
+          for (int w = 1; w < ksplit; ++w) {
+            const float4 o = *reinterpret_cast<const float4*>(mine + static_cast<size_t>(w) * 32 * S::kLaneFloats + 4 * j);
+            c[j][0][0] += o.x; c[j][0][1] += o.y; c[j][0][2] += o.z; c[j][0][3] += o.w;
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) c[j][1][e] = c[j][2][e] = 0.0f;
+        }
+      }
+      __syncthreads();
+      if (member != 0) continue;
+    }
 #pragma unroll
     for (int j = 0; j < R / 8; ++j) {
       float v[4];
@@ -491,11 +538,20 @@ bool LaunchDown(const float* x, const float* A, float* out, uint16_t* pieces, ui
                 float alpha, cudaStream_t s) {
   static std::atomic<bool> configured[64] = {};
   const size_t smem = DownSmem<K, R>::kFloats * sizeof(float);
-  if (!Configure(LoraDownKernel<K, R>, smem, configured)) return false;
+  static std::atomic<bool> configured_split[64] = {};
+  if (!Configure(LoraDownKernel<K, R, false>, smem, configured)) return false;
+  if (!Configure(LoraDownKernel<K, R, true>, smem, configured_split)) return false;
   // One block per SM as soon as there is a tile per SM: the tiles go round the blocks first.
   const size_t tiles = (M + kTileRows - 1) / kTileRows;
-  const unsigned grid = static_cast<unsigned>(tiles < static_cast<size_t>(SmCount()) ? tiles : SmCount());
-  LoraDownKernel<K, R><<<grid, kDownThreads, smem, s>>>(x, A, out, pieces, piece_cols, M, alpha);
+  const size_t sms = static_cast<size_t>(SmCount());
+  const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
+  // Warps per tile: the largest power of two that still leaves every tile a group of warps.
+  int ksplit = 1;
+  while (ksplit < kDownWarps && (K / 16) % (2 * ksplit) == 0 && tiles * (2 * ksplit) <= sms * kDownWarps) ksplit *= 2;
+  if (ksplit > 1)
+    LoraDownKernel<K, R, true><<<grid, kDownThreads, smem, s>>>(x, A, out, pieces, piece_cols, M, alpha, ksplit);
+  else
+    LoraDownKernel<K, R, false><<<grid, kDownThreads, smem, s>>>(x, A, out, pieces, piece_cols, M, alpha, 1);
   return true;
 }
 

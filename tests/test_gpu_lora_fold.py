@@ -251,15 +251,17 @@ def test_adapter_products_with_contracted_multiply_adds():
     assert differs, "the contracted kernels gave the exact kernels' bits: did they run?"
 
 
-@pytest.mark.parametrize("shape", [(4096, 768, 16), (4100, 768, 8), (1000, 256, 8)],
-                         ids=["4096x768r16", "4100x768r8-ragged", "1000x256r8"])
+@pytest.mark.parametrize("shape", [(4096, 768, 16), (4100, 768, 8), (1000, 256, 8), (8200, 768, 16), (16400, 768, 16)],
+                         ids=["4096x768r16", "4100x768r8-ragged", "1000x256r8", "8200x768r16-four-warps-a-tile",
+                              "16400x768r16-two-warps-a-tile"])
 def test_one_pass_adapter_backward_and_tensor_core_down_product(shape):
     """In lazy coherence the down product t = x A runs as 3xTF32 on the tensor cores,
     and the three backward products of a site — dT = a dY B^T, dB = a t^T dY,
     dA = x^T dT, three instructions that each stream an activation — run as one
     pass over dY and x.  Held to 2e-6 of 1 + sum|a_k b_k| against float64 (the
     reference's bound for its own GEMMs); identical run to run; the strict seam
-    keeps the exact kernels' bits."""
+    keeps the exact kernels' bits.  The row counts cover the down product's forms for a
+    data-parallel rank's share of the rows (16, 8, 4 and 2 warps sharing a 16-row tile)."""
     M, D, r = shape
     rng = np.random.default_rng(M + r)
     a = Arena(rng)
