@@ -119,6 +119,13 @@ int see_cuda_set_split_gemm(see_cuda_backend* h, int mode);
  * weight tile).  Default on; 0 = one CTA per 128 x 256 tile.  Results are identical either way (the same
  * products in the same order).  Process-wide, not per handle. */
 int see_cuda_set_cta_pairs(int enabled);
+/* In lazy coherence an adapter site's three backward products (dT = a dY B^T, dB = a t^T dY,
+ * dA = x^T dT) run as 3xTF32 on the tcgen05 tensor cores where the site's shape allows (rank 16,
+ * widths multiples of 128).  Default on; 0 = the legacy tensor instruction's kernel for every site.
+ * Both hold the reference's bound for its own GEMMs (2e-6 of 1 + sum|a_k b_k|,
+ * test/runtime/executor/kernels_test.cc:1803-1822); their bits differ.  Process-wide, not per handle.
+ * No counterpart in the reference. */
+int see_cuda_set_adapter_tensor_backward(int enabled);
 /* Data parallelism: optimizer steps read gradients inside [block_offset,
  * block_offset + block_bytes) as the rank-ordered sum of `ranks` gathered
  * copies (device memory, copy r at gathered + r * block_bytes) times 1/ranks. */

@@ -32,7 +32,7 @@ EXPORTED_SYMBOLS = [
     "see_cuda_set_gradient_gather",
     "see_cuda_set_profiling", "see_cuda_take_profile",
     "see_cuda_xent_forward_static", "see_cuda_static_max_rows", "see_cuda_static_last_error",
-    "see_cuda_quantize_columns", "see_cuda_set_lora_fold", "see_cuda_set_adapter_fma", "see_cuda_set_split_gemm", "see_cuda_set_cta_pairs", "see_cuda_set_attention_one_walk",
+    "see_cuda_quantize_columns", "see_cuda_set_lora_fold", "see_cuda_set_adapter_fma", "see_cuda_set_split_gemm", "see_cuda_set_cta_pairs", "see_cuda_set_adapter_tensor_backward", "see_cuda_set_attention_one_walk",
 ]
 
 
@@ -108,6 +108,7 @@ def load_library() -> ctypes.CDLL:
     lib.see_cuda_set_adapter_fma.argtypes = [vp, i32]
     lib.see_cuda_set_split_gemm.argtypes = [vp, i32]
     lib.see_cuda_set_cta_pairs.argtypes = [i32]
+    lib.see_cuda_set_adapter_tensor_backward.argtypes = [i32]
     lib.see_cuda_set_attention_one_walk.argtypes = [vp, i32]
     lib.see_cuda_xent_forward_static.argtypes = [vp, vp, vp, vp, u64, u64, i32, vp]
     lib.see_cuda_static_max_rows.restype = u64
@@ -263,6 +264,10 @@ class CudaBackend:
     def set_cta_pairs(self, enabled: bool):
         """Process-wide: large tensor-core products on CTA pairs (default) or one CTA per tile."""
         self._check(self.lib.see_cuda_set_cta_pairs(int(enabled)))
+
+    def set_adapter_tensor_backward(self, enabled: bool):
+        """Process-wide: adapter backward sites on the tcgen05 tensor cores (default) or the legacy instruction."""
+        self._check(self.lib.see_cuda_set_adapter_tensor_backward(int(enabled)))
 
     def set_gradient_gather(self, ranks: int, gathered_ptr: int, block_offset: int,
                             block_bytes: int):

@@ -37,6 +37,7 @@ CU_SOURCES = {
     "k_lora.cu": [],
     "k_gemm_skinny_fast.cu": [],
     "k_lora_mma.cu": [],
+    "k_lora_umma.cu": [],
 }
 CC_SOURCES = ["extents.cc", "cuda_backend.cc", "c_api.cc", "umma_gemm.cc", "engine.cc", "exchange.cc"]
 

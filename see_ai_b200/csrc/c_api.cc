@@ -9,6 +9,7 @@
 
 #include "cuda_backend.h"
 #include "engine.h"
+#include "lora_umma.h"
 #include "umma_kernel.h"
 
 struct see_cuda_backend {
@@ -137,6 +138,11 @@ int see_cuda_set_split_gemm(see_cuda_backend* h, int mode) {
 
 int see_cuda_set_cta_pairs(int enabled) {
   see::k::UmmaSetCtaPairs(enabled != 0);
+  return SEE_OK;
+}
+
+int see_cuda_set_adapter_tensor_backward(int enabled) {
+  see::k::LoraBackwardUmmaSet(enabled != 0);
   return SEE_OK;
 }
 

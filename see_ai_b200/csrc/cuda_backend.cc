@@ -1871,7 +1871,10 @@ Status CudaBackend::DispatchGemm(const Instruction& ins) {
                      b.M * k::LoraSplitColumns(static_cast<uint32_t>(b.r)) <= lora_t_capacity_;
     if (cut) b.dt_pieces = d_lora_t_;
     lora_rows_tag_.valid = false;
-    if (!k::LoraBackward(b, stream_))
+    int tensor_launches = 0;
+    if (const std::string err = umma::TryLoraBackward(&umma_->ctx, b, stream_, &tensor_launches); !err.empty())
+      return std::unexpected("cuda: " + err);
+    if (tensor_launches == 0 && !k::LoraBackward(b, stream_))
       return std::unexpected("cuda: the fused adapter backward refused a site it was planned on");
     if (cut) lora_rows_tag_ = LoraRowsTag{true, RefOffset(ins.in[2]), b.M, static_cast<uint32_t>(b.r), range_index_};
     counters_.kernel_launches += 3;

@@ -34,6 +34,7 @@
 
 #include "kernels.h"
 #include "lora_split.cuh"
+#include "lora_umma.h"
 
 namespace see::k {
 
@@ -592,6 +593,12 @@ bool LoraDown(const float* x, const float* A, float* out, size_t M, size_t K, si
   if (K == 768 && r == 16) return LaunchDown<768, 16>(x, A, out, pieces, cols, M, alpha, s);
   if (K == 768 && r == 8) return LaunchDown<768, 8>(x, A, out, pieces, cols, M, alpha, s);
   return LaunchDown<256, 8>(x, A, out, pieces, cols, M, alpha, s);
+}
+
+void LoraFoldPartials(const LoraBackwardArgs& a, int blocks, cudaStream_t s) {
+  const size_t stride = a.r * a.N + a.K * a.r;
+  FoldPartialsKernel<<<static_cast<unsigned>((4 * stride + 255) / 256), 256, 0, s>>>(
+      a.partials, stride, blocks, a.r * a.N, a.K * a.r, a.alpha_db, a.alpha_da, a.dB, a.dA);
 }
 
 bool LoraBackwardSupported(size_t M, size_t N, size_t K, size_t r) {

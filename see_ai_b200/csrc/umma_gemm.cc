@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "attn_umma.h"
+#include "lora_umma.h"
 #include "umma_kernel.h"
 
 namespace see::umma {
@@ -208,6 +209,42 @@ static bool EncodeBf16Map(Impl* impl, CUtensorMap* map, const void* base, uint64
                       strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool EncodeF32Map(Impl* impl, CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                         uint32_t box_rows) {
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 4};
+  const cuuint32_t box[2] = {128, box_rows};   // plain row-major in shared memory: the kernel re-tiles it itself
+  const cuuint32_t elem[2] = {1, 1};
+  return impl->encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, elem,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+std::string TryLoraBackward(Context* ctx, const k::LoraBackwardArgs& a, cudaStream_t stream, int* launches) {
+  *launches = 0;
+  Impl* impl = ctx->impl;
+  if (!impl || !k::LoraBackwardUmmaEnabled() || !k::LoraBackwardUmmaSupported(a.M, a.N, a.K, a.r)) return {};
+  auto misaligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+  if (misaligned(a.dy) || misaligned(a.x) || misaligned(a.t) || misaligned(a.B) || misaligned(a.dt) ||
+      misaligned(a.partials) || misaligned(a.dt_pieces))
+    return {};
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) return {};
+  const int blocks = k::LoraBackwardUmmaBlocks(a.M, sms);
+  if (static_cast<size_t>(blocks) * (a.r * a.N + a.K * a.r) > a.partials_floats) return {};
+  CUtensorMap map_dy, map_x, map_b;
+  if (!EncodeF32Map(impl, &map_dy, a.dy, a.M, a.N, 64) || !EncodeF32Map(impl, &map_x, a.x, a.M, a.K, 64) ||
+      !EncodeF32Map(impl, &map_b, a.B, a.r, a.N, 16))
+    return "tensor-core adapter backward: cuTensorMapEncodeTiled refused an operand layout";
+  if (k::LoraBackwardUmmaLaunch(map_dy, map_x, map_b, a, blocks, impl->status, stream) != cudaSuccess)
+    return "tensor-core adapter backward: launch failed";
+  k::LoraFoldPartials(a, blocks, stream);
+  *launches = 2;
+  return {};
 }
 
 std::string TryGemm(Context* ctx, const k::GemmArgs& a, int b_space, uint64_t b_off,

@@ -41,6 +41,11 @@ void PlanRange(Context* ctx, const Instruction* program, size_t begin, size_t en
 std::string TryGemm(Context* ctx, const k::GemmArgs& args, int b_space, uint64_t b_off,
                     uint64_t a_off, uint64_t a_scale_off, cudaStream_t stream, int* launches);
 
+// An adapter site's three backward products (k::LoraBackwardArgs) as 3xTF32 on the tcgen05
+// tensor cores, one pass over dY and x, when the shape is inside that kernel's domain.
+// *launches == 0 with an empty return value: not applicable, use k::LoraBackward.
+std::string TryLoraBackward(Context* ctx, const k::LoraBackwardArgs& args, cudaStream_t stream, int* launches);
+
 // An EXACT f32 product on the tensor cores: both operands cut into three bf16
 // pieces, the six largest piece products summed over a K axis six times as long
 // (k::SplitMatrix), f32 accumulation in tensor memory.  The result is the f32

@@ -314,3 +314,60 @@ def test_one_pass_adapter_backward_and_tensor_core_down_product(shape):
     want_part = _f32(arena0, acc, M * D).reshape(M, D) + DT @ Am.T
     got_part = _f32(fast1, part, M * D).reshape(M, D)
     assert np.abs(got_part - want_part).max() < 1e-4
+
+
+def test_adapter_backward_on_tcgen05_and_on_the_legacy_instruction_agree():
+    """A site of rank 16 with widths that are multiples of 128 takes its three backward
+    products on the tcgen05 tensor cores (bf16 pieces: two of the streamed operands, three
+    of the small ones); the process-wide switch sends it to the legacy tensor
+    instruction's 3xTF32 kernel instead.  Both are held to 2e-6 of 1 + sum|a_k b_k|
+    against float64, agree with each other to that, are each identical run to run, and
+    differ in bits (which shows that the switch chose between them).  8200 rows: a ragged
+    last tile for both."""
+    M, D, r = 8200, 768, 16
+    rng = np.random.default_rng(4242)
+    a = Arena(rng)
+    x = a.alloc(M * D, "normal"); dy = a.alloc(M * D, "normal")
+    A = a.alloc(D * r, "normal", scale=0.05); Bm = a.alloc(r * D, "normal", scale=0.05)
+    t = a.alloc(M * r); dt = a.alloc(M * r); gB = a.alloc(r * D); gA = a.alloc(D * r)
+    s = 2.0
+    prog = [
+        P.Instr(Op.GEMM_NN, 0, 0, (x, A, t, P.NULL_REF), (M, r, D)),
+        P.Instr(Op.GEMM_NT, 0, P.f32_bits(s), (dy, Bm, dt, P.NULL_REF), (M, r, D)),
+        P.Instr(Op.GEMM_TN, 0, P.f32_bits(s), (t, dy, gB, P.NULL_REF), (r, D, M)),
+        P.Instr(Op.GEMM_TN, 0, 0, (x, dt, gA, P.NULL_REF), (D, r, M)),
+    ]
+    arena0, ro = a.build()
+
+    def run(tensor_backward):
+        arena = arena0.copy()
+        be = B.CudaBackend(0)
+        be.set_adapter_tensor_backward(tensor_backward)
+        try:
+            be.set_coherence(B.COHERENCE_LAZY)
+            be.bind(arena, ro)
+            be.run(prog)
+            be.host_needs(0, arena.size)
+            be.flush()
+        finally:
+            be.set_adapter_tensor_backward(True)
+            be.close()
+        return arena
+
+    new1, new2, old1, old2 = run(True), run(True), run(False), run(False)
+    assert np.array_equal(new1, new2) and np.array_equal(old1, old2)
+    X = _f32(arena0, x, M * D).reshape(M, D); DY = _f32(arena0, dy, M * D).reshape(M, D)
+    Bmm = _f32(arena0, Bm, r * D).reshape(r, D)
+    differs = False
+    for got in (new1, old1):
+        T = _f32(got, t, M * r).reshape(M, r); DT = _f32(got, dt, M * r).reshape(M, r)
+        cases = [
+            ("dT", DT, s * (DY @ Bmm.T), s * (np.abs(DY) @ np.abs(Bmm.T))),
+            ("dB", _f32(got, gB, r * D).reshape(r, D), s * (T.T @ DY), s * (np.abs(T.T) @ np.abs(DY))),
+            ("dA", _f32(got, gA, D * r).reshape(D, r), X.T @ DT, np.abs(X.T) @ np.abs(DT)),
+        ]
+        worst = {name: float((np.abs(g - want) / (1.0 + mag)).max()) for name, g, want, mag in cases}
+        assert max(worst.values()) < 2e-6, worst
+    for off, n in ((dt, M * r), (gB, r * D), (gA, D * r)):
+        differs = differs or not np.array_equal(new1[off:off + 4 * n], old1[off:off + 4 * n])
+    assert differs, "the switch made no difference: did both kernels run?"
