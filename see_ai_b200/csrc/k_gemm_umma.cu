@@ -105,6 +105,56 @@ __device__ __forceinline__ void EpilogueStore(const UmmaEpilogue& ep, size_t at,
   }
 }
 
+// EpilogueStore for the one form in which instruction count bounds the whole kernel: an absorbed GELU
+// gradient and nothing else (no addend, bias, activation or attention copy).  The same values, without
+// the per-element tests of the general form.
+__device__ __forceinline__ bool IsGeluGradOnly(const UmmaEpilogue& ep) {
+  return ep.fuse_mode == kFuseActBwd && ep.fuse_act == kActGelu && ep.addend == nullptr && ep.bias == nullptr &&
+         ep.act == kActNone && ep.pack_dst == nullptr;
+}
+__device__ __forceinline__ void EpilogueStoreGeluGrad(const UmmaEpilogue& ep, size_t at, const float4& acc,
+                                                      const float4& scale, const float4& kscale, const float4& x) {
+  const float4 v = make_float4(acc.x * scale.x, acc.y * scale.y, acc.z * scale.z, acc.w * scale.w);
+  if (ep.store_c) *reinterpret_cast<float4*>(ep.C + at) = v;
+  float4 g;
+  UnpackF2(GeluGrad2(PackF2(v.x, v.y), PackF2(x.x, x.y)), &g.x, &g.y);
+  UnpackF2(GeluGrad2(PackF2(v.z, v.w), PackF2(x.z, x.w)), &g.z, &g.w);
+  uint2 r;
+  r.x = ShadowBf16x2(g.x * kscale.x, g.y * kscale.y);
+  r.y = ShadowBf16x2(g.z * kscale.z, g.w * kscale.w);
+  reinterpret_cast<uint2*>(ep.shadow_dst)[at >> 2] = r;
+}
+
+// Likewise for an addend and nothing else (the accumulating gradient products): C = addend + acc * scale.
+__device__ __forceinline__ bool IsAddendOnly(const UmmaEpilogue& ep) {
+  return ep.addend != nullptr && ep.bias == nullptr && ep.act == kActNone && ep.pack_dst == nullptr &&
+         ep.fuse_mode == kFuseNone && ep.store_c;
+}
+__device__ __forceinline__ void EpilogueStoreAddend(const UmmaEpilogue& ep, size_t at, const float4& acc,
+                                                    const float4& scale, const float4& d) {
+  *reinterpret_cast<float4*>(ep.C + at) =
+      make_float4(d.x + acc.x * scale.x, d.y + acc.y * scale.y, d.z + acc.z * scale.z, d.w + acc.w * scale.w);
+}
+// ... and for a bias followed by an absorbed GELU (the feed-forward up product): C = acc * scale + bias,
+// the bf16 operand copy of gelu(C) beside it.
+__device__ __forceinline__ bool IsBiasGeluOnly(const UmmaEpilogue& ep) {
+  return ep.addend == nullptr && ep.bias != nullptr && ep.act == kActNone && ep.pack_dst == nullptr &&
+         ep.fuse_mode == kFuseActFwd && ep.fuse_act == kActGelu && ep.store_c;
+}
+__device__ __forceinline__ void EpilogueStoreBiasGelu(const UmmaEpilogue& ep, size_t at, const float4& acc,
+                                                      const float4& scale, const float4& bias, const float4& kscale) {
+  float4 v = make_float4(acc.x * scale.x, acc.y * scale.y, acc.z * scale.z, acc.w * scale.w);
+  v = make_float4(v.x + bias.x, v.y + bias.y, v.z + bias.z, v.w + bias.w);
+  *reinterpret_cast<float4*>(ep.C + at) = v;
+  float4 g;
+  UnpackF2(GeluExpr2(PackF2(v.x, v.y)), &g.x, &g.y);
+  UnpackF2(GeluExpr2(PackF2(v.z, v.w)), &g.z, &g.w);
+  uint2 r;
+  r.x = ShadowBf16x2(g.x * kscale.x, g.y * kscale.y);
+  r.y = ShadowBf16x2(g.z * kscale.z, g.w * kscale.w);
+  reinterpret_cast<uint2*>(ep.shadow_dst)[at >> 2] = r;
+}
+
 struct __align__(8) Barriers {
   uint64_t full[kStages];
   uint64_t empty[kStages];
@@ -513,6 +563,9 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t row0 = m0 + quarter * 32;
       const uint32_t rows = row0 < ep.M ? (ep.M - row0 < 32 ? ep.M - row0 : 32) : 0;
       [[maybe_unused]] const float* side_ptr = ep.fuse_mode == kFuseActBwd ? ep.fuse_x : ep.addend;
+      [[maybe_unused]] const bool gelu_grad_only = IsGeluGradOnly(ep);
+      [[maybe_unused]] const bool addend_only = IsAddendOnly(ep);
+      [[maybe_unused]] const bool bias_gelu_only = IsBiasGeluOnly(ep);
       [[maybe_unused]] float4 side_a[4], side_b[4];
       if constexpr (kSideLoads) {   // the first group's loads fly during the wait for the accumulator
         const uint32_t n_g = n0 + col_group * kColsPerEpiWarp + cl * 4;
@@ -572,7 +625,10 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
               const float4 acc = *reinterpret_cast<const float4*>(
                   slab + rr * kSlabCols + ((cl ^ (rr & (kChunks - 1))) * 4));
               const size_t at = static_cast<size_t>(row0 + rr) * ep.N + n;
-              EpilogueStore(ep, at, n, acc, scale, bias, true, kscale);
+              if (bias_gelu_only)
+                EpilogueStoreBiasGelu(ep, at, acc, scale, bias, kscale);
+              else
+                EpilogueStore(ep, at, n, acc, scale, bias, true, kscale);
             }
           }
           __syncwarp();   // the slab is rewritten next
@@ -629,7 +685,12 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
                 const float4 acc = *reinterpret_cast<const float4*>(
                     slab + rr * kSlabCols + ((cl ^ (rr & (kChunks - 1))) * 4));
                 const size_t at = static_cast<size_t>(row0 + rr) * ep.N + n;
-                EpilogueStore(ep, at, n, acc, scale, bias, true, kscale, true, sv[u]);
+                if (gelu_grad_only)
+                  EpilogueStoreGeluGrad(ep, at, acc, scale, kscale, sv[u]);
+                else if (addend_only)
+                  EpilogueStoreAddend(ep, at, acc, scale, sv[u]);
+                else
+                  EpilogueStore(ep, at, n, acc, scale, bias, true, kscale, true, sv[u]);
               }
             }
           };
