@@ -135,6 +135,18 @@ __device__ __forceinline__ void EpilogueStoreAddend(const UmmaEpilogue& ep, size
   *reinterpret_cast<float4*>(ep.C + at) =
       make_float4(d.x + acc.x * scale.x, d.y + acc.y * scale.y, d.z + acc.z * scale.z, d.w + acc.w * scale.w);
 }
+// ... for a product that leaves only as the bf16 copy a tiled attention instruction reads (Q, K, V) ...
+__device__ __forceinline__ bool IsCopyOnly(const UmmaEpilogue& ep) {
+  return ep.addend == nullptr && ep.bias == nullptr && ep.act == kActNone && ep.pack_dst != nullptr &&
+         ep.fuse_mode == kFuseNone && !ep.store_c;
+}
+__device__ __forceinline__ void EpilogueStoreCopy(const UmmaEpilogue& ep, size_t at, const float4& acc,
+                                                  const float4& scale) {
+  uint32_t lo, hi;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(acc.y * scale.y), "f"(acc.x * scale.x));
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(acc.w * scale.w), "f"(acc.z * scale.z));
+  *reinterpret_cast<uint2*>(ep.pack_dst + at) = make_uint2(lo, hi);
+}
 // ... and for a bias followed by an absorbed GELU (the feed-forward up product): C = acc * scale + bias,
 // the bf16 operand copy of gelu(C) beside it.
 __device__ __forceinline__ bool IsBiasGeluOnly(const UmmaEpilogue& ep) {
@@ -566,6 +578,7 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
       [[maybe_unused]] const bool gelu_grad_only = IsGeluGradOnly(ep);
       [[maybe_unused]] const bool addend_only = IsAddendOnly(ep);
       [[maybe_unused]] const bool bias_gelu_only = IsBiasGeluOnly(ep);
+      [[maybe_unused]] const bool copy_only = IsCopyOnly(ep);
       [[maybe_unused]] float4 side_a[4], side_b[4];
       if constexpr (kSideLoads) {   // the first group's loads fly during the wait for the accumulator
         const uint32_t n_g = n0 + col_group * kColsPerEpiWarp + cl * 4;
@@ -625,7 +638,9 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
               const float4 acc = *reinterpret_cast<const float4*>(
                   slab + rr * kSlabCols + ((cl ^ (rr & (kChunks - 1))) * 4));
               const size_t at = static_cast<size_t>(row0 + rr) * ep.N + n;
-              if (bias_gelu_only)
+              if (copy_only)
+                EpilogueStoreCopy(ep, at, acc, scale);
+              else if (bias_gelu_only)
                 EpilogueStoreBiasGelu(ep, at, acc, scale, bias, kscale);
               else
                 EpilogueStore(ep, at, n, acc, scale, bias, true, kscale);
