@@ -147,6 +147,16 @@ __device__ __forceinline__ void EpilogueStoreCopy(const UmmaEpilogue& ep, size_t
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(acc.w * scale.w), "f"(acc.z * scale.z));
   *reinterpret_cast<uint2*>(ep.pack_dst + at) = make_uint2(lo, hi);
 }
+// ... for a product stored as it is (the vocabulary head, the gradient products that carry nothing else) ...
+__device__ __forceinline__ bool IsPlainStore(const UmmaEpilogue& ep) {
+  return ep.addend == nullptr && ep.bias == nullptr && ep.act == kActNone && ep.pack_dst == nullptr &&
+         ep.fuse_mode == kFuseNone && ep.store_c;
+}
+__device__ __forceinline__ void EpilogueStorePlain(const UmmaEpilogue& ep, size_t at, const float4& acc,
+                                                   const float4& scale) {
+  *reinterpret_cast<float4*>(ep.C + at) =
+      make_float4(acc.x * scale.x, acc.y * scale.y, acc.z * scale.z, acc.w * scale.w);
+}
 // ... and for a bias followed by an absorbed GELU (the feed-forward up product): C = acc * scale + bias,
 // the bf16 operand copy of gelu(C) beside it.
 __device__ __forceinline__ bool IsBiasGeluOnly(const UmmaEpilogue& ep) {
@@ -579,6 +589,7 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
       [[maybe_unused]] const bool addend_only = IsAddendOnly(ep);
       [[maybe_unused]] const bool bias_gelu_only = IsBiasGeluOnly(ep);
       [[maybe_unused]] const bool copy_only = IsCopyOnly(ep);
+      [[maybe_unused]] const bool plain_store = IsPlainStore(ep);
       [[maybe_unused]] float4 side_a[4], side_b[4];
       if constexpr (kSideLoads) {   // the first group's loads fly during the wait for the accumulator
         const uint32_t n_g = n0 + col_group * kColsPerEpiWarp + cl * 4;
@@ -638,7 +649,9 @@ UmmaGemmPersistentKernel(const __grid_constant__ CUtensorMap map_a,
               const float4 acc = *reinterpret_cast<const float4*>(
                   slab + rr * kSlabCols + ((cl ^ (rr & (kChunks - 1))) * 4));
               const size_t at = static_cast<size_t>(row0 + rr) * ep.N + n;
-              if (copy_only)
+              if (plain_store)
+                EpilogueStorePlain(ep, at, acc, scale);
+              else if (copy_only)
                 EpilogueStoreCopy(ep, at, acc, scale);
               else if (bias_gelu_only)
                 EpilogueStoreBiasGelu(ep, at, acc, scale, bias, kscale);
